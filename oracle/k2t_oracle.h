@@ -1,0 +1,137 @@
+/*
+ * k2t_oracle.h — CPU restatement of the kronos-2t quantized decode path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This library is the checker the CUDA backend is
+ * compared against (and the timed CPU baseline of the benchmark).  Nothing in
+ * the product path links, imports or calls it.
+ *
+ * Parity status: PARITY UNPINNED.  The reference is a Rust crate and no Rust
+ * toolchain exists in the build environment, and the reference ships no golden
+ * vectors for this path (its own tests compare two implementations with each
+ * other).  The oracle is therefore pinned only by (a) the structural constants
+ * the reference publishes (codebooks, E8Q2 templates, SplitMix64 constants,
+ * record sizes, published model byte counts) and (b) the reference's own
+ * cross-implementation equalities, all of which tests/ re-checks.
+ *
+ * Where the reference's aarch64 (NEON) and portable fallbacks differ, the
+ * NEON arithmetic is followed: exact int32 dot per 64-column chunk, then
+ * f = fmaf((float)dot * sx, w_scale, f) in ascending chunk order.
+ *
+ * Every function names the reference source it restates
+ * (path within the reference project : line).
+ */
+#ifndef K2T_ORACLE_H
+#define K2T_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- src/kernels/hadamard.rs ------------------------------------------- */
+/* rademacher_sign_masks_64 (hadamard.rs:29-44): 0 or 0x80000000 per element. */
+void k2o_rademacher_masks(uint64_t block_idx, uint32_t out[64]);
+/* fwht64_signed_inplace_scalar (hadamard.rs:71-99). block0 = index of data[0]'s block. */
+void k2o_fwht64(float *data, size_t n, uint64_t block0);
+/* ifwht64_signed_inplace_scalar (hadamard.rs:200-228). */
+void k2o_ifwht64(float *data, size_t n, uint64_t block0);
+
+/* ---- src/kernels/simd_lut.rs:1375-1388 --------------------------------- */
+uint16_t k2o_f32_to_bf16(float v);
+float    k2o_bf16_to_f32(uint16_t b);
+
+/* ---- Int8ChunkActivation (simd_lut.rs:2921-3256) ----------------------- */
+/* populate_scalar (3235-3255): no rotation. */
+void k2o_act_populate(const float *x, size_t cols, int8_t *q, float *scales, int32_t *sums);
+/* populate_fwht / populate_rmsnorm_fwht via populate_chunk_fwht_scalar (3133-3196).
+ * norm_w may be NULL (then inv_rms is ignored). chunk0 = global chunk index of x[0]. */
+void k2o_act_populate_fwht(const float *x, size_t cols, const float *norm_w, float inv_rms,
+                           uint64_t chunk0, int8_t *q, float *scales, int32_t *sums);
+
+/* dot_f32_neon_16 (src/model/real_llm.rs:931-963): 16 fma lanes, NEON combine order. */
+float k2o_dot_f32(const float *a, const float *b, size_t n);
+/* rms_norm's inv_rms (real_llm.rs:9858-9860). */
+float k2o_inv_rms(const float *x, size_t n, float eps);
+
+/* ---- bipolar bit-plane matrices ---------------------------------------- */
+size_t k2o_bipolar_data_bytes(size_t rows, size_t cols, size_t planes);
+size_t k2o_bipolar_scale_count(size_t rows, size_t cols);
+/* compile_hadamard_gptq_bipolar with hessian=None (src/model/compiler.rs:912-1107)
+ * followed by FusedBipolarLutMatrix::pack_interleaved (simd_lut.rs:1772-1794). */
+void k2o_bipolar_quantize_rtn(const float *weights, size_t rows, size_t cols, size_t planes,
+                              size_t threads, uint8_t *interleaved, uint16_t *bf16_scales);
+/* pack_interleaved alone, from row-major codes u[rows*cols]. */
+void k2o_bipolar_pack(const uint8_t *u_grid, size_t rows, size_t cols, size_t planes, uint8_t *interleaved);
+/* unpack_row_codes (1804-1820) / dequantize_row_rotated (1823-1835). */
+void k2o_bipolar_unpack_row(const uint8_t *interleaved, size_t rows, size_t cols, size_t planes,
+                            size_t r, uint8_t *codes);
+void k2o_bipolar_dequant_row(const uint8_t *interleaved, const uint16_t *bf16_scales, size_t rows,
+                             size_t cols, size_t planes, size_t r, float *out);
+
+/* Nibble4SdotMatrix::from_bipolar_with_perm (simd_lut.rs:3297-3400). */
+size_t k2o_nibble4_pair_bytes(size_t rows, size_t cols, size_t planes);
+size_t k2o_nibble4_tail_bytes(size_t rows, size_t cols, size_t planes);
+void k2o_nibble4_from_bipolar(const uint8_t *interleaved, const uint16_t *bf16_scales, size_t rows,
+                              size_t cols, size_t planes, int interleave_gate_up,
+                              uint8_t *pair_stream, uint8_t *tail_stream);
+/* Nibble4SdotMatrix::dequantize_row_rotated (3441-3481). */
+void k2o_nibble4_dequant_row(const uint8_t *pair_stream, const uint8_t *tail_stream, size_t rows,
+                             size_t cols, size_t planes, size_t r, float *out);
+/* sdot_one_stripe_neon (3763-3868) in scalar form over the Nibble4 records.
+ * n_tok tokens share the weights (sdot_batch_tile_neon, 4228-4331: same per-(row,token) order).
+ * xq[n_tok][cols], xs/xsum[n_tok][nc]; out[t*out_stride + r].
+ * int_dots (optional) receives dot = 2a - max_odd*sum per [t][row][chunk]. threads>=1. */
+void k2o_nibble4_gemv(const uint8_t *pair_stream, const uint8_t *tail_stream, size_t rows, size_t cols,
+                      size_t planes, const int8_t *xq, const float *xs, const int32_t *xsum,
+                      size_t n_tok, float *out, size_t out_stride, int32_t *int_dots, size_t threads);
+/* Definition-level GEMV straight from the file format (codes via unpack_row_codes):
+ * used to cross-check the Nibble4 path. Single token. */
+void k2o_bipolar_gemv_def(const uint8_t *interleaved, const uint16_t *bf16_scales, size_t rows,
+                          size_t cols, size_t planes, const int8_t *xq, const float *xs,
+                          const int32_t *xsum, float *out, int32_t *int_dots);
+
+/* ---- NF5/NF4/NF3/E8Q2 codebook matrices -------------------------------- */
+extern const int8_t K2O_NF5_DEFAULT_POS[16];   /* simd_lut.rs:4338-4340 */
+extern const int8_t K2O_NF4_DEFAULT[16];       /* 4343-4345 */
+extern const int8_t K2O_NF3_DEFAULT[16];       /* 4348-4350 */
+extern const int8_t K2O_E8Q2_EVEN_TEMPLATES[28][4]; /* 4354-4383 */
+/* nf_expand_codebook32 (4636-4647). */
+void k2o_nf_expand_codebook32(size_t bits, const int8_t codebook[16], int8_t out[32]);
+/* e8q2_decode_8d (4436-4459). */
+void k2o_e8q2_decode_8d(uint8_t tpl, uint8_t sgn, int8_t out[8]);
+/* stripe_chunk_bytes / pair_total_bytes / tail_total_bytes (4818-4841). */
+size_t k2o_nf_chunk_bytes(size_t bits);
+size_t k2o_nf_pair_stream_bytes(size_t rows, size_t cols, size_t bits, size_t sgc);
+size_t k2o_nf_tail_stream_bytes(size_t rows, size_t cols, size_t bits, size_t sgc);
+size_t k2o_nf_scale_count(size_t rows, size_t cols, size_t sgc);
+/* fit_empirical_nf_codebook (compiler.rs:1404-1528). returns mu_top. */
+float k2o_nf_fit_codebook(const float *weights, size_t rows, size_t cols, size_t bits, size_t sgc,
+                          int8_t codebook[16]);
+/* compile_hadamard_gptq_nf with hessian=None, bits 3..5 (compiler.rs:1530-1860):
+ * writes row-major indices and stripe-major bf16 scales [stripes][nsg][16]. */
+void k2o_nf_quantize_rtn(const float *weights, size_t rows, size_t cols, size_t bits, size_t sgc,
+                         size_t threads, int8_t codebook[16], uint8_t *flat_idx, uint16_t *bf16_scales);
+/* NfSdotMatrix::from_indices (simd_lut.rs:4850-5023). */
+void k2o_nf_pack(const uint8_t *flat_idx, const uint16_t *bf16_scales, size_t rows, size_t cols,
+                 size_t bits, size_t sgc, uint8_t *pair_stream, uint8_t *tail_stream);
+/* NfSdotMatrix::from_e8q2_codes (5118-5226): tpl/sgn are [rows][cols/8]. */
+void k2o_e8q2_pack(const uint8_t *tpl, const uint8_t *sgn, const uint16_t *bf16_scales, size_t rows,
+                   size_t cols, size_t sgc, uint8_t *pair_stream, uint8_t *tail_stream);
+/* to_gate_up_interleaved (5500-5524). */
+void k2o_nf_gate_up_interleave(const uint8_t *pair_stream, size_t rows, size_t cols, size_t bits,
+                               size_t sgc, uint8_t *out_pair_stream);
+/* dequantize_row_rotated (5560-5635). */
+void k2o_nf_dequant_row(const uint8_t *pair_stream, const uint8_t *tail_stream, const int8_t codebook[16],
+                        size_t rows, size_t cols, size_t bits, size_t sgc, size_t r, float *out);
+/* nf_sdot_one_stripe_neon (6071-6181) / nf_sdot_batch_tile_neon (6689-7029) in scalar form,
+ * index unpack as in the scalar pair-stream kernel (6459-6539). Same calling shape as k2o_nibble4_gemv. */
+void k2o_nf_gemv(const uint8_t *pair_stream, const uint8_t *tail_stream, const int8_t codebook[16],
+                 size_t rows, size_t cols, size_t bits, size_t sgc, const int8_t *xq, const float *xs,
+                 size_t n_tok, float *out, size_t out_stride, int32_t *int_dots, size_t threads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
