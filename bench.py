@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized GEMV hot path (BASELINE.json configs[1]: the standalone GEMV sweep).
+
+A step = one pass over the sweep at batch 1: for every K x N shape (2048x2048, 2048x8192, 8192x2048,
+2048x49152) and every format (b4, b5, b6, nf4g128): rotate+quantize an fp32 activation vector
+(FWHT-64 + int8) and run the GEMV.  One pass streams ~343 MB of distinct weights, more than the
+126 MB L2, so every launch reads its weights from HBM.
+
+  value     GB/s of algorithmic bytes (reference file-format weight bytes + activations + outputs)
+            with inputs resident in HBM; whole-job aggregate over all ranks (each rank runs its own
+            independent sweep: weak scaling, no collective on the data path).
+  e2e       same metric through the host-buffer C-ABI call kronos_cuda_linear (pinned host vectors,
+            H2D + kernels + D2H inside the timed region).
+  roofline  GEMV kernels of the sweep timed one by one with CUDA events (aggregate and per case).
+  cpu_baseline  the CPU oracle (a C++ port of the reference CPU path) on one pass, all host threads.
+
+`--impl reference` times that CPU port alone (the reference is a Rust crate and cannot be built
+here; its GPU path is Apple Metal and unavailable on this box).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)]   # (K = cols, N = rows)
+FORMATS = ["b4", "b5", "b6", "nf4g128"]
+WORKLOAD = "gemv_sweep_batch1: K x N in 2048x2048, 2048x8192, 8192x2048, 2048x49152; b4, b5, b6, nf4g128"
+
+
+def fmt_spec(fmt):
+    if fmt.startswith("b"):
+        return ("bipolar", int(fmt[1]), 1)
+    return ("nf", int(fmt[2]), 2 if fmt.endswith("g128") else 1)
+
+
+def algorithmic_bytes(fmt, cols, rows, n_tok=1):
+    """weights in the reference file format + int8 activations with scale and sum + fp32 outputs."""
+    from kronos_2t_b200 import synth
+    kind, bits, sgc = fmt_spec(fmt)
+    return synth.file_bytes(kind, rows, cols, bits, sgc) + n_tok * (cols + 8 * (cols // 64)) + n_tok * 4 * rows
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_sweep_host(seed0):
+    """File-format bytes of the 16 sweep matrices (random codes; see kronos_2t_b200.synth)."""
+    from kronos_2t_b200 import synth
+    mats = []
+    for si, (cols, rows) in enumerate(SHAPES):
+        for fi, fmt in enumerate(FORMATS):
+            kind, bits, sgc = fmt_spec(fmt)
+            seed = seed0 + 16 * si + fi
+            if kind == "bipolar":
+                d0, d1 = synth.random_bipolar_bytes(seed, rows, cols, bits)
+            else:
+                d0, d1 = synth.random_nf_bytes(seed, rows, cols, bits, sgc)
+            mats.append(dict(fmt=fmt, kind=kind, bits=bits, sgc=sgc, rows=rows, cols=cols, d0=d0, d1=d1))
+    return mats
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle's stripe-parallel GEMV (C++ port of the reference CPU path), all host threads."""
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import oracle as o
+    threads = os.cpu_count() or 1
+    mats = build_sweep_host(1000)
+    rng = np.random.Generator(np.random.PCG64(7))
+    cases = []
+    for m in mats:
+        x = rng.standard_normal(m["cols"]).astype(np.float32)
+        if m["kind"] == "bipolar":
+            om = o.nibble4_from_bipolar(o.Bipolar(m["rows"], m["cols"], m["bits"], m["d0"], m["d1"]))
+        else:
+            om = o.Nf(m["rows"], m["cols"], m["bits"], m["sgc"], _default_cb(m["bits"]), m["d0"], m["d1"])
+        cases.append((m, om, x))
+    total_bytes = sum(algorithmic_bytes(m["fmt"], m["cols"], m["rows"]) for m in mats)
+
+    def one_pass():
+        for m, om, x in cases:
+            act = o.act_populate_fwht(x)
+            if m["kind"] == "bipolar":
+                o.nibble4_gemv(om, act, threads=threads)
+            else:
+                o.nf_gemv(om, act, threads=threads)
+
+    for _ in range(args.warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_pass()
+    dt = time.perf_counter() - t0
+    val = total_bytes * args.steps / dt / 1e9
+    sample = f"{args.steps} full passes of the 16-matrix sweep (stripe-parallel, {threads} threads)"
+    print(json.dumps({
+        "impl": "reference", "metric": "quantized_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4..6 -> int32, fp32 epilogue", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of weights per pass)"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def _default_cb(bits):
+    from kronos_2t_b200 import synth
+    return synth.NF4_DEFAULT if bits == 4 else synth.NF3_DEFAULT
+
+
+def run_b200(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import kronos_2t_b200 as k2
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    ctx = k2.Context(local_rank)
+    stream = torch.cuda.current_stream()
+    ctx.set_stream(stream.cuda_stream)
+
+    mats = build_sweep_host(1000 + 100 * rank)
+    cases = []
+    g = torch.Generator(device="cpu").manual_seed(7 + rank)
+    for m in mats:
+        if m["kind"] == "bipolar":
+            dm = ctx.upload_bipolar(m["rows"], m["cols"], m["bits"], m["d0"], m["d1"])
+        else:
+            dm = ctx.upload_nf(m["rows"], m["cols"], m["bits"], m["sgc"], _default_cb(m["bits"]), m["d0"], m["d1"])
+        cols, rows, nc = m["cols"], m["rows"], m["cols"] // 64
+        x_host = torch.randn(cols, generator=g, dtype=torch.float32).pin_memory()
+        case = dict(m=m, dm=dm, x_host=x_host, out_host=torch.empty(rows, dtype=torch.float32).pin_memory(),
+                    x=x_host.to(dev), q=torch.empty(cols, dtype=torch.int8, device=dev),
+                    s=torch.empty(nc, dtype=torch.float32, device=dev), sums=torch.empty(nc, dtype=torch.int32, device=dev),
+                    out=torch.empty(rows, dtype=torch.float32, device=dev),
+                    bytes=algorithmic_bytes(m["fmt"], cols, rows))
+        cases.append(case)
+    bytes_per_step = sum(c["bytes"] for c in cases)
+
+    def step():
+        for c in cases:
+            ctx.fwht_quant_dev(c["x"].data_ptr(), 1, c["m"]["cols"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr())
+            ctx.gemv_dev(c["dm"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr(), 1, c["out"].data_ptr())
+
+    def step_e2e():
+        for c in cases:
+            ctx.linear_ptr(c["dm"], c["x_host"].data_ptr(), 1, c["out_host"].data_ptr())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, sample_clocks=False):
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        barrier()
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if sampler else None
+        if dist:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    launches0 = ctx.launch_count
+    ms, clocks = timed(step, args.steps, sample_clocks=True)
+    gpu_launches = ctx.launch_count - launches0
+    value = bytes_per_step * world * args.steps / (ms / 1e3) / 1e9
+
+    for _ in range(3):
+        step_e2e()
+    ms_e2e, _ = timed(step_e2e, args.steps)
+    e2e_value = bytes_per_step * world * args.steps / (ms_e2e / 1e3) / 1e9
+    h2d = sum(c["m"]["cols"] * 4 for c in cases)
+    d2h = sum(c["m"]["rows"] * 4 for c in cases)
+
+    # roofline: every GEMV launch of the sweep timed on its own, in sweep order (weights cold in L2)
+    peak, peak_kind = peaks()
+    reps = 5
+    per = {i: [] for i in range(len(cases))}
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
+    for _ in range(reps):
+        for i, c in enumerate(cases):
+            ctx.fwht_quant_dev(c["x"].data_ptr(), 1, c["m"]["cols"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr())
+            evs[i][0].record(stream)
+            ctx.gemv_dev(c["dm"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr(), 1, c["out"].data_ptr())
+            evs[i][1].record(stream)
+        torch.cuda.synchronize()
+        for i in range(len(cases)):
+            per[i].append(evs[i][0].elapsed_time(evs[i][1]))
+    kernels = []
+    tot_b = tot_ms = 0.0
+    for i, c in enumerate(cases):
+        t = statistics.mean(per[i])
+        gbs = c["bytes"] / (t / 1e3) / 1e9
+        kernels.append({"case": f"{c['m']['fmt']} {c['m']['cols']}x{c['m']['rows']}", "us": round(t * 1e3, 2),
+                        "GBps": round(gbs, 1), "frac": round(gbs / peak, 3)})
+        tot_b += c["bytes"]; tot_ms += t
+    big = [k for k in kernels if k["case"].endswith("x49152")]
+    achieved = tot_b / (tot_ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gemv_kernel (all 16 launches of one sweep pass)", "achieved": achieved, "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "largest_launch_frac": max(k["frac"] for k in big), "per_launch": kernels}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(mats)
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "quantized_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x 4..6-bit codes -> int32, fp32 epilogue", "data": "synthetic (random codes)",
+            "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of distinct weights per step)",
+                       "per_rank": "each rank runs its own sweep (replicas, no collective)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(gpu_launches),
+            "roofline": roofline, "cpu_baseline": cpu,
+        }))
+    for c in cases:
+        c["dm"].free()
+    ctx.close()
+    if dist:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(mats):
+    """Oracle (C++ port of the reference CPU path) on one pass of the same sweep, all host threads."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import oracle as o
+    threads = os.cpu_count() or 1
+    rng = np.random.Generator(np.random.PCG64(7))
+    prepared = []
+    for m in mats:
+        x = rng.standard_normal(m["cols"]).astype(np.float32)
+        if m["kind"] == "bipolar":
+            om = o.nibble4_from_bipolar(o.Bipolar(m["rows"], m["cols"], m["bits"], m["d0"], m["d1"]))
+        else:
+            om = o.Nf(m["rows"], m["cols"], m["bits"], m["sgc"], _default_cb(m["bits"]), m["d0"], m["d1"])
+        prepared.append((m, om, x))
+    passes, t0 = 0, time.perf_counter()
+    while passes < 2 or (time.perf_counter() - t0 < 10.0 and passes < 50):
+        if passes == 1:
+            t0 = time.perf_counter()   # first pass is warm-up
+        for m, om, x in prepared:
+            act = o.act_populate_fwht(x)
+            (o.nibble4_gemv if m["kind"] == "bipolar" else o.nf_gemv)(om, act, threads=threads)
+        passes += 1
+    dt = time.perf_counter() - t0
+    total = sum(algorithmic_bytes(m["fmt"], m["cols"], m["rows"]) for m in mats) * (passes - 1)
+    return {"value": total / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{passes - 1} full passes of the 16-matrix sweep after one warm-up pass"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

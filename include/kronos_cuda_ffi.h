@@ -1,0 +1,134 @@
+/*
+ * kronos_cuda_ffi.h — C ABI of the B200 (sm_100a) backend for kronos-2t's quantized
+ * decode / prefill hot path.
+ *
+ * Conventions follow the reference's include/kronos_ffi.h:12-30 and
+ * src/ffi/mobile_ffi.rs:32-41,159-168: opaque handles, int32_t 0 / -1 returns,
+ * `*_last_error()` returns a NUL-terminated string that stays valid until the next
+ * mutating call on the same handle, NULL handles are tolerated, nothing unwinds
+ * across the boundary.  One caller at a time per handle (the reference's forward
+ * methods are `&mut self`).
+ *
+ * Matrices are passed in the byte formats the reference stores in .k2tb/.k2tm files;
+ * the backend copies them into HBM (repacked for coalesced streaming) and owns that
+ * memory.  Host buffers only need to live for the duration of the call.
+ *
+ * There is no CPU fallback: every entry point fails with an error when no CUDA
+ * device is usable.
+ */
+#ifndef KRONOS_CUDA_FFI_H
+#define KRONOS_CUDA_FFI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct KronosCudaContext KronosCudaContext;
+typedef struct KronosCudaMatrix KronosCudaMatrix;
+
+/* Matrix kinds use the tags of the .k2tb container (src/model/real_llm.rs:3805-3823,
+ * matrix tags in save_bipolar 3705-3895). */
+#define KRONOS_CUDA_MATRIX_BIPOLAR 0u /* FusedBipolarLutMatrix, src/kernels/simd_lut.rs:1754-1836 */
+#define KRONOS_CUDA_MATRIX_NF      2u /* NfSdotMatrix (bits 5,4,3; 2 = E8Q2), simd_lut.rs:4796-5226 */
+
+/* Upload flag: reorder gate_up rows from [gate; up] into 64-row [gate_64(ic), up_64(ic)] blocks,
+ * as Nibble4SdotMatrix::from_bipolar_with_perm (simd_lut.rs:3297-3327) and
+ * NfSdotMatrix::to_gate_up_interleaved (5500-5524) do for the CPU path. */
+#define KRONOS_CUDA_UPLOAD_GATE_UP_INTERLEAVE 1u
+
+/* A weight matrix exactly as the reference holds it after loading a .k2tb file.
+ * Replaces the `&LinearBackend` borrows of LayerBorrow (src/backend/metal_gpu.rs:428-439),
+ * extended to bipolar matrices.
+ *   BIPOLAR: bits = planes (4..6); data0 = interleaved planes
+ *            [stripes][cols/8][planes][16]; data1 = bf16 scales [stripes][cols/64][16] (bytes, LE).
+ *   NF:      bits = 5,4,3 or 2 (E8Q2); data0 = pair_stream; data1 = tail_stream (len1 may be 0);
+ *            codebook = the 16 stored int8 centroids; scale_group_chunks = 64-col chunks per scale. */
+typedef struct KronosCudaMatrixDesc {
+    uint32_t kind;
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t bits;
+    uint32_t scale_group_chunks;
+    int8_t codebook[16];
+    const uint8_t *data0;
+    size_t len0;
+    const uint8_t *data1;
+    size_t len1;
+} KronosCudaMatrixDesc;
+
+/* ---- context ------------------------------------------------------------------------------ */
+
+/* Opens CUDA device `device` and creates the stream all calls of this context are ordered on.
+ * Returns NULL when the device cannot be used (see kronos_cuda_last_error(NULL)).
+ * Counterpart of MetalLlamaEngine's device/queue acquisition in try_new (metal_gpu.rs:1196-1206). */
+KronosCudaContext *kronos_cuda_context_create(int32_t device);
+void kronos_cuda_context_destroy(KronosCudaContext *ctx);
+/* Last error of `ctx`, or of the last failed context_create when ctx is NULL. */
+const char *kronos_cuda_last_error(const KronosCudaContext *ctx);
+/* Blocks until everything queued on the context's stream has finished. */
+int32_t kronos_cuda_synchronize(KronosCudaContext *ctx);
+/* Number of kernels this context has launched so far (own kernels only). */
+uint64_t kronos_cuda_launch_count(const KronosCudaContext *ctx);
+/* Routes subsequent launches of this context onto an existing cudaStream_t (NULL = the context's
+ * own stream).  Lets a host harness time calls with events it records on its own stream. */
+int32_t kronos_cuda_set_stream(KronosCudaContext *ctx, void *cuda_stream);
+
+/* ---- matrices ----------------------------------------------------------------------------- */
+
+/* Copies a matrix to HBM in the backend's streaming layout.  Replaces the buffer wrapping of
+ * MetalLlamaEngine::try_new (metal_gpu.rs:1094-1172) and, for bipolar matrices,
+ * RealLlamaEngine::repack_sdot (real_llm.rs:3657-3702). */
+KronosCudaMatrix *kronos_cuda_matrix_upload(KronosCudaContext *ctx, const KronosCudaMatrixDesc *desc,
+                                            uint32_t flags);
+void kronos_cuda_matrix_free(KronosCudaContext *ctx, KronosCudaMatrix *m);
+/* Bytes the matrix occupies in the reference's file format (the "algorithmic" weight bytes)
+ * and in HBM. */
+size_t kronos_cuda_matrix_file_bytes(const KronosCudaMatrix *m);
+size_t kronos_cuda_matrix_device_bytes(const KronosCudaMatrix *m);
+
+/* Host-only diagnostic: writes the HBM image kronos_cuda_matrix_upload would copy (records, then
+ * bf16 scales) into `out` and returns its size in bytes; with out == NULL or cap too small nothing is
+ * written.  Needs no GPU.  Returns 0 for a malformed descriptor.  No counterpart in the reference. */
+size_t kronos_cuda_matrix_image(const KronosCudaMatrixDesc *desc, uint32_t flags, uint8_t *out, size_t cap);
+
+/* ---- kernels, host buffers (copies to and from the device happen inside the call) ---------- */
+
+/* Int8ChunkActivation::populate_fwht / populate_rmsnorm_fwht (simd_lut.rs:2954-2991):
+ * optional (x*inv_rms)*norm_w, signed FWHT-64 with global chunk index chunk0 + c, per-chunk int8.
+ * x[n_tok][cols]; norm_w[cols] or NULL; inv_rms[n_tok] or NULL (required with norm_w);
+ * q[n_tok][cols], scales[n_tok][cols/64], sums[n_tok][cols/64]. */
+int32_t kronos_cuda_fwht_quant(KronosCudaContext *ctx, const float *x, size_t n_tok, size_t cols,
+                               const float *norm_w, const float *inv_rms, uint64_t chunk0,
+                               int8_t *q, float *scales, int32_t *sums);
+
+/* nibble4_sdot_stripe_range_raw (simd_lut.rs:3536-3582) / nf_sdot_stripe_range_raw (5687-5760) for
+ * n_tok = 1 and the batch forms (4101-4331, 6689-7029) for n_tok <= 8, over all rows:
+ * out[t*out_stride + r] = sum over chunks of fmaf((float)dot*xs, w_scale, acc), ascending chunks,
+ * chunks with xs == 0 skipped.  int_dots (optional, [n_tok][rows][cols/64]) receives the exact
+ * int32 chunk dots (bipolar: 2*sum(u*q) - (2^B-1)*xsum; NF: sum(cb[idx]*q)). xsum may be NULL for NF. */
+int32_t kronos_cuda_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, const int8_t *xq,
+                         const float *xs, const int32_t *xsum, size_t n_tok, float *out,
+                         size_t out_stride, int32_t *int_dots);
+
+/* LinearBackend::forward for the Nibble4 / NfSdot arms (real_llm.rs:825-858) fed by
+ * Int8ChunkActivation::populate_fwht: y[t] = W * rotate_quantize(x[t]).  x[n_tok][cols] fp32 in,
+ * out[n_tok][rows] fp32.  This is the host-buffer call the benchmark's end-to-end number uses. */
+int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x,
+                           size_t n_tok, float *out);
+
+/* ---- kernels, device buffers (no copies; pointers are device addresses on ctx's device) ---- */
+
+int32_t kronos_cuda_fwht_quant_dev(KronosCudaContext *ctx, const float *d_x, size_t n_tok, size_t cols,
+                                   const float *d_norm_w, const float *d_inv_rms, uint64_t chunk0,
+                                   int8_t *d_q, float *d_scales, int32_t *d_sums);
+int32_t kronos_cuda_gemv_dev(KronosCudaContext *ctx, const KronosCudaMatrix *m, const int8_t *d_xq,
+                             const float *d_xs, const int32_t *d_xsum, size_t n_tok, float *d_out,
+                             size_t out_stride, int32_t *d_int_dots);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,63 @@
+// Small device helpers shared by the kernels (sm_100a).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace k2t {
+
+// dp4a with unsigned bytes in `a` (codes, possibly pre-scaled) and signed bytes in `b` (int8 activations).
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// dp4a with signed bytes on both sides (codebook centroids x int8 activations).
+__device__ __forceinline__ int dp4a_ss(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// (a & b) | c  and  a | (b & c) as single LOP3s
+__device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t b, uint32_t c) {  // a | (b & c)
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xF8;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// bytewise select: mask ? hi : lo
+__device__ __forceinline__ uint32_t lop3_select(uint32_t lo, uint32_t hi, uint32_t mask) {
+    uint32_t d;  // (lo & ~mask) | (hi & mask): truth table over (lo, hi, mask) = 0xCA with inputs (mask, hi, lo)
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(d) : "r"(mask), "r"(hi), "r"(lo));
+    return d;
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+// Streaming 128-bit load that does not allocate in L1 (weights are read exactly once).
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// Rademacher sign of element i (0..63) of 64-block `block`: the SplitMix64 stream of
+// rademacher_sign_masks_64 (src/kernels/hadamard.rs:29-44) evaluated at position i directly.
+__device__ __forceinline__ uint32_t rademacher_sign(uint64_t block, uint32_t i) {
+    const uint64_t G = 0x9E3779B97F4A7C15ull;
+    uint64_t z = G + block * 0xBF58476D1CE4E5B9ull + (uint64_t)(i + 1) * G;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (uint32_t)(z & 1ull) << 31;
+}
+
+}  // namespace k2t

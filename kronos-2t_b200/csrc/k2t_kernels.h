@@ -1,0 +1,32 @@
+// Host-callable launchers of the sm_100a kernels (implemented in the .cu files of this folder).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "k2t_layout.h"
+
+namespace k2t {
+
+// Device-resident matrix (image produced by repack_matrix, uploaded once).
+struct DeviceMatrix {
+    MatrixGeom geom;
+    uint8_t *d_base = nullptr;      // one allocation: records then scales
+    const uint8_t *d_rec = nullptr;
+    const uint16_t *d_scales = nullptr;
+    size_t device_bytes = 0;
+};
+
+cudaError_t launch_fwht_quant(cudaStream_t stream, const float *x, const float *norm_w, const float *inv_rms,
+                              uint32_t n_tok, uint32_t cols, uint64_t chunk0, int8_t *q, float *scales,
+                              int32_t *sums);
+
+// Quantized GEMV / small-N GEMM over all rows. n_tok in 1..8. Returns the number of kernel launches
+// in *launches. xsum may be null for NF formats.
+cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs,
+                        const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
+                        int sm_count, uint32_t *launches);
+
+// Largest n_tok one launch_gemv call accepts for this matrix (shared-memory bound), at most 8.
+uint32_t gemv_max_tokens(const DeviceMatrix &m);
+
+}  // namespace k2t

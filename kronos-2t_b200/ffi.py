@@ -1,0 +1,213 @@
+"""ctypes binding of include/kronos_cuda_ffi.h.
+
+Host-buffer methods take numpy arrays; `*_dev` methods take raw device addresses (for example
+`torch.Tensor.data_ptr()`), so a harness can keep inputs resident in HBM.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+MATRIX_BIPOLAR = 0
+MATRIX_NF = 2
+UPLOAD_GATE_UP_INTERLEAVE = 1
+
+
+class KronosCudaError(RuntimeError):
+    pass
+
+
+def lib_path():
+    return os.path.join(_HERE, "lib", "libkronos_cuda.so")
+
+
+class MatrixDesc(C.Structure):
+    _fields_ = [
+        ("kind", C.c_uint32), ("rows", C.c_uint32), ("cols", C.c_uint32), ("bits", C.c_uint32),
+        ("scale_group_chunks", C.c_uint32), ("codebook", C.c_int8 * 16),
+        ("data0", C.c_void_p), ("len0", C.c_size_t), ("data1", C.c_void_p), ("len1", C.c_size_t),
+    ]
+
+
+def load_library():
+    """Loads libkronos_cuda.so; raises if it has not been built (no fallback exists)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not os.path.exists(path):
+        raise KronosCudaError(f"{path} is missing: run `python kronos-2t_b200/build.py` (needs nvcc)")
+    L = C.CDLL(path)
+    vp, sz, i32, u32, u64 = C.c_void_p, C.c_size_t, C.c_int32, C.c_uint32, C.c_uint64
+
+    def sig(name, res, *args):
+        f = getattr(L, name)
+        f.restype, f.argtypes = res, list(args)
+
+    sig("kronos_cuda_context_create", vp, i32)
+    sig("kronos_cuda_context_destroy", None, vp)
+    sig("kronos_cuda_last_error", C.c_char_p, vp)
+    sig("kronos_cuda_synchronize", i32, vp)
+    sig("kronos_cuda_launch_count", u64, vp)
+    sig("kronos_cuda_set_stream", i32, vp, vp)
+    sig("kronos_cuda_matrix_upload", vp, vp, C.POINTER(MatrixDesc), u32)
+    sig("kronos_cuda_matrix_free", None, vp, vp)
+    sig("kronos_cuda_matrix_file_bytes", sz, vp)
+    sig("kronos_cuda_matrix_device_bytes", sz, vp)
+    sig("kronos_cuda_matrix_image", sz, C.POINTER(MatrixDesc), u32, vp, sz)
+    sig("kronos_cuda_fwht_quant", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
+    sig("kronos_cuda_gemv", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
+    sig("kronos_cuda_linear", i32, vp, vp, vp, sz, vp)
+    sig("kronos_cuda_fwht_quant_dev", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
+    sig("kronos_cuda_gemv_dev", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
+    _LIB = L
+    return L
+
+
+def bipolar_desc(rows, cols, planes, interleaved, bf16_scales):
+    d0, d1 = _np(interleaved, np.uint8), _np(bf16_scales, np.uint16)
+    desc = MatrixDesc(kind=MATRIX_BIPOLAR, rows=rows, cols=cols, bits=planes, scale_group_chunks=1,
+                      data0=d0.ctypes.data, len0=d0.nbytes, data1=d1.ctypes.data, len1=d1.nbytes)
+    desc._keep = (d0, d1)
+    return desc
+
+
+def nf_desc(rows, cols, bits, sgc, codebook, pair_stream, tail_stream):
+    d0, d1 = _np(pair_stream, np.uint8), _np(tail_stream, np.uint8)
+    desc = MatrixDesc(kind=MATRIX_NF, rows=rows, cols=cols, bits=bits, scale_group_chunks=sgc,
+                      data0=d0.ctypes.data if d0.size else None, len0=d0.nbytes,
+                      data1=d1.ctypes.data if d1.size else None, len1=d1.nbytes)
+    cb = _np(codebook, np.int8)
+    for i in range(16):
+        desc.codebook[i] = int(cb[i])
+    desc._keep = (d0, d1)
+    return desc
+
+
+def matrix_image(desc, gate_up_interleave=False):
+    """Host-only: the HBM image (records + scales) of a matrix, as a uint8 array."""
+    L = load_library()
+    flags = UPLOAD_GATE_UP_INTERLEAVE if gate_up_interleave else 0
+    n = L.kronos_cuda_matrix_image(C.byref(desc), flags, None, 0)
+    if n == 0:
+        raise KronosCudaError("malformed matrix descriptor")
+    out = np.zeros(n, np.uint8)
+    L.kronos_cuda_matrix_image(C.byref(desc), flags, out.ctypes.data_as(C.c_void_p), n)
+    return out
+
+
+def _np(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Matrix:
+    """A quantized matrix resident in HBM (KronosCudaMatrix)."""
+
+    def __init__(self, ctx, handle, rows, cols):
+        self.ctx, self.handle, self.rows, self.cols = ctx, handle, rows, cols
+
+    @property
+    def file_bytes(self):
+        return load_library().kronos_cuda_matrix_file_bytes(self.handle)
+
+    @property
+    def device_bytes(self):
+        return load_library().kronos_cuda_matrix_device_bytes(self.handle)
+
+    def free(self):
+        if self.handle:
+            load_library().kronos_cuda_matrix_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Context:
+    """One CUDA device + stream (KronosCudaContext)."""
+
+    def __init__(self, device=0):
+        self.L = load_library()
+        self.handle = self.L.kronos_cuda_context_create(device)
+        if not self.handle:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(None).decode())
+
+    def close(self):
+        if self.handle:
+            self.L.kronos_cuda_context_destroy(self.handle)
+            self.handle = None
+
+    def _check(self, rc):
+        if rc != 0:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(self.handle).decode())
+
+    def synchronize(self):
+        self._check(self.L.kronos_cuda_synchronize(self.handle))
+
+    @property
+    def launch_count(self):
+        return self.L.kronos_cuda_launch_count(self.handle)
+
+    def set_stream(self, cuda_stream):
+        self._check(self.L.kronos_cuda_set_stream(self.handle, cuda_stream))
+
+    # ---- matrices
+    def upload_bipolar(self, rows, cols, planes, interleaved, bf16_scales, gate_up_interleave=False):
+        return self._upload(bipolar_desc(rows, cols, planes, interleaved, bf16_scales), rows, cols, gate_up_interleave)
+
+    def upload_nf(self, rows, cols, bits, sgc, codebook, pair_stream, tail_stream, gate_up_interleave=False):
+        return self._upload(nf_desc(rows, cols, bits, sgc, codebook, pair_stream, tail_stream), rows, cols,
+                            gate_up_interleave)
+
+    def _upload(self, desc, rows, cols, interleave):
+        h = self.L.kronos_cuda_matrix_upload(self.handle, C.byref(desc), UPLOAD_GATE_UP_INTERLEAVE if interleave else 0)
+        if not h:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(self.handle).decode())
+        return Matrix(self, h, rows, cols)
+
+    # ---- host-buffer kernels
+    def fwht_quant(self, x, norm_w=None, inv_rms=None, chunk0=0):
+        x = _np(x, np.float32)
+        if x.ndim == 1:
+            x = x[None]
+        n, cols = x.shape
+        q = np.empty((n, cols), np.int8)
+        s = np.empty((n, cols // 64), np.float32)
+        m = np.empty((n, cols // 64), np.int32)
+        w = None if norm_w is None else _np(norm_w, np.float32)
+        inv = None if inv_rms is None else _np(np.broadcast_to(np.asarray(inv_rms, np.float32), (n,)), np.float32)
+        self._check(self.L.kronos_cuda_fwht_quant(self.handle, _p(x), n, cols, _p(w), _p(inv), chunk0, _p(q), _p(s), _p(m)))
+        return q, s, m
+
+    def gemv(self, mat, xq, xs, xsum=None, want_dots=False):
+        xq = _np(xq, np.int8).reshape(-1, mat.cols)
+        n, nc = xq.shape[0], mat.cols // 64
+        xs = _np(xs, np.float32).reshape(n, nc)
+        xm = None if xsum is None else _np(xsum, np.int32).reshape(n, nc)
+        out = np.empty((n, mat.rows), np.float32)
+        dots = np.empty((n, mat.rows, nc), np.int32) if want_dots else None
+        self._check(self.L.kronos_cuda_gemv(self.handle, mat.handle, _p(xq), _p(xs), _p(xm), n, _p(out), mat.rows, _p(dots)))
+        return (out, dots) if want_dots else out
+
+    def linear(self, mat, x):
+        x = _np(x, np.float32).reshape(-1, mat.cols)
+        out = np.empty((x.shape[0], mat.rows), np.float32)
+        self._check(self.L.kronos_cuda_linear(self.handle, mat.handle, _p(x), x.shape[0], _p(out)))
+        return out
+
+    def linear_ptr(self, mat, x_ptr, n_tok, out_ptr):
+        """kronos_cuda_linear on raw host addresses (e.g. pinned torch tensors)."""
+        self._check(self.L.kronos_cuda_linear(self.handle, mat.handle, x_ptr, n_tok, out_ptr))
+
+    # ---- device-buffer kernels
+    def fwht_quant_dev(self, d_x, n_tok, cols, d_q, d_scales, d_sums, d_norm_w=None, d_inv_rms=None, chunk0=0):
+        self._check(self.L.kronos_cuda_fwht_quant_dev(self.handle, d_x, n_tok, cols, d_norm_w, d_inv_rms, chunk0,
+                                                      d_q, d_scales, d_sums))
+
+    def gemv_dev(self, mat, d_xq, d_xs, d_xsum, n_tok, d_out, out_stride=None, d_dots=None):
+        self._check(self.L.kronos_cuda_gemv_dev(self.handle, mat.handle, d_xq, d_xs, d_xsum, n_tok, d_out,
+                                                out_stride or mat.rows, d_dots))

@@ -1,0 +1,186 @@
+"""CPU tests of the host-side repack (kronos_cuda_matrix_image) and of the kernels' decode logic.
+
+The decode step of the GEMV kernel (k2t_gemv.cu: decode<FMT>) is re-enacted here word for word
+in numpy, including the byte-permute selector tricks, and must reproduce the codes / centroids
+the oracle reads out of the reference file formats.  No GPU is needed.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import kronos_2t_b200 as k2
+from k2t_rng import normal
+
+U32 = np.uint32
+
+
+def prmt(a, b, sel):
+    """PTX prmt.b32 (generic mode): selector nibble = byte index 0..7 (+8: replicate the sign bit)."""
+    src = [(a >> (8 * i)) & 0xFF for i in range(4)] + [(b >> (8 * i)) & 0xFF for i in range(4)]
+    out = 0
+    for i in range(4):
+        nib = (sel >> (4 * i)) & 0xF
+        v = src[nib & 7]
+        if nib & 8:
+            v = 0xFF if v & 0x80 else 0
+        out |= v << (8 * i)
+    return out
+
+
+def _words(buf):
+    return [int(x) for x in np.frombuffer(bytes(buf), dtype="<u4")]
+
+
+def decode_record(fmt, rec, r, cb_words):
+    """Returns the 64 weight bytes (unsigned for bit-planes, signed for NF) of row r of a record."""
+    a = _words(rec[r * 16: r * 16 + 16])
+    u = [0] * 16
+    M = 0xFFFFFFFF
+    if fmt in ("bp4", "bp5", "bp6"):
+        b = _words(rec[128 + r * 16: 128 + r * 16 + 16])
+        for i in range(4):
+            u[2 * i], u[2 * i + 1] = a[i] & 0x0F0F0F0F, (a[i] >> 4) & 0x0F0F0F0F
+            u[8 + 2 * i], u[8 + 2 * i + 1] = b[i] & 0x0F0F0F0F, (b[i] >> 4) & 0x0F0F0F0F
+        if fmt == "bp5":
+            h = _words(rec[256 + r * 8: 256 + r * 8 + 8])
+            for j in range(8):
+                for half in range(2):
+                    hv = (h[half] << (4 - j)) & M if j <= 4 else h[half] >> (j - 4)
+                    u[8 * half + j] |= hv & 0x10101010
+        if fmt == "bp6":
+            h = _words(rec[256 + r * 16: 256 + r * 16 + 16])
+            for v in range(4):
+                u[4 * v + 0] |= ((h[v] << 4) & M) & 0x30303030
+                u[4 * v + 1] |= ((h[v] << 2) & M) & 0x30303030
+                u[4 * v + 2] |= h[v] & 0x30303030
+                u[4 * v + 3] |= (h[v] >> 2) & 0x30303030
+        dt = np.uint8
+    elif fmt == "nf4":
+        b = _words(rec[128 + r * 16: 128 + r * 16 + 16])
+        for i in range(8):
+            x = a[i] if i < 4 else b[i - 4]
+            lo3, hb = x & 0x77777777, x & 0x88888888
+            hs = (hb << 4) & M
+            m0, m1 = prmt(hs, hb, 0xD9C8), prmt(hs, hb, 0xFBEA)
+            r_lo, r_hi = prmt(cb_words[0], cb_words[1], lo3), prmt(cb_words[2], cb_words[3], lo3)
+            u[2 * i] = (r_lo & ~m0 & M) | (r_hi & m0)
+            r_lo, r_hi = prmt(cb_words[0], cb_words[1], lo3 >> 16), prmt(cb_words[2], cb_words[3], lo3 >> 16)
+            u[2 * i + 1] = (r_lo & ~m1 & M) | (r_hi & m1)
+        dt = np.int8
+    elif fmt == "nf3":
+        W = a + _words(rec[128 + r * 8: 128 + r * 8 + 8])
+        for i in range(6):
+            s = W[i] & 0x77777777
+            u[2 * i], u[2 * i + 1] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
+        for h in range(2):
+            s = (W[3 * h] >> 3) & 0x11111111
+            s |= (W[3 * h + 1] >> 2) & 0x22222222
+            s |= (W[3 * h + 2] >> 1) & 0x44444444
+            u[12 + 2 * h], u[13 + 2 * h] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
+        dt = np.int8
+    else:
+        raise ValueError(fmt)
+    return np.array(u, dtype="<u4").view(np.uint8).view(dt)
+
+
+REC_BYTES = {"bp4": 256, "bp5": 320, "bp6": 384, "nf4": 256, "nf3": 192}
+
+
+def image_rows(fmt, image, rows, cols, nsg, cb_words=None):
+    """Decodes a whole device image into weight bytes [rows, cols] and bf16 scales [rows, nsg]."""
+    nc, ng, rb = cols // 64, (rows + 7) // 8, REC_BYTES[fmt]
+    recs = image[: ng * nc * rb].reshape(ng, nc, rb)
+    scales = image[ng * nc * rb:].view("<u2").reshape(ng * 8, nsg)
+    out = np.zeros((ng * 8, cols), np.int16)
+    for g in range(ng):
+        for c in range(nc):
+            for r in range(8):
+                out[g * 8 + r, c * 64:(c + 1) * 64] = decode_record(fmt, recs[g, c], r, cb_words)
+    return out, scales
+
+
+@pytest.mark.parametrize("planes", [4, 5, 6])
+@pytest.mark.parametrize("rows", [54, 64])
+def test_bitplane_image_decodes_to_file_codes(oracle, planes, rows):
+    cols = 192
+    m = oracle.bipolar_quantize_rtn(normal(planes, (rows, cols), 0.02), planes, threads=2)
+    image = k2.matrix_image(k2.bipolar_desc(rows, cols, planes, m.data, m.scales))
+    assert image.size == ((rows + 7) // 8) * (cols // 64) * (REC_BYTES[f"bp{planes}"] + 16)
+    codes, scales = image_rows(f"bp{planes}", image, rows, cols, cols // 64)
+    sc_file = m.scales.reshape(-1, cols // 64, 16)
+    for r in range(rows):
+        assert np.array_equal(codes[r], oracle.bipolar_unpack_row(m, r))
+        assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
+    assert not codes[rows:].any() and not scales[rows:].any()   # padding rows
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+@pytest.mark.parametrize("rows,sgc", [(71, 1), (71, 2), (128, 2)])
+def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
+    cols = 192
+    m, idx, sc = oracle.nf_quantize_rtn(normal(40 + bits, (rows, cols), 0.02), bits, sgc, threads=2, return_indices=True)
+    # an asymmetric codebook exercises the general 16-entry lookup, not just the fitted symmetric one
+    cb = m.codebook.copy()
+    if bits == 4:
+        cb = np.array([-120, -90, -70, -50, -33, -20, -9, -1, 3, 14, 29, 47, 60, 80, 101, 127], np.int8)
+    cb_words = _words(cb.tobytes())
+    image = k2.matrix_image(k2.nf_desc(rows, cols, bits, sgc, cb, m.pair, m.tail))
+    nsg = -(-(cols // 64) // sgc)
+    vals, scales = image_rows(f"nf{bits}", image, rows, cols, nsg, cb_words)
+    assert np.array_equal(vals[:rows], cb.astype(np.int16)[idx])
+    sc_file = sc.reshape(-1, nsg, 16)
+    for r in range(rows):
+        assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
+    assert not scales[rows:].any()
+
+
+def test_gate_up_interleave_image(oracle):
+    rows, cols = 256, 128
+    m = oracle.bipolar_quantize_rtn(normal(3, (rows, cols), 0.02), 4)
+    desc = k2.bipolar_desc(rows, cols, 4, m.data, m.scales)
+    plain, _ = image_rows("bp4", k2.matrix_image(desc), rows, cols, 2)
+    inter, _ = image_rows("bp4", k2.matrix_image(desc, gate_up_interleave=True), rows, cols, 2)
+    half = rows // 2
+    for ic in range(half // 64):
+        assert np.array_equal(inter[ic * 128: ic * 128 + 64], plain[ic * 64: ic * 64 + 64])
+        assert np.array_equal(inter[ic * 128 + 64: ic * 128 + 128], plain[half + ic * 64: half + ic * 64 + 64])
+    n = oracle.nf_quantize_rtn(normal(4, (rows, cols), 0.02), 4, 2)
+    nd = k2.nf_desc(rows, cols, 4, 2, n.codebook, n.pair, n.tail)
+    cbw = _words(n.codebook.tobytes())
+    plain, _ = image_rows("nf4", k2.matrix_image(nd), rows, cols, 1, cbw)
+    inter, _ = image_rows("nf4", k2.matrix_image(nd, gate_up_interleave=True), rows, cols, 1, cbw)
+    assert np.array_equal(inter[64:128], plain[128:192]) and np.array_equal(inter[128:192], plain[64:128])
+
+
+def test_malformed_descriptors_are_rejected(oracle):
+    m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
+    L = k2.load_library()
+    good = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
+    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 16 * 2 * 1 * 16 + 16 * 2
+    for kw in ({"cols": 65}, {"bits": 7}, {"rows": 0}, {"kind": 1}, {"len0": 5}):
+        bad = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
+        for key, val in kw.items():
+            setattr(bad, key, val)
+        assert L.kronos_cuda_matrix_image(C.byref(bad), 0, None, 0) == 0
+    assert L.kronos_cuda_matrix_image(C.byref(good), 1, None, 0) == 0  # interleave needs rows % 128 == 0
+
+
+def test_library_exports_every_declared_symbol():
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "kronos_cuda_ffi.h")).read()
+    names = set(re.findall(r"\b(kronos_cuda_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 12
+    L = k2.load_library()
+    for n in sorted(names):
+        assert hasattr(L, n), n
+
+
+def test_no_gpu_means_error_not_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(k2.KronosCudaError):
+        k2.Context(0)

@@ -1,0 +1,184 @@
+"""GPU parity tests: every kernel is called through the C ABI (host-buffer entry points) and
+compared with the CPU oracle on the same seeded inputs.
+
+Bar: bit-exact for the int8 activations, their scales and sums, for the int32 chunk dots, and -
+because the kernels keep the reference's ascending-chunk fmaf order - for the fp32 outputs too
+(np.array_equal, no tolerance).
+"""
+import numpy as np
+import pytest
+
+from k2t_rng import normal
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import kronos_2t_b200 as k2
+    c = k2.Context(0)
+    yield c
+    c.close()
+
+
+def upload(ctx, m, interleave=False):
+    if m.kind == 0:
+        return ctx.upload_bipolar(m.rows, m.cols, m.planes, m.data, m.scales, interleave)
+    return ctx.upload_nf(m.rows, m.cols, m.bits, m.sgc, m.codebook, m.pair, m.tail, interleave)
+
+
+def random_bipolar(oracle, seed, rows, cols, planes):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    u = rng.integers(0, 1 << planes, (rows, cols), dtype=np.uint8)
+    sc = rng.integers(0x3800, 0x3C00, (rows, cols // 64)).astype(np.uint16)   # bf16 in [2^-15, 2^-7)
+    return oracle.bipolar_from_codes(u, sc, planes)
+
+
+def random_nf(oracle, seed, rows, cols, bits, sgc, codebook=None):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    idx = rng.integers(0, 1 << bits, (rows, cols), dtype=np.uint8)
+    n_sc = oracle.lib().k2o_nf_scale_count(rows, cols, sgc)
+    sc = rng.integers(0x3800, 0x3C00, n_sc).astype(np.uint16)
+    if codebook is None:
+        codebook = np.array([-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127], np.int8) if bits == 4 \
+            else np.array([-127, -79, -45, -14, 14, 45, 79, 127] + [0] * 8, np.int8)
+    return oracle.nf_pack(idx, sc, bits, sgc, codebook)
+
+
+# ----------------------------------------------------------------------------- K1
+@pytest.mark.parametrize("cols", [64, 576, 2048, 18944])
+def test_fwht_quant_bit_exact(ctx, oracle, cols):
+    x = normal(cols, (3, cols))
+    x[1, :64] = 0.0                       # a chunk that quantizes to zeros (scale 0, skipped by the GEMV)
+    x[2, 5] = 300.0                       # outlier
+    want = oracle.act_populate_fwht(x)
+    q, s, m = ctx.fwht_quant(x)
+    assert np.array_equal(q, want.q) and np.array_equal(s, want.scales) and np.array_equal(m, want.sums)
+    assert s[1, 0] == 0.0 and not q[1, :64].any()
+
+
+def test_fwht_quant_rmsnorm_and_chunk_offset(ctx, oracle):
+    cols = 1536
+    x = normal(7, (4, cols)) * np.float32(3.0)
+    w = (np.float32(1.0) + normal(8, cols) * np.float32(0.2)).astype(np.float32)
+    inv = np.array([oracle.inv_rms(x[t], 1e-5) for t in range(4)], np.float32)
+    want = oracle.act_populate_fwht(x, w, inv)
+    q, s, m = ctx.fwht_quant(x, w, inv)
+    assert np.array_equal(q, want.q) and np.array_equal(s, want.scales) and np.array_equal(m, want.sums)
+    # a column slice of a tensor-parallel rank uses the global chunk index (and blocks >= 256 use the generator)
+    for chunk0 in (5, 300):
+        want = oracle.act_populate_fwht(x[0], chunk0=chunk0)
+        q, s, m = ctx.fwht_quant(x[0], chunk0=chunk0)
+        assert np.array_equal(q, want.q) and np.array_equal(s, want.scales) and np.array_equal(m, want.sums)
+
+
+# ----------------------------------------------------------------------------- GEMV, quantized weights
+def _check_gemv(ctx, oracle, m, x, interleave=False):
+    act = oracle.act_populate_fwht(x)
+    dm = upload(ctx, m, interleave)
+    try:
+        out, dots = ctx.gemv(dm, act.q, act.scales, act.sums, want_dots=True)
+    finally:
+        dm.free()
+    if m.kind == 0:
+        want, want_dots = oracle.nibble4_gemv(oracle.nibble4_from_bipolar(m, interleave), act, want_dots=True)
+    else:
+        mm = oracle.nf_gate_up_interleave(m) if interleave else m
+        want, want_dots = oracle.nf_gemv(mm, act, want_dots=True)
+    assert np.array_equal(dots, want_dots), "int32 chunk dots differ"
+    assert np.array_equal(out, want), "fp32 outputs differ"
+    return out
+
+
+@pytest.mark.parametrize("planes", [4, 5, 6])
+@pytest.mark.parametrize("rows,cols", [(54, 192), (71, 576), (960, 576), (128, 1536)])
+def test_bitplane_gemv_bit_exact(ctx, oracle, planes, rows, cols):
+    m = oracle.bipolar_quantize_rtn(normal(rows + planes, (rows, cols), 0.02), planes)
+    x = normal(rows * 3 + cols, cols)
+    out = _check_gemv(ctx, oracle, m, x)
+    ref = np.stack([oracle.ifwht64(oracle.bipolar_dequant_row(m, r)) for r in range(rows)]).astype(np.float64) @ x.astype(np.float64)
+    assert np.dot(out[0], ref) / (np.linalg.norm(out[0]) * np.linalg.norm(ref)) > 0.9995
+
+
+@pytest.mark.parametrize("bits,sgc", [(4, 1), (4, 2), (3, 1), (3, 2)])
+@pytest.mark.parametrize("rows,cols", [(71, 192), (128, 576), (1536, 2048)])
+def test_nf_gemv_bit_exact(ctx, oracle, bits, sgc, rows, cols):
+    m = oracle.nf_quantize_rtn(normal(rows + bits + sgc, (rows, cols), 0.02), bits, sgc)
+    _check_gemv(ctx, oracle, m, normal(rows + cols, cols))
+
+
+def test_nf4_general_codebook(ctx, oracle):
+    cb = np.array([-120, -90, -70, -50, -33, -20, -9, -1, 3, 14, 29, 47, 60, 80, 101, 127], np.int8)
+    m = random_nf(oracle, 5, 96, 256, 4, 2, cb)
+    _check_gemv(ctx, oracle, m, normal(6, 256))
+
+
+@pytest.mark.parametrize("n_tok", [2, 3, 4, 7, 8, 15])
+def test_batch_gemv_matches_oracle(ctx, oracle, n_tok):
+    # batch forms: same per-(row, token) arithmetic as the single-token kernel
+    rows, cols = 54, 1536
+    x = normal(n_tok, (n_tok, cols))
+    x[n_tok - 1, 128:192] = 0.0
+    for m in (oracle.bipolar_quantize_rtn(normal(1, (rows, cols), 0.02), 5),
+              oracle.nf_quantize_rtn(normal(2, (rows, cols), 0.02), 4, 2)):
+        _check_gemv(ctx, oracle, m, x)
+
+
+def test_gate_up_interleave_upload(ctx, oracle):
+    rows, cols = 256, 576
+    _check_gemv(ctx, oracle, oracle.bipolar_quantize_rtn(normal(3, (rows, cols), 0.02), 4), normal(4, cols), interleave=True)
+    _check_gemv(ctx, oracle, oracle.nf_quantize_rtn(normal(5, (rows, cols), 0.02), 4, 2), normal(6, cols), interleave=True)
+
+
+def test_linear_end_to_end(ctx, oracle):
+    rows, cols = 576, 1536
+    m = oracle.bipolar_quantize_rtn(normal(11, (rows, cols), 0.02), 4)
+    x = normal(12, (5, cols))
+    dm = upload(ctx, m)
+    got = ctx.linear(dm, x)
+    dm.free()
+    want = oracle.nibble4_gemv(oracle.nibble4_from_bipolar(m), oracle.act_populate_fwht(x))
+    assert np.array_equal(got, want)
+
+
+# ----------------------------------------------------------------------------- sweep shapes (random codes)
+@pytest.mark.parametrize("fmt", ["b4", "b5", "b6", "nf4g128", "nf3g128"])
+@pytest.mark.parametrize("cols,rows", [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)])
+def test_sweep_shapes_bit_exact(ctx, oracle, fmt, cols, rows):
+    if fmt[0] == "b":
+        m = random_bipolar(oracle, rows + cols, rows, cols, int(fmt[1]))
+    else:
+        m = random_nf(oracle, rows + cols, rows, cols, int(fmt[2]), 2)
+    x = normal(99, (4, cols))
+    act = oracle.act_populate_fwht(x)
+    dm = upload(ctx, m)
+    try:
+        assert dm.file_bytes == m.file_bytes()
+        one = ctx.gemv(dm, act.q[0], act.scales[0], act.sums[0])
+        four, dots = ctx.gemv(dm, act.q, act.scales, act.sums, want_dots=True)
+    finally:
+        dm.free()
+    want, want_dots = oracle.gemv(m, act, want_dots=True, threads=8)
+    assert np.array_equal(dots, want_dots)
+    assert np.array_equal(four, want) and np.array_equal(one[0], want[0])
+    # size-independent property: column sums of the chunk dots equal the dots of the column-summed codes
+    if fmt[0] == "b":
+        planes = int(fmt[1])
+        u = np.stack([oracle.bipolar_unpack_row(m, r) for r in range(0, rows, max(1, rows // 64))]).astype(np.int64)
+        sel = np.arange(0, rows, max(1, rows // 64))
+        a = np.einsum("rci,ci->rc", u.reshape(len(sel), -1, 64), act.q[0].reshape(-1, 64).astype(np.int64))
+        assert np.array_equal(dots[0][sel], (2 * a - ((1 << planes) - 1) * act.sums[0][None, :]).astype(np.int32))
+
+
+def test_errors_are_reported_not_swallowed(ctx, oracle):
+    import kronos_2t_b200 as k2
+    m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
+    dm = upload(ctx, m)
+    with pytest.raises(k2.KronosCudaError):
+        ctx.gemv(dm, np.zeros(64, np.int8), np.zeros(1, np.float32), None)     # bit-planes need xsum
+    with pytest.raises(k2.KronosCudaError):
+        ctx.upload_bipolar(16, 64, 7, m.data, m.scales)
+    dm.free()
+    before = ctx.launch_count
+    ctx.fwht_quant(normal(2, 64))
+    assert ctx.launch_count == before + 1
