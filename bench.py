@@ -56,50 +56,69 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only queries) every ~2 ms while the
+    timed region runs."""
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.sm, self.reasons, self.max_mhz, self.err = index, [], set(), None, None
+        self._stop = threading.Event()
+        self.thread = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if vis:
+                try:
+                    idx = int(vis.split(",")[self.index])
+                except ValueError:
+                    idx = self.index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # noqa: BLE001
+            self.err = f"nvml unavailable: {e}"
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _sample(self):
+        nv = self.nv
+        self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+        try:
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+        except Exception:  # noqa: BLE001
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+        for name, bit in (("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40),
+                          ("sw_power_cap", 0x4), ("hw_power_brake_slowdown", 0x80)):
+            if r & bit:
+                self.reasons.add(name)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self._sample()
+            except Exception as e:  # noqa: BLE001
+                self.err = str(e)
+                return
+            time.sleep(0.002)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            if len(r) < 6:
-                continue
-            try:
-                sm.append(float(r[0])); mx.append(float(r[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, r[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self.thread:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            if not self.sm:
+                try:
+                    self._sample()
+                except Exception:  # noqa: BLE001
+                    pass
+        out = {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+               "samples": len(self.sm), "reasons": sorted(self.reasons)}
+        if self.err:
+            out["note"] = self.err
+        return out
 
 
 def build_sweep_host(seed0):
@@ -185,7 +204,9 @@ def run_b200(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
 
     ctx = k2.Context(local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream(device=dev)      # a real (non-default) stream: events and kernels share it
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
     ctx.set_stream(stream.cuda_stream)
 
     mats = build_sweep_host(1000 + 100 * rank)
@@ -306,6 +327,63 @@ def run_b200(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_case(args, local_rank):
+    """Single-case loop for profiling: `--case b4:2048x49152 [--tokens 4]` rotates over enough copies of
+    one matrix to exceed L2 (>= 256 MB of distinct weights) and times the GEMV launches with CUDA events."""
+    import torch
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+
+    fmt, shape = args.case.split(":")
+    cols, rows = (int(v) for v in shape.split("x"))
+    kind, bits, sgc = fmt_spec(fmt)
+    n_tok = args.tokens
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = k2.Context(local_rank)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    ctx.set_stream(stream.cuda_stream)
+    wbytes = synth.file_bytes(kind, rows, cols, bits, sgc)
+    copies = max(3, -(-(256 << 20) // wbytes))
+    mats = []
+    for i in range(copies):
+        if kind == "bipolar":
+            d0, d1 = synth.random_bipolar_bytes(i, rows, cols, bits)
+            mats.append(ctx.upload_bipolar(rows, cols, bits, d0, d1))
+        else:
+            d0, d1 = synth.random_nf_bytes(i, rows, cols, bits, sgc)
+            mats.append(ctx.upload_nf(rows, cols, bits, sgc, _default_cb(bits), d0, d1))
+    nc = cols // 64
+    x = torch.randn(n_tok, cols, device=dev)
+    q = torch.empty(n_tok, cols, dtype=torch.int8, device=dev)
+    sc = torch.empty(n_tok, nc, dtype=torch.float32, device=dev)
+    sums = torch.empty(n_tok, nc, dtype=torch.int32, device=dev)
+    out = torch.empty(n_tok, rows, dtype=torch.float32, device=dev)
+    ctx.fwht_quant_dev(x.data_ptr(), n_tok, cols, q.data_ptr(), sc.data_ptr(), sums.data_ptr())
+
+    def launch(i):
+        ctx.gemv_dev(mats[i % copies], q.data_ptr(), sc.data_ptr(), sums.data_ptr(), n_tok, out.data_ptr())
+
+    for i in range(args.warmup):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        launch(args.warmup + i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    b = algorithmic_bytes(fmt, cols, rows, n_tok)
+    peak, kind_p = peaks()
+    print(json.dumps({"case": args.case, "tokens": n_tok, "copies": copies, "us_per_launch": us,
+                      "algorithmic_bytes": b, "GBps": b / us / 1e3, "frac_of_" + kind_p: b / us / 1e3 / peak}))
+    for m in mats:
+        m.free()
+    ctx.close()
+
+
 def cpu_baseline(mats):
     """Oracle (C++ port of the reference CPU path) on one pass of the same sweep, all host threads."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -338,15 +416,19 @@ def cpu_baseline(mats):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")
+    ap.add_argument("--tokens", type=int, default=1, help="tokens per launch in --case mode (1..8)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.case:
+        run_case(args, local_rank)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_b200(args, rank, world, local_rank)

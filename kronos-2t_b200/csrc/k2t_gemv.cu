@@ -1,4 +1,5 @@
-// Quantized GEMV / small-N GEMM for bit-plane (b4/b5/b6) and codebook (NF4/NF3) matrices.
+// Quantized GEMV (batch 1) and small-N GEMM (2..8 tokens) for bit-plane (b4/b5/b6) and codebook
+// (NF4/NF3) matrices.
 //
 // Arithmetic contract (reference: sdot_one_stripe_neon, src/kernels/simd_lut.rs:3763-3868, and
 // nf_sdot_one_stripe_neon, 6071-6181; batch forms 4228-4331 / 6689-7029):
@@ -6,14 +7,17 @@
 //       bit-plane: dot = 2a - (2^B-1) * xsum[c]      NF: dot = a
 //   f = 0;  for c ascending, skipping chunks with xs[c] == 0:
 //       f = fmaf((float)dot * xs[c], w_scale[r, c / sgc], f)
-// The integer part is computed in parallel by all lanes; the fp32 chain is then run per row in
-// ascending chunk order by one lane, so outputs are bit-identical to the reference order.
+// The integer dots are computed by all lanes in parallel; the fp32 chain always runs per row in
+// ascending chunk order, so outputs are bit-identical to the reference order.
 //
-// Work decomposition: a CTA owns `gpb` consecutive 8-row groups and all K.  A quarter-warp
-// (8 lanes = 8 rows) handles one (group, chunk) record per step; the four quarter-warps of a warp
-// take four consecutive records, i.e. 1 KiB (b4) of contiguous weights per warp step, each
-// 128-bit load of a quarter-warp covering one 128-byte line.  Activations (int8, <= 18.5 KiB)
-// sit in shared memory and are read as quarter-warp broadcasts.
+// Batch-1 kernel (gemv1_kernel).  A quarter-warp (8 lanes = the 8 rows of a group) walks the records
+// of its group; with S K-slices, slice s takes chunks s, s+S, s+2S, ...  Each 128-bit load of a
+// quarter-warp covers one 128-byte line, a warp step reads up to 1 KiB of contiguous weights, and
+// every lane keeps UNROLL records in flight (registers) while it computes the previous batch.
+//   S == 1 : one lane owns a row for all K; the fp32 chain runs in registers as chunks arrive.
+//   S  > 1 : lanes park (v, w_scale) per chunk in shared memory; after a CTA barrier one lane per
+//            row runs the chain.  Used when rows alone do not provide enough warps.
+// Activations (int8, <= 18.5 KiB) are staged once per CTA in shared memory and read as broadcasts.
 #include "k2t_device.cuh"
 #include "k2t_kernels.h"
 
@@ -21,64 +25,69 @@ namespace k2t {
 
 struct GemvArgs {
     const uint8_t *rec;
-    const uint16_t *scales;
+    const uint16_t *scales;   // [group][nsg][8] bf16
     const int8_t *xq;
     const float *xs;
     const int32_t *xsum;
     float *out;
     int32_t *int_dots;
     size_t out_stride;
-    uint32_t rows, cols, nc, nsg, sgc, ngroups, rec_bytes, n_tok, gpb;
+    uint32_t rows, cols, nc, nsg, sgc, sgc_shift, ngroups, rec_bytes, n_tok, gpb, slices;   // sgc_shift: log2(sgc) or 32
     int32_t max_odd;
-    uint32_t cb[8];   // expanded codebook, 4 centroids per word
+    int32_t nf4_offset;
+    uint32_t cb[8];    // expanded codebook, 4 centroids per word (NF4: sorted ascending)
+    uint32_t tab[4];   // NF4 two-table decode: hi[0..3], hi[4..7], lo[0..3], lo[4..7]
 };
 
-struct Raw {          // the bytes one lane loads for one (group, chunk) record
-    uint4 a, b, c;
+constexpr int FMT_NF4G = FMT_COUNT;   // NF4 with a codebook the two-table decode cannot represent
+
+template <int FMT> struct RawWords { static constexpr int N = 8; };
+template <> struct RawWords<FMT_BP5> { static constexpr int N = 10; };
+template <> struct RawWords<FMT_BP6> { static constexpr int N = 12; };
+template <> struct RawWords<FMT_NF3> { static constexpr int N = 6; };
+
+template <int FMT>
+struct Raw {          // the words one lane loads for one (group, chunk) record
+    uint32_t w[RawWords<FMT>::N];
 };
 
 template <int FMT>
-__device__ __forceinline__ Raw load_raw(const uint8_t *rec, uint32_t r) {
-    Raw w;
+__device__ __forceinline__ void load_raw(Raw<FMT> &o, const uint8_t *rec, uint32_t r) {
     const uint4 *p = reinterpret_cast<const uint4 *>(rec);
-    w.a = ldg_stream(p + r);
-    w.b = make_uint4(0, 0, 0, 0);
-    w.c = make_uint4(0, 0, 0, 0);
-    if (FMT == FMT_BP4 || FMT == FMT_BP5 || FMT == FMT_BP6 || FMT == FMT_NF4 || FMT == FMT_NF5) w.b = ldg_stream(p + 8 + r);
-    if (FMT == FMT_BP5 || FMT == FMT_NF5) {
-        uint2 h = ldg_stream(reinterpret_cast<const uint2 *>(rec + 256) + r);
-        w.c.x = h.x; w.c.y = h.y;
-    }
-    if (FMT == FMT_BP6) w.c = ldg_stream(p + 16 + r);
+    uint4 a = ldg_stream(p + r);
+    o.w[0] = a.x; o.w[1] = a.y; o.w[2] = a.z; o.w[3] = a.w;
     if (FMT == FMT_NF3) {
         uint2 h = ldg_stream(reinterpret_cast<const uint2 *>(rec + 128) + r);
-        w.c.x = h.x; w.c.y = h.y;
+        o.w[4] = h.x; o.w[5] = h.y;
+        return;
     }
-    return w;
-}
-
-__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
-    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+    uint4 b = ldg_stream(p + 8 + r);
+    o.w[4] = b.x; o.w[5] = b.y; o.w[6] = b.z; o.w[7] = b.w;
+    if (FMT == FMT_BP5) {
+        uint2 h = ldg_stream(reinterpret_cast<const uint2 *>(rec + 256) + r);
+        o.w[8] = h.x; o.w[9] = h.y;
+    }
+    if (FMT == FMT_BP6) {
+        uint4 h = ldg_stream(p + 16 + r);
+        o.w[8] = h.x; o.w[9] = h.y; o.w[10] = h.z; o.w[11] = h.w;
+    }
 }
 
 // Expands a record into 16 words of four weight bytes each: u[j] holds columns 4j..4j+3 of the chunk.
 // Bit-plane formats give unsigned codes 0..63, NF formats signed centroids.
 template <int FMT>
-__device__ __forceinline__ void decode(const Raw &w, const uint32_t (&cb)[8], uint32_t (&u)[16]) {
+__device__ __forceinline__ void decode(const Raw<FMT> &w, const uint32_t (&cb)[8], uint32_t (&u)[16]) {
     if (FMT == FMT_BP4 || FMT == FMT_BP5 || FMT == FMT_BP6) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t x = word_of(w.a, i), y = word_of(w.b, i);
-            u[2 * i] = x & 0x0F0F0F0Fu;
-            u[2 * i + 1] = (x >> 4) & 0x0F0F0F0Fu;
-            u[8 + 2 * i] = y & 0x0F0F0F0Fu;
-            u[8 + 2 * i + 1] = (y >> 4) & 0x0F0F0F0Fu;
+        for (int i = 0; i < 8; ++i) {
+            u[2 * i] = w.w[i] & 0x0F0F0F0Fu;
+            u[2 * i + 1] = (w.w[i] >> 4) & 0x0F0F0F0Fu;
         }
         if (FMT == FMT_BP5) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {   // plane-4 bit of column 4j+b sits at bit j of byte b
-                uint32_t h0 = j <= 4 ? (w.c.x << (4 - j)) : (w.c.x >> (j - 4));
-                uint32_t h1 = j <= 4 ? (w.c.y << (4 - j)) : (w.c.y >> (j - 4));
+                uint32_t h0 = j <= 4 ? (w.w[8] << (4 - j)) : (w.w[8] >> (j - 4));
+                uint32_t h1 = j <= 4 ? (w.w[9] << (4 - j)) : (w.w[9] >> (j - 4));
                 u[j] = lop3_or_and(u[j], h0, 0x10101010u);
                 u[8 + j] = lop3_or_and(u[8 + j], h1, 0x10101010u);
             }
@@ -86,17 +95,17 @@ __device__ __forceinline__ void decode(const Raw &w, const uint32_t (&cb)[8], ui
         if (FMT == FMT_BP6) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {   // planes 4,5 of column 16v+4f+b sit at bits 2f,2f+1 of byte b
-                uint32_t h = word_of(w.c, v);
+                uint32_t h = w.w[8 + v];
                 u[4 * v + 0] = lop3_or_and(u[4 * v + 0], h << 4, 0x30303030u);
                 u[4 * v + 1] = lop3_or_and(u[4 * v + 1], h << 2, 0x30303030u);
                 u[4 * v + 2] = lop3_or_and(u[4 * v + 2], h, 0x30303030u);
                 u[4 * v + 3] = lop3_or_and(u[4 * v + 3], h >> 2, 0x30303030u);
             }
         }
-    } else if (FMT == FMT_NF4) {
+    } else if (FMT == FMT_NF4 || FMT == FMT_NF4G) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {      // word i = eight consecutive 4-bit indices (columns 8i..8i+7)
-            uint32_t x = i < 4 ? word_of(w.a, i) : word_of(w.b, i - 4);
+            uint32_t x = w.w[i];
             uint32_t lo3 = x & 0x77777777u, hb = x & 0x88888888u, hs = hb << 4;
             uint32_t lo3h = lo3 >> 16;
             uint32_t m0 = prmt(hs, hb, 0xD9C8u), m1 = prmt(hs, hb, 0xFBEAu);   // byte masks: index bit 3
@@ -104,18 +113,17 @@ __device__ __forceinline__ void decode(const Raw &w, const uint32_t (&cb)[8], ui
             u[2 * i + 1] = lop3_select(prmt(cb[0], cb[1], lo3h), prmt(cb[2], cb[3], lo3h), m1);
         }
     } else if (FMT == FMT_NF3) {
-        uint32_t W[6] = {w.a.x, w.a.y, w.a.z, w.a.w, w.c.x, w.c.y};
 #pragma unroll
         for (int i = 0; i < 6; ++i) {      // columns 8i..8i+7: index in the low 3 bits of each nibble
-            uint32_t s = W[i] & 0x77777777u;
+            uint32_t s = w.w[i] & 0x77777777u;
             u[2 * i] = prmt(cb[0], cb[1], s);
             u[2 * i + 1] = prmt(cb[0], cb[1], s >> 16);
         }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {      // columns 48+8h..: index bit j = bit 3 of the nibbles of W[3h+j]
-            uint32_t s = (W[3 * h] >> 3) & 0x11111111u;
-            s = lop3_or_and(s, W[3 * h + 1] >> 2, 0x22222222u);
-            s = lop3_or_and(s, W[3 * h + 2] >> 1, 0x44444444u);
+            uint32_t s = (w.w[3 * h] >> 3) & 0x11111111u;
+            s = lop3_or_and(s, w.w[3 * h + 1] >> 2, 0x22222222u);
+            s = lop3_or_and(s, w.w[3 * h + 2] >> 1, 0x44444444u);
             u[12 + 2 * h] = prmt(cb[0], cb[1], s);
             u[13 + 2 * h] = prmt(cb[0], cb[1], s >> 16);
         }
@@ -139,11 +147,162 @@ __device__ __forceinline__ int dot16(const uint32_t (&u)[16], const int4 *q) {
     return acc;
 }
 
+// Integer sum(code * q) of one record against one 64-column activation chunk, single token.
+// b4 keeps high nibbles in place (x16) in a second accumulator; NF4 looks the eight largest and the
+// eight smallest centroids up in two non-negative 8-entry tables: a prmt selector nibble with bit 3
+// set yields the replicated sign bit of the table byte, i.e. 0 here, so `x ^ 0x88888888` selects the
+// upper half where bit 3 is set and `x` the lower half where it is clear, with no masks or blends.
+template <int FMT>
+__device__ __forceinline__ int cell_dot(const Raw<FMT> &w, const GemvArgs &a, const int4 *q4, int xsum_c) {
+    if (FMT == FMT_BP4) {
+        int lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int4 v = q4[i];
+            lo = dp4a_us(w.w[2 * i] & 0x0F0F0F0Fu, v.x, lo);
+            hi = dp4a_us(w.w[2 * i] & 0xF0F0F0F0u, v.y, hi);
+            lo = dp4a_us(w.w[2 * i + 1] & 0x0F0F0F0Fu, v.z, lo);
+            hi = dp4a_us(w.w[2 * i + 1] & 0xF0F0F0F0u, v.w, hi);
+        }
+        return lo + (hi >> 4);   // hi is an exact multiple of 16
+    } else if (FMT == FMT_NF4) {
+        int up = 0, dn = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int4 v = q4[i];
+            uint32_t x0 = w.w[2 * i], x1 = w.w[2 * i + 1];
+            uint32_t y0 = x0 ^ 0x88888888u, y1 = x1 ^ 0x88888888u;
+            up = dp4a_us(prmt(a.tab[0], a.tab[1], y0), v.x, up);
+            dn = dp4a_us(prmt(a.tab[2], a.tab[3], x0), v.x, dn);
+            up = dp4a_us(prmt(a.tab[0], a.tab[1], __umulhi(y0, 65536u)), v.y, up);   // >> 16 on the FMA pipe
+            dn = dp4a_us(prmt(a.tab[2], a.tab[3], __umulhi(x0, 65536u)), v.y, dn);
+            up = dp4a_us(prmt(a.tab[0], a.tab[1], y1), v.z, up);
+            dn = dp4a_us(prmt(a.tab[2], a.tab[3], x1), v.z, dn);
+            up = dp4a_us(prmt(a.tab[0], a.tab[1], __umulhi(y1, 65536u)), v.w, up);
+            dn = dp4a_us(prmt(a.tab[2], a.tab[3], __umulhi(x1, 65536u)), v.w, dn);
+        }
+        return up - dn + a.nf4_offset * xsum_c;
+    } else {
+        uint32_t u[16];
+        decode<FMT>(w, a.cb, u);
+        return dot16<FMT>(u, q4);
+    }
+}
+
+__device__ __forceinline__ uint32_t scale_group_of(const GemvArgs &a, uint32_t c) {
+    return a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
+}
+
+template <int FMT> __device__ __forceinline__ constexpr bool is_bitplane() {
+    return FMT == FMT_BP4 || FMT == FMT_BP5 || FMT == FMT_BP6;
+}
+
 __host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
 
-struct SmemPlan {
-    size_t xq, xs, xsum, ws, v, total;
-};
+// ------------------------------------------------------------------------------------------------
+// batch-1 kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int G1_THREADS = 128;   // 16 quarter-warps
+constexpr int G1_UNROLL = 4;
+
+struct Smem1 { size_t xs, xsum, v, total; };
+__host__ __device__ inline Smem1 smem1_plan(uint32_t cols, uint32_t nc, uint32_t gpb, bool split) {
+    Smem1 p;
+    p.xs = align16(cols);
+    p.xsum = p.xs + align16((size_t)nc * 4);
+    p.v = p.xsum + align16((size_t)nc * 4);
+    p.total = p.v + (split ? (size_t)gpb * nc * 8 * 8 : 0);
+    return p;
+}
+
+template <int FMT, bool SPLIT>
+__global__ void __launch_bounds__(G1_THREADS) gemv1_kernel(const GemvArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const Smem1 sp = smem1_plan(a.cols, a.nc, a.gpb, SPLIT);
+    int8_t *s_xq = reinterpret_cast<int8_t *>(smem);
+    float *s_xs = reinterpret_cast<float *>(smem + sp.xs);
+    int32_t *s_xsum = reinterpret_cast<int32_t *>(smem + sp.xsum);
+    float2 *s_v = reinterpret_cast<float2 *>(smem + sp.v);
+
+    const uint32_t tid = threadIdx.x, r = tid & 7, qw = tid >> 3;
+    const uint32_t S = SPLIT ? a.slices : 1;
+    const uint32_t gl = SPLIT ? qw / S : qw, s = SPLIT ? qw % S : 0;
+    const uint32_t g = blockIdx.x * a.gpb + gl;
+    const bool live = g < a.ngroups;
+    const uint32_t n_i = live ? (a.nc - s + S - 1) / S : 0;     // chunks s, s+S, ... of this lane's slice
+    const uint8_t *rec = a.rec + ((size_t)g * a.nc + s) * a.rec_bytes;
+    const size_t rec_step = (size_t)S * a.rec_bytes;
+    const uint16_t *wsp = a.scales + (size_t)g * a.nsg * 8 + r;
+
+    // first batch of weight records goes out before anything else: its latency covers the staging
+    Raw<FMT> cur[G1_UNROLL];
+    uint16_t cur_ws[G1_UNROLL];
+#pragma unroll
+    for (int k = 0; k < G1_UNROLL; ++k)
+        if ((uint32_t)k < n_i) {
+            load_raw<FMT>(cur[k], rec + k * rec_step, r);
+            cur_ws[k] = __ldg(wsp + (size_t)scale_group_of(a, s + k * S) * 8);
+        }
+
+    for (uint32_t i = tid; i < a.cols / 16; i += G1_THREADS)
+        reinterpret_cast<int4 *>(s_xq)[i] = reinterpret_cast<const int4 *>(a.xq)[i];
+    for (uint32_t i = tid; i < a.nc; i += G1_THREADS) {
+        s_xs[i] = a.xs[i];
+        s_xsum[i] = a.xsum != nullptr ? a.xsum[i] : 0;
+    }
+    __syncthreads();
+
+    const uint32_t row = g * 8 + r;
+    float f = 0.0f;
+    for (uint32_t i0 = 0; i0 < n_i; i0 += G1_UNROLL) {
+        Raw<FMT> nxt[G1_UNROLL];
+        uint16_t nxt_ws[G1_UNROLL];
+#pragma unroll
+        for (int k = 0; k < G1_UNROLL; ++k) {
+            const uint32_t i = i0 + G1_UNROLL + k;
+            if (i < n_i) {
+                load_raw<FMT>(nxt[k], rec + (size_t)i * rec_step, r);
+                nxt_ws[k] = __ldg(wsp + (size_t)scale_group_of(a, s + i * S) * 8);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < G1_UNROLL; ++k) {
+            const uint32_t i = i0 + k;
+            if (i < n_i) {
+                const uint32_t c = s + i * S;
+                const int xsum_c = s_xsum[c];
+                const int acc = cell_dot<FMT>(cur[k], a, reinterpret_cast<const int4 *>(s_xq + (size_t)c * 64), xsum_c);
+                const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum_c : acc;
+                const float sx = s_xs[c];
+                const float v = __fmul_rn(__int2float_rn(dot), sx);
+                const float ws = bf16_bits_to_f32(cur_ws[k]);
+                if (SPLIT) s_v[((size_t)gl * a.nc + c) * 8 + r] = make_float2(v, ws);
+                else if (sx != 0.0f) f = __fmaf_rn(v, ws, f);
+                if (a.int_dots != nullptr && row < a.rows) a.int_dots[(size_t)row * a.nc + c] = dot;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < G1_UNROLL; ++k) { cur[k] = nxt[k]; cur_ws[k] = nxt_ws[k]; }
+    }
+
+    if (SPLIT) {
+        __syncthreads();
+        if (s == 0 && live) {      // ordered fp32 chain: one lane per row
+            const float2 *vv = s_v + (size_t)gl * a.nc * 8 + r;
+#pragma unroll 4
+            for (uint32_t c = 0; c < a.nc; ++c) {
+                const float2 t = vv[(size_t)c * 8];
+                if (s_xs[c] != 0.0f) f = __fmaf_rn(t.x, t.y, f);
+            }
+        }
+    }
+    if (s == 0 && live && row < a.rows) a.out[row] = f;
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2..8-token kernel: weights decoded once per record, reused for every token
+// ------------------------------------------------------------------------------------------------
+struct SmemPlan { size_t xq, xs, xsum, ws, v, total; };
 __host__ __device__ inline SmemPlan smem_plan(uint32_t nt, uint32_t cols, uint32_t nc, uint32_t nsg, uint32_t gpb) {
     SmemPlan p;
     p.xq = 0;
@@ -156,7 +315,7 @@ __host__ __device__ inline SmemPlan smem_plan(uint32_t nt, uint32_t cols, uint32
 }
 
 template <int FMT, int NT>
-__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(256) gemm_small_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     const SmemPlan sp = smem_plan(NT, a.cols, a.nc, a.nsg, a.gpb);
     int8_t *s_xq = reinterpret_cast<int8_t *>(smem + sp.xq);
@@ -171,12 +330,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
     const uint32_t total = ng * a.nc;
     const uint8_t *rec0 = a.rec + (size_t)g0 * a.nc * a.rec_bytes;
 
-    // first weight record is requested before anything else so HBM latency overlaps the staging below
     uint32_t L = qw;
-    Raw cur;
-    if (L < total) cur = load_raw<FMT>(rec0 + (size_t)L * a.rec_bytes, r);
+    Raw<FMT> cur;
+    if (L < total) load_raw<FMT>(cur, rec0 + (size_t)L * a.rec_bytes, r);
 
-    // stage activations (tokens beyond n_tok are zero and skipped) and this CTA's weight scales
     {
         const uint32_t vec_per_tok = a.cols / 16;
         for (uint32_t i = tid; i < NT * vec_per_tok; i += 256) {
@@ -190,25 +347,24 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
             s_xs[i] = t < a.n_tok ? a.xs[i] : 0.0f;
             s_xsum[i] = (t < a.n_tok && a.xsum != nullptr) ? a.xsum[i] : 0;
         }
-        const uint32_t n_ws = ng * 8 * a.nsg;                       // bf16 count, contiguous for the CTA
+        const uint32_t n_ws = ng * 8 * a.nsg;                       // [group][sg][row], contiguous for the CTA
         const uint16_t *ws_src = a.scales + (size_t)g0 * 8 * a.nsg;
         for (uint32_t i = tid; i < n_ws; i += 256) s_ws[i] = ws_src[i];
     }
     __syncthreads();
 
+    uint32_t c = L % a.nc, gl = L / a.nc;
     while (L < total) {
         const uint32_t Ln = L + 32;
-        Raw nxt;
-        if (Ln < total) nxt = load_raw<FMT>(rec0 + (size_t)Ln * a.rec_bytes, r);
+        Raw<FMT> nxt;
+        if (Ln < total) load_raw<FMT>(nxt, rec0 + (size_t)Ln * a.rec_bytes, r);
         uint32_t u[16];
         decode<FMT>(cur, a.cb, u);
-        const uint32_t c = L % a.nc, gl = L / a.nc;
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const int4 *q = reinterpret_cast<const int4 *>(s_xq + (size_t)t * a.cols + (size_t)c * 64);
             int acc = dot16<FMT>(u, q);
-            int dot = (FMT == FMT_BP4 || FMT == FMT_BP5 || FMT == FMT_BP6)
-                          ? 2 * acc - a.max_odd * s_xsum[t * a.nc + c] : acc;
+            int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * s_xsum[t * a.nc + c] : acc;
             s_v[((size_t)(t * a.gpb + gl) * a.nc + c) * 8 + r] = __fmul_rn(__int2float_rn(dot), s_xs[t * a.nc + c]);
             if (a.int_dots != nullptr && t < (int)a.n_tok) {
                 uint32_t row = (g0 + gl) * 8 + r;
@@ -217,53 +373,72 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
         }
         cur = nxt;
         L = Ln;
+        c += 32;
+        while (c >= a.nc) { c -= a.nc; ++gl; }
     }
     __syncthreads();
 
-    // ordered fp32 chain: one lane per (token, row)
     for (uint32_t idx = tid; idx < NT * ng * 8; idx += 256) {
-        const uint32_t rr = idx & 7, gl = (idx >> 3) % ng, t = idx / (8 * ng);
-        const uint32_t row = (g0 + gl) * 8 + rr;
+        const uint32_t rr = idx & 7, gli = (idx >> 3) % ng, t = idx / (8 * ng);
+        const uint32_t row = (g0 + gli) * 8 + rr;
         if (row >= a.rows || t >= a.n_tok) continue;
-        const float *vv = s_v + ((size_t)(t * a.gpb + gl) * a.nc) * 8 + rr;
-        const uint16_t *wsr = s_ws + (size_t)(gl * 8 + rr) * a.nsg;
+        const float *vv = s_v + ((size_t)(t * a.gpb + gli) * a.nc) * 8 + rr;
+        const uint16_t *wsr = s_ws + (size_t)gli * a.nsg * 8 + rr;
         const float *sx = s_xs + (size_t)t * a.nc;
         float f = 0.0f;
-        uint32_t c = 0;
+        uint32_t cc = 0;
         for (uint32_t sg = 0; sg < a.nsg; ++sg) {
-            const float ws = bf16_bits_to_f32(wsr[sg]);
-            const uint32_t c_end = min(c + a.sgc, a.nc);
-            for (; c < c_end; ++c)
-                if (sx[c] != 0.0f) f = __fmaf_rn(vv[(size_t)c * 8], ws, f);
+            const float ws = bf16_bits_to_f32(wsr[(size_t)sg * 8]);
+            const uint32_t c_end = min(cc + a.sgc, a.nc);
+            for (; cc < c_end; ++cc)
+                if (sx[cc] != 0.0f) f = __fmaf_rn(vv[(size_t)cc * 8], ws, f);
         }
         a.out[(size_t)t * a.out_stride + row] = f;
     }
 }
 
-template <int FMT, int NT>
-static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, size_t smem, uint32_t grid) {
-    static bool configured = false;   // per instantiation; the attribute is process-wide for the function
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static const size_t kSmemBudget = 196 * 1024;
+
+template <typename K>
+static cudaError_t allow_big_smem(K kernel, size_t smem) {
+    if (smem <= 48 * 1024) return cudaSuccess;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+}
+
+template <int FMT>
+static cudaError_t launch_gemv1(cudaStream_t stream, const GemvArgs &a, bool split, size_t smem, uint32_t grid) {
+    cudaError_t e;
+    if (split) {
+        if ((e = allow_big_smem(gemv1_kernel<FMT, true>, smem)) != cudaSuccess) return e;
+        gemv1_kernel<FMT, true><<<grid, G1_THREADS, smem, stream>>>(a);
+    } else {
+        if ((e = allow_big_smem(gemv1_kernel<FMT, false>, smem)) != cudaSuccess) return e;
+        gemv1_kernel<FMT, false><<<grid, G1_THREADS, smem, stream>>>(a);
     }
-    gemv_kernel<FMT, NT><<<grid, 256, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+template <int FMT, int NT>
+static cudaError_t launch_small_one(cudaStream_t stream, const GemvArgs &a, size_t smem, uint32_t grid) {
+    cudaError_t e = allow_big_smem(gemm_small_kernel<FMT, NT>, smem);
+    if (e != cudaSuccess) return e;
+    gemm_small_kernel<FMT, NT><<<grid, 256, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(cudaStream_t stream, const GemvArgs &a, uint32_t nt, size_t smem, uint32_t grid) {
+static cudaError_t launch_small(cudaStream_t stream, const GemvArgs &a, uint32_t nt, size_t smem, uint32_t grid) {
     switch (nt) {
-        case 1: return launch_one<FMT, 1>(stream, a, smem, grid);
-        case 2: return launch_one<FMT, 2>(stream, a, smem, grid);
-        case 4: return launch_one<FMT, 4>(stream, a, smem, grid);
-        default: return launch_one<FMT, 8>(stream, a, smem, grid);
+        case 2: return launch_small_one<FMT, 2>(stream, a, smem, grid);
+        case 4: return launch_small_one<FMT, 4>(stream, a, smem, grid);
+        default: return launch_small_one<FMT, 8>(stream, a, smem, grid);
     }
 }
 
 static uint32_t round_tokens(uint32_t n) { return n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : 8; }
-static const size_t kSmemBudget = 196 * 1024;
 
 uint32_t gemv_max_tokens(const DeviceMatrix &m) {
     for (uint32_t nt = 8; nt > 1; nt >>= 1)
@@ -278,33 +453,63 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
     if (launches) *launches = 0;
     if (n_tok == 0) return cudaSuccess;
     if (n_tok > 8 || g.fmt == FMT_NF5 || g.fmt == FMT_E8Q2) return cudaErrorNotSupported;
-    const uint32_t nt = round_tokens(n_tok);
-    // groups per CTA: as many as keep >= 2 CTAs per SM and fit shared memory
-    uint32_t gpb = 1;
-    for (uint32_t cand : {4u, 2u}) {
-        if ((g.ngroups + cand - 1) / cand >= (uint32_t)(2 * sm_count) &&
-            smem_plan(nt, g.cols, g.nc, g.nsg, cand).total <= 64 * 1024) { gpb = cand; break; }
-    }
-    const size_t smem = smem_plan(nt, g.cols, g.nc, g.nsg, gpb).total;
-    if (smem > kSmemBudget) return cudaErrorInvalidValue;
     GemvArgs a;
     a.rec = m.d_rec; a.scales = m.d_scales; a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.int_dots = int_dots;
     a.out_stride = out_stride;
     a.rows = g.rows; a.cols = g.cols; a.nc = g.nc; a.nsg = g.nsg; a.sgc = g.sgc; a.ngroups = g.ngroups;
-    a.rec_bytes = g.rec_bytes; a.n_tok = n_tok; a.gpb = gpb; a.max_odd = g.max_odd;
+    a.sgc_shift = 32;
+    for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
+    a.rec_bytes = g.rec_bytes; a.n_tok = n_tok; a.max_odd = g.max_odd; a.nf4_offset = g.nf4_offset;
     for (int i = 0; i < 8; ++i) {
         const uint8_t *b = reinterpret_cast<const uint8_t *>(g.codebook32) + 4 * i;
         a.cb[i] = (uint32_t)b[0] | ((uint32_t)b[1] << 8) | ((uint32_t)b[2] << 16) | ((uint32_t)b[3] << 24);
     }
-    const uint32_t grid = (g.ngroups + gpb - 1) / gpb;
+    for (int i = 0; i < 2; ++i) {
+        const uint8_t *h = g.nf4_hi + 4 * i, *l = g.nf4_lo + 4 * i;
+        a.tab[i] = (uint32_t)h[0] | ((uint32_t)h[1] << 8) | ((uint32_t)h[2] << 16) | ((uint32_t)h[3] << 24);
+        a.tab[2 + i] = (uint32_t)l[0] | ((uint32_t)l[1] << 8) | ((uint32_t)l[2] << 16) | ((uint32_t)l[3] << 24);
+    }
     cudaError_t e;
-    switch (g.fmt) {
-        case FMT_BP4: e = launch_fmt<FMT_BP4>(stream, a, nt, smem, grid); break;
-        case FMT_BP5: e = launch_fmt<FMT_BP5>(stream, a, nt, smem, grid); break;
-        case FMT_BP6: e = launch_fmt<FMT_BP6>(stream, a, nt, smem, grid); break;
-        case FMT_NF4: e = launch_fmt<FMT_NF4>(stream, a, nt, smem, grid); break;
-        case FMT_NF3: e = launch_fmt<FMT_NF3>(stream, a, nt, smem, grid); break;
-        default: return cudaErrorNotSupported;
+    if (n_tok == 1) {
+        // K-slices: enough warps to keep ~8 per SM in flight, at least two chunks per slice
+        const uint32_t want_warps = 8u * (uint32_t)sm_count;
+        uint32_t S = 1;
+        while (S < 16 && (g.ngroups * S) / 4 < want_warps && g.nc / (2 * S) >= 2) S *= 2;
+        const bool split = S > 1;
+        a.slices = S;
+        a.gpb = (G1_THREADS / 8) / S;
+        const size_t smem = smem1_plan(g.cols, g.nc, a.gpb, split).total;
+        if (smem > kSmemBudget) return cudaErrorInvalidValue;
+        const uint32_t grid = (g.ngroups + a.gpb - 1) / a.gpb;
+        const bool nf4_fast = g.fmt == FMT_NF4 && g.nf4_split_ok && (g.nf4_offset == 0 || xsum != nullptr);
+        switch (g.fmt) {
+            case FMT_BP4: e = launch_gemv1<FMT_BP4>(stream, a, split, smem, grid); break;
+            case FMT_BP5: e = launch_gemv1<FMT_BP5>(stream, a, split, smem, grid); break;
+            case FMT_BP6: e = launch_gemv1<FMT_BP6>(stream, a, split, smem, grid); break;
+            case FMT_NF4: e = nf4_fast ? launch_gemv1<FMT_NF4>(stream, a, split, smem, grid)
+                                       : launch_gemv1<FMT_NF4G>(stream, a, split, smem, grid); break;
+            case FMT_NF3: e = launch_gemv1<FMT_NF3>(stream, a, split, smem, grid); break;
+            default: return cudaErrorNotSupported;
+        }
+    } else {
+        const uint32_t nt = round_tokens(n_tok);
+        uint32_t gpb = 1;
+        for (uint32_t cand : {4u, 2u}) {
+            if ((g.ngroups + cand - 1) / cand >= (uint32_t)(2 * sm_count) &&
+                smem_plan(nt, g.cols, g.nc, g.nsg, cand).total <= 64 * 1024) { gpb = cand; break; }
+        }
+        a.gpb = gpb; a.slices = 1;
+        const size_t smem = smem_plan(nt, g.cols, g.nc, g.nsg, gpb).total;
+        if (smem > kSmemBudget) return cudaErrorInvalidValue;
+        const uint32_t grid = (g.ngroups + gpb - 1) / gpb;
+        switch (g.fmt) {
+            case FMT_BP4: e = launch_small<FMT_BP4>(stream, a, nt, smem, grid); break;
+            case FMT_BP5: e = launch_small<FMT_BP5>(stream, a, nt, smem, grid); break;
+            case FMT_BP6: e = launch_small<FMT_BP6>(stream, a, nt, smem, grid); break;
+            case FMT_NF4: e = launch_small<FMT_NF4G>(stream, a, nt, smem, grid); break;
+            case FMT_NF3: e = launch_small<FMT_NF3>(stream, a, nt, smem, grid); break;
+            default: return cudaErrorNotSupported;
+        }
     }
     if (e == cudaSuccess && launches) *launches = 1;
     return e;

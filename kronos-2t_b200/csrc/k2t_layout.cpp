@@ -107,7 +107,6 @@ inline void put_u16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)(v & 0xFF); p[1] =
 bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &err) {
     std::memset(&g, 0, sizeof g);
     if (d.rows == 0 || d.cols == 0 || d.cols % 64 != 0) { err = "matrix: cols must be a positive multiple of 64"; return false; }
-    if (!d.data0) { err = "matrix: data0 is NULL"; return false; }
     g.rows = d.rows; g.cols = d.cols; g.nc = d.cols / 64; g.ngroups = (d.rows + 7) / 8;
     const size_t ns = (d.rows + STRIPE - 1) / STRIPE;
     if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
@@ -116,7 +115,7 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         g.sgc = 1; g.nsg = g.nc; g.max_odd = (1 << d.bits) - 1;
         g.rec_bytes = 256 + 64 * (d.bits - 4);
         size_t want0 = ns * (d.cols / 8) * d.bits * STRIPE, want1 = ns * g.nc * STRIPE * 2;
-        if (d.len0 != want0 || d.len1 != want1 || !d.data1) { err = "bipolar matrix: plane/scale byte counts do not match rows x cols"; return false; }
+        if (d.len0 != want0 || d.len1 != want1 || !d.data0 || !d.data1) { err = "bipolar matrix: plane/scale byte counts do not match rows x cols"; return false; }
         g.file_bytes = want0 + want1;
     } else if (d.kind == KRONOS_CUDA_MATRIX_NF) {
         if (d.bits < 2 || d.bits > 5) { err = "NF matrix: bits must be 2..5"; return false; }
@@ -127,11 +126,32 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         size_t cb = nf_chunk_bytes(d.bits);
         size_t want0 = (ns / 2) * ((size_t)g.nsg * 64 + (size_t)g.nc * 2 * cb);
         size_t want1 = (ns & 1) * ((size_t)g.nsg * 32 + (size_t)g.nc * cb);
-        if (d.len0 != want0 || d.len1 != want1 || (want1 && !d.data1)) { err = "NF matrix: pair/tail stream byte counts do not match rows x cols"; return false; }
+        if (d.len0 != want0 || d.len1 != want1 || (want0 && !d.data0) || (want1 && !d.data1)) { err = "NF matrix: pair/tail stream byte counts do not match rows x cols"; return false; }
         if (d.bits == 5) {
             for (int m = 0; m < 16; ++m) { g.codebook32[15 - m] = (int8_t)(-d.codebook[m]); g.codebook32[16 + m] = d.codebook[m]; }
-        } else if (d.bits >= 3) {
+        } else if (d.bits == 3) {
             std::memcpy(g.codebook32, d.codebook, 16);
+        } else if (d.bits == 4) {
+            // rank of every centroid in ascending order (stable), sorted device codebook
+            for (int i = 0; i < 16; ++i) {
+                int rank = 0;
+                for (int j = 0; j < 16; ++j)
+                    if (d.codebook[j] < d.codebook[i] || (d.codebook[j] == d.codebook[i] && j < i)) ++rank;
+                g.nf4_rank[i] = (uint8_t)rank;
+                g.codebook32[rank] = d.codebook[i];
+            }
+            // two-table decode: value = hi[l] + off for ranks 8..15, = off - lo[l] for ranks 0..7, tables in 0..127
+            int max_lo = g.codebook32[7], min_lo = g.codebook32[0], min_hi = g.codebook32[8], max_hi = g.codebook32[15];
+            int off_min = std::max(max_lo, max_hi - 127), off_max = std::min(min_hi, min_lo + 127);
+            if (off_min <= off_max) {
+                int off = std::min(std::max(0, off_min), off_max);
+                g.nf4_split_ok = 1;
+                g.nf4_offset = off;
+                for (int l = 0; l < 8; ++l) {
+                    g.nf4_hi[l] = (uint8_t)(g.codebook32[8 + l] - off);
+                    g.nf4_lo[l] = (uint8_t)(off - g.codebook32[l]);
+                }
+            }
         }
         g.file_bytes = want0 + want1 + 16;
     } else {
@@ -165,7 +185,7 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
                 for (uint32_t c = 0; c < g.nc; ++c) {
                     uint8_t *rec = out + ((size_t)grp * g.nc + c) * g.rec_bytes;
                     if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
-                        put_u16(scales + ((size_t)r_dst * g.nsg + c) * 2, fv.bp_scale(r, c));
+                        put_u16(scales + (((size_t)grp * g.nsg + c) * 8 + rr) * 2, fv.bp_scale(r, c));
                         for (uint32_t col = 0; col < 64; ++col) {
                             uint32_t u = fv.bp_code(r, c * 64 + col);
                             uint32_t cc = col % 32, k = cc % 8;
@@ -183,7 +203,7 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
                     }
                     const uint8_t *blk, *sc;
                     fv.nf_ptrs(r / STRIPE, c, blk, sc);
-                    if (c % g.sgc == 0) put_u16(scales + ((size_t)r_dst * g.nsg + c / g.sgc) * 2, fv.nf_scale(r, c));
+                    if (c % g.sgc == 0) put_u16(scales + (((size_t)grp * g.nsg + c / g.sgc) * 8 + rr) * 2, fv.nf_scale(r, c));
                     if (d.bits == 2) {
                         for (uint32_t eb8 = 0; eb8 < 8; ++eb8) {
                             uint8_t tpl, sgn;
@@ -207,6 +227,7 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
                     } else {  // 4 or 5 bits
                         for (uint32_t col = 0; col < 64; ++col) {
                             uint32_t idx = fv.nf_index(blk, lane, col);
+                            if (d.bits == 4) idx = g.nf4_rank[idx];
                             uint32_t cc = col % 32, nib = cc % 8;
                             rec[(col / 32) * 128 + rr * 16 + (cc / 8) * 4 + nib / 2] |= (uint8_t)((idx & 0x0F) << (4 * (nib % 2)));
                             if (d.bits == 5) {

@@ -19,7 +19,11 @@
 //        three bits of nibble (col%8) of word col/8; column 48+t (t<16) has index bit j in bit 3 of
 //        nibble t%8 of word 3*(t/8) + j
 //   E8Q2: 128 B: row r at r*16, byte 2*blk = template byte, 2*blk+1 = sign byte of columns 8*blk..8*blk+7
-// Scales: one bf16 per (row, scale group), row-major [groups*8][nsg], after the records.
+// Scales: one bf16 per (row, scale group), stored [group][scale group][row in group] after the
+// records, so the eight lanes of a quarter-warp read 16 contiguous bytes per scale group.
+// NF4 indices are re-encoded at upload: the 16 centroids are sorted ascending and the stored nibble is
+// the rank of the centroid, so bit 3 of a nibble separates the eight largest from the eight smallest
+// centroids (identity for the sorted codebooks the reference compiler emits).
 // Rows beyond `rows` are padding: zero codes / index 0 and zero scales, never written to the output.
 #pragma once
 #include <cstddef>
@@ -37,7 +41,12 @@ struct MatrixGeom {
     Format fmt;
     uint32_t rows, cols, nc, sgc, nsg, ngroups, rec_bytes;
     int32_t max_odd;          // 2^B - 1 for bit-planes, 0 otherwise
-    int8_t codebook32[32];    // expanded codebook (NF), zero otherwise
+    int8_t codebook32[32];    // expanded codebook (NF; NF4: sorted ascending), zero otherwise
+    uint8_t nf4_rank[16];     // NF4: file index -> device nibble
+    int32_t nf4_split_ok;     // NF4: 1 when the two-table decode applies (see k2t_gemv.cu)
+    int32_t nf4_offset;       // NF4 two-table decode: centroid = table value + offset
+    uint8_t nf4_hi[8];        // codebook32[8+l] - offset   (0..127)
+    uint8_t nf4_lo[8];        // offset - codebook32[l]     (0..127)
     size_t rec_total;         // ngroups * nc * rec_bytes
     size_t scale_total;       // ngroups * 8 * nsg * 2
     size_t file_bytes;        // bytes of the matrix in the reference file format

@@ -91,7 +91,7 @@ def image_rows(fmt, image, rows, cols, nsg, cb_words=None):
     """Decodes a whole device image into weight bytes [rows, cols] and bf16 scales [rows, nsg]."""
     nc, ng, rb = cols // 64, (rows + 7) // 8, REC_BYTES[fmt]
     recs = image[: ng * nc * rb].reshape(ng, nc, rb)
-    scales = image[ng * nc * rb:].view("<u2").reshape(ng * 8, nsg)
+    scales = image[ng * nc * rb:].view("<u2").reshape(ng, nsg, 8).transpose(0, 2, 1).reshape(ng * 8, nsg)
     out = np.zeros((ng * 8, cols), np.int16)
     for g in range(ng):
         for c in range(nc):
@@ -124,7 +124,9 @@ def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
     cb = m.codebook.copy()
     if bits == 4:
         cb = np.array([-120, -90, -70, -50, -33, -20, -9, -1, 3, 14, 29, 47, 60, 80, 101, 127], np.int8)
-    cb_words = _words(cb.tobytes())
+    # NF4 indices are re-encoded to the rank of their centroid: the device codebook is the sorted one
+    cb_dev = np.sort(cb[:16]) if bits == 4 else cb
+    cb_words = _words(cb_dev.tobytes())
     image = k2.matrix_image(k2.nf_desc(rows, cols, bits, sgc, cb, m.pair, m.tail))
     nsg = -(-(cols // 64) // sgc)
     vals, scales = image_rows(f"nf{bits}", image, rows, cols, nsg, cb_words)
@@ -133,6 +135,49 @@ def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
     for r in range(rows):
         assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
     assert not scales[rows:].any()
+
+
+def nf4_two_table_values(rec, r, cb_sorted):
+    """cell_dot<FMT_NF4>'s decode: centroid = hi[l] + off where index bit 3 is set, off - lo[l] elsewhere,
+    each table looked up with one prmt whose selector has bit 3 set for the lanes that must yield 0."""
+    cb = cb_sorted.astype(int)
+    off_min, off_max = max(cb[7], cb[15] - 127), min(cb[8], cb[0] + 127)
+    assert off_min <= off_max
+    off = min(max(0, off_min), off_max)
+    hi, lo = [int(cb[8 + l] - off) for l in range(8)], [int(off - cb[l]) for l in range(8)]
+    assert all(0 <= v <= 127 for v in hi + lo)
+    tab = _words(bytes(hi + lo))
+    words = _words(rec[r * 16: r * 16 + 16]) + _words(rec[128 + r * 16: 128 + r * 16 + 16])
+    vals = []
+    for x in words:
+        y = x ^ 0x88888888
+        for sel_hi, sel_lo in ((y, x), (y >> 16, x >> 16)):
+            up = np.array([prmt(tab[0], tab[1], sel_hi)], "<u4").view(np.uint8).astype(int)
+            dn = np.array([prmt(tab[2], tab[3], sel_lo)], "<u4").view(np.uint8).astype(int)
+            vals.extend((up - dn).tolist())
+    # every column got exactly one of the two tables; adding the offset restores the centroid
+    return np.array(vals) + off
+
+
+@pytest.mark.parametrize("cb", [
+    [-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127],      # reference default
+    [29, -90, -70, 127, -33, -20, -9, -1, 3, 14, -120, 47, 60, 80, 101, -50],      # unsorted, asymmetric
+    [100, 101, 102, 103, 104, 105, 106, 107, 108, 109, 110, 111, 112, 113, 114, 115],  # needs an offset
+])
+def test_nf4_two_table_decode(oracle, cb):
+    rows, cols = 16, 128
+    cb = np.array(cb, np.int8)
+    rng = np.random.Generator(np.random.PCG64(11))
+    idx = rng.integers(0, 16, (rows, cols), dtype=np.uint8)
+    sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, 1)).astype(np.uint16)
+    m = oracle.nf_pack(idx, sc, 4, 1, cb)
+    image = k2.matrix_image(k2.nf_desc(rows, cols, 4, 1, cb, m.pair, m.tail))
+    recs = image[: 2 * 2 * 256].reshape(2, 2, 256)
+    for g in range(2):
+        for c in range(2):
+            for r in range(8):
+                got = nf4_two_table_values(recs[g, c], r, np.sort(cb))
+                assert np.array_equal(got, cb.astype(int)[idx[g * 8 + r, c * 64:(c + 1) * 64]])
 
 
 def test_gate_up_interleave_image(oracle):
@@ -148,6 +193,7 @@ def test_gate_up_interleave_image(oracle):
     n = oracle.nf_quantize_rtn(normal(4, (rows, cols), 0.02), 4, 2)
     nd = k2.nf_desc(rows, cols, 4, 2, n.codebook, n.pair, n.tail)
     cbw = _words(n.codebook.tobytes())
+    cbw = _words(np.sort(n.codebook).tobytes())
     plain, _ = image_rows("nf4", k2.matrix_image(nd), rows, cols, 1, cbw)
     inter, _ = image_rows("nf4", k2.matrix_image(nd, gate_up_interleave=True), rows, cols, 1, cbw)
     assert np.array_equal(inter[64:128], plain[128:192]) and np.array_equal(inter[128:192], plain[64:128])
@@ -157,7 +203,7 @@ def test_malformed_descriptors_are_rejected(oracle):
     m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
     L = k2.load_library()
     good = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
-    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 16 * 2 * 1 * 16 + 16 * 2
+    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 2 * 256 + 2 * 8 * 2
     for kw in ({"cols": 65}, {"bits": 7}, {"rows": 0}, {"kind": 1}, {"len0": 5}):
         bad = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
         for key, val in kw.items():

@@ -107,10 +107,17 @@ def test_nf_gemv_bit_exact(ctx, oracle, bits, sgc, rows, cols):
     _check_gemv(ctx, oracle, m, normal(rows + cols, cols))
 
 
-def test_nf4_general_codebook(ctx, oracle):
-    cb = np.array([-120, -90, -70, -50, -33, -20, -9, -1, 3, 14, 29, 47, 60, 80, 101, 127], np.int8)
-    m = random_nf(oracle, 5, 96, 256, 4, 2, cb)
-    _check_gemv(ctx, oracle, m, normal(6, 256))
+@pytest.mark.parametrize("cb", [
+    [-120, -90, -70, -50, -33, -20, -9, -1, 3, 14, 29, 47, 60, 80, 101, 127],          # asymmetric, sorted
+    [29, -90, -70, 127, -33, -20, -9, -1, 3, 14, -120, 47, 60, 80, 101, -50],          # unsorted: indices re-ranked at upload
+    [100, 101, 102, 103, 104, 105, 106, 107, 108, 109, 110, 111, 112, 113, 114, 115],  # two-table decode needs an offset
+    [-127, -100, -50, 0, 20, 40, 60, 80, 81, 82, 83, 84, 85, 86, 87, 127],             # lower half spans > 127: general decode
+])
+@pytest.mark.parametrize("rows,cols", [(96, 256), (1024, 2048)])
+def test_nf4_arbitrary_codebooks(ctx, oracle, cb, rows, cols):
+    m = random_nf(oracle, 5, rows, cols, 4, 2, np.array(cb, np.int8))
+    _check_gemv(ctx, oracle, m, normal(6, (2, cols)))
+    _check_gemv(ctx, oracle, m, normal(7, cols))
 
 
 @pytest.mark.parametrize("n_tok", [2, 3, 4, 7, 8, 15])
