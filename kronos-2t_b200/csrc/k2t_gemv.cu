@@ -10,13 +10,12 @@
 // The integer dots are computed by all lanes in parallel; the fp32 chain always runs per row in
 // ascending chunk order, so outputs are bit-identical to the reference order.
 //
-// Batch-1 kernel (gemv1_kernel).  A quarter-warp (8 lanes = the 8 rows of a group) walks the records
-// of its group; with S K-slices, slice s takes chunks s, s+S, s+2S, ...  Each 128-bit load of a
-// quarter-warp covers one 128-byte line, a warp step reads up to 1 KiB of contiguous weights, and
-// every lane keeps UNROLL records in flight (registers) while it computes the previous batch.
-//   S == 1 : one lane owns a row for all K; the fp32 chain runs in registers as chunks arrive.
-//   S  > 1 : lanes park (v, w_scale) per chunk in shared memory; after a CTA barrier one lane per
-//            row runs the chain.  Used when rows alone do not provide enough warps.
+// Batch-1 kernel (gemv1_kernel).  One row group (8 rows) is served by W warps = 4W quarter-warps;
+// quarter-warp j owns the j-th contiguous slice of the chunks and its 8 lanes are the 8 rows, so each
+// 128-bit access of a quarter-warp covers one 128-byte line and each quarter-warp streams one
+// contiguous byte range.  Lanes park (v, w_scale) per chunk in a private shared-memory column; the
+// fp32 chain then runs slice after slice, handed from quarter-warp to quarter-warp with a shuffle and
+// from warp to warp through shared memory, which keeps the reference's ascending-chunk order exactly.
 // Activations (int8, <= 18.5 KiB) are staged once per CTA in shared memory and read as broadcasts.
 #include "k2t_device.cuh"
 #include "k2t_kernels.h"
@@ -32,7 +31,7 @@ struct GemvArgs {
     float *out;
     int32_t *int_dots;
     size_t out_stride;
-    uint32_t rows, cols, nc, nsg, sgc, sgc_shift, ngroups, rec_bytes, n_tok, gpb, slices;   // sgc_shift: log2(sgc) or 32
+    uint32_t rows, cols, nc, nsg, sgc, sgc_shift, ngroups, rec_bytes, n_tok, gpb, wpg;   // sgc_shift: log2(sgc) or 32
     int32_t max_odd;
     int32_t nf4_offset;
     uint32_t cb[8];    // expanded codebook, 4 centroids per word (NF4: sorted ascending)
@@ -202,101 +201,162 @@ __host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~(size_t
 // ------------------------------------------------------------------------------------------------
 // batch-1 kernel
 // ------------------------------------------------------------------------------------------------
-constexpr int G1_THREADS = 128;   // 16 quarter-warps
-constexpr int G1_UNROLL = 4;
+// Weight records travel global -> shared memory with cp.async (16-byte LDGSTS, L1 bypass).  Every
+// quarter-warp owns a ring of NBATCH batches of BATCH slots; a slot holds one record plus the 16-byte
+// granule with the eight bf16 scales of its rows.  One commit group per batch, retired strictly
+// oldest-first by `cp.async.wait_group NBATCH-1`.  Unlike loads into registers, whose completion is
+// tracked by a handful of per-warp scoreboards shared between old and new requests, this keeps
+// (NBATCH-1)*BATCH .. NBATCH*BATCH records per quarter-warp in flight for the whole stream and costs
+// no registers.
+constexpr int BATCH = 2;
+constexpr int NBATCH = 3;
 
-struct Smem1 { size_t xs, xsum, v, total; };
-__host__ __device__ inline Smem1 smem1_plan(uint32_t cols, uint32_t nc, uint32_t gpb, bool split) {
+template <int FMT> __host__ __device__ constexpr uint32_t slot_bytes() { return RawWords<FMT>::N * 32 + 16; }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int FMT>
+__device__ __forceinline__ void read_slot(Raw<FMT> &o, const uint8_t *slot, uint32_t r) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(slot);
+    uint4 a = p[r];
+    o.w[0] = a.x; o.w[1] = a.y; o.w[2] = a.z; o.w[3] = a.w;
+    if (FMT == FMT_NF3) {
+        uint2 h = reinterpret_cast<const uint2 *>(slot + 128)[r];
+        o.w[4] = h.x; o.w[5] = h.y;
+        return;
+    }
+    uint4 b = p[8 + r];
+    o.w[4] = b.x; o.w[5] = b.y; o.w[6] = b.z; o.w[7] = b.w;
+    if (FMT == FMT_BP5) {
+        uint2 h = reinterpret_cast<const uint2 *>(slot + 256)[r];
+        o.w[8] = h.x; o.w[9] = h.y;
+    }
+    if (FMT == FMT_BP6) {
+        uint4 h = p[16 + r];
+        o.w[8] = h.x; o.w[9] = h.y; o.w[10] = h.z; o.w[11] = h.w;
+    }
+}
+
+struct Smem1 { size_t xa, f, v, ring, total; };
+__host__ __device__ inline Smem1 smem1_plan(uint32_t cols, uint32_t nc, uint32_t threads, uint32_t n_max, uint32_t slot) {
     Smem1 p;
-    p.xs = align16(cols);
-    p.xsum = p.xs + align16((size_t)nc * 4);
-    p.v = p.xsum + align16((size_t)nc * 4);
-    p.total = p.v + (split ? (size_t)gpb * nc * 8 * 8 : 0);
+    p.xa = align16(cols);                                   // {xs, xsum} pairs after the int8 activations
+    p.f = p.xa + align16((size_t)nc * 8);                   // chain hand-off between the warps of a group
+    p.v = p.f + align16((size_t)(threads / 32) * 8 * 4);
+    p.ring = p.v + (size_t)n_max * threads * 8;             // private (v, w_scale) columns
+    p.total = p.ring + (size_t)(threads / 8) * NBATCH * BATCH * slot;
     return p;
 }
 
-template <int FMT, bool SPLIT>
-__global__ void __launch_bounds__(G1_THREADS) gemv1_kernel(const GemvArgs a) {
+// blockDim.x = 32 * wpg * gpb: gpb row groups per CTA, each served by wpg warps (4*wpg K-slices).
+template <int FMT>
+__global__ void __launch_bounds__(256) gemv1_kernel(const GemvArgs a) {
+    constexpr uint32_t SLOT = slot_bytes<FMT>();
+    constexpr uint32_t GRANULES = RawWords<FMT>::N * 2;     // 16-byte pieces of one record
     extern __shared__ __align__(16) uint8_t smem[];
-    const Smem1 sp = smem1_plan(a.cols, a.nc, a.gpb, SPLIT);
+    const uint32_t threads = blockDim.x;
+    const uint32_t W = a.wpg, n_sl = 4 * W;
+    const uint32_t base = a.nc / n_sl, rem = a.nc % n_sl;
+    const uint32_t n_max = base + (rem != 0);               // CTA-uniform trip count
+    const Smem1 sp = smem1_plan(a.cols, a.nc, threads, n_max, SLOT);
     int8_t *s_xq = reinterpret_cast<int8_t *>(smem);
-    float *s_xs = reinterpret_cast<float *>(smem + sp.xs);
-    int32_t *s_xsum = reinterpret_cast<int32_t *>(smem + sp.xsum);
+    float2 *s_xa = reinterpret_cast<float2 *>(smem + sp.xa);   // .x = activation scale, .y = bits of the int32 chunk sum
+    float *s_f = reinterpret_cast<float *>(smem + sp.f);
     float2 *s_v = reinterpret_cast<float2 *>(smem + sp.v);
 
-    const uint32_t tid = threadIdx.x, r = tid & 7, qw = tid >> 3;
-    const uint32_t S = SPLIT ? a.slices : 1;
-    const uint32_t gl = SPLIT ? qw / S : qw, s = SPLIT ? qw % S : 0;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, r = lane & 7, q = lane >> 3;
+    const uint32_t gl = warp / W, wg = warp % W;
     const uint32_t g = blockIdx.x * a.gpb + gl;
     const bool live = g < a.ngroups;
-    const uint32_t n_i = live ? (a.nc - s + S - 1) / S : 0;     // chunks s, s+S, ... of this lane's slice
-    const uint8_t *rec = a.rec + ((size_t)g * a.nc + s) * a.rec_bytes;
-    const size_t rec_step = (size_t)S * a.rec_bytes;
-    const uint16_t *wsp = a.scales + (size_t)g * a.nsg * 8 + r;
+    const uint32_t sl = wg * 4 + q;                             // this quarter-warp's slice of the chunks
+    const uint32_t c0 = sl * base + min(sl, rem);
+    const uint32_t n_i = live ? base + (sl < rem) : 0;
+    const uint8_t *rec = a.rec + ((size_t)g * a.nc + c0) * a.rec_bytes + r * 16;
+    const uint16_t *ws_g = a.scales + (size_t)g * a.nsg * 8;
+    uint8_t *ring = smem + sp.ring + (size_t)(tid >> 3) * (NBATCH * BATCH) * SLOT;
+    const uint32_t ring_sa = (uint32_t)__cvta_generic_to_shared(ring) + r * 16;
 
-    // first batch of weight records goes out before anything else: its latency covers the staging
-    Raw<FMT> cur[G1_UNROLL];
-    uint16_t cur_ws[G1_UNROLL];
+    auto issue_batch = [&](uint32_t i0, uint32_t slot0) {     // records i0..i0+BATCH-1 -> slots slot0..
 #pragma unroll
-    for (int k = 0; k < G1_UNROLL; ++k)
-        if ((uint32_t)k < n_i) {
-            load_raw<FMT>(cur[k], rec + k * rec_step, r);
-            cur_ws[k] = __ldg(wsp + (size_t)scale_group_of(a, s + k * S) * 8);
+        for (uint32_t k = 0; k < BATCH; ++k) {
+            const uint32_t i = i0 + k;
+            if (i < n_i) {
+                const uint8_t *src = rec + (size_t)i * a.rec_bytes;
+                const uint32_t dst = ring_sa + (slot0 + k) * SLOT;
+#pragma unroll
+                for (uint32_t j = 0; j < (GRANULES + 7) / 8; ++j)
+                    if (j * 8 + r < GRANULES) cp_async16(dst + j * 128, src + j * 128);
+                if (r == 0) cp_async16(dst + GRANULES * 16, ws_g + (size_t)scale_group_of(a, c0 + i) * 8);
+            }
         }
+        cp_async_commit();          // one group per batch, possibly empty: keeps the group count in step
+    };
 
-    for (uint32_t i = tid; i < a.cols / 16; i += G1_THREADS)
-        reinterpret_cast<int4 *>(s_xq)[i] = reinterpret_cast<const int4 *>(a.xq)[i];
-    for (uint32_t i = tid; i < a.nc; i += G1_THREADS) {
-        s_xs[i] = a.xs[i];
-        s_xsum[i] = a.xsum != nullptr ? a.xsum[i] : 0;
-    }
+    // the first NBATCH batches go out before anything else: their latency covers the staging below
+#pragma unroll
+    for (uint32_t b = 0; b < NBATCH; ++b) issue_batch(b * BATCH, b * BATCH);
+
+    for (uint32_t i = tid; i < a.cols / 16; i += threads)
+        reinterpret_cast<int4 *>(s_xq)[i] = __ldg(reinterpret_cast<const int4 *>(a.xq) + i);
+    for (uint32_t i = tid; i < a.nc; i += threads)
+        s_xa[i] = make_float2(__ldg(a.xs + i), __int_as_float(a.xsum != nullptr ? __ldg(a.xsum + i) : 0));
     __syncthreads();
 
     const uint32_t row = g * 8 + r;
-    float f = 0.0f;
-    for (uint32_t i0 = 0; i0 < n_i; i0 += G1_UNROLL) {
-        Raw<FMT> nxt[G1_UNROLL];
-        uint16_t nxt_ws[G1_UNROLL];
+    float2 *my_v = s_v + tid;
+    uint32_t slot0 = 0;
+    for (uint32_t i0 = 0; i0 < n_max; i0 += BATCH) {
+        cp_async_wait<NBATCH - 1>();                // this thread's share of the oldest batch has landed
+        __syncwarp();                               // ... and so have the scale granules lane 0 fetched
 #pragma unroll
-        for (int k = 0; k < G1_UNROLL; ++k) {
-            const uint32_t i = i0 + G1_UNROLL + k;
-            if (i < n_i) {
-                load_raw<FMT>(nxt[k], rec + (size_t)i * rec_step, r);
-                nxt_ws[k] = __ldg(wsp + (size_t)scale_group_of(a, s + i * S) * 8);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < G1_UNROLL; ++k) {
+        for (uint32_t k = 0; k < BATCH; ++k) {
             const uint32_t i = i0 + k;
             if (i < n_i) {
-                const uint32_t c = s + i * S;
-                const int xsum_c = s_xsum[c];
-                const int acc = cell_dot<FMT>(cur[k], a, reinterpret_cast<const int4 *>(s_xq + (size_t)c * 64), xsum_c);
+                const uint8_t *slot = ring + (slot0 + k) * SLOT;
+                Raw<FMT> w;
+                read_slot<FMT>(w, slot, r);
+                const float ws = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(slot + GRANULES * 16)[r]);
+                const uint32_t c = c0 + i;
+                const float2 xa = s_xa[c];
+                const int xsum_c = __float_as_int(xa.y);
+                const int acc = cell_dot<FMT>(w, a, reinterpret_cast<const int4 *>(s_xq + (size_t)c * 64), xsum_c);
                 const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum_c : acc;
-                const float sx = s_xs[c];
-                const float v = __fmul_rn(__int2float_rn(dot), sx);
-                const float ws = bf16_bits_to_f32(cur_ws[k]);
-                if (SPLIT) s_v[((size_t)gl * a.nc + c) * 8 + r] = make_float2(v, ws);
-                else if (sx != 0.0f) f = __fmaf_rn(v, ws, f);
+                my_v[(size_t)i * threads] = make_float2(__fmul_rn(__int2float_rn(dot), xa.x), ws);
                 if (a.int_dots != nullptr && row < a.rows) a.int_dots[(size_t)row * a.nc + c] = dot;
             }
         }
-#pragma unroll
-        for (int k = 0; k < G1_UNROLL; ++k) { cur[k] = nxt[k]; cur_ws[k] = nxt_ws[k]; }
+        __syncwarp();                               // every lane is done with the batch before it is refilled
+        issue_batch(i0 + NBATCH * BATCH, slot0);
+        slot0 = slot0 + BATCH == NBATCH * BATCH ? 0 : slot0 + BATCH;
     }
+    cp_async_wait<0>();
 
-    if (SPLIT) {
-        __syncthreads();
-        if (s == 0 && live) {      // ordered fp32 chain: one lane per row
-            const float2 *vv = s_v + (size_t)gl * a.nc * 8 + r;
-#pragma unroll 4
-            for (uint32_t c = 0; c < a.nc; ++c) {
-                const float2 t = vv[(size_t)c * 8];
-                if (s_xs[c] != 0.0f) f = __fmaf_rn(t.x, t.y, f);
+    // ordered fp32 chain: slice after slice, quarter-warp to quarter-warp by shuffle, warp to warp via s_f
+    float f = 0.0f;
+    for (uint32_t round = 0; round < W; ++round) {
+        if (wg == round) {
+            if (round > 0) f = s_f[gl * 8 + r];
+#pragma unroll
+            for (uint32_t qq = 0; qq < 4; ++qq) {
+                if (q == qq)
+                    for (uint32_t i = 0; i < n_i; ++i) {
+                        const float2 t = my_v[(size_t)i * threads];
+                        if (s_xa[c0 + i].x != 0.0f) f = __fmaf_rn(t.x, t.y, f);
+                    }
+                const float up = __shfl_up_sync(0xffffffffu, f, 8);
+                if (q == qq + 1) f = up;
+            }
+            if (q == 3 && live) {
+                if (round + 1 == W) { if (row < a.rows) a.out[row] = f; }
+                else s_f[gl * 8 + r] = f;
             }
         }
+        if (W > 1) __syncthreads();
     }
-    if (s == 0 && live && row < a.rows) a.out[row] = f;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -409,15 +469,14 @@ static cudaError_t allow_big_smem(K kernel, size_t smem) {
 }
 
 template <int FMT>
-static cudaError_t launch_gemv1(cudaStream_t stream, const GemvArgs &a, bool split, size_t smem, uint32_t grid) {
-    cudaError_t e;
-    if (split) {
-        if ((e = allow_big_smem(gemv1_kernel<FMT, true>, smem)) != cudaSuccess) return e;
-        gemv1_kernel<FMT, true><<<grid, G1_THREADS, smem, stream>>>(a);
-    } else {
-        if ((e = allow_big_smem(gemv1_kernel<FMT, false>, smem)) != cudaSuccess) return e;
-        gemv1_kernel<FMT, false><<<grid, G1_THREADS, smem, stream>>>(a);
-    }
+static cudaError_t launch_gemv1(cudaStream_t stream, const GemvArgs &a, uint32_t grid) {
+    const uint32_t threads = 32 * a.wpg * a.gpb, n_sl = 4 * a.wpg;
+    const uint32_t n_max = a.nc / n_sl + (a.nc % n_sl != 0);
+    const size_t smem = smem1_plan(a.cols, a.nc, threads, n_max, slot_bytes<FMT>()).total;
+    if (smem > kSmemBudget) return cudaErrorInvalidValue;
+    cudaError_t e = allow_big_smem(gemv1_kernel<FMT>, smem);
+    if (e != cudaSuccess) return e;
+    gemv1_kernel<FMT><<<grid, threads, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
@@ -471,24 +530,20 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
     }
     cudaError_t e;
     if (n_tok == 1) {
-        // K-slices: enough warps to keep ~8 per SM in flight, at least two chunks per slice
-        const uint32_t want_warps = 8u * (uint32_t)sm_count;
-        uint32_t S = 1;
-        while (S < 16 && (g.ngroups * S) / 4 < want_warps && g.nc / (2 * S) >= 2) S *= 2;
-        const bool split = S > 1;
-        a.slices = S;
-        a.gpb = (G1_THREADS / 8) / S;
-        const size_t smem = smem1_plan(g.cols, g.nc, a.gpb, split).total;
-        if (smem > kSmemBudget) return cudaErrorInvalidValue;
+        // warps per row group: enough warps to keep ~24 per SM busy, at least one chunk per K-slice
+        const uint32_t want_warps = 24u * (uint32_t)sm_count;
+        uint32_t W = 1;
+        while (W < 8 && g.ngroups * W < want_warps && 8 * W <= g.nc) W *= 2;
+        a.wpg = W;
+        a.gpb = W >= 4 ? 1 : 4 / W;
         const uint32_t grid = (g.ngroups + a.gpb - 1) / a.gpb;
         const bool nf4_fast = g.fmt == FMT_NF4 && g.nf4_split_ok && (g.nf4_offset == 0 || xsum != nullptr);
         switch (g.fmt) {
-            case FMT_BP4: e = launch_gemv1<FMT_BP4>(stream, a, split, smem, grid); break;
-            case FMT_BP5: e = launch_gemv1<FMT_BP5>(stream, a, split, smem, grid); break;
-            case FMT_BP6: e = launch_gemv1<FMT_BP6>(stream, a, split, smem, grid); break;
-            case FMT_NF4: e = nf4_fast ? launch_gemv1<FMT_NF4>(stream, a, split, smem, grid)
-                                       : launch_gemv1<FMT_NF4G>(stream, a, split, smem, grid); break;
-            case FMT_NF3: e = launch_gemv1<FMT_NF3>(stream, a, split, smem, grid); break;
+            case FMT_BP4: e = launch_gemv1<FMT_BP4>(stream, a, grid); break;
+            case FMT_BP5: e = launch_gemv1<FMT_BP5>(stream, a, grid); break;
+            case FMT_BP6: e = launch_gemv1<FMT_BP6>(stream, a, grid); break;
+            case FMT_NF4: e = nf4_fast ? launch_gemv1<FMT_NF4>(stream, a, grid) : launch_gemv1<FMT_NF4G>(stream, a, grid); break;
+            case FMT_NF3: e = launch_gemv1<FMT_NF3>(stream, a, grid); break;
             default: return cudaErrorNotSupported;
         }
     } else {
@@ -498,7 +553,7 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
             if ((g.ngroups + cand - 1) / cand >= (uint32_t)(2 * sm_count) &&
                 smem_plan(nt, g.cols, g.nc, g.nsg, cand).total <= 64 * 1024) { gpb = cand; break; }
         }
-        a.gpb = gpb; a.slices = 1;
+        a.gpb = gpb; a.wpg = 1;
         const size_t smem = smem_plan(nt, g.cols, g.nc, g.nsg, gpb).total;
         if (smem > kSmemBudget) return cudaErrorInvalidValue;
         const uint32_t grid = (g.ngroups + gpb - 1) / gpb;
