@@ -83,13 +83,17 @@ int32_t kronos_cuda_set_stream(KronosCudaContext *ctx, void *cuda_stream);
  * RealLlamaEngine::repack_sdot (real_llm.rs:3657-3702). */
 KronosCudaMatrix *kronos_cuda_matrix_upload(KronosCudaContext *ctx, const KronosCudaMatrixDesc *desc,
                                             uint32_t flags);
+/* A second, independent HBM copy of an uploaded matrix (device-to-device).  Benchmarks rotate over
+ * such copies so that consecutive launches never find their weights in L2.  No counterpart in the
+ * reference. */
+KronosCudaMatrix *kronos_cuda_matrix_clone(KronosCudaContext *ctx, const KronosCudaMatrix *m);
 void kronos_cuda_matrix_free(KronosCudaContext *ctx, KronosCudaMatrix *m);
 /* Bytes the matrix occupies in the reference's file format (the "algorithmic" weight bytes)
  * and in HBM. */
 size_t kronos_cuda_matrix_file_bytes(const KronosCudaMatrix *m);
 size_t kronos_cuda_matrix_device_bytes(const KronosCudaMatrix *m);
 
-/* Host-only diagnostic: writes the HBM image kronos_cuda_matrix_upload would copy (records, then
+/* Host-only diagnostic: writes the HBM image kronos_cuda_matrix_upload would copy (code planes, then
  * bf16 scales) into `out` and returns its size in bytes; with out == NULL or cap too small nothing is
  * written.  Needs no GPU.  Returns 0 for a malformed descriptor.  No counterpart in the reference. */
 size_t kronos_cuda_matrix_image(const KronosCudaMatrixDesc *desc, uint32_t flags, uint8_t *out, size_t cap);

@@ -170,7 +170,7 @@ KronosCudaMatrix *kronos_cuda_matrix_upload(KronosCudaContext *ctx, const Kronos
     if (!make_current(ctx)) return nullptr;
     std::vector<uint8_t> image;
     try {
-        image.resize(g.rec_total + g.scale_total);
+        image.resize(g.image_bytes());
     } catch (...) { fail(ctx, "matrix_upload: out of host memory"); return nullptr; }
     unsigned hw = std::max(1u, std::thread::hardware_concurrency());
     repack_matrix(*desc, g, interleave, image.data(), std::min(hw, 16u));
@@ -186,8 +186,32 @@ KronosCudaMatrix *kronos_cuda_matrix_upload(KronosCudaContext *ctx, const Kronos
         delete m;
         return nullptr;
     }
-    m->dm.d_rec = m->dm.d_base;
-    m->dm.d_scales = reinterpret_cast<const uint16_t *>(m->dm.d_base + g.rec_total);
+    m->dm.d_a = m->dm.d_base;
+    m->dm.d_b = m->dm.d_base + g.plane_a;
+    m->dm.d_scales = reinterpret_cast<const uint16_t *>(m->dm.d_base + g.plane_a + g.plane_b);
+    return m;
+}
+
+KronosCudaMatrix *kronos_cuda_matrix_clone(KronosCudaContext *ctx, const KronosCudaMatrix *src) {
+    if (!ctx) return nullptr;
+    ctx->err.clear();
+    if (!src) { fail(ctx, "matrix_clone: matrix is NULL"); return nullptr; }
+    if (src->device != ctx->device) { fail(ctx, "matrix_clone: matrix lives on another device"); return nullptr; }
+    if (!make_current(ctx)) return nullptr;
+    KronosCudaMatrix *m = new (std::nothrow) KronosCudaMatrix(*src);
+    if (!m) { fail(ctx, "matrix_clone: out of host memory"); return nullptr; }
+    m->dm.d_base = nullptr;
+    if (!cuda_ok(ctx, cudaMalloc(reinterpret_cast<void **>(&m->dm.d_base), src->dm.device_bytes), "cudaMalloc(matrix)")) { delete m; return nullptr; }
+    if (!cuda_ok(ctx, cudaMemcpyAsync(m->dm.d_base, src->dm.d_base, src->dm.device_bytes, cudaMemcpyDeviceToDevice, ctx->stream), "cudaMemcpy(matrix)") ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "matrix clone sync")) {
+        cudaFree(m->dm.d_base);
+        delete m;
+        return nullptr;
+    }
+    const MatrixGeom &g = m->dm.geom;
+    m->dm.d_a = m->dm.d_base;
+    m->dm.d_b = m->dm.d_base + g.plane_a;
+    m->dm.d_scales = reinterpret_cast<const uint16_t *>(m->dm.d_base + g.plane_a + g.plane_b);
     return m;
 }
 
@@ -206,7 +230,7 @@ size_t kronos_cuda_matrix_image(const KronosCudaMatrixDesc *desc, uint32_t flags
     if (!matrix_geometry(*desc, g, why)) return 0;
     const bool interleave = (flags & KRONOS_CUDA_UPLOAD_GATE_UP_INTERLEAVE) != 0;
     if (interleave && (desc->rows % 128 != 0)) return 0;
-    const size_t need = g.rec_total + g.scale_total;
+    const size_t need = g.image_bytes();
     if (out && cap >= need) repack_matrix(*desc, g, interleave, out, 4);
     return need;
 }

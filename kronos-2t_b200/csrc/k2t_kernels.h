@@ -10,8 +10,9 @@ namespace k2t {
 // Device-resident matrix (image produced by repack_matrix, uploaded once).
 struct DeviceMatrix {
     MatrixGeom geom;
-    uint8_t *d_base = nullptr;      // one allocation: records then scales
-    const uint8_t *d_rec = nullptr;
+    uint8_t *d_base = nullptr;      // one allocation: plane A, plane B, scales
+    const uint8_t *d_a = nullptr;
+    const uint8_t *d_b = nullptr;
     const uint16_t *d_scales = nullptr;
     size_t device_bytes = 0;
 };

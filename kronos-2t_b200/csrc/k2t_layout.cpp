@@ -1,4 +1,4 @@
-// Host-side repack of reference-format matrices into the device group-record layout (k2t_layout.h).
+// Host-side repack of reference-format matrices into the device cell-plane layout (k2t_layout.h).
 // Input formats: FusedBipolarLutMatrix (src/kernels/simd_lut.rs:1761-1794) and NfSdotMatrix
 // pair_stream / tail_stream (simd_lut.rs:4850-5023, E8Q2 5118-5226) exactly as stored in .k2tb/.k2tm.
 #include "k2t_layout.h"
@@ -107,13 +107,13 @@ inline void put_u16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)(v & 0xFF); p[1] =
 bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &err) {
     std::memset(&g, 0, sizeof g);
     if (d.rows == 0 || d.cols == 0 || d.cols % 64 != 0) { err = "matrix: cols must be a positive multiple of 64"; return false; }
-    g.rows = d.rows; g.cols = d.cols; g.nc = d.cols / 64; g.ngroups = (d.rows + 7) / 8;
+    g.rows = d.rows; g.cols = d.cols; g.nc = d.cols / 64;
     const size_t ns = (d.rows + STRIPE - 1) / STRIPE;
     if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
         if (d.bits < 4 || d.bits > 6) { err = "bipolar matrix: planes must be 4, 5 or 6"; return false; }
         g.fmt = (Format)(FMT_BP4 + (d.bits - 4));
         g.sgc = 1; g.nsg = g.nc; g.max_odd = (1 << d.bits) - 1;
-        g.rec_bytes = 256 + 64 * (d.bits - 4);
+        g.cell_a = 32; g.cell_b = 8 * (d.bits - 4);
         size_t want0 = ns * (d.cols / 8) * d.bits * STRIPE, want1 = ns * g.nc * STRIPE * 2;
         if (d.len0 != want0 || d.len1 != want1 || !d.data0 || !d.data1) { err = "bipolar matrix: plane/scale byte counts do not match rows x cols"; return false; }
         g.file_bytes = want0 + want1;
@@ -122,7 +122,7 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         if (d.scale_group_chunks < 1 || d.scale_group_chunks > 8) { err = "NF matrix: scale_group_chunks must be 1..8"; return false; }
         g.fmt = d.bits == 4 ? FMT_NF4 : d.bits == 3 ? FMT_NF3 : d.bits == 5 ? FMT_NF5 : FMT_E8Q2;
         g.sgc = d.scale_group_chunks; g.nsg = (g.nc + g.sgc - 1) / g.sgc; g.max_odd = 0;
-        g.rec_bytes = d.bits == 4 ? 256 : d.bits == 5 ? 320 : d.bits == 3 ? 192 : 128;
+        g.cell_a = d.bits >= 4 ? 32 : 16; g.cell_b = d.bits == 5 ? 8 : d.bits == 3 ? 8 : 0;
         size_t cb = nf_chunk_bytes(d.bits);
         size_t want0 = (ns / 2) * ((size_t)g.nsg * 64 + (size_t)g.nc * 2 * cb);
         size_t want1 = (ns & 1) * ((size_t)g.nsg * 32 + (size_t)g.nc * cb);
@@ -158,14 +158,16 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         err = "matrix: unsupported kind (only bipolar=0 and NF=2)";
         return false;
     }
-    g.rec_total = (size_t)g.ngroups * g.nc * g.rec_bytes;
-    g.scale_total = (size_t)g.ngroups * 8 * g.nsg * 2;
+    auto up16 = [](size_t x) { return (x + 15) & ~(size_t)15; };
+    g.plane_a = up16((size_t)g.rows * g.nc * g.cell_a);
+    g.plane_b = up16((size_t)g.rows * g.nc * g.cell_b);
+    g.scale_total = up16((size_t)g.rows * g.nsg * 2);
     return true;
 }
 
 void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool interleave, uint8_t *out,
                    unsigned threads) {
-    std::memset(out, 0, g.rec_total + g.scale_total);
+    std::memset(out, 0, g.image_bytes());
     const FileView fv(d);
     const uint32_t inter = d.rows / 2;
     // destination row -> source row (gate_up interleave puts gate block ic at rows [128ic, +64), up block at [128ic+64, +64))
@@ -174,66 +176,63 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
         uint32_t blk = r / 128, w = r % 128;
         return w < 64 ? blk * 64 + w : inter + blk * 64 + (w - 64);
     };
-    uint8_t *scales = out + g.rec_total;
+    uint8_t *plane_a = out, *plane_b = out + g.plane_a, *scales = out + g.plane_a + g.plane_b;
 
-    auto do_groups = [&](uint32_t g_lo, uint32_t g_hi) {
-        for (uint32_t grp = g_lo; grp < g_hi; ++grp) {
-            for (uint32_t rr = 0; rr < 8; ++rr) {
-                uint32_t r_dst = grp * 8 + rr;
-                if (r_dst >= d.rows) break;
-                uint32_t r = src_row(r_dst), lane = r % STRIPE;
-                for (uint32_t c = 0; c < g.nc; ++c) {
-                    uint8_t *rec = out + ((size_t)grp * g.nc + c) * g.rec_bytes;
-                    if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
-                        put_u16(scales + (((size_t)grp * g.nsg + c) * 8 + rr) * 2, fv.bp_scale(r, c));
-                        for (uint32_t col = 0; col < 64; ++col) {
-                            uint32_t u = fv.bp_code(r, c * 64 + col);
-                            uint32_t cc = col % 32, k = cc % 8;
-                            uint8_t *byte = rec + (col / 32) * 128 + rr * 16 + (cc / 8) * 4 + (k % 4);
-                            *byte |= (uint8_t)((u & 0x0F) << (k < 4 ? 0 : 4));
-                            if (d.bits == 5) {
-                                uint32_t bit = 8 * (col % 4) + cc / 4;
-                                rec[256 + rr * 8 + (col / 32) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 1) << (bit % 8));
-                            } else if (d.bits == 6) {
-                                uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
-                                rec[256 + rr * 16 + (col / 16) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 3) << (bit % 8));
-                            }
+    auto do_rows = [&](uint32_t r_lo, uint32_t r_hi) {
+        for (uint32_t r_dst = r_lo; r_dst < r_hi; ++r_dst) {
+            const uint32_t r = src_row(r_dst), lane = r % STRIPE;
+            for (uint32_t c = 0; c < g.nc; ++c) {
+                const size_t cell = (size_t)r_dst * g.nc + c;
+                uint8_t *ca = plane_a + cell * g.cell_a;
+                uint8_t *cb = plane_b + cell * g.cell_b;
+                if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
+                    put_u16(scales + ((size_t)r_dst * g.nsg + c) * 2, fv.bp_scale(r, c));
+                    for (uint32_t col = 0; col < 64; ++col) {
+                        uint32_t u = fv.bp_code(r, c * 64 + col);
+                        uint32_t k = col % 8;
+                        ca[(col / 8) * 4 + (k % 4)] |= (uint8_t)((u & 0x0F) << (k < 4 ? 0 : 4));
+                        if (d.bits == 5) {
+                            uint32_t bit = 8 * (col % 4) + (col % 32) / 4;
+                            cb[(col / 32) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 1) << (bit % 8));
+                        } else if (d.bits == 6) {
+                            uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
+                            cb[(col / 16) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 3) << (bit % 8));
                         }
-                        continue;
                     }
-                    const uint8_t *blk, *sc;
-                    fv.nf_ptrs(r / STRIPE, c, blk, sc);
-                    if (c % g.sgc == 0) put_u16(scales + (((size_t)grp * g.nsg + c / g.sgc) * 8 + rr) * 2, fv.nf_scale(r, c));
-                    if (d.bits == 2) {
-                        for (uint32_t eb8 = 0; eb8 < 8; ++eb8) {
-                            uint8_t tpl, sgn;
-                            fv.e8_codes(blk, lane, eb8, tpl, sgn);
-                            rec[rr * 16 + 2 * eb8] = tpl;
-                            rec[rr * 16 + 2 * eb8 + 1] = sgn;
+                    continue;
+                }
+                const uint8_t *blk, *sc;
+                fv.nf_ptrs(r / STRIPE, c, blk, sc);
+                if (c % g.sgc == 0) put_u16(scales + ((size_t)r_dst * g.nsg + c / g.sgc) * 2, fv.nf_scale(r, c));
+                if (d.bits == 2) {
+                    for (uint32_t eb8 = 0; eb8 < 8; ++eb8) {
+                        uint8_t tpl, sgn;
+                        fv.e8_codes(blk, lane, eb8, tpl, sgn);
+                        ca[2 * eb8] = tpl;
+                        ca[2 * eb8 + 1] = sgn;
+                    }
+                } else if (d.bits == 3) {
+                    auto word_ptr = [&](uint32_t w) { return w < 4 ? ca + w * 4 : cb + (w - 4) * 4; };
+                    for (uint32_t col = 0; col < 64; ++col) {
+                        uint32_t idx = fv.nf_index(blk, lane, col);
+                        if (col < 48) {
+                            uint32_t nib = col % 8;
+                            word_ptr(col / 8)[nib / 2] |= (uint8_t)(idx << (4 * (nib % 2)));
+                        } else {
+                            uint32_t t = col - 48, nib = t % 8;
+                            for (uint32_t j = 0; j < 3; ++j)
+                                word_ptr(3 * (t / 8) + j)[nib / 2] |= (uint8_t)(((idx >> j) & 1) << (4 * (nib % 2) + 3));
                         }
-                    } else if (d.bits == 3) {
-                        auto word_ptr = [&](uint32_t w) { return w < 4 ? rec + rr * 16 + w * 4 : rec + 128 + rr * 8 + (w - 4) * 4; };
-                        for (uint32_t col = 0; col < 64; ++col) {
-                            uint32_t idx = fv.nf_index(blk, lane, col);
-                            if (col < 48) {
-                                uint32_t nib = col % 8;
-                                word_ptr(col / 8)[nib / 2] |= (uint8_t)(idx << (4 * (nib % 2)));
-                            } else {
-                                uint32_t t = col - 48, nib = t % 8;
-                                for (uint32_t j = 0; j < 3; ++j)
-                                    word_ptr(3 * (t / 8) + j)[nib / 2] |= (uint8_t)(((idx >> j) & 1) << (4 * (nib % 2) + 3));
-                            }
-                        }
-                    } else {  // 4 or 5 bits
-                        for (uint32_t col = 0; col < 64; ++col) {
-                            uint32_t idx = fv.nf_index(blk, lane, col);
-                            if (d.bits == 4) idx = g.nf4_rank[idx];
-                            uint32_t cc = col % 32, nib = cc % 8;
-                            rec[(col / 32) * 128 + rr * 16 + (cc / 8) * 4 + nib / 2] |= (uint8_t)((idx & 0x0F) << (4 * (nib % 2)));
-                            if (d.bits == 5) {
-                                uint32_t bit = 8 * (col % 4) + cc / 4;
-                                rec[256 + rr * 8 + (col / 32) * 4 + bit / 8] |= (uint8_t)(((idx >> 4) & 1) << (bit % 8));
-                            }
+                    }
+                } else {  // 4 or 5 bits
+                    for (uint32_t col = 0; col < 64; ++col) {
+                        uint32_t idx = fv.nf_index(blk, lane, col);
+                        if (d.bits == 4) idx = g.nf4_rank[idx];
+                        uint32_t nib = col % 8;
+                        ca[(col / 8) * 4 + nib / 2] |= (uint8_t)((idx & 0x0F) << (4 * (nib % 2)));
+                        if (d.bits == 5) {
+                            uint32_t bit = 8 * (col % 4) + (col % 32) / 4;
+                            cb[(col / 32) * 4 + bit / 8] |= (uint8_t)(((idx >> 4) & 1) << (bit % 8));
                         }
                     }
                 }
@@ -241,14 +240,14 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
         }
     };
 
-    threads = std::max(1u, std::min(threads, g.ngroups));
-    if (threads == 1 || (size_t)d.rows * d.cols < (1u << 20)) { do_groups(0, g.ngroups); return; }
+    threads = std::max(1u, std::min(threads, d.rows));
+    if (threads == 1 || (size_t)d.rows * d.cols < (1u << 20)) { do_rows(0, d.rows); return; }
     std::vector<std::thread> pool;
-    uint32_t per = (g.ngroups + threads - 1) / threads;
+    uint32_t per = (d.rows + threads - 1) / threads;
     for (unsigned t = 0; t < threads; ++t) {
-        uint32_t lo = t * per, hi = std::min(g.ngroups, lo + per);
+        uint32_t lo = t * per, hi = std::min(d.rows, lo + per);
         if (lo >= hi) break;
-        pool.emplace_back(do_groups, lo, hi);
+        pool.emplace_back(do_rows, lo, hi);
     }
     for (auto &th : pool) th.join();
 }

@@ -54,6 +54,7 @@ def load_library():
     sig("kronos_cuda_launch_count", u64, vp)
     sig("kronos_cuda_set_stream", i32, vp, vp)
     sig("kronos_cuda_matrix_upload", vp, vp, C.POINTER(MatrixDesc), u32)
+    sig("kronos_cuda_matrix_clone", vp, vp, vp)
     sig("kronos_cuda_matrix_free", None, vp, vp)
     sig("kronos_cuda_matrix_file_bytes", sz, vp)
     sig("kronos_cuda_matrix_device_bytes", sz, vp)
@@ -120,6 +121,12 @@ class Matrix:
     @property
     def device_bytes(self):
         return load_library().kronos_cuda_matrix_device_bytes(self.handle)
+
+    def clone(self):
+        h = load_library().kronos_cuda_matrix_clone(self.ctx.handle, self.handle)
+        if not h:
+            raise KronosCudaError(load_library().kronos_cuda_last_error(self.ctx.handle).decode())
+        return Matrix(self.ctx, h, self.rows, self.cols)
 
     def free(self):
         if self.handle:

@@ -32,24 +32,22 @@ def _words(buf):
     return [int(x) for x in np.frombuffer(bytes(buf), dtype="<u4")]
 
 
-def decode_record(fmt, rec, r, cb_words):
-    """Returns the 64 weight bytes (unsigned for bit-planes, signed for NF) of row r of a record."""
-    a = _words(rec[r * 16: r * 16 + 16])
+def decode_cell(fmt, ca, cb, cb_words):
+    """Returns the 64 weight bytes (unsigned for bit-planes, signed for NF) of one cell (row x chunk),
+    given its plane A and plane B bytes, following decode<FMT> of k2t_gemv.cu."""
+    a = _words(ca)
+    h = _words(cb) if len(cb) else []
     u = [0] * 16
     M = 0xFFFFFFFF
     if fmt in ("bp4", "bp5", "bp6"):
-        b = _words(rec[128 + r * 16: 128 + r * 16 + 16])
-        for i in range(4):
+        for i in range(8):
             u[2 * i], u[2 * i + 1] = a[i] & 0x0F0F0F0F, (a[i] >> 4) & 0x0F0F0F0F
-            u[8 + 2 * i], u[8 + 2 * i + 1] = b[i] & 0x0F0F0F0F, (b[i] >> 4) & 0x0F0F0F0F
         if fmt == "bp5":
-            h = _words(rec[256 + r * 8: 256 + r * 8 + 8])
             for j in range(8):
                 for half in range(2):
                     hv = (h[half] << (4 - j)) & M if j <= 4 else h[half] >> (j - 4)
                     u[8 * half + j] |= hv & 0x10101010
         if fmt == "bp6":
-            h = _words(rec[256 + r * 16: 256 + r * 16 + 16])
             for v in range(4):
                 u[4 * v + 0] |= ((h[v] << 4) & M) & 0x30303030
                 u[4 * v + 1] |= ((h[v] << 2) & M) & 0x30303030
@@ -57,9 +55,8 @@ def decode_record(fmt, rec, r, cb_words):
                 u[4 * v + 3] |= (h[v] >> 2) & 0x30303030
         dt = np.uint8
     elif fmt == "nf4":
-        b = _words(rec[128 + r * 16: 128 + r * 16 + 16])
         for i in range(8):
-            x = a[i] if i < 4 else b[i - 4]
+            x = a[i]
             lo3, hb = x & 0x77777777, x & 0x88888888
             hs = (hb << 4) & M
             m0, m1 = prmt(hs, hb, 0xD9C8), prmt(hs, hb, 0xFBEA)
@@ -69,34 +66,46 @@ def decode_record(fmt, rec, r, cb_words):
             u[2 * i + 1] = (r_lo & ~m1 & M) | (r_hi & m1)
         dt = np.int8
     elif fmt == "nf3":
-        W = a + _words(rec[128 + r * 8: 128 + r * 8 + 8])
+        W = a + h
         for i in range(6):
             s = W[i] & 0x77777777
             u[2 * i], u[2 * i + 1] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
-        for h in range(2):
-            s = (W[3 * h] >> 3) & 0x11111111
-            s |= (W[3 * h + 1] >> 2) & 0x22222222
-            s |= (W[3 * h + 2] >> 1) & 0x44444444
-            u[12 + 2 * h], u[13 + 2 * h] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
+        for hh in range(2):
+            s = (W[3 * hh] >> 3) & 0x11111111
+            s |= (W[3 * hh + 1] >> 2) & 0x22222222
+            s |= (W[3 * hh + 2] >> 1) & 0x44444444
+            u[12 + 2 * hh], u[13 + 2 * hh] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
         dt = np.int8
     else:
         raise ValueError(fmt)
     return np.array(u, dtype="<u4").view(np.uint8).view(dt)
 
 
-REC_BYTES = {"bp4": 256, "bp5": 320, "bp6": 384, "nf4": 256, "nf3": 192}
+CELL_BYTES = {"bp4": (32, 0), "bp5": (32, 8), "bp6": (32, 16), "nf4": (32, 0), "nf3": (16, 8)}
+
+
+def up16(x):
+    return (x + 15) & ~15
+
+
+def split_image(fmt, image, rows, cols, nsg):
+    nc = cols // 64
+    ca, cb = CELL_BYTES[fmt]
+    na, nb, ns = up16(rows * nc * ca), up16(rows * nc * cb), up16(rows * nsg * 2)
+    assert image.size == na + nb + ns
+    pa = image[: rows * nc * ca].reshape(rows, nc, ca)
+    pb = image[na: na + rows * nc * cb].reshape(rows, nc, cb) if cb else np.zeros((rows, nc, 0), np.uint8)
+    scales = image[na + nb: na + nb + rows * nsg * 2].view("<u2").reshape(rows, nsg)
+    return pa, pb, scales
 
 
 def image_rows(fmt, image, rows, cols, nsg, cb_words=None):
     """Decodes a whole device image into weight bytes [rows, cols] and bf16 scales [rows, nsg]."""
-    nc, ng, rb = cols // 64, (rows + 7) // 8, REC_BYTES[fmt]
-    recs = image[: ng * nc * rb].reshape(ng, nc, rb)
-    scales = image[ng * nc * rb:].view("<u2").reshape(ng, nsg, 8).transpose(0, 2, 1).reshape(ng * 8, nsg)
-    out = np.zeros((ng * 8, cols), np.int16)
-    for g in range(ng):
-        for c in range(nc):
-            for r in range(8):
-                out[g * 8 + r, c * 64:(c + 1) * 64] = decode_record(fmt, recs[g, c], r, cb_words)
+    pa, pb, scales = split_image(fmt, image, rows, cols, nsg)
+    out = np.zeros((rows, cols), np.int16)
+    for r in range(rows):
+        for c in range(cols // 64):
+            out[r, c * 64:(c + 1) * 64] = decode_cell(fmt, pa[r, c], pb[r, c], cb_words)
     return out, scales
 
 
@@ -106,13 +115,11 @@ def test_bitplane_image_decodes_to_file_codes(oracle, planes, rows):
     cols = 192
     m = oracle.bipolar_quantize_rtn(normal(planes, (rows, cols), 0.02), planes, threads=2)
     image = k2.matrix_image(k2.bipolar_desc(rows, cols, planes, m.data, m.scales))
-    assert image.size == ((rows + 7) // 8) * (cols // 64) * (REC_BYTES[f"bp{planes}"] + 16)
     codes, scales = image_rows(f"bp{planes}", image, rows, cols, cols // 64)
     sc_file = m.scales.reshape(-1, cols // 64, 16)
     for r in range(rows):
         assert np.array_equal(codes[r], oracle.bipolar_unpack_row(m, r))
         assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
-    assert not codes[rows:].any() and not scales[rows:].any()   # padding rows
 
 
 @pytest.mark.parametrize("bits", [3, 4])
@@ -134,10 +141,9 @@ def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
     sc_file = sc.reshape(-1, nsg, 16)
     for r in range(rows):
         assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
-    assert not scales[rows:].any()
 
 
-def nf4_two_table_values(rec, r, cb_sorted):
+def nf4_two_table_values(cell, cb_sorted):
     """cell_dot<FMT_NF4>'s decode: centroid = hi[l] + off where index bit 3 is set, off - lo[l] elsewhere,
     each table looked up with one prmt whose selector has bit 3 set for the lanes that must yield 0."""
     cb = cb_sorted.astype(int)
@@ -147,9 +153,8 @@ def nf4_two_table_values(rec, r, cb_sorted):
     hi, lo = [int(cb[8 + l] - off) for l in range(8)], [int(off - cb[l]) for l in range(8)]
     assert all(0 <= v <= 127 for v in hi + lo)
     tab = _words(bytes(hi + lo))
-    words = _words(rec[r * 16: r * 16 + 16]) + _words(rec[128 + r * 16: 128 + r * 16 + 16])
     vals = []
-    for x in words:
+    for x in _words(cell):
         y = x ^ 0x88888888
         for sel_hi, sel_lo in ((y, x), (y >> 16, x >> 16)):
             up = np.array([prmt(tab[0], tab[1], sel_hi)], "<u4").view(np.uint8).astype(int)
@@ -172,12 +177,11 @@ def test_nf4_two_table_decode(oracle, cb):
     sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, 1)).astype(np.uint16)
     m = oracle.nf_pack(idx, sc, 4, 1, cb)
     image = k2.matrix_image(k2.nf_desc(rows, cols, 4, 1, cb, m.pair, m.tail))
-    recs = image[: 2 * 2 * 256].reshape(2, 2, 256)
-    for g in range(2):
+    pa, _, _ = split_image("nf4", image, rows, cols, 2)
+    for r in range(rows):
         for c in range(2):
-            for r in range(8):
-                got = nf4_two_table_values(recs[g, c], r, np.sort(cb))
-                assert np.array_equal(got, cb.astype(int)[idx[g * 8 + r, c * 64:(c + 1) * 64]])
+            got = nf4_two_table_values(pa[r, c], np.sort(cb))
+            assert np.array_equal(got, cb.astype(int)[idx[r, c * 64:(c + 1) * 64]])
 
 
 def test_gate_up_interleave_image(oracle):
@@ -203,7 +207,7 @@ def test_malformed_descriptors_are_rejected(oracle):
     m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
     L = k2.load_library()
     good = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
-    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 2 * 256 + 2 * 8 * 2
+    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 16 * 32 + 16 * 2
     for kw in ({"cols": 65}, {"bits": 7}, {"rows": 0}, {"kind": 1}, {"len0": 5}):
         bad = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
         for key, val in kw.items():
