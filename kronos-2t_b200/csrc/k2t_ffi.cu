@@ -30,6 +30,7 @@ struct KronosCudaContext {
     uint64_t launches = 0;
     std::string err;
     DeviceBuffer x, q, xs, xsum, out, dots, inv, normw;
+    uint32_t *d_err = nullptr;      // device word kernels set when a bounded wait gives up
 };
 
 namespace {
@@ -57,6 +58,18 @@ void release(DeviceBuffer &b) {
     if (b.p) cudaFree(b.p);
     b.p = nullptr; b.cap = 0;
 }
+// Waits for the stream and reports a kernel-side timeout (a bounded wait that gave up) as an error.
+bool sync_and_check(KronosCudaContext *ctx, const char *what) {
+    uint32_t flag = 0;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(&flag, ctx->d_err, 4, cudaMemcpyDeviceToHost, ctx->stream), what) ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), what))
+        return false;
+    if (flag != 0) {
+        cudaMemsetAsync(ctx->d_err, 0, 4, ctx->stream);
+        return fail(ctx, std::string(what) + ": a kernel gave up waiting for its weight pipeline (results invalid)");
+    }
+    return true;
+}
 bool make_current(KronosCudaContext *ctx) { return cuda_ok(ctx, cudaSetDevice(ctx->device), "cudaSetDevice"); }
 
 bool check_gemv_args(KronosCudaContext *ctx, const KronosCudaMatrix *m, const void *xq, const void *xs,
@@ -79,7 +92,7 @@ bool run_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, const int8_t *d
         uint32_t n = (uint32_t)std::min<size_t>(max_t, n_tok - t0), launched = 0;
         cudaError_t e = launch_gemv(ctx->stream, m->dm, d_xq + t0 * g.cols, d_xs + t0 * g.nc,
                                     d_xsum ? d_xsum + t0 * g.nc : nullptr, n, d_out + t0 * out_stride, out_stride,
-                                    d_dots ? d_dots + t0 * (size_t)g.rows * g.nc : nullptr, ctx->sm_count, &launched);
+                                    d_dots ? d_dots + t0 * (size_t)g.rows * g.nc : nullptr, ctx->sm_count, ctx->d_err, &launched);
         ctx->launches += launched;
         if (!cuda_ok(ctx, e, "gemv launch")) return false;
     }
@@ -120,6 +133,13 @@ KronosCudaContext *kronos_cuda_context_create(int32_t device) {
         return nullptr;
     }
     ctx->stream = ctx->own_stream;
+    if ((e = cudaMalloc(reinterpret_cast<void **>(&ctx->d_err), 4)) != cudaSuccess ||
+        (e = cudaMemset(ctx->d_err, 0, 4)) != cudaSuccess) {
+        set_err(std::string("cudaMalloc(error word): ") + cudaGetErrorString(e));
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return nullptr;
+    }
     return ctx;
 }
 
@@ -128,6 +148,7 @@ void kronos_cuda_context_destroy(KronosCudaContext *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     for (DeviceBuffer *b : {&ctx->x, &ctx->q, &ctx->xs, &ctx->xsum, &ctx->out, &ctx->dots, &ctx->inv, &ctx->normw}) release(*b);
+    if (ctx->d_err) cudaFree(ctx->d_err);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }
@@ -146,7 +167,7 @@ int32_t kronos_cuda_synchronize(KronosCudaContext *ctx) {
     if (!ctx) return -1;
     ctx->err.clear();
     if (!make_current(ctx)) return -1;
-    return cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize") ? 0 : -1;
+    return sync_and_check(ctx, "synchronize") ? 0 : -1;
 }
 
 uint64_t kronos_cuda_launch_count(const KronosCudaContext *ctx) { return ctx ? ctx->launches : 0; }
@@ -186,9 +207,6 @@ KronosCudaMatrix *kronos_cuda_matrix_upload(KronosCudaContext *ctx, const Kronos
         delete m;
         return nullptr;
     }
-    m->dm.d_a = m->dm.d_base;
-    m->dm.d_b = m->dm.d_base + g.plane_a;
-    m->dm.d_scales = reinterpret_cast<const uint16_t *>(m->dm.d_base + g.plane_a + g.plane_b);
     return m;
 }
 
@@ -208,10 +226,6 @@ KronosCudaMatrix *kronos_cuda_matrix_clone(KronosCudaContext *ctx, const KronosC
         delete m;
         return nullptr;
     }
-    const MatrixGeom &g = m->dm.geom;
-    m->dm.d_a = m->dm.d_base;
-    m->dm.d_b = m->dm.d_base + g.plane_a;
-    m->dm.d_scales = reinterpret_cast<const uint16_t *>(m->dm.d_base + g.plane_a + g.plane_b);
     return m;
 }
 
@@ -322,7 +336,7 @@ int32_t kronos_cuda_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, cons
         if (!cuda_ok(ctx, cudaMemcpyAsync(out + t * out_stride, (const float *)ctx->out.p + t * out_stride,
                                           (size_t)g.rows * 4, cudaMemcpyDeviceToHost, s), "copy out")) return -1;
     if (int_dots && !cuda_ok(ctx, cudaMemcpyAsync(int_dots, ctx->dots.p, n_dots * 4, cudaMemcpyDeviceToHost, s), "copy dots")) return -1;
-    return cuda_ok(ctx, cudaStreamSynchronize(s), "gemv sync") ? 0 : -1;
+    return sync_and_check(ctx, "gemv") ? 0 : -1;
 }
 
 int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out) {
@@ -347,7 +361,7 @@ int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, co
                   (float *)ctx->out.p, g.rows, nullptr))
         return -1;
     if (!cuda_ok(ctx, cudaMemcpyAsync(out, ctx->out.p, n_out * 4, cudaMemcpyDeviceToHost, s), "copy out")) return -1;
-    return cuda_ok(ctx, cudaStreamSynchronize(s), "linear sync") ? 0 : -1;
+    return sync_and_check(ctx, "linear") ? 0 : -1;
 }
 
 }  // extern "C"

@@ -12,31 +12,37 @@
 //
 // Mapping.  A lane owns a CELL (one row x one 64-column chunk) at a time.  In a warp, lane l works on
 // chunk 32p + l of the current pass p, so the int8 activations of that chunk (64 B), their scale and
-// their sum stay in the lane's registers while the warp walks down the rows of its tile: the inner
-// loop touches no shared memory for activations.  A warp step reads 32 cells x 32 B = 1 KiB of
-// contiguous weights with 128-bit loads (cells are stored row-major, [row][chunk]); loads are issued
-// in register batches of UB rows, the next batch in flight while the current one is reduced, and the
-// UB cells of a batch are independent, which gives the lane UB-way instruction-level parallelism.
-// Every cell parks (v, w_scale) in a shared-memory tile [row][chunk]; when the tile is complete, lane
-// i of the tile's first warp runs the fp32 chain of row i over all chunks.  With `wk` warps per tile
-// the passes are dealt round-robin to the warps (K split), with `tr` rows per tile the rows are.
+// their sum stay in the lane's registers while the warp walks down its rows: the inner loop touches
+// no shared memory for activations.  Warps are independent (one warp per CTA, persistent grid): warp
+// w owns the 4-row blocks w, w + W, w + 2W, ... and works through them 8 blocks (32 rows) at a time.
+//
+// Weight streaming.  Each warp runs its own bulk-copy pipeline: a stage receives the cells of one
+// 4-row block for one pass (16-byte half cells of columns 0..31 and 32..63, the extra-bit plane and
+// the bf16 scales, one `cp.async.bulk` per contiguous run) and signals an mbarrier with the byte
+// count.  NSTAGE stages per warp keep 9..13 KiB per warp in flight without holding a register; the
+// stage is refilled right after its four rows have been reduced.  Cells are 16 bytes apart in a
+// stage, so the 128-bit shared-memory reads of a warp are conflict-free.
+//
+// Chain.  Every cell parks (v, w_scale) in a [32 rows][32 chunks] shared-memory tile; after the
+// eight blocks of a pass, lane i continues the fp32 chain of row i over the 32 chunks of that pass
+// (f stays in a register between passes), which keeps the reference's ascending-chunk order.
 #include "k2t_device.cuh"
 #include "k2t_kernels.h"
 
 namespace k2t {
 
 struct GemvArgs {
-    const uint8_t *pa;        // plane A  [rows][nc] cells
-    const uint8_t *pb;        // plane B  [rows][nc] cells (formats with more than 4 bits, NF3)
-    const uint16_t *scales;   // [rows][nsg] bf16
+    const uint8_t *plane[3];  // code planes, [rows][pitch] bytes
+    const uint16_t *scales;   // [rows][nsg_pad] bf16
     const int8_t *xq;
     const float *xs;
     const int32_t *xsum;
     float *out;
     int32_t *int_dots;
+    uint32_t *err_flag;       // set to 1 when a bounded mbarrier wait gives up
     size_t out_stride;
-    uint32_t rows, cols, nc, nsg, sgc, sgc_shift, n_tok;   // sgc_shift: log2(sgc) or 32
-    uint32_t tr, wk, tpc;     // rows per tile, warps per tile, tiles per CTA
+    uint32_t rows, cols, nc, nsg, nsg_pad, sgc, sgc_shift, n_tok;   // sgc_shift: log2(sgc) or 32
+    uint32_t pitch[3];
     int32_t max_odd;
     int32_t nf4_offset;
     uint32_t cb[8];    // expanded codebook, 4 centroids per word (NF4: sorted ascending)
@@ -45,34 +51,16 @@ struct GemvArgs {
 
 constexpr int FMT_NF4G = FMT_COUNT;   // NF4 with a codebook the two-table decode cannot represent
 
-template <int FMT> struct CellWords { static constexpr int A = 8, B = 0; };
-template <> struct CellWords<FMT_BP5> { static constexpr int A = 8, B = 2; };
-template <> struct CellWords<FMT_BP6> { static constexpr int A = 8, B = 4; };
-template <> struct CellWords<FMT_NF3> { static constexpr int A = 4, B = 2; };
+// bytes per cell in each code plane, and the words of a cell a lane holds (plane 0, 1, 2 in order)
+template <int FMT> struct Cell { static constexpr int B0 = 16, B1 = 16, B2 = 0; };
+template <> struct Cell<FMT_BP5> { static constexpr int B0 = 16, B1 = 16, B2 = 8; };
+template <> struct Cell<FMT_BP6> { static constexpr int B0 = 16, B1 = 16, B2 = 16; };
+template <> struct Cell<FMT_NF3> { static constexpr int B0 = 16, B1 = 8, B2 = 0; };
 
 template <int FMT>
-struct Raw {          // the words of one cell: plane A words first, then plane B words
-    uint32_t w[CellWords<FMT>::A + CellWords<FMT>::B];
+struct Raw {
+    uint32_t w[(Cell<FMT>::B0 + Cell<FMT>::B1 + Cell<FMT>::B2) / 4];
 };
-
-template <int FMT>
-__device__ __forceinline__ void load_cell(Raw<FMT> &o, const uint8_t *ca, const uint8_t *cb) {
-    constexpr int A = CellWords<FMT>::A, B = CellWords<FMT>::B;
-    uint4 a = ldg_stream(reinterpret_cast<const uint4 *>(ca));
-    o.w[0] = a.x; o.w[1] = a.y; o.w[2] = a.z; o.w[3] = a.w;
-    if (A == 8) {
-        uint4 b = ldg_stream(reinterpret_cast<const uint4 *>(ca) + 1);
-        o.w[4] = b.x; o.w[5] = b.y; o.w[6] = b.z; o.w[7] = b.w;
-    }
-    if (B == 2) {
-        uint2 h = ldg_stream(reinterpret_cast<const uint2 *>(cb));
-        o.w[A] = h.x; o.w[A + 1] = h.y;
-    }
-    if (B == 4) {
-        uint4 h = ldg_stream(reinterpret_cast<const uint4 *>(cb));
-        o.w[A] = h.x; o.w[A + 1] = h.y; o.w[A + 2] = h.z; o.w[A + 3] = h.w;
-    }
-}
 
 // Expands a cell into 16 words of four weight bytes each: u[j] holds columns 4j..4j+3 of the chunk.
 // Bit-plane formats give unsigned codes 0..63, NF formats signed centroids.
@@ -183,130 +171,240 @@ __device__ __forceinline__ uint32_t scale_group_of(const GemvArgs &a, uint32_t c
     return a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
 }
 
-__host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+__host__ __device__ inline uint32_t up16(uint32_t x) { return (x + 15u) & ~15u; }
 
-// rows of a register batch: about 32 words of cells per buffer, two buffers
-template <int FMT> struct Batch { static constexpr int UB = 32 / (CellWords<FMT>::A + CellWords<FMT>::B); };
-template <> struct Batch<FMT_NF3> { static constexpr int UB = 4; };
+// ------------------------------------------------------------------------------------------------
+// bulk-copy pipeline primitives
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-struct SmemPlan { size_t nz, tile, tile_stride, total; };
-__host__ __device__ inline SmemPlan smem_plan(uint32_t nt, uint32_t nc, uint32_t tr, uint32_t tpc) {
-    SmemPlan p;
-    const uint32_t np = (nc + 31) / 32;
-    p.nz = 0;                                                   // [nt][np] masks of chunks with xs != 0
-    p.tile = align16((size_t)nt * np * 4);
-    p.tile_stride = (size_t)nt * tr * (nc + 1) * 8;             // float2 [nt][tr][nc + 1] per tile
-    p.total = p.tile + p.tile_stride * tpc;
-    return p;
+constexpr int RS = 4;           // rows per stage (one 4-row block, one pass)
+constexpr int NSTAGE = 3;       // stages per warp
+constexpr int SCALE_PITCH = 80; // bytes reserved per row for the scales of a pass (32 bf16 + alignment slack)
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+template <int FMT> struct Stage {
+    static constexpr uint32_t OFF0 = 0;
+    static constexpr uint32_t OFF1 = RS * 32 * Cell<FMT>::B0;
+    static constexpr uint32_t OFF2 = OFF1 + RS * 32 * Cell<FMT>::B1;
+    static constexpr uint32_t OFFS = OFF2 + RS * 32 * Cell<FMT>::B2;
+    static constexpr uint32_t BYTES = OFFS + RS * SCALE_PITCH;
+    static constexpr uint32_t NPL = 1 + (Cell<FMT>::B1 ? 1 : 0) + (Cell<FMT>::B2 ? 1 : 0) + 1;   // code planes + scales
+};
+
+// shared memory of one warp: stages, (v, w_scale) tile [NT][32][33], mbarriers
+template <int FMT> __host__ __device__ constexpr uint32_t warp_smem(uint32_t nt) {
+    return NSTAGE * Stage<FMT>::BYTES + nt * 32 * 33 * 8 + 64;
 }
 
-template <int FMT, int NT>
-__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
-    constexpr int UB = Batch<FMT>::UB;
-    constexpr int CA = CellWords<FMT>::A * 4, CB = CellWords<FMT>::B * 4;
-    extern __shared__ __align__(16) uint8_t smem[];
+template <int FMT>
+__device__ __forceinline__ void read_cell(Raw<FMT> &o, const uint8_t *st, uint32_t rr, uint32_t lane,
+                                          uint32_t p0, uint32_t p1, uint32_t p2) {
+    const uint4 a = *reinterpret_cast<const uint4 *>(st + Stage<FMT>::OFF0 + rr * p0 + lane * 16);
+    o.w[0] = a.x; o.w[1] = a.y; o.w[2] = a.z; o.w[3] = a.w;
+    if (Cell<FMT>::B1 == 16) {
+        const uint4 b = *reinterpret_cast<const uint4 *>(st + Stage<FMT>::OFF1 + rr * p1 + lane * 16);
+        o.w[4] = b.x; o.w[5] = b.y; o.w[6] = b.z; o.w[7] = b.w;
+    } else if (Cell<FMT>::B1 == 8) {
+        const uint2 b = *reinterpret_cast<const uint2 *>(st + Stage<FMT>::OFF1 + rr * p1 + lane * 8);
+        o.w[4] = b.x; o.w[5] = b.y;
+    }
+    if (Cell<FMT>::B2 == 8) {
+        const uint2 h = *reinterpret_cast<const uint2 *>(st + Stage<FMT>::OFF2 + rr * p2 + lane * 8);
+        o.w[8] = h.x; o.w[9] = h.y;
+    } else if (Cell<FMT>::B2 == 16) {
+        const uint4 h = *reinterpret_cast<const uint4 *>(st + Stage<FMT>::OFF2 + rr * p2 + lane * 16);
+        o.w[8] = h.x; o.w[9] = h.y; o.w[10] = h.z; o.w[11] = h.w;
+    }
+}
+
+template <int FMT, int NT, bool DOTS>
+__global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
+    using St = Stage<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t lane = threadIdx.x;
+    const uint32_t gw = blockIdx.x, nw = gridDim.x;
+    const uint32_t n_rb = (a.rows + RS - 1) / RS;              // 4-row blocks of the matrix
+    if (gw >= n_rb) return;
+    const uint32_t J = (n_rb - gw + nw - 1) / nw;              // blocks of this warp: gw, gw + nw, ...
     const uint32_t np = (a.nc + 31) / 32;
-    const SmemPlan sp = smem_plan(NT, a.nc, a.tr, a.tpc);
-    uint32_t *s_nz = reinterpret_cast<uint32_t *>(smem + sp.nz);
+    const bool merged = np == 1;                               // a block's rows are contiguous in every plane
 
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t tl = warp / a.wk, kw = warp % a.wk;
-    const uint32_t tile = blockIdx.x * a.tpc + tl;
-    const uint32_t row0 = tile * a.tr;
-    const uint32_t trv = row0 < a.rows ? min(a.tr, a.rows - row0) : 0;      // valid rows of this tile
-    const uint32_t stride = a.nc + 1;
-    float2 *s_tile = reinterpret_cast<float2 *>(smem + sp.tile + sp.tile_stride * tl);
+    uint8_t *stages = smem;
+    float2 *s_v = reinterpret_cast<float2 *>(smem + NSTAGE * St::BYTES);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(smem + NSTAGE * St::BYTES + NT * 32 * 33 * 8);
+    const uint32_t stage_sa = (uint32_t)__cvta_generic_to_shared(stages);
+    if (lane == 0) {
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(bar0 + 8 * s, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    __syncwarp();
 
-    for (uint32_t p = kw; p < np; p += a.wk) {
-        const uint32_t c = p * 32 + lane;
-        const bool act = c < a.nc;
-        // this lane's activation chunk(s): 64 int8 per token, kept in registers for the whole tile
-        int q[NT][16];
-        float sx[NT];
-        int xsum[NT];
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const bool on = act && (uint32_t)t < a.n_tok;
-            sx[t] = on ? __ldg(a.xs + (size_t)t * a.nc + c) : 0.0f;
-            xsum[t] = (on && a.xsum != nullptr) ? __ldg(a.xsum + (size_t)t * a.nc + c) : 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                int4 v = on ? __ldg(reinterpret_cast<const int4 *>(a.xq + (size_t)t * a.cols + (size_t)c * 64) + j) : make_int4(0, 0, 0, 0);
-                q[t][4 * j] = v.x; q[t][4 * j + 1] = v.y; q[t][4 * j + 2] = v.z; q[t][4 * j + 3] = v.w;
+    const uint32_t cellb[3] = {Cell<FMT>::B0, Cell<FMT>::B1, Cell<FMT>::B2};
+    const uint32_t soff[3] = {St::OFF0, St::OFF1, St::OFF2};
+
+    // ---- producer: unit (j, p) = block gw + j*nw, pass p; order: 8 blocks of a pass, then the next pass
+    uint32_t pj0 = 0, pp = 0, pjj = 0;          // producer cursor (first block of the 32-row group, pass, block in group)
+    auto issue = [&](uint32_t stage) {
+        if (pj0 >= J) return;                                   // nothing left: the stage stays idle
+        const uint32_t j = pj0 + pjj;
+        const uint32_t row0 = (gw + j * nw) * RS;
+        const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
+        const uint32_t c0 = pp * 32, n = min(32u, a.nc - c0);
+        const uint32_t sg0 = scale_group_of(a, c0), sg1 = scale_group_of(a, c0 + n - 1), sga = sg0 & ~7u;
+        const uint32_t bar = bar0 + 8 * stage;
+        const uint32_t dst0 = stage_sa + stage * St::BYTES;
+        // what lane `lane` copies: merged -> one run per plane; else one run per (row, plane)
+        const uint32_t k = lane % St::NPL, rr = lane / St::NPL;
+        const bool is_scale = k == St::NPL - 1;
+        uint32_t bytes = 0, dst = 0;
+        const uint8_t *src = nullptr;
+        if (merged) {
+            if (rr == 0) {
+                if (is_scale) { bytes = nrows * a.nsg_pad * 2; src = reinterpret_cast<const uint8_t *>(a.scales) + (size_t)row0 * a.nsg_pad * 2; dst = dst0 + St::OFFS; }
+                else { bytes = nrows * a.pitch[k]; src = a.plane[k] + (size_t)row0 * a.pitch[k]; dst = dst0 + soff[k]; }
             }
-            const uint32_t nz = __ballot_sync(0xffffffffu, sx[t] != 0.0f);
-            if (tl == 0 && lane == 0) s_nz[t * np + p] = nz;
+        } else if (rr < nrows) {
+            if (is_scale) {
+                bytes = up16((sg1 - sga + 1) * 2);
+                src = reinterpret_cast<const uint8_t *>(a.scales) + ((size_t)(row0 + rr) * a.nsg_pad + sga) * 2;
+                dst = dst0 + St::OFFS + rr * SCALE_PITCH;
+            } else {
+                bytes = up16(n * cellb[k]);
+                src = a.plane[k] + (size_t)(row0 + rr) * a.pitch[k] + (size_t)c0 * cellb[k];
+                dst = dst0 + soff[k] + rr * 32 * cellb[k];
+            }
         }
-
-        const uint8_t *ca = a.pa + ((size_t)row0 * a.nc + c) * CA;
-        const uint8_t *cb = a.pb + ((size_t)row0 * a.nc + c) * CB;
-        const size_t sa = (size_t)a.nc * CA, sb = (size_t)a.nc * CB;
-        const uint16_t *wsp = a.scales + (size_t)row0 * a.nsg + scale_group_of(a, act ? c : 0);
-
-        Raw<FMT> cur[UB], nxt[UB];
-        uint16_t cur_ws[UB], nxt_ws[UB];
+        uint32_t total = bytes;
 #pragma unroll
-        for (int u = 0; u < UB; ++u)
-            if (act && (uint32_t)u < trv) {
-                load_cell<FMT>(cur[u], ca + u * sa, cb + u * sb);
-                cur_ws[u] = __ldg(wsp + (size_t)u * a.nsg);
-            }
-        for (uint32_t i0 = 0; i0 < trv; i0 += UB) {
+        for (uint32_t m = 16; m > 0; m >>= 1) total += __shfl_xor_sync(0xffffffffu, total, m);
+        if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, total); }
+        __syncwarp();
+        if (bytes) bulk_g2s(dst, src, bytes, bar);
+        // advance the cursor
+        const uint32_t in_group = min(8u, J - pj0);
+        if (++pjj == in_group) { pjj = 0; if (++pp == np) { pp = 0; pj0 += 8; } }
+    };
 #pragma unroll
-            for (int u = 0; u < UB; ++u) {
-                const uint32_t i = i0 + UB + u;
-                if (act && i < trv) {
-                    load_cell<FMT>(nxt[u], ca + (size_t)i * sa, cb + (size_t)i * sb);
-                    nxt_ws[u] = __ldg(wsp + (size_t)i * a.nsg);
+    for (int s = 0; s < NSTAGE; ++s) issue(s);
+
+    // ---- consumer
+    int q[NT][16];
+    float sx[NT];
+    int xsum[NT];
+    uint32_t nz[NT];
+    uint32_t stage = 0, phase = 0;
+    const uint32_t slot_j = lane / RS, slot_r = lane % RS;       // chain: lane -> (block in group, row in block)
+    for (uint32_t j0 = 0; j0 < J; j0 += 8) {
+        const uint32_t in_group = min(8u, J - j0);
+        float f[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) f[t] = 0.0f;
+        for (uint32_t p = 0; p < np; ++p) {
+            const uint32_t c = p * 32 + lane, n = min(32u, a.nc - p * 32);
+            const bool act = lane < n;
+            if (np > 1 || j0 == 0) {          // this lane's activation chunk(s) for the pass, kept in registers
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const bool on = act && (uint32_t)t < a.n_tok;
+                    sx[t] = on ? __ldg(a.xs + (size_t)t * a.nc + c) : 0.0f;
+                    xsum[t] = (on && a.xsum != nullptr) ? __ldg(a.xsum + (size_t)t * a.nc + c) : 0;
+#pragma unroll
+                    for (int jq = 0; jq < 4; ++jq) {
+                        const int4 v = on ? __ldg(reinterpret_cast<const int4 *>(a.xq + (size_t)t * a.cols + (size_t)c * 64) + jq) : make_int4(0, 0, 0, 0);
+                        q[t][4 * jq] = v.x; q[t][4 * jq + 1] = v.y; q[t][4 * jq + 2] = v.z; q[t][4 * jq + 3] = v.w;
+                    }
+                    nz[t] = __ballot_sync(0xffffffffu, sx[t] != 0.0f);
                 }
             }
+            // stage geometry of this pass
+            const uint32_t sg0 = scale_group_of(a, p * 32), sga = merged ? 0 : (sg0 & ~7u);
+            const uint32_t p0 = merged ? a.pitch[0] : 32 * Cell<FMT>::B0, p1 = merged ? a.pitch[1] : 32 * Cell<FMT>::B1;
+            const uint32_t p2 = merged ? a.pitch[2] : 32 * Cell<FMT>::B2, ps = merged ? a.nsg_pad * 2 : SCALE_PITCH;
+            const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - sga) * 2;
+
+            for (uint32_t jj = 0; jj < in_group; ++jj) {
+                const uint32_t row0 = (gw + (j0 + jj) * nw) * RS;
+                const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
+                // wait for the stage (bounded)
+                uint32_t ok = 0;
+                for (uint32_t spin = 0; spin < WAIT_LIMIT && !ok; ++spin) ok = mbar_try_wait(bar0 + 8 * stage, (phase >> stage) & 1u);
+                if (__any_sync(0xffffffffu, !ok)) {
+                    if (lane == 0) atomicExch(a.err_flag, 1u);
+                    return;
+                }
+                phase ^= 1u << stage;
+                const uint8_t *st = stages + stage * St::BYTES;
 #pragma unroll
-            for (int u = 0; u < UB; ++u) {
-                const uint32_t i = i0 + u;
-                if (act && i < trv) {
-                    const float ws = bf16_bits_to_f32(cur_ws[u]);
-                    if (NT == 1) {
-                        const int acc = cell_dot<FMT>(cur[u], a, q[0], xsum[0]);
-                        const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
-                        s_tile[(size_t)i * stride + c] = make_float2(__fmul_rn(__int2float_rn(dot), sx[0]), ws);
-                        if (a.int_dots != nullptr) a.int_dots[(size_t)(row0 + i) * a.nc + c] = dot;
-                    } else {
-                        uint32_t ub[16];
-                        decode<FMT>(cur[u], a.cb, ub);
+                for (uint32_t rr = 0; rr < RS; ++rr) {
+                    if (act && rr < nrows) {
+                        Raw<FMT> w;
+                        read_cell<FMT>(w, st, rr, lane, p0, p1, p2);
+                        const float ws = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(st + St::OFFS + rr * ps + ws_off));
+                        float2 *vrow = s_v + (size_t)(jj * RS + rr) * 33 + lane;
+                        if (NT == 1) {
+                            const int acc = cell_dot<FMT>(w, a, q[0], xsum[0]);
+                            const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
+                            *vrow = make_float2(__fmul_rn(__int2float_rn(dot), sx[0]), ws);
+                            if (DOTS) a.int_dots[(size_t)(row0 + rr) * a.nc + c] = dot;
+                        } else {
+                            uint32_t ub[16];
+                            decode<FMT>(w, a.cb, ub);
 #pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            const int acc = dot16<FMT>(ub, q[t]);
-                            const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
-                            s_tile[((size_t)t * a.tr + i) * stride + c] = make_float2(__fmul_rn(__int2float_rn(dot), sx[t]), ws);
-                            if (a.int_dots != nullptr && (uint32_t)t < a.n_tok)
-                                a.int_dots[((size_t)t * a.rows + row0 + i) * a.nc + c] = dot;
+                            for (int t = 0; t < NT; ++t) {
+                                const int acc = dot16<FMT>(ub, q[t]);
+                                const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
+                                vrow[(size_t)t * 32 * 33] = make_float2(__fmul_rn(__int2float_rn(dot), sx[t]), ws);
+                                if (DOTS && (uint32_t)t < a.n_tok) a.int_dots[((size_t)t * a.rows + row0 + rr) * a.nc + c] = dot;
+                            }
                         }
                     }
                 }
+                __syncwarp();                  // every lane has read the stage: refill it
+                issue(stage);
+                stage = stage + 1 == NSTAGE ? 0 : stage + 1;
             }
+            // fp32 chain over the chunks of this pass: lane -> row slot
+            if (slot_j < in_group) {
 #pragma unroll
-            for (int u = 0; u < UB; ++u) { cur[u] = nxt[u]; cur_ws[u] = nxt_ws[u]; }
-        }
-    }
-    __syncthreads();
-
-    // ordered fp32 chain: lane i of the tile's first warp owns row i (token t)
-    if (kw == 0) {
-        for (uint32_t item = lane; item < NT * trv; item += 32) {
-            const uint32_t t = item / trv, i = item % trv;
-            if (t >= a.n_tok) continue;
-            const float2 *vv = s_tile + ((size_t)t * a.tr + i) * stride;
-            float f = 0.0f;
-            for (uint32_t p = 0; p < np; ++p) {
-                const uint32_t nz = s_nz[t * np + p];
-                const uint32_t c_end = min(32u, a.nc - p * 32);
+                for (int t = 0; t < NT; ++t) {
+                    const float2 *vv = s_v + (size_t)t * 32 * 33 + (size_t)lane * 33;
+                    float ft = f[t];
 #pragma unroll 8
-                for (uint32_t l = 0; l < c_end; ++l) {
-                    const float2 v = vv[p * 32 + l];
-                    if ((nz >> l) & 1u) f = __fmaf_rn(v.x, v.y, f);
+                    for (uint32_t l = 0; l < n; ++l) {
+                        const float2 v = vv[l];
+                        if ((nz[t] >> l) & 1u) ft = __fmaf_rn(v.x, v.y, ft);
+                    }
+                    f[t] = ft;
                 }
             }
-            a.out[(size_t)t * a.out_stride + row0 + i] = f;
+            __syncwarp();                      // the tile is free for the next pass
+        }
+        if (slot_j < in_group) {
+            const uint32_t row = (gw + (j0 + slot_j) * nw) * RS + slot_r;
+            if (row < a.rows) {
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    if ((uint32_t)t < a.n_tok) a.out[(size_t)t * a.out_stride + row] = f[t];
+            }
         }
     }
 }
@@ -314,28 +412,30 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-static const size_t kSmemBudget = 196 * 1024;
-
-template <typename K>
-static cudaError_t allow_big_smem(K kernel, size_t smem) {
-    if (smem <= 48 * 1024) return cudaSuccess;
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
-}
-
-template <int FMT, int NT>
-static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, size_t smem, uint32_t grid) {
-    cudaError_t e = allow_big_smem(gemv_kernel<FMT, NT>, smem);
+template <int FMT, int NT, bool DOTS>
+static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_count) {
+    const uint32_t smem = warp_smem<FMT>(NT);
+    cudaError_t e = cudaSuccess;
+    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gemv_kernel<FMT, NT><<<grid, 32 * a.wk * a.tpc, smem, stream>>>(a);
+    // persistent grid of one-warp CTAs: as many as fit per SM (shared memory, 1 KiB reserved per CTA; at most 32)
+    uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
+    if (per_sm > 16) per_sm = 16;
+    if (per_sm == 0) return cudaErrorInvalidValue;
+    const uint32_t n_rb = (a.rows + RS - 1) / RS;
+    uint32_t grid = per_sm * (uint32_t)sm_count;
+    if (grid > n_rb) grid = n_rb;
+    gemv_kernel<FMT, NT, DOTS><<<grid, 32, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(cudaStream_t stream, const GemvArgs &a, uint32_t nt, size_t smem, uint32_t grid) {
+static cudaError_t launch_fmt(cudaStream_t stream, const GemvArgs &a, uint32_t nt, int sm_count) {
+    const bool dots = a.int_dots != nullptr;
     switch (nt) {
-        case 1: return launch_one<FMT, 1>(stream, a, smem, grid);
-        case 2: return launch_one<FMT, 2>(stream, a, smem, grid);
-        default: return launch_one<FMT, 4>(stream, a, smem, grid);
+        case 1: return dots ? launch_one<FMT, 1, true>(stream, a, sm_count) : launch_one<FMT, 1, false>(stream, a, sm_count);
+        case 2: return dots ? launch_one<FMT, 2, true>(stream, a, sm_count) : launch_one<FMT, 2, false>(stream, a, sm_count);
+        default: return dots ? launch_one<FMT, 4, true>(stream, a, sm_count) : launch_one<FMT, 4, false>(stream, a, sm_count);
     }
 }
 
@@ -343,16 +443,18 @@ uint32_t gemv_max_tokens(const DeviceMatrix &) { return 4; }
 
 cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs,
                         const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
-                        int sm_count, uint32_t *launches) {
+                        int sm_count, uint32_t *err_flag, uint32_t *launches) {
     const MatrixGeom &g = m.geom;
     if (launches) *launches = 0;
     if (n_tok == 0) return cudaSuccess;
     if (n_tok > 4 || g.fmt == FMT_NF5 || g.fmt == FMT_E8Q2) return cudaErrorNotSupported;
     const uint32_t nt = n_tok <= 1 ? 1 : n_tok <= 2 ? 2 : 4;
     GemvArgs a;
-    a.pa = m.d_a; a.pb = m.d_b; a.scales = m.d_scales; a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.int_dots = int_dots;
+    for (int k = 0; k < 3; ++k) { a.plane[k] = m.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; }
+    a.scales = reinterpret_cast<const uint16_t *>(m.d_base + g.scale_off);
+    a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.int_dots = int_dots; a.err_flag = err_flag;
     a.out_stride = out_stride;
-    a.rows = g.rows; a.cols = g.cols; a.nc = g.nc; a.nsg = g.nsg; a.sgc = g.sgc; a.n_tok = n_tok;
+    a.rows = g.rows; a.cols = g.cols; a.nc = g.nc; a.nsg = g.nsg; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.n_tok = n_tok;
     a.sgc_shift = 32;
     for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
     a.max_odd = g.max_odd; a.nf4_offset = g.nf4_offset;
@@ -365,28 +467,14 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
         a.tab[i] = (uint32_t)h[0] | ((uint32_t)h[1] << 8) | ((uint32_t)h[2] << 16) | ((uint32_t)h[3] << 24);
         a.tab[2 + i] = (uint32_t)l[0] | ((uint32_t)l[1] << 8) | ((uint32_t)l[2] << 16) | ((uint32_t)l[3] << 24);
     }
-    // tiling: K split over up to 4 warps (one 32-chunk pass each), rows per tile as large as still
-    // leaves about 16 warps per SM
-    const uint32_t np = (g.nc + 31) / 32;
-    a.wk = np < 4 ? np : 4;
-    const uint32_t want_warps = 16u * (uint32_t)sm_count;
-    a.tr = 32;
-    while (a.tr > 4 && ((g.rows + a.tr - 1) / a.tr) * a.wk < want_warps) a.tr /= 2;
-    a.tpc = a.wk >= 4 ? 1 : 4 / a.wk;
-    size_t smem = smem_plan(nt, g.nc, a.tr, a.tpc).total;
-    while (smem > kSmemBudget && a.tpc > 1) { a.tpc /= 2; smem = smem_plan(nt, g.nc, a.tr, a.tpc).total; }
-    while (smem > kSmemBudget && a.tr > 1) { a.tr /= 2; smem = smem_plan(nt, g.nc, a.tr, a.tpc).total; }
-    if (smem > kSmemBudget) return cudaErrorInvalidValue;
-    const uint32_t tiles = (g.rows + a.tr - 1) / a.tr;
-    const uint32_t grid = (tiles + a.tpc - 1) / a.tpc;
     const bool nf4_fast = g.fmt == FMT_NF4 && g.nf4_split_ok && (g.nf4_offset == 0 || xsum != nullptr);
     cudaError_t e;
     switch (g.fmt) {
-        case FMT_BP4: e = launch_fmt<FMT_BP4>(stream, a, nt, smem, grid); break;
-        case FMT_BP5: e = launch_fmt<FMT_BP5>(stream, a, nt, smem, grid); break;
-        case FMT_BP6: e = launch_fmt<FMT_BP6>(stream, a, nt, smem, grid); break;
-        case FMT_NF4: e = nf4_fast ? launch_fmt<FMT_NF4>(stream, a, nt, smem, grid) : launch_fmt<FMT_NF4G>(stream, a, nt, smem, grid); break;
-        case FMT_NF3: e = launch_fmt<FMT_NF3>(stream, a, nt, smem, grid); break;
+        case FMT_BP4: e = launch_fmt<FMT_BP4>(stream, a, nt, sm_count); break;
+        case FMT_BP5: e = launch_fmt<FMT_BP5>(stream, a, nt, sm_count); break;
+        case FMT_BP6: e = launch_fmt<FMT_BP6>(stream, a, nt, sm_count); break;
+        case FMT_NF4: e = nf4_fast ? launch_fmt<FMT_NF4>(stream, a, nt, sm_count) : launch_fmt<FMT_NF4G>(stream, a, nt, sm_count); break;
+        case FMT_NF3: e = launch_fmt<FMT_NF3>(stream, a, nt, sm_count); break;
         default: return cudaErrorNotSupported;
     }
     if (e == cudaSuccess && launches) *launches = 1;

@@ -10,10 +10,7 @@ namespace k2t {
 // Device-resident matrix (image produced by repack_matrix, uploaded once).
 struct DeviceMatrix {
     MatrixGeom geom;
-    uint8_t *d_base = nullptr;      // one allocation: plane A, plane B, scales
-    const uint8_t *d_a = nullptr;
-    const uint8_t *d_b = nullptr;
-    const uint16_t *d_scales = nullptr;
+    uint8_t *d_base = nullptr;      // one allocation: code planes, scales (offsets in geom)
     size_t device_bytes = 0;
 };
 
@@ -25,7 +22,7 @@ cudaError_t launch_fwht_quant(cudaStream_t stream, const float *x, const float *
 // in *launches. xsum may be null for NF formats.
 cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs,
                         const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
-                        int sm_count, uint32_t *launches);
+                        int sm_count, uint32_t *err_flag, uint32_t *launches);
 
 // Largest n_tok one launch_gemv call accepts for this matrix (shared-memory bound), at most 8.
 uint32_t gemv_max_tokens(const DeviceMatrix &m);

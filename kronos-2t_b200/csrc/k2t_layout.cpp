@@ -113,7 +113,7 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         if (d.bits < 4 || d.bits > 6) { err = "bipolar matrix: planes must be 4, 5 or 6"; return false; }
         g.fmt = (Format)(FMT_BP4 + (d.bits - 4));
         g.sgc = 1; g.nsg = g.nc; g.max_odd = (1 << d.bits) - 1;
-        g.cell_a = 32; g.cell_b = 8 * (d.bits - 4);
+        g.cell[0] = 16; g.cell[1] = 16; g.cell[2] = 8 * (d.bits - 4);
         size_t want0 = ns * (d.cols / 8) * d.bits * STRIPE, want1 = ns * g.nc * STRIPE * 2;
         if (d.len0 != want0 || d.len1 != want1 || !d.data0 || !d.data1) { err = "bipolar matrix: plane/scale byte counts do not match rows x cols"; return false; }
         g.file_bytes = want0 + want1;
@@ -122,7 +122,7 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         if (d.scale_group_chunks < 1 || d.scale_group_chunks > 8) { err = "NF matrix: scale_group_chunks must be 1..8"; return false; }
         g.fmt = d.bits == 4 ? FMT_NF4 : d.bits == 3 ? FMT_NF3 : d.bits == 5 ? FMT_NF5 : FMT_E8Q2;
         g.sgc = d.scale_group_chunks; g.nsg = (g.nc + g.sgc - 1) / g.sgc; g.max_odd = 0;
-        g.cell_a = d.bits >= 4 ? 32 : 16; g.cell_b = d.bits == 5 ? 8 : d.bits == 3 ? 8 : 0;
+        g.cell[0] = 16; g.cell[1] = d.bits >= 4 ? 16 : d.bits == 3 ? 8 : 0; g.cell[2] = d.bits == 5 ? 8 : 0;
         size_t cb = nf_chunk_bytes(d.bits);
         size_t want0 = (ns / 2) * ((size_t)g.nsg * 64 + (size_t)g.nc * 2 * cb);
         size_t want1 = (ns & 1) * ((size_t)g.nsg * 32 + (size_t)g.nc * cb);
@@ -159,9 +159,16 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         return false;
     }
     auto up16 = [](size_t x) { return (x + 15) & ~(size_t)15; };
-    g.plane_a = up16((size_t)g.rows * g.nc * g.cell_a);
-    g.plane_b = up16((size_t)g.rows * g.nc * g.cell_b);
-    g.scale_total = up16((size_t)g.rows * g.nsg * 2);
+    size_t off = 0;
+    for (int k = 0; k < 3; ++k) {
+        g.pitch[k] = (uint32_t)up16((size_t)g.nc * g.cell[k]);
+        g.plane_off[k] = off;
+        off += (size_t)g.rows * g.pitch[k];
+    }
+    g.nsg_pad = (g.nsg + 7) & ~7u;
+    g.scale_off = off;
+    off += (size_t)g.rows * g.nsg_pad * 2;
+    g.image_total = off + 16;
     return true;
 }
 
@@ -176,43 +183,47 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
         uint32_t blk = r / 128, w = r % 128;
         return w < 64 ? blk * 64 + w : inter + blk * 64 + (w - 64);
     };
-    uint8_t *plane_a = out, *plane_b = out + g.plane_a, *scales = out + g.plane_a + g.plane_b;
+    uint8_t *scales = out + g.scale_off;
 
     auto do_rows = [&](uint32_t r_lo, uint32_t r_hi) {
         for (uint32_t r_dst = r_lo; r_dst < r_hi; ++r_dst) {
             const uint32_t r = src_row(r_dst), lane = r % STRIPE;
+            uint8_t *row_k[3];
+            for (int k = 0; k < 3; ++k) row_k[k] = out + g.plane_off[k] + (size_t)r_dst * g.pitch[k];
+            uint8_t *row_s = scales + (size_t)r_dst * g.nsg_pad * 2;
             for (uint32_t c = 0; c < g.nc; ++c) {
-                const size_t cell = (size_t)r_dst * g.nc + c;
-                uint8_t *ca = plane_a + cell * g.cell_a;
-                uint8_t *cb = plane_b + cell * g.cell_b;
+                uint8_t *c0 = row_k[0] + (size_t)c * g.cell[0];
+                uint8_t *c1 = row_k[1] + (size_t)c * g.cell[1];
+                uint8_t *c2 = row_k[2] + (size_t)c * g.cell[2];
                 if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
-                    put_u16(scales + ((size_t)r_dst * g.nsg + c) * 2, fv.bp_scale(r, c));
+                    put_u16(row_s + (size_t)c * 2, fv.bp_scale(r, c));
                     for (uint32_t col = 0; col < 64; ++col) {
                         uint32_t u = fv.bp_code(r, c * 64 + col);
-                        uint32_t k = col % 8;
-                        ca[(col / 8) * 4 + (k % 4)] |= (uint8_t)((u & 0x0F) << (k < 4 ? 0 : 4));
+                        uint32_t k = col % 8, cc = col % 32;
+                        uint8_t *half = col < 32 ? c0 : c1;
+                        half[(cc / 8) * 4 + (k % 4)] |= (uint8_t)((u & 0x0F) << (k < 4 ? 0 : 4));
                         if (d.bits == 5) {
-                            uint32_t bit = 8 * (col % 4) + (col % 32) / 4;
-                            cb[(col / 32) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 1) << (bit % 8));
+                            uint32_t bit = 8 * (col % 4) + cc / 4;
+                            c2[(col / 32) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 1) << (bit % 8));
                         } else if (d.bits == 6) {
                             uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
-                            cb[(col / 16) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 3) << (bit % 8));
+                            c2[(col / 16) * 4 + bit / 8] |= (uint8_t)(((u >> 4) & 3) << (bit % 8));
                         }
                     }
                     continue;
                 }
                 const uint8_t *blk, *sc;
                 fv.nf_ptrs(r / STRIPE, c, blk, sc);
-                if (c % g.sgc == 0) put_u16(scales + ((size_t)r_dst * g.nsg + c / g.sgc) * 2, fv.nf_scale(r, c));
+                if (c % g.sgc == 0) put_u16(row_s + (size_t)(c / g.sgc) * 2, fv.nf_scale(r, c));
                 if (d.bits == 2) {
                     for (uint32_t eb8 = 0; eb8 < 8; ++eb8) {
                         uint8_t tpl, sgn;
                         fv.e8_codes(blk, lane, eb8, tpl, sgn);
-                        ca[2 * eb8] = tpl;
-                        ca[2 * eb8 + 1] = sgn;
+                        c0[2 * eb8] = tpl;
+                        c0[2 * eb8 + 1] = sgn;
                     }
                 } else if (d.bits == 3) {
-                    auto word_ptr = [&](uint32_t w) { return w < 4 ? ca + w * 4 : cb + (w - 4) * 4; };
+                    auto word_ptr = [&](uint32_t w) { return w < 4 ? c0 + w * 4 : c1 + (w - 4) * 4; };
                     for (uint32_t col = 0; col < 64; ++col) {
                         uint32_t idx = fv.nf_index(blk, lane, col);
                         if (col < 48) {
@@ -228,11 +239,12 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
                     for (uint32_t col = 0; col < 64; ++col) {
                         uint32_t idx = fv.nf_index(blk, lane, col);
                         if (d.bits == 4) idx = g.nf4_rank[idx];
-                        uint32_t nib = col % 8;
-                        ca[(col / 8) * 4 + nib / 2] |= (uint8_t)((idx & 0x0F) << (4 * (nib % 2)));
+                        uint32_t nib = col % 8, cc = col % 32;
+                        uint8_t *half = col < 32 ? c0 : c1;
+                        half[(cc / 8) * 4 + nib / 2] |= (uint8_t)((idx & 0x0F) << (4 * (nib % 2)));
                         if (d.bits == 5) {
-                            uint32_t bit = 8 * (col % 4) + (col % 32) / 4;
-                            cb[(col / 32) * 4 + bit / 8] |= (uint8_t)(((idx >> 4) & 1) << (bit % 8));
+                            uint32_t bit = 8 * (col % 4) + cc / 4;
+                            c2[(col / 32) * 4 + bit / 8] |= (uint8_t)(((idx >> 4) & 1) << (bit % 8));
                         }
                     }
                 }

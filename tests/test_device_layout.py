@@ -81,7 +81,7 @@ def decode_cell(fmt, ca, cb, cb_words):
     return np.array(u, dtype="<u4").view(np.uint8).view(dt)
 
 
-CELL_BYTES = {"bp4": (32, 0), "bp5": (32, 8), "bp6": (32, 16), "nf4": (32, 0), "nf3": (16, 8)}
+CELL_BYTES = {"bp4": (16, 16, 0), "bp5": (16, 16, 8), "bp6": (16, 16, 16), "nf4": (16, 16, 0), "nf3": (16, 8, 0)}
 
 
 def up16(x):
@@ -89,14 +89,22 @@ def up16(x):
 
 
 def split_image(fmt, image, rows, cols, nsg):
+    """-> (plane A bytes [rows, nc, a], plane B bytes [rows, nc, b], scales [rows, nsg]) where A is what
+    decode<FMT> sees first (32 B: planes 0+1 for 4-bit formats, 16 B for NF3) and B the rest."""
     nc = cols // 64
-    ca, cb = CELL_BYTES[fmt]
-    na, nb, ns = up16(rows * nc * ca), up16(rows * nc * cb), up16(rows * nsg * 2)
-    assert image.size == na + nb + ns
-    pa = image[: rows * nc * ca].reshape(rows, nc, ca)
-    pb = image[na: na + rows * nc * cb].reshape(rows, nc, cb) if cb else np.zeros((rows, nc, 0), np.uint8)
-    scales = image[na + nb: na + nb + rows * nsg * 2].view("<u2").reshape(rows, nsg)
-    return pa, pb, scales
+    cells = CELL_BYTES[fmt]
+    off, planes = 0, []
+    for cb in cells:
+        pitch = up16(nc * cb)
+        planes.append(image[off: off + rows * pitch].reshape(rows, pitch)[:, : nc * cb].reshape(rows, nc, cb))
+        off += rows * pitch
+    nsg_pad = (nsg + 7) & ~7
+    scales = image[off: off + rows * nsg_pad * 2].view("<u2").reshape(rows, nsg_pad)
+    assert not scales[:, nsg:].any()
+    assert image.size == off + rows * nsg_pad * 2 + 16
+    if fmt == "nf3":
+        return planes[0], planes[1], scales[:, :nsg]
+    return np.concatenate([planes[0], planes[1]], axis=2), planes[2], scales[:, :nsg]
 
 
 def image_rows(fmt, image, rows, cols, nsg, cb_words=None):
@@ -207,7 +215,7 @@ def test_malformed_descriptors_are_rejected(oracle):
     m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
     L = k2.load_library()
     good = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
-    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 16 * 32 + 16 * 2
+    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 2 * 16 * 16 + 16 * 8 * 2 + 16
     for kw in ({"cols": 65}, {"bits": 7}, {"rows": 0}, {"kind": 1}, {"len0": 5}):
         bad = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
         for key, val in kw.items():
