@@ -258,48 +258,45 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
     }
     __syncwarp();
 
-    const uint32_t cellb[3] = {Cell<FMT>::B0, Cell<FMT>::B1, Cell<FMT>::B2};
-    const uint32_t soff[3] = {St::OFF0, St::OFF1, St::OFF2};
+    // ---- producer role of this lane: which run of bytes it copies for every unit.
+    // merged: lane k < NPL copies plane k (or the scales) of the whole block; otherwise lane
+    // rr*NPL + k copies row rr of plane k.  Everything that does not depend on the unit is fixed here.
+    const uint32_t my_k = lane % St::NPL, my_rr = lane / St::NPL;
+    const bool my_scale = my_k == St::NPL - 1;
+    const uint32_t my_cell = my_scale ? 0u : (my_k == 0 ? (uint32_t)Cell<FMT>::B0 : my_k == 1 ? (uint32_t)Cell<FMT>::B1 : (uint32_t)Cell<FMT>::B2);
+    const uint32_t my_pitch = my_scale ? a.nsg_pad * 2 : a.pitch[my_scale ? 0 : my_k];
+    const uint8_t *my_base = my_scale ? reinterpret_cast<const uint8_t *>(a.scales) : a.plane[my_scale ? 0 : my_k];
+    const uint32_t my_soff = my_scale ? St::OFFS : (my_k == 0 ? St::OFF0 : my_k == 1 ? St::OFF1 : St::OFF2);
+    const uint32_t my_spitch = my_scale ? (uint32_t)SCALE_PITCH : 32u * my_cell;       // stage pitch when not merged
+    const bool my_role = merged ? my_rr == 0 : my_rr < RS;
+    uint32_t sum_pitch = a.nsg_pad * 2;                         // bytes of one row over all planes (merged case)
+#pragma unroll
+    for (int k = 0; k < 3; ++k) sum_pitch += (k == 0 || (k == 1 && Cell<FMT>::B1) || (k == 2 && Cell<FMT>::B2)) ? a.pitch[k] : 0u;
 
-    // ---- producer: unit (j, p) = block gw + j*nw, pass p; order: 8 blocks of a pass, then the next pass
     uint32_t pj0 = 0, pp = 0, pjj = 0;          // producer cursor (first block of the 32-row group, pass, block in group)
     auto issue = [&](uint32_t stage) {
         if (pj0 >= J) return;                                   // nothing left: the stage stays idle
-        const uint32_t j = pj0 + pjj;
-        const uint32_t row0 = (gw + j * nw) * RS;
+        const uint32_t row0 = (gw + (pj0 + pjj) * nw) * RS;
         const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
-        const uint32_t c0 = pp * 32, n = min(32u, a.nc - c0);
-        const uint32_t sg0 = scale_group_of(a, c0), sg1 = scale_group_of(a, c0 + n - 1), sga = sg0 & ~7u;
         const uint32_t bar = bar0 + 8 * stage;
-        const uint32_t dst0 = stage_sa + stage * St::BYTES;
-        // what lane `lane` copies: merged -> one run per plane; else one run per (row, plane)
-        const uint32_t k = lane % St::NPL, rr = lane / St::NPL;
-        const bool is_scale = k == St::NPL - 1;
-        uint32_t bytes = 0, dst = 0;
-        const uint8_t *src = nullptr;
+        uint32_t bytes, total, dst = stage_sa + stage * St::BYTES + my_soff;
+        const uint8_t *src;
         if (merged) {
-            if (rr == 0) {
-                if (is_scale) { bytes = nrows * a.nsg_pad * 2; src = reinterpret_cast<const uint8_t *>(a.scales) + (size_t)row0 * a.nsg_pad * 2; dst = dst0 + St::OFFS; }
-                else { bytes = nrows * a.pitch[k]; src = a.plane[k] + (size_t)row0 * a.pitch[k]; dst = dst0 + soff[k]; }
-            }
-        } else if (rr < nrows) {
-            if (is_scale) {
-                bytes = up16((sg1 - sga + 1) * 2);
-                src = reinterpret_cast<const uint8_t *>(a.scales) + ((size_t)(row0 + rr) * a.nsg_pad + sga) * 2;
-                dst = dst0 + St::OFFS + rr * SCALE_PITCH;
-            } else {
-                bytes = up16(n * cellb[k]);
-                src = a.plane[k] + (size_t)(row0 + rr) * a.pitch[k] + (size_t)c0 * cellb[k];
-                dst = dst0 + soff[k] + rr * 32 * cellb[k];
-            }
+            bytes = nrows * my_pitch;
+            total = nrows * sum_pitch;
+            src = my_base + (size_t)row0 * my_pitch;
+        } else {
+            const uint32_t c0 = pp * 32, n = min(32u, a.nc - c0);
+            const uint32_t sga = scale_group_of(a, c0) & ~7u;
+            const uint32_t sbytes = up16((scale_group_of(a, c0 + n - 1) - sga + 1) * 2);
+            bytes = my_scale ? sbytes : up16(n * my_cell);
+            total = nrows * (sbytes + up16(n * Cell<FMT>::B0) + up16(n * Cell<FMT>::B1) + up16(n * Cell<FMT>::B2));
+            src = my_base + (size_t)(row0 + my_rr) * my_pitch + (my_scale ? sga * 2 : c0 * my_cell);
+            dst += my_rr * my_spitch;
         }
-        uint32_t total = bytes;
-#pragma unroll
-        for (uint32_t m = 16; m > 0; m >>= 1) total += __shfl_xor_sync(0xffffffffu, total, m);
         if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, total); }
         __syncwarp();
-        if (bytes) bulk_g2s(dst, src, bytes, bar);
-        // advance the cursor
+        if (my_role && my_rr < nrows) bulk_g2s(dst, src, bytes, bar);
         const uint32_t in_group = min(8u, J - pj0);
         if (++pjj == in_group) { pjj = 0; if (++pp == np) { pp = 0; pj0 += 8; } }
     };
@@ -336,7 +333,7 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
                 }
             }
             // stage geometry of this pass
-            const uint32_t sg0 = scale_group_of(a, p * 32), sga = merged ? 0 : (sg0 & ~7u);
+            const uint32_t sga = merged ? 0 : (scale_group_of(a, p * 32) & ~7u);
             const uint32_t p0 = merged ? a.pitch[0] : 32 * Cell<FMT>::B0, p1 = merged ? a.pitch[1] : 32 * Cell<FMT>::B1;
             const uint32_t p2 = merged ? a.pitch[2] : 32 * Cell<FMT>::B2, ps = merged ? a.nsg_pad * 2 : SCALE_PITCH;
             const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - sga) * 2;
@@ -344,8 +341,7 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
             for (uint32_t jj = 0; jj < in_group; ++jj) {
                 const uint32_t row0 = (gw + (j0 + jj) * nw) * RS;
                 const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
-                // wait for the stage (bounded)
-                uint32_t ok = 0;
+                uint32_t ok = 0;                // wait for the stage (bounded)
                 for (uint32_t spin = 0; spin < WAIT_LIMIT && !ok; ++spin) ok = mbar_try_wait(bar0 + 8 * stage, (phase >> stage) & 1u);
                 if (__any_sync(0xffffffffu, !ok)) {
                     if (lane == 0) atomicExch(a.err_flag, 1u);
@@ -353,26 +349,40 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
                 }
                 phase ^= 1u << stage;
                 const uint8_t *st = stages + stage * St::BYTES;
+                // all four rows are read and reduced unconditionally (stale bytes of absent rows are
+                // harmless): no branches, so the four independent dot chains interleave
+                Raw<FMT> w[RS];
+                float ws[RS];
 #pragma unroll
                 for (uint32_t rr = 0; rr < RS; ++rr) {
-                    if (act && rr < nrows) {
-                        Raw<FMT> w;
-                        read_cell<FMT>(w, st, rr, lane, p0, p1, p2);
-                        const float ws = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(st + St::OFFS + rr * ps + ws_off));
-                        float2 *vrow = s_v + (size_t)(jj * RS + rr) * 33 + lane;
-                        if (NT == 1) {
-                            const int acc = cell_dot<FMT>(w, a, q[0], xsum[0]);
-                            const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
-                            *vrow = make_float2(__fmul_rn(__int2float_rn(dot), sx[0]), ws);
-                            if (DOTS) a.int_dots[(size_t)(row0 + rr) * a.nc + c] = dot;
-                        } else {
-                            uint32_t ub[16];
-                            decode<FMT>(w, a.cb, ub);
+                    read_cell<FMT>(w[rr], st, rr, lane, p0, p1, p2);
+                    ws[rr] = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(st + St::OFFS + rr * ps + ws_off));
+                }
+                if (NT == 1) {
+                    int dot[RS];
 #pragma unroll
-                            for (int t = 0; t < NT; ++t) {
-                                const int acc = dot16<FMT>(ub, q[t]);
-                                const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
-                                vrow[(size_t)t * 32 * 33] = make_float2(__fmul_rn(__int2float_rn(dot), sx[t]), ws);
+                    for (uint32_t rr = 0; rr < RS; ++rr) {
+                        const int acc = cell_dot<FMT>(w[rr], a, q[0], xsum[0]);
+                        dot[rr] = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
+                    }
+#pragma unroll
+                    for (uint32_t rr = 0; rr < RS; ++rr) {
+                        if (act && rr < nrows) {
+                            s_v[(size_t)(jj * RS + rr) * 33 + lane] = make_float2(__fmul_rn(__int2float_rn(dot[rr]), sx[0]), ws[rr]);
+                            if (DOTS) a.int_dots[(size_t)(row0 + rr) * a.nc + c] = dot[rr];
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t rr = 0; rr < RS; ++rr) {
+                        uint32_t ub[16];
+                        decode<FMT>(w[rr], a.cb, ub);
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            const int acc = dot16<FMT>(ub, q[t]);
+                            const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
+                            if (act && rr < nrows) {
+                                s_v[(size_t)t * 32 * 33 + (size_t)(jj * RS + rr) * 33 + lane] = make_float2(__fmul_rn(__int2float_rn(dot), sx[t]), ws[rr]);
                                 if (DOTS && (uint32_t)t < a.n_tok) a.int_dots[((size_t)t * a.rows + row0 + rr) * a.nc + c] = dot;
                             }
                         }
@@ -388,10 +398,14 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
                 for (int t = 0; t < NT; ++t) {
                     const float2 *vv = s_v + (size_t)t * 32 * 33 + (size_t)lane * 33;
                     float ft = f[t];
+                    if (nz[t] == (n == 32 ? 0xffffffffu : (1u << n) - 1u)) {
 #pragma unroll 8
-                    for (uint32_t l = 0; l < n; ++l) {
-                        const float2 v = vv[l];
-                        if ((nz[t] >> l) & 1u) ft = __fmaf_rn(v.x, v.y, ft);
+                        for (uint32_t l = 0; l < n; ++l) { const float2 v = vv[l]; ft = __fmaf_rn(v.x, v.y, ft); }
+                    } else {
+                        for (uint32_t l = 0; l < n; ++l) {
+                            const float2 v = vv[l];
+                            if ((nz[t] >> l) & 1u) ft = __fmaf_rn(v.x, v.y, ft);
+                        }
                     }
                     f[t] = ft;
                 }
