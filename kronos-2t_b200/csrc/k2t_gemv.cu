@@ -156,8 +156,8 @@ __device__ __forceinline__ int cell_dot(const Raw<FMT> &w, const GemvArgs &a, co
             const uint32_t x = w.w[i], y = x ^ 0x88888888u;
             up = dp4a_us(prmt(a.tab[0], a.tab[1], y), q[2 * i], up);
             dn = dp4a_us(prmt(a.tab[2], a.tab[3], x), q[2 * i], dn);
-            up = dp4a_us(prmt(a.tab[0], a.tab[1], __umulhi(y, 65536u)), q[2 * i + 1], up);   // >> 16 on the FMA pipe
-            dn = dp4a_us(prmt(a.tab[2], a.tab[3], __umulhi(x, 65536u)), q[2 * i + 1], dn);
+            up = dp4a_us(prmt(a.tab[0], a.tab[1], y >> 16), q[2 * i + 1], up);
+            dn = dp4a_us(prmt(a.tab[2], a.tab[3], __umulhi(x, 65536u)), q[2 * i + 1], dn);   // >> 16 on the FMA pipe
         }
         return up - dn + a.nf4_offset * xsum_c;
     } else {
@@ -196,7 +196,7 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 constexpr int RS = 4;           // rows per stage (one 4-row block, one pass)
-constexpr int NSTAGE = 3;       // stages per warp
+constexpr int NSTAGE = 2;       // stages per warp
 constexpr int SCALE_PITCH = 80; // bytes reserved per row for the scales of a pass (32 bf16 + alignment slack)
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -209,9 +209,10 @@ template <int FMT> struct Stage {
     static constexpr uint32_t NPL = 1 + (Cell<FMT>::B1 ? 1 : 0) + (Cell<FMT>::B2 ? 1 : 0) + 1;   // code planes + scales
 };
 
-// shared memory of one warp: stages, (v, w_scale) tile [NT][32][33], mbarriers
+// shared memory of one warp: stages, v tile float [NT][32][33], w_scale tile bf16 [32][34], mbarriers
+constexpr uint32_t TILE_V = 32 * 33 * 4, TILE_WS = 32 * 34 * 2;
 template <int FMT> __host__ __device__ constexpr uint32_t warp_smem(uint32_t nt) {
-    return NSTAGE * Stage<FMT>::BYTES + nt * 32 * 33 * 8 + 64;
+    return NSTAGE * Stage<FMT>::BYTES + nt * TILE_V + TILE_WS + 64;
 }
 
 template <int FMT>
@@ -235,22 +236,29 @@ __device__ __forceinline__ void read_cell(Raw<FMT> &o, const uint8_t *st, uint32
     }
 }
 
+// blockDim.x = 32 * WK.  WK = 1: every warp is on its own.  WK > 1 (long rows, few of them): the WK
+// warps of a CTA share the CTA's row blocks and split the passes (warp w takes passes w, w + WK, ...);
+// the fp32 chain is handed from pass to pass through shared memory in pass order.
 template <int FMT, int NT, bool DOTS>
-__global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
     using St = Stage<FMT>;
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t lane = threadIdx.x;
+    const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, WK = blockDim.x >> 5;
     const uint32_t gw = blockIdx.x, nw = gridDim.x;
     const uint32_t n_rb = (a.rows + RS - 1) / RS;              // 4-row blocks of the matrix
-    if (gw >= n_rb) return;
-    const uint32_t J = (n_rb - gw + nw - 1) / nw;              // blocks of this warp: gw, gw + nw, ...
+    const uint32_t J = gw < n_rb ? (n_rb - gw + nw - 1) / nw : 0;   // blocks of this CTA: gw, gw + nw, ...
     const uint32_t np = (a.nc + 31) / 32;
+    const uint32_t my_np = wid < np ? (np - wid + WK - 1) / WK : 0; // passes of this warp: wid, wid + WK, ...
+    const uint32_t rounds = (np + WK - 1) / WK;
     const bool merged = np == 1;                               // a block's rows are contiguous in every plane
 
-    uint8_t *stages = smem;
-    float2 *s_v = reinterpret_cast<float2 *>(smem + NSTAGE * St::BYTES);
-    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(smem + NSTAGE * St::BYTES + NT * 32 * 33 * 8);
+    uint8_t *wsm = smem + (size_t)wid * warp_smem<FMT>(NT);
+    uint8_t *stages = wsm;
+    float *s_v = reinterpret_cast<float *>(wsm + NSTAGE * St::BYTES);
+    uint16_t *s_ws = reinterpret_cast<uint16_t *>(wsm + NSTAGE * St::BYTES + NT * TILE_V);
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(wsm + NSTAGE * St::BYTES + NT * TILE_V + TILE_WS);
     const uint32_t stage_sa = (uint32_t)__cvta_generic_to_shared(stages);
+    float *s_f = reinterpret_cast<float *>(smem + (size_t)WK * warp_smem<FMT>(NT));   // [NT][32] chain hand-off
     if (lane == 0) {
         for (int s = 0; s < NSTAGE; ++s) mbar_init(bar0 + 8 * s, 1);
         fence_mbar_init();
@@ -273,9 +281,10 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
 #pragma unroll
     for (int k = 0; k < 3; ++k) sum_pitch += (k == 0 || (k == 1 && Cell<FMT>::B1) || (k == 2 && Cell<FMT>::B2)) ? a.pitch[k] : 0u;
 
-    uint32_t pj0 = 0, pp = 0, pjj = 0;          // producer cursor (first block of the 32-row group, pass, block in group)
+    // producer cursor: 32-row group, own pass index, block in group
+    uint32_t pj0 = 0, ppi = 0, pjj = 0;
     auto issue = [&](uint32_t stage) {
-        if (pj0 >= J) return;                                   // nothing left: the stage stays idle
+        if (pj0 >= J || my_np == 0) return;                     // nothing left: the stage stays idle
         const uint32_t row0 = (gw + (pj0 + pjj) * nw) * RS;
         const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
         const uint32_t bar = bar0 + 8 * stage;
@@ -286,7 +295,7 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
             total = nrows * sum_pitch;
             src = my_base + (size_t)row0 * my_pitch;
         } else {
-            const uint32_t c0 = pp * 32, n = min(32u, a.nc - c0);
+            const uint32_t c0 = (wid + ppi * WK) * 32, n = min(32u, a.nc - c0);
             const uint32_t sga = scale_group_of(a, c0) & ~7u;
             const uint32_t sbytes = up16((scale_group_of(a, c0 + n - 1) - sga + 1) * 2);
             bytes = my_scale ? sbytes : up16(n * my_cell);
@@ -298,7 +307,7 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
         __syncwarp();
         if (my_role && my_rr < nrows) bulk_g2s(dst, src, bytes, bar);
         const uint32_t in_group = min(8u, J - pj0);
-        if (++pjj == in_group) { pjj = 0; if (++pp == np) { pp = 0; pj0 += 8; } }
+        if (++pjj == in_group) { pjj = 0; if (++ppi == my_np) { ppi = 0; pj0 += 8; } }
     };
 #pragma unroll
     for (int s = 0; s < NSTAGE; ++s) issue(s);
@@ -309,115 +318,119 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
     int xsum[NT];
     uint32_t nz[NT];
     uint32_t stage = 0, phase = 0;
+    bool failed = false;                                         // a wait gave up: keep the barriers in step, skip waiting
     const uint32_t slot_j = lane / RS, slot_r = lane % RS;       // chain: lane -> (block in group, row in block)
     for (uint32_t j0 = 0; j0 < J; j0 += 8) {
         const uint32_t in_group = min(8u, J - j0);
-        float f[NT];
-#pragma unroll
-        for (int t = 0; t < NT; ++t) f[t] = 0.0f;
-        for (uint32_t p = 0; p < np; ++p) {
-            const uint32_t c = p * 32 + lane, n = min(32u, a.nc - p * 32);
+        for (uint32_t r = 0; r < rounds; ++r) {
+            const uint32_t p = r * WK + wid;
+            const bool has = p < np;
+            const uint32_t c = p * 32 + lane, n = has ? min(32u, a.nc - p * 32) : 0;
             const bool act = lane < n;
-            if (np > 1 || j0 == 0) {          // this lane's activation chunk(s) for the pass, kept in registers
+            if (has) {
+                if (my_np > 1 || j0 == 0) {       // this lane's activation chunk(s) for the pass, kept in registers
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    const bool on = act && (uint32_t)t < a.n_tok;
-                    sx[t] = on ? __ldg(a.xs + (size_t)t * a.nc + c) : 0.0f;
-                    xsum[t] = (on && a.xsum != nullptr) ? __ldg(a.xsum + (size_t)t * a.nc + c) : 0;
+                    for (int t = 0; t < NT; ++t) {
+                        const bool on = act && (uint32_t)t < a.n_tok;
+                        sx[t] = on ? __ldg(a.xs + (size_t)t * a.nc + c) : 0.0f;
+                        xsum[t] = (on && a.xsum != nullptr) ? __ldg(a.xsum + (size_t)t * a.nc + c) : 0;
 #pragma unroll
-                    for (int jq = 0; jq < 4; ++jq) {
-                        const int4 v = on ? __ldg(reinterpret_cast<const int4 *>(a.xq + (size_t)t * a.cols + (size_t)c * 64) + jq) : make_int4(0, 0, 0, 0);
-                        q[t][4 * jq] = v.x; q[t][4 * jq + 1] = v.y; q[t][4 * jq + 2] = v.z; q[t][4 * jq + 3] = v.w;
+                        for (int jq = 0; jq < 4; ++jq) {
+                            const int4 v = on ? __ldg(reinterpret_cast<const int4 *>(a.xq + (size_t)t * a.cols + (size_t)c * 64) + jq) : make_int4(0, 0, 0, 0);
+                            q[t][4 * jq] = v.x; q[t][4 * jq + 1] = v.y; q[t][4 * jq + 2] = v.z; q[t][4 * jq + 3] = v.w;
+                        }
+                        nz[t] = __ballot_sync(0xffffffffu, sx[t] != 0.0f);
                     }
-                    nz[t] = __ballot_sync(0xffffffffu, sx[t] != 0.0f);
                 }
-            }
-            // stage geometry of this pass
-            const uint32_t sga = merged ? 0 : (scale_group_of(a, p * 32) & ~7u);
-            const uint32_t p0 = merged ? a.pitch[0] : 32 * Cell<FMT>::B0, p1 = merged ? a.pitch[1] : 32 * Cell<FMT>::B1;
-            const uint32_t p2 = merged ? a.pitch[2] : 32 * Cell<FMT>::B2, ps = merged ? a.nsg_pad * 2 : SCALE_PITCH;
-            const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - sga) * 2;
+                // stage geometry of this pass
+                const uint32_t sga = merged ? 0 : (scale_group_of(a, p * 32) & ~7u);
+                const uint32_t p0 = merged ? a.pitch[0] : 32 * Cell<FMT>::B0, p1 = merged ? a.pitch[1] : 32 * Cell<FMT>::B1;
+                const uint32_t p2 = merged ? a.pitch[2] : 32 * Cell<FMT>::B2, ps = merged ? a.nsg_pad * 2 : SCALE_PITCH;
+                const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - sga) * 2;
 
-            for (uint32_t jj = 0; jj < in_group; ++jj) {
-                const uint32_t row0 = (gw + (j0 + jj) * nw) * RS;
-                const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
-                uint32_t ok = 0;                // wait for the stage (bounded)
-                for (uint32_t spin = 0; spin < WAIT_LIMIT && !ok; ++spin) ok = mbar_try_wait(bar0 + 8 * stage, (phase >> stage) & 1u);
-                if (__any_sync(0xffffffffu, !ok)) {
-                    if (lane == 0) atomicExch(a.err_flag, 1u);
-                    return;
-                }
-                phase ^= 1u << stage;
-                const uint8_t *st = stages + stage * St::BYTES;
-                // all four rows are read and reduced unconditionally (stale bytes of absent rows are
-                // harmless): no branches, so the four independent dot chains interleave
-                Raw<FMT> w[RS];
-                float ws[RS];
-#pragma unroll
-                for (uint32_t rr = 0; rr < RS; ++rr) {
-                    read_cell<FMT>(w[rr], st, rr, lane, p0, p1, p2);
-                    ws[rr] = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(st + St::OFFS + rr * ps + ws_off));
-                }
-                if (NT == 1) {
-                    int dot[RS];
-#pragma unroll
-                    for (uint32_t rr = 0; rr < RS; ++rr) {
-                        const int acc = cell_dot<FMT>(w[rr], a, q[0], xsum[0]);
-                        dot[rr] = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
-                    }
-#pragma unroll
-                    for (uint32_t rr = 0; rr < RS; ++rr) {
-                        if (act && rr < nrows) {
-                            s_v[(size_t)(jj * RS + rr) * 33 + lane] = make_float2(__fmul_rn(__int2float_rn(dot[rr]), sx[0]), ws[rr]);
-                            if (DOTS) a.int_dots[(size_t)(row0 + rr) * a.nc + c] = dot[rr];
+                for (uint32_t jj = 0; jj < in_group; ++jj) {
+                    const uint32_t row0 = (gw + (j0 + jj) * nw) * RS;
+                    const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
+                    if (!failed) {                 // wait for the stage (bounded)
+                        uint32_t ok = 0;
+                        for (uint32_t spin = 0; spin < WAIT_LIMIT && !ok; ++spin) ok = mbar_try_wait(bar0 + 8 * stage, (phase >> stage) & 1u);
+                        if (__any_sync(0xffffffffu, !ok)) {
+                            if (lane == 0) atomicExch(a.err_flag, 1u);
+                            failed = true;
                         }
                     }
-                } else {
+                    phase ^= 1u << stage;
+                    const uint8_t *st = stages + stage * St::BYTES;
+                    // all four rows are read and reduced unconditionally (stale bytes of absent rows are
+                    // harmless): no branches, so the four independent dot chains interleave
+                    Raw<FMT> w[RS];
+                    uint16_t wsb[RS];
 #pragma unroll
                     for (uint32_t rr = 0; rr < RS; ++rr) {
-                        uint32_t ub[16];
-                        decode<FMT>(w[rr], a.cb, ub);
+                        read_cell<FMT>(w[rr], st, rr, lane, p0, p1, p2);
+                        wsb[rr] = *reinterpret_cast<const uint16_t *>(st + St::OFFS + rr * ps + ws_off);
+                    }
+                    if (NT == 1) {
+                        int dot[RS];
 #pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            const int acc = dot16<FMT>(ub, q[t]);
-                            const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
+                        for (uint32_t rr = 0; rr < RS; ++rr) {
+                            const int acc = cell_dot<FMT>(w[rr], a, q[0], xsum[0]);
+                            dot[rr] = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[0] : acc;
+                        }
+#pragma unroll
+                        for (uint32_t rr = 0; rr < RS; ++rr) {
                             if (act && rr < nrows) {
-                                s_v[(size_t)t * 32 * 33 + (size_t)(jj * RS + rr) * 33 + lane] = make_float2(__fmul_rn(__int2float_rn(dot), sx[t]), ws[rr]);
-                                if (DOTS && (uint32_t)t < a.n_tok) a.int_dots[((size_t)t * a.rows + row0 + rr) * a.nc + c] = dot;
+                                s_v[(jj * RS + rr) * 33 + lane] = __fmul_rn(__int2float_rn(dot[rr]), sx[0]);
+                                s_ws[(jj * RS + rr) * 34 + lane] = wsb[rr];
+                                if (DOTS) a.int_dots[(size_t)(row0 + rr) * a.nc + c] = dot[rr];
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t rr = 0; rr < RS; ++rr) {
+                            uint32_t ub[16];
+                            decode<FMT>(w[rr], a.cb, ub);
+                            if (act && rr < nrows) s_ws[(jj * RS + rr) * 34 + lane] = wsb[rr];
+#pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                const int acc = dot16<FMT>(ub, q[t]);
+                                const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
+                                if (act && rr < nrows) {
+                                    s_v[t * (32 * 33) + (jj * RS + rr) * 33 + lane] = __fmul_rn(__int2float_rn(dot), sx[t]);
+                                    if (DOTS && (uint32_t)t < a.n_tok) a.int_dots[((size_t)t * a.rows + row0 + rr) * a.nc + c] = dot;
+                                }
                             }
                         }
                     }
+                    __syncwarp();                  // every lane has read the stage: refill it
+                    issue(stage);
+                    stage = stage + 1 == NSTAGE ? 0 : stage + 1;
                 }
-                __syncwarp();                  // every lane has read the stage: refill it
-                issue(stage);
-                stage = stage + 1 == NSTAGE ? 0 : stage + 1;
+                __syncwarp();
             }
-            // fp32 chain over the chunks of this pass: lane -> row slot
-            if (slot_j < in_group) {
+            // fp32 chain over the chunks of the passes of this round, in pass order: warp k continues
+            // where warp k-1 stopped (f travels through s_f); lane -> row slot
+            for (uint32_t k = 0; k < WK; ++k) {
+                if (k == wid && has && slot_j < in_group) {
+                    const uint32_t row = (gw + (j0 + slot_j) * nw) * RS + slot_r;
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    const float2 *vv = s_v + (size_t)t * 32 * 33 + (size_t)lane * 33;
-                    float ft = f[t];
-                    if (nz[t] == (n == 32 ? 0xffffffffu : (1u << n) - 1u)) {
+                    for (int t = 0; t < NT; ++t) {
+                        const float *vv = s_v + t * (32 * 33) + lane * 33;
+                        const uint16_t *wv = s_ws + lane * 34;
+                        float ft = p == 0 ? 0.0f : s_f[t * 32 + lane];
+                        if (nz[t] == (n == 32 ? 0xffffffffu : (1u << n) - 1u)) {
 #pragma unroll 8
-                        for (uint32_t l = 0; l < n; ++l) { const float2 v = vv[l]; ft = __fmaf_rn(v.x, v.y, ft); }
-                    } else {
-                        for (uint32_t l = 0; l < n; ++l) {
-                            const float2 v = vv[l];
-                            if ((nz[t] >> l) & 1u) ft = __fmaf_rn(v.x, v.y, ft);
+                            for (uint32_t l = 0; l < n; ++l) ft = __fmaf_rn(vv[l], bf16_bits_to_f32(wv[l]), ft);
+                        } else {
+                            for (uint32_t l = 0; l < n; ++l)
+                                if ((nz[t] >> l) & 1u) ft = __fmaf_rn(vv[l], bf16_bits_to_f32(wv[l]), ft);
                         }
+                        if (p + 1 == np) { if (row < a.rows && (uint32_t)t < a.n_tok) a.out[(size_t)t * a.out_stride + row] = ft; }
+                        else s_f[t * 32 + lane] = ft;
                     }
-                    f[t] = ft;
                 }
-            }
-            __syncwarp();                      // the tile is free for the next pass
-        }
-        if (slot_j < in_group) {
-            const uint32_t row = (gw + (j0 + slot_j) * nw) * RS + slot_r;
-            if (row < a.rows) {
-#pragma unroll
-                for (int t = 0; t < NT; ++t)
-                    if ((uint32_t)t < a.n_tok) a.out[(size_t)t * a.out_stride + row] = f[t];
+                if (WK > 1) __syncthreads();
+                else __syncwarp();
             }
         }
     }
@@ -428,18 +441,24 @@ __global__ void __launch_bounds__(32) gemv_kernel(const GemvArgs a) {
 // ------------------------------------------------------------------------------------------------
 template <int FMT, int NT, bool DOTS>
 static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_count) {
-    const uint32_t smem = warp_smem<FMT>(NT);
+    const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
+    // warps per CTA: split the passes when rows alone give fewer than ~12 warps per SM
+    uint32_t wk = 1;
+    while (wk < 8 && wk * 2 <= np && n_rb * wk < 12u * (uint32_t)sm_count) wk *= 2;
+    const uint32_t smem = wk * warp_smem<FMT>(NT) + NT * 32 * 4;
     cudaError_t e = cudaSuccess;
     if (smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    // persistent grid of one-warp CTAs: as many as fit per SM (shared memory, 1 KiB reserved per CTA; at most 32)
+    // persistent grid: as many CTAs as fit per SM (shared memory, 1 KiB reserved per CTA; <= 2048 threads),
+    // then evened out so that every CTA gets the same number of row blocks
     uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
-    if (per_sm > 16) per_sm = 16;
-    if (per_sm == 0) return cudaErrorInvalidValue;
-    const uint32_t n_rb = (a.rows + RS - 1) / RS;
-    uint32_t grid = per_sm * (uint32_t)sm_count;
-    if (grid > n_rb) grid = n_rb;
-    gemv_kernel<FMT, NT, DOTS><<<grid, 32, smem, stream>>>(a);
+    per_sm = per_sm < 1 ? 1 : per_sm;
+    if (per_sm > 32) per_sm = 32;
+    if (per_sm * wk > 48) per_sm = 48 / wk;
+    uint32_t max_grid = per_sm * (uint32_t)sm_count;
+    const uint32_t per_cta = (n_rb + max_grid - 1) / max_grid;
+    const uint32_t grid = (n_rb + per_cta - 1) / per_cta;
+    gemv_kernel<FMT, NT, DOTS><<<grid, 32 * wk, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
