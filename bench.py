@@ -227,10 +227,14 @@ def run_b200(args, rank, world, local_rank):
         cases.append(case)
     bytes_per_step = sum(c["bytes"] for c in cases)
 
-    def step():
+    for c in cases:
+        c["p"] = (c["x"].data_ptr(), c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr(), c["out"].data_ptr())
+
+    def step_launches():
         for c in cases:
-            ctx.fwht_quant_dev(c["x"].data_ptr(), 1, c["m"]["cols"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr())
-            ctx.gemv_dev(c["dm"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr(), 1, c["out"].data_ptr())
+            px, pq, ps, pm, po = c["p"]
+            ctx.fwht_quant_dev(px, 1, c["m"]["cols"], pq, ps, pm)
+            ctx.gemv_dev(c["dm"], pq, ps, pm, 1, po)
 
     def step_e2e():
         for c in cases:
@@ -241,6 +245,19 @@ def run_b200(args, rank, world, local_rank):
         if dist:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # one step = one CUDA graph (32 kernel nodes): decode loops are launch-bound otherwise
+    step_launches()
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step_launches()
+    launches_per_step = ctx.launch_count - l0
+    ctx.set_stream(stream.cuda_stream)
+
+    def step():
+        graph.replay()
 
     def timed(fn, steps, sample_clocks=False):
         sampler = ClockSampler(local_rank) if sample_clocks else None
@@ -263,45 +280,59 @@ def run_b200(args, rank, world, local_rank):
 
     for _ in range(max(args.warmup, 3)):
         step()
-    launches0 = ctx.launch_count
     ms, clocks = timed(step, args.steps, sample_clocks=True)
-    gpu_launches = ctx.launch_count - launches0
+    gpu_launches = launches_per_step * args.steps
     value = bytes_per_step * world * args.steps / (ms / 1e3) / 1e9
 
     for _ in range(3):
         step_e2e()
-    ms_e2e, _ = timed(step_e2e, args.steps)
-    e2e_value = bytes_per_step * world * args.steps / (ms_e2e / 1e3) / 1e9
+    e2e_steps = min(args.steps, 50)
+    ms_e2e, _ = timed(step_e2e, e2e_steps)
+    e2e_value = bytes_per_step * world * e2e_steps / (ms_e2e / 1e3) / 1e9
     h2d = sum(c["m"]["cols"] * 4 for c in cases)
     d2h = sum(c["m"]["rows"] * 4 for c in cases)
 
-    # roofline: every GEMV launch of the sweep timed on its own, in sweep order (weights cold in L2)
+    # roofline: the GEMV kernel of every case timed alone, replayed from a graph over enough distinct
+    # HBM copies of the matrix (>= 256 MB) that no launch finds its weights in L2
     peak, peak_kind = peaks()
-    reps = 5
-    per = {i: [] for i in range(len(cases))}
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
-    for _ in range(reps):
-        for i, c in enumerate(cases):
-            ctx.fwht_quant_dev(c["x"].data_ptr(), 1, c["m"]["cols"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr())
-            evs[i][0].record(stream)
-            ctx.gemv_dev(c["dm"], c["q"].data_ptr(), c["s"].data_ptr(), c["sums"].data_ptr(), 1, c["out"].data_ptr())
-            evs[i][1].record(stream)
-        torch.cuda.synchronize()
-        for i in range(len(cases)):
-            per[i].append(evs[i][0].elapsed_time(evs[i][1]))
     kernels = []
-    tot_b = tot_ms = 0.0
-    for i, c in enumerate(cases):
-        t = statistics.mean(per[i])
-        gbs = c["bytes"] / (t / 1e3) / 1e9
-        kernels.append({"case": f"{c['m']['fmt']} {c['m']['cols']}x{c['m']['rows']}", "us": round(t * 1e3, 2),
+    tot_b = tot_us = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for c in cases:
+        wbytes = c["dm"].file_bytes
+        copies = max(3, -(-(256 << 20) // wbytes))
+        clones = [c["dm"]] + [c["dm"].clone() for _ in range(copies - 1)]
+        px, pq, ps, pm, po = c["p"]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for r in range(2):
+                for m in clones:
+                    ctx.gemv_dev(m, pq, ps, pm, 1, po)
+        ctx.set_stream(stream.cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(3):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (3 * 2 * copies)
+        gbs = c["bytes"] / us / 1e3
+        kernels.append({"case": f"{c['m']['fmt']} {c['m']['cols']}x{c['m']['rows']}", "us": round(us, 2),
                         "GBps": round(gbs, 1), "frac": round(gbs / peak, 3)})
-        tot_b += c["bytes"]; tot_ms += t
+        tot_b += c["bytes"]; tot_us += us
+        del g
+        for m in clones[1:]:
+            m.free()
     big = [k for k in kernels if k["case"].endswith("x49152")]
-    achieved = tot_b / (tot_ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel (all 16 launches of one sweep pass)", "achieved": achieved, "peak": peak,
-                "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                "largest_launch_frac": max(k["frac"] for k in big), "per_launch": kernels}
+    big_b = sum(c["bytes"] for c in cases if c["m"]["rows"] == 49152)
+    big_us = sum(k["us"] for k in big)
+    achieved = big_b / big_us / 1e3
+    roofline = {"bound": "hbm", "kernel": "gemv_kernel, the four 2048x49152 launches of a sweep pass (78% of its bytes)",
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "traffic_note": "ncu dram bytes per launch = algorithmic bytes within 0.1% (profiles/)",
+                "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak},
+                "per_launch": kernels}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -310,12 +341,12 @@ def run_b200(args, rank, world, local_rank):
     if rank == 0:
         print(json.dumps({
             "metric": "quantized_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "step_form": "one CUDA graph of 32 kernels per step", "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x 4..6-bit codes -> int32, fp32 epilogue", "data": "synthetic (random codes)",
             "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of distinct weights per step)",
                        "per_rank": "each rank runs its own sweep (replicas, no collective)"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(gpu_launches),
             "roofline": roofline, "cpu_baseline": cpu,

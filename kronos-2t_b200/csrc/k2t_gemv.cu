@@ -449,15 +449,15 @@ static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_cou
     cudaError_t e = cudaSuccess;
     if (smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    // persistent grid: as many CTAs as fit per SM (shared memory, 1 KiB reserved per CTA; <= 2048 threads),
-    // then evened out so that every CTA gets the same number of row blocks
+    // persistent grid: as many CTAs as fit per SM (shared memory, 1 KiB reserved per CTA), with the warps
+    // per SM a multiple of 4 so that the four schedulers of an SM get the same number of warps
     uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
     per_sm = per_sm < 1 ? 1 : per_sm;
     if (per_sm > 32) per_sm = 32;
     if (per_sm * wk > 48) per_sm = 48 / wk;
-    uint32_t max_grid = per_sm * (uint32_t)sm_count;
-    const uint32_t per_cta = (n_rb + max_grid - 1) / max_grid;
-    const uint32_t grid = (n_rb + per_cta - 1) / per_cta;
+    if (per_sm * wk >= 4) per_sm = ((per_sm * wk) & ~3u) / wk;
+    uint32_t grid = per_sm * (uint32_t)sm_count;
+    if (grid > n_rb) grid = n_rb;
     gemv_kernel<FMT, NT, DOTS><<<grid, 32 * wk, smem, stream>>>(a);
     return cudaGetLastError();
 }
