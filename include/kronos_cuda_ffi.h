@@ -132,6 +132,28 @@ int32_t kronos_cuda_gemv_dev(KronosCudaContext *ctx, const KronosCudaMatrix *m, 
                              const float *d_xs, const int32_t *d_xsum, size_t n_tok, float *d_out,
                              size_t out_stride, int32_t *d_int_dots);
 
+/* ---- no-allocation variant ------------------------------------------------------------------- */
+
+/* Widest matrix (columns) kronos_cuda_linear_noalloc accepts, and the bytes of device memory its
+ * static scratch occupies on every GPU that loads the library, until the process exits. */
+#define KRONOS_CUDA_NOALLOC_MAX_COLS 32768u
+#define KRONOS_CUDA_NOALLOC_SCRATCH_BYTES (4u * 32768u + 2u * 4u * (32768u / 64u) * 4u)
+
+/* Same result as kronos_cuda_linear, for callers that must not allocate on the decode path (a host
+ * with a fixed device-memory plan, a real-time loop, a process under a memory cap): inputs and
+ * outputs are DEVICE buffers (d_x[n_tok][cols] fp32, d_out[n_tok][rows] fp32), launches are queued on
+ * the context's stream and the call returns without synchronizing.  It calls no cudaMalloc / cudaFree
+ * and no allocating library routine: the quantized activations between its two kernels live in a
+ * fixed __device__ array inside the library (KRONOS_CUDA_NOALLOC_SCRATCH_BYTES per GPU).
+ *   - Matrices wider than KRONOS_CUDA_NOALLOC_MAX_COLS columns are rejected with an error.
+ *   - All calls on a device share that array: calls that overlap on the GPU (other streams, other
+ *     contexts) race; calls on one stream are safe. Nothing in it needs clearing between calls.
+ *   - The first call on a device looks the array's device address up (cudaGetSymbolAddress); make
+ *     that first call before starting any stream capture.
+ * This entry point has no counterpart in the reference. */
+int32_t kronos_cuda_linear_noalloc(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *d_x,
+                                   size_t n_tok, float *d_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,70 +7,14 @@
 #include <thread>
 #include <vector>
 
-#include "../../include/kronos_cuda_ffi.h"
-#include "k2t_kernels.h"
+#include "k2t_context.h"
 
 using namespace k2t;
-
-struct KronosCudaMatrix {
-    DeviceMatrix dm;
-    int device;
-};
-
-struct DeviceBuffer {   // grow-only scratch owned by a context
-    void *p = nullptr;
-    size_t cap = 0;
-};
-
-struct KronosCudaContext {
-    int device = 0;
-    int sm_count = 0;
-    cudaStream_t own_stream = nullptr;
-    cudaStream_t stream = nullptr;
-    uint64_t launches = 0;
-    std::string err;
-    DeviceBuffer x, q, xs, xsum, out, dots, inv, normw;
-    uint32_t *d_err = nullptr;      // device word kernels set when a bounded wait gives up
-};
 
 namespace {
 
 std::mutex g_err_mu;
 std::string g_create_err = "";
-
-bool fail(KronosCudaContext *ctx, const std::string &msg) {
-    if (ctx) ctx->err = msg;
-    return false;
-}
-bool cuda_ok(KronosCudaContext *ctx, cudaError_t e, const char *what) {
-    if (e == cudaSuccess) return true;
-    return fail(ctx, std::string(what) + ": " + cudaGetErrorString(e));
-}
-bool reserve(KronosCudaContext *ctx, DeviceBuffer &b, size_t bytes) {
-    if (bytes <= b.cap) return true;
-    if (b.p) { cudaFree(b.p); b.p = nullptr; b.cap = 0; }
-    size_t want = (bytes + 255) & ~(size_t)255;
-    if (!cuda_ok(ctx, cudaMalloc(&b.p, want), "cudaMalloc(scratch)")) return false;
-    b.cap = want;
-    return true;
-}
-void release(DeviceBuffer &b) {
-    if (b.p) cudaFree(b.p);
-    b.p = nullptr; b.cap = 0;
-}
-// Waits for the stream and reports a kernel-side timeout (a bounded wait that gave up) as an error.
-bool sync_and_check(KronosCudaContext *ctx, const char *what) {
-    uint32_t flag = 0;
-    if (!cuda_ok(ctx, cudaMemcpyAsync(&flag, ctx->d_err, 4, cudaMemcpyDeviceToHost, ctx->stream), what) ||
-        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), what))
-        return false;
-    if (flag != 0) {
-        cudaMemsetAsync(ctx->d_err, 0, 4, ctx->stream);
-        return fail(ctx, std::string(what) + ": a kernel gave up waiting for its weight pipeline (results invalid)");
-    }
-    return true;
-}
-bool make_current(KronosCudaContext *ctx) { return cuda_ok(ctx, cudaSetDevice(ctx->device), "cudaSetDevice"); }
 
 bool check_gemv_args(KronosCudaContext *ctx, const KronosCudaMatrix *m, const void *xq, const void *xs,
                      const void *xsum, size_t n_tok, const void *out, size_t out_stride) {

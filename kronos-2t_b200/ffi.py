@@ -63,6 +63,7 @@ def load_library():
     sig("kronos_cuda_gemv", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
     sig("kronos_cuda_linear", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_fwht_quant_dev", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
+    sig("kronos_cuda_linear_noalloc", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_gemv_dev", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
     _LIB = L
     return L
@@ -214,6 +215,10 @@ class Context:
     def fwht_quant_dev(self, d_x, n_tok, cols, d_q, d_scales, d_sums, d_norm_w=None, d_inv_rms=None, chunk0=0):
         self._check(self.L.kronos_cuda_fwht_quant_dev(self.handle, d_x, n_tok, cols, d_norm_w, d_inv_rms, chunk0,
                                                       d_q, d_scales, d_sums))
+
+    def linear_noalloc_dev(self, mat, d_x, n_tok, d_out):
+        """kronos_cuda_linear_noalloc: device buffers in and out, static scratch, no synchronization."""
+        self._check(self.L.kronos_cuda_linear_noalloc(self.handle, mat.handle, d_x, n_tok, d_out))
 
     def gemv_dev(self, mat, d_xq, d_xs, d_xsum, n_tok, d_out, out_stride=None, d_dots=None):
         self._check(self.L.kronos_cuda_gemv_dev(self.handle, mat.handle, d_xq, d_xs, d_xsum, n_tok, d_out,
