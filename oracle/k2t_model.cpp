@@ -1,0 +1,346 @@
+// k2t_model.cpp — CPU restatement of the kronos-2t dense Llama/Qwen decode step.
+// TEST INFRASTRUCTURE ONLY (see k2t_oracle.h).  PARITY UNPINNED: no reference binary exists to run.
+//
+// Follows RealLlamaEngine::forward_token, generic per-op path (src/model/real_llm.rs:6485-6790), for
+// engines whose projections are bit-plane (Nibble4) or NF matrices and whose KV cache is the int8
+// Hadamard cache.  Where aarch64 and portable code differ the aarch64 arithmetic is followed:
+// polynomial exp (9430-9454) in SwiGLU and softmax bodies, fused multiply-adds where NEON uses them.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "k2t_oracle.h"
+
+namespace {
+
+inline float bits_f32(uint32_t u) { float f; std::memcpy(&f, &u, 4); return f; }
+
+// exp_f32_neon (real_llm.rs:9430-9454), one lane.
+inline float exp_poly(float x_raw) {
+    float x = std::fmin(std::fmax(x_raw, -87.33654f), 88.0f);
+    float kf = std::nearbyintf(x * 1.44269504088896340736f);
+    float r = std::fmaf(-kf, 1.4286068e-6f, std::fmaf(-kf, 0.69314575f, x));
+    float y = std::fmaf(1.9875691e-4f, r, 1.3982e-3f);
+    y = std::fmaf(y, r, 8.333452e-3f);
+    y = std::fmaf(y, r, 4.1665796e-2f);
+    y = std::fmaf(y, r, 1.6666666e-1f);
+    y = std::fmaf(y, r, 0.5f);
+    y = std::fmaf(y, r, 1.0f);
+    y = std::fmaf(y, r, 1.0f);
+    int32_t ki = (int32_t)kf;
+    return y * bits_f32((uint32_t)(ki + 127) << 23);
+}
+
+struct Mat {
+    uint32_t kind = 0, rows = 0, cols = 0, bits = 0, sgc = 1;
+    int8_t codebook[16] = {0};
+    std::vector<uint8_t> a, b;   // bipolar: Nibble4 pair/tail streams; NF: pair/tail streams
+    // bipolar source kept for tied-embedding row dequantization
+    void gemv(const int8_t *q, const float *xs, const int32_t *xsum, float *out, size_t threads) const {
+        if (kind == 0)
+            k2o_nibble4_gemv(a.data(), b.data(), rows, cols, bits, q, xs, xsum, 1, out, rows, nullptr, threads);
+        else
+            k2o_nf_gemv(a.data(), b.data(), codebook, rows, cols, bits, sgc, q, xs, 1, out, rows, nullptr, threads);
+    }
+    void dequant_row(size_t r, float *out) const {
+        if (kind == 0) k2o_nibble4_dequant_row(a.data(), b.data(), rows, cols, bits, r, out);
+        else k2o_nf_dequant_row(a.data(), b.data(), codebook, rows, cols, bits, sgc, r, out);
+    }
+};
+
+bool load_mat(Mat &m, const K2oMatrixDesc *d) {
+    if (!d) return false;
+    m.kind = d->kind; m.rows = d->rows; m.cols = d->cols; m.bits = d->bits; m.sgc = d->scale_group_chunks ? d->scale_group_chunks : 1;
+    std::memcpy(m.codebook, d->codebook, 16);
+    if (d->kind == 0) {   // FusedBipolar -> Nibble4 (repack_sdot, real_llm.rs:3657-3702; no gate_up interleave: a row permutation)
+        m.a.resize(std::max<size_t>(1, k2o_nibble4_pair_bytes(d->rows, d->cols, d->bits)));
+        m.b.resize(std::max<size_t>(1, k2o_nibble4_tail_bytes(d->rows, d->cols, d->bits)));
+        k2o_nibble4_from_bipolar(d->data0, reinterpret_cast<const uint16_t *>(d->data1), d->rows, d->cols, d->bits, 0,
+                                 m.a.data(), m.b.data());
+    } else if (d->kind == 2) {
+        m.a.assign(d->data0, d->data0 + d->len0);
+        m.b.assign(d->data1, d->data1 + d->len1);
+        if (m.a.empty()) m.a.resize(1);
+        if (m.b.empty()) m.b.resize(1);
+    } else {
+        return false;
+    }
+    return true;
+}
+
+struct Layer {
+    std::vector<float> input_norm, post_norm, qkv_bias, q_norm, k_norm;
+    Mat qkv, o, gate_up, down;
+};
+
+}  // namespace
+
+struct K2oModel {
+    K2oConfig cfg;
+    std::vector<float> rope;          // [max_seq][head_dim]: cos(hd/2), sin(hd/2)
+    std::vector<Layer> layers;
+    std::vector<float> final_norm;
+    Mat lm_head;
+    std::vector<uint16_t> embed_bf16; // empty = tied (row of lm_head, inverse rotated)
+    // int8 Hadamard KV cache (QuantizedKvCache, real_llm.rs:1093-1412): [layer][kv head][pos][hd] + scale per (head,pos)
+    std::vector<int8_t> k_q8, v_q8;
+    std::vector<float> k_sc, v_sc;
+    size_t pos = 0;
+    // taps of the last forward (for tests)
+    std::vector<float> tap_hidden;    // hidden state after every layer [layers][hidden]
+
+    size_t kv_slot(size_t l, size_t h, size_t p) const { return (l * cfg.n_kv + h) * cfg.max_seq + p; }
+};
+
+namespace {
+
+void rms_norm(const float *x, const float *w, size_t n, float eps, float *out) {
+    float inv = k2o_inv_rms(x, n, eps);
+    for (size_t i = 0; i < n; ++i) out[i] = (x[i] * inv) * w[i];
+}
+
+void head_rms_norm(float *buf, size_t heads, size_t hd, const float *w, float eps) {   // apply_per_head_rms_norm 8167-8178
+    const float inv_hd = 1.0f / (float)hd;
+    for (size_t h = 0; h < heads; ++h) {
+        float *v = buf + h * hd;
+        float inv = 1.0f / std::sqrt(k2o_dot_f32(v, v, hd) * inv_hd + eps);
+        for (size_t i = 0; i < hd; ++i) v[i] = (v[i] * inv) * w[i];
+    }
+}
+
+void rope_heads(float *buf, size_t heads, size_t hd, const float *row) {    // apply_llama_rope_head64/128_neon 9287-9326
+    const size_t half = hd / 2;
+    for (size_t h = 0; h < heads; ++h) {
+        float *v = buf + h * hd;
+        for (size_t i = 0; i < half; ++i) {
+            float x0 = v[i], x1 = v[half + i], c = row[i], s = row[half + i];
+            float a = x0 * c, b = x1 * s, d = x1 * c, e = x0 * s;
+            v[i] = a - b;
+            v[half + i] = d + e;
+        }
+    }
+}
+
+// store_hadamard_q8_head{64,128}_raw (8303-8365): rotate with block index 0 (,1), one scale per head.
+void quant_head(const float *src, size_t hd, int8_t *q, float *scale) {
+    float rot[128];
+    std::memcpy(rot, src, hd * sizeof(float));
+    k2o_fwht64(rot, hd, 0);
+    float mx = 0.0f;
+    for (size_t i = 0; i < hd; ++i) mx = std::max(mx, std::fabs(rot[i]));
+    if (mx <= 1.1920929e-07f) { std::memset(q, 0, hd); *scale = 0.0f; return; }
+    float inv = 127.0f / mx;
+    for (size_t i = 0; i < hd; ++i) q[i] = (int8_t)(int32_t)std::nearbyintf(rot[i] * inv);
+    *scale = mx / 127.0f;
+}
+
+// causal_gqa_group_q8 (8471-8594) for one query head; aarch64 arithmetic.
+void attend_head(const K2oModel &m, size_t l, size_t kvh, const float *q_head, size_t seq_len, float attn_scale,
+                 std::vector<float> &sc, float *out) {
+    const size_t hd = m.cfg.head_dim;
+    int8_t qi[128];
+    float qs;
+    quant_head(q_head, hd, qi, &qs);
+    const float qas = qs * attn_scale;
+    const int8_t *K = m.k_q8.data() + m.kv_slot(l, kvh, 0) * hd;
+    const int8_t *V = m.v_q8.data() + m.kv_slot(l, kvh, 0) * hd;
+    const float *ks = m.k_sc.data() + m.kv_slot(l, kvh, 0);
+    const float *vs = m.v_sc.data() + m.kv_slot(l, kvh, 0);
+    sc.resize(seq_len);
+    // scores: 256-position tiles; groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+    for (size_t t0 = 0; t0 < seq_len; t0 += 256) {
+        size_t t1 = std::min(seq_len, t0 + 256), n8 = t0 + ((t1 - t0) / 8) * 8;
+        for (size_t t = t0; t < t1; ++t) {
+            int32_t dot = 0;
+            for (size_t i = 0; i < hd; ++i) dot += (int32_t)qi[i] * (int32_t)K[t * hd + i];
+            sc[t] = t < n8 ? (float)dot * (ks[t] * qas) : ((float)dot * ks[t]) * qas;
+        }
+    }
+    float mx = -INFINITY;
+    for (size_t t = 0; t < seq_len; ++t) mx = std::max(mx, sc[t]);
+    // softmax_unnorm_neon (9603-9632): 4 lanes accumulate, pairwise horizontal add, libm exp for the tail
+    float acc[4] = {0, 0, 0, 0};
+    size_t t = 0;
+    for (; t + 4 <= seq_len; t += 4)
+        for (int j = 0; j < 4; ++j) { float e = exp_poly(sc[t + j] - mx); sc[t + j] = e; acc[j] += e; }
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    for (; t < seq_len; ++t) { float e = std::exp(sc[t] - mx); sc[t] = e; sum += e; }
+    const float inv = 1.0f / sum;
+    float o[128] = {0};
+    for (size_t tt = 0; tt < seq_len; ++tt) {      // attn_values_head*_q8_accum_neon (9121-9162)
+        float w = (sc[tt] * inv) * vs[tt];
+        if (w == 0.0f) continue;
+        for (size_t i = 0; i < hd; ++i) o[i] = std::fmaf((float)V[tt * hd + i], w, o[i]);
+    }
+    k2o_ifwht64(o, hd, 0);
+    std::memcpy(out, o, hd * sizeof(float));
+}
+
+struct Act {
+    std::vector<int8_t> q;
+    std::vector<float> s;
+    std::vector<int32_t> m;
+    void populate(const float *x, size_t cols) {   // fwht64_signed_inplace + populate (exec_hidden_proj!, 6521-6562)
+        q.resize(cols); s.resize(cols / 64); m.resize(cols / 64);
+        k2o_act_populate_fwht(x, cols, nullptr, 1.0f, 0, q.data(), s.data(), m.data());
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table) {
+    if (!cfg || !rope_table) return nullptr;
+    if (cfg->head_dim != 64 && cfg->head_dim != 128) return nullptr;
+    auto m = std::make_unique<K2oModel>();
+    m->cfg = *cfg;
+    m->rope.assign(rope_table, rope_table + (size_t)cfg->max_seq * cfg->head_dim);
+    m->layers.resize(cfg->layers);
+    size_t slots = (size_t)cfg->layers * cfg->n_kv * cfg->max_seq;
+    m->k_q8.assign(slots * cfg->head_dim, 0);
+    m->v_q8.assign(slots * cfg->head_dim, 0);
+    m->k_sc.assign(slots, 0.0f);
+    m->v_sc.assign(slots, 0.0f);
+    return m.release();
+}
+
+void k2o_model_free(K2oModel *m) { delete m; }
+
+int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const float *post_norm, const float *qkv_bias,
+                        const float *q_norm, const float *k_norm, const K2oMatrixDesc *qkv, const K2oMatrixDesc *o,
+                        const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down) {
+    if (!m || l >= m->layers.size()) return -1;
+    const K2oConfig &c = m->cfg;
+    Layer &L = m->layers[l];
+    L.input_norm.assign(input_norm, input_norm + c.hidden);
+    L.post_norm.assign(post_norm, post_norm + c.hidden);
+    size_t qkv_rows = (size_t)(c.n_q + 2 * c.n_kv) * c.head_dim;
+    if (qkv_bias) L.qkv_bias.assign(qkv_bias, qkv_bias + qkv_rows); else L.qkv_bias.clear();
+    if (q_norm) L.q_norm.assign(q_norm, q_norm + c.head_dim); else L.q_norm.clear();
+    if (k_norm) L.k_norm.assign(k_norm, k_norm + c.head_dim); else L.k_norm.clear();
+    if (!load_mat(L.qkv, qkv) || !load_mat(L.o, o) || !load_mat(L.gate_up, gate_up) || !load_mat(L.down, down)) return -1;
+    if (L.qkv.rows != qkv_rows || L.qkv.cols != c.hidden || L.o.rows != c.hidden || L.o.cols != c.n_q * c.head_dim ||
+        L.gate_up.rows != 2 * c.inter || L.gate_up.cols != c.hidden || L.down.rows != c.hidden || L.down.cols != c.inter)
+        return -1;
+    return 0;
+}
+
+int k2o_model_set_head(K2oModel *m, const float *final_norm, const K2oMatrixDesc *lm_head, const uint16_t *embed_bf16) {
+    if (!m || !final_norm || !load_mat(m->lm_head, lm_head)) return -1;
+    m->final_norm.assign(final_norm, final_norm + m->cfg.hidden);
+    if (embed_bf16) m->embed_bf16.assign(embed_bf16, embed_bf16 + (size_t)m->cfg.vocab * m->cfg.hidden);
+    else m->embed_bf16.clear();
+    return (m->lm_head.rows == m->cfg.vocab && m->lm_head.cols == m->cfg.hidden) ? 0 : -1;
+}
+
+void k2o_model_reset(K2oModel *m) { if (m) m->pos = 0; }
+size_t k2o_model_pos(const K2oModel *m) { return m ? m->pos : 0; }
+void k2o_model_set_pos(K2oModel *m, size_t pos) { if (m) m->pos = pos; }
+
+// embed_token_into (real_llm.rs:8063-8097)
+void k2o_model_embed(const K2oModel *m, uint32_t token, float *out) {
+    const size_t h = m->cfg.hidden;
+    if (!m->embed_bf16.empty()) {
+        for (size_t i = 0; i < h; ++i) out[i] = k2o_bf16_to_f32(m->embed_bf16[(size_t)token * h + i]);
+        return;
+    }
+    m->lm_head.dequant_row(token, out);
+    k2o_ifwht64(out, h, 0);
+}
+
+const float *k2o_model_tap_hidden(const K2oModel *m) { return m->tap_hidden.data(); }
+
+// One decode step from an embedding vector (what the device boundary receives); logits[vocab].
+int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads) {
+    if (!m || m->pos >= m->cfg.max_seq) return -1;
+    const K2oConfig &c = m->cfg;
+    const size_t h = c.hidden, hd = c.head_dim, q_dim = (size_t)c.n_q * hd, kv_dim = (size_t)c.n_kv * hd, inter = c.inter;
+    const size_t group = c.n_q / c.n_kv, pos = m->pos;
+    const float attn_scale = 1.0f / std::sqrt((float)hd);
+    const float *rope_row = m->rope.data() + pos * hd;
+    std::vector<float> hidden(embedding, embedding + h), norm(std::max(h, inter)), qkv(q_dim + 2 * kv_dim), attn(q_dim),
+        proj(h), gu(2 * inter), sw(inter), sc;
+    Act act;
+    m->tap_hidden.assign((size_t)c.layers * h, 0.0f);
+    for (size_t l = 0; l < c.layers; ++l) {
+        const Layer &L = m->layers[l];
+        rms_norm(hidden.data(), L.input_norm.data(), h, c.eps, norm.data());
+        act.populate(norm.data(), h);
+        L.qkv.gemv(act.q.data(), act.s.data(), act.m.data(), qkv.data(), threads);
+        if (!L.qkv_bias.empty()) for (size_t i = 0; i < qkv.size(); ++i) qkv[i] = std::fmaf(L.qkv_bias[i], 1.0f, qkv[i]);
+        float *q = qkv.data(), *k = q + q_dim, *v = k + kv_dim;
+        // apply_qk_norm_rope (8139-8165)
+        if (c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
+        if (!L.q_norm.empty()) head_rms_norm(q, c.n_q, hd, L.q_norm.data(), c.eps);
+        if (!L.k_norm.empty()) head_rms_norm(k, c.n_kv, hd, L.k_norm.data(), c.eps);
+        if (!c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
+        for (size_t kvh = 0; kvh < c.n_kv; ++kvh) {
+            size_t slot = m->kv_slot(l, kvh, pos);
+            quant_head(k + kvh * hd, hd, m->k_q8.data() + slot * hd, &m->k_sc[slot]);
+            quant_head(v + kvh * hd, hd, m->v_q8.data() + slot * hd, &m->v_sc[slot]);
+        }
+        for (size_t qh = 0; qh < c.n_q; ++qh)
+            attend_head(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
+        act.populate(attn.data(), q_dim);
+        L.o.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
+        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);   // add_inplace = axpy(1.0)
+        rms_norm(hidden.data(), L.post_norm.data(), h, c.eps, norm.data());
+        act.populate(norm.data(), h);
+        L.gate_up.gemv(act.q.data(), act.s.data(), act.m.data(), gu.data(), threads);
+        for (size_t i = 0; i < inter; ++i) {       // swiglu_activate_neon (9811-9842): inter is a multiple of 8
+            float g = gu[i], u = gu[inter + i];
+            sw[i] = (g / (1.0f + exp_poly(-g))) * u;
+        }
+        act.populate(sw.data(), inter);
+        L.down.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
+        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);
+        std::memcpy(m->tap_hidden.data() + l * h, hidden.data(), h * sizeof(float));
+    }
+    rms_norm(hidden.data(), m->final_norm.data(), h, c.eps, norm.data());
+    act.populate(norm.data(), h);
+    m->lm_head.gemv(act.q.data(), act.s.data(), act.m.data(), logits, threads);
+    m->pos += 1;
+    return 0;
+}
+
+int k2o_model_forward_token(K2oModel *m, uint32_t token, float *logits, size_t threads) {
+    if (!m || token >= m->cfg.vocab) return -1;
+    std::vector<float> e(m->cfg.hidden);
+    k2o_model_embed(m, token, e.data());
+    return k2o_model_forward_embedding(m, e.data(), logits, threads);
+}
+
+// argmax_scalar (9914-9924): first maximum.
+uint32_t k2o_argmax(const float *v, size_t n) {
+    size_t best = 0;
+    float bv = -INFINITY;
+    for (size_t i = 0; i < n; ++i) if (v[i] > bv) { bv = v[i]; best = i; }
+    return (uint32_t)best;
+}
+
+// build_rope_table (9212-9236).
+void k2o_build_rope_table(size_t max_seq, size_t head_dim, double theta, float *table) {
+    const size_t half = head_dim / 2;
+    std::vector<float> inv_freq(half);
+    for (size_t i = 0; i < half; ++i) inv_freq[i] = (float)(1.0 / std::pow(theta, (double)(2 * i) / (double)head_dim));
+    for (size_t p = 0; p < max_seq; ++p)
+        for (size_t i = 0; i < half; ++i) {
+            float ang = (float)p * inv_freq[i];
+            table[p * head_dim + i] = std::cos(ang);
+            table[p * head_dim + half + i] = std::sin(ang);
+        }
+}
+
+// exposed pieces for kernel-level parity tests
+float k2o_exp_poly(float x) { return exp_poly(x); }
+void k2o_swiglu(const float *gate, const float *up, size_t n, float *out) {
+    for (size_t i = 0; i < n; ++i) out[i] = (gate[i] / (1.0f + exp_poly(-gate[i]))) * up[i];
+}
+void k2o_rope_heads(float *buf, size_t heads, size_t head_dim, const float *rope_row) { rope_heads(buf, heads, head_dim, rope_row); }
+void k2o_head_rms_norm(float *buf, size_t heads, size_t head_dim, const float *w, float eps) { head_rms_norm(buf, heads, head_dim, w, eps); }
+void k2o_kv_quant_head(const float *src, size_t head_dim, int8_t *q, float *scale) { quant_head(src, head_dim, q, scale); }
+
+}  // extern "C"

@@ -131,6 +131,46 @@ void k2o_nf_gemv(const uint8_t *pair_stream, const uint8_t *tail_stream, const i
                  size_t rows, size_t cols, size_t bits, size_t sgc, const int8_t *xq, const float *xs,
                  size_t n_tok, float *out, size_t out_stride, int32_t *int_dots, size_t threads);
 
+/* ---- dense Llama/Qwen decode step (k2t_model.cpp) ---------------------------------------------- */
+/* A matrix in the reference's storage (same fields as the descriptors the device backend takes):
+ * kind 0 = FusedBipolar (data0 interleaved planes, data1 bf16 scales), kind 2 = NF (pair/tail streams). */
+typedef struct K2oMatrixDesc {
+    uint32_t kind, rows, cols, bits, scale_group_chunks;
+    int8_t codebook[16];
+    const uint8_t *data0; size_t len0;
+    const uint8_t *data1; size_t len1;
+} K2oMatrixDesc;
+/* LlamaConfig scalars the decode step needs (src/model/real_llm.rs:91-457). */
+typedef struct K2oConfig {
+    uint32_t hidden, layers, n_q, n_kv, head_dim, inter, vocab, max_seq;
+    float eps;
+    int32_t qk_norm_after_rope;
+} K2oConfig;
+typedef struct K2oModel K2oModel;
+K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table);
+void k2o_model_free(K2oModel *m);
+int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const float *post_norm, const float *qkv_bias,
+                        const float *q_norm, const float *k_norm, const K2oMatrixDesc *qkv, const K2oMatrixDesc *o,
+                        const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down);
+int k2o_model_set_head(K2oModel *m, const float *final_norm, const K2oMatrixDesc *lm_head, const uint16_t *embed_bf16);
+void k2o_model_reset(K2oModel *m);
+size_t k2o_model_pos(const K2oModel *m);
+void k2o_model_set_pos(K2oModel *m, size_t pos);
+/* embed_token_into (real_llm.rs:8063-8097). */
+void k2o_model_embed(const K2oModel *m, uint32_t token, float *out);
+/* forward_token, generic path (6485-6790), int8 Hadamard KV; advances pos by one. */
+int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads);
+int k2o_model_forward_token(K2oModel *m, uint32_t token, float *logits, size_t threads);
+/* hidden state after every layer of the last step, [layers][hidden]. */
+const float *k2o_model_tap_hidden(const K2oModel *m);
+uint32_t k2o_argmax(const float *v, size_t n);                                   /* argmax_scalar 9914-9924 */
+void k2o_build_rope_table(size_t max_seq, size_t head_dim, double theta, float *table);   /* 9212-9236 */
+float k2o_exp_poly(float x);                                                     /* exp_f32_neon 9430-9454 */
+void k2o_swiglu(const float *gate, const float *up, size_t n, float *out);       /* swiglu_activate_neon 9811-9842 */
+void k2o_rope_heads(float *buf, size_t heads, size_t head_dim, const float *rope_row);    /* 9287-9326 */
+void k2o_head_rms_norm(float *buf, size_t heads, size_t head_dim, const float *w, float eps); /* 8167-8178 */
+void k2o_kv_quant_head(const float *src, size_t head_dim, int8_t *q, float *scale);       /* 8303-8365 */
+
 #ifdef __cplusplus
 }
 #endif

@@ -360,3 +360,177 @@ def gemv(m, act, want_dots=False, threads=1):
     if m.kind == 0:
         return nibble4_gemv(nibble4_from_bipolar(m), act, want_dots, threads)
     return nf_gemv(m, act, want_dots, threads)
+
+
+# --------------------------------------------------------------------------- dense decode model
+class MatrixDesc(C.Structure):
+    _fields_ = [("kind", C.c_uint32), ("rows", C.c_uint32), ("cols", C.c_uint32), ("bits", C.c_uint32),
+                ("scale_group_chunks", C.c_uint32), ("codebook", C.c_int8 * 16),
+                ("data0", C.c_void_p), ("len0", C.c_size_t), ("data1", C.c_void_p), ("len1", C.c_size_t)]
+
+
+class Config(C.Structure):
+    _fields_ = [("hidden", C.c_uint32), ("layers", C.c_uint32), ("n_q", C.c_uint32), ("n_kv", C.c_uint32),
+                ("head_dim", C.c_uint32), ("inter", C.c_uint32), ("vocab", C.c_uint32), ("max_seq", C.c_uint32),
+                ("eps", C.c_float), ("qk_norm_after_rope", C.c_int32)]
+
+
+def desc_of(m):
+    """MatrixDesc of a Bipolar / Nf object (keeps the arrays alive on the descriptor)."""
+    d = MatrixDesc()
+    d.rows, d.cols = m.rows, m.cols
+    if m.kind == 0:
+        d.kind, d.bits, d.scale_group_chunks = 0, m.planes, 1
+        a, b = _c(m.data, np.uint8), _c(m.scales, np.uint16)
+    else:
+        d.kind, d.bits, d.scale_group_chunks = 2, m.bits, m.sgc
+        a, b = _c(m.pair, np.uint8), _c(m.tail, np.uint8)
+        for i in range(16):
+            d.codebook[i] = int(m.codebook[i])
+    d.data0, d.len0 = (a.ctypes.data if a.size else None), a.nbytes
+    d.data1, d.len1 = (b.ctypes.data if b.size else None), b.nbytes
+    d._keep = (a, b)
+    return d
+
+
+_model_declared = False
+
+
+def _declare_model(L):
+    global _model_declared
+    if _model_declared:
+        return
+    D, P = C.POINTER(MatrixDesc), C.c_void_p
+    L.k2o_model_new.restype, L.k2o_model_new.argtypes = P, [C.POINTER(Config), P]
+    L.k2o_model_free.restype, L.k2o_model_free.argtypes = None, [P]
+    L.k2o_model_set_layer.restype, L.k2o_model_set_layer.argtypes = C.c_int, [P, C.c_uint32, P, P, P, P, P, D, D, D, D]
+    L.k2o_model_set_head.restype, L.k2o_model_set_head.argtypes = C.c_int, [P, P, D, P]
+    L.k2o_model_reset.restype, L.k2o_model_reset.argtypes = None, [P]
+    L.k2o_model_pos.restype, L.k2o_model_pos.argtypes = C.c_size_t, [P]
+    L.k2o_model_set_pos.restype, L.k2o_model_set_pos.argtypes = None, [P, C.c_size_t]
+    L.k2o_model_embed.restype, L.k2o_model_embed.argtypes = None, [P, C.c_uint32, P]
+    L.k2o_model_forward_embedding.restype, L.k2o_model_forward_embedding.argtypes = C.c_int, [P, P, P, C.c_size_t]
+    L.k2o_model_forward_token.restype, L.k2o_model_forward_token.argtypes = C.c_int, [P, C.c_uint32, P, C.c_size_t]
+    L.k2o_model_tap_hidden.restype, L.k2o_model_tap_hidden.argtypes = P, [P]
+    L.k2o_argmax.restype, L.k2o_argmax.argtypes = C.c_uint32, [P, C.c_size_t]
+    L.k2o_build_rope_table.restype, L.k2o_build_rope_table.argtypes = None, [C.c_size_t, C.c_size_t, C.c_double, P]
+    L.k2o_exp_poly.restype, L.k2o_exp_poly.argtypes = C.c_float, [C.c_float]
+    L.k2o_swiglu.restype, L.k2o_swiglu.argtypes = None, [P, P, C.c_size_t, P]
+    L.k2o_rope_heads.restype, L.k2o_rope_heads.argtypes = None, [P, C.c_size_t, C.c_size_t, P]
+    L.k2o_head_rms_norm.restype, L.k2o_head_rms_norm.argtypes = None, [P, C.c_size_t, C.c_size_t, P, C.c_float]
+    L.k2o_kv_quant_head.restype, L.k2o_kv_quant_head.argtypes = None, [P, C.c_size_t, P, P]
+    _model_declared = True
+
+
+def build_rope_table(max_seq, head_dim, theta):
+    L = lib(); _declare_model(L)
+    t = np.zeros((max_seq, head_dim), np.float32)
+    L.k2o_build_rope_table(max_seq, head_dim, float(theta), _ptr(t))
+    return t
+
+
+def swiglu(gate, up):
+    L = lib(); _declare_model(L)
+    g, u = _c(gate, np.float32), _c(up, np.float32)
+    out = np.zeros_like(g)
+    L.k2o_swiglu(_ptr(g), _ptr(u), g.size, _ptr(out))
+    return out
+
+
+def rope_heads(buf, heads, head_dim, rope_row):
+    L = lib(); _declare_model(L)
+    b = _c(buf, np.float32).copy()
+    r = _c(rope_row, np.float32)
+    L.k2o_rope_heads(_ptr(b), heads, head_dim, _ptr(r))
+    return b
+
+
+def head_rms_norm(buf, heads, head_dim, w, eps):
+    L = lib(); _declare_model(L)
+    b = _c(buf, np.float32).copy()
+    ww = _c(w, np.float32)
+    L.k2o_head_rms_norm(_ptr(b), heads, head_dim, _ptr(ww), float(eps))
+    return b
+
+
+def kv_quant_head(src):
+    L = lib(); _declare_model(L)
+    s = _c(src, np.float32)
+    q = np.zeros(s.size, np.int8)
+    sc = np.zeros(1, np.float32)
+    L.k2o_kv_quant_head(_ptr(s), s.size, _ptr(q), _ptr(sc))
+    return q, sc[0]
+
+
+def argmax(v):
+    L = lib(); _declare_model(L)
+    v = _c(v, np.float32)
+    return int(L.k2o_argmax(_ptr(v), v.size))
+
+
+class Model:
+    """Dense Llama/Qwen decode model on the CPU oracle. `spec` is the dict produced by tests/k2t_models.py."""
+
+    def __init__(self, spec):
+        L = lib(); _declare_model(L)
+        self.L, self.spec = L, spec
+        c = spec["cfg"]
+        self.cfg = Config(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"], c["max_seq"],
+                          c["eps"], int(c.get("qk_norm_after_rope", 0)))
+        rope = _c(spec["rope"], np.float32)
+        self.h = L.k2o_model_new(C.byref(self.cfg), _ptr(rope))
+        assert self.h, "k2o_model_new failed"
+        for l, ly in enumerate(spec["layers"]):
+            ds = [desc_of(ly[k]) for k in ("qkv", "o", "gate_up", "down")]
+            arrs = [None if ly.get(k) is None else _c(ly[k], np.float32) for k in ("input_norm", "post_norm", "qkv_bias", "q_norm", "k_norm")]
+            rc = L.k2o_model_set_layer(self.h, l, *[_ptr(a) for a in arrs], *[C.byref(d) for d in ds])
+            assert rc == 0, f"set_layer {l} failed"
+        emb = None if spec.get("embed_bf16") is None else _c(spec["embed_bf16"], np.uint16)
+        d = desc_of(spec["lm_head"])
+        fn = _c(spec["final_norm"], np.float32)
+        assert L.k2o_model_set_head(self.h, _ptr(fn), C.byref(d), _ptr(emb)) == 0
+
+    def close(self):
+        if self.h:
+            self.L.k2o_model_free(self.h)
+            self.h = None
+
+    def reset(self):
+        self.L.k2o_model_reset(self.h)
+
+    @property
+    def pos(self):
+        return self.L.k2o_model_pos(self.h)
+
+    def embed(self, token):
+        out = np.zeros(self.cfg.hidden, np.float32)
+        self.L.k2o_model_embed(self.h, int(token), _ptr(out))
+        return out
+
+    def forward_token(self, token, threads=8):
+        logits = np.zeros(self.cfg.vocab, np.float32)
+        assert self.L.k2o_model_forward_token(self.h, int(token), _ptr(logits), threads) == 0
+        return logits
+
+    def forward_embedding(self, e, threads=8):
+        e = _c(e, np.float32)
+        logits = np.zeros(self.cfg.vocab, np.float32)
+        assert self.L.k2o_model_forward_embedding(self.h, _ptr(e), _ptr(logits), threads) == 0
+        return logits
+
+    def tap_hidden(self):
+        p = self.L.k2o_model_tap_hidden(self.h)
+        n = self.cfg.layers * self.cfg.hidden
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).reshape(self.cfg.layers, self.cfg.hidden).copy()
+
+    def greedy(self, prompt, steps, threads=8):
+        """Feeds `prompt` token by token, then decodes `steps` tokens greedily. Returns (tokens, last logits)."""
+        logits = None
+        for t in prompt:
+            logits = self.forward_token(t, threads)
+        out = []
+        for _ in range(steps):
+            nxt = argmax(logits)
+            out.append(nxt)
+            logits = self.forward_token(nxt, threads)
+        return out, logits

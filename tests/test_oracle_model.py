@@ -1,0 +1,103 @@
+"""CPU tests of the oracle's dense decode step against an independent float64 transformer built from the
+same (dequantized) weights: checks RoPE, GQA attention, KV handling, SwiGLU and the residual wiring.
+Thresholds follow the reference's own float-vs-quantized tests (cos > 0.999 class, real_llm.rs:10189-10284)."""
+import numpy as np
+import pytest
+
+import k2t_models as km
+
+
+def dequant(oracle, m):
+    rows = [oracle.ifwht64(oracle.bipolar_dequant_row(m, r) if m.kind == 0 else oracle.nf_dequant_row(m, r)) for r in range(m.rows)]
+    return np.stack(rows).astype(np.float64)
+
+
+def float_model_logits(oracle, spec, tokens):
+    c = spec["cfg"]
+    h, hd, nq, nkv, inter = c["hidden"], c["head_dim"], c["n_q"], c["n_kv"], c["inter"]
+    W = [{k: dequant(oracle, ly[k]) for k in ("qkv", "o", "gate_up", "down")} for ly in spec["layers"]]
+    head = dequant(oracle, spec["lm_head"])
+    emb = head if spec["embed_bf16"] is None else (spec["embed_bf16"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    rope = spec["rope"].astype(np.float64)
+    norm = lambda x, w: x / np.sqrt(np.mean(x * x) + c["eps"]) * w
+
+    def rot(v, pos):
+        half = hd // 2
+        v = v.reshape(-1, hd).copy()
+        x0, x1, co, si = v[:, :half].copy(), v[:, half:].copy(), rope[pos, :half], rope[pos, half:]
+        v[:, :half], v[:, half:] = x0 * co - x1 * si, x1 * co + x0 * si
+        return v
+
+    K = [[] for _ in W]
+    V = [[] for _ in W]
+    out = []
+    for pos, tok in enumerate(tokens):
+        x = emb[tok].copy()
+        for l, ly in enumerate(spec["layers"]):
+            qkv = W[l]["qkv"] @ norm(x, ly["input_norm"])
+            if ly["qkv_bias"] is not None:
+                qkv = qkv + ly["qkv_bias"]
+            q, k, v = qkv[: nq * hd].reshape(nq, hd), qkv[nq * hd: (nq + nkv) * hd].reshape(nkv, hd), qkv[(nq + nkv) * hd:].reshape(nkv, hd)
+            if ly["q_norm"] is not None:
+                q = np.stack([norm(r, ly["q_norm"]) for r in q])
+                k = np.stack([norm(r, ly["k_norm"]) for r in k])
+            q, k = rot(q, pos), rot(k, pos)
+            K[l].append(k); V[l].append(v)
+            Ks, Vs = np.stack(K[l]), np.stack(V[l])        # [t, nkv, hd]
+            att = np.zeros((nq, hd))
+            for qh in range(nq):
+                kvh = qh // (nq // nkv)
+                s = Ks[:, kvh] @ q[qh] / np.sqrt(hd)
+                p = np.exp(s - s.max()); p /= p.sum()
+                att[qh] = p @ Vs[:, kvh]
+            x = x + W[l]["o"] @ att.reshape(-1)
+            gu = W[l]["gate_up"] @ norm(x, ly["post_norm"])
+            g, u = gu[:inter], gu[inter:]
+            x = x + W[l]["down"] @ (g / (1 + np.exp(-g)) * u)
+        out.append(head @ norm(x, spec["final_norm"]))
+    return np.stack(out)
+
+
+@pytest.mark.parametrize("mode,kw", [("b6", {}), ("nf4g128", dict(qkv_bias=True, qk_norm=True, tied=False)), ("b5", dict(qkv_bias=True))])
+def test_oracle_model_tracks_float_model(oracle, mode, kw):
+    spec = km.build(oracle, km.TINY, mode, seed=3, **kw)
+    tokens = [5, 17, 300, 42, 7, 199, 63, 250, 11, 90]
+    ref = float_model_logits(oracle, spec, tokens)
+    m = oracle.Model(spec)
+    got = np.stack([m.forward_token(t, threads=2) for t in tokens])
+    m.close()
+    for t in range(len(tokens)):
+        cos = np.dot(got[t], ref[t]) / (np.linalg.norm(got[t]) * np.linalg.norm(ref[t]))
+        assert cos > 0.995, (mode, t, cos)
+    assert m.h is None
+
+
+def test_oracle_model_determinism_threads_and_reset(oracle):
+    spec = km.build(oracle, km.TINY, "b4", seed=1)
+    m = oracle.Model(spec)
+    a, la = m.greedy([1, 2, 3, 4], 6, threads=1)
+    m.reset()
+    b, lb = m.greedy([1, 2, 3, 4], 6, threads=4)
+    assert a == b and np.array_equal(la, lb) and m.pos == 10
+    e = m.embed(7)
+    assert e.shape == (128,) and np.isfinite(e).all()
+    m.close()
+
+
+def test_model_helpers(oracle):
+    # exp polynomial close to libm, swiglu definition, rope rotation is norm preserving, argmax takes the first maximum
+    x = np.linspace(-20, 20, 401, dtype=np.float32)
+    L = oracle.lib()
+    oracle.build_rope_table(1, 64, 1e4)   # declares signatures
+    approx = np.array([L.k2o_exp_poly(float(v)) for v in x])
+    assert np.max(np.abs(approx / np.exp(x.astype(np.float64)) - 1)) < 3e-6
+    g, u = x, (x * 0.5 + 1).astype(np.float32)
+    assert np.allclose(oracle.swiglu(g, u), g / (1 + np.exp(-g.astype(np.float64))) * u, rtol=1e-5, atol=1e-6)
+    rope = oracle.build_rope_table(40, 64, 1e5)
+    v = np.random.default_rng(0).standard_normal(3 * 64).astype(np.float32)
+    r = oracle.rope_heads(v, 3, 64, rope[17])
+    assert np.allclose(np.linalg.norm(r.reshape(3, 64), axis=1), np.linalg.norm(v.reshape(3, 64), axis=1), rtol=1e-5)
+    assert np.array_equal(oracle.rope_heads(v, 3, 64, rope[0]), v)       # position 0: cos 1, sin 0
+    assert oracle.argmax(np.array([1, 5, 5, 2], np.float32)) == 1
+    q, s = oracle.kv_quant_head(v[:64])
+    assert np.abs(q).max() == 127 and s > 0
