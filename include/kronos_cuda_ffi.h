@@ -132,6 +132,71 @@ int32_t kronos_cuda_gemv_dev(KronosCudaContext *ctx, const KronosCudaMatrix *m, 
                              const float *d_xs, const int32_t *d_xsum, size_t n_tok, float *d_out,
                              size_t out_stride, int32_t *d_int_dots);
 
+/* ---- whole-token engine ------------------------------------------------------------------------ */
+
+typedef struct KronosCudaEngine KronosCudaEngine;
+
+/* LlamaConfig scalars the device forward needs (src/model/real_llm.rs:91-457), as MetalLlamaEngine::try_new
+ * receives them through `cfg`, plus the KV format (kv_bits: 8 = int8 Hadamard cache). */
+typedef struct KronosCudaEngineConfig {
+    uint32_t hidden_size, num_layers, num_attention_heads, num_key_value_heads, head_dim,
+             intermediate_size, vocab_size, max_seq_len;
+    float rms_norm_eps;
+    int32_t qk_norm_after_rope;
+    uint32_t kv_bits;
+} KronosCudaEngineConfig;
+
+/* One decoder layer as borrowed from the host engine: counterpart of LayerBorrow
+ * (src/backend/metal_gpu.rs:428-439).  Optional vectors are NULL when absent.  qkv_proj is the row
+ * concatenation [q; k; v], gate_up_proj = [gate; up] (not interleaved), as stored in .k2tb files. */
+typedef struct KronosCudaLayerDesc {
+    const float *input_norm, *post_attn_norm;      /* [hidden] */
+    const float *qkv_bias;                         /* [q_dim + 2 kv_dim] or NULL */
+    const float *q_norm, *k_norm;                  /* [head_dim] or NULL */
+    KronosCudaMatrixDesc qkv_proj, o_proj, gate_up_proj, down_proj;
+} KronosCudaLayerDesc;
+
+/* MetalLlamaEngine::try_new (metal_gpu.rs:1196-1206): copies every tensor to HBM, allocates the KV cache
+ * for max_seq_len positions and the per-token workspace.  rope_cos_sin = build_rope_table()'s
+ * [max_seq_len][head_dim] rows (cos half, sin half; real_llm.rs:9212-9236).  embed_bf16 = untied
+ * embedding table [vocab][hidden] or NULL for tied embeddings (the lm_head row, rotated back:
+ * embed_token_into, real_llm.rs:8063-8097).  Returns NULL on error (kronos_cuda_last_error(ctx)). */
+KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const KronosCudaEngineConfig *cfg,
+                                            const float *rope_cos_sin, const KronosCudaLayerDesc *layers,
+                                            size_t n_layers, const float *final_norm,
+                                            const KronosCudaMatrixDesc *lm_head, const uint16_t *embed_bf16);
+void kronos_cuda_engine_destroy(KronosCudaEngine *engine);
+
+/* MetalLlamaEngine::forward_tokens (metal_gpu.rs:1619-1627): runs n_tok tokens whose embeddings the
+ * host supplies (embeds[n_tok][hidden]) at positions pos_start.., writes the logits of the last token
+ * to last_logits[vocab] and, if all_logits is not NULL, of every token to all_logits[n_tok][vocab]. */
+int32_t kronos_cuda_engine_forward_tokens(KronosCudaEngine *engine, const float *embeds, size_t n_tok,
+                                          size_t pos_start, float *all_logits, float *last_logits);
+/* Same with token ids; the embedding lookup runs on the device (RealLlamaEngine::forward_token /
+ * forward_prompt, real_llm.rs:6455, 7407-7448). */
+int32_t kronos_cuda_engine_forward_token_ids(KronosCudaEngine *engine, const uint32_t *tokens, size_t n_tok,
+                                             size_t pos_start, float *all_logits, float *last_logits);
+/* RealLlamaEngine::generate_greedy's decode loop (real_llm.rs:7879-7913) with the argmax on the device:
+ * feeds first_token at pos_start, then n_steps times takes the argmax (first maximum) as the next
+ * token.  out_tokens[n_steps] receives the chosen tokens; last_logits (optional) the logits that
+ * produced the last one.  One CUDA graph replay per step, no host round trip inside the loop. */
+int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *engine, uint32_t first_token, size_t pos_start,
+                                         size_t n_steps, uint32_t *out_tokens, float *last_logits);
+/* kv_cache_bytes (metal_gpu.rs:1454-1617 family): bytes of KV cache held for `positions` positions. */
+size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *engine, size_t positions);
+/* Bytes of weights (reference file format) one decode step streams: all layer matrices + lm_head. */
+size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
+/* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */
+int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
+/* Diagnostic: attention output of the last layer for the last forwarded token, before o_proj:
+ * [num_attention_heads * head_dim] (the `attn` vector of forward_token, real_llm.rs:6651-6700). */
+int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *engine, float *attention);
+/* Diagnostic: one KV cache entry (layer, kv head, position): k_q8/v_q8[head_dim] rotated int8 values and
+ * their fp32 scales - the contents of the reference's k_q8 / k_scales / v_q8 / v_scales slot
+ * (KvCache, real_llm.rs:8303-8365). */
+int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *engine, uint32_t layer, uint32_t kv_head, size_t position,
+                                   int8_t *k_q8, float *k_scale, int8_t *v_q8, float *v_scale);
+
 /* ---- no-allocation variant ------------------------------------------------------------------- */
 
 /* Widest matrix (columns) kronos_cuda_linear_noalloc accepts, and the bytes of device memory its

@@ -5,6 +5,7 @@ shared object has not been built, and context creation fails when no B200 is vis
 """
 from .ffi import (  # noqa: F401
     Context,
+    Engine,
     KronosCudaError,
     Matrix,
     MatrixDesc,

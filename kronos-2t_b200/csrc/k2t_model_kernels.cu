@@ -1,0 +1,582 @@
+// Per-token kernels of the dense decode step around the GEMVs (reference: RealLlamaEngine::forward_token,
+// src/model/real_llm.rs:6485-6790): embedding, RMSNorm + rotation + int8 quantization, bias / qk-norm /
+// RoPE / KV store / query quantization, split-KV decode attention over the int8 Hadamard cache,
+// SwiGLU + rotation + quantization, argmax.  Everything position dependent reads the position from
+// device memory so that one captured CUDA graph serves every decode step.
+#include "k2t_fwht.cuh"
+#include "k2t_model_kernels.h"
+
+namespace k2t {
+
+// exp_f32_neon (src/model/real_llm.rs:9430-9454), one lane, same operations in the same order.
+__device__ __forceinline__ float exp_poly(float x_raw) {
+    const float x = fminf(fmaxf(x_raw, -87.33654f), 88.0f);
+    const float kf = rintf(__fmul_rn(x, 1.44269504088896340736f));
+    const float r = __fmaf_rn(-kf, 1.4286068e-6f, __fmaf_rn(-kf, 0.69314575f, x));
+    float y = __fmaf_rn(1.9875691e-4f, r, 1.3982e-3f);
+    y = __fmaf_rn(y, r, 8.333452e-3f);
+    y = __fmaf_rn(y, r, 4.1665796e-2f);
+    y = __fmaf_rn(y, r, 1.6666666e-1f);
+    y = __fmaf_rn(y, r, 0.5f);
+    y = __fmaf_rn(y, r, 1.0f);
+    y = __fmaf_rn(y, r, 1.0f);
+    const int ki = (int)kf;
+    return __fmul_rn(y, __int_as_float((ki + 127) << 23));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// embedding (embed_token_into, real_llm.rs:8063-8097)
+// ------------------------------------------------------------------------------------------------
+// weight value (rotated domain) of element `col` (0..63) of cell (row, c)
+__device__ float cell_value(const EmbedArgs &a, uint32_t row, uint32_t c, uint32_t col) {
+    const size_t cell = c;
+    const uint8_t *p0 = a.plane[0] + (size_t)row * a.pitch[0] + cell * a.cell[0];
+    const uint8_t *p1 = a.plane[1] + (size_t)row * a.pitch[1] + cell * a.cell[1];
+    const uint8_t *p2 = a.plane[2] + (size_t)row * a.pitch[2] + cell * a.cell[2];
+    const uint32_t sg = a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
+    const float delta = bf16_bits_to_f32(a.scales[(size_t)row * a.nsg_pad + sg]);
+    if (a.fmt == FMT_BP4 || a.fmt == FMT_BP5 || a.fmt == FMT_BP6) {
+        const uint8_t *half = col < 32 ? p0 : p1;
+        const uint32_t cc = col % 32, k = col % 8;
+        uint32_t u = (half[(cc / 8) * 4 + (k % 4)] >> (k < 4 ? 0 : 4)) & 0x0F;
+        if (a.fmt == FMT_BP5) {
+            const uint32_t bit = 8 * (col % 4) + cc / 4;
+            u |= ((p2[(col / 32) * 4 + bit / 8] >> (bit % 8)) & 1u) << 4;
+        } else if (a.fmt == FMT_BP6) {
+            const uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
+            u |= ((p2[(col / 16) * 4 + bit / 8] >> (bit % 8)) & 3u) << 4;
+        }
+        return __fmul_rn((float)(2 * (int)u - a.max_odd), delta);
+    }
+    uint32_t idx;
+    if (a.fmt == FMT_NF3) {
+        auto word = [&](uint32_t w) { return w < 4 ? reinterpret_cast<const uint32_t *>(p0)[w] : reinterpret_cast<const uint32_t *>(p1)[w - 4]; };
+        if (col < 48) idx = (word(col / 8) >> (4 * (col % 8))) & 7u;
+        else {
+            const uint32_t t = col - 48;
+            idx = 0;
+            for (uint32_t j = 0; j < 3; ++j) idx |= ((word(3 * (t / 8) + j) >> (4 * (t % 8) + 3)) & 1u) << j;
+        }
+    } else {
+        const uint8_t *half = col < 32 ? p0 : p1;
+        const uint32_t cc = col % 32, nib = col % 8;
+        idx = (half[(cc / 8) * 4 + nib / 2] >> (4 * (nib % 2))) & 0x0F;
+    }
+    return __fmul_rn((float)a.codebook[idx], delta);
+}
+
+__global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
+    const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (c >= a.nc) return;
+    const uint32_t tok = *a.token;
+    float v0, v1;
+    if (a.embed_bf16 != nullptr) {
+        const uint16_t *row = a.embed_bf16 + (size_t)tok * a.nc * 64 + (size_t)c * 64;
+        v0 = bf16_bits_to_f32(row[2 * lane]);
+        v1 = bf16_bits_to_f32(row[2 * lane + 1]);
+    } else {   // tied: lm_head row, dequantized in the rotated domain, rotated back
+        v0 = cell_value(a, tok, c, 2 * lane);
+        v1 = cell_value(a, tok, c, 2 * lane + 1);
+        warp_ifwht64(v0, v1, c, lane);
+    }
+    reinterpret_cast<float2 *>(a.hidden + (size_t)c * 64)[lane] = make_float2(v0, v1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// residual add + RMSNorm + FWHT-64 + int8  (rms_norm 9858-9898 + exec_hidden_proj!)
+// ------------------------------------------------------------------------------------------------
+// One CTA of 256 threads (8 warps).  hidden += delta (if given, written back), then the activation of
+// the next projection.  The sum of squares follows dot_f32_neon (real_llm.rs:9736-9800) exactly: 16 fma
+// accumulators over 16-element strides (lanes 0..15 of warp 0 run the 16 chains over the staged vector),
+// combined (a0+a1)+(a2+a3) lane-wise and then pairwise - so inv_rms is the CPU value bit for bit.
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
+                                                            const float *__restrict__ w, uint32_t n, float eps,
+                                                            int8_t *__restrict__ q, float *__restrict__ scales,
+                                                            int32_t *__restrict__ sums) {
+    extern __shared__ float s_x[];           // n floats
+    __shared__ float s_inv;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
+    for (uint32_t i = tid; i < n / 4; i += 256) {
+        float4 v = reinterpret_cast<const float4 *>(hidden)[i];
+        if (delta != nullptr) {
+            const float4 d = reinterpret_cast<const float4 *>(delta)[i];
+            v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
+            reinterpret_cast<float4 *>(hidden)[i] = v;
+        }
+        reinterpret_cast<float4 *>(s_x)[i] = v;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float acc = 0.0f;
+        if (lane < 16) {
+#pragma unroll 8
+            for (uint32_t i = lane; i < n; i += 16) { const float v = s_x[i]; acc = __fmaf_rn(v, v, acc); }
+        }
+        float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));      // lanes 0..3: a0+a1, lanes 8..11: a2+a3
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 8));                // lanes 0..3: the four vector lanes
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 1));                // lane 0: v0+v1, lane 2: v2+v3
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2));
+        if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)n), eps)));
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (uint32_t c = warp; c < nc; c += 8) {
+        float2 v = reinterpret_cast<const float2 *>(s_x + (size_t)c * 64)[lane];
+        const float2 ww = reinterpret_cast<const float2 *>(w + (size_t)c * 64)[lane];
+        v.x = __fmul_rn(__fmul_rn(v.x, inv), ww.x);
+        v.y = __fmul_rn(__fmul_rn(v.y, inv), ww.y);
+        warp_fwht64(v.x, v.y, c, lane);
+        int q0, q1, sum;
+        float sc;
+        warp_quant64(v.x, v.y, q0, q1, sc, sum);
+        reinterpret_cast<char2 *>(q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+        if (lane == 0) { scales[c] = sc; sums[c] = sum; }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// bias + qk-norm + RoPE + KV store + query quantization  (6609-6650, 8139-8178, 8303-8365, 9287-9326)
+// ------------------------------------------------------------------------------------------------
+// One warp per head of the fused qkv vector: heads [0, n_q) are queries, then n_kv keys, then n_kv values.
+// Keys/values go to the int8 cache at position *pos; queries are rotated and quantized the same way
+// (one scale per head) for the attention kernel.
+__global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
+    __shared__ float s_head[4][128];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t head = blockIdx.x * 4 + warp, hd = a.head_dim, half = hd / 2;
+    if (head >= a.n_q + 2 * a.n_kv) return;
+    const uint32_t pos = *a.pos;
+    const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
+    float *sh = s_head[warp];
+    const float *src = a.qkv + (size_t)head * hd;
+    for (uint32_t i = lane; i < hd; i += 32) {
+        float v = src[i];
+        if (a.bias != nullptr) v = __fadd_rn(v, a.bias[(size_t)head * hd + i]);
+        sh[i] = v;
+    }
+    __syncwarp();
+    const float *norm_w = is_q ? a.q_norm : (is_k ? a.k_norm : nullptr);
+    const float *rope = a.rope + (size_t)pos * hd;
+    auto do_rope = [&]() {
+        for (uint32_t i = lane; i < half; i += 32) {
+            const float x0 = sh[i], x1 = sh[half + i], c = rope[i], s = rope[half + i];
+            sh[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            sh[half + i] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+        }
+        __syncwarp();
+    };
+    auto do_norm = [&]() {
+        // dot_f32_neon order (16 fma accumulators, (a0+a1)+(a2+a3), pairwise), as in rmsnorm_quant_kernel
+        float ss = 0.0f;
+        if (lane < 16)
+            for (uint32_t i = lane; i < hd; i += 16) ss = __fmaf_rn(sh[i], sh[i], ss);
+        ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 4));
+        ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 8));
+        ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 1));
+        ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 2));
+        ss = __shfl_sync(0xffffffffu, ss, 0);
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, __fdiv_rn(1.0f, (float)hd)), a.eps)));
+        for (uint32_t i = lane; i < hd; i += 32) sh[i] = __fmul_rn(__fmul_rn(sh[i], inv), norm_w[i]);
+        __syncwarp();
+    };
+    if (is_q || is_k) {
+        if (a.qk_norm_after_rope) do_rope();
+        if (norm_w != nullptr) do_norm();
+        if (!a.qk_norm_after_rope) do_rope();
+    }
+    // rotate (block index = block within the head) and quantize with one scale for the whole head
+    const uint32_t nb = hd / 64;
+    float v0[2], v1[2], mx = 0.0f;
+    for (uint32_t b = 0; b < nb; ++b) {
+        v0[b] = sh[b * 64 + 2 * lane];
+        v1[b] = sh[b * 64 + 2 * lane + 1];
+        warp_fwht64(v0[b], v1[b], b, lane);
+        mx = fmaxf(mx, fmaxf(fabsf(v0[b]), fabsf(v1[b])));
+    }
+    mx = warp_max(mx);
+    int8_t *dst_q;
+    float *dst_s;
+    if (is_q) { dst_q = a.q_i8 + (size_t)head * hd; dst_s = a.q_scale + head; }
+    else {
+        const uint32_t kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + pos;
+        dst_q = (is_k ? a.k_q8 : a.v_q8) + slot * hd;
+        dst_s = (is_k ? a.k_scale : a.v_scale) + slot;
+    }
+    const bool zero = mx <= 1.1920929e-07f;
+    const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx);
+    for (uint32_t b = 0; b < nb; ++b) {
+        const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
+        reinterpret_cast<char2 *>(dst_q + b * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+    }
+    if (lane == 0) *dst_s = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
+}
+
+// ------------------------------------------------------------------------------------------------
+// split-KV decode attention over the int8 Hadamard cache (causal_gqa_group_q8, 8471-8594)
+// ------------------------------------------------------------------------------------------------
+// One warp per (kv head, split).  Scores: lane = position (K row of hd bytes, dp4a against the
+// group's int8 queries); values: lane = four dimensions (two half-warps take alternate positions).
+// Used for contexts longer than ATTN_EXACT_CTX positions.  Scores (and so the maximum) are the CPU's bit
+// for bit.  Softmax is the online form; partial (max, sum, out) per split are merged by attn_finish_kernel.  Sums run in a different order than the CPU's
+// position-ascending chains: the output agrees to fp32 rounding, not bit for bit.
+// positions per split: the context divided over the splits, in whole 32-position tiles
+__device__ __forceinline__ uint32_t split_span(uint32_t ctx, uint32_t n_split) {
+    return (((ctx + n_split - 1) / n_split) + 31u) & ~31u;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
+    constexpr int QW = HD / 4;            // int32 words per query / key row
+    constexpr int NB = HD / 64;
+    __shared__ int s_q[4][8][QW];         // [warp][query in group][words]
+    __shared__ float s_p[4][8][32];       // probabilities of the current 32 positions
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t split = blockIdx.x * 4 + warp, kvh = blockIdx.y;
+    if (split >= a.n_split) return;
+    const uint32_t ctx = *a.pos + 1, G = a.group;
+    if (ctx <= ATTN_EXACT_CTX) return;     // short contexts are computed in the CPU's order by attn_finish_kernel
+    const uint32_t per = split_span(ctx, a.n_split);
+    const uint32_t t_lo = min(ctx, split * per), t_hi = min(ctx, t_lo + per);
+    const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
+    const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
+    const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
+    for (uint32_t i = lane; i < G * QW; i += 32)
+        s_q[warp][i / QW][i % QW] = reinterpret_cast<const int *>(a.q_i8 + (size_t)(kvh * G) * HD)[i];
+    __syncwarp();
+    float qas[8], m[8], l[8], o[8][HD / 16];   // lane owns dims d0..d0+3 of (HD/16 ... ) see below
+    // value phase mapping: 16 lanes x 4 dims cover 64 dims; for HD = 128 each lane owns two such groups
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        qas[g] = g < (int)G ? __fmul_rn(a.q_scale[kvh * G + g], a.attn_scale) : 0.0f;
+        m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int d = 0; d < HD / 16; ++d) o[g][d] = 0.0f;
+    }
+    const uint32_t hw = lane >> 4, dl = lane & 15;   // half-warp, dim group
+    for (uint32_t t0 = t_lo; t0 < t_hi; t0 += 32) {
+        const uint32_t t = t0 + lane;
+        const bool on = t < t_hi;
+        // scores of position t for every query of the group
+        int kw[QW];
+        if (on) {
+#pragma unroll
+            for (int i = 0; i < QW / 4; ++i) {
+                const int4 v = __ldg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
+                kw[4 * i] = v.x; kw[4 * i + 1] = v.y; kw[4 * i + 2] = v.z; kw[4 * i + 3] = v.w;
+            }
+        }
+        const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
+        const bool grouped = t - tile0 < (tile_n & ~7u);
+        const float kst = on ? __ldg(ks + t) : 0.0f;
+        const float vst = on ? __ldg(vs + t) : 0.0f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g >= (int)G) break;
+            int dot = 0;
+            if (on) {
+#pragma unroll
+                for (int i = 0; i < QW; ++i) dot = __dp4a(kw[i], s_q[warp][g][i], dot);
+            }
+            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+            const float s = !on ? -INFINITY
+                          : grouped ? __fmul_rn((float)dot, __fmul_rn(kst, qas[g]))
+                                    : __fmul_rn(__fmul_rn((float)dot, kst), qas[g]);
+            const float m_new = fmaxf(m[g], warp_max(s));
+            const float corr = m[g] == -INFINITY ? 0.0f : exp_poly(m[g] - m_new);
+            const float p = on ? exp_poly(s - m_new) : 0.0f;
+            l[g] = __fmaf_rn(l[g], corr, warp_sum(p));
+#pragma unroll
+            for (int d = 0; d < HD / 16; ++d) o[g][d] *= corr;
+            m[g] = m_new;
+            s_p[warp][g][lane] = __fmul_rn(p, vst);     // weight of V row t
+        }
+        __syncwarp();
+        // values: half-warp hw takes positions t0 + hw, t0 + hw + 2, ...
+        const uint32_t n_here = min(32u, t_hi - t0);
+        for (uint32_t j = hw; j < n_here; j += 2) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const char4 v = *reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * HD + b * 64 + dl * 4);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if (g >= (int)G) break;
+                    const float w = s_p[warp][g][j];
+                    o[g][4 * b + 0] = __fmaf_rn((float)v.x, w, o[g][4 * b + 0]);
+                    o[g][4 * b + 1] = __fmaf_rn((float)v.y, w, o[g][4 * b + 1]);
+                    o[g][4 * b + 2] = __fmaf_rn((float)v.z, w, o[g][4 * b + 2]);
+                    o[g][4 * b + 3] = __fmaf_rn((float)v.w, w, o[g][4 * b + 3]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    // combine the two half-warps and write the partial result
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        if (g >= (int)G) break;
+        const uint32_t qh = kvh * G + g;
+        float *po = a.part_o + ((size_t)qh * a.n_split + split) * HD;
+#pragma unroll
+        for (int d = 0; d < HD / 16; ++d) {
+            const float other = __shfl_xor_sync(0xffffffffu, o[g][d], 16);
+            if (hw == 0) po[(d / 4) * 64 + dl * 4 + (d % 4)] = o[g][d] + other;
+        }
+        if (lane == 0) { a.part_m[(size_t)qh * a.n_split + split] = m[g]; a.part_l[(size_t)qh * a.n_split + split] = l[g]; }
+    }
+}
+
+// Finishes the attention of one query head (one CTA of HD threads, thread i = dimension i) and turns it
+// into the int8 activation of o_proj.
+//   context <= ATTN_EXACT_CTX: the whole head is computed here in the CPU's order (causal_gqa_group_q8,
+//     8471-8594): scores, maximum, exp (polynomial body in groups of 4, correctly rounded exp for the
+//     remainder), the 4-accumulator sum, then for every dimension the position-ascending fma chain over
+//     the int8 values - bit for bit the CPU result; the split kernel above exits at once.
+//   longer contexts: merges the split partials (sums in split order; fp32-rounding agreement).
+// Then: inverse rotation (block index 0/1), forward rotation with the global chunk index
+// qh*(hd/64)+b and quantization for o_proj (7059-7084).
+template <int HD>
+__global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
+    constexpr int QW = HD / 4, NB = HD / 64, VT = 64;      // VT positions per staged value tile
+    __shared__ float s_sc[ATTN_EXACT_CTX];
+    __shared__ __align__(16) int8_t s_v[VT * HD];
+    __shared__ float s_o[HD];
+    __shared__ float s_red[HD / 32];
+    __shared__ float s_inv;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = *a.pos + 1;
+    float o = 0.0f;
+    if (ctx <= ATTN_EXACT_CTX) {
+        const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
+        const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
+        const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
+        const float qas = __fmul_rn(a.q_scale[qh], a.attn_scale);
+        int qw[QW];
+#pragma unroll
+        for (int i = 0; i < QW / 4; ++i) {
+            const int4 v = reinterpret_cast<const int4 *>(a.q_i8 + (size_t)qh * HD)[i];
+            qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
+        }
+        float mx = -INFINITY;
+        for (uint32_t t = tid; t < ctx; t += HD) {
+            int dot = 0;
+#pragma unroll
+            for (int i = 0; i < QW / 4; ++i) {
+                const int4 v = __ldg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
+                dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
+                dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
+            }
+            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+            const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
+            const float kst = __ldg(ks + t);
+            const float sc = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
+                                                           : __fmul_rn(__fmul_rn((float)dot, kst), qas);
+            s_sc[t] = sc;
+            mx = fmaxf(mx, sc);
+        }
+        mx = warp_max(mx);
+        if (lane == 0) s_red[warp] = mx;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < HD / 32; ++i) mx = fmaxf(mx, s_red[i]);
+        // softmax_unnorm (9603-9632): polynomial exp for whole groups of 4 positions, libm exp for the rest
+        const uint32_t n4 = ctx & ~3u;
+        for (uint32_t t = tid; t < ctx; t += HD) {
+            const float x = __fsub_rn(s_sc[t], mx);
+            s_sc[t] = t < n4 ? exp_poly(x) : (float)exp((double)x);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            float acc = 0.0f;
+            if (lane < 4)
+                for (uint32_t t = lane; t < n4; t += 4) acc = __fadd_rn(acc, s_sc[t]);
+            acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0+a1, lane 2: a2+a3
+            acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
+            if (lane == 0) {
+                for (uint32_t t = n4; t < ctx; ++t) acc = __fadd_rn(acc, s_sc[t]);
+                s_inv = __fdiv_rn(1.0f, acc);
+            }
+        }
+        __syncthreads();
+        const float inv = s_inv;
+        for (uint32_t t = tid; t < ctx; t += HD) s_sc[t] = __fmul_rn(__fmul_rn(s_sc[t], inv), __ldg(vs + t));
+        // values: tiles of VT positions staged in shared memory (next tile prefetched into registers)
+        constexpr int LD = VT / 16;            // int4 loads per thread and tile: VT*HD/16 over HD threads
+        int4 nxt[LD];
+        auto fetch = [&](uint32_t t0) {
+#pragma unroll
+            for (int j = 0; j < LD; ++j) {
+                const uint32_t e = (uint32_t)j * HD + tid;             // int4 index within the tile
+                const uint32_t t = t0 + e / (HD / 16);
+                nxt[j] = t < ctx ? __ldg(reinterpret_cast<const int4 *>(V + (size_t)t0 * HD) + e) : make_int4(0, 0, 0, 0);
+            }
+        };
+        fetch(0);
+        for (uint32_t t0 = 0; t0 < ctx; t0 += VT) {
+            __syncthreads();                   // weights written / previous tile consumed
+#pragma unroll
+            for (int j = 0; j < LD; ++j) reinterpret_cast<int4 *>(s_v)[(uint32_t)j * HD + tid] = nxt[j];
+            __syncthreads();
+            if (t0 + VT < ctx) fetch(t0 + VT);
+            const uint32_t n_here = min((uint32_t)VT, ctx - t0);
+#pragma unroll 8
+            for (uint32_t j = 0; j < n_here; ++j) {
+                const float w = s_sc[t0 + j];
+                if (w != 0.0f) o = __fmaf_rn((float)s_v[j * HD + tid], w, o);
+            }
+        }
+    } else {
+        const uint32_t per = split_span(ctx, a.n_split);
+        const uint32_t used = (ctx + per - 1) / per;           // splits that hold positions
+        const float *pm = a.part_m + (size_t)qh * a.n_split, *pl = a.part_l + (size_t)qh * a.n_split;
+        float M = -INFINITY, L = 0.0f;
+        for (uint32_t s = 0; s < used; ++s) M = fmaxf(M, pm[s]);
+        for (uint32_t s = 0; s < used; ++s) {
+            const float wgt = exp_poly(pm[s] - M);
+            L = __fmaf_rn(pl[s], wgt, L);
+            o = __fmaf_rn(a.part_o[((size_t)qh * a.n_split + s) * HD + tid], wgt, o);
+        }
+        o = __fmul_rn(o, __fdiv_rn(1.0f, L));
+    }
+    s_o[tid] = o;
+    __syncthreads();
+    if (warp < NB) {
+        const uint32_t b = warp;
+        float x0 = s_o[b * 64 + 2 * lane], x1 = s_o[b * 64 + 2 * lane + 1];
+        warp_ifwht64(x0, x1, b, lane);
+        if (a.attn_out != nullptr) reinterpret_cast<float2 *>(a.attn_out + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
+        const uint32_t c = qh * NB + b;
+        warp_fwht64(x0, x1, c, lane);
+        int q0, q1, sum;
+        float sc;
+        warp_quant64(x0, x1, q0, q1, sc, sum);
+        reinterpret_cast<char2 *>(a.out_q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+        if (lane == 0) { a.out_scales[c] = sc; a.out_sums[c] = sum; }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU + FWHT-64 + int8  (swiglu_activate_neon 9811-9842, then the down_proj activation)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restrict__ gate_up, uint32_t inter,
+                                                           int8_t *__restrict__ q, float *__restrict__ scales,
+                                                           int32_t *__restrict__ sums, float *__restrict__ dbg) {
+    const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (c >= inter / 64) return;
+    const float2 g = reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64)[lane];
+    const float2 u = reinterpret_cast<const float2 *>(gate_up + inter + (size_t)c * 64)[lane];
+    float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_poly(-g.x))), u.x);
+    float x1 = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, exp_poly(-g.y))), u.y);
+    if (dbg != nullptr) reinterpret_cast<float2 *>(dbg + (size_t)c * 64)[lane] = make_float2(x0, x1);
+    warp_fwht64(x0, x1, c, lane);
+    int q0, q1, sum;
+    float sc;
+    warp_quant64(x0, x1, q0, q1, sc, sum);
+    reinterpret_cast<char2 *>(q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+    if (lane == 0) { scales[c] = sc; sums[c] = sum; }
+}
+
+// ------------------------------------------------------------------------------------------------
+// greedy step: argmax (first maximum, argmax_scalar 9914-9924), record the token, advance the position
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restrict__ logits, uint32_t n,
+                                                           uint32_t *__restrict__ token, uint32_t *__restrict__ pos,
+                                                           uint32_t *__restrict__ history, uint32_t *__restrict__ step) {
+    __shared__ float s_v[32];
+    __shared__ uint32_t s_i[32];
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t i = threadIdx.x; i < n; i += 1024) {
+        const float v = logits[i];
+        if (v > bv) { bv = v; bi = i; }         // ascending i per thread: keeps the first maximum
+    }
+    auto better = [](float v, uint32_t i, float bv2, uint32_t bi2) { return v > bv2 || (v == bv2 && i < bi2); };
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, m);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        bv = s_v[threadIdx.x]; bi = s_i[threadIdx.x];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, m);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) {
+            if (bi == 0xffffffffu) bi = 0;      // all NaN / -inf: the scalar loop also returns 0
+            *token = bi;
+            if (history != nullptr) history[*step] = bi;
+            *step += 1;
+            *pos += 1;
+        }
+    }
+}
+
+__global__ void advance_pos_kernel(uint32_t *pos) { *pos += 1; }
+
+// ------------------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------------------
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a) {
+    embed_kernel<<<(a.nc + 7) / 8, 256, 0, s>>>(a);
+    return cudaGetLastError();
+}
+cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                 int8_t *q, float *scales, int32_t *sums) {
+    const size_t smem = (size_t)n * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    rmsnorm_quant_kernel<<<1, 256, smem, s>>>(hidden, delta, w, n, eps, q, scales, sums);
+    return cudaGetLastError();
+}
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a) {
+    const uint32_t heads = a.n_q + 2 * a.n_kv;
+    qkv_post_kernel<<<(heads + 3) / 4, 128, 0, s>>>(a);
+    return cudaGetLastError();
+}
+cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a) {
+    dim3 grid((a.n_split + 3) / 4, a.n_kv);
+    if (a.head_dim == 64) attn_partial_kernel<64><<<grid, 128, 0, s>>>(a);
+    else if (a.head_dim == 128) attn_partial_kernel<128><<<grid, 128, 0, s>>>(a);
+    else return cudaErrorInvalidValue;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (a.head_dim == 64) attn_finish_kernel<64><<<a.n_kv * a.group, 64, 0, s>>>(a);
+    else attn_finish_kernel<128><<<a.n_kv * a.group, 128, 0, s>>>(a);
+    return cudaGetLastError();
+}
+cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
+                                float *dbg) {
+    swiglu_quant_kernel<<<(inter / 64 + 7) / 8, 256, 0, s>>>(gate_up, inter, q, scales, sums, dbg);
+    return cudaGetLastError();
+}
+cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
+                               uint32_t *history, uint32_t *step) {
+    argmax_step_kernel<<<1, 1024, 0, s>>>(logits, n, token, pos, history, step);
+    return cudaGetLastError();
+}
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos) {
+    advance_pos_kernel<<<1, 1, 0, s>>>(pos);
+    return cudaGetLastError();
+}
+
+}  // namespace k2t

@@ -1,0 +1,60 @@
+// Launchers of the per-token kernels around the GEMVs (k2t_model_kernels.cu).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "k2t_layout.h"
+
+namespace k2t {
+
+struct EmbedArgs {               // tied embedding = row of the lm_head matrix (device layout), or a bf16 table
+    const uint8_t *plane[3];
+    const uint16_t *scales;
+    const uint16_t *embed_bf16;  // [vocab][hidden] or null
+    const uint32_t *token;       // device
+    float *hidden;
+    uint32_t fmt, nc, nsg_pad, sgc, sgc_shift;
+    uint32_t pitch[3], cell[3];
+    int32_t max_odd;
+    int8_t codebook[32];
+};
+
+struct QkvPostArgs {
+    const float *qkv;            // [n_q + 2 n_kv][head_dim]
+    const float *bias, *q_norm, *k_norm;     // null when absent
+    const float *rope;           // [max_seq][head_dim]: cos(hd/2), sin(hd/2)
+    const uint32_t *pos;         // device
+    int8_t *q_i8; float *q_scale;            // rotated int8 queries, one scale per head
+    int8_t *k_q8, *v_q8; float *k_scale, *v_scale;   // cache: [layer][kv head][max_seq][head_dim] / [..][max_seq]
+    uint32_t n_q, n_kv, head_dim, max_seq, layer;
+    float eps;
+    int32_t qk_norm_after_rope;
+};
+
+// Contexts up to this many positions are attended in the CPU's summation order (bit-identical output);
+// longer ones by the split-KV kernel (fp32-rounding agreement).
+#define ATTN_EXACT_CTX 512u
+
+struct AttnArgs {
+    const int8_t *q_i8; const float *q_scale;
+    const int8_t *k_q8, *v_q8; const float *k_scale, *v_scale;
+    const uint32_t *pos;         // device: position of the current token (context = pos + 1)
+    float *part_m, *part_l, *part_o;         // [n_q][n_split], [n_q][n_split], [n_q][n_split][head_dim]
+    float *attn_out;             // optional fp32 attention output [n_q][head_dim] (tests), may be null
+    int8_t *out_q; float *out_scales; int32_t *out_sums;   // activation of o_proj
+    uint32_t n_kv, group, head_dim, max_seq, layer, n_split;
+    float attn_scale;
+};
+
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a);
+cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                 int8_t *q, float *scales, int32_t *sums);
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a);
+cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a);     // two kernels
+cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
+                                float *dbg);
+cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
+                               uint32_t *history, uint32_t *step);
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos);
+
+}  // namespace k2t

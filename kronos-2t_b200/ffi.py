@@ -32,6 +32,18 @@ class MatrixDesc(C.Structure):
     ]
 
 
+class EngineConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("hidden_size", "num_layers", "num_attention_heads", "num_key_value_heads",
+                                          "head_dim", "intermediate_size", "vocab_size", "max_seq_len")] + \
+               [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)]
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("input_norm", C.c_void_p), ("post_attn_norm", C.c_void_p), ("qkv_bias", C.c_void_p),
+                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("qkv_proj", MatrixDesc), ("o_proj", MatrixDesc), ("gate_up_proj", MatrixDesc), ("down_proj", MatrixDesc)]
+
+
 def load_library():
     """Loads libkronos_cuda.so; raises if it has not been built (no fallback exists)."""
     global _LIB
@@ -65,6 +77,17 @@ def load_library():
     sig("kronos_cuda_fwht_quant_dev", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
     sig("kronos_cuda_linear_noalloc", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_gemv_dev", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
+    sig("kronos_cuda_engine_create", vp, vp, C.POINTER(EngineConfig), vp, C.POINTER(LayerDesc), sz, vp,
+        C.POINTER(MatrixDesc), vp)
+    sig("kronos_cuda_engine_destroy", None, vp)
+    sig("kronos_cuda_engine_forward_tokens", i32, vp, vp, sz, sz, vp, vp)
+    sig("kronos_cuda_engine_forward_token_ids", i32, vp, vp, sz, sz, vp, vp)
+    sig("kronos_cuda_engine_decode_greedy", i32, vp, u32, sz, sz, vp, vp)
+    sig("kronos_cuda_engine_kv_bytes", sz, vp, sz)
+    sig("kronos_cuda_engine_weight_bytes", sz, vp)
+    sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
+    sig("kronos_cuda_engine_read_attention", i32, vp, vp)
+    sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     _LIB = L
     return L
 
@@ -223,3 +246,101 @@ class Context:
     def gemv_dev(self, mat, d_xq, d_xs, d_xsum, n_tok, d_out, out_stride=None, d_dots=None):
         self._check(self.L.kronos_cuda_gemv_dev(self.handle, mat.handle, d_xq, d_xs, d_xsum, n_tok, d_out,
                                                 out_stride or mat.rows, d_dots))
+
+
+def desc_of(m):
+    """MatrixDesc of a host matrix object with the fields of the file formats: kind 0 (bit-planes: rows, cols,
+    planes, data, scales) or kind 2 (NF: rows, cols, bits, sgc, codebook, pair, tail)."""
+    if m.kind == MATRIX_BIPOLAR:
+        return bipolar_desc(m.rows, m.cols, m.planes, m.data, m.scales)
+    return nf_desc(m.rows, m.cols, m.bits, m.sgc, m.codebook, m.pair, m.tail)
+
+
+class Engine:
+    """Whole-token decode engine (KronosCudaEngine).  `spec`: dict with cfg {hidden, layers, n_q, n_kv, head_dim,
+    inter, vocab, max_seq, eps[, qk_norm_after_rope]}, layers [{input_norm, post_norm, qkv_bias, q_norm, k_norm,
+    qkv, o, gate_up, down}], final_norm, lm_head, rope [max_seq][head_dim], embed_bf16 (or None = tied)."""
+
+    def __init__(self, ctx, spec):
+        self.ctx, self.L = ctx, ctx.L
+        c = spec["cfg"]
+        self.cfg = EngineConfig(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
+                                c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), 8)
+        keep = []
+
+        def vec(a):
+            if a is None:
+                return None
+            a = _np(a, np.float32)
+            keep.append(a)
+            return a.ctypes.data
+
+        layers = (LayerDesc * c["layers"])()
+        for l, ly in enumerate(spec["layers"]):
+            d = layers[l]
+            d.input_norm, d.post_attn_norm = vec(ly["input_norm"]), vec(ly["post_norm"])
+            d.qkv_bias, d.q_norm, d.k_norm = vec(ly.get("qkv_bias")), vec(ly.get("q_norm")), vec(ly.get("k_norm"))
+            for name, key in (("qkv_proj", "qkv"), ("o_proj", "o"), ("gate_up_proj", "gate_up"), ("down_proj", "down")):
+                md = desc_of(ly[key])
+                keep.append(md._keep)
+                setattr(d, name, md)
+        head = desc_of(spec["lm_head"])
+        rope, fn = _np(spec["rope"], np.float32), _np(spec["final_norm"], np.float32)
+        emb = None if spec.get("embed_bf16") is None else _np(spec["embed_bf16"], np.uint16)
+        self.handle = self.L.kronos_cuda_engine_create(ctx.handle, C.byref(self.cfg), _p(rope), layers, c["layers"],
+                                                       _p(fn), C.byref(head), _p(emb))
+        if not self.handle:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(ctx.handle).decode())
+
+    def close(self):
+        if self.handle:
+            self.L.kronos_cuda_engine_destroy(self.handle)
+            self.handle = None
+
+    def forward_tokens(self, embeds, pos_start=0, want_all=False):
+        e = _np(embeds, np.float32).reshape(-1, self.cfg.hidden_size)
+        n, v = e.shape[0], self.cfg.vocab_size
+        last = np.empty(v, np.float32)
+        allv = np.empty((n, v), np.float32) if want_all else None
+        self.ctx._check(self.L.kronos_cuda_engine_forward_tokens(self.handle, _p(e), n, pos_start, _p(allv), _p(last)))
+        return allv if want_all else last
+
+    def forward_token_ids(self, tokens, pos_start=0, want_all=False):
+        t = _np(tokens, np.uint32).reshape(-1)
+        n, v = t.size, self.cfg.vocab_size
+        last = np.empty(v, np.float32)
+        allv = np.empty((n, v), np.float32) if want_all else None
+        self.ctx._check(self.L.kronos_cuda_engine_forward_token_ids(self.handle, _p(t), n, pos_start, _p(allv), _p(last)))
+        return allv if want_all else last
+
+    def decode_greedy(self, first_token, pos_start, n_steps, want_logits=False):
+        out = np.empty(n_steps, np.uint32)
+        logits = np.empty(self.cfg.vocab_size, np.float32) if want_logits else None
+        self.ctx._check(self.L.kronos_cuda_engine_decode_greedy(self.handle, int(first_token), pos_start, n_steps, _p(out),
+                                                                _p(logits)))
+        return (out, logits) if want_logits else out
+
+    def kv_bytes(self, positions):
+        return self.L.kronos_cuda_engine_kv_bytes(self.handle, positions)
+
+    @property
+    def weight_bytes(self):
+        return self.L.kronos_cuda_engine_weight_bytes(self.handle)
+
+    def read_hidden(self):
+        out = np.empty(self.cfg.hidden_size, np.float32)
+        self.ctx._check(self.L.kronos_cuda_engine_read_hidden(self.handle, _p(out)))
+        return out
+
+    def read_attention(self):
+        out = np.empty(self.cfg.num_attention_heads * self.cfg.head_dim, np.float32)
+        self.ctx._check(self.L.kronos_cuda_engine_read_attention(self.handle, _p(out)))
+        return out
+
+    def read_kv(self, layer, kv_head, position):
+        """(k_q8, k_scale, v_q8, v_scale) of one cache slot."""
+        hd = self.cfg.head_dim
+        k, v = np.empty(hd, np.int8), np.empty(hd, np.int8)
+        ks, vs = np.empty(1, np.float32), np.empty(1, np.float32)
+        self.ctx._check(self.L.kronos_cuda_engine_read_kv(self.handle, layer, kv_head, position, _p(k), _p(ks), _p(v), _p(vs)))
+        return k, float(ks[0]), v, float(vs[0])

@@ -90,6 +90,7 @@ struct K2oModel {
     size_t pos = 0;
     // taps of the last forward (for tests)
     std::vector<float> tap_hidden;    // hidden state after every layer [layers][hidden]
+    std::vector<float> tap_attn;      // attention output of the last layer, last token [n_q * head_dim]
 
     size_t kv_slot(size_t l, size_t h, size_t p) const { return (l * cfg.n_kv + h) * cfg.max_seq + p; }
 };
@@ -160,13 +161,15 @@ void attend_head(const K2oModel &m, size_t l, size_t kvh, const float *q_head, s
     }
     float mx = -INFINITY;
     for (size_t t = 0; t < seq_len; ++t) mx = std::max(mx, sc[t]);
-    // softmax_unnorm_neon (9603-9632): 4 lanes accumulate, pairwise horizontal add, libm exp for the tail
+    // softmax_unnorm_neon (9603-9632): 4 lanes accumulate, pairwise horizontal add, libm exp for the tail.
+    // The tail's f32::exp is the platform libm's expf in the reference; libms differ in the last bit on a small
+    // fraction of inputs, so the correctly rounded value (double exp rounded to float) stands in for it here.
     float acc[4] = {0, 0, 0, 0};
     size_t t = 0;
     for (; t + 4 <= seq_len; t += 4)
         for (int j = 0; j < 4; ++j) { float e = exp_poly(sc[t + j] - mx); sc[t + j] = e; acc[j] += e; }
     float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    for (; t < seq_len; ++t) { float e = std::exp(sc[t] - mx); sc[t] = e; sum += e; }
+    for (; t < seq_len; ++t) { float e = (float)std::exp((double)(sc[t] - mx)); sc[t] = e; sum += e; }
     const float inv = 1.0f / sum;
     float o[128] = {0};
     for (size_t tt = 0; tt < seq_len; ++tt) {      // attn_values_head*_q8_accum_neon (9121-9162)
@@ -252,6 +255,17 @@ void k2o_model_embed(const K2oModel *m, uint32_t token, float *out) {
 }
 
 const float *k2o_model_tap_hidden(const K2oModel *m) { return m->tap_hidden.data(); }
+const float *k2o_model_tap_attention(const K2oModel *m) { return m->tap_attn.data(); }
+int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, int8_t *k_q8, float *k_scale,
+                      int8_t *v_q8, float *v_scale) {
+    if (!m || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;
+    const size_t slot = m->kv_slot(layer, kv_head, pos), hd = m->cfg.head_dim;
+    std::memcpy(k_q8, m->k_q8.data() + slot * hd, hd);
+    std::memcpy(v_q8, m->v_q8.data() + slot * hd, hd);
+    *k_scale = m->k_sc[slot];
+    *v_scale = m->v_sc[slot];
+    return 0;
+}
 
 // One decode step from an embedding vector (what the device boundary receives); logits[vocab].
 int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads) {
@@ -284,6 +298,7 @@ int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logi
         }
         for (size_t qh = 0; qh < c.n_q; ++qh)
             attend_head(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
+        if (l + 1 == c.layers) m->tap_attn = attn;
         act.populate(attn.data(), q_dim);
         L.o.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
         for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);   // add_inplace = axpy(1.0)

@@ -163,6 +163,11 @@ int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logi
 int k2o_model_forward_token(K2oModel *m, uint32_t token, float *logits, size_t threads);
 /* hidden state after every layer of the last step, [layers][hidden]. */
 const float *k2o_model_tap_hidden(const K2oModel *m);
+/* Attention output (before o_proj) of the last layer for the last token: [n_q * head_dim]. */
+const float *k2o_model_tap_attention(const K2oModel *m);
+/* One KV cache slot (layer, kv head, position): int8 rotated values [head_dim] and fp32 scales. */
+int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, int8_t *k_q8, float *k_scale,
+                      int8_t *v_q8, float *v_scale);
 uint32_t k2o_argmax(const float *v, size_t n);                                   /* argmax_scalar 9914-9924 */
 void k2o_build_rope_table(size_t max_seq, size_t head_dim, double theta, float *table);   /* 9212-9236 */
 float k2o_exp_poly(float x);                                                     /* exp_f32_neon 9430-9454 */

@@ -412,6 +412,8 @@ def _declare_model(L):
     L.k2o_model_forward_embedding.restype, L.k2o_model_forward_embedding.argtypes = C.c_int, [P, P, P, C.c_size_t]
     L.k2o_model_forward_token.restype, L.k2o_model_forward_token.argtypes = C.c_int, [P, C.c_uint32, P, C.c_size_t]
     L.k2o_model_tap_hidden.restype, L.k2o_model_tap_hidden.argtypes = P, [P]
+    L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
+    L.k2o_model_read_kv.restype, L.k2o_model_read_kv.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
     L.k2o_argmax.restype, L.k2o_argmax.argtypes = C.c_uint32, [P, C.c_size_t]
     L.k2o_build_rope_table.restype, L.k2o_build_rope_table.argtypes = None, [C.c_size_t, C.c_size_t, C.c_double, P]
     L.k2o_exp_poly.restype, L.k2o_exp_poly.argtypes = C.c_float, [C.c_float]
@@ -522,6 +524,18 @@ class Model:
         p = self.L.k2o_model_tap_hidden(self.h)
         n = self.cfg.layers * self.cfg.hidden
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).reshape(self.cfg.layers, self.cfg.hidden).copy()
+
+    def tap_attention(self):
+        p = self.L.k2o_model_tap_attention(self.h)
+        n = self.cfg.n_q * self.cfg.head_dim
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).copy()
+
+    def read_kv(self, layer, kv_head, pos):
+        hd = self.cfg.head_dim
+        k, v = np.zeros(hd, np.int8), np.zeros(hd, np.int8)
+        ks, vs = np.zeros(1, np.float32), np.zeros(1, np.float32)
+        assert self.L.k2o_model_read_kv(self.h, layer, kv_head, pos, _ptr(k), _ptr(ks), _ptr(v), _ptr(vs)) == 0
+        return k, float(ks[0]), v, float(vs[0])
 
     def greedy(self, prompt, steps, threads=8):
         """Feeds `prompt` token by token, then decodes `steps` tokens greedily. Returns (tokens, last logits)."""
