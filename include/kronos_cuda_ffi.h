@@ -191,6 +191,11 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
 /* Diagnostic: attention output of the last layer for the last forwarded token, before o_proj:
  * [num_attention_heads * head_dim] (the `attn` vector of forward_token, real_llm.rs:6651-6700). */
 int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *engine, float *attention);
+/* Diagnostic: phase trace of the whole-token decode kernel (the last step of the last decode_greedy call that
+ * used it): global-timer readings in ns taken by CTA 0 at the start of the step, then around every phase
+ * (activation prologue done / GEMV done / grid barrier passed; the attention phase has two marks).  Returns
+ * the number of marks written (0 when that kernel is not in use).  No counterpart in the reference. */
+size_t kronos_cuda_engine_decode_trace(KronosCudaEngine *engine, uint64_t *marks_ns, size_t cap);
 /* Diagnostic: one KV cache entry (layer, kv head, position): k_q8/v_q8[head_dim] rotated int8 values and
  * their fp32 scales - the contents of the reference's k_q8 / k_scales / v_q8 / v_scales slot
  * (KvCache, real_llm.rs:8303-8365). */

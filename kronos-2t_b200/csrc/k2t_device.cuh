@@ -34,6 +34,28 @@ __device__ __forceinline__ uint32_t lop3_select(uint32_t lo, uint32_t hi, uint32
     asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(d) : "r"(mask), "r"(hi), "r"(lo));
     return d;
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream still runs.  pdl_wait() returns once the predecessor grid has
+// completed and its writes are visible; everything a kernel reads that another kernel wrote, and every
+// global write, comes after it (weights are immutable and may be fetched before).  pdl_trigger() lets the
+// successor start launching.  Both are no-ops for a kernel launched the ordinary way.  Data produced
+// by other kernels is read with ld.global.cg (L2) so that no SM-local cache line from before the wait is used.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches `kernel` on `stream`, optionally as a programmatic dependent of the previous kernel in the stream.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
 
 // Streaming 128-bit load that does not allocate in L1 (weights are read exactly once).

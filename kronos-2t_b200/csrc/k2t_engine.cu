@@ -4,11 +4,13 @@
 // forward replay a captured CUDA graph (position, token and step counter live in device memory).
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
 
 #include "k2t_context.h"
+#include "k2t_decode_mega.h"
 #include "k2t_model_kernels.h"
 
 using namespace k2t;
@@ -35,9 +37,20 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
     size_t weight_bytes = 0;
     std::vector<void *> allocs;
-    cudaGraphExec_t graph_greedy = nullptr, graph_ids = nullptr;
+    // whole-token decode kernel (contexts up to ATTN_EXACT_CTX positions)
+    bool mega_ok = false;
+    std::string mega_why;                     // why the kernel is not used, when it is not
+    float *hidden2 = nullptr;
+    k2t::MegaLayer *d_mega_layers = nullptr;
+    k2t::MegaMatrix *d_mega_head = nullptr;
+    uint32_t *d_barrier = nullptr;
+    unsigned long long *d_trace = nullptr;    // phase trace of the last step of the last decode-kernel call
+    uint32_t mega_warp_smem = 0, mega_kmax = 0;
+    size_t mega_smem = 0;
+    cudaGraphExec_t graphs[4] = {nullptr, nullptr, nullptr, nullptr};      // [greedy ? 0 : 1][long context ? 1 : 0] -> 2 * ids + long
     cudaStream_t graph_stream = nullptr;      // the stream the graphs were captured on
 };
 
@@ -57,7 +70,7 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
 bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out) {
     uint32_t launched = 0;
     cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q, e->act_s, e->act_m, 1, out, m->dm.geom.rows, nullptr,
-                                  e->ctx->sm_count, e->ctx->d_err, &launched);
+                                  e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
     e->ctx->launches += launched;
     return cuda_ok(e->ctx, err, "engine gemv");
 }
@@ -67,52 +80,58 @@ bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 
     return cuda_ok(e->ctx, err, what);
 }
 
+void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a);
+
 // Queues the kernels of one token on the context's stream.  `embed`: look d_token up first.
 // `greedy`: finish with argmax (next token, history, step, position); otherwise only advance the position.
-bool enqueue_step(KronosCudaEngine *e, bool embed, bool greedy) {
+bool enqueue_step(KronosCudaEngine *e, bool embed, bool greedy, bool long_ctx) {
     const KronosCudaEngineConfig &c = e->cfg;
     cudaStream_t s = e->ctx->stream;
     const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd;
     if (embed) {
-        const MatrixGeom &g = e->lm_head->dm.geom;
         EmbedArgs a{};
-        for (int k = 0; k < 3; ++k) { a.plane[k] = e->lm_head->dm.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; a.cell[k] = g.cell[k]; }
-        a.scales = reinterpret_cast<const uint16_t *>(e->lm_head->dm.d_base + g.scale_off);
-        a.embed_bf16 = e->embed_bf16; a.token = e->d_token; a.hidden = e->hidden;
-        a.fmt = g.fmt; a.nc = g.nc; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.max_odd = g.max_odd;
-        a.sgc_shift = 32;
-        for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
-        for (int i = 0; i < 32; ++i) a.codebook[i] = g.codebook32[i];
-        if (!count(e, launch_embed(s, a), "embed")) return false;
+        fill_embed_args(e, a);
+        if (!count(e, launch_embed(s, a, false), "embed")) return false;
     }
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const EngineLayer &L = e->layers[l];
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, l == 0 ? nullptr : e->proj, L.input_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m), "rmsnorm")) return false;
+        if (!count(e, launch_rmsnorm_quant(s, e->hidden, l == 0 ? nullptr : e->proj, L.input_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl && (embed || l > 0)), "rmsnorm")) return false;
         if (!gemv(e, L.qkv, e->qkv)) return false;
-        QkvPostArgs qa{};
-        qa.qkv = e->qkv; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope; qa.pos = e->d_pos;
-        qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
-        qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
-        qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope;
-        if (!count(e, launch_qkv_post(s, qa), "qkv_post")) return false;
-        AttnArgs aa{};
-        aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
-        aa.pos = e->d_pos; aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = l + 1 == c.num_layers ? e->attn_tap : nullptr;
-        aa.out_q = e->act_q; aa.out_scales = e->act_s; aa.out_sums = e->act_m;
-        aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
-        aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
-        if (!count(e, launch_attention(s, aa), "attention", 2)) return false;
+        if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
+            FusedAttnArgs fa{};
+            fa.qkv = e->qkv; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope; fa.pos = e->d_pos;
+            fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
+            fa.attn_tap = l + 1 == c.num_layers ? e->attn_tap : nullptr;
+            fa.out_q = e->act_q; fa.out_scales = e->act_s; fa.out_sums = e->act_m; fa.err_flag = e->ctx->d_err;
+            fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
+            fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
+            if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
+        } else {
+            QkvPostArgs qa{};
+            qa.qkv = e->qkv; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope; qa.pos = e->d_pos;
+            qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
+            qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
+            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope;
+            if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
+            AttnArgs aa{};
+            aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
+            aa.pos = e->d_pos; aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = l + 1 == c.num_layers ? e->attn_tap : nullptr;
+            aa.out_q = e->act_q; aa.out_scales = e->act_s; aa.out_sums = e->act_m;
+            aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
+            aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
+            if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
+        }
         if (!gemv(e, L.o, e->proj)) return false;
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m), "rmsnorm")) return false;
+        if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl), "rmsnorm")) return false;
         if (!gemv(e, L.gate_up, e->gate_up)) return false;
-        if (!count(e, launch_swiglu_quant(s, e->gate_up, c.intermediate_size, e->act_q, e->act_s, e->act_m, nullptr), "swiglu")) return false;
+        if (!count(e, launch_swiglu_quant(s, e->gate_up, c.intermediate_size, e->act_q, e->act_s, e->act_m, nullptr, e->pdl), "swiglu")) return false;
         if (!gemv(e, L.down, e->proj)) return false;
     }
-    if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m), "rmsnorm")) return false;
+    if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl), "rmsnorm")) return false;
     if (!gemv(e, e->lm_head, e->logits)) return false;
     (void)q_dim;
-    if (greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step), "argmax");
-    return count(e, launch_advance_pos(s, e->d_pos), "advance");
+    if (greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
+    return count(e, launch_advance_pos(s, e->d_pos, e->pdl), "advance");
 }
 
 bool set_u32(KronosCudaEngine *e, uint32_t *dst, uint32_t v) {
@@ -123,33 +142,125 @@ bool set_u32(KronosCudaEngine *e, uint32_t *dst, uint32_t v) {
 // Captures one step into an executable graph (first use on the current stream).
 bool ensure_graphs(KronosCudaEngine *e) {
     KronosCudaContext *ctx = e->ctx;
-    if (e->graph_greedy && e->graph_stream == ctx->stream) return true;
-    if (e->graph_greedy) { cudaGraphExecDestroy(e->graph_greedy); e->graph_greedy = nullptr; }
-    if (e->graph_ids) { cudaGraphExecDestroy(e->graph_ids); e->graph_ids = nullptr; }
-    // one eager step first (position 0, token 0; callers set both before every replay): loads every kernel
+    if (e->graphs[0] && e->graph_stream == ctx->stream) return true;
+    for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+    // eager steps first (position 0, token 0; callers set both before every replay): loads every kernel
     // and sets its attributes outside a capture, where an error is also easier to attribute
-    if (!set_u32(e, e->d_pos, 0) || !set_u32(e, e->d_token, 0) || !enqueue_step(e, true, true) ||
-        !sync_and_check(ctx, "engine warm-up step"))
-        return false;
+    for (int long_ctx = 0; long_ctx < 2; ++long_ctx)
+        if (!set_u32(e, e->d_pos, 0) || !set_u32(e, e->d_token, 0) || !enqueue_step(e, true, true, long_ctx != 0) ||
+            !sync_and_check(ctx, "engine warm-up step"))
+            return false;
     const uint64_t launches_before = ctx->launches;
-    for (int which = 0; which < 2; ++which) {
+    for (int which = 0; which < 4; ++which) {
         cudaGraph_t graph = nullptr;
         if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return false;
-        const bool ok = enqueue_step(e, true, which == 0);
+        const bool ok = enqueue_step(e, true, which < 2, (which & 1) != 0);
         cudaError_t err = cudaStreamEndCapture(ctx->stream, &graph);
         if (!ok || !cuda_ok(ctx, err, "end capture")) { if (graph) cudaGraphDestroy(graph); return false; }
         cudaGraphExec_t exec = nullptr;
         err = cudaGraphInstantiate(&exec, graph, 0);
         cudaGraphDestroy(graph);
         if (!cuda_ok(ctx, err, "graph instantiate")) return false;
-        (which == 0 ? e->graph_greedy : e->graph_ids) = exec;
+        e->graphs[which] = exec;
     }
     ctx->launches = launches_before;          // captured, not launched
     e->graph_stream = ctx->stream;
     return true;
 }
 
-uint32_t launches_per_step(const KronosCudaEngine *e) { return 1 + e->cfg.num_layers * 10 + 2 + 1; }
+// the graph of one step: greedy (argmax on the device) or logits only, for the context length this position gives
+cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
+    return e->graphs[(greedy ? 0 : 2) + (pos + 1 > ATTN_EXACT_CTX ? 1 : 0)];
+}
+uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
+    return 1 + e->cfg.num_layers * (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + 2 + 1;
+}
+
+constexpr uint32_t TRACE_CAP = 2048;
+
+// Builds the device-side tables of the whole-token decode kernel.  Leaves mega_ok false (with the reason in
+// mega_why) when the model does not fit the kernel; the per-operator path then serves every call.
+bool setup_mega(KronosCudaEngine *e) {
+    KronosCudaContext *ctx = e->ctx;
+    const KronosCudaEngineConfig &c = e->cfg;
+    // Off unless KRONOS_CUDA_MEGA=1: at the model sizes measured so far a grid barrier costs as much as a kernel
+    // boundary of the CUDA-graph path (about 2 us) and the phases between them are latency-bound, so the graph of
+    // per-operator kernels decodes faster; the kernel is kept for its phase trace and as the base for further work.
+    const char *want = std::getenv("KRONOS_CUDA_MEGA");
+    if (!want || want[0] != '1') { e->mega_why = "not requested (KRONOS_CUDA_MEGA=1 enables it)"; return true; }
+    if (c.num_attention_heads > (uint32_t)ctx->sm_count) { e->mega_why = "more query heads than SMs"; return true; }
+    uint32_t warp_smem = 0;
+    auto fill = [&](const KronosCudaMatrix *m, MegaMatrix &mm) {
+        const int fmt = fill_gemv_args(m->dm, true, mm.g);
+        mm.fmt = (uint32_t)fmt;
+        mm.g.err_flag = ctx->d_err;
+        const uint32_t np = (mm.g.nc + 31) / 32, n_rb = (mm.g.rows + 3) / 4;
+        uint32_t wk = 1;
+        while (wk < 8 && wk * 2 <= np && n_rb * wk < 8u * (uint32_t)ctx->sm_count) wk *= 2;
+        mm.wk = wk;
+        warp_smem = std::max(warp_smem, gemv_warp_smem_bytes(fmt));
+    };
+    std::vector<MegaLayer> layers(c.num_layers);
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const EngineLayer &L = e->layers[l];
+        fill(L.qkv, layers[l].qkv); fill(L.o, layers[l].o); fill(L.gate_up, layers[l].gate_up); fill(L.down, layers[l].down);
+        layers[l].input_norm = L.input_norm; layers[l].post_norm = L.post_norm; layers[l].qkv_bias = L.qkv_bias;
+        layers[l].q_norm = L.q_norm; layers[l].k_norm = L.k_norm;
+    }
+    MegaMatrix head;
+    fill(e->lm_head, head);
+    e->mega_warp_smem = (warp_smem + 127u) & ~127u;
+    e->mega_kmax = std::max(std::max(c.hidden_size, c.num_attention_heads * c.head_dim), c.intermediate_size);
+    e->mega_smem = decode_mega_smem(e->mega_warp_smem, e->mega_kmax);
+    cudaError_t chk = decode_mega_check(e->mega_smem, ctx->sm_count);
+    if (chk != cudaSuccess) {
+        cudaGetLastError();
+        e->mega_why = std::string("kernel does not fit one CTA per SM: ") + cudaGetErrorString(chk);
+        return true;
+    }
+    if (!dev_alloc(e, e->hidden2, c.hidden_size) || !dev_alloc(e, e->d_barrier, 1) || !dev_alloc(e, e->d_trace, TRACE_CAP + 1) ||
+        !dev_alloc(e, e->d_mega_layers, layers.size(), layers.data()) || !dev_alloc(e, e->d_mega_head, 1, &head) ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "decode kernel tables"))      // the host vectors go out of scope
+        return false;
+    e->mega_ok = true;
+    return true;
+}
+
+void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a) {
+    const MatrixGeom &g = e->lm_head->dm.geom;
+    for (int k = 0; k < 3; ++k) { a.plane[k] = e->lm_head->dm.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; a.cell[k] = g.cell[k]; }
+    a.scales = reinterpret_cast<const uint16_t *>(e->lm_head->dm.d_base + g.scale_off);
+    a.embed_bf16 = e->embed_bf16; a.token = e->d_token; a.hidden = e->hidden;
+    a.fmt = g.fmt; a.nc = g.nc; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.max_odd = g.max_odd;
+    a.sgc_shift = 32;
+    for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
+    for (int i = 0; i < 32; ++i) a.codebook[i] = g.codebook32[i];
+}
+
+// n_steps greedy tokens in one cooperative launch (contexts up to ATTN_EXACT_CTX positions)
+bool decode_mega(KronosCudaEngine *e, uint32_t first_token, uint32_t pos_start, uint32_t n_steps) {
+    KronosCudaContext *ctx = e->ctx;
+    const KronosCudaEngineConfig &c = e->cfg;
+    MegaArgs a{};
+    a.layers = e->d_mega_layers; a.head = e->d_mega_head;
+    a.n_layers = c.num_layers; a.hidden = c.hidden_size; a.n_q = c.num_attention_heads; a.n_kv = c.num_key_value_heads;
+    a.head_dim = c.head_dim; a.inter = c.intermediate_size; a.vocab = c.vocab_size; a.max_seq = c.max_seq_len;
+    a.eps = c.rms_norm_eps; a.attn_scale = 1.0f / sqrtf((float)c.head_dim); a.qk_norm_after_rope = c.qk_norm_after_rope;
+    a.final_norm = e->final_norm; a.rope = e->rope;
+    fill_embed_args(e, a.embed);
+    a.hidden_a = e->hidden2; a.hidden_b = e->hidden; a.proj = e->proj; a.qkv = e->qkv; a.gate_up = e->gate_up; a.logits = e->logits;
+    a.attn_tap = e->attn_tap; a.act_q = e->act_q; a.act_s = e->act_s; a.act_m = e->act_m;
+    a.k_q8 = e->k_q8; a.v_q8 = e->v_q8; a.k_scale = e->k_scale; a.v_scale = e->v_scale;
+    a.token = e->d_token; a.pos = e->d_pos; a.step = e->d_step; a.history = e->d_history;
+    a.barrier = e->d_barrier; a.err_flag = ctx->d_err;
+    a.first_token = first_token; a.pos0 = pos_start; a.n_steps = n_steps;
+    a.warp_smem = e->mega_warp_smem; a.kmax = e->mega_kmax;
+    a.trace = e->d_trace; a.trace_cap = TRACE_CAP;
+    if (!cuda_ok(ctx, cudaMemsetAsync(e->d_barrier, 0, 4, ctx->stream), "clear barrier")) return false;
+    ctx->launches += 1;
+    return cuda_ok(ctx, launch_decode_mega(ctx->stream, a, e->mega_smem, ctx->sm_count), "decode kernel launch");
+}
+
 
 }  // namespace
 
@@ -159,8 +270,7 @@ void kronos_cuda_engine_destroy(KronosCudaEngine *e) {
     if (!e) return;
     cudaSetDevice(e->ctx->device);
     cudaStreamSynchronize(e->ctx->stream);
-    if (e->graph_greedy) cudaGraphExecDestroy(e->graph_greedy);
-    if (e->graph_ids) cudaGraphExecDestroy(e->graph_ids);
+    for (cudaGraphExec_t g : e->graphs) if (g) cudaGraphExecDestroy(g);
     for (EngineLayer &L : e->layers)
         for (KronosCudaMatrix *m : {L.qkv, L.o, L.gate_up, L.down})
             if (m) kronos_cuda_matrix_free(e->ctx, m);
@@ -189,6 +299,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     KronosCudaEngine *e = new (std::nothrow) KronosCudaEngine();
     if (!e) { fail(ctx, "engine_create: out of host memory"); return nullptr; }
     e->ctx = ctx; e->cfg = c;
+    if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
     e->layers.resize(c.num_layers);
     auto bad = [&](const std::string &why) { std::string keep = why; kronos_cuda_engine_destroy(e); fail(ctx, keep); return (KronosCudaEngine *)nullptr; };
     auto shape_ok = [](const KronosCudaMatrixDesc &d, uint32_t rows, uint32_t cols) { return d.rows == rows && d.cols == cols; };
@@ -233,6 +344,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->d_token, 1) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
+    if (!setup_mega(e)) return bad(ctx->err);
     return e;
 }
 
@@ -266,6 +378,20 @@ int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *e, float *attention)
         !sync_and_check(ctx, "read attention"))
         return -1;
     return 0;
+}
+
+size_t kronos_cuda_engine_decode_trace(KronosCudaEngine *e, uint64_t *marks_ns, size_t cap) {
+    if (!e || !e->mega_ok || !marks_ns) return 0;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!make_current(ctx)) return 0;
+    std::vector<unsigned long long> buf(TRACE_CAP + 1);
+    if (!cuda_ok(ctx, cudaMemcpyAsync(buf.data(), e->d_trace, buf.size() * 8, cudaMemcpyDeviceToHost, ctx->stream), "read trace") ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "read trace"))
+        return 0;
+    const size_t n = std::min<size_t>(std::min<size_t>(buf[TRACE_CAP], TRACE_CAP), cap);
+    for (size_t i = 0; i < n; ++i) marks_ns[i] = buf[i];
+    return n;
 }
 
 int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *e, uint32_t layer, uint32_t kv_head, size_t position, int8_t *k_q8,
@@ -306,11 +432,11 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     for (size_t t = 0; t < n_tok; ++t) {
         if (tokens) {
             if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens + t, 4, cudaMemcpyHostToDevice, ctx->stream), "copy token")) return -1;
-            if (!cuda_ok(ctx, cudaGraphLaunch(e->graph_ids, ctx->stream), "graph launch")) return -1;
-            ctx->launches += launches_per_step(e);
+            if (!cuda_ok(ctx, cudaGraphLaunch(step_graph(e, false, pos_start + t), ctx->stream), "graph launch")) return -1;
+            ctx->launches += step_launches(e, pos_start + t);
         } else {
             if (!cuda_ok(ctx, cudaMemcpyAsync(e->hidden, embeds + t * h, h * 4, cudaMemcpyHostToDevice, ctx->stream), "copy embedding")) return -1;
-            if (!enqueue_step(e, false, false)) return -1;
+            if (!enqueue_step(e, false, false, pos_start + t + 1 > ATTN_EXACT_CTX)) return -1;
         }
         float *dst = all_logits ? all_logits + t * v : (t + 1 == n_tok ? last_logits : nullptr);
         if (dst && !cuda_ok(ctx, cudaMemcpyAsync(dst, e->logits, v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
@@ -340,7 +466,14 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     if (first_token >= e->cfg.vocab_size) return fail(ctx, "decode_greedy: token id out of range"), -1;
     if (pos_start + n_steps > e->cfg.max_seq_len) return fail(ctx, "decode_greedy: sequence would exceed max_seq_len"), -1;
     if (n_steps == 0) return 0;
-    if (!make_current(ctx) || !ensure_graphs(e)) return -1;
+    if (!make_current(ctx)) return -1;
+    if (e->mega_ok && pos_start + n_steps <= ATTN_EXACT_CTX) {
+        if (!decode_mega(e, first_token, (uint32_t)pos_start, (uint32_t)n_steps)) return -1;
+        if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
+        if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
+        return sync_and_check(ctx, "decode_greedy") ? 0 : -1;
+    }
+    if (!ensure_graphs(e)) return -1;
     const uint32_t init[3] = {first_token, (uint32_t)pos_start, 0u};
     if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, &init[0], 4, cudaMemcpyHostToDevice, ctx->stream), "set token") ||
         !cuda_ok(ctx, cudaMemcpyAsync(e->d_pos, &init[1], 4, cudaMemcpyHostToDevice, ctx->stream), "set pos") ||
@@ -348,8 +481,8 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
         !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "decode_greedy setup"))
         return -1;
     for (size_t i = 0; i < n_steps; ++i) {
-        if (!cuda_ok(ctx, cudaGraphLaunch(e->graph_greedy, ctx->stream), "graph launch")) return -1;
-        ctx->launches += launches_per_step(e);
+        if (!cuda_ok(ctx, cudaGraphLaunch(step_graph(e, true, pos_start + i), ctx->stream), "graph launch")) return -1;
+        ctx->launches += step_launches(e, pos_start + i);
     }
     if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
     if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;

@@ -19,10 +19,11 @@ cudaError_t launch_fwht_quant(cudaStream_t stream, const float *x, const float *
                               int32_t *sums);
 
 // Quantized GEMV / small-N GEMM over all rows. n_tok in 1..8. Returns the number of kernel launches
-// in *launches. xsum may be null for NF formats.
+// in *launches. xsum may be null for NF formats.  pdl: launch as a programmatic dependent of the previous
+// kernel in the stream (the weight pipeline starts before that kernel has finished).
 cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs,
                         const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
-                        int sm_count, uint32_t *err_flag, uint32_t *launches);
+                        int sm_count, uint32_t *err_flag, uint32_t *launches, bool pdl = false);
 
 // Largest n_tok one launch_gemv call accepts for this matrix (shared-memory bound), at most 8.
 uint32_t gemv_max_tokens(const DeviceMatrix &m);

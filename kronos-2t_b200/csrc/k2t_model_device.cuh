@@ -1,0 +1,370 @@
+// Device helpers shared by the per-token kernels and the whole-token decode kernel.
+#pragma once
+#include "k2t_device.cuh"
+#include "k2t_fwht.cuh"
+#include "k2t_model_kernels.h"
+
+namespace k2t {
+
+// exp_f32_neon (src/model/real_llm.rs:9430-9454), one lane, same operations in the same order.
+__device__ __forceinline__ float exp_poly(float x_raw) {
+    const float x = fminf(fmaxf(x_raw, -87.33654f), 88.0f);
+    const float kf = rintf(__fmul_rn(x, 1.44269504088896340736f));
+    const float r = __fmaf_rn(-kf, 1.4286068e-6f, __fmaf_rn(-kf, 0.69314575f, x));
+    float y = __fmaf_rn(1.9875691e-4f, r, 1.3982e-3f);
+    y = __fmaf_rn(y, r, 8.333452e-3f);
+    y = __fmaf_rn(y, r, 4.1665796e-2f);
+    y = __fmaf_rn(y, r, 1.6666666e-1f);
+    y = __fmaf_rn(y, r, 0.5f);
+    y = __fmaf_rn(y, r, 1.0f);
+    y = __fmaf_rn(y, r, 1.0f);
+    const int ki = (int)kf;
+    return __fmul_rn(y, __int_as_float((ki + 127) << 23));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// embedding (embed_token_into, real_llm.rs:8063-8097)
+// ------------------------------------------------------------------------------------------------
+// weight value (rotated domain) of element `col` (0..63) of cell (row, c)
+__device__ __forceinline__ float cell_value(const EmbedArgs &a, uint32_t row, uint32_t c, uint32_t col) {
+    const size_t cell = c;
+    const uint8_t *p0 = a.plane[0] + (size_t)row * a.pitch[0] + cell * a.cell[0];
+    const uint8_t *p1 = a.plane[1] + (size_t)row * a.pitch[1] + cell * a.cell[1];
+    const uint8_t *p2 = a.plane[2] + (size_t)row * a.pitch[2] + cell * a.cell[2];
+    const uint32_t sg = a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
+    const float delta = bf16_bits_to_f32(a.scales[(size_t)row * a.nsg_pad + sg]);
+    if (a.fmt == FMT_BP4 || a.fmt == FMT_BP5 || a.fmt == FMT_BP6) {
+        const uint8_t *half = col < 32 ? p0 : p1;
+        const uint32_t cc = col % 32, k = col % 8;
+        uint32_t u = (half[(cc / 8) * 4 + (k % 4)] >> (k < 4 ? 0 : 4)) & 0x0F;
+        if (a.fmt == FMT_BP5) {
+            const uint32_t bit = 8 * (col % 4) + cc / 4;
+            u |= ((p2[(col / 32) * 4 + bit / 8] >> (bit % 8)) & 1u) << 4;
+        } else if (a.fmt == FMT_BP6) {
+            const uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
+            u |= ((p2[(col / 16) * 4 + bit / 8] >> (bit % 8)) & 3u) << 4;
+        }
+        return __fmul_rn((float)(2 * (int)u - a.max_odd), delta);
+    }
+    uint32_t idx;
+    if (a.fmt == FMT_NF3) {
+        auto word = [&](uint32_t w) { return w < 4 ? reinterpret_cast<const uint32_t *>(p0)[w] : reinterpret_cast<const uint32_t *>(p1)[w - 4]; };
+        if (col < 48) idx = (word(col / 8) >> (4 * (col % 8))) & 7u;
+        else {
+            const uint32_t t = col - 48;
+            idx = 0;
+            for (uint32_t j = 0; j < 3; ++j) idx |= ((word(3 * (t / 8) + j) >> (4 * (t % 8) + 3)) & 1u) << j;
+        }
+    } else {
+        const uint8_t *half = col < 32 ? p0 : p1;
+        const uint32_t cc = col % 32, nib = col % 8;
+        idx = (half[(cc / 8) * 4 + nib / 2] >> (4 * (nib % 2))) & 0x0F;
+    }
+    return __fmul_rn((float)a.codebook[idx], delta);
+}
+
+
+// split-KV attention: positions per split = the context divided over the splits, in whole 32-position tiles
+__device__ __forceinline__ uint32_t split_span(uint32_t ctx, uint32_t n_split) {
+    return (((ctx + n_split - 1) / n_split) + 31u) & ~31u;
+}
+
+// ------------------------------------------------------------------------------------------------
+// One query head, from the fused qkv vector to the int8 activation of o_proj, by one CTA of 256 threads, for
+// contexts of up to ATTN_EXACT_CTX positions: bias, qk-norm, RoPE, rotation + int8 of the head's query and
+// of its kv head's key and value (6609-6650, 8139-8178, 8303-8365, 9287-9326; the first query head of a
+// group stores them in the cache), then causal_gqa_group_q8 (8471-8594) in the CPU's order - scores, maximum,
+// exp (polynomial body in groups of 4, correctly rounded exp for the remainder), the 4-accumulator sum, one
+// position-ascending fma chain per dimension - then the inverse rotation, the forward rotation with the
+// global chunk index and the quantization for o_proj (7059-7084).  Bit for bit the CPU result.
+// ------------------------------------------------------------------------------------------------
+constexpr uint32_t ATTN_THREADS = 256;
+
+struct AttnSmem {
+    float *sc;                 // [ATTN_EXACT_CTX]
+    int8_t *vbuf;              // [ATTN_EXACT_CTX][head_dim <= 128] cached value rows (one bulk copy)
+    uint64_t *bar;             // mbarrier of that copy
+    float *head;               // [3][128] q / k / v head being processed
+    int8_t *hq;                // [3][128] their int8 form
+    float *hs;                 // [3] scales
+    float *o;                  // [128]
+    float *red;                // [32 words]
+    float *inv;                // [1]
+};
+__host__ __device__ inline size_t attn_round(size_t v) { return (v + 127) & ~(size_t)127; }
+__host__ __device__ inline size_t attn_smem_bytes() {
+    return attn_round(ATTN_EXACT_CTX * 4) + attn_round(ATTN_EXACT_CTX * 128) + 128 + attn_round(3 * 128 * 4) + attn_round(3 * 128) + 128 +
+           attn_round(128 * 4) + 128 + 128;
+}
+__device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
+    AttnSmem s;
+    size_t off = 0;
+    s.sc = reinterpret_cast<float *>(base + off); off += attn_round(ATTN_EXACT_CTX * 4);
+    s.vbuf = reinterpret_cast<int8_t *>(base + off); off += attn_round(ATTN_EXACT_CTX * 128);
+    s.bar = reinterpret_cast<uint64_t *>(base + off); off += 128;
+    s.head = reinterpret_cast<float *>(base + off); off += attn_round(3 * 128 * 4);
+    s.hq = reinterpret_cast<int8_t *>(base + off); off += attn_round(3 * 128);
+    s.hs = reinterpret_cast<float *>(base + off); off += 128;
+    s.o = reinterpret_cast<float *>(base + off); off += attn_round(128 * 4);
+    s.red = reinterpret_cast<float *>(base + off); off += 128;
+    s.inv = reinterpret_cast<float *>(base + off); off += 128;
+    return s;
+}
+
+template <int HD>
+__device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
+    constexpr int QW = HD / 4, NB = HD / 64;
+    constexpr uint32_t MEGA_THREADS = ATTN_THREADS, MEGA_WARPS = ATTN_THREADS / 32;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t group = A.n_q / A.n_kv, kvh = qh / group, ctx = pos + 1, layer = A.layer;
+    const FusedAttnArgs *L = &A;
+    const size_t slot0 = ((size_t)layer * A.n_kv + kvh) * A.max_seq;
+    const int8_t *K = A.k_q8 + slot0 * HD, *V = A.v_q8 + slot0 * HD;
+    const float *ks = A.k_scale + slot0, *vs = A.v_scale + slot0;
+    // ---- everything that does not depend on the current token is requested first, so that its L2 latency
+    // overlaps the head preparation.  First of all (its fences would otherwise wait for the loads below) the
+    // cached value rows [0, pos): they are contiguous, so one bulk copy into shared memory, completion on an
+    // mbarrier; then this lane's head inputs, and the key rows and scales of this thread's (at most two)
+    // cached positions.
+    const uint32_t vbar = (uint32_t)__cvta_generic_to_shared(s.bar);
+    if (tid == 0 && pos > 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vbar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");       // barrier init, and the cache rows other CTAs / kernels stored
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vbar), "r"(pos * HD) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(s.vbuf)), "l"(V), "r"(pos * HD), "r"(vbar) : "memory");
+    }
+    constexpr int HV = HD / 32;                            // head elements per lane (warps 0..2)
+    const uint32_t my_head = warp == 0 ? qh : warp == 1 ? A.n_q + kvh : A.n_q + A.n_kv + kvh;
+    float hv[HV], rc[HV], rs[HV];                          // head values (+bias), rope cos / sin of the lane's pair
+    if (warp < 3) {
+#pragma unroll
+        for (int k = 0; k < HV; ++k) {
+            const uint32_t i = lane + 32 * k;
+            hv[k] = __ldcg(A.qkv + (size_t)my_head * HD + i);
+            if (A.bias != nullptr) hv[k] = __fadd_rn(hv[k], __ldg(A.bias + (size_t)my_head * HD + i));
+            rc[k] = __ldg(A.rope + (size_t)pos * HD + (i % (HD / 2)));
+            rs[k] = __ldg(A.rope + (size_t)pos * HD + HD / 2 + (i % (HD / 2)));
+        }
+    }
+    constexpr int PT = ATTN_EXACT_CTX / ATTN_THREADS;     // positions per thread
+    int4 kreg[PT][QW / 4];
+    float ksr[PT], vsr[PT];
+#pragma unroll
+    for (int k = 0; k < PT; ++k) {
+        const uint32_t t = tid + k * MEGA_THREADS;
+        const bool cached = t < pos;
+#pragma unroll
+        for (int i = 0; i < QW / 4; ++i)
+            kreg[k][i] = cached ? __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i) : make_int4(0, 0, 0, 0);
+        ksr[k] = cached ? __ldcg(ks + t) : 0.0f;
+        vsr[k] = cached ? __ldcg(vs + t) : 0.0f;
+    }
+    // ---- the three heads of this CTA: warp 0 = query qh, warp 1 = key kvh, warp 2 = value kvh
+    if (warp < 3) {
+        float *sh = s.head + warp * 128;
+#pragma unroll
+        for (int k = 0; k < HV; ++k) sh[lane + 32 * k] = hv[k];
+        __syncwarp();
+        const float *norm_w = warp == 0 ? L->q_norm : (warp == 1 ? L->k_norm : nullptr);
+        auto do_rope = [&]() {       // element i pairs with i +- hd/2: x0' = x0 c - x1 s, x1' = x1 c + x0 s
+            float nv[HV];
+#pragma unroll
+            for (int k = 0; k < HV; ++k) {
+                const uint32_t i = lane + 32 * k;
+                const float me = sh[i], other = sh[i < HD / 2 ? i + HD / 2 : i - HD / 2];
+                nv[k] = i < HD / 2 ? __fsub_rn(__fmul_rn(me, rc[k]), __fmul_rn(other, rs[k]))
+                                   : __fadd_rn(__fmul_rn(me, rc[k]), __fmul_rn(other, rs[k]));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < HV; ++k) sh[lane + 32 * k] = nv[k];
+            __syncwarp();
+        };
+        auto do_norm = [&]() {
+            float ss = 0.0f;
+            if (lane < 16)
+                for (uint32_t i = lane; i < HD; i += 16) ss = __fmaf_rn(sh[i], sh[i], ss);
+            ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 4));
+            ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 8));
+            ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 1));
+            ss = __fadd_rn(ss, __shfl_down_sync(0xffffffffu, ss, 2));
+            ss = __shfl_sync(0xffffffffu, ss, 0);
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, __fdiv_rn(1.0f, (float)HD)), A.eps)));
+            for (uint32_t i = lane; i < HD; i += 32) sh[i] = __fmul_rn(__fmul_rn(sh[i], inv), __ldg(norm_w + i));
+            __syncwarp();
+        };
+        if (warp < 2) {
+            if (A.qk_norm_after_rope) do_rope();
+            if (norm_w != nullptr) do_norm();
+            if (!A.qk_norm_after_rope) do_rope();
+        }
+        float v0[NB], v1[NB], mx = 0.0f;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            v0[b] = sh[b * 64 + 2 * lane];
+            v1[b] = sh[b * 64 + 2 * lane + 1];
+            warp_fwht64(v0[b], v1[b], b, lane);
+            mx = fmaxf(mx, fmaxf(fabsf(v0[b]), fabsf(v1[b])));
+        }
+        mx = warp_max(mx);
+        const bool zero = mx <= 1.1920929e-07f;
+        const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx), scale = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
+        const bool store = warp > 0 && qh % group == 0;     // one CTA of the group writes the cache entry
+        int8_t *cache = (warp == 1 ? A.k_q8 : A.v_q8) + (slot0 + pos) * HD;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
+            const char2 pk = make_char2((signed char)q0, (signed char)q1);
+            reinterpret_cast<char2 *>(s.hq + warp * 128 + b * 64)[lane] = pk;
+            if (store) reinterpret_cast<char2 *>(cache + b * 64)[lane] = pk;
+        }
+        if (lane == 0) {
+            s.hs[warp] = scale;
+            if (store) (warp == 1 ? A.k_scale : A.v_scale)[slot0 + pos] = scale;
+        }
+    }
+    __syncthreads();
+    // ---- scores (positions < pos from the prefetched cache rows, position pos from shared memory)
+    const float qas = __fmul_rn(s.hs[0], A.attn_scale);
+    int qw[QW];
+#pragma unroll
+    for (int i = 0; i < QW; ++i) qw[i] = reinterpret_cast<const int *>(s.hq)[i];
+    float mx = -INFINITY, scr[PT];
+#pragma unroll
+    for (int k = 0; k < PT; ++k) {
+        const uint32_t t = tid + k * MEGA_THREADS;
+        scr[k] = -INFINITY;
+        if (t < ctx) {
+            int dot = 0;
+#pragma unroll
+            for (int i = 0; i < QW / 4; ++i) {
+                const int4 v = t < pos ? kreg[k][i] : reinterpret_cast<const int4 *>(s.hq + 128)[i];
+                dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
+                dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
+            }
+            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+            const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
+            const float kst = t < pos ? ksr[k] : s.hs[1];
+            scr[k] = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
+                                                   : __fmul_rn(__fmul_rn((float)dot, kst), qas);
+            mx = fmaxf(mx, scr[k]);
+        }
+    }
+    mx = warp_max(mx);
+    if (lane == 0) s.red[warp] = mx;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < (int)MEGA_WARPS; ++i) mx = fmaxf(mx, s.red[i]);
+    // softmax_unnorm (9603-9632): polynomial exp for whole groups of 4 positions, libm exp for the rest
+    // (correctly rounded: double exp rounded to float; those run while warp 0 sums the body)
+    const uint32_t n4 = ctx & ~3u;
+#pragma unroll
+    for (int k = 0; k < PT; ++k) {
+        const uint32_t t = tid + k * MEGA_THREADS;
+        if (t < n4) s.sc[t] = exp_poly(__fsub_rn(scr[k], mx));
+    }
+    __syncthreads();
+    float acc = 0.0f;
+    if (warp == 0) {
+        if (lane < 4) {
+            uint32_t t = lane;
+            for (; t + 28 < n4; t += 32) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = s.sc[t + 4 * j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, v[j]);
+            }
+            for (; t < n4; t += 4) acc = __fadd_rn(acc, s.sc[t]);
+        }
+        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0+a1, lane 2: a2+a3
+        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
+    }
+#pragma unroll
+    for (int k = 0; k < PT; ++k) {
+        const uint32_t t = tid + k * MEGA_THREADS;
+        if (t >= n4 && t < ctx) s.sc[t] = (float)exp((double)__fsub_rn(scr[k], mx));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (uint32_t t = n4; t < ctx; ++t) acc = __fadd_rn(acc, s.sc[t]);
+        *s.inv = __fdiv_rn(1.0f, acc);
+    }
+    __syncthreads();
+    const float inv = *s.inv;
+#pragma unroll
+    for (int k = 0; k < PT; ++k) {
+        const uint32_t t = tid + k * MEGA_THREADS;
+        if (t < ctx) s.sc[t] = __fmul_rn(__fmul_rn(s.sc[t], inv), t < pos ? vsr[k] : s.hs[2]);
+    }
+    // ---- values: thread i < HD = dimension i runs the position-ascending chain over the staged rows
+    __syncthreads();                       // weights complete
+    float o = 0.0f;
+    bool copy_failed = false;
+    if (pos > 0) {                         // bounded wait for the bulk copy
+        uint32_t ok = 0;
+        for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(vbar) : "memory");
+        copy_failed = !ok;
+    }
+    if (tid < HD && !copy_failed) {
+        // a zero weight skips the position (as the CPU loop does): select, not branch.  Eight positions are
+        // loaded before their fma chain starts, so the chain runs at fma latency, not shared-memory latency.
+        // int8 -> fp32 without the conversion unit (a quarter-rate pipe that would bound this loop): for a byte b,
+        // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
+        const float *wp = s.sc;
+        const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + tid;
+        auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
+        uint32_t j = 0;
+        for (; j + 8 <= pos; j += 8) {
+            float w[8];
+            uint32_t v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; v[u] = vp[(j + u) * HD]; }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(to_f32(v[u]), w[u], o); o = w[u] != 0.0f ? nv : o; }
+        }
+        for (; j < pos; ++j) {
+            const float w = wp[j];
+            const float nv = __fmaf_rn(to_f32(vp[j * HD]), w, o);
+            o = w != 0.0f ? nv : o;
+        }
+        const float w = wp[pos];           // the current position: its value row is still in shared memory
+        const float nv = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), w, o);
+        o = w != 0.0f ? nv : o;
+    }
+    if (__syncthreads_or(copy_failed) && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
+    if (tid == 0 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
+    if (tid < HD) s.o[tid] = o;
+    __syncthreads();
+    if (warp < NB) {
+        const uint32_t b = warp;
+        float x0 = s.o[b * 64 + 2 * lane], x1 = s.o[b * 64 + 2 * lane + 1];
+        warp_ifwht64(x0, x1, b, lane);
+        if (A.attn_tap != nullptr) reinterpret_cast<float2 *>(A.attn_tap + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
+        const uint32_t c = qh * NB + b;
+        warp_fwht64(x0, x1, c, lane);
+        int q0, q1, sum;
+        float sc;
+        warp_quant64(x0, x1, q0, q1, sc, sum);
+        reinterpret_cast<char2 *>(A.out_q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+        if (lane == 0) { A.out_scales[c] = sc; A.out_sums[c] = sum; }
+    }
+}
+
+
+}  // namespace k2t

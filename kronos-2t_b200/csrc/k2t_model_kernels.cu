@@ -3,83 +3,16 @@
 // RoPE / KV store / query quantization, split-KV decode attention over the int8 Hadamard cache,
 // SwiGLU + rotation + quantization, argmax.  Everything position dependent reads the position from
 // device memory so that one captured CUDA graph serves every decode step.
-#include "k2t_fwht.cuh"
-#include "k2t_model_kernels.h"
+#include "k2t_model_device.cuh"
 
 namespace k2t {
 
-// exp_f32_neon (src/model/real_llm.rs:9430-9454), one lane, same operations in the same order.
-__device__ __forceinline__ float exp_poly(float x_raw) {
-    const float x = fminf(fmaxf(x_raw, -87.33654f), 88.0f);
-    const float kf = rintf(__fmul_rn(x, 1.44269504088896340736f));
-    const float r = __fmaf_rn(-kf, 1.4286068e-6f, __fmaf_rn(-kf, 0.69314575f, x));
-    float y = __fmaf_rn(1.9875691e-4f, r, 1.3982e-3f);
-    y = __fmaf_rn(y, r, 8.333452e-3f);
-    y = __fmaf_rn(y, r, 4.1665796e-2f);
-    y = __fmaf_rn(y, r, 1.6666666e-1f);
-    y = __fmaf_rn(y, r, 0.5f);
-    y = __fmaf_rn(y, r, 1.0f);
-    y = __fmaf_rn(y, r, 1.0f);
-    const int ki = (int)kf;
-    return __fmul_rn(y, __int_as_float((ki + 127) << 23));
-}
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
-    return v;
-}
-
-// ------------------------------------------------------------------------------------------------
-// embedding (embed_token_into, real_llm.rs:8063-8097)
-// ------------------------------------------------------------------------------------------------
-// weight value (rotated domain) of element `col` (0..63) of cell (row, c)
-__device__ float cell_value(const EmbedArgs &a, uint32_t row, uint32_t c, uint32_t col) {
-    const size_t cell = c;
-    const uint8_t *p0 = a.plane[0] + (size_t)row * a.pitch[0] + cell * a.cell[0];
-    const uint8_t *p1 = a.plane[1] + (size_t)row * a.pitch[1] + cell * a.cell[1];
-    const uint8_t *p2 = a.plane[2] + (size_t)row * a.pitch[2] + cell * a.cell[2];
-    const uint32_t sg = a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
-    const float delta = bf16_bits_to_f32(a.scales[(size_t)row * a.nsg_pad + sg]);
-    if (a.fmt == FMT_BP4 || a.fmt == FMT_BP5 || a.fmt == FMT_BP6) {
-        const uint8_t *half = col < 32 ? p0 : p1;
-        const uint32_t cc = col % 32, k = col % 8;
-        uint32_t u = (half[(cc / 8) * 4 + (k % 4)] >> (k < 4 ? 0 : 4)) & 0x0F;
-        if (a.fmt == FMT_BP5) {
-            const uint32_t bit = 8 * (col % 4) + cc / 4;
-            u |= ((p2[(col / 32) * 4 + bit / 8] >> (bit % 8)) & 1u) << 4;
-        } else if (a.fmt == FMT_BP6) {
-            const uint32_t bit = 8 * (col % 4) + 2 * ((col % 16) / 4);
-            u |= ((p2[(col / 16) * 4 + bit / 8] >> (bit % 8)) & 3u) << 4;
-        }
-        return __fmul_rn((float)(2 * (int)u - a.max_odd), delta);
-    }
-    uint32_t idx;
-    if (a.fmt == FMT_NF3) {
-        auto word = [&](uint32_t w) { return w < 4 ? reinterpret_cast<const uint32_t *>(p0)[w] : reinterpret_cast<const uint32_t *>(p1)[w - 4]; };
-        if (col < 48) idx = (word(col / 8) >> (4 * (col % 8))) & 7u;
-        else {
-            const uint32_t t = col - 48;
-            idx = 0;
-            for (uint32_t j = 0; j < 3; ++j) idx |= ((word(3 * (t / 8) + j) >> (4 * (t % 8) + 3)) & 1u) << j;
-        }
-    } else {
-        const uint8_t *half = col < 32 ? p0 : p1;
-        const uint32_t cc = col % 32, nib = col % 8;
-        idx = (half[(cc / 8) * 4 + nib / 2] >> (4 * (nib % 2))) & 0x0F;
-    }
-    return __fmul_rn((float)a.codebook[idx], delta);
-}
-
 __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     if (c >= a.nc) return;
-    const uint32_t tok = *a.token;
+    const uint32_t tok = __ldcg(a.token);
     float v0, v1;
     if (a.embed_bf16 != nullptr) {
         const uint16_t *row = a.embed_bf16 + (size_t)tok * a.nc * 64 + (size_t)c * 64;
@@ -107,10 +40,12 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     extern __shared__ float s_x[];           // n floats
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
+    pdl_trigger();
+    pdl_wait();
     for (uint32_t i = tid; i < n / 4; i += 256) {
-        float4 v = reinterpret_cast<const float4 *>(hidden)[i];
+        float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
-            const float4 d = reinterpret_cast<const float4 *>(delta)[i];
+            const float4 d = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
             v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
             reinterpret_cast<float4 *>(hidden)[i] = v;
         }
@@ -155,13 +90,15 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     __shared__ float s_head[4][128];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t head = blockIdx.x * 4 + warp, hd = a.head_dim, half = hd / 2;
+    pdl_trigger();
+    pdl_wait();
     if (head >= a.n_q + 2 * a.n_kv) return;
-    const uint32_t pos = *a.pos;
+    const uint32_t pos = __ldcg(a.pos);
     const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
     float *sh = s_head[warp];
     const float *src = a.qkv + (size_t)head * hd;
     for (uint32_t i = lane; i < hd; i += 32) {
-        float v = src[i];
+        float v = __ldcg(src + i);
         if (a.bias != nullptr) v = __fadd_rn(v, a.bias[(size_t)head * hd + i]);
         sh[i] = v;
     }
@@ -231,10 +168,6 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
 // Used for contexts longer than ATTN_EXACT_CTX positions.  Scores (and so the maximum) are the CPU's bit
 // for bit.  Softmax is the online form; partial (max, sum, out) per split are merged by attn_finish_kernel.  Sums run in a different order than the CPU's
 // position-ascending chains: the output agrees to fp32 rounding, not bit for bit.
-// positions per split: the context divided over the splits, in whole 32-position tiles
-__device__ __forceinline__ uint32_t split_span(uint32_t ctx, uint32_t n_split) {
-    return (((ctx + n_split - 1) / n_split) + 31u) & ~31u;
-}
 
 template <int HD>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
@@ -244,8 +177,10 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     __shared__ float s_p[4][8][32];       // probabilities of the current 32 positions
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t split = blockIdx.x * 4 + warp, kvh = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();
     if (split >= a.n_split) return;
-    const uint32_t ctx = *a.pos + 1, G = a.group;
+    const uint32_t ctx = __ldcg(a.pos) + 1, G = a.group;
     if (ctx <= ATTN_EXACT_CTX) return;     // short contexts are computed in the CPU's order by attn_finish_kernel
     const uint32_t per = split_span(ctx, a.n_split);
     const uint32_t t_lo = min(ctx, split * per), t_hi = min(ctx, t_lo + per);
@@ -253,13 +188,13 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
     const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
     for (uint32_t i = lane; i < G * QW; i += 32)
-        s_q[warp][i / QW][i % QW] = reinterpret_cast<const int *>(a.q_i8 + (size_t)(kvh * G) * HD)[i];
+        s_q[warp][i / QW][i % QW] = __ldcg(reinterpret_cast<const int *>(a.q_i8 + (size_t)(kvh * G) * HD) + i);
     __syncwarp();
     float qas[8], m[8], l[8], o[8][HD / 16];   // lane owns dims d0..d0+3 of (HD/16 ... ) see below
     // value phase mapping: 16 lanes x 4 dims cover 64 dims; for HD = 128 each lane owns two such groups
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
-        qas[g] = g < (int)G ? __fmul_rn(a.q_scale[kvh * G + g], a.attn_scale) : 0.0f;
+        qas[g] = g < (int)G ? __fmul_rn(__ldcg(a.q_scale + kvh * G + g), a.attn_scale) : 0.0f;
         m[g] = -INFINITY; l[g] = 0.0f;
 #pragma unroll
         for (int d = 0; d < HD / 16; ++d) o[g][d] = 0.0f;
@@ -273,14 +208,14 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         if (on) {
 #pragma unroll
             for (int i = 0; i < QW / 4; ++i) {
-                const int4 v = __ldg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
+                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
                 kw[4 * i] = v.x; kw[4 * i + 1] = v.y; kw[4 * i + 2] = v.z; kw[4 * i + 3] = v.w;
             }
         }
         const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
         const bool grouped = t - tile0 < (tile_n & ~7u);
-        const float kst = on ? __ldg(ks + t) : 0.0f;
-        const float vst = on ? __ldg(vs + t) : 0.0f;
+        const float kst = on ? __ldcg(ks + t) : 0.0f;
+        const float vst = on ? __ldcg(vs + t) : 0.0f;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             if (g >= (int)G) break;
@@ -308,7 +243,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         for (uint32_t j = hw; j < n_here; j += 2) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-                const char4 v = *reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * HD + b * 64 + dl * 4);
+                const char4 v = __ldcg(reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * HD + b * 64 + dl * 4));
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     if (g >= (int)G) break;
@@ -355,17 +290,19 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
     __shared__ float s_red[HD / 32];
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = *a.pos + 1;
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + 1;
     float o = 0.0f;
     if (ctx <= ATTN_EXACT_CTX) {
         const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
         const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
         const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
-        const float qas = __fmul_rn(a.q_scale[qh], a.attn_scale);
+        const float qas = __fmul_rn(__ldcg(a.q_scale + qh), a.attn_scale);
         int qw[QW];
 #pragma unroll
         for (int i = 0; i < QW / 4; ++i) {
-            const int4 v = reinterpret_cast<const int4 *>(a.q_i8 + (size_t)qh * HD)[i];
+            const int4 v = __ldcg(reinterpret_cast<const int4 *>(a.q_i8 + (size_t)qh * HD) + i);
             qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
         }
         float mx = -INFINITY;
@@ -373,13 +310,13 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
             int dot = 0;
 #pragma unroll
             for (int i = 0; i < QW / 4; ++i) {
-                const int4 v = __ldg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
+                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
                 dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
                 dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
             }
             // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
             const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
-            const float kst = __ldg(ks + t);
+            const float kst = __ldcg(ks + t);
             const float sc = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
                                                            : __fmul_rn(__fmul_rn((float)dot, kst), qas);
             s_sc[t] = sc;
@@ -410,7 +347,7 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
         }
         __syncthreads();
         const float inv = s_inv;
-        for (uint32_t t = tid; t < ctx; t += HD) s_sc[t] = __fmul_rn(__fmul_rn(s_sc[t], inv), __ldg(vs + t));
+        for (uint32_t t = tid; t < ctx; t += HD) s_sc[t] = __fmul_rn(__fmul_rn(s_sc[t], inv), __ldcg(vs + t));
         // values: tiles of VT positions staged in shared memory (next tile prefetched into registers)
         constexpr int LD = VT / 16;            // int4 loads per thread and tile: VT*HD/16 over HD threads
         int4 nxt[LD];
@@ -419,7 +356,7 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
             for (int j = 0; j < LD; ++j) {
                 const uint32_t e = (uint32_t)j * HD + tid;             // int4 index within the tile
                 const uint32_t t = t0 + e / (HD / 16);
-                nxt[j] = t < ctx ? __ldg(reinterpret_cast<const int4 *>(V + (size_t)t0 * HD) + e) : make_int4(0, 0, 0, 0);
+                nxt[j] = t < ctx ? __ldcg(reinterpret_cast<const int4 *>(V + (size_t)t0 * HD) + e) : make_int4(0, 0, 0, 0);
             }
         };
         fetch(0);
@@ -441,11 +378,11 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
         const uint32_t used = (ctx + per - 1) / per;           // splits that hold positions
         const float *pm = a.part_m + (size_t)qh * a.n_split, *pl = a.part_l + (size_t)qh * a.n_split;
         float M = -INFINITY, L = 0.0f;
-        for (uint32_t s = 0; s < used; ++s) M = fmaxf(M, pm[s]);
+        for (uint32_t s = 0; s < used; ++s) M = fmaxf(M, __ldcg(pm + s));
         for (uint32_t s = 0; s < used; ++s) {
-            const float wgt = exp_poly(pm[s] - M);
-            L = __fmaf_rn(pl[s], wgt, L);
-            o = __fmaf_rn(a.part_o[((size_t)qh * a.n_split + s) * HD + tid], wgt, o);
+            const float wgt = exp_poly(__ldcg(pm + s) - M);
+            L = __fmaf_rn(__ldcg(pl + s), wgt, L);
+            o = __fmaf_rn(__ldcg(a.part_o + ((size_t)qh * a.n_split + s) * HD + tid), wgt, o);
         }
         o = __fmul_rn(o, __fdiv_rn(1.0f, L));
     }
@@ -466,6 +403,19 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
     }
 }
 
+// Contexts of up to ATTN_EXACT_CTX positions: bias / qk-norm / RoPE / KV store / attention / o_proj activation
+// in one kernel, CTA q = query head q (attention_head_cta).  Longer contexts: returns at once, the split-KV
+// kernels serve them.
+template <int HD>
+__global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t pos = __ldcg(a.pos);
+    if (pos + 1 > ATTN_EXACT_CTX) return;
+    attention_head_cta<HD>(a, blockIdx.x, pos, attn_carve(smem));
+}
+
 // ------------------------------------------------------------------------------------------------
 // SwiGLU + FWHT-64 + int8  (swiglu_activate_neon 9811-9842, then the down_proj activation)
 // ------------------------------------------------------------------------------------------------
@@ -473,9 +423,11 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
                                                            int8_t *__restrict__ q, float *__restrict__ scales,
                                                            int32_t *__restrict__ sums, float *__restrict__ dbg) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    pdl_trigger();
+    pdl_wait();
     if (c >= inter / 64) return;
-    const float2 g = reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64)[lane];
-    const float2 u = reinterpret_cast<const float2 *>(gate_up + inter + (size_t)c * 64)[lane];
+    const float2 g = __ldcg(reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64) + lane);
+    const float2 u = __ldcg(reinterpret_cast<const float2 *>(gate_up + inter + (size_t)c * 64) + lane);
     float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_poly(-g.x))), u.x);
     float x1 = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, exp_poly(-g.y))), u.y);
     if (dbg != nullptr) reinterpret_cast<float2 *>(dbg + (size_t)c * 64)[lane] = make_float2(x0, x1);
@@ -497,8 +449,10 @@ __global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restri
     __shared__ uint32_t s_i[32];
     float bv = -INFINITY;
     uint32_t bi = 0xffffffffu;
+    pdl_trigger();
+    pdl_wait();
     for (uint32_t i = threadIdx.x; i < n; i += 1024) {
-        const float v = logits[i];
+        const float v = __ldcg(logits + i);
         if (v > bv) { bv = v; bi = i; }         // ascending i per thread: keeps the first maximum
     }
     auto better = [](float v, uint32_t i, float bv2, uint32_t bi2) { return v > bv2 || (v == bv2 && i < bi2); };
@@ -521,62 +475,68 @@ __global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restri
         if (threadIdx.x == 0) {
             if (bi == 0xffffffffu) bi = 0;      // all NaN / -inf: the scalar loop also returns 0
             *token = bi;
-            if (history != nullptr) history[*step] = bi;
-            *step += 1;
-            *pos += 1;
+            const uint32_t st = __ldcg(step);
+            if (history != nullptr) history[st] = bi;
+            *step = st + 1;
+            *pos = __ldcg(pos) + 1;
         }
     }
 }
 
-__global__ void advance_pos_kernel(uint32_t *pos) { *pos += 1; }
+__global__ void advance_pos_kernel(uint32_t *pos) {
+    pdl_wait();
+    *pos = __ldcg(pos) + 1;
+}
 
 // ------------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------------
-cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a) {
-    embed_kernel<<<(a.nc + 7) / 8, 256, 0, s>>>(a);
-    return cudaGetLastError();
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, bool pdl) {
+    return launch_kernel(embed_kernel, dim3((a.nc + 7) / 8), dim3(256), 0, s, pdl, a);
 }
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
-                                 int8_t *q, float *scales, int32_t *sums) {
+                                 int8_t *q, float *scales, int32_t *sums, bool pdl) {
     const size_t smem = (size_t)n * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    rmsnorm_quant_kernel<<<1, 256, smem, s>>>(hidden, delta, w, n, eps, q, scales, sums);
-    return cudaGetLastError();
+    return launch_kernel(rmsnorm_quant_kernel, dim3(1), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums);
 }
-cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a) {
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;
-    qkv_post_kernel<<<(heads + 3) / 4, 128, 0, s>>>(a);
-    return cudaGetLastError();
+    return launch_kernel(qkv_post_kernel, dim3((heads + 3) / 4), dim3(128), 0, s, pdl, a);
 }
-cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a) {
+cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
     dim3 grid((a.n_split + 3) / 4, a.n_kv);
-    if (a.head_dim == 64) attn_partial_kernel<64><<<grid, 128, 0, s>>>(a);
-    else if (a.head_dim == 128) attn_partial_kernel<128><<<grid, 128, 0, s>>>(a);
+    cudaError_t e;
+    if (a.head_dim == 64) e = launch_kernel(attn_partial_kernel<64>, grid, dim3(128), 0, s, pdl, a);
+    else if (a.head_dim == 128) e = launch_kernel(attn_partial_kernel<128>, grid, dim3(128), 0, s, pdl, a);
     else return cudaErrorInvalidValue;
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    if (a.head_dim == 64) attn_finish_kernel<64><<<a.n_kv * a.group, 64, 0, s>>>(a);
-    else attn_finish_kernel<128><<<a.n_kv * a.group, 128, 0, s>>>(a);
-    return cudaGetLastError();
+    if (a.head_dim == 64) return launch_kernel(attn_finish_kernel<64>, dim3(a.n_kv * a.group), dim3(64), 0, s, pdl, a);
+    return launch_kernel(attn_finish_kernel<128>, dim3(a.n_kv * a.group), dim3(128), 0, s, pdl, a);
+}
+cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl) {
+    const size_t smem = attn_smem_bytes();
+    cudaError_t e = cudaFuncSetAttribute(a.head_dim == 64 ? (const void *)attn_fused_kernel<64> : (const void *)attn_fused_kernel<128>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    if (a.head_dim == 64) return launch_kernel(attn_fused_kernel<64>, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
+    if (a.head_dim == 128) return launch_kernel(attn_fused_kernel<128>, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
+    return cudaErrorInvalidValue;
 }
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg) {
-    swiglu_quant_kernel<<<(inter / 64 + 7) / 8, 256, 0, s>>>(gate_up, inter, q, scales, sums, dbg);
-    return cudaGetLastError();
+                                float *dbg, bool pdl) {
+    return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg);
 }
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
-                               uint32_t *history, uint32_t *step) {
-    argmax_step_kernel<<<1, 1024, 0, s>>>(logits, n, token, pos, history, step);
-    return cudaGetLastError();
+                               uint32_t *history, uint32_t *step, bool pdl) {
+    return launch_kernel(argmax_step_kernel, dim3(1), dim3(1024), 0, s, pdl, logits, n, token, pos, history, step);
 }
-cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos) {
-    advance_pos_kernel<<<1, 1, 0, s>>>(pos);
-    return cudaGetLastError();
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, bool pdl) {
+    return launch_kernel(advance_pos_kernel, dim3(1), dim3(1), 0, s, pdl, pos);
 }
 
 }  // namespace k2t

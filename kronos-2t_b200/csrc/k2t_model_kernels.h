@@ -46,15 +46,32 @@ struct AttnArgs {
     float attn_scale;
 };
 
-cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a);
+struct FusedAttnArgs {           // one layer's attention from the fused qkv vector to the o_proj activation
+    const float *qkv;            // [n_q + 2 n_kv][head_dim]
+    const float *bias, *q_norm, *k_norm;     // null when absent
+    const float *rope;           // [max_seq][head_dim]
+    const uint32_t *pos;         // device (stand-alone kernel; the whole-token kernel passes the position itself)
+    int8_t *k_q8, *v_q8; float *k_scale, *v_scale;
+    float *attn_tap;             // optional fp32 attention output [n_q][head_dim]
+    int8_t *out_q; float *out_scales; int32_t *out_sums;
+    uint32_t *err_flag;          // set when the bounded wait for the value rows gives up
+    uint32_t n_q, n_kv, head_dim, max_seq, layer;
+    float eps, attn_scale;
+    int32_t qk_norm_after_rope;
+};
+
+// pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, bool pdl);
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
-                                 int8_t *q, float *scales, int32_t *sums);
-cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a);
-cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a);     // two kernels
+                                 int8_t *q, float *scales, int32_t *sums, bool pdl);
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl);
+cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl);     // two kernels
+// contexts of up to ATTN_EXACT_CTX positions: qkv_post + attention in one kernel (leaves longer contexts untouched)
+cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl);
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg);
+                                float *dbg, bool pdl);
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
-                               uint32_t *history, uint32_t *step);
-cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos);
+                               uint32_t *history, uint32_t *step, bool pdl);
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, bool pdl);
 
 }  // namespace k2t

@@ -87,6 +87,7 @@ def load_library():
     sig("kronos_cuda_engine_weight_bytes", sz, vp)
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
+    sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
     sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     _LIB = L
     return L
@@ -336,6 +337,12 @@ class Engine:
         out = np.empty(self.cfg.num_attention_heads * self.cfg.head_dim, np.float32)
         self.ctx._check(self.L.kronos_cuda_engine_read_attention(self.handle, _p(out)))
         return out
+
+    def decode_trace(self):
+        """Global-timer marks (ns) of the last step of the last whole-token-kernel decode call."""
+        buf = np.zeros(4096, np.uint64)
+        n = self.L.kronos_cuda_engine_decode_trace(self.handle, _p(buf), buf.size)
+        return buf[:n].copy()
 
     def read_kv(self, layer, kv_head, position):
         """(k_q8, k_scale, v_q8, v_scale) of one cache slot."""
