@@ -334,9 +334,15 @@ def run_b200(args, rank, world, local_rank):
                 "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak},
                 "per_launch": kernels}
 
+    decode = None
+    if not args.no_decode:
+        decode = decode_tok_s(ctx, stream, timed_region=lambda fn: timed(fn, 1)[0], world=world)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(mats)
+        if decode is not None:
+            decode["cpu_baseline"] = cpu_decode_baseline()
 
     if rank == 0:
         print(json.dumps({
@@ -349,7 +355,7 @@ def run_b200(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(gpu_launches),
-            "roofline": roofline, "cpu_baseline": cpu,
+            "roofline": roofline, "cpu_baseline": cpu, "decode": decode,
         }))
     for c in cases:
         c["dm"].free()
@@ -436,6 +442,56 @@ def run_case(args, local_rank):
     ctx.close()
 
 
+DECODE_WORKLOAD = ("SmolLM2-135M-shaped Llama (hidden 576, 30 layers, 9q/3kv heads of 64, MLP 1536, vocab 49152, tied), b4 "
+                   "bit-planes with random codes, int8 Hadamard KV, 128-token prompt then 128 greedy steps, batch 1")
+
+
+def decode_tok_s(ctx, stream, timed_region, world):
+    """Whole-token decode through kronos_cuda_engine_*: prompt token by token, then the device-side greedy loop."""
+    import numpy as np
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+    spec = synth.random_model(synth.SMOLLM2_135M, "b4", seed=3)
+    eng = k2.Engine(ctx, spec)
+    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, spec["cfg"]["vocab"], 128).astype(np.uint32)
+    l0 = ctx.launch_count
+    eng.forward_token_ids(prompt[:-1])
+    eng.decode_greedy(int(prompt[-1]), 127, 128)                      # warm-up (graph capture, caches)
+    l1 = ctx.launch_count
+    ms_prompt = timed_region(lambda: eng.forward_token_ids(prompt[:-1]))
+    ms_decode = min(timed_region(lambda: eng.decode_greedy(int(prompt[-1]), 127, 128)) for _ in range(3))
+    out = {"workload": DECODE_WORKLOAD, "tok_s": 128 * world / (ms_decode / 1e3), "ms_per_token": ms_decode / 128,
+           "prompt_tok_s": 127 * world / (ms_prompt / 1e3), "weight_bytes_per_token": eng.weight_bytes,
+           "weight_gbs": eng.weight_bytes * 128 * world / (ms_decode / 1e3) / 1e9, "kv_bytes_at_256": eng.kv_bytes(256),
+           "form": "one CUDA graph replay per token (8 kernels per layer + 4), argmax on the device",
+           "note": "each rank decodes its own replica; tok_s is the aggregate"}
+    eng.close()
+    return out
+
+
+def cpu_decode_baseline():
+    """The oracle's dense decode step on the same model shape, all host threads: 16 prompt tokens, 16 greedy steps."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import oracle as o
+    from kronos_2t_b200 import synth
+    spec = synth.random_model(synth.SMOLLM2_135M, "b4", seed=3)
+    threads = os.cpu_count() or 1
+    m = o.Model(spec)
+    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, spec["cfg"]["vocab"], 16)
+    logits = None
+    for t in prompt:
+        logits = m.forward_token(int(t), threads)
+    t0 = time.perf_counter()
+    n = 0
+    while n < 16 or (time.perf_counter() - t0 < 5.0 and n < 256):
+        logits = m.forward_token(o.argmax(logits), threads)
+        n += 1
+    dt = time.perf_counter() - t0
+    m.close()
+    return {"value": n / dt, "unit": "tok/s", "cores": threads, "kind": "port", "sample": f"{n} greedy steps after a 16-token prompt"}
+
+
 def cpu_baseline(mats):
     """Oracle (C++ port of the reference CPU path) on one pass of the same sweep, all host threads."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -472,6 +528,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode measurement")
     ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")
     ap.add_argument("--tokens", type=int, default=1, help="tokens per launch in --case mode (1..4)")
     ap.add_argument("--no-graph", action="store_true", help="--case mode: skip the CUDA-graph replay timing")

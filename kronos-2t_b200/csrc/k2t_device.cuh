@@ -38,8 +38,9 @@ __device__ __forceinline__ uint32_t lop3_select(uint32_t lo, uint32_t hi, uint32
 // start while its predecessor in the stream still runs.  pdl_wait() returns once the predecessor grid has
 // completed and its writes are visible; everything a kernel reads that another kernel wrote, and every
 // global write, comes after it (weights are immutable and may be fetched before).  pdl_trigger() lets the
-// successor start launching.  Both are no-ops for a kernel launched the ordinary way.  Data produced
-// by other kernels is read with ld.global.cg (L2) so that no SM-local cache line from before the wait is used.
+// successor start launching; kernels call it AFTER their own pdl_wait(), so that at most two consecutive
+// kernels are ever resident together (a kernel two steps back can then no longer refill an SM's L1 with
+// lines its successor is about to overwrite).  Both are no-ops for a kernel launched the ordinary way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

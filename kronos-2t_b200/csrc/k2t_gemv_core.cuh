@@ -214,7 +214,7 @@ template <int FMT> struct Stage {
 // shared memory of one warp: stages, v tile float [NT][32][33], w_scale tile bf16 [32][34], mbarriers
 constexpr uint32_t TILE_V = 32 * 33 * 4, TILE_WS = 32 * 34 * 2;
 template <int FMT> __host__ __device__ constexpr uint32_t warp_smem(uint32_t nt) {
-    return NSTAGE * Stage<FMT>::BYTES + nt * TILE_V + TILE_WS + 64;
+    return ((NSTAGE * Stage<FMT>::BYTES + nt * TILE_V + TILE_WS + 128) + 127u) & ~127u;
 }
 
 template <int FMT>
@@ -248,7 +248,9 @@ __device__ __forceinline__ void read_cell(Raw<FMT> &o, const uint8_t *st, uint32
 // split the passes of their row blocks; `gw` / `nw` are the team's index and the number of teams, `wid`
 // the warp's index in the team, `wsm` the warp's own shared-memory region (warp_smem bytes, 128-byte
 // aligned), `s_f` the team's [NT][32] hand-off array, `bar_id` the named barrier of the team (0 = the whole CTA).  The activations come through
-// xq / xs / xsum (global memory when !MEGA, read through L2; any address space otherwise); `ps` carries the
+// xq / xs / xsum (global memory when !MEGA, read through the read-only L1 path: every warp of an SM reads the
+// same few KB, and sending each of those reads to L2 makes its slices a hot spot - measured 19 us instead of
+// 11 us for a 2048 x 49152 b4 launch; any address space otherwise); `ps` carries the
 // stage cursor and mbarrier parities from one call to the next (the mbarriers are initialised once by the caller).
 struct PipeState { uint32_t stage = 0, phase = 0; };
 
@@ -276,10 +278,11 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     const uint32_t rounds = (np + WK - 1) / WK;
     const bool merged = np == 1;                               // a block's rows are contiguous in every plane
 
-    // warp region: mbarriers (64 B), stages, v tile, w_scale tile
-    uint8_t *stages = wsm + 64;
-    float *s_v = reinterpret_cast<float *>(wsm + 64 + NSTAGE * St::BYTES);
-    uint16_t *s_ws = reinterpret_cast<uint16_t *>(wsm + 64 + NSTAGE * St::BYTES + NT * TILE_V);
+    // warp region: mbarriers (first 128 B, so that the stages keep their 128-byte alignment and a quarter-warp's
+    // 128-bit reads stay within one 128-byte line), stages, v tile, w_scale tile
+    uint8_t *stages = wsm + 128;
+    float *s_v = reinterpret_cast<float *>(wsm + 128 + NSTAGE * St::BYTES);
+    uint16_t *s_ws = reinterpret_cast<uint16_t *>(wsm + 128 + NSTAGE * St::BYTES + NT * TILE_V);
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(wsm);
     const uint32_t stage_sa = (uint32_t)__cvta_generic_to_shared(stages);
 
@@ -330,7 +333,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
 #pragma unroll
     for (int s = 0; s < NSTAGE; ++s) issue((ps.stage + s) % NSTAGE);
     // weights are on their way; the activations (and the output buffer) belong to the preceding kernels
-    if (!MEGA) { pdl_trigger(); pdl_wait(); }
+    if (!MEGA) { pdl_wait(); pdl_trigger(); }
 
     // ---- consumer
     int q[NT][16];
@@ -352,12 +355,12 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         const bool on = act && (uint32_t)t < a.n_tok;
-                        sx[t] = on ? (MEGA ? xs[(size_t)t * a.nc + c] : __ldcg(xs + (size_t)t * a.nc + c)) : 0.0f;
-                        xsum[t] = (on && xsum_p != nullptr) ? (MEGA ? xsum_p[(size_t)t * a.nc + c] : __ldcg(xsum_p + (size_t)t * a.nc + c)) : 0;
+                        sx[t] = on ? (MEGA ? xs[(size_t)t * a.nc + c] : __ldg(xs + (size_t)t * a.nc + c)) : 0.0f;
+                        xsum[t] = (on && xsum_p != nullptr) ? (MEGA ? xsum_p[(size_t)t * a.nc + c] : __ldg(xsum_p + (size_t)t * a.nc + c)) : 0;
 #pragma unroll
                         for (int jq = 0; jq < 4; ++jq) {
                             const int4 *src4 = reinterpret_cast<const int4 *>(xq + (size_t)t * a.cols + (size_t)c * 64) + jq;
-                            const int4 v = on ? (MEGA ? *src4 : __ldcg(src4)) : make_int4(0, 0, 0, 0);
+                            const int4 v = on ? (MEGA ? *src4 : __ldg(src4)) : make_int4(0, 0, 0, 0);
                             q[t][4 * jq] = v.x; q[t][4 * jq + 1] = v.y; q[t][4 * jq + 2] = v.z; q[t][4 * jq + 3] = v.w;
                         }
                         nz[t] = __ballot_sync(0xffffffffu, sx[t] != 0.0f);

@@ -9,8 +9,8 @@ namespace k2t {
 
 __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     if (c >= a.nc) return;
     const uint32_t tok = __ldcg(a.token);
     float v0, v1;
@@ -40,8 +40,8 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     extern __shared__ float s_x[];           // n floats
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     for (uint32_t i = tid; i < n / 4; i += 256) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
@@ -90,8 +90,8 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     __shared__ float s_head[4][128];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t head = blockIdx.x * 4 + warp, hd = a.head_dim, half = hd / 2;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     if (head >= a.n_q + 2 * a.n_kv) return;
     const uint32_t pos = __ldcg(a.pos);
     const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     __shared__ float s_p[4][8][32];       // probabilities of the current 32 positions
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t split = blockIdx.x * 4 + warp, kvh = blockIdx.y;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     if (split >= a.n_split) return;
     const uint32_t ctx = __ldcg(a.pos) + 1, G = a.group;
     if (ctx <= ATTN_EXACT_CTX) return;     // short contexts are computed in the CPU's order by attn_finish_kernel
@@ -290,8 +290,8 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
     __shared__ float s_red[HD / 32];
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + 1;
     float o = 0.0f;
     if (ctx <= ATTN_EXACT_CTX) {
@@ -409,8 +409,8 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
 template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const uint32_t pos = __ldcg(a.pos);
     if (pos + 1 > ATTN_EXACT_CTX) return;
     attention_head_cta<HD>(a, blockIdx.x, pos, attn_carve(smem));
@@ -423,8 +423,8 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
                                                            int8_t *__restrict__ q, float *__restrict__ scales,
                                                            int32_t *__restrict__ sums, float *__restrict__ dbg) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     if (c >= inter / 64) return;
     const float2 g = __ldcg(reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64) + lane);
     const float2 u = __ldcg(reinterpret_cast<const float2 *>(gate_up + inter + (size_t)c * 64) + lane);
@@ -449,8 +449,8 @@ __global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restri
     __shared__ uint32_t s_i[32];
     float bv = -INFINITY;
     uint32_t bi = 0xffffffffu;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     for (uint32_t i = threadIdx.x; i < n; i += 1024) {
         const float v = __ldcg(logits + i);
         if (v > bv) { bv = v; bi = i; }         // ascending i per thread: keeps the first maximum

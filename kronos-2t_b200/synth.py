@@ -41,3 +41,55 @@ def file_bytes(kind, rows, cols, bits, sgc=1):
         return ns * (cols // 8) * bits * 16 + ns * nc * 16 * 2
     nsg, cb = -(-nc // sgc), _NF_CHUNK[bits]
     return (ns // 2) * (nsg * 64 + nc * 2 * cb) + (ns & 1) * (nsg * 32 + nc * cb) + 16
+
+
+class HostMatrix:
+    """A matrix in the reference file format: the fields kronos_2t_b200.ffi.desc_of (and the oracle) read."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+    def file_bytes(self):
+        if self.kind == 0:
+            return self.data.nbytes + self.scales.nbytes
+        return self.pair.nbytes + self.tail.nbytes + 16
+
+
+def random_matrix(seed, rows, cols, mode):
+    """mode: b4 / b5 / b6 / nf4 / nf4g128 / nf3 / nf3g128."""
+    if mode.startswith("b"):
+        planes = int(mode[1])
+        data, scales = random_bipolar_bytes(seed, rows, cols, planes)
+        return HostMatrix(kind=0, rows=rows, cols=cols, planes=planes, data=data, scales=scales)
+    bits, sgc = int(mode[2]), 2 if mode.endswith("g128") else 1
+    if (cols // 64) % sgc:
+        sgc = 1
+    pair, tail = random_nf_bytes(seed, rows, cols, bits, sgc)
+    return HostMatrix(kind=2, rows=rows, cols=cols, bits=bits, sgc=sgc, codebook=NF4_DEFAULT if bits == 4 else NF3_DEFAULT,
+                      pair=pair, tail=tail)
+
+
+def rope_table(max_seq, head_dim, theta):
+    """build_rope_table (src/model/real_llm.rs:9212-9236): rows [cos(hd/2), sin(hd/2)], inv_freq in f64 -> f32."""
+    half = head_dim // 2
+    inv_freq = (1.0 / np.power(float(theta), (2.0 * np.arange(half)) / head_dim)).astype(np.float32)
+    ang = (np.arange(max_seq, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float32)
+    return np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)
+
+
+SMOLLM2_135M = dict(hidden=576, layers=30, n_q=9, n_kv=3, head_dim=64, inter=1536, vocab=49152, max_seq=512, eps=1e-5, theta=1e5)
+
+
+def random_model(cfg, mode, seed=0):
+    """Engine spec of a dense Llama-shaped model with random codes (decode time does not depend on the values)."""
+    c = dict(cfg)
+    h, hd, inter = c["hidden"], c["head_dim"], c["inter"]
+    q_dim, kv_dim = c["n_q"] * hd, c["n_kv"] * hd
+    layers = []
+    for l in range(c["layers"]):
+        s = seed * 100003 + 10 * l
+        layers.append(dict(input_norm=np.ones(h, np.float32), post_norm=np.ones(h, np.float32), qkv_bias=None, q_norm=None, k_norm=None,
+                           qkv=random_matrix(s + 1, q_dim + 2 * kv_dim, h, mode), o=random_matrix(s + 2, h, q_dim, mode),
+                           gate_up=random_matrix(s + 3, 2 * inter, h, mode), down=random_matrix(s + 4, h, inter, mode)))
+    return dict(cfg=c, layers=layers, final_norm=np.ones(h, np.float32), lm_head=random_matrix(seed * 100003 + 7, c["vocab"], h, mode),
+                rope=rope_table(c["max_seq"], hd, c["theta"]), embed_bf16=None)
