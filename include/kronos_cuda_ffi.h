@@ -137,7 +137,9 @@ int32_t kronos_cuda_gemv_dev(KronosCudaContext *ctx, const KronosCudaMatrix *m, 
 typedef struct KronosCudaEngine KronosCudaEngine;
 
 /* LlamaConfig scalars the device forward needs (src/model/real_llm.rs:91-457), as MetalLlamaEngine::try_new
- * receives them through `cfg`, plus the KV format (kv_bits: 8 = int8 Hadamard cache). */
+ * receives them through `cfg`, plus the KV format (kv_bits: 8 = int8 Hadamard cache, 4 = NF4 Hadamard cache as
+ * selected by RealLlamaEngine::set_kv_bits, real_llm.rs:1731-1735; the NF4 cache serves contexts of up to 512
+ * positions in this version). */
 typedef struct KronosCudaEngineConfig {
     uint32_t hidden_size, num_layers, num_attention_heads, num_key_value_heads, head_dim,
              intermediate_size, vocab_size, max_seq_len;
@@ -191,6 +193,11 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
 /* Diagnostic: attention output of the last layer for the last forwarded token, before o_proj:
  * [num_attention_heads * head_dim] (the `attn` vector of forward_token, real_llm.rs:6651-6700). */
 int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *engine, float *attention);
+/* Same for an NF4 Hadamard cache (kv_bits = 4): packed indices [head_dim / 2] (byte 16h+i of a 64-value group
+ * = columns 32h+i low nibble, 32h+16+i high nibble) and one bf16 scale per 64 values [head_dim / 64]
+ * (store_hadamard_q4_head_raw, real_llm.rs:8646-8701). */
+int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *engine, uint32_t layer, uint32_t kv_head, size_t position,
+                                      uint8_t *k_q4, uint16_t *k_s16, uint8_t *v_q4, uint16_t *v_s16);
 /* Diagnostic: phase trace of the whole-token decode kernel (the last step of the last decode_greedy call that
  * used it): global-timer readings in ns taken by CTA 0 at the start of the step, then around every phase
  * (activation prologue done / GEMV done / grid barrier passed; the attention phase has two marks).  Returns

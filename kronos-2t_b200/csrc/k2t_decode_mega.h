@@ -19,7 +19,7 @@ struct MegaLayer {           // lives in device memory
 struct MegaArgs {
     const MegaLayer *layers;
     const MegaMatrix *head;
-    uint32_t n_layers, hidden, n_q, n_kv, head_dim, inter, vocab, max_seq;
+    uint32_t n_layers, hidden, n_q, n_kv, head_dim, inter, vocab, max_seq, kv_bits;
     float eps, attn_scale;
     int32_t qk_norm_after_rope;
     const float *final_norm, *rope;

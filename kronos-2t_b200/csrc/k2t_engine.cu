@@ -105,6 +105,7 @@ bool enqueue_step(KronosCudaEngine *e, bool embed, bool greedy, bool long_ctx) {
             fa.out_q = e->act_q; fa.out_scales = e->act_s; fa.out_sums = e->act_m; fa.err_flag = e->ctx->d_err;
             fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
             fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
+            fa.kv_bits = c.kv_bits;
             if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
         } else {
             QkvPostArgs qa{};
@@ -146,12 +147,14 @@ bool ensure_graphs(KronosCudaEngine *e) {
     for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     // eager steps first (position 0, token 0; callers set both before every replay): loads every kernel
     // and sets its attributes outside a capture, where an error is also easier to attribute
-    for (int long_ctx = 0; long_ctx < 2; ++long_ctx)
+    const int variants = e->cfg.kv_bits == 8 ? 2 : 1;       // the split-KV (long context) kernels read the int8 cache only
+    for (int long_ctx = 0; long_ctx < variants; ++long_ctx)
         if (!set_u32(e, e->d_pos, 0) || !set_u32(e, e->d_token, 0) || !enqueue_step(e, true, true, long_ctx != 0) ||
             !sync_and_check(ctx, "engine warm-up step"))
             return false;
     const uint64_t launches_before = ctx->launches;
     for (int which = 0; which < 4; ++which) {
+        if ((which & 1) && variants == 1) continue;
         cudaGraph_t graph = nullptr;
         if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return false;
         const bool ok = enqueue_step(e, true, which < 2, (which & 1) != 0);
@@ -244,7 +247,7 @@ bool decode_mega(KronosCudaEngine *e, uint32_t first_token, uint32_t pos_start, 
     MegaArgs a{};
     a.layers = e->d_mega_layers; a.head = e->d_mega_head;
     a.n_layers = c.num_layers; a.hidden = c.hidden_size; a.n_q = c.num_attention_heads; a.n_kv = c.num_key_value_heads;
-    a.head_dim = c.head_dim; a.inter = c.intermediate_size; a.vocab = c.vocab_size; a.max_seq = c.max_seq_len;
+    a.head_dim = c.head_dim; a.inter = c.intermediate_size; a.vocab = c.vocab_size; a.max_seq = c.max_seq_len; a.kv_bits = c.kv_bits;
     a.eps = c.rms_norm_eps; a.attn_scale = 1.0f / sqrtf((float)c.head_dim); a.qk_norm_after_rope = c.qk_norm_after_rope;
     a.final_norm = e->final_norm; a.rope = e->rope;
     fill_embed_args(e, a.embed);
@@ -291,7 +294,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     if (c.hidden_size % 64 || c.intermediate_size % 64 || c.hidden_size == 0) { fail(ctx, "engine_create: hidden and intermediate sizes must be multiples of 64"); return nullptr; }
     if (c.num_key_value_heads == 0 || c.num_attention_heads % c.num_key_value_heads || c.num_attention_heads / c.num_key_value_heads > 8) {
         fail(ctx, "engine_create: query heads must be a multiple (at most 8x) of the kv heads"); return nullptr; }
-    if (c.kv_bits != 8) { fail(ctx, "engine_create: only the int8 Hadamard KV cache (kv_bits = 8) is implemented"); return nullptr; }
+    if (c.kv_bits != 8 && c.kv_bits != 4) { fail(ctx, "engine_create: kv_bits must be 8 (int8 Hadamard cache) or 4 (NF4 Hadamard cache)"); return nullptr; }
     if (c.max_seq_len == 0) { fail(ctx, "engine_create: max_seq_len is 0"); return nullptr; }
     if (!make_current(ctx)) return nullptr;
     const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd, kv_dim = c.num_key_value_heads * hd;
@@ -339,8 +342,9 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
-              dev_alloc(e, e->k_q8, slots * hd) && dev_alloc(e, e->v_q8, slots * hd) &&
-              dev_alloc(e, e->k_scale, slots) && dev_alloc(e, e->v_scale, slots) &&
+              dev_alloc(e, e->k_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) &&
+              dev_alloc(e, e->k_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
+              dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
               dev_alloc(e, e->d_token, 1) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
@@ -352,7 +356,8 @@ size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *e, size_t positions) 
     if (!e) return 0;
     // int8 keys and values plus one fp32 scale each per (layer, kv head, position): the reference's
     // 2 * layers * n_kv * (head_dim + 4) bytes per position (real_llm.rs:10223)
-    return positions * 2 * (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads * (e->cfg.head_dim + 4);
+    const size_t hd = e->cfg.head_dim, per_head = e->cfg.kv_bits == 4 ? hd / 2 + 2 * (hd / 64) : hd + 4;   // NF4: packed + bf16 per 64
+    return positions * 2 * (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads * per_head;
 }
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *e) { return e ? e->weight_bytes : 0; }
 
@@ -402,6 +407,7 @@ int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *e, uint32_t layer, uint32_t
     if (!k_q8 || !k_scale || !v_q8 || !v_scale) return fail(ctx, "read_kv: NULL buffer"), -1;
     if (layer >= e->cfg.num_layers || kv_head >= e->cfg.num_key_value_heads || position >= e->cfg.max_seq_len)
         return fail(ctx, "read_kv: index out of range"), -1;
+    if (e->cfg.kv_bits != 8) return fail(ctx, "read_kv: the engine holds an NF4 cache (use read_kv_q4)"), -1;
     if (!make_current(ctx)) return -1;
     const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->cfg.max_seq_len + position, hd = e->cfg.head_dim;
     cudaStream_t s = ctx->stream;
@@ -413,6 +419,27 @@ int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *e, uint32_t layer, uint32_t
     return sync_and_check(ctx, "read_kv") ? 0 : -1;
 }
 
+int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *e, uint32_t layer, uint32_t kv_head, size_t position, uint8_t *k_q4,
+                                      uint16_t *k_s16, uint8_t *v_q4, uint16_t *v_s16) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!k_q4 || !k_s16 || !v_q4 || !v_s16) return fail(ctx, "read_kv_q4: NULL buffer"), -1;
+    if (layer >= e->cfg.num_layers || kv_head >= e->cfg.num_key_value_heads || position >= e->cfg.max_seq_len)
+        return fail(ctx, "read_kv_q4: index out of range"), -1;
+    if (e->cfg.kv_bits != 4) return fail(ctx, "read_kv_q4: the engine holds an int8 cache (use read_kv)"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->cfg.max_seq_len + position, hd = e->cfg.head_dim;
+    const size_t nb = hd / 64;
+    cudaStream_t s = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(k_q4, reinterpret_cast<uint8_t *>(e->k_q8) + slot * hd / 2, hd / 2, cudaMemcpyDeviceToHost, s), "read_kv_q4") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(v_q4, reinterpret_cast<uint8_t *>(e->v_q8) + slot * hd / 2, hd / 2, cudaMemcpyDeviceToHost, s), "read_kv_q4") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(k_s16, reinterpret_cast<uint16_t *>(e->k_scale) + slot * nb, nb * 2, cudaMemcpyDeviceToHost, s), "read_kv_q4") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(v_s16, reinterpret_cast<uint16_t *>(e->v_scale) + slot * nb, nb * 2, cudaMemcpyDeviceToHost, s), "read_kv_q4"))
+        return -1;
+    return sync_and_check(ctx, "read_kv_q4") ? 0 : -1;
+}
+
 static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const uint32_t *tokens, size_t n_tok, size_t pos_start,
                               float *all_logits, float *last_logits) {
     if (!e) return -1;
@@ -421,6 +448,8 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     if ((!embeds && !tokens) || !last_logits) return fail(ctx, "forward: NULL buffer"), -1;
     if (n_tok == 0) return fail(ctx, "forward: n_tok is 0"), -1;
     if (pos_start + n_tok > e->cfg.max_seq_len) return fail(ctx, "forward: sequence would exceed max_seq_len"), -1;
+    if (e->cfg.kv_bits == 4 && pos_start + n_tok > ATTN_EXACT_CTX)
+        return fail(ctx, "forward: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (!make_current(ctx)) return -1;
     if (tokens) {
         for (size_t t = 0; t < n_tok; ++t)
@@ -465,6 +494,8 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     if (!out_tokens) return fail(ctx, "decode_greedy: out_tokens is NULL"), -1;
     if (first_token >= e->cfg.vocab_size) return fail(ctx, "decode_greedy: token id out of range"), -1;
     if (pos_start + n_steps > e->cfg.max_seq_len) return fail(ctx, "decode_greedy: sequence would exceed max_seq_len"), -1;
+    if (e->cfg.kv_bits == 4 && pos_start + n_steps > ATTN_EXACT_CTX)
+        return fail(ctx, "decode_greedy: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (n_steps == 0) return 0;
     if (!make_current(ctx)) return -1;
     if (e->mega_ok && pos_start + n_steps <= ATTN_EXACT_CTX) {

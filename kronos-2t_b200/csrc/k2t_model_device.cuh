@@ -81,6 +81,60 @@ __device__ __forceinline__ uint32_t split_span(uint32_t ctx, uint32_t n_split) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// NF4 Hadamard KV cache (kv_bits = 4): store_hadamard_q4_head_raw / nf4_nearest_idx (real_llm.rs:8615-8701)
+// ------------------------------------------------------------------------------------------------
+__constant__ float NF4_KV_CENTROIDS[16] = {-127.f, -96.f, -75.f, -58.f, -44.f, -31.f, -18.f, -6.f, 6.f, 18.f, 31.f, 44.f, 58.f, 75.f, 96.f, 127.f};
+// two-table decode of four packed indices at once (see cell_dot in k2t_gemv_core.cuh): centroid = hi[idx & 7] for
+// idx >= 8, -lo[idx] below; a selector nibble with bit 3 set yields the replicated sign bit of a non-negative byte = 0
+constexpr uint32_t NF4_KV_HI0 = 0x2C1F1206u, NF4_KV_HI1 = 0x7F604B3Au, NF4_KV_LO0 = 0x3A4B607Fu, NF4_KV_LO1 = 0x06121F2Cu;
+
+__device__ __forceinline__ uint32_t nf4_nearest_idx(float y) {
+    const float a = fabsf(y);
+    const uint32_t p = a < 37.5f ? (a < 12.0f ? 0u : a < 24.5f ? 1u : 2u) : a < 85.5f ? (a < 51.0f ? 3u : a < 66.5f ? 4u : 5u) : a < 111.5f ? 6u : 7u;
+    return y >= 0.0f ? 8u + p : 7u - p;
+}
+__device__ __forceinline__ uint16_t bf16_rne_bits(float v) {        // f32_to_bf16 (simd_lut.rs:1375-1382)
+    const uint32_t bits = __float_as_uint(v);
+    if ((bits & 0x7F800000u) == 0x7F800000u && (bits & 0x007FFFFFu) != 0) return (uint16_t)((bits >> 16) | 0x0040u);
+    return (uint16_t)((bits + 0x00007FFFu + ((bits >> 16) & 1u)) >> 16);
+}
+
+// One 64-value group held by a warp (lane l: rotated elements 2l, 2l+1) -> 32 packed bytes + bf16 scale.  The
+// least-squares sums run sequentially in element order, as on the CPU (lane 0: numerator, lane 1: denominator).
+// s_val / s_c: 64 floats each, s_idx: 64 bytes of per-warp scratch.  Lane j returns byte j; *scale_bits = the scale.
+__device__ __forceinline__ uint32_t warp_quant64_q4(float v0, float v1, uint32_t lane, float *s_val, float *s_c, uint8_t *s_idx,
+                                                    uint16_t *scale_bits) {
+    const float max_abs = warp_max(fmaxf(fabsf(v0), fabsf(v1)));
+    if (max_abs < 1e-30f) { *scale_bits = 0; return 0x88u; }
+    const float inv0 = __fdiv_rn(127.0f, max_abs);
+    s_val[2 * lane] = v0; s_val[2 * lane + 1] = v1;
+    s_c[2 * lane] = NF4_KV_CENTROIDS[nf4_nearest_idx(__fmul_rn(v0, inv0))];
+    s_c[2 * lane + 1] = NF4_KV_CENTROIDS[nf4_nearest_idx(__fmul_rn(v1, inv0))];
+    __syncwarp();
+    float acc = 0.0f;
+    if (lane == 0) {
+#pragma unroll 8
+        for (int i = 0; i < 64; ++i) acc = __fadd_rn(acc, __fmul_rn(s_val[i], s_c[i]));
+    } else if (lane == 1) {
+#pragma unroll 8
+        for (int i = 0; i < 64; ++i) acc = __fadd_rn(acc, __fmul_rn(s_c[i], s_c[i]));
+    }
+    const float num = __shfl_sync(0xffffffffu, acc, 0), den = __shfl_sync(0xffffffffu, acc, 1);
+    const float refined = (den > 1e-12f && num > 0.0f) ? __fdiv_rn(num, den) : __fdiv_rn(max_abs, 127.0f);
+    const uint16_t sb = bf16_rne_bits(refined);
+    const float s_final = bf16_bits_to_f32(sb);
+    const float inv_final = s_final > 1e-30f ? __fdiv_rn(1.0f, s_final) : 0.0f;
+    *scale_bits = sb;
+    s_idx[2 * lane] = (uint8_t)nf4_nearest_idx(__fmul_rn(v0, inv_final));
+    s_idx[2 * lane + 1] = (uint8_t)nf4_nearest_idx(__fmul_rn(v1, inv_final));
+    __syncwarp();
+    const uint32_t h = lane / 16, i = lane % 16;       // byte j = 16h + i packs columns 32h+i (low) and 32h+16+i (high)
+    const uint32_t byte = (uint32_t)s_idx[h * 32 + i] | ((uint32_t)s_idx[h * 32 + 16 + i] << 4);
+    __syncwarp();
+    return byte;
+}
+
+// ------------------------------------------------------------------------------------------------
 // One query head, from the fused qkv vector to the int8 activation of o_proj, by one CTA of 256 threads, for
 // contexts of up to ATTN_EXACT_CTX positions: bias, qk-norm, RoPE, rotation + int8 of the head's query and
 // of its kv head's key and value (6609-6650, 8139-8178, 8303-8365, 9287-9326; the first query head of a
@@ -95,6 +149,13 @@ struct AttnSmem {
     float *sc;                 // [ATTN_EXACT_CTX]
     int8_t *vbuf;              // [ATTN_EXACT_CTX][head_dim <= 128] cached value rows (one bulk copy)
     uint64_t *bar;             // mbarrier of that copy
+    // kv_bits = 4 only
+    float *wg;                 // [2][ATTN_EXACT_CTX] value weights per 64-value group
+    float *cbf;                // [16] centroids as floats
+    float *qs_val, *qs_c;      // [3][64] quantizer scratch per head warp
+    uint8_t *qs_idx;           // [3][64]
+    uint8_t *hq4;              // [2][64] packed key / value of the current position
+    uint16_t *hs16;            // [2][2] their group scales
     float *head;               // [3][128] q / k / v head being processed
     int8_t *hq;                // [3][128] their int8 form
     float *hs;                 // [3] scales
@@ -104,7 +165,8 @@ struct AttnSmem {
 };
 __host__ __device__ inline size_t attn_round(size_t v) { return (v + 127) & ~(size_t)127; }
 __host__ __device__ inline size_t attn_smem_bytes() {
-    return attn_round(ATTN_EXACT_CTX * 4) + attn_round(ATTN_EXACT_CTX * 128) + 128 + attn_round(3 * 128 * 4) + attn_round(3 * 128) + 128 +
+    return attn_round(2 * ATTN_EXACT_CTX * 4) + 128 + 2 * attn_round(3 * 64 * 4) + attn_round(3 * 64) + 128 + 128 +
+           attn_round(ATTN_EXACT_CTX * 4) + attn_round(ATTN_EXACT_CTX * 128) + 128 + attn_round(3 * 128 * 4) + attn_round(3 * 128) + 128 +
            attn_round(128 * 4) + 128 + 128;
 }
 __device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
@@ -113,6 +175,13 @@ __device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
     s.sc = reinterpret_cast<float *>(base + off); off += attn_round(ATTN_EXACT_CTX * 4);
     s.vbuf = reinterpret_cast<int8_t *>(base + off); off += attn_round(ATTN_EXACT_CTX * 128);
     s.bar = reinterpret_cast<uint64_t *>(base + off); off += 128;
+    s.wg = reinterpret_cast<float *>(base + off); off += attn_round(2 * ATTN_EXACT_CTX * 4);
+    s.cbf = reinterpret_cast<float *>(base + off); off += 128;
+    s.qs_val = reinterpret_cast<float *>(base + off); off += attn_round(3 * 64 * 4);
+    s.qs_c = reinterpret_cast<float *>(base + off); off += attn_round(3 * 64 * 4);
+    s.qs_idx = reinterpret_cast<uint8_t *>(base + off); off += attn_round(3 * 64);
+    s.hq4 = reinterpret_cast<uint8_t *>(base + off); off += 128;
+    s.hs16 = reinterpret_cast<uint16_t *>(base + off); off += 128;
     s.head = reinterpret_cast<float *>(base + off); off += attn_round(3 * 128 * 4);
     s.hq = reinterpret_cast<int8_t *>(base + off); off += attn_round(3 * 128);
     s.hs = reinterpret_cast<float *>(base + off); off += 128;
@@ -122,16 +191,18 @@ __device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
     return s;
 }
 
-template <int HD>
+template <int HD, bool KV4>
 __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
     constexpr int QW = HD / 4, NB = HD / 64;
-    constexpr uint32_t MEGA_THREADS = ATTN_THREADS, MEGA_WARPS = ATTN_THREADS / 32;
+    constexpr uint32_t NT = ATTN_THREADS, NW = ATTN_THREADS / 32;
+    constexpr uint32_t ROW = KV4 ? HD / 2 : HD;            // bytes of one cached key / value row
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t group = A.n_q / A.n_kv, kvh = qh / group, ctx = pos + 1, layer = A.layer;
-    const FusedAttnArgs *L = &A;
     const size_t slot0 = ((size_t)layer * A.n_kv + kvh) * A.max_seq;
-    const int8_t *K = A.k_q8 + slot0 * HD, *V = A.v_q8 + slot0 * HD;
+    const uint8_t *K = reinterpret_cast<const uint8_t *>(A.k_q8) + slot0 * ROW, *V = reinterpret_cast<const uint8_t *>(A.v_q8) + slot0 * ROW;
+    // scales: one fp32 per slot (int8 cache) or NB bf16 per slot (NF4 cache)
     const float *ks = A.k_scale + slot0, *vs = A.v_scale + slot0;
+    const uint16_t *ks16 = reinterpret_cast<const uint16_t *>(A.k_scale) + slot0 * NB, *vs16 = reinterpret_cast<const uint16_t *>(A.v_scale) + slot0 * NB;
     // ---- everything that does not depend on the current token is requested first, so that its L2 latency
     // overlaps the head preparation.  First of all (its fences would otherwise wait for the loads below) the
     // cached value rows [0, pos): they are contiguous, so one bulk copy into shared memory, completion on an
@@ -142,10 +213,11 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vbar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async;" ::: "memory");       // barrier init, and the cache rows other CTAs / kernels stored
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vbar), "r"(pos * HD) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(vbar), "r"(pos * ROW) : "memory");
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"((uint32_t)__cvta_generic_to_shared(s.vbuf)), "l"(V), "r"(pos * HD), "r"(vbar) : "memory");
+                     ::"r"((uint32_t)__cvta_generic_to_shared(s.vbuf)), "l"(V), "r"(pos * ROW), "r"(vbar) : "memory");
     }
+    if (KV4 && tid < 16) s.cbf[tid] = NF4_KV_CENTROIDS[tid];
     constexpr int HV = HD / 32;                            // head elements per lane (warps 0..2)
     const uint32_t my_head = warp == 0 ? qh : warp == 1 ? A.n_q + kvh : A.n_q + A.n_kv + kvh;
     float hv[HV], rc[HV], rs[HV];                          // head values (+bias), rope cos / sin of the lane's pair
@@ -160,17 +232,26 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         }
     }
     constexpr int PT = ATTN_EXACT_CTX / ATTN_THREADS;     // positions per thread
-    int4 kreg[PT][QW / 4];
-    float ksr[PT], vsr[PT];
+    constexpr int KR = ROW / 16;                           // int4 per key row
+    int4 kreg[PT][KR];
+    float ksr[PT][KV4 ? NB : 1], vsr[PT][KV4 ? NB : 1];
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * MEGA_THREADS;
+        const uint32_t t = tid + k * NT;
         const bool cached = t < pos;
 #pragma unroll
-        for (int i = 0; i < QW / 4; ++i)
-            kreg[k][i] = cached ? __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i) : make_int4(0, 0, 0, 0);
-        ksr[k] = cached ? __ldcg(ks + t) : 0.0f;
-        vsr[k] = cached ? __ldcg(vs + t) : 0.0f;
+        for (int i = 0; i < KR; ++i)
+            kreg[k][i] = cached ? __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * ROW) + i) : make_int4(0, 0, 0, 0);
+        if (KV4) {
+#pragma unroll
+            for (int g = 0; g < NB; ++g) {
+                ksr[k][g] = cached ? bf16_bits_to_f32(__ldcg(ks16 + (size_t)t * NB + g)) : 0.0f;
+                vsr[k][g] = cached ? bf16_bits_to_f32(__ldcg(vs16 + (size_t)t * NB + g)) : 0.0f;
+            }
+        } else {
+            ksr[k][0] = cached ? __ldcg(ks + t) : 0.0f;
+            vsr[k][0] = cached ? __ldcg(vs + t) : 0.0f;
+        }
     }
     // ---- the three heads of this CTA: warp 0 = query qh, warp 1 = key kvh, warp 2 = value kvh
     if (warp < 3) {
@@ -178,7 +259,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
 #pragma unroll
         for (int k = 0; k < HV; ++k) sh[lane + 32 * k] = hv[k];
         __syncwarp();
-        const float *norm_w = warp == 0 ? L->q_norm : (warp == 1 ? L->k_norm : nullptr);
+        const float *norm_w = warp == 0 ? A.q_norm : (warp == 1 ? A.k_norm : nullptr);
         auto do_rope = [&]() {       // element i pairs with i +- hd/2: x0' = x0 c - x1 s, x1' = x1 c + x0 s
             float nv[HV];
 #pragma unroll
@@ -219,47 +300,103 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             warp_fwht64(v0[b], v1[b], b, lane);
             mx = fmaxf(mx, fmaxf(fabsf(v0[b]), fabsf(v1[b])));
         }
-        mx = warp_max(mx);
-        const bool zero = mx <= 1.1920929e-07f;
-        const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx), scale = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
         const bool store = warp > 0 && qh % group == 0;     // one CTA of the group writes the cache entry
-        int8_t *cache = (warp == 1 ? A.k_q8 : A.v_q8) + (slot0 + pos) * HD;
+        if (KV4 && warp > 0) {       // NF4 key / value: per 64-value group a refined bf16 scale and packed indices
+            uint8_t *cache = const_cast<uint8_t *>(warp == 1 ? K : V) + (size_t)pos * ROW;
+            uint16_t *cache_s = const_cast<uint16_t *>(warp == 1 ? ks16 : vs16) + (size_t)pos * NB;
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
-            const char2 pk = make_char2((signed char)q0, (signed char)q1);
-            reinterpret_cast<char2 *>(s.hq + warp * 128 + b * 64)[lane] = pk;
-            if (store) reinterpret_cast<char2 *>(cache + b * 64)[lane] = pk;
-        }
-        if (lane == 0) {
-            s.hs[warp] = scale;
-            if (store) (warp == 1 ? A.k_scale : A.v_scale)[slot0 + pos] = scale;
+            for (int b = 0; b < NB; ++b) {
+                uint16_t sb;
+                const uint32_t byte = warp_quant64_q4(v0[b], v1[b], lane, s.qs_val + warp * 64, s.qs_c + warp * 64, s.qs_idx + warp * 64, &sb);
+                s.hq4[(warp - 1) * 64 + b * 32 + lane] = (uint8_t)byte;
+                if (store) cache[b * 32 + lane] = (uint8_t)byte;
+                if (lane == 0) {
+                    s.hs16[(warp - 1) * 2 + b] = sb;
+                    if (store) cache_s[b] = sb;
+                }
+            }
+        } else {                     // int8 with one scale for the whole head (queries always)
+            mx = warp_max(mx);
+            const bool zero = mx <= 1.1920929e-07f;
+            const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx), scale = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
+            int8_t *cache = reinterpret_cast<int8_t *>(const_cast<uint8_t *>(warp == 1 ? K : V)) + (size_t)pos * HD;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
+                const char2 pk = make_char2((signed char)q0, (signed char)q1);
+                reinterpret_cast<char2 *>(s.hq + warp * 128 + b * 64)[lane] = pk;
+                if (store) reinterpret_cast<char2 *>(cache + b * 64)[lane] = pk;
+            }
+            if (lane == 0) {
+                s.hs[warp] = scale;
+                if (store) const_cast<float *>(warp == 1 ? ks : vs)[pos] = scale;
+            }
         }
     }
     __syncthreads();
     // ---- scores (positions < pos from the prefetched cache rows, position pos from shared memory)
     const float qas = __fmul_rn(s.hs[0], A.attn_scale);
     int qw[QW];
+    if (KV4) {
+        // a packed word holds columns (i, 16+i, i+1, 16+i+1 | i+2, 16+i+2, i+3, 16+i+3) of a 32-column half in its
+        // eight nibbles: the query bytes are gathered in that order once
 #pragma unroll
-    for (int i = 0; i < QW; ++i) qw[i] = reinterpret_cast<const int *>(s.hq)[i];
+        for (int g = 0; g < NB; ++g)
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                const int8_t *qb = s.hq + g * 64 + (w / 4) * 32 + 4 * (w % 4);
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    qw[g * 16 + 2 * w + u] = (int)((uint32_t)(uint8_t)qb[2 * u] | ((uint32_t)(uint8_t)qb[16 + 2 * u] << 8) |
+                                                   ((uint32_t)(uint8_t)qb[2 * u + 1] << 16) | ((uint32_t)(uint8_t)qb[16 + 2 * u + 1] << 24));
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < QW; ++i) qw[i] = reinterpret_cast<const int *>(s.hq)[i];
+    }
     float mx = -INFINITY, scr[PT];
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * MEGA_THREADS;
+        const uint32_t t = tid + k * NT;
         scr[k] = -INFINITY;
         if (t < ctx) {
-            int dot = 0;
+            if (KV4) {        // causal_gqa_group_q4_or_window (8794-8988): total += ((dot * ks_g) * q_s) per 64-value group
+                float total = 0.0f;
 #pragma unroll
-            for (int i = 0; i < QW / 4; ++i) {
-                const int4 v = t < pos ? kreg[k][i] : reinterpret_cast<const int4 *>(s.hq + 128)[i];
-                dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
-                dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
+                for (int g = 0; g < NB; ++g) {
+                    int up = 0, dn = 0;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int4 v = t < pos ? kreg[k][2 * g + i] : reinterpret_cast<const int4 *>(s.hq4 + g * 32)[i];
+                        const uint32_t xw[4] = {(uint32_t)v.x, (uint32_t)v.y, (uint32_t)v.z, (uint32_t)v.w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const uint32_t x = xw[w], y = x ^ 0x88888888u;
+                            const int q0 = qw[g * 16 + 2 * (4 * i + w)], q1 = qw[g * 16 + 2 * (4 * i + w) + 1];
+                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y), q0, up);
+                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x), q0, dn);
+                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y >> 16), q1, up);
+                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x >> 16), q1, dn);
+                        }
+                    }
+                    const float ksg = t < pos ? ksr[k][g] : bf16_bits_to_f32(s.hs16[g]);
+                    total = __fadd_rn(total, __fmul_rn(__fmul_rn((float)(up - dn), ksg), qas));
+                }
+                scr[k] = total;
+            } else {
+                int dot = 0;
+#pragma unroll
+                for (int i = 0; i < QW / 4; ++i) {
+                    const int4 v = t < pos ? kreg[k][i] : reinterpret_cast<const int4 *>(s.hq + 128)[i];
+                    dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
+                    dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
+                }
+                // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+                const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
+                const float kst = t < pos ? ksr[k][0] : s.hs[1];
+                scr[k] = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
+                                                       : __fmul_rn(__fmul_rn((float)dot, kst), qas);
             }
-            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
-            const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
-            const float kst = t < pos ? ksr[k] : s.hs[1];
-            scr[k] = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
-                                                   : __fmul_rn(__fmul_rn((float)dot, kst), qas);
             mx = fmaxf(mx, scr[k]);
         }
     }
@@ -267,13 +404,13 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     if (lane == 0) s.red[warp] = mx;
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < (int)MEGA_WARPS; ++i) mx = fmaxf(mx, s.red[i]);
+    for (int i = 0; i < (int)NW; ++i) mx = fmaxf(mx, s.red[i]);
     // softmax_unnorm (9603-9632): polynomial exp for whole groups of 4 positions, libm exp for the rest
     // (correctly rounded: double exp rounded to float; those run while warp 0 sums the body)
     const uint32_t n4 = ctx & ~3u;
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * MEGA_THREADS;
+        const uint32_t t = tid + k * NT;
         if (t < n4) s.sc[t] = exp_poly(__fsub_rn(scr[k], mx));
     }
     __syncthreads();
@@ -295,7 +432,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * MEGA_THREADS;
+        const uint32_t t = tid + k * NT;
         if (t >= n4 && t < ctx) s.sc[t] = (float)exp((double)__fsub_rn(scr[k], mx));
     }
     __syncthreads();
@@ -307,8 +444,17 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     const float inv = *s.inv;
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * MEGA_THREADS;
-        if (t < ctx) s.sc[t] = __fmul_rn(__fmul_rn(s.sc[t], inv), t < pos ? vsr[k] : s.hs[2]);
+        const uint32_t t = tid + k * NT;
+        if (t < ctx) {
+            const float p_norm = __fmul_rn(s.sc[t], inv);
+            if (KV4) {
+#pragma unroll
+                for (int g = 0; g < NB; ++g)
+                    s.wg[g * ATTN_EXACT_CTX + t] = __fmul_rn(p_norm, t < pos ? vsr[k][g] : bf16_bits_to_f32(s.hs16[2 + g]));
+            } else {
+                s.sc[t] = __fmul_rn(p_norm, t < pos ? vsr[k][0] : s.hs[2]);
+            }
+        }
     }
     // ---- values: thread i < HD = dimension i runs the position-ascending chain over the staged rows
     __syncthreads();                       // weights complete
@@ -324,28 +470,51 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     if (tid < HD && !copy_failed) {
         // a zero weight skips the position (as the CPU loop does): select, not branch.  Eight positions are
         // loaded before their fma chain starts, so the chain runs at fma latency, not shared-memory latency.
-        // int8 -> fp32 without the conversion unit (a quarter-rate pipe that would bound this loop): for a byte b,
-        // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
-        const float *wp = s.sc;
-        const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + tid;
-        auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
-        uint32_t j = 0;
-        for (; j + 8 <= pos; j += 8) {
-            float w[8];
-            uint32_t v[8];
+        if (KV4) {
+            const uint32_t g = tid / 64, e = tid % 64, r = e % 32;
+            const uint32_t byte_off = g * 32 + (e / 32) * 16 + (r % 16), shift = r < 16 ? 0u : 4u;
+            const float *wp = s.wg + g * ATTN_EXACT_CTX;
+            const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + byte_off;
+            uint32_t j = 0;
+            for (; j + 8 <= pos; j += 8) {
+                float w[8], c[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; v[u] = vp[(j + u) * HD]; }
+                for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; c[u] = s.cbf[(vp[(j + u) * ROW] >> shift) & 15u]; }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(to_f32(v[u]), w[u], o); o = w[u] != 0.0f ? nv : o; }
-        }
-        for (; j < pos; ++j) {
-            const float w = wp[j];
-            const float nv = __fmaf_rn(to_f32(vp[j * HD]), w, o);
+                for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(c[u], w[u], o); o = w[u] != 0.0f ? nv : o; }
+            }
+            for (; j < pos; ++j) {
+                const float w = wp[j];
+                const float nv = __fmaf_rn(s.cbf[(vp[j * ROW] >> shift) & 15u], w, o);
+                o = w != 0.0f ? nv : o;
+            }
+            const float w = wp[pos];       // the current position: its value row is still in shared memory
+            const float nv = __fmaf_rn(s.cbf[(s.hq4[64 + byte_off] >> shift) & 15u], w, o);
+            o = w != 0.0f ? nv : o;
+        } else {
+            // int8 -> fp32 without the conversion unit (a quarter-rate pipe that would bound this loop): for a byte b,
+            // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
+            const float *wp = s.sc;
+            const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + tid;
+            auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
+            uint32_t j = 0;
+            for (; j + 8 <= pos; j += 8) {
+                float w[8];
+                uint32_t v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; v[u] = vp[(j + u) * HD]; }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(to_f32(v[u]), w[u], o); o = w[u] != 0.0f ? nv : o; }
+            }
+            for (; j < pos; ++j) {
+                const float w = wp[j];
+                const float nv = __fmaf_rn(to_f32(vp[j * HD]), w, o);
+                o = w != 0.0f ? nv : o;
+            }
+            const float w = wp[pos];       // the current position: its value row is still in shared memory
+            const float nv = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), w, o);
             o = w != 0.0f ? nv : o;
         }
-        const float w = wp[pos];           // the current position: its value row is still in shared memory
-        const float nv = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), w, o);
-        o = w != 0.0f ? nv : o;
     }
     if (__syncthreads_or(copy_failed) && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
     if (tid == 0 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
@@ -366,5 +535,15 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
 }
 
+// runtime dispatch on head_dim / cache format
+__device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
+    if (A.kv_bits == 4) {
+        if (A.head_dim == 64) attention_head_cta<64, true>(A, qh, pos, s);
+        else attention_head_cta<128, true>(A, qh, pos, s);
+    } else {
+        if (A.head_dim == 64) attention_head_cta<64, false>(A, qh, pos, s);
+        else attention_head_cta<128, false>(A, qh, pos, s);
+    }
+}
 
 }  // namespace k2t

@@ -406,14 +406,13 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
 // Contexts of up to ATTN_EXACT_CTX positions: bias / qk-norm / RoPE / KV store / attention / o_proj activation
 // in one kernel, CTA q = query head q (attention_head_cta).  Longer contexts: returns at once, the split-KV
 // kernels serve them.
-template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_wait();
     pdl_trigger();
     const uint32_t pos = __ldcg(a.pos);
     if (pos + 1 > ATTN_EXACT_CTX) return;
-    attention_head_cta<HD>(a, blockIdx.x, pos, attn_carve(smem));
+    attention_head_dispatch(a, blockIdx.x, pos, attn_carve(smem));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -520,12 +519,10 @@ cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
 }
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl) {
     const size_t smem = attn_smem_bytes();
-    cudaError_t e = cudaFuncSetAttribute(a.head_dim == 64 ? (const void *)attn_fused_kernel<64> : (const void *)attn_fused_kernel<128>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (a.head_dim != 64 && a.head_dim != 128) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(attn_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    if (a.head_dim == 64) return launch_kernel(attn_fused_kernel<64>, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
-    if (a.head_dim == 128) return launch_kernel(attn_fused_kernel<128>, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
-    return cudaErrorInvalidValue;
+    return launch_kernel(attn_fused_kernel, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
 }
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
                                 float *dbg, bool pdl) {

@@ -56,6 +56,7 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     int8_t *out_q; float *out_scales; int32_t *out_sums;
     uint32_t *err_flag;          // set when the bounded wait for the value rows gives up
     uint32_t n_q, n_kv, head_dim, max_seq, layer;
+    uint32_t kv_bits;            // 8: int8 rows [head_dim] + fp32 scale per slot; 4: NF4 rows [head_dim / 2] + bf16 scale per 64 values
     float eps, attn_scale;
     int32_t qk_norm_after_rope;
 };

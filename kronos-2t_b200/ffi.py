@@ -88,6 +88,7 @@ def load_library():
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
     sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
+    sig("kronos_cuda_engine_read_kv_q4", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     _LIB = L
     return L
@@ -266,7 +267,7 @@ class Engine:
         self.ctx, self.L = ctx, ctx.L
         c = spec["cfg"]
         self.cfg = EngineConfig(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
-                                c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), 8)
+                                c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
         keep = []
 
         def vec(a):
@@ -347,6 +348,11 @@ class Engine:
     def read_kv(self, layer, kv_head, position):
         """(k_q8, k_scale, v_q8, v_scale) of one cache slot."""
         hd = self.cfg.head_dim
+        if self.cfg.kv_bits == 4:
+            k, v = np.empty(hd // 2, np.uint8), np.empty(hd // 2, np.uint8)
+            ks, vs = np.empty(hd // 64, np.uint16), np.empty(hd // 64, np.uint16)
+            self.ctx._check(self.L.kronos_cuda_engine_read_kv_q4(self.handle, layer, kv_head, position, _p(k), _p(ks), _p(v), _p(vs)))
+            return k, ks, v, vs
         k, v = np.empty(hd, np.int8), np.empty(hd, np.int8)
         ks, vs = np.empty(1, np.float32), np.empty(1, np.float32)
         self.ctx._check(self.L.kronos_cuda_engine_read_kv(self.handle, layer, kv_head, position, _p(k), _p(ks), _p(v), _p(vs)))

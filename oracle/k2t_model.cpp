@@ -87,6 +87,9 @@ struct K2oModel {
     // int8 Hadamard KV cache (QuantizedKvCache, real_llm.rs:1093-1412): [layer][kv head][pos][hd] + scale per (head,pos)
     std::vector<int8_t> k_q8, v_q8;
     std::vector<float> k_sc, v_sc;
+    // NF4 Hadamard KV cache (kv_bits = 4): packed indices [..][hd / 2], bf16 scale per 64-value group [..][hd / 64]
+    std::vector<uint8_t> k_q4, v_q4;
+    std::vector<uint16_t> k_s16, v_s16;
     size_t pos = 0;
     // taps of the last forward (for tests)
     std::vector<float> tap_hidden;    // hidden state after every layer [layers][hidden]
@@ -181,6 +184,110 @@ void attend_head(const K2oModel &m, size_t l, size_t kvh, const float *q_head, s
     std::memcpy(out, o, hd * sizeof(float));
 }
 
+const int8_t NF4_CB[16] = {-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127};   // simd_lut.rs:4343
+
+// nf4_nearest_idx (8615-8644): nearest default centroid by magnitude thresholds, sign picks the half.
+uint8_t nf4_nearest_idx(float y) {
+    const float a = std::fabs(y);
+    const int p = a < 37.5f ? (a < 12.0f ? 0 : a < 24.5f ? 1 : 2) : a < 85.5f ? (a < 51.0f ? 3 : a < 66.5f ? 4 : 5) : a < 111.5f ? 6 : 7;
+    return (uint8_t)(y >= 0.0f ? 8 + p : 7 - p);
+}
+
+inline uint16_t bf16_rne(float v) {      // f32_to_bf16 (simd_lut.rs:1375-1382)
+    uint32_t bits;
+    std::memcpy(&bits, &v, 4);
+    if ((bits & 0x7F800000u) == 0x7F800000u && (bits & 0x007FFFFFu) != 0) return (uint16_t)((bits >> 16) | 0x0040u);
+    return (uint16_t)((bits + 0x00007FFFu + ((bits >> 16) & 1u)) >> 16);
+}
+inline float bf16_f32(uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; std::memcpy(&f, &u, 4); return f; }
+
+// store_hadamard_q4_head_raw (8646-8701): per 64-value group a least-squares scale over the first assignment,
+// rounded to bf16, then the final assignment; byte i of half h packs columns 32h+i (low) and 32h+16+i (high).
+void quant_head_q4(const float *src, size_t hd, uint8_t *q4, uint16_t *s16) {
+    float rot[128];
+    std::memcpy(rot, src, hd * sizeof(float));
+    k2o_fwht64(rot, hd, 0);
+    for (size_t g = 0; g < hd / 64; ++g) {
+        const float *blk = rot + g * 64;
+        float max_abs = 0.0f;
+        for (size_t i = 0; i < 64; ++i) { float a = std::fabs(blk[i]); if (a > max_abs) max_abs = a; }
+        if (max_abs < 1e-30f) { s16[g] = 0; std::memset(q4 + g * 32, 0x88, 32); continue; }
+        const float inv0 = 127.0f / max_abs;
+        float num = 0.0f, den = 0.0f;
+        for (size_t i = 0; i < 64; ++i) {
+            const float c = (float)NF4_CB[nf4_nearest_idx(blk[i] * inv0)];
+            num += blk[i] * c;
+            den += c * c;
+        }
+        const float refined = (den > 1e-12f && num > 0.0f) ? num / den : max_abs / 127.0f;
+        const uint16_t sb = bf16_rne(refined);
+        const float s_final = bf16_f32(sb);
+        const float inv_final = s_final > 1e-30f ? 1.0f / s_final : 0.0f;
+        s16[g] = sb;
+        for (size_t h = 0; h < 2; ++h)
+            for (size_t i = 0; i < 16; ++i) {
+                const uint8_t lo = nf4_nearest_idx(blk[h * 32 + i] * inv_final), hi = nf4_nearest_idx(blk[h * 32 + 16 + i] * inv_final);
+                q4[g * 32 + h * 16 + i] = (uint8_t)(lo | (hi << 4));
+            }
+    }
+}
+
+// causal_gqa_group_q4_or_window (8794-8988) with bits == 4, no window, for one query head; aarch64 arithmetic
+// (integer dots, fma value accumulation, softmax_unnorm_neon).
+void attend_head_q4(const K2oModel &m, size_t l, size_t kvh, const float *q_head, size_t seq_len, float attn_scale,
+                    std::vector<float> &sc, float *out) {
+    const size_t hd = m.cfg.head_dim, gph = hd / 64, half = hd / 2;
+    int8_t qi[128];
+    float qs;
+    quant_head(q_head, hd, qi, &qs);
+    const float q_s = qs * attn_scale;
+    const size_t slot0 = m.kv_slot(l, kvh, 0);
+    sc.resize(seq_len);
+    for (size_t t = 0; t < seq_len; ++t) {
+        float total = 0.0f;
+        for (size_t g = 0; g < gph; ++g) {
+            const float ks = bf16_f32(m.k_s16[(slot0 + t) * gph + g]);
+            const uint8_t *kp = m.k_q4.data() + (slot0 + t) * half + g * 32;
+            int32_t dot = 0;
+            for (size_t h = 0; h < 2; ++h)
+                for (size_t i = 0; i < 16; ++i) {
+                    const uint8_t b = kp[h * 16 + i];
+                    dot += (int32_t)NF4_CB[b & 15] * qi[g * 64 + h * 32 + i] + (int32_t)NF4_CB[b >> 4] * qi[g * 64 + h * 32 + 16 + i];
+                }
+            total += ((float)dot * ks) * q_s;
+        }
+        sc[t] = total;
+    }
+    float mx = -INFINITY;
+    for (size_t t = 0; t < seq_len; ++t) mx = std::max(mx, sc[t]);
+    float acc[4] = {0, 0, 0, 0};
+    size_t t = 0;
+    for (; t + 4 <= seq_len; t += 4)
+        for (int j = 0; j < 4; ++j) { float e = exp_poly(sc[t + j] - mx); sc[t + j] = e; acc[j] += e; }
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    for (; t < seq_len; ++t) { float e = (float)std::exp((double)(sc[t] - mx)); sc[t] = e; sum += e; }
+    const float inv = 1.0f / sum;
+    float o[128] = {0};
+    for (size_t tt = 0; tt < seq_len; ++tt) {
+        const float p_norm = sc[tt] * inv;
+        if (p_norm == 0.0f) continue;
+        for (size_t g = 0; g < gph; ++g) {
+            const float w = p_norm * bf16_f32(m.v_s16[(slot0 + tt) * gph + g]);
+            if (w == 0.0f) continue;
+            const uint8_t *vp = m.v_q4.data() + (slot0 + tt) * half + g * 32;
+            for (size_t h = 0; h < 2; ++h)
+                for (size_t i = 0; i < 16; ++i) {
+                    const uint8_t b = vp[h * 16 + i];
+                    float &lo = o[g * 64 + h * 32 + i], &hi = o[g * 64 + h * 32 + 16 + i];
+                    lo = std::fmaf((float)NF4_CB[b & 15], w, lo);
+                    hi = std::fmaf((float)NF4_CB[b >> 4], w, hi);
+                }
+        }
+    }
+    k2o_ifwht64(o, hd, 0);
+    std::memcpy(out, o, hd * sizeof(float));
+}
+
 struct Act {
     std::vector<int8_t> q;
     std::vector<float> s;
@@ -203,10 +310,19 @@ K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table) {
     m->rope.assign(rope_table, rope_table + (size_t)cfg->max_seq * cfg->head_dim);
     m->layers.resize(cfg->layers);
     size_t slots = (size_t)cfg->layers * cfg->n_kv * cfg->max_seq;
-    m->k_q8.assign(slots * cfg->head_dim, 0);
-    m->v_q8.assign(slots * cfg->head_dim, 0);
-    m->k_sc.assign(slots, 0.0f);
-    m->v_sc.assign(slots, 0.0f);
+    if (m->cfg.kv_bits == 0) m->cfg.kv_bits = 8;
+    if (m->cfg.kv_bits != 8 && m->cfg.kv_bits != 4) return nullptr;
+    if (m->cfg.kv_bits == 8) {
+        m->k_q8.assign(slots * cfg->head_dim, 0);
+        m->v_q8.assign(slots * cfg->head_dim, 0);
+        m->k_sc.assign(slots, 0.0f);
+        m->v_sc.assign(slots, 0.0f);
+    } else {
+        m->k_q4.assign(slots * cfg->head_dim / 2, 0x88);
+        m->v_q4.assign(slots * cfg->head_dim / 2, 0x88);
+        m->k_s16.assign(slots * cfg->head_dim / 64, 0);
+        m->v_s16.assign(slots * cfg->head_dim / 64, 0);
+    }
     return m.release();
 }
 
@@ -256,9 +372,22 @@ void k2o_model_embed(const K2oModel *m, uint32_t token, float *out) {
 
 const float *k2o_model_tap_hidden(const K2oModel *m) { return m->tap_hidden.data(); }
 const float *k2o_model_tap_attention(const K2oModel *m) { return m->tap_attn.data(); }
+int k2o_model_read_kv_q4(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, uint8_t *k_q4, uint16_t *k_s16,
+                         uint8_t *v_q4, uint16_t *v_s16) {
+    if (!m || m->cfg.kv_bits != 4 || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;
+    const size_t slot = m->kv_slot(layer, kv_head, pos), hd = m->cfg.head_dim;
+    std::memcpy(k_q4, m->k_q4.data() + slot * hd / 2, hd / 2);
+    std::memcpy(v_q4, m->v_q4.data() + slot * hd / 2, hd / 2);
+    std::memcpy(k_s16, m->k_s16.data() + slot * (hd / 64), hd / 64 * 2);
+    std::memcpy(v_s16, m->v_s16.data() + slot * (hd / 64), hd / 64 * 2);
+    return 0;
+}
+void k2o_kv_quant_head_q4(const float *src, size_t head_dim, uint8_t *q4, uint16_t *s16) { quant_head_q4(src, head_dim, q4, s16); }
+uint8_t k2o_nf4_nearest_idx(float y) { return nf4_nearest_idx(y); }
+
 int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, int8_t *k_q8, float *k_scale,
                       int8_t *v_q8, float *v_scale) {
-    if (!m || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;
+    if (!m || m->cfg.kv_bits != 8 || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;
     const size_t slot = m->kv_slot(layer, kv_head, pos), hd = m->cfg.head_dim;
     std::memcpy(k_q8, m->k_q8.data() + slot * hd, hd);
     std::memcpy(v_q8, m->v_q8.data() + slot * hd, hd);
@@ -293,11 +422,16 @@ int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logi
         if (!c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
         for (size_t kvh = 0; kvh < c.n_kv; ++kvh) {
             size_t slot = m->kv_slot(l, kvh, pos);
-            quant_head(k + kvh * hd, hd, m->k_q8.data() + slot * hd, &m->k_sc[slot]);
-            quant_head(v + kvh * hd, hd, m->v_q8.data() + slot * hd, &m->v_sc[slot]);
+            if (c.kv_bits == 4) {
+                quant_head_q4(k + kvh * hd, hd, m->k_q4.data() + slot * hd / 2, m->k_s16.data() + slot * (hd / 64));
+                quant_head_q4(v + kvh * hd, hd, m->v_q4.data() + slot * hd / 2, m->v_s16.data() + slot * (hd / 64));
+            } else {
+                quant_head(k + kvh * hd, hd, m->k_q8.data() + slot * hd, &m->k_sc[slot]);
+                quant_head(v + kvh * hd, hd, m->v_q8.data() + slot * hd, &m->v_sc[slot]);
+            }
         }
         for (size_t qh = 0; qh < c.n_q; ++qh)
-            attend_head(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
+            (c.kv_bits == 4 ? attend_head_q4 : attend_head)(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
         if (l + 1 == c.layers) m->tap_attn = attn;
         act.populate(attn.data(), q_dim);
         L.o.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);

@@ -145,6 +145,7 @@ typedef struct K2oConfig {
     uint32_t hidden, layers, n_q, n_kv, head_dim, inter, vocab, max_seq;
     float eps;
     int32_t qk_norm_after_rope;
+    uint32_t kv_bits;   /* 8 = int8 Hadamard cache, 4 = NF4 Hadamard cache (set_kv_bits, real_llm.rs:1731-1735) */
 } K2oConfig;
 typedef struct K2oModel K2oModel;
 K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table);
@@ -165,6 +166,12 @@ int k2o_model_forward_token(K2oModel *m, uint32_t token, float *logits, size_t t
 const float *k2o_model_tap_hidden(const K2oModel *m);
 /* Attention output (before o_proj) of the last layer for the last token: [n_q * head_dim]. */
 const float *k2o_model_tap_attention(const K2oModel *m);
+/* NF4 Hadamard cache (kv_bits = 4): packed indices [head_dim / 2] and bf16 scales [head_dim / 64] of one slot. */
+int k2o_model_read_kv_q4(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, uint8_t *k_q4, uint16_t *k_s16,
+                         uint8_t *v_q4, uint16_t *v_s16);
+/* store_hadamard_q4_head_raw (real_llm.rs:8646-8701) on one head: packed NF4 indices and one bf16 scale per 64 values. */
+void k2o_kv_quant_head_q4(const float *src, size_t head_dim, uint8_t *q4, uint16_t *s16);
+uint8_t k2o_nf4_nearest_idx(float y);
 /* One KV cache slot (layer, kv head, position): int8 rotated values [head_dim] and fp32 scales. */
 int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, int8_t *k_q8, float *k_scale,
                       int8_t *v_q8, float *v_scale);

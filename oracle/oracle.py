@@ -372,7 +372,7 @@ class MatrixDesc(C.Structure):
 class Config(C.Structure):
     _fields_ = [("hidden", C.c_uint32), ("layers", C.c_uint32), ("n_q", C.c_uint32), ("n_kv", C.c_uint32),
                 ("head_dim", C.c_uint32), ("inter", C.c_uint32), ("vocab", C.c_uint32), ("max_seq", C.c_uint32),
-                ("eps", C.c_float), ("qk_norm_after_rope", C.c_int32)]
+                ("eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)]
 
 
 def desc_of(m):
@@ -414,6 +414,9 @@ def _declare_model(L):
     L.k2o_model_tap_hidden.restype, L.k2o_model_tap_hidden.argtypes = P, [P]
     L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
     L.k2o_model_read_kv.restype, L.k2o_model_read_kv.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
+    L.k2o_model_read_kv_q4.restype, L.k2o_model_read_kv_q4.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
+    L.k2o_kv_quant_head_q4.restype, L.k2o_kv_quant_head_q4.argtypes = None, [P, C.c_size_t, P, P]
+    L.k2o_nf4_nearest_idx.restype, L.k2o_nf4_nearest_idx.argtypes = C.c_uint8, [C.c_float]
     L.k2o_argmax.restype, L.k2o_argmax.argtypes = C.c_uint32, [P, C.c_size_t]
     L.k2o_build_rope_table.restype, L.k2o_build_rope_table.argtypes = None, [C.c_size_t, C.c_size_t, C.c_double, P]
     L.k2o_exp_poly.restype, L.k2o_exp_poly.argtypes = C.c_float, [C.c_float]
@@ -455,6 +458,19 @@ def head_rms_norm(buf, heads, head_dim, w, eps):
     return b
 
 
+def kv_quant_head_q4(src):
+    L = lib(); _declare_model(L)
+    x = _c(src, np.float32)
+    q4, s16 = np.zeros(x.size // 2, np.uint8), np.zeros(x.size // 64, np.uint16)
+    L.k2o_kv_quant_head_q4(_ptr(x), x.size, _ptr(q4), _ptr(s16))
+    return q4, s16
+
+
+def nf4_nearest_idx(y):
+    L = lib(); _declare_model(L)
+    return int(L.k2o_nf4_nearest_idx(float(y)))
+
+
 def kv_quant_head(src):
     L = lib(); _declare_model(L)
     s = _c(src, np.float32)
@@ -478,7 +494,7 @@ class Model:
         self.L, self.spec = L, spec
         c = spec["cfg"]
         self.cfg = Config(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"], c["max_seq"],
-                          c["eps"], int(c.get("qk_norm_after_rope", 0)))
+                          c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
         rope = _c(spec["rope"], np.float32)
         self.h = L.k2o_model_new(C.byref(self.cfg), _ptr(rope))
         assert self.h, "k2o_model_new failed"
@@ -532,6 +548,11 @@ class Model:
 
     def read_kv(self, layer, kv_head, pos):
         hd = self.cfg.head_dim
+        if self.cfg.kv_bits == 4:
+            k, v = np.zeros(hd // 2, np.uint8), np.zeros(hd // 2, np.uint8)
+            ks, vs = np.zeros(hd // 64, np.uint16), np.zeros(hd // 64, np.uint16)
+            assert self.L.k2o_model_read_kv_q4(self.h, layer, kv_head, pos, _ptr(k), _ptr(ks), _ptr(v), _ptr(vs)) == 0
+            return k, ks, v, vs
         k, v = np.zeros(hd, np.int8), np.zeros(hd, np.int8)
         ks, vs = np.zeros(1, np.float32), np.zeros(1, np.float32)
         assert self.L.k2o_model_read_kv(self.h, layer, kv_head, pos, _ptr(k), _ptr(ks), _ptr(v), _ptr(vs)) == 0

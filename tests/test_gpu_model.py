@@ -74,6 +74,31 @@ def test_prompt_logits_and_kv(ctx, oracle, mode, kw):
         eng.close(); ref.close()
 
 
+@pytest.mark.parametrize("cfg,mode,kw", [(km.TINY, "b4", {}), (km.TINY, "nf4g128", dict(qkv_bias=True, qk_norm=True)),
+                                         (dict(hidden=256, layers=2, n_q=4, n_kv=2, head_dim=128, inter=512, vocab=512, max_seq=80, eps=1e-6, theta=1e6),
+                                          "b5", dict(qk_norm=True))])
+def test_nf4_kv_cache_logits_and_entries(ctx, oracle, cfg, mode, kw, decode_path):
+    """kv_bits = 4: NF4 Hadamard cache (refined bf16 scale per 64 values).  Entries, logits and greedy tokens are identical."""
+    cfg = dict(cfg, kv_bits=4)
+    spec, eng, ref = make(ctx, oracle, cfg, mode, seed=13, **kw)
+    try:
+        rng = np.random.Generator(np.random.PCG64(5))
+        tokens = [int(t) for t in rng.integers(0, cfg["vocab"], 45)]
+        want = np.stack([ref.forward_token(t, threads=2) for t in tokens])
+        got = eng.forward_token_ids(tokens, want_all=True)
+        assert np.array_equal(got, want)
+        for l in range(cfg["layers"]):
+            for pos in (0, 1, 31, 44):
+                for kvh in range(cfg["n_kv"]):
+                    g, w = eng.read_kv(l, kvh, pos), ref.read_kv(l, kvh, pos)
+                    assert all(np.array_equal(a, b) for a, b in zip(g, w)), (l, pos, kvh)
+        assert eng.kv_bytes(10) == 10 * 2 * cfg["layers"] * cfg["n_kv"] * (cfg["head_dim"] // 2 + 2 * (cfg["head_dim"] // 64))
+        ref.reset()
+        _greedy_check(eng, ref, tokens[:6], 25)
+    finally:
+        eng.close(); ref.close()
+
+
 def test_host_embeddings_equal_device_lookup(ctx, oracle):
     spec, eng, ref = make(ctx, oracle, km.TINY, "b5", seed=4)
     try:

@@ -101,3 +101,55 @@ def test_model_helpers(oracle):
     assert oracle.argmax(np.array([1, 5, 5, 2], np.float32)) == 1
     q, s = oracle.kv_quant_head(v[:64])
     assert np.abs(q).max() == 127 and s > 0
+
+
+# ----------------------------------------------------------------------------- NF4 Hadamard KV cache (kv_bits = 4)
+NF4 = np.array([-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127], np.float32)
+
+
+def test_nf4_nearest_idx_is_the_nearest_centroid(oracle):
+    ys = np.concatenate([np.linspace(-140, 140, 2801, dtype=np.float32), NF4, (NF4[:-1] + NF4[1:]) / 2])
+    for y in ys:
+        idx = oracle.nf4_nearest_idx(y)
+        best = np.abs(NF4 - y).min()
+        assert abs(NF4[idx] - y) == best, (y, idx)             # ties at the midpoints may go either way
+    assert oracle.nf4_nearest_idx(0.0) == 8 and oracle.nf4_nearest_idx(-0.0) == 8 and oracle.nf4_nearest_idx(-1e-3) == 7
+
+
+def test_q4_head_quantizer_layout_and_error(oracle):
+    from k2t_rng import normal
+    for hd in (64, 128):
+        x = normal(hd, hd) * np.float32(0.7)
+        q4, s16 = oracle.kv_quant_head_q4(x)
+        assert q4.size == hd // 2 and s16.size == hd // 64
+        rot = oracle.fwht64(x)                                 # block index = group within the head
+        for g in range(hd // 64):
+            scale = (np.uint32(s16[g]) << 16).view(np.float32)
+            blk = rot[g * 64:(g + 1) * 64]
+            deq = np.zeros(64, np.float32)
+            for h in range(2):
+                for i in range(16):
+                    b = q4[g * 32 + h * 16 + i]
+                    deq[h * 32 + i], deq[h * 32 + 16 + i] = NF4[b & 15] * scale, NF4[b >> 4] * scale
+            # every index is the nearest centroid at the stored scale, and the scale is the bf16 least-squares fit
+            for j in range(64):
+                assert abs(deq[j] - blk[j]) <= np.abs(NF4 * scale - blk[j]).min() + 1e-7
+            assert np.linalg.norm(deq - blk) / np.linalg.norm(blk) < 0.12
+    z, s = oracle.kv_quant_head_q4(np.zeros(64, np.float32))
+    assert s[0] == 0 and (z == 0x88).all()                     # an all-zero group: scale 0, indices 8|8
+
+
+def test_oracle_q4_cache_tracks_int8_cache_and_byte_count(oracle):
+    cfg4 = dict(km.TINY, kv_bits=4)
+    spec4, spec8 = km.build(oracle, cfg4, "b5", seed=3), km.build(oracle, km.TINY, "b5", seed=3)
+    m4, m8 = oracle.Model(spec4), oracle.Model(spec8)
+    for t in [5, 17, 300, 42, 7, 199]:
+        a, b = m4.forward_token(t, 2), m8.forward_token(t, 2)
+        assert np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)) > 0.985
+    k, ks, v, vs = m4.read_kv(1, 1, 3)
+    assert k.dtype == np.uint8 and k.size == 32 and ks.size == 1
+    m4.close(); m8.close()
+    # KV bytes per token of the 135M shape: 12,240 (int8) and 6,120 (NF4), as published with the reference's benchmarks
+    c = km.SMOL_135M
+    assert 2 * c["layers"] * c["n_kv"] * (c["head_dim"] + 4) == 12240
+    assert 2 * c["layers"] * c["n_kv"] * (c["head_dim"] // 2 + 2 * (c["head_dim"] // 64)) == 6120
