@@ -212,6 +212,8 @@ __device__ __noinline__ void mega_gemv(const MegaMatrix *mm, float *out, const M
         case FMT_BP6: mega_gemv_fmt<FMT_BP6>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
         case FMT_NF4: mega_gemv_fmt<FMT_NF4>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
         case FMT_NF3: mega_gemv_fmt<FMT_NF3>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
+        case FMT_NF5: mega_gemv_fmt<FMT_NF5>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
+        case FMT_E8Q2: mega_gemv_fmt<FMT_E8Q2>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
         default: mega_gemv_fmt<FMT_NF4G>(mm, s.xq, s.xs, s.xm, out, t, ps); break;
     }
 }

@@ -57,6 +57,13 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// E8Q2 even-coset templates (simd_lut.rs:4354-4383): four magnitudes per entry, packed little-endian.  The decode
+// reads them from shared memory (28 words in 28 banks: lanes with different entries do not conflict).
+__constant__ uint32_t E8Q2_TEMPLATE_WORDS[28] = {
+    0x00000000u, 0x00002020u, 0x00200020u, 0x20000020u, 0x00202000u, 0x20002000u, 0x20200000u, 0x00000040u, 0x00004000u, 0x00400000u,
+    0x40000000u, 0x20202020u, 0x00000020u, 0x00002000u, 0x00200000u, 0x20000000u, 0x00202020u, 0x20002020u, 0x20200020u, 0x20202000u,
+    0x00000060u, 0x00006000u, 0x00600000u, 0x60000000u, 0x20202040u, 0x20204020u, 0x20402020u, 0x40202020u};
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
 
 // Streaming 128-bit load that does not allocate in L1 (weights are read exactly once).

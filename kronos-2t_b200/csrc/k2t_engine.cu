@@ -323,14 +323,12 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         L.down = L.gate_up ? kronos_cuda_matrix_upload(ctx, &d.down_proj, 0) : nullptr;
         if (!L.down) return bad("engine_create: layer " + std::to_string(l) + ": " + ctx->err);
         for (KronosCudaMatrix *m : {L.qkv, L.o, L.gate_up, L.down}) {
-            if (m->dm.geom.fmt == FMT_NF5 || m->dm.geom.fmt == FMT_E8Q2) return bad("engine_create: NF5 / E8Q2 projections are not implemented");
             e->weight_bytes += m->dm.geom.file_bytes;
         }
     }
     if (!shape_ok(*lm_head, c.vocab_size, h)) return bad("engine_create: lm_head shape does not match the config");
     e->lm_head = kronos_cuda_matrix_upload(ctx, lm_head, 0);
     if (!e->lm_head) return bad("engine_create: lm_head: " + ctx->err);
-    if (e->lm_head->dm.geom.fmt == FMT_NF5 || e->lm_head->dm.geom.fmt == FMT_E8Q2) return bad("engine_create: NF5 / E8Q2 lm_head is not implemented");
     e->weight_bytes += e->lm_head->dm.geom.file_bytes;
     const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * c.max_seq_len;
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;

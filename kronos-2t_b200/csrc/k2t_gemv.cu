@@ -57,7 +57,6 @@ uint32_t gemv_max_tokens(const DeviceMatrix &) { return 4; }
 // (FMT_NF4G for an NF4 codebook the two-table decode cannot represent), or -1 when unsupported.
 int fill_gemv_args(const DeviceMatrix &m, bool has_xsum, GemvArgs &a) {
     const MatrixGeom &g = m.geom;
-    if (g.fmt == FMT_NF5 || g.fmt == FMT_E8Q2) return -1;
     for (int k = 0; k < 3; ++k) { a.plane[k] = m.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; }
     a.scales = reinterpret_cast<const uint16_t *>(m.d_base + g.scale_off);
     a.xq = nullptr; a.xs = nullptr; a.xsum = nullptr; a.out = nullptr; a.int_dots = nullptr; a.err_flag = nullptr;
@@ -87,6 +86,8 @@ uint32_t gemv_warp_smem_bytes(int fmt_index) {
         case FMT_NF4: return warp_smem<FMT_NF4>(1);
         case FMT_NF3: return warp_smem<FMT_NF3>(1);
         case FMT_NF4G: return warp_smem<FMT_NF4G>(1);
+        case FMT_NF5: return warp_smem<FMT_NF5>(1);
+        case FMT_E8Q2: return warp_smem<FMT_E8Q2>(1);
         default: return 0;
     }
 }
@@ -111,6 +112,8 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
         case FMT_NF4: e = launch_fmt<FMT_NF4>(stream, a, nt, sm_count); break;
         case FMT_NF4G: e = launch_fmt<FMT_NF4G>(stream, a, nt, sm_count); break;
         case FMT_NF3: e = launch_fmt<FMT_NF3>(stream, a, nt, sm_count); break;
+        case FMT_NF5: e = launch_fmt<FMT_NF5>(stream, a, nt, sm_count); break;
+        case FMT_E8Q2: e = launch_fmt<FMT_E8Q2>(stream, a, nt, sm_count); break;
         default: return cudaErrorNotSupported;
     }
     if (e == cudaSuccess && launches) *launches = 1;

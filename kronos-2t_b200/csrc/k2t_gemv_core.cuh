@@ -58,6 +58,15 @@ template <int FMT> struct Cell { static constexpr int B0 = 16, B1 = 16, B2 = 0; 
 template <> struct Cell<FMT_BP5> { static constexpr int B0 = 16, B1 = 16, B2 = 8; };
 template <> struct Cell<FMT_BP6> { static constexpr int B0 = 16, B1 = 16, B2 = 16; };
 template <> struct Cell<FMT_NF3> { static constexpr int B0 = 16, B1 = 8, B2 = 0; };
+template <> struct Cell<FMT_NF5> { static constexpr int B0 = 16, B1 = 16, B2 = 8; };
+template <> struct Cell<FMT_E8Q2> { static constexpr int B0 = 16, B1 = 0, B2 = 0; };
+
+__device__ __forceinline__ uint32_t *e8q2_templates_smem() {
+    __shared__ uint32_t tab[32];
+    return tab;
+}
+// four flag bits (bit i -> byte i) as a byte mask 0xFF / 0x00
+__device__ __forceinline__ uint32_t spread4(uint32_t bits4) { return ((bits4 * 0x00204081u) & 0x01010101u) * 0xFFu; }
 
 template <int FMT>
 struct Raw {
@@ -117,6 +126,43 @@ __device__ __forceinline__ void decode(const Raw<FMT> &w, const uint32_t (&cb)[8
             s = lop3_or_and(s, w.w[3 * h + 2] >> 1, 0x44444444u);
             u[12 + 2 * h] = prmt(cb[0], cb[1], s);
             u[13 + 2 * h] = prmt(cb[0], cb[1], s >> 16);
+        }
+    } else if (FMT == FMT_NF5) {
+        // 32-entry codebook: bits 0..3 in the nibbles of words 0..7 (as NF4), bit 4 of column 4j+b at bit j of byte b of
+        // word 8 (columns 0..31) / 9 (columns 32..63), as for b5
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = w.w[i];
+            const uint32_t lo3 = x & 0x77777777u, hb = x & 0x88888888u, hs = hb << 4, lo3h = lo3 >> 16;
+            const uint32_t m0 = prmt(hs, hb, 0xD9C8u), m1 = prmt(hs, hb, 0xFBEAu);          // byte masks: index bit 3
+            const uint32_t hw = w.w[8 + i / 4];
+            const int j0 = 2 * (i % 4), j1 = j0 + 1;
+            const uint32_t t0 = ((j0 <= 4 ? (hw << (4 - j0)) : (hw >> (j0 - 4))) & 0x10101010u) >> 4;
+            const uint32_t t1 = ((j1 <= 4 ? (hw << (4 - j1)) : (hw >> (j1 - 4))) & 0x10101010u) >> 4;
+            const uint32_t b0 = t0 * 0xFFu, b1 = t1 * 0xFFu;                                   // byte masks: index bit 4
+            const uint32_t a0 = lop3_select(prmt(cb[0], cb[1], lo3), prmt(cb[2], cb[3], lo3), m0);
+            const uint32_t c0 = lop3_select(prmt(cb[4], cb[5], lo3), prmt(cb[6], cb[7], lo3), m0);
+            const uint32_t a1 = lop3_select(prmt(cb[0], cb[1], lo3h), prmt(cb[2], cb[3], lo3h), m1);
+            const uint32_t c1 = lop3_select(prmt(cb[4], cb[5], lo3h), prmt(cb[6], cb[7], lo3h), m1);
+            u[2 * i] = lop3_select(a0, c0, b0);
+            u[2 * i + 1] = lop3_select(a1, c1, b1);
+        }
+    } else if (FMT == FMT_E8Q2) {
+        // e8q2_decode_8d (simd_lut.rs:4385-4459): byte 2b = template, 2b+1 = signs of columns 8b..8b+7
+        const uint32_t *tab = e8q2_templates_smem();
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const uint32_t pair = (w.w[b / 2] >> (16 * (b % 2))) & 0xFFFFu, tpl = pair & 0xFFu, sgn = pair >> 8;
+            const bool even = (__popc(tpl ^ sgn) & 1) != 0;
+            const uint32_t tu = tpl & 15u, tv = tpl >> 4;
+            const uint32_t ui = (tu < 12u && tv >= 12u) ? 16u + tu : tu, vi = (tv < 12u && tu >= 12u) ? 16u + tv : tv;
+            // odd coset: magnitude 16 or 48 per column; even coset: two template entries (indices stay below 28 for
+            // every byte pair the packer emits; masked so that a stray pair cannot read outside the table)
+            const uint32_t mu = even ? tab[ui & 31u] : ((spread4(tu) & 0x20202020u) + 0x10101010u);
+            const uint32_t mv = even ? tab[vi & 31u] : ((spread4(tv) & 0x20202020u) + 0x10101010u);
+            const uint32_t su = spread4(sgn & 15u), sv = spread4(sgn >> 4);
+            u[2 * b] = __vsub4(mu & ~su, mu & su);          // per byte: +m or -m
+            u[2 * b + 1] = __vsub4(mv & ~sv, mv & sv);
         }
     }
 }
@@ -271,6 +317,11 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
                                           uint32_t bar_id, PipeState &ps) {
     using St = Stage<FMT>;
     const uint32_t lane = threadIdx.x & 31;
+    if (FMT == FMT_E8Q2) {          // every warp fills the (same) table itself, so no CTA-wide barrier is needed
+        uint32_t *tab = e8q2_templates_smem();
+        tab[lane] = lane < 28 ? E8Q2_TEMPLATE_WORDS[lane] : 0u;
+        __syncwarp();
+    }
     const uint32_t n_rb = (a.rows + RS - 1) / RS;              // 4-row blocks of the matrix
     const uint32_t J = gw < n_rb ? (n_rb - gw + nw - 1) / nw : 0;   // blocks of this CTA: gw, gw + nw, ...
     const uint32_t np = (a.nc + 31) / 32;

@@ -57,6 +57,18 @@ __device__ __forceinline__ float cell_value(const EmbedArgs &a, uint32_t row, ui
         }
         return __fmul_rn((float)(2 * (int)u - a.max_odd), delta);
     }
+    if (a.fmt == FMT_E8Q2) {      // e8q2_decode_8d on the (template, sign) pair of the column's 8-column block
+        const uint32_t blk = col / 8, i = col % 8, tpl = p0[2 * blk], sgn = p0[2 * blk + 1];
+        int mag;
+        if ((__popc(tpl ^ sgn) & 1) != 0) {
+            const uint32_t tu = tpl & 15u, tv = tpl >> 4;
+            const uint32_t ui = (tu < 12u && tv >= 12u) ? 16u + tu : tu, vi = (tv < 12u && tu >= 12u) ? 16u + tv : tv;
+            mag = (int)((E8Q2_TEMPLATE_WORDS[i < 4 ? ui : vi] >> (8 * (i % 4))) & 0xFFu);
+        } else {
+            mag = ((tpl >> i) & 1u) ? 48 : 16;
+        }
+        return __fmul_rn((float)(((sgn >> i) & 1u) ? -mag : mag), delta);
+    }
     uint32_t idx;
     if (a.fmt == FMT_NF3) {
         auto word = [&](uint32_t w) { return w < 4 ? reinterpret_cast<const uint32_t *>(p0)[w] : reinterpret_cast<const uint32_t *>(p1)[w - 4]; };
@@ -70,6 +82,10 @@ __device__ __forceinline__ float cell_value(const EmbedArgs &a, uint32_t row, ui
         const uint8_t *half = col < 32 ? p0 : p1;
         const uint32_t cc = col % 32, nib = col % 8;
         idx = (half[(cc / 8) * 4 + nib / 2] >> (4 * (nib % 2))) & 0x0F;
+        if (a.fmt == FMT_NF5) {
+            const uint32_t bit = 8 * (col % 4) + cc / 4;
+            idx |= ((p2[(col / 32) * 4 + bit / 8] >> (bit % 8)) & 1u) << 4;
+        }
     }
     return __fmul_rn((float)a.codebook[idx], delta);
 }

@@ -12,6 +12,15 @@ SMOL_135M = dict(hidden=576, layers=30, n_q=9, n_kv=3, head_dim=64, inter=1536, 
 def quantize(oracle, w, mode):
     if mode.startswith("b"):
         return oracle.bipolar_quantize_rtn(w, int(mode[1]))
+    if mode.startswith("e8q2"):
+        # no lattice quantizer here: random E8 codewords with scales that keep the outputs at the size of w @ x
+        rows, cols = w.shape
+        sgc = 2 if mode.endswith("g128") and (cols // 64) % 2 == 0 else 1
+        rng = np.random.Generator(np.random.PCG64(int(abs(float(w[0, 0])) * 1e9) % (1 << 31)))
+        tpl = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+        sgn = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+        sc = rng.integers(0x3A00, 0x3A80, oracle.lib().k2o_nf_scale_count(rows, cols, sgc)).astype(np.uint16)    # ~5e-4
+        return oracle.e8q2_pack(tpl, sgn, sc, sgc)
     bits = int(mode[2])
     return oracle.nf_quantize_rtn(w, bits, 2 if mode.endswith("g128") else 1)
 

@@ -120,6 +120,31 @@ def test_nf4_arbitrary_codebooks(ctx, oracle, cb, rows, cols):
     _check_gemv(ctx, oracle, m, normal(7, cols))
 
 
+NF5_POS = [3, 8, 13, 19, 24, 30, 36, 42, 49, 56, 64, 72, 82, 93, 107, 127]      # the reference's default NF5 magnitudes
+
+
+@pytest.mark.parametrize("cb", [NF5_POS, [1, -2, 5, 9, 17, 21, 33, 40, 41, 59, 70, 77, 90, 100, 120, 127]])
+@pytest.mark.parametrize("sgc,rows,cols", [(1, 71, 192), (2, 128, 576), (2, 1536, 2048)])
+def test_nf5_gemv_bit_exact(ctx, oracle, cb, sgc, rows, cols):
+    """5-bit codebook: index bit 4 picks the sign half of the mirrored 32-entry table (nf_expand_codebook32)."""
+    m = random_nf(oracle, rows + sgc, rows, cols, 5, sgc, np.array(cb, np.int8))
+    _check_gemv(ctx, oracle, m, normal(rows + cols, cols))
+    _check_gemv(ctx, oracle, m, normal(3, (3, cols)))
+
+
+@pytest.mark.parametrize("sgc,rows,cols", [(2, 71, 128), (2, 256, 1536), (1, 960, 576), (2, 3072, 2048)])
+def test_e8q2_gemv_bit_exact(ctx, oracle, sgc, rows, cols):
+    """E8 lattice codewords, 2 bits per weight: every (template, sign) byte pair, both cosets."""
+    rng = np.random.Generator(np.random.PCG64(rows))
+    tpl = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+    sgn = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+    tpl[0, :8], sgn[0, :8] = 0, 1                                   # the padding codeword (decodes to zeros)
+    sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, sgc)).astype(np.uint16)
+    m = oracle.e8q2_pack(tpl, sgn, sc, sgc)
+    _check_gemv(ctx, oracle, m, normal(rows + 1, cols))
+    _check_gemv(ctx, oracle, m, normal(rows + 2, (4, cols)))
+
+
 @pytest.mark.parametrize("n_tok", [2, 3, 4, 7, 8, 15])
 def test_batch_gemv_matches_oracle(ctx, oracle, n_tok):
     # batch forms: same per-(row, token) arithmetic as the single-token kernel

@@ -48,6 +48,8 @@ VARIANTS = [
     ("nf4g128", dict(qk_norm=True)),
     ("nf4", dict(tied=False)),
     ("nf3g128", {}),
+    ("nf5g128", dict(qkv_bias=True)),
+    ("e8q2g128", {}),
     ("b4", dict(modes=dict(qkv="b5", o="b5", gate_up="b4", down="b5", head="b4"))),      # the p55454-style mix
 ]
 
