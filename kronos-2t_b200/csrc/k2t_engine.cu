@@ -37,6 +37,7 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    uint32_t last_row = 0;                    // row of `hidden` that holds the last forwarded token (prompt batches)
     bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
     size_t weight_bytes = 0;
     std::vector<void *> allocs;
@@ -67,10 +68,12 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
     return cuda_ok(e->ctx, cudaMemsetAsync(p, 0, bytes, e->ctx->stream), "clear");
 }
 
-bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out) {
+// y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
+bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, uint32_t n_tok = 1, size_t act_tok0 = 0) {
     uint32_t launched = 0;
-    cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q, e->act_s, e->act_m, 1, out, m->dm.geom.rows, nullptr,
-                                  e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
+    const size_t cols = m->dm.geom.cols, nc = cols / 64;
+    cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q + act_tok0 * cols, e->act_s + act_tok0 * nc, e->act_m + act_tok0 * nc, n_tok, out,
+                                  m->dm.geom.rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
     e->ctx->launches += launched;
     return cuda_ok(e->ctx, err, "engine gemv");
 }
@@ -82,57 +85,77 @@ bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 
 
 void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a);
 
-// Queues the kernels of one token on the context's stream.  `embed`: look d_token up first.
-// `greedy`: finish with argmax (next token, history, step, position); otherwise only advance the position.
-bool enqueue_step(KronosCudaEngine *e, bool embed, bool greedy, bool long_ctx) {
+constexpr uint32_t MAX_BATCH = 4;      // tokens per weight pass in prompt processing (the reference's 4-token tiles)
+
+enum class Tail { Greedy, LastLogits, AllLogits, None };
+
+// Queues the kernels of a batch of T <= 4 consecutive tokens on the context's stream (T = 1: one decode step).
+// `embed`: look the T tokens of d_token up first (otherwise `hidden` already holds the T embeddings).  Every
+// projection reads its weights once for the whole batch (small-N GEMM); attention runs token by token because
+// token t attends to the keys of the tokens before it in the same batch.  `tail`: Greedy = lm_head + argmax for
+// the (single) token; LastLogits = lm_head for the last token of the batch; AllLogits = for all T; None = no lm_head.
+// The position word is advanced by T at the end (by the argmax kernel when Greedy).
+bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool long_ctx) {
     const KronosCudaEngineConfig &c = e->cfg;
     cudaStream_t s = e->ctx->stream;
-    const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd;
+    const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd, inter = c.intermediate_size;
+    const uint32_t qkv_rows = q_dim + 2 * c.num_key_value_heads * hd;
     if (embed) {
         EmbedArgs a{};
         fill_embed_args(e, a);
-        if (!count(e, launch_embed(s, a, false), "embed")) return false;
+        if (!count(e, launch_embed(s, a, T, false), "embed")) return false;
     }
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const EngineLayer &L = e->layers[l];
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, l == 0 ? nullptr : e->proj, L.input_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl && (embed || l > 0)), "rmsnorm")) return false;
-        if (!gemv(e, L.qkv, e->qkv)) return false;
-        if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
-            FusedAttnArgs fa{};
-            fa.qkv = e->qkv; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope; fa.pos = e->d_pos;
-            fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
-            fa.attn_tap = l + 1 == c.num_layers ? e->attn_tap : nullptr;
-            fa.out_q = e->act_q; fa.out_scales = e->act_s; fa.out_sums = e->act_m; fa.err_flag = e->ctx->d_err;
-            fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
-            fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
-            fa.kv_bits = c.kv_bits;
-            if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
-        } else {
-            QkvPostArgs qa{};
-            qa.qkv = e->qkv; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope; qa.pos = e->d_pos;
-            qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
-            qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
-            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope;
-            if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
-            AttnArgs aa{};
-            aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
-            aa.pos = e->d_pos; aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = l + 1 == c.num_layers ? e->attn_tap : nullptr;
-            aa.out_q = e->act_q; aa.out_scales = e->act_s; aa.out_sums = e->act_m;
-            aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
-            aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
-            if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
+        if (!count(e, launch_rmsnorm_quant(s, e->hidden, l == 0 ? nullptr : e->proj, L.input_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl && (embed || l > 0)), "rmsnorm")) return false;
+        if (!gemv(e, L.qkv, e->qkv, T)) return false;
+        for (uint32_t t = 0; t < T; ++t) {      // the attention output of token t becomes row t of the o_proj activation
+            float *qkv_t = e->qkv + (size_t)t * qkv_rows;
+            int8_t *oq = e->act_q + (size_t)t * q_dim;
+            float *os = e->act_s + (size_t)t * (q_dim / 64);
+            int32_t *om = e->act_m + (size_t)t * (q_dim / 64);
+            float *tap = (l + 1 == c.num_layers && t + 1 == T) ? e->attn_tap : nullptr;
+            if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
+                FusedAttnArgs fa{};
+                fa.qkv = qkv_t; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope;
+                fa.pos = e->d_pos; fa.pos_offset = t;
+                fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
+                fa.attn_tap = tap;
+                fa.out_q = oq; fa.out_scales = os; fa.out_sums = om; fa.err_flag = e->ctx->d_err;
+                fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
+                fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
+                fa.kv_bits = c.kv_bits;
+                if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
+            } else {
+                QkvPostArgs qa{};
+                qa.qkv = qkv_t; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope;
+                qa.pos = e->d_pos; qa.pos_offset = t;
+                qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
+                qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
+                qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope;
+                if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
+                AttnArgs aa{};
+                aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
+                aa.pos = e->d_pos; aa.pos_offset = t;
+                aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
+                aa.out_q = oq; aa.out_scales = os; aa.out_sums = om;
+                aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
+                aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
+                if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
+            }
         }
-        if (!gemv(e, L.o, e->proj)) return false;
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl), "rmsnorm")) return false;
-        if (!gemv(e, L.gate_up, e->gate_up)) return false;
-        if (!count(e, launch_swiglu_quant(s, e->gate_up, c.intermediate_size, e->act_q, e->act_s, e->act_m, nullptr, e->pdl), "swiglu")) return false;
-        if (!gemv(e, L.down, e->proj)) return false;
+        if (!gemv(e, L.o, e->proj, T)) return false;
+        if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
+        if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
+        if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, T, e->pdl), "swiglu")) return false;
+        if (!gemv(e, L.down, e->proj, T)) return false;
     }
-    if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->pdl), "rmsnorm")) return false;
-    if (!gemv(e, e->lm_head, e->logits)) return false;
-    (void)q_dim;
-    if (greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
-    return count(e, launch_advance_pos(s, e->d_pos, e->pdl), "advance");
+    // the last residual is folded into `hidden` by the final norm even when no logits are wanted
+    if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
+    if (tail == Tail::AllLogits || tail == Tail::Greedy) { if (!gemv(e, e->lm_head, e->logits, T)) return false; }
+    else if (tail == Tail::LastLogits) { if (!gemv(e, e->lm_head, e->logits, 1, T - 1)) return false; }
+    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
+    return count(e, launch_advance_pos(s, e->d_pos, T, e->pdl), "advance");
 }
 
 bool set_u32(KronosCudaEngine *e, uint32_t *dst, uint32_t v) {
@@ -145,11 +168,13 @@ bool ensure_graphs(KronosCudaEngine *e) {
     KronosCudaContext *ctx = e->ctx;
     if (e->graphs[0] && e->graph_stream == ctx->stream) return true;
     for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
-    // eager steps first (position 0, token 0; callers set both before every replay): loads every kernel
-    // and sets its attributes outside a capture, where an error is also easier to attribute
+    // eager steps first: loads every kernel and sets its attributes outside a capture, where an error is also
+    // easier to attribute.  They run token 0 at the LAST position of the cache: that slot is only ever read after a
+    // real token has been written to it, so a prompt already in the cache is not disturbed (callers set position
+    // and token before every replay).
     const int variants = e->cfg.kv_bits == 8 ? 2 : 1;       // the split-KV (long context) kernels read the int8 cache only
     for (int long_ctx = 0; long_ctx < variants; ++long_ctx)
-        if (!set_u32(e, e->d_pos, 0) || !set_u32(e, e->d_token, 0) || !enqueue_step(e, true, true, long_ctx != 0) ||
+        if (!set_u32(e, e->d_pos, e->cfg.max_seq_len - 1) || !set_u32(e, e->d_token, 0) || !enqueue_batch(e, 1, true, Tail::Greedy, long_ctx != 0) ||
             !sync_and_check(ctx, "engine warm-up step"))
             return false;
     const uint64_t launches_before = ctx->launches;
@@ -157,7 +182,7 @@ bool ensure_graphs(KronosCudaEngine *e) {
         if ((which & 1) && variants == 1) continue;
         cudaGraph_t graph = nullptr;
         if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return false;
-        const bool ok = enqueue_step(e, true, which < 2, (which & 1) != 0);
+        const bool ok = enqueue_batch(e, 1, true, which < 2 ? Tail::Greedy : Tail::LastLogits, (which & 1) != 0);
         cudaError_t err = cudaStreamEndCapture(ctx->stream, &graph);
         if (!ok || !cuda_ok(ctx, err, "end capture")) { if (graph) cudaGraphDestroy(graph); return false; }
         cudaGraphExec_t exec = nullptr;
@@ -334,16 +359,18 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
               (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)c.vocab_size * h, embed_bf16)) &&
-              dev_alloc(e, e->hidden, h) && dev_alloc(e, e->proj, h) && dev_alloc(e, e->qkv, qkv_rows) &&
-              dev_alloc(e, e->gate_up, (size_t)2 * inter) && dev_alloc(e, e->logits, c.vocab_size) &&
-              dev_alloc(e, e->act_q, act_n) && dev_alloc(e, e->act_s, act_n / 64) && dev_alloc(e, e->act_m, act_n / 64) &&
+              // per-token vectors hold MAX_BATCH tokens (prompt batches), [token][n]
+              dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
+              dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
+              dev_alloc(e, e->logits, (size_t)MAX_BATCH * c.vocab_size) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
+              dev_alloc(e, e->act_s, (size_t)MAX_BATCH * act_n / 64) && dev_alloc(e, e->act_m, (size_t)MAX_BATCH * act_n / 64) &&
               dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
               dev_alloc(e, e->k_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) &&
               dev_alloc(e, e->k_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
-              dev_alloc(e, e->d_token, 1) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
+              dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
     if (!setup_mega(e)) return bad(ctx->err);
@@ -365,7 +392,8 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *e, float *hidden) {
     ctx->err.clear();
     if (!make_current(ctx)) return -1;
     // the final norm kernel has already folded the last down_proj into the residual stream
-    if (!cuda_ok(ctx, cudaMemcpyAsync(hidden, e->hidden, (size_t)e->cfg.hidden_size * 4, cudaMemcpyDeviceToHost, ctx->stream), "read hidden") ||
+    if (!cuda_ok(ctx, cudaMemcpyAsync(hidden, e->hidden + (size_t)e->last_row * e->cfg.hidden_size, (size_t)e->cfg.hidden_size * 4,
+                                      cudaMemcpyDeviceToHost, ctx->stream), "read hidden") ||
         !sync_and_check(ctx, "read hidden"))
         return -1;
     return 0;
@@ -449,25 +477,40 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     if (e->cfg.kv_bits == 4 && pos_start + n_tok > ATTN_EXACT_CTX)
         return fail(ctx, "forward: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (!make_current(ctx)) return -1;
-    if (tokens) {
+    if (tokens)
         for (size_t t = 0; t < n_tok; ++t)
             if (tokens[t] >= e->cfg.vocab_size) return fail(ctx, "forward: token id out of range"), -1;
-        if (!ensure_graphs(e)) return -1;
-    }
-    if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
     const size_t h = e->cfg.hidden_size, v = e->cfg.vocab_size;
-    for (size_t t = 0; t < n_tok; ++t) {
+    if (tokens && n_tok == 1) {         // one decode step: the captured graph
+        if (!ensure_graphs(e) || !set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
+        if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens, 4, cudaMemcpyHostToDevice, ctx->stream), "copy token") ||
+            !cuda_ok(ctx, cudaGraphLaunch(step_graph(e, false, pos_start), ctx->stream), "graph launch"))
+            return -1;
+        ctx->launches += step_launches(e, pos_start);
+        e->last_row = 0;
+        if (!cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits") ||
+            !sync_and_check(ctx, "forward"))
+            return -1;
+        if (all_logits) std::memcpy(all_logits, last_logits, v * 4);
+        return 0;
+    }
+    // prompt: batches of up to MAX_BATCH tokens per weight pass (forward_prompt / forward_batch_sdot_impl,
+    // real_llm.rs:7407-7448, 7450-7860)
+    if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
+    for (size_t t0 = 0; t0 < n_tok; t0 += MAX_BATCH) {
+        const uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
+        const bool last = t0 + T == n_tok;
         if (tokens) {
-            if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens + t, 4, cudaMemcpyHostToDevice, ctx->stream), "copy token")) return -1;
-            if (!cuda_ok(ctx, cudaGraphLaunch(step_graph(e, false, pos_start + t), ctx->stream), "graph launch")) return -1;
-            ctx->launches += step_launches(e, pos_start + t);
+            if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens + t0, T * 4, cudaMemcpyHostToDevice, ctx->stream), "copy tokens")) return -1;
         } else {
-            if (!cuda_ok(ctx, cudaMemcpyAsync(e->hidden, embeds + t * h, h * 4, cudaMemcpyHostToDevice, ctx->stream), "copy embedding")) return -1;
-            if (!enqueue_step(e, false, false, pos_start + t + 1 > ATTN_EXACT_CTX)) return -1;
+            if (!cuda_ok(ctx, cudaMemcpyAsync(e->hidden, embeds + t0 * h, (size_t)T * h * 4, cudaMemcpyHostToDevice, ctx->stream), "copy embeddings")) return -1;
         }
-        float *dst = all_logits ? all_logits + t * v : (t + 1 == n_tok ? last_logits : nullptr);
-        if (dst && !cuda_ok(ctx, cudaMemcpyAsync(dst, e->logits, v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
-        if (tokens && !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "forward sync")) return -1;   // the token word is reused
+        const Tail tail = all_logits ? Tail::AllLogits : (last ? Tail::LastLogits : Tail::None);
+        if (!enqueue_batch(e, T, tokens != nullptr, tail, pos_start + t0 + T > ATTN_EXACT_CTX)) return -1;
+        e->last_row = T - 1;
+        if (all_logits && !cuda_ok(ctx, cudaMemcpyAsync(all_logits + t0 * v, e->logits, (size_t)T * v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
+        if (!all_logits && last && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
+        // the token / embedding staging buffers are reused by the next batch: the copies above are stream-ordered
     }
     if (!sync_and_check(ctx, "forward")) return -1;
     if (all_logits) std::memcpy(last_logits, all_logits + (n_tok - 1) * v, v * 4);
@@ -496,6 +539,7 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
         return fail(ctx, "decode_greedy: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (n_steps == 0) return 0;
     if (!make_current(ctx)) return -1;
+    e->last_row = 0;
     if (e->mega_ok && pos_start + n_steps <= ATTN_EXACT_CTX) {
         if (!decode_mega(e, first_token, (uint32_t)pos_start, (uint32_t)n_steps)) return -1;
         if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;

@@ -12,7 +12,8 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
     pdl_wait();
     pdl_trigger();
     if (c >= a.nc) return;
-    const uint32_t tok = __ldcg(a.token);
+    const uint32_t tok = __ldcg(a.token + blockIdx.y);          // blockIdx.y = token of the batch
+    float *hidden = a.hidden + (size_t)blockIdx.y * a.nc * 64;
     float v0, v1;
     if (a.embed_bf16 != nullptr) {
         const uint16_t *row = a.embed_bf16 + (size_t)tok * a.nc * 64 + (size_t)c * 64;
@@ -23,7 +24,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
         v1 = cell_value(a, tok, c, 2 * lane + 1);
         warp_ifwht64(v0, v1, c, lane);
     }
-    reinterpret_cast<float2 *>(a.hidden + (size_t)c * 64)[lane] = make_float2(v0, v1);
+    reinterpret_cast<float2 *>(hidden + (size_t)c * 64)[lane] = make_float2(v0, v1);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -40,6 +41,11 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     extern __shared__ float s_x[];           // n floats
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
+    {   // blockIdx.x = token of the batch: every per-token vector is contiguous
+        const size_t t = blockIdx.x;
+        hidden += t * n; q += t * n; scales += t * nc; sums += t * nc;
+        if (delta != nullptr) delta += t * n;
+    }
     pdl_wait();
     pdl_trigger();
     for (uint32_t i = tid; i < n / 4; i += 256) {
@@ -93,7 +99,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     pdl_wait();
     pdl_trigger();
     if (head >= a.n_q + 2 * a.n_kv) return;
-    const uint32_t pos = __ldcg(a.pos);
+    const uint32_t pos = __ldcg(a.pos) + a.pos_offset;
     const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
     float *sh = s_head[warp];
     const float *src = a.qkv + (size_t)head * hd;
@@ -180,7 +186,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     pdl_wait();
     pdl_trigger();
     if (split >= a.n_split) return;
-    const uint32_t ctx = __ldcg(a.pos) + 1, G = a.group;
+    const uint32_t ctx = __ldcg(a.pos) + a.pos_offset + 1, G = a.group;
     if (ctx <= ATTN_EXACT_CTX) return;     // short contexts are computed in the CPU's order by attn_finish_kernel
     const uint32_t per = split_span(ctx, a.n_split);
     const uint32_t t_lo = min(ctx, split * per), t_hi = min(ctx, t_lo + per);
@@ -292,7 +298,7 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_wait();
     pdl_trigger();
-    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + 1;
+    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + a.pos_offset + 1;
     float o = 0.0f;
     if (ctx <= ATTN_EXACT_CTX) {
         const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
@@ -410,7 +416,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAtt
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_wait();
     pdl_trigger();
-    const uint32_t pos = __ldcg(a.pos);
+    const uint32_t pos = __ldcg(a.pos) + a.pos_offset;
     if (pos + 1 > ATTN_EXACT_CTX) return;
     attention_head_dispatch(a, blockIdx.x, pos, attn_carve(smem));
 }
@@ -425,6 +431,11 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
     pdl_wait();
     pdl_trigger();
     if (c >= inter / 64) return;
+    {   // blockIdx.y = token of the batch
+        const size_t t = blockIdx.y;
+        gate_up += t * 2 * inter; q += t * inter; scales += t * (inter / 64); sums += t * (inter / 64);
+        if (dbg != nullptr) dbg += t * inter;
+    }
     const float2 g = __ldcg(reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64) + lane);
     const float2 u = __ldcg(reinterpret_cast<const float2 *>(gate_up + inter + (size_t)c * 64) + lane);
     float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_poly(-g.x))), u.x);
@@ -482,26 +493,26 @@ __global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restri
     }
 }
 
-__global__ void advance_pos_kernel(uint32_t *pos) {
+__global__ void advance_pos_kernel(uint32_t *pos, uint32_t by) {
     pdl_wait();
-    *pos = __ldcg(pos) + 1;
+    *pos = __ldcg(pos) + by;
 }
 
 // ------------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------------
-cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, bool pdl) {
-    return launch_kernel(embed_kernel, dim3((a.nc + 7) / 8), dim3(256), 0, s, pdl, a);
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, uint32_t n_tok, bool pdl) {
+    return launch_kernel(embed_kernel, dim3((a.nc + 7) / 8, n_tok), dim3(256), 0, s, pdl, a);
 }
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
-                                 int8_t *q, float *scales, int32_t *sums, bool pdl) {
+                                 int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl) {
     const size_t smem = (size_t)n * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(rmsnorm_quant_kernel, dim3(1), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums);
+    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums);
 }
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;
@@ -525,15 +536,15 @@ cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool 
     return launch_kernel(attn_fused_kernel, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
 }
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg, bool pdl) {
-    return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg);
+                                float *dbg, uint32_t n_tok, bool pdl) {
+    return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8, n_tok), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg);
 }
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl) {
     return launch_kernel(argmax_step_kernel, dim3(1), dim3(1024), 0, s, pdl, logits, n, token, pos, history, step);
 }
-cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, bool pdl) {
-    return launch_kernel(advance_pos_kernel, dim3(1), dim3(1), 0, s, pdl, pos);
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl) {
+    return launch_kernel(advance_pos_kernel, dim3(1), dim3(1), 0, s, pdl, pos, by);
 }
 
 }  // namespace k2t

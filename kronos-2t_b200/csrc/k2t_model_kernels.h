@@ -11,7 +11,7 @@ struct EmbedArgs {               // tied embedding = row of the lm_head matrix (
     const uint8_t *plane[3];
     const uint16_t *scales;
     const uint16_t *embed_bf16;  // [vocab][hidden] or null
-    const uint32_t *token;       // device
+    const uint32_t *token;       // device, [n_tok]
     float *hidden;
     uint32_t fmt, nc, nsg_pad, sgc, sgc_shift;
     uint32_t pitch[3], cell[3];
@@ -24,6 +24,7 @@ struct QkvPostArgs {
     const float *bias, *q_norm, *k_norm;     // null when absent
     const float *rope;           // [max_seq][head_dim]: cos(hd/2), sin(hd/2)
     const uint32_t *pos;         // device
+    uint32_t pos_offset;         // token of the batch: position = *pos + pos_offset
     int8_t *q_i8; float *q_scale;            // rotated int8 queries, one scale per head
     int8_t *k_q8, *v_q8; float *k_scale, *v_scale;   // cache: [layer][kv head][max_seq][head_dim] / [..][max_seq]
     uint32_t n_q, n_kv, head_dim, max_seq, layer;
@@ -39,6 +40,7 @@ struct AttnArgs {
     const int8_t *q_i8; const float *q_scale;
     const int8_t *k_q8, *v_q8; const float *k_scale, *v_scale;
     const uint32_t *pos;         // device: position of the current token (context = pos + 1)
+    uint32_t pos_offset;         // token of the batch: position = *pos + pos_offset
     float *part_m, *part_l, *part_o;         // [n_q][n_split], [n_q][n_split], [n_q][n_split][head_dim]
     float *attn_out;             // optional fp32 attention output [n_q][head_dim] (tests), may be null
     int8_t *out_q; float *out_scales; int32_t *out_sums;   // activation of o_proj
@@ -51,6 +53,7 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     const float *bias, *q_norm, *k_norm;     // null when absent
     const float *rope;           // [max_seq][head_dim]
     const uint32_t *pos;         // device (stand-alone kernel; the whole-token kernel passes the position itself)
+    uint32_t pos_offset;         // token of the batch: position = *pos + pos_offset
     int8_t *k_q8, *v_q8; float *k_scale, *v_scale;
     float *attn_tap;             // optional fp32 attention output [n_q][head_dim]
     int8_t *out_q; float *out_scales; int32_t *out_sums;
@@ -62,17 +65,18 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
 };
 
 // pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).
-cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, bool pdl);
+// n_tok: tokens of the batch (per-token vectors are contiguous: [n_tok][n])
+cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, uint32_t n_tok, bool pdl);
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
-                                 int8_t *q, float *scales, int32_t *sums, bool pdl);
+                                 int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl);
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl);
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl);     // two kernels
 // contexts of up to ATTN_EXACT_CTX positions: qkv_post + attention in one kernel (leaves longer contexts untouched)
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl);
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg, bool pdl);
+                                float *dbg, uint32_t n_tok, bool pdl);
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl);
-cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, bool pdl);
+cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
 
 }  // namespace k2t
