@@ -146,6 +146,12 @@ typedef struct KronosCudaEngineConfig {
     float rms_norm_eps;
     int32_t qk_norm_after_rope;
     uint32_t kv_bits;
+    /* MoeGeometry (metal_gpu.rs:443-456), all zero for a dense model: experts per MoE layer, routes per token,
+     * renormalise the top-k weights, expert MLP width, NF bits (2..5) and scale group of the expert matrices, bytes of
+     * one .k2tm expert record (nf_expert_byte_layout, moe_800b.rs:1330-1383).  Router scoring is the full softmax
+     * (MoeRouterScoring::Softmax); shared experts are not accepted. */
+    uint32_t moe_num_experts, moe_top_k, moe_norm_topk, moe_d_ff, moe_bits, moe_scale_group_chunks;
+    uint64_t moe_expert_bytes;
 } KronosCudaEngineConfig;
 
 /* One decoder layer as borrowed from the host engine: counterpart of LayerBorrow
@@ -156,6 +162,13 @@ typedef struct KronosCudaLayerDesc {
     const float *qkv_bias;                         /* [q_dim + 2 kv_dim] or NULL */
     const float *q_norm, *k_norm;                  /* [head_dim] or NULL */
     KronosCudaMatrixDesc qkv_proj, o_proj, gate_up_proj, down_proj;
+    /* MoeLayerBorrow (metal_gpu.rs:418-426); moe_router_w == NULL for a dense layer.  On a MoE layer gate_up_proj and
+     * down_proj are ignored (rows = 0): the FFN is the router [moe_num_experts][hidden] fp32 (+ optional bias) and
+     * moe_num_experts expert records (.k2tm record layout: codebooks at 0 / 16, gate_up pair_stream at 64, down
+     * pair_stream at the next multiple of 64) stored back to back in moe_shard. */
+    const float *moe_router_w, *moe_router_bias;
+    const uint8_t *moe_shard;
+    size_t moe_shard_len;
 } KronosCudaLayerDesc;
 
 /* MetalLlamaEngine::try_new (metal_gpu.rs:1196-1206): copies every tensor to HBM, allocates the KV cache
@@ -190,6 +203,9 @@ size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *engine, size_t positi
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
 /* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */
 int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
+/* Diagnostic: routes of the last forwarded token through MoE layer `layer` (route_sorted, sparse_moe.rs:86-182):
+ * up to 32 (expert id, weight) pairs in ascending expert order; returns their number (0 for a dense layer). */
+size_t kronos_cuda_engine_read_routes(KronosCudaEngine *engine, uint32_t layer, uint32_t *experts, float *weights);
 /* Diagnostic: attention output of the last layer for the last forwarded token, before o_proj:
  * [num_attention_heads * head_dim] (the `attn` vector of forward_token, real_llm.rs:6651-6700). */
 int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *engine, float *attention);

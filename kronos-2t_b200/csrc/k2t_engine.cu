@@ -18,6 +18,15 @@ using namespace k2t;
 struct EngineLayer {
     float *input_norm = nullptr, *post_norm = nullptr, *qkv_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
     KronosCudaMatrix *qkv = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;
+    // sparse-MoE FFN (router + expert records) instead of gate_up / down
+    bool moe = false;
+    float *router_w = nullptr, *router_bias = nullptr;
+    std::vector<KronosCudaMatrix *> expert_gu, expert_dn;
+    const uint8_t **d_gu_bases = nullptr, **d_dn_bases = nullptr;     // device tables: image base of every expert
+    k2t::ExpertCodebook *d_gu_books = nullptr, *d_dn_books = nullptr; // device tables: decode tables of every expert
+    int gu_fmt = -1, dn_fmt = -1;                                     // kernel format of the layer's experts
+    uint32_t *d_route_ids = nullptr;                                  // [MAX_BATCH][32] routes of the last batch
+    float *d_route_w = nullptr;
 };
 
 struct KronosCudaEngine {
@@ -37,6 +46,10 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    // sparse-MoE workspace: normalised hidden state, per-route expert buffers
+    float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr;
+    int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
+    bool has_moe = false;
     uint32_t last_row = 0;                    // row of `hidden` that holds the last forwarded token (prompt batches)
     bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
     size_t weight_bytes = 0;
@@ -145,6 +158,24 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             }
         }
         if (!gemv(e, L.o, e->proj, T)) return false;
+        if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
+            if (!count(e, launch_rmsnorm_quant_x(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->x_norm, T, e->pdl), "rmsnorm")) return false;
+            const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
+            for (uint32_t t = 0; t < T; ++t) {
+                RouterArgs ra{};
+                ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm + (size_t)t * h;
+                ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)c.moe_norm_topk;
+                ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32;
+                if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
+                if (!count(e, launch_gemv_experts(s, L.expert_gu[0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
+                                                  e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert gate_up")) return false;
+                if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
+                if (!count(e, launch_gemv_experts(s, L.expert_dn[0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
+                                                  e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert down")) return false;
+                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl), "moe combine")) return false;
+            }
+            continue;
+        }
         if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
         if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
         if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, T, e->pdl), "swiglu")) return false;
@@ -201,7 +232,9 @@ cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
     return e->graphs[(greedy ? 0 : 2) + (pos + 1 > ATTN_EXACT_CTX ? 1 : 0)];
 }
 uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
-    return 1 + e->cfg.num_layers * (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + 2 + 1;
+    uint32_t n = 1 + 2 + 1;
+    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4
+    return n;
 }
 
 constexpr uint32_t TRACE_CAP = 2048;
@@ -217,6 +250,7 @@ bool setup_mega(KronosCudaEngine *e) {
     const char *want = std::getenv("KRONOS_CUDA_MEGA");
     if (!want || want[0] != '1') { e->mega_why = "not requested (KRONOS_CUDA_MEGA=1 enables it)"; return true; }
     if (c.num_attention_heads > (uint32_t)ctx->sm_count) { e->mega_why = "more query heads than SMs"; return true; }
+    if (e->has_moe) { e->mega_why = "sparse-MoE layers are served by the per-operator path"; return true; }
     uint32_t warp_smem = 0;
     auto fill = [&](const KronosCudaMatrix *m, MegaMatrix &mm) {
         const int fmt = fill_gemv_args(m->dm, true, mm.g);
@@ -290,6 +324,56 @@ bool decode_mega(KronosCudaEngine *e, uint32_t first_token, uint32_t pos_start, 
 }
 
 
+// Uploads the experts of one MoE layer from its .k2tm records (nf_expert_byte_layout, moe_800b.rs:1330-1383).
+// Returns an error text, empty on success.
+std::string setup_moe_layer(KronosCudaEngine *e, EngineLayer &L, const KronosCudaLayerDesc &d) {
+    KronosCudaContext *ctx = e->ctx;
+    const KronosCudaEngineConfig &c = e->cfg;
+    const uint32_t E = c.moe_num_experts, h = c.hidden_size, dff = c.moe_d_ff, bits = c.moe_bits, sgc = std::max(1u, c.moe_scale_group_chunks);
+    if (E < 2 || E > 256 || c.moe_top_k == 0 || c.moe_top_k > 32) return "MoE geometry: 2..256 experts and 1..32 routes per token are supported";
+    if (bits < 2 || bits > 5 || dff == 0 || dff % 64 || (2 * dff) % 32 || h % 32) return "MoE geometry: NF bits 2..5, d_ff a multiple of 64";
+    static const size_t chunk_bytes[6] = {0, 0, 256, 384, 512, 640};
+    const size_t cb = chunk_bytes[bits];
+    const size_t gu_chunks = h / 64, gu_sg = (gu_chunks + sgc - 1) / sgc, dn_chunks = dff / 64, dn_sg = (dn_chunks + sgc - 1) / sgc;
+    const size_t gu_bytes = (size_t)(2 * dff / 32) * (gu_sg * 64 + gu_chunks * 2 * cb), dn_bytes = (size_t)(h / 32) * (dn_sg * 64 + dn_chunks * 2 * cb);
+    const size_t gu_off = 64, dn_off = (gu_off + gu_bytes + 63) / 64 * 64, rec = (dn_off + dn_bytes + 16383) / 16384 * 16384;
+    if (rec != c.moe_expert_bytes) return "moe_expert_bytes does not match the record layout of this geometry";
+    if (!d.moe_shard || d.moe_shard_len < (size_t)E * rec) return "expert shard is shorter than moe_num_experts records";
+    if (!dev_alloc(e, L.router_w, (size_t)E * h, d.moe_router_w)) return ctx->err;
+    if (d.moe_router_bias && !dev_alloc(e, L.router_bias, E, d.moe_router_bias)) return ctx->err;
+    std::vector<const uint8_t *> gu_bases(E), dn_bases(E);
+    std::vector<ExpertCodebook> gu_books(E), dn_books(E);
+    for (uint32_t x = 0; x < E; ++x) {
+        const uint8_t *r = d.moe_shard + (size_t)x * rec;
+        KronosCudaMatrixDesc m{};
+        m.kind = KRONOS_CUDA_MATRIX_NF; m.bits = bits; m.scale_group_chunks = sgc;
+        m.rows = 2 * dff; m.cols = h; std::memcpy(m.codebook, r, 16); m.data0 = r + gu_off; m.len0 = gu_bytes;
+        KronosCudaMatrix *gu = kronos_cuda_matrix_upload(ctx, &m, 0);
+        if (!gu) return "expert " + std::to_string(x) + " gate_up: " + ctx->err;
+        L.expert_gu.push_back(gu);
+        m.rows = h; m.cols = dff; std::memcpy(m.codebook, r + 16, 16); m.data0 = r + dn_off; m.len0 = dn_bytes;
+        KronosCudaMatrix *dn = kronos_cuda_matrix_upload(ctx, &m, 0);
+        if (!dn) return "expert " + std::to_string(x) + " down: " + ctx->err;
+        L.expert_dn.push_back(dn);
+        // every expert of a layer decodes with one kernel: NF4 falls back to the general decode for all of them as soon
+        // as one codebook does not fit the two-table form
+        const int fg = expert_codebook(gu->dm, gu_books[x]), fd = expert_codebook(dn->dm, dn_books[x]);
+        if (fg < 0 || fd < 0) return "expert matrices in an unsupported format";
+        L.gu_fmt = x == 0 ? fg : (L.gu_fmt == fg ? fg : (int)FMT_COUNT);
+        L.dn_fmt = x == 0 ? fd : (L.dn_fmt == fd ? fd : (int)FMT_COUNT);
+        gu_bases[x] = gu->dm.d_base; dn_bases[x] = dn->dm.d_base;
+    }
+    if (!dev_alloc(e, L.d_gu_books, E, gu_books.data()) || !dev_alloc(e, L.d_dn_books, E, dn_books.data()) ||
+        !dev_alloc(e, L.d_gu_bases, E, gu_bases.data()) || !dev_alloc(e, L.d_dn_bases, E, dn_bases.data()) ||
+        !dev_alloc(e, L.d_route_ids, (size_t)MAX_BATCH * 32) || !dev_alloc(e, L.d_route_w, (size_t)MAX_BATCH * 32) ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "MoE tables"))
+        return ctx->err;
+    e->has_moe = true;
+    // one token streams the router and the routed experts
+    e->weight_bytes += (size_t)E * h * 4 + (size_t)std::min(c.moe_top_k, E) * (gu_bytes + dn_bytes + 32);
+    return std::string();
+}
+
 }  // namespace
 
 extern "C" {
@@ -300,8 +384,12 @@ void kronos_cuda_engine_destroy(KronosCudaEngine *e) {
     cudaStreamSynchronize(e->ctx->stream);
     for (cudaGraphExec_t g : e->graphs) if (g) cudaGraphExecDestroy(g);
     for (EngineLayer &L : e->layers)
+    {
         for (KronosCudaMatrix *m : {L.qkv, L.o, L.gate_up, L.down})
             if (m) kronos_cuda_matrix_free(e->ctx, m);
+        for (KronosCudaMatrix *m : L.expert_gu) if (m) kronos_cuda_matrix_free(e->ctx, m);
+        for (KronosCudaMatrix *m : L.expert_dn) if (m) kronos_cuda_matrix_free(e->ctx, m);
+    }
     if (e->lm_head) kronos_cuda_matrix_free(e->ctx, e->lm_head);
     for (void *p : e->allocs) cudaFree(p);
     delete e;
@@ -335,8 +423,9 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         const KronosCudaLayerDesc &d = layers[l];
         EngineLayer &L = e->layers[l];
         if (!d.input_norm || !d.post_attn_norm) return bad("engine_create: a layer has no norm weights");
-        if (!shape_ok(d.qkv_proj, qkv_rows, h) || !shape_ok(d.o_proj, h, q_dim) || !shape_ok(d.gate_up_proj, 2 * inter, h) ||
-            !shape_ok(d.down_proj, h, inter))
+        L.moe = d.moe_router_w != nullptr;
+        if (!shape_ok(d.qkv_proj, qkv_rows, h) || !shape_ok(d.o_proj, h, q_dim) ||
+            (!L.moe && (!shape_ok(d.gate_up_proj, 2 * inter, h) || !shape_ok(d.down_proj, h, inter))))
             return bad("engine_create: layer " + std::to_string(l) + " has a projection whose shape does not match the config");
         if (!dev_alloc(e, L.input_norm, h, d.input_norm) || !dev_alloc(e, L.post_norm, h, d.post_attn_norm)) return bad(ctx->err);
         if (d.qkv_bias && !dev_alloc(e, L.qkv_bias, qkv_rows, d.qkv_bias)) return bad(ctx->err);
@@ -344,12 +433,17 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         if (d.k_norm && !dev_alloc(e, L.k_norm, hd, d.k_norm)) return bad(ctx->err);
         L.qkv = kronos_cuda_matrix_upload(ctx, &d.qkv_proj, 0);
         L.o = L.qkv ? kronos_cuda_matrix_upload(ctx, &d.o_proj, 0) : nullptr;
-        L.gate_up = L.o ? kronos_cuda_matrix_upload(ctx, &d.gate_up_proj, 0) : nullptr;
+        if (!L.o) return bad("engine_create: layer " + std::to_string(l) + ": " + ctx->err);
+        e->weight_bytes += L.qkv->dm.geom.file_bytes + L.o->dm.geom.file_bytes;
+        if (L.moe) {
+            const std::string why = setup_moe_layer(e, L, d);
+            if (!why.empty()) return bad("engine_create: layer " + std::to_string(l) + ": " + why);
+            continue;
+        }
+        L.gate_up = kronos_cuda_matrix_upload(ctx, &d.gate_up_proj, 0);
         L.down = L.gate_up ? kronos_cuda_matrix_upload(ctx, &d.down_proj, 0) : nullptr;
         if (!L.down) return bad("engine_create: layer " + std::to_string(l) + ": " + ctx->err);
-        for (KronosCudaMatrix *m : {L.qkv, L.o, L.gate_up, L.down}) {
-            e->weight_bytes += m->dm.geom.file_bytes;
-        }
+        e->weight_bytes += L.gate_up->dm.geom.file_bytes + L.down->dm.geom.file_bytes;
     }
     if (!shape_ok(*lm_head, c.vocab_size, h)) return bad("engine_create: lm_head shape does not match the config");
     e->lm_head = kronos_cuda_matrix_upload(ctx, lm_head, 0);
@@ -372,6 +466,12 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
+    if (ok && e->has_moe) {
+        const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
+        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->moe_gu, (size_t)k * 2 * dff) &&
+             dev_alloc(e, e->moe_out, (size_t)k * h) && dev_alloc(e, e->moe_q, (size_t)k * dff) &&
+             dev_alloc(e, e->moe_s, (size_t)k * dff / 64) && dev_alloc(e, e->moe_m, (size_t)k * dff / 64);
+    }
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
     if (!setup_mega(e)) return bad(ctx->err);
     return e;
@@ -397,6 +497,20 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *e, float *hidden) {
         !sync_and_check(ctx, "read hidden"))
         return -1;
     return 0;
+}
+
+size_t kronos_cuda_engine_read_routes(KronosCudaEngine *e, uint32_t layer, uint32_t *experts, float *weights) {
+    if (!e || !experts || !weights || layer >= e->cfg.num_layers || !e->layers[layer].moe) return 0;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!make_current(ctx)) return 0;
+    const EngineLayer &L = e->layers[layer];
+    const size_t k = std::min(e->cfg.moe_top_k, e->cfg.moe_num_experts);
+    if (!cuda_ok(ctx, cudaMemcpyAsync(experts, L.d_route_ids + e->last_row * 32, k * 4, cudaMemcpyDeviceToHost, ctx->stream), "read routes") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(weights, L.d_route_w + e->last_row * 32, k * 4, cudaMemcpyDeviceToHost, ctx->stream), "read routes") ||
+        !sync_and_check(ctx, "read routes"))
+        return 0;
+    return k;
 }
 
 int32_t kronos_cuda_engine_read_attention(KronosCudaEngine *e, float *attention) {

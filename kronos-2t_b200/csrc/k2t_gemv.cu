@@ -1,4 +1,6 @@
 // Stand-alone quantized GEMV / small-N GEMM kernel and its host launcher (body: k2t_gemv_core.cuh).
+#include <algorithm>
+
 #include "k2t_gemv_core.cuh"
 
 namespace k2t {
@@ -52,6 +54,92 @@ static cudaError_t launch_fmt(cudaStream_t stream, const GemvArgs &a, uint32_t n
 }
 
 uint32_t gemv_max_tokens(const DeviceMatrix &) { return 4; }
+
+int fill_gemv_args(const DeviceMatrix &m, bool has_xsum, GemvArgs &a);
+
+// Expert-batched GEMV: grid.y = route slot.  Every routed expert has the same geometry; slot s reads the matrix of
+// expert route_ids[s] (written by the router kernel just before, so the ids are read after the dependency wait),
+// its own activation rows (stride 0 = one activation shared by all slots) and writes its own output row.
+struct ExpertBatch {
+    const ExpertCodebook *books;   // device: decode tables of every expert (each expert has its own codebook)
+    const uint8_t *const *bases;   // device: image base of every expert of the layer
+    const uint8_t *base0;          // the base the GemvArgs plane pointers were filled with
+    const uint32_t *route_ids;     // device [n_slot]
+    size_t xq_stride, xs_stride;   // per-slot strides of the activation
+    size_t out_stride;             // per-slot stride of the output
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const ExpertBatch b) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t wid = threadIdx.x >> 5, WK = blockDim.x >> 5;
+    uint8_t *wsm = smem + (size_t)wid * warp_smem<FMT>(1);
+    if ((threadIdx.x & 31) == 0) gemv_init_barriers(wsm);
+    __syncwarp();
+    pdl_wait();
+    const uint32_t slot = blockIdx.y, e = __ldcg(b.route_ids + slot);
+    const uint8_t *base = b.bases[e];
+    {
+        const uint4 *bk = reinterpret_cast<const uint4 *>(b.books + e);
+        const uint4 c0 = __ldg(bk), c1 = __ldg(bk + 1), t = __ldg(bk + 2), o = __ldg(bk + 3);
+        a.cb[0] = c0.x; a.cb[1] = c0.y; a.cb[2] = c0.z; a.cb[3] = c0.w; a.cb[4] = c1.x; a.cb[5] = c1.y; a.cb[6] = c1.z; a.cb[7] = c1.w;
+        a.tab[0] = t.x; a.tab[1] = t.y; a.tab[2] = t.z; a.tab[3] = t.w;
+        a.nf4_offset = (int32_t)o.x;
+    }
+#pragma unroll
+    for (int k = 0; k < 3; ++k) a.plane[k] = base + (a.plane[k] - b.base0);
+    a.scales = reinterpret_cast<const uint16_t *>(base + (reinterpret_cast<const uint8_t *>(a.scales) - b.base0));
+    PipeState ps;
+    gemv_body<FMT, 1, false, false>(a, a.xq + slot * b.xq_stride, a.xs + slot * b.xs_stride,
+                                    a.xsum != nullptr ? a.xsum + slot * b.xs_stride : nullptr, a.out + slot * b.out_stride, wsm,
+                                    reinterpret_cast<float *>(smem + (size_t)WK * warp_smem<FMT>(1)), blockIdx.x, gridDim.x, wid, WK, 0, ps);
+}
+
+template <int FMT>
+static cudaError_t launch_expert_fmt(cudaStream_t stream, const GemvArgs &a, const ExpertBatch &b, uint32_t n_slot, int sm_count) {
+    const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
+    uint32_t wk = 1;
+    while (wk < 8 && wk * 2 <= np && n_rb * n_slot * wk < 12u * (uint32_t)sm_count) wk *= 2;
+    const uint32_t smem = wk * warp_smem<FMT>(1) + 32 * 4;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_expert_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
+    per_sm = per_sm < 1 ? 1 : per_sm > 32 ? 32 : per_sm;
+    if (per_sm * wk > 48) per_sm = 48 / wk;
+    uint32_t grid = std::max(1u, per_sm * (uint32_t)sm_count / n_slot);
+    if (grid > n_rb) grid = n_rb;
+    return launch_kernel(gemv_expert_kernel<FMT>, dim3(grid, n_slot), dim3(32 * wk), smem, stream, a.pdl != 0, a, b);
+}
+
+int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out) {
+    GemvArgs a;
+    const int fmt = fill_gemv_args(m, true, a);
+    for (int i = 0; i < 8; ++i) out.cb[i] = a.cb[i];
+    for (int i = 0; i < 4; ++i) out.tab[i] = a.tab[i];
+    out.nf4_offset = a.nf4_offset;
+    out.pad[0] = out.pad[1] = out.pad[2] = 0;
+    return fmt;
+}
+
+cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases, const uint32_t *route_ids,
+                                uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum, size_t xq_stride,
+                                size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl) {
+    if (n_slot == 0) return cudaSuccess;
+    GemvArgs a;
+    if (fill_gemv_args(m0, xsum != nullptr, a) < 0) return cudaErrorNotSupported;
+    a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.err_flag = err_flag; a.out_stride = m0.geom.rows; a.pdl = pdl ? 1u : 0u; a.n_tok = 1;
+    ExpertBatch b{books, bases, m0.d_base, route_ids, xq_stride, xs_stride, out_stride};
+    switch (fmt) {
+        case FMT_NF4: return launch_expert_fmt<FMT_NF4>(stream, a, b, n_slot, sm_count);
+        case FMT_NF4G: return launch_expert_fmt<FMT_NF4G>(stream, a, b, n_slot, sm_count);
+        case FMT_NF3: return launch_expert_fmt<FMT_NF3>(stream, a, b, n_slot, sm_count);
+        case FMT_NF5: return launch_expert_fmt<FMT_NF5>(stream, a, b, n_slot, sm_count);
+        case FMT_E8Q2: return launch_expert_fmt<FMT_E8Q2>(stream, a, b, n_slot, sm_count);
+        default: return cudaErrorNotSupported;       // experts are NF matrices (2..5 bits)
+    }
+}
 
 // Fills the matrix part of GemvArgs (planes, pitches, codebooks) and returns the kernel format index
 // (FMT_NF4G for an NF4 codebook the two-table decode cannot represent), or -1 when unsupported.

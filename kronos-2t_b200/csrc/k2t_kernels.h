@@ -25,6 +25,23 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
                         const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
                         int sm_count, uint32_t *err_flag, uint32_t *launches, bool pdl = false);
 
+// Decode tables of one expert matrix (every expert of a MoE layer carries its own codebook): 64 bytes.
+struct ExpertCodebook {
+    uint32_t cb[8];      // expanded codebook, 4 centroids per word
+    uint32_t tab[4];     // NF4 two-table decode
+    int32_t nf4_offset;
+    uint32_t pad[3];
+};
+// Fills `out` for matrix m and returns its kernel format index (FMT_*; FMT_COUNT = NF4 with the general decode).
+int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out);
+
+// Expert-batched GEMV (one token): slot s of n_slot multiplies the matrix of expert route_ids[s] (device memory; all
+// experts share the geometry of m0 and the kernel format `fmt`; bases[e] / books[e] = device image and decode tables of
+// expert e) with activation row s (strides 0 = shared) into out + s * out_stride.
+cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases,
+                                const uint32_t *route_ids, uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum,
+                                size_t xq_stride, size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl);
+
 // Largest n_tok one launch_gemv call accepts for this matrix (shared-memory bound), at most 8.
 uint32_t gemv_max_tokens(const DeviceMatrix &m);
 

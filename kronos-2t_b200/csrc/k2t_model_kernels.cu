@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
                                                             const float *__restrict__ w, uint32_t n, float eps,
                                                             int8_t *__restrict__ q, float *__restrict__ scales,
-                                                            int32_t *__restrict__ sums) {
+                                                            int32_t *__restrict__ sums, float *__restrict__ x_norm) {
     extern __shared__ float s_x[];           // n floats
     __shared__ float s_inv;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
         const size_t t = blockIdx.x;
         hidden += t * n; q += t * n; scales += t * nc; sums += t * nc;
         if (delta != nullptr) delta += t * n;
+        if (x_norm != nullptr) x_norm += t * n;
     }
     pdl_wait();
     pdl_trigger();
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
         const float2 ww = reinterpret_cast<const float2 *>(w + (size_t)c * 64)[lane];
         v.x = __fmul_rn(__fmul_rn(v.x, inv), ww.x);
         v.y = __fmul_rn(__fmul_rn(v.y, inv), ww.y);
+        if (x_norm != nullptr) reinterpret_cast<float2 *>(x_norm + (size_t)c * 64)[lane] = v;
         warp_fwht64(v.x, v.y, c, lane);
         int q0, q1, sum;
         float sc;
@@ -84,6 +86,121 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
         reinterpret_cast<char2 *>(q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
         if (lane == 0) { scales[c] = sc; sums[c] = sum; }
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// sparse-MoE FFN pieces (SparseMoeRuntime::forward_layer_single, sparse_moe.rs:961-1084)
+// ------------------------------------------------------------------------------------------------
+// The scalar paths of the reference call the platform expf; the correctly rounded value stands in for it here
+// as in the CPU restatement these kernels are compared with.
+__device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x); }
+
+// Router: one CTA.  Logits in the accumulator order of dot_f32_moe_neon (16 fma lanes over 16-element strides,
+// (a0+a1)+(a2+a3), pairwise): half a warp per expert.  Softmax over all experts with a sequential sum, top-k by
+// insertion with strict '>' (select_topk_by_score), optional renormalisation, sort by expert id: one thread,
+// a few thousand operations.
+constexpr uint32_t ROUTER_THREADS = 512, ROUTER_MAX_EXPERTS = 256, ROUTER_MAX_TOPK = 32;
+__global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const RouterArgs a) {
+    extern __shared__ float s_xr[];          // hidden floats
+    __shared__ float s_z[ROUTER_MAX_EXPERTS];
+    __shared__ float s_max;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = lane >> 4, l16 = lane & 15;
+    pdl_wait();
+    pdl_trigger();
+    for (uint32_t i = tid; i < a.hidden; i += ROUTER_THREADS) s_xr[i] = __ldcg(a.x + i);
+    __syncthreads();
+    for (uint32_t e0 = warp * 2; e0 < a.n_experts; e0 += (ROUTER_THREADS / 32) * 2) {
+        const uint32_t e = e0 + half;
+        float acc = 0.0f;
+        if (e < a.n_experts) {
+            const float *row = a.w + (size_t)e * a.hidden;
+#pragma unroll 8
+            for (uint32_t i = l16; i < a.hidden; i += 16) acc = __fmaf_rn(__ldg(row + i), s_xr[i], acc);
+        }
+        float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));      // within each half: lanes 0..3 and 8..11
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 8));
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 1));
+        t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2));
+        if (l16 == 0 && e < a.n_experts) s_z[e] = a.bias != nullptr ? __fadd_rn(t, __ldg(a.bias + e)) : t;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float m = -INFINITY;
+        for (uint32_t e = lane; e < a.n_experts; e += 32) m = fmaxf(m, s_z[e]);
+        m = warp_max(m);
+        if (lane == 0) s_max = m;
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = exp_cr(__fsub_rn(s_z[e], s_max));
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+        for (uint32_t e = 0; e < a.n_experts; ++e) sum = __fadd_rn(sum, s_z[e]);
+        const float inv_all = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)a.n_experts);
+        const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
+        uint32_t ids[ROUTER_MAX_TOPK];
+        float w[ROUTER_MAX_TOPK];
+        uint32_t len = 0;
+        for (uint32_t e = 0; e < a.n_experts; ++e) {
+            const float sc = __fmul_rn(s_z[e], inv_all);
+            if (len < k) {
+                uint32_t pos = len;
+                while (pos > 0 && sc > w[pos - 1]) { ids[pos] = ids[pos - 1]; w[pos] = w[pos - 1]; --pos; }
+                ids[pos] = e; w[pos] = sc; ++len;
+            } else if (sc > w[k - 1]) {
+                uint32_t pos = k - 1;
+                while (pos > 0 && sc > w[pos - 1]) { ids[pos] = ids[pos - 1]; w[pos] = w[pos - 1]; --pos; }
+                ids[pos] = e; w[pos] = sc;
+            }
+        }
+        if (a.norm_topk) {
+            float top_sum = 0.0f;
+            for (uint32_t i = 0; i < k; ++i) top_sum = __fadd_rn(top_sum, w[i]);
+            if (top_sum > 0.0f) { const float inv_top = __fdiv_rn(1.0f, top_sum); for (uint32_t i = 0; i < k; ++i) w[i] = __fmul_rn(w[i], inv_top); }
+        }
+        for (uint32_t i = 1; i < k; ++i) {
+            const uint32_t ce = ids[i]; const float cw = w[i];
+            uint32_t j = i;
+            while (j > 0 && ids[j - 1] > ce) { ids[j] = ids[j - 1]; w[j] = w[j - 1]; --j; }
+            ids[j] = ce; w[j] = cw;
+        }
+        for (uint32_t i = 0; i < k; ++i) { a.route_ids[i] = ids[i]; a.route_w[i] = w[i]; }
+    }
+}
+
+// SwiGLU of the routed experts' gate_up outputs [slot][2 * d_ff] (gate = rows [0, d_ff), up = the rest), chunk by chunk
+// with the scalar-path exp, then rotation (chunk index c) + int8: the activation of each expert's down projection.
+__global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *__restrict__ gate_up, uint32_t d_ff,
+                                                                  int8_t *__restrict__ q, float *__restrict__ scales,
+                                                                  int32_t *__restrict__ sums) {
+    const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5), nc = d_ff / 64;
+    pdl_wait();
+    pdl_trigger();
+    if (c >= nc) return;
+    const size_t slot = blockIdx.y;
+    gate_up += slot * 2 * d_ff; q += slot * d_ff; scales += slot * nc; sums += slot * nc;
+    const float2 g = __ldcg(reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64) + lane);
+    const float2 u = __ldcg(reinterpret_cast<const float2 *>(gate_up + d_ff + (size_t)c * 64) + lane);
+    float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_cr(-g.x))), u.x);
+    float x1 = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, exp_cr(-g.y))), u.y);
+    warp_fwht64(x0, x1, c, lane);
+    int q0, q1, sum;
+    float sc;
+    warp_quant64(x0, x1, q0, q1, sc, sum);
+    reinterpret_cast<char2 *>(q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+    if (lane == 0) { scales[c] = sc; sums[c] = sum; }
+}
+
+// out[i] = 0; for every route in ascending expert order: out[i] += w * expert_out[slot][i]   (separate multiply and add)
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ expert_out, const float *__restrict__ route_w,
+                                                          uint32_t n_slot, uint32_t n, float *__restrict__ out) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    pdl_wait();
+    pdl_trigger();
+    if (i >= n) return;
+    float acc = 0.0f;
+    for (uint32_t s = 0; s < n_slot; ++s) acc = __fadd_rn(acc, __fmul_rn(__ldcg(route_w + s), __ldcg(expert_out + (size_t)s * n + i)));
+    out[i] = acc;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -506,13 +623,34 @@ cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, uint32_t n_tok, boo
 }
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                  int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl) {
+    return launch_rmsnorm_quant_x(s, hidden, delta, w, n, eps, q, scales, sums, nullptr, n_tok, pdl);
+}
+cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl) {
+    if (a.n_experts > ROUTER_MAX_EXPERTS || a.top_k > ROUTER_MAX_TOPK || a.hidden * 4 > 160 * 1024) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)a.hidden * 4;
+    if (smem > 40 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_kernel(moe_router_kernel, dim3(1), dim3(ROUTER_THREADS), smem, s, pdl, a);
+}
+cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
+                                       int32_t *sums, bool pdl) {
+    return launch_kernel(expert_swiglu_quant_kernel, dim3((d_ff / 64 + 7) / 8, n_slot), dim3(256), 0, s, pdl, gate_up, d_ff, q, scales, sums);
+}
+cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
+                               bool pdl) {
+    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out);
+}
+cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                   int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {
     const size_t smem = (size_t)n * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums);
+    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm);
 }
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;

@@ -64,6 +64,15 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     int32_t qk_norm_after_rope;
 };
 
+struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scoring (sparse_moe.rs:86-182)
+    const float *w, *bias;       // [n_experts][hidden], [n_experts] or null
+    const float *x;              // normalised hidden state (fp32, not rotated)
+    uint32_t n_experts, hidden, top_k;
+    int32_t norm_topk;
+    uint32_t *route_ids;         // out: [top_k] expert ids, ascending
+    float *route_w;              // out: [top_k]
+};
+
 // pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).
 // n_tok: tokens of the batch (per-token vectors are contiguous: [n_tok][n])
 cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, uint32_t n_tok, bool pdl);
@@ -77,6 +86,16 @@ cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t i
                                 float *dbg, uint32_t n_tok, bool pdl);
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl);
+// x_norm (optional): also write the normalised fp32 vector (the MoE router reads it)
+cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                   int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl);
+cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl);
+// SwiGLU of n_slot expert outputs [n_slot][2 * d_ff] with the scalar-path exp (moe_800b.rs:1498-1517), then rotation + int8
+cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
+                                       int32_t *sums, bool pdl);
+// out[i] = sum over slots, in slot order, of route_w[s] * expert_out[s][i]   (sparse_moe.rs:1046-1048)
+cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
+                               bool pdl);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
 
 }  // namespace k2t

@@ -35,13 +35,16 @@ class MatrixDesc(C.Structure):
 class EngineConfig(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("hidden_size", "num_layers", "num_attention_heads", "num_key_value_heads",
                                           "head_dim", "intermediate_size", "vocab_size", "max_seq_len")] + \
-               [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)]
+               [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)] + \
+               [(n, C.c_uint32) for n in ("moe_num_experts", "moe_top_k", "moe_norm_topk", "moe_d_ff", "moe_bits",
+                                          "moe_scale_group_chunks")] + [("moe_expert_bytes", C.c_uint64)]
 
 
 class LayerDesc(C.Structure):
     _fields_ = [("input_norm", C.c_void_p), ("post_attn_norm", C.c_void_p), ("qkv_bias", C.c_void_p),
                 ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
-                ("qkv_proj", MatrixDesc), ("o_proj", MatrixDesc), ("gate_up_proj", MatrixDesc), ("down_proj", MatrixDesc)]
+                ("qkv_proj", MatrixDesc), ("o_proj", MatrixDesc), ("gate_up_proj", MatrixDesc), ("down_proj", MatrixDesc),
+                ("moe_router_w", C.c_void_p), ("moe_router_bias", C.c_void_p), ("moe_shard", C.c_void_p), ("moe_shard_len", C.c_size_t)]
 
 
 def load_library():
@@ -87,6 +90,7 @@ def load_library():
     sig("kronos_cuda_engine_weight_bytes", sz, vp)
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
+    sig("kronos_cuda_engine_read_routes", sz, vp, u32, vp, vp)
     sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
     sig("kronos_cuda_engine_read_kv_q4", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
@@ -268,6 +272,13 @@ class Engine:
         c = spec["cfg"]
         self.cfg = EngineConfig(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
                                 c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
+        moes = [ly["moe"] for ly in spec["layers"] if ly.get("moe")]
+        if moes:        # one geometry for every MoE layer of a model (MoeGeometry)
+            m0 = moes[0]
+            assert all(all(m[k] == m0[k] for k in ("n_experts", "top_k", "norm_topk", "d_ff", "bits", "sgc", "expert_bytes")) for m in moes)
+            self.cfg.moe_num_experts, self.cfg.moe_top_k, self.cfg.moe_norm_topk = m0["n_experts"], m0["top_k"], int(m0["norm_topk"])
+            self.cfg.moe_d_ff, self.cfg.moe_bits, self.cfg.moe_scale_group_chunks = m0["d_ff"], m0["bits"], m0["sgc"]
+            self.cfg.moe_expert_bytes = m0["expert_bytes"]
         keep = []
 
         def vec(a):
@@ -282,7 +293,13 @@ class Engine:
             d = layers[l]
             d.input_norm, d.post_attn_norm = vec(ly["input_norm"]), vec(ly["post_norm"])
             d.qkv_bias, d.q_norm, d.k_norm = vec(ly.get("qkv_bias")), vec(ly.get("q_norm")), vec(ly.get("k_norm"))
-            for name, key in (("qkv_proj", "qkv"), ("o_proj", "o"), ("gate_up_proj", "gate_up"), ("down_proj", "down")):
+            moe = ly.get("moe")
+            if moe:
+                shard = _np(moe["shard"], np.uint8)
+                keep.append(shard)
+                d.moe_router_w, d.moe_router_bias = vec(moe["router_w"]), vec(moe.get("router_bias"))
+                d.moe_shard, d.moe_shard_len = shard.ctypes.data, shard.nbytes
+            for name, key in (("qkv_proj", "qkv"), ("o_proj", "o")) + (() if moe else (("gate_up_proj", "gate_up"), ("down_proj", "down"))):
                 md = desc_of(ly[key])
                 keep.append(md._keep)
                 setattr(d, name, md)
@@ -333,6 +350,11 @@ class Engine:
         out = np.empty(self.cfg.hidden_size, np.float32)
         self.ctx._check(self.L.kronos_cuda_engine_read_hidden(self.handle, _p(out)))
         return out
+
+    def read_routes(self, layer):
+        e, w = np.zeros(32, np.uint32), np.zeros(32, np.float32)
+        k = self.L.kronos_cuda_engine_read_routes(self.handle, layer, _p(e), _p(w))
+        return e[:k].copy(), w[:k].copy()
 
     def read_attention(self):
         out = np.empty(self.cfg.num_attention_heads * self.cfg.head_dim, np.float32)

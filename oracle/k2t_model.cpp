@@ -70,9 +70,21 @@ bool load_mat(Mat &m, const K2oMatrixDesc *d) {
     return true;
 }
 
+struct Expert { Mat gu, dn; };
+struct Moe {
+    bool on = false;
+    uint32_t n_experts = 0, top_k = 0, d_ff = 0;
+    bool norm_topk = false;
+    std::vector<float> router_w, router_bias;
+    std::vector<Expert> experts;
+    uint32_t last_k = 0;                 // routes of the last token (tests)
+    uint32_t last_e[32] = {0};
+    float last_w[32] = {0};
+};
 struct Layer {
     std::vector<float> input_norm, post_norm, qkv_bias, q_norm, k_norm;
     Mat qkv, o, gate_up, down;
+    Moe moe;
 };
 
 }  // namespace
@@ -288,6 +300,26 @@ void attend_head_q4(const K2oModel &m, size_t l, size_t kvh, const float *q_head
     std::memcpy(out, o, hd * sizeof(float));
 }
 
+// The platform expf of the reference's scalar paths, replaced by the correctly rounded value (see attend_head).
+inline float exp_cr(float x) { return (float)std::exp((double)x); }
+
+// select_topk_by_score (sparse_moe.rs:185-206): insertion with strict '>' (the earlier expert wins ties), descending.
+void select_topk(const float *scores, size_t n, size_t k, uint32_t *ids, float *vals) {
+    size_t len = 0;
+    for (size_t e = 0; e < n; ++e) {
+        const float sc = scores[e];
+        if (len < k) {
+            size_t pos = len;
+            while (pos > 0 && sc > vals[pos - 1]) { ids[pos] = ids[pos - 1]; vals[pos] = vals[pos - 1]; --pos; }
+            ids[pos] = (uint32_t)e; vals[pos] = sc; ++len;
+        } else if (sc > vals[k - 1]) {
+            size_t pos = k - 1;
+            while (pos > 0 && sc > vals[pos - 1]) { ids[pos] = ids[pos - 1]; vals[pos] = vals[pos - 1]; --pos; }
+            ids[pos] = (uint32_t)e; vals[pos] = sc;
+        }
+    }
+}
+
 struct Act {
     std::vector<int8_t> q;
     std::vector<float> s;
@@ -298,9 +330,108 @@ struct Act {
     }
 };
 
+// SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), zero-copy NF experts, softmax router, no shared expert.
+void moe_forward(Moe &M, const float *x_norm, size_t h, float *out, size_t threads) {
+    const size_t E = M.n_experts, k = std::min<size_t>(std::min<size_t>(M.top_k, E), 32);
+    std::vector<float> logits(E);
+    for (size_t e = 0; e < E; ++e) {
+        float v = k2o_dot_f32(M.router_w.data() + e * h, x_norm, h);      // dot_f32_moe_neon = the 16-lane fma order
+        if (!M.router_bias.empty()) v += M.router_bias[e];
+        logits[e] = v;
+    }
+    float max_z = -INFINITY;
+    for (size_t e = 0; e < E; ++e) max_z = std::max(max_z, logits[e]);
+    float sum = 0.0f;
+    for (size_t e = 0; e < E; ++e) { logits[e] = exp_cr(logits[e] - max_z); sum += logits[e]; }
+    const float inv_all = sum > 0.0f ? 1.0f / sum : 1.0f / (float)E;
+    for (size_t e = 0; e < E; ++e) logits[e] *= inv_all;
+    uint32_t ids[32];
+    float w[32];
+    select_topk(logits.data(), E, k, ids, w);
+    if (M.norm_topk) {
+        float top_sum = 0.0f;
+        for (size_t i = 0; i < k; ++i) top_sum += w[i];
+        if (top_sum > 0.0f) { const float inv_top = 1.0f / top_sum; for (size_t i = 0; i < k; ++i) w[i] *= inv_top; }
+    }
+    for (size_t i = 1; i < k; ++i) {                  // insertion sort by ascending expert id
+        const uint32_t ce = ids[i]; const float cw = w[i];
+        size_t j = i;
+        while (j > 0 && ids[j - 1] > ce) { ids[j] = ids[j - 1]; w[j] = w[j - 1]; --j; }
+        ids[j] = ce; w[j] = cw;
+    }
+    M.last_k = (uint32_t)k;
+    for (size_t i = 0; i < k; ++i) { M.last_e[i] = ids[i]; M.last_w[i] = w[i]; }
+    Act act_in, act_mid;
+    act_in.populate(x_norm, h);
+    std::vector<float> gu(2 * (size_t)M.d_ff), sw(M.d_ff), eo(h);
+    std::fill(out, out + h, 0.0f);
+    for (size_t i = 0; i < k; ++i) {
+        const Expert &X = M.experts[ids[i]];
+        X.gu.gemv(act_in.q.data(), act_in.s.data(), act_in.m.data(), gu.data(), threads);
+        for (size_t j = 0; j < M.d_ff; ++j) {          // moe_800b.rs:1498-1505: scalar libm exp, gate = rows [0, d_ff), up = the rest
+            const float g = gu[j], u = gu[M.d_ff + j];
+            sw[j] = (g / (1.0f + exp_cr(-g))) * u;
+        }
+        act_mid.populate(sw.data(), M.d_ff);
+        X.dn.gemv(act_mid.q.data(), act_mid.s.data(), act_mid.m.data(), eo.data(), threads);
+        for (size_t j = 0; j < h; ++j) out[j] += w[i] * eo[j];
+    }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
 }  // namespace
 
 extern "C" {
+
+size_t k2o_nf_expert_layout(size_t d_model, size_t d_ff, size_t bits, size_t sgc, size_t *gu_pair_off, size_t *gu_pair_bytes,
+                            size_t *dn_pair_off, size_t *dn_pair_bytes) {
+    sgc = std::max<size_t>(sgc, 1);
+    const size_t cb = k2o_nf_chunk_bytes(bits);
+    const size_t gu_chunks = d_model / 64, gu_sg = (gu_chunks + sgc - 1) / sgc, gu_pairs = 2 * d_ff / 32;
+    const size_t dn_chunks = d_ff / 64, dn_sg = (dn_chunks + sgc - 1) / sgc, dn_pairs = d_model / 32;
+    const size_t gub = gu_pairs * (gu_sg * 64 + gu_chunks * 2 * cb), dnb = dn_pairs * (dn_sg * 64 + dn_chunks * 2 * cb);
+    const size_t gu_off = 64, dn_off = align_up(gu_off + gub, 64);
+    if (gu_pair_off) *gu_pair_off = gu_off;
+    if (gu_pair_bytes) *gu_pair_bytes = gub;
+    if (dn_pair_off) *dn_pair_off = dn_off;
+    if (dn_pair_bytes) *dn_pair_bytes = dnb;
+    return align_up(dn_off + dnb, 16384);             // K2TM_VM_PAGE_BYTES
+}
+
+int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const float *router_bias, uint32_t n_experts,
+                      uint32_t top_k, int norm_topk, uint32_t d_ff, uint32_t bits, uint32_t sgc, const uint8_t *shard,
+                      size_t expert_bytes) {
+    if (!m || l >= m->layers.size() || !router_w || !shard || n_experts < 2 || top_k == 0 || d_ff % 64 || bits < 2 || bits > 5) return -1;
+    const size_t h = m->cfg.hidden;
+    if ((2 * (size_t)d_ff) % 32 || h % 32) return -1;
+    size_t gu_off, gub, dn_off, dnb;
+    if (k2o_nf_expert_layout(h, d_ff, bits, sgc, &gu_off, &gub, &dn_off, &dnb) != expert_bytes) return -1;
+    Moe &M = m->layers[l].moe;
+    M.on = true; M.n_experts = n_experts; M.top_k = top_k; M.d_ff = d_ff; M.norm_topk = norm_topk != 0;
+    M.router_w.assign(router_w, router_w + (size_t)n_experts * h);
+    if (router_bias) M.router_bias.assign(router_bias, router_bias + n_experts); else M.router_bias.clear();
+    M.experts.resize(n_experts);
+    for (uint32_t e = 0; e < n_experts; ++e) {
+        const uint8_t *rec = shard + (size_t)e * expert_bytes;
+        K2oMatrixDesc d{};
+        d.kind = 2; d.bits = bits; d.scale_group_chunks = sgc ? sgc : 1;
+        d.rows = 2 * d_ff; d.cols = (uint32_t)h; std::memcpy(d.codebook, rec, 16);
+        d.data0 = rec + gu_off; d.len0 = gub; d.data1 = nullptr; d.len1 = 0;
+        if (!load_mat(M.experts[e].gu, &d)) return -1;
+        d.rows = (uint32_t)h; d.cols = d_ff; std::memcpy(d.codebook, rec + 16, 16);
+        d.data0 = rec + dn_off; d.len0 = dnb;
+        if (!load_mat(M.experts[e].dn, &d)) return -1;
+    }
+    return 0;
+}
+
+uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts, float *weights) {
+    if (!m || l >= m->layers.size() || !m->layers[l].moe.on) return 0;
+    const Moe &M = m->layers[l].moe;
+    for (uint32_t i = 0; i < M.last_k; ++i) { experts[i] = M.last_e[i]; weights[i] = M.last_w[i]; }
+    return M.last_k;
+}
 
 K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table) {
     if (!cfg || !rope_table) return nullptr;
@@ -340,10 +471,11 @@ int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const 
     if (qkv_bias) L.qkv_bias.assign(qkv_bias, qkv_bias + qkv_rows); else L.qkv_bias.clear();
     if (q_norm) L.q_norm.assign(q_norm, q_norm + c.head_dim); else L.q_norm.clear();
     if (k_norm) L.k_norm.assign(k_norm, k_norm + c.head_dim); else L.k_norm.clear();
-    if (!load_mat(L.qkv, qkv) || !load_mat(L.o, o) || !load_mat(L.gate_up, gate_up) || !load_mat(L.down, down)) return -1;
-    if (L.qkv.rows != qkv_rows || L.qkv.cols != c.hidden || L.o.rows != c.hidden || L.o.cols != c.n_q * c.head_dim ||
-        L.gate_up.rows != 2 * c.inter || L.gate_up.cols != c.hidden || L.down.rows != c.hidden || L.down.cols != c.inter)
-        return -1;
+    if (!load_mat(L.qkv, qkv) || !load_mat(L.o, o)) return -1;
+    if (L.qkv.rows != qkv_rows || L.qkv.cols != c.hidden || L.o.rows != c.hidden || L.o.cols != c.n_q * c.head_dim) return -1;
+    if (!gate_up && !down) return 0;                    // a sparse-MoE layer: k2o_model_set_moe supplies the FFN
+    if (!load_mat(L.gate_up, gate_up) || !load_mat(L.down, down)) return -1;
+    if (L.gate_up.rows != 2 * c.inter || L.gate_up.cols != c.hidden || L.down.rows != c.hidden || L.down.cols != c.inter) return -1;
     return 0;
 }
 
@@ -409,7 +541,7 @@ int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logi
     Act act;
     m->tap_hidden.assign((size_t)c.layers * h, 0.0f);
     for (size_t l = 0; l < c.layers; ++l) {
-        const Layer &L = m->layers[l];
+        Layer &L = m->layers[l];
         rms_norm(hidden.data(), L.input_norm.data(), h, c.eps, norm.data());
         act.populate(norm.data(), h);
         L.qkv.gemv(act.q.data(), act.s.data(), act.m.data(), qkv.data(), threads);
@@ -437,6 +569,12 @@ int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logi
         L.o.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
         for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);   // add_inplace = axpy(1.0)
         rms_norm(hidden.data(), L.post_norm.data(), h, c.eps, norm.data());
+        if (L.moe.on) {                                 // real_llm.rs:6709-6714
+            moe_forward(m->layers[l].moe, norm.data(), h, proj.data(), threads);
+            for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);
+            std::memcpy(m->tap_hidden.data() + l * h, hidden.data(), h * sizeof(float));
+            continue;
+        }
         act.populate(norm.data(), h);
         L.gate_up.gemv(act.q.data(), act.s.data(), act.m.data(), gu.data(), threads);
         for (size_t i = 0; i < inter; ++i) {       // swiglu_activate_neon (9811-9842): inter is a multiple of 8

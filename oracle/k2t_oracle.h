@@ -153,6 +153,19 @@ void k2o_model_free(K2oModel *m);
 int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const float *post_norm, const float *qkv_bias,
                         const float *q_norm, const float *k_norm, const K2oMatrixDesc *qkv, const K2oMatrixDesc *o,
                         const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down);
+/* Makes layer l a sparse-MoE layer (its dense gate_up / down are ignored): router [n_experts][hidden] fp32 (+ optional
+ * bias), softmax scoring, top_k with optional renormalisation (DenseMoeRouter::route_sorted, sparse_moe.rs:86-206), experts
+ * as .k2tm records (nf_expert_byte_layout / pack_nf_expert_record, moe_800b.rs:1330-1407): record e of `shard` starts at
+ * e * expert_bytes.  Forward = SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084) with the zero-copy NF
+ * expert (MmapNfExpertView::forward_swiglu_zero_copy, moe_800b.rs:1440-1563). */
+int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const float *router_bias, uint32_t n_experts,
+                      uint32_t top_k, int norm_topk, uint32_t d_ff, uint32_t bits, uint32_t scale_group_chunks,
+                      const uint8_t *shard, size_t expert_bytes);
+/* Routes of the last token through MoE layer l: up to 32 (expert, weight) pairs sorted by expert id; returns k. */
+uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts, float *weights);
+/* .k2tm record geometry (NfExpertByteLayout): returns aligned_expert_bytes, fills the pair-stream offsets / sizes. */
+size_t k2o_nf_expert_layout(size_t d_model, size_t d_ff, size_t bits, size_t sgc, size_t *gu_pair_off, size_t *gu_pair_bytes,
+                            size_t *dn_pair_off, size_t *dn_pair_bytes);
 int k2o_model_set_head(K2oModel *m, const float *final_norm, const K2oMatrixDesc *lm_head, const uint16_t *embed_bf16);
 void k2o_model_reset(K2oModel *m);
 size_t k2o_model_pos(const K2oModel *m);

@@ -412,6 +412,11 @@ def _declare_model(L):
     L.k2o_model_forward_embedding.restype, L.k2o_model_forward_embedding.argtypes = C.c_int, [P, P, P, C.c_size_t]
     L.k2o_model_forward_token.restype, L.k2o_model_forward_token.argtypes = C.c_int, [P, C.c_uint32, P, C.c_size_t]
     L.k2o_model_tap_hidden.restype, L.k2o_model_tap_hidden.argtypes = P, [P]
+    L.k2o_model_set_moe.restype = C.c_int
+    L.k2o_model_set_moe.argtypes = [P, C.c_uint32, P, P, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, P, C.c_size_t]
+    L.k2o_model_last_routes.restype, L.k2o_model_last_routes.argtypes = C.c_uint32, [P, C.c_uint32, P, P]
+    L.k2o_nf_expert_layout.restype = C.c_size_t
+    L.k2o_nf_expert_layout.argtypes = [C.c_size_t] * 4 + [P] * 4
     L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
     L.k2o_model_read_kv.restype, L.k2o_model_read_kv.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
     L.k2o_model_read_kv_q4.restype, L.k2o_model_read_kv_q4.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
@@ -458,6 +463,29 @@ def head_rms_norm(buf, heads, head_dim, w, eps):
     return b
 
 
+def nf_expert_layout(d_model, d_ff, bits, sgc):
+    """NfExpertByteLayout of a .k2tm record: dict(expert_bytes, gu_off, gu_bytes, dn_off, dn_bytes)."""
+    L = lib(); _declare_model(L)
+    v = [C.c_size_t() for _ in range(4)]
+    total = L.k2o_nf_expert_layout(d_model, d_ff, bits, sgc, *[C.byref(x) for x in v])
+    return dict(expert_bytes=total, gu_off=v[0].value, gu_bytes=v[1].value, dn_off=v[2].value, dn_bytes=v[3].value)
+
+
+def pack_expert_shard(experts, d_model, d_ff, bits, sgc):
+    """pack_nf_expert_record (moe_800b.rs:1385-1407) for a list of (gate_up Nf, down Nf): codebooks at 0 / 16, gate_up
+    pair_stream at 64, down pair_stream at the next multiple of 64, zero-padded to a 16 KiB multiple per record."""
+    lay = nf_expert_layout(d_model, d_ff, bits, sgc)
+    shard = np.zeros(len(experts) * lay["expert_bytes"], np.uint8)
+    for e, (gu, dn) in enumerate(experts):
+        assert gu.tail.size == 0 and dn.tail.size == 0 and gu.pair.size == lay["gu_bytes"] and dn.pair.size == lay["dn_bytes"]
+        rec = shard[e * lay["expert_bytes"]:(e + 1) * lay["expert_bytes"]]
+        rec[0:16] = np.asarray(gu.codebook, np.int8).view(np.uint8)
+        rec[16:32] = np.asarray(dn.codebook, np.int8).view(np.uint8)
+        rec[lay["gu_off"]:lay["gu_off"] + lay["gu_bytes"]] = gu.pair
+        rec[lay["dn_off"]:lay["dn_off"] + lay["dn_bytes"]] = dn.pair
+    return shard, lay
+
+
 def kv_quant_head_q4(src):
     L = lib(); _declare_model(L)
     x = _c(src, np.float32)
@@ -499,10 +527,19 @@ class Model:
         self.h = L.k2o_model_new(C.byref(self.cfg), _ptr(rope))
         assert self.h, "k2o_model_new failed"
         for l, ly in enumerate(spec["layers"]):
-            ds = [desc_of(ly[k]) for k in ("qkv", "o", "gate_up", "down")]
+            moe = ly.get("moe")
+            ds = [desc_of(ly[k]) for k in (("qkv", "o") if moe else ("qkv", "o", "gate_up", "down"))]
             arrs = [None if ly.get(k) is None else _c(ly[k], np.float32) for k in ("input_norm", "post_norm", "qkv_bias", "q_norm", "k_norm")]
-            rc = L.k2o_model_set_layer(self.h, l, *[_ptr(a) for a in arrs], *[C.byref(d) for d in ds])
+            refs = [C.byref(d) for d in ds] + ([None, None] if moe else [])
+            rc = L.k2o_model_set_layer(self.h, l, *[_ptr(a) for a in arrs], *refs)
             assert rc == 0, f"set_layer {l} failed"
+            if moe:
+                rw = _c(moe["router_w"], np.float32)
+                rb = None if moe.get("router_bias") is None else _c(moe["router_bias"], np.float32)
+                shard = _c(moe["shard"], np.uint8)
+                rc = L.k2o_model_set_moe(self.h, l, _ptr(rw), _ptr(rb), moe["n_experts"], moe["top_k"], int(moe["norm_topk"]), moe["d_ff"],
+                                         moe["bits"], moe["sgc"], _ptr(shard), moe["expert_bytes"])
+                assert rc == 0, f"set_moe {l} failed"
         emb = None if spec.get("embed_bf16") is None else _c(spec["embed_bf16"], np.uint16)
         d = desc_of(spec["lm_head"])
         fn = _c(spec["final_norm"], np.float32)
@@ -540,6 +577,11 @@ class Model:
         p = self.L.k2o_model_tap_hidden(self.h)
         n = self.cfg.layers * self.cfg.hidden
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).reshape(self.cfg.layers, self.cfg.hidden).copy()
+
+    def last_routes(self, layer):
+        e, w = np.zeros(32, np.uint32), np.zeros(32, np.float32)
+        k = self.L.k2o_model_last_routes(self.h, layer, _ptr(e), _ptr(w))
+        return e[:k].copy(), w[:k].copy()
 
     def tap_attention(self):
         p = self.L.k2o_model_tap_attention(self.h)

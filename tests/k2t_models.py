@@ -25,8 +25,27 @@ def quantize(oracle, w, mode):
     return oracle.nf_quantize_rtn(w, bits, 2 if mode.endswith("g128") else 1)
 
 
-def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=True, head_mode=None, modes=None):
-    """modes: optional dict {qkv, o, gate_up, down, head} overriding `mode` per matrix (e.g. p55454)."""
+MOE_TINY = dict(hidden=128, layers=3, n_q=4, n_kv=2, head_dim=64, inter=256, vocab=320, max_seq=96, eps=1e-6, theta=1e6)
+
+
+def build_moe(oracle, seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk=True, bias=False):
+    """One sparse-MoE FFN: router N(0, 0.02) (near-uniform routing) and NF experts in .k2tm record form."""
+    experts = []
+    mode = ("e8q2" if bits == 2 else f"nf{bits}") + ("g128" if sgc == 2 else "")     # bits = 2: E8 lattice codewords
+    for e in range(n_experts):
+        gu = quantize(oracle, normal(seed + 2 * e, (2 * d_ff, hidden), 0.02), mode)
+        dn = quantize(oracle, normal(seed + 2 * e + 1, (hidden, d_ff), 0.02), mode)
+        assert gu.sgc == sgc and dn.sgc == sgc
+        experts.append((gu, dn))
+    shard, lay = oracle.pack_expert_shard(experts, hidden, d_ff, bits, sgc)
+    return dict(router_w=normal(seed + 999, (n_experts, hidden), 0.02), router_bias=normal(seed + 998, n_experts, 0.01) if bias else None,
+                n_experts=n_experts, top_k=top_k, norm_topk=norm_topk, d_ff=d_ff, bits=bits, sgc=sgc, shard=shard,
+                expert_bytes=lay["expert_bytes"])
+
+
+def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=True, head_mode=None, modes=None, moe=None):
+    """modes: optional dict {qkv, o, gate_up, down, head} overriding `mode` per matrix (e.g. p55454).
+    moe: optional dict(layers=[...], n_experts, top_k, d_ff, bits, sgc[, norm_topk, bias]): those layers get a sparse-MoE FFN."""
     c = dict(cfg)
     h, hd, inter = c["hidden"], c["head_dim"], c["inter"]
     q_dim, kv_dim = c["n_q"] * hd, c["n_kv"] * hd
@@ -46,6 +65,10 @@ def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=Tr
             gate_up=quantize(oracle, normal(s + 10 * l + 8, (2 * inter, h), 0.02), pick("gate_up")),
             down=quantize(oracle, normal(s + 10 * l + 9, (h, inter), 0.02), pick("down")),
         )
+        if moe and l in moe["layers"]:
+            ly["gate_up"] = ly["down"] = None
+            ly["moe"] = build_moe(oracle, s + 100 * l + 50, h, moe["n_experts"], moe["top_k"], moe["d_ff"], moe["bits"], moe["sgc"],
+                                  moe.get("norm_topk", True), moe.get("bias", False))
         layers.append(ly)
     head_w = normal(s + 999, (c["vocab"], h), 0.02)
     spec = dict(cfg=c, layers=layers, final_norm=(1.0 + 0.1 * normal(s + 998, h)).astype(np.float32),

@@ -101,6 +101,34 @@ def test_nf4_kv_cache_logits_and_entries(ctx, oracle, cfg, mode, kw, decode_path
         eng.close(); ref.close()
 
 
+@pytest.mark.parametrize("mode,moe,kw", [
+    ("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2), dict(qk_norm=True)),        # Qwen3-MoE style: nf3 experts
+    ("b5", dict(layers=[1], n_experts=16, top_k=4, d_ff=128, bits=4, sgc=1, norm_topk=False, bias=True), dict(qkv_bias=True)),
+    ("nf4", dict(layers=[0, 1, 2], n_experts=6, top_k=6, d_ff=64, bits=5, sgc=2), {}),                          # every expert routed
+    ("b4", dict(layers=[2], n_experts=4, top_k=2, d_ff=128, bits=2, sgc=2), {}),                                # E8Q2 experts
+])
+def test_sparse_moe_layers_match_oracle(ctx, oracle, mode, moe, kw):
+    """Router (softmax, top-k, renormalisation, expert order), .k2tm expert records, expert SwiGLU and the weighted sum."""
+    spec, eng, ref = make(ctx, oracle, km.MOE_TINY, mode, seed=17, moe=moe, **kw)
+    try:
+        rng = np.random.Generator(np.random.PCG64(9))
+        tokens = [int(t) for t in rng.integers(0, km.MOE_TINY["vocab"], 23)]
+        want = np.stack([ref.forward_token(t, threads=2) for t in tokens])
+        got = eng.forward_token_ids(tokens, want_all=True)
+        assert np.array_equal(got, want)
+        for l in moe["layers"]:
+            ge, gw = eng.read_routes(l)
+            we, ww = ref.last_routes(l)
+            assert np.array_equal(ge, we) and np.array_equal(gw, ww), (l, ge, we)
+            assert len(ge) == min(moe["top_k"], moe["n_experts"]) and list(ge) == sorted(ge)
+        assert len(eng.read_routes([l for l in range(3) if l not in moe["layers"]][0])[0]) == 0 if len(moe["layers"]) < 3 else True
+        assert np.array_equal(eng.read_hidden(), ref.tap_hidden()[-1])
+        ref.reset()
+        _greedy_check(eng, ref, tokens[:5], 30)
+    finally:
+        eng.close(); ref.close()
+
+
 def test_host_embeddings_equal_device_lookup(ctx, oracle):
     spec, eng, ref = make(ctx, oracle, km.TINY, "b5", seed=4)
     try:
