@@ -225,6 +225,32 @@ size_t kronos_cuda_engine_decode_trace(KronosCudaEngine *engine, uint64_t *marks
 int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *engine, uint32_t layer, uint32_t kv_head, size_t position,
                                    int8_t *k_q8, float *k_scale, int8_t *v_q8, float *v_scale);
 
+/* ---- .k2tb compiled-model container ---------------------------------------------------------- */
+
+/* Reader / writer of the reference's dense cache file (RealLlamaEngine::save_bipolar / load_bipolar,
+ * real_llm.rs:3705-3895, 3902-4186; magics K2TBIPOLAR1, K2TKRONOS2/3/4/6).  Host code, no GPU needed.  The descriptors
+ * handed out point into storage owned by the handle and stay valid until kronos_cuda_k2tb_close; they are exactly what
+ * kronos_cuda_engine_create takes, so a cached model runs with no recompile.  Shapes (heads, head_dim, ...) are not in
+ * the file: they come from the model's config.json as in the reference.  VQ2 / Q2c matrices and the sparse-MoE core
+ * (K2TKRONOS5) are rejected.  Errors: NULL / -1 and kronos_cuda_k2tb_last_error() (per thread). */
+typedef struct KronosCudaK2tb KronosCudaK2tb;
+KronosCudaK2tb *kronos_cuda_k2tb_open(const char *path);
+void kronos_cuda_k2tb_close(KronosCudaK2tb *file);
+const char *kronos_cuda_k2tb_last_error(void);
+/* version = 1, 2, 3, 4 or 6; mode_words = the six RealWeightMode words (real_llm.rs:3805-3829). */
+int32_t kronos_cuda_k2tb_info(const KronosCudaK2tb *file, uint32_t *version, uint64_t mode_words[6], size_t *n_layers);
+/* Layer l as a KronosCudaLayerDesc (MoE fields NULL); qkv_bias_len = elements of the bias (0 = none). */
+int32_t kronos_cuda_k2tb_layer(const KronosCudaK2tb *file, size_t l, KronosCudaLayerDesc *out, size_t *qkv_bias_len);
+int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *file, const float **final_norm, size_t *final_norm_len,
+                              KronosCudaMatrixDesc *lm_head, const uint16_t **embed_bf16, size_t *embed_bf16_len,
+                              const float **embed_f32, size_t *embed_f32_len);
+/* Writes a container the reference's load_bipolar reads: the version follows save_bipolar's rule (6 with q/k norms, 3 with
+ * a qkv bias or a bf16 embedding table, 2 with NF matrices, else 1).  hidden / qkv_rows / head_dim give the lengths of the
+ * per-layer vectors. */
+int32_t kronos_cuda_k2tb_save(const char *path, const uint64_t mode_words[6], const KronosCudaLayerDesc *layers, size_t n_layers,
+                              size_t hidden, size_t qkv_rows, size_t head_dim, const float *final_norm,
+                              const KronosCudaMatrixDesc *lm_head, const uint16_t *embed_bf16, size_t embed_bf16_len);
+
 /* ---- no-allocation variant ------------------------------------------------------------------- */
 
 /* Widest matrix (columns) kronos_cuda_linear_noalloc accepts, and the bytes of device memory its

@@ -10,6 +10,8 @@ from .ffi import (  # noqa: F401
     Matrix,
     MatrixDesc,
     bipolar_desc,
+    k2tb_load,
+    k2tb_save,
     matrix_image,
     nf_desc,
     lib_path,

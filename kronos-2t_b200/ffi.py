@@ -91,6 +91,15 @@ def load_library():
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
     sig("kronos_cuda_engine_read_routes", sz, vp, u32, vp, vp)
+    sig("kronos_cuda_k2tb_open", vp, C.c_char_p)
+    sig("kronos_cuda_k2tb_close", None, vp)
+    sig("kronos_cuda_k2tb_last_error", C.c_char_p)
+    sig("kronos_cuda_k2tb_info", i32, vp, C.POINTER(u32), C.POINTER(u64 * 6), C.POINTER(sz))
+    sig("kronos_cuda_k2tb_layer", i32, vp, sz, C.POINTER(LayerDesc), C.POINTER(sz))
+    sig("kronos_cuda_k2tb_head", i32, vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(MatrixDesc), C.POINTER(vp), C.POINTER(sz),
+        C.POINTER(vp), C.POINTER(sz))
+    sig("kronos_cuda_k2tb_save", i32, C.c_char_p, C.POINTER(u64 * 6), C.POINTER(LayerDesc), sz, sz, sz, sz, vp,
+        C.POINTER(MatrixDesc), vp, sz)
     sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
     sig("kronos_cuda_engine_read_kv_q4", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
@@ -379,3 +388,89 @@ class Engine:
         ks, vs = np.empty(1, np.float32), np.empty(1, np.float32)
         self.ctx._check(self.L.kronos_cuda_engine_read_kv(self.handle, layer, kv_head, position, _p(k), _p(ks), _p(v), _p(vs)))
         return k, float(ks[0]), v, float(vs[0])
+
+
+# ---- .k2tb container (host only)
+class _HostMatrix:
+    """Matrix read from a container: the fields desc_of (and the CPU oracle) read."""
+
+    def __init__(self, d):
+        self.kind, self.rows, self.cols = d.kind, d.rows, d.cols
+        a = np.ctypeslib.as_array(C.cast(d.data0, C.POINTER(C.c_uint8)), shape=(d.len0,)).copy() if d.len0 else np.zeros(0, np.uint8)
+        b = np.ctypeslib.as_array(C.cast(d.data1, C.POINTER(C.c_uint8)), shape=(d.len1,)).copy() if d.len1 else np.zeros(0, np.uint8)
+        if d.kind == MATRIX_BIPOLAR:
+            self.planes, self.data, self.scales = d.bits, a, b.view(np.uint16)
+        else:
+            self.bits, self.sgc, self.pair, self.tail = d.bits, d.scale_group_chunks, a, b
+            self.codebook = np.array([d.codebook[i] for i in range(16)], np.int8)
+
+    def file_bytes(self):
+        return self.data.nbytes + self.scales.nbytes if self.kind == MATRIX_BIPOLAR else self.pair.nbytes + self.tail.nbytes + 16
+
+
+def _f32(ptr, n):
+    return None if not ptr or n == 0 else np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_float)), shape=(n,)).copy()
+
+
+def k2tb_load(path, cfg, rope):
+    """Reads a .k2tb dense container into an engine spec (cfg = shapes from the model's config.json, rope = its rope table).
+    Returns (spec, version, mode_words)."""
+    L = load_library()
+    h = L.kronos_cuda_k2tb_open(os.fsencode(path))
+    if not h:
+        raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())
+    try:
+        ver, mode, nl = C.c_uint32(), (C.c_uint64 * 6)(), C.c_size_t()
+        L.kronos_cuda_k2tb_info(h, C.byref(ver), C.byref(mode), C.byref(nl))
+        hd, hid = cfg["head_dim"], cfg["hidden"]
+        layers = []
+        for l in range(nl.value):
+            d, nb = LayerDesc(), C.c_size_t()
+            L.kronos_cuda_k2tb_layer(h, l, C.byref(d), C.byref(nb))
+            layers.append(dict(input_norm=_f32(d.input_norm, hid), post_norm=_f32(d.post_attn_norm, hid), qkv_bias=_f32(d.qkv_bias, nb.value),
+                               q_norm=_f32(d.q_norm, hd), k_norm=_f32(d.k_norm, hd), qkv=_HostMatrix(d.qkv_proj), o=_HostMatrix(d.o_proj),
+                               gate_up=_HostMatrix(d.gate_up_proj), down=_HostMatrix(d.down_proj)))
+        fn, fnl, emb, embl, ef, efl = C.c_void_p(), C.c_size_t(), C.c_void_p(), C.c_size_t(), C.c_void_p(), C.c_size_t()
+        head = MatrixDesc()
+        L.kronos_cuda_k2tb_head(h, C.byref(fn), C.byref(fnl), C.byref(head), C.byref(emb), C.byref(embl), C.byref(ef), C.byref(efl))
+        embed = None
+        if embl.value:
+            embed = np.ctypeslib.as_array(C.cast(emb, C.POINTER(C.c_uint16)), shape=(embl.value,)).copy()
+        spec = dict(cfg=dict(cfg, layers=nl.value), layers=layers, final_norm=_f32(fn, fnl.value), lm_head=_HostMatrix(head), rope=rope,
+                    embed_bf16=embed)
+        return spec, ver.value, [int(x) for x in mode]
+    finally:
+        L.kronos_cuda_k2tb_close(h)
+
+
+def k2tb_save(path, spec, mode_words):
+    """Writes an engine spec as a .k2tb dense container (version chosen as the reference's save_bipolar does)."""
+    L = load_library()
+    c = spec["cfg"]
+    keep = []
+
+    def vec(a):
+        if a is None:
+            return None
+        a = _np(a, np.float32)
+        keep.append(a)
+        return a.ctypes.data
+
+    layers = (LayerDesc * len(spec["layers"]))()
+    for l, ly in enumerate(spec["layers"]):
+        d = layers[l]
+        d.input_norm, d.post_attn_norm = vec(ly["input_norm"]), vec(ly["post_norm"])
+        d.qkv_bias, d.q_norm, d.k_norm = vec(ly.get("qkv_bias")), vec(ly.get("q_norm")), vec(ly.get("k_norm"))
+        for name, key in (("qkv_proj", "qkv"), ("o_proj", "o"), ("gate_up_proj", "gate_up"), ("down_proj", "down")):
+            md = desc_of(ly[key])
+            keep.append(md._keep)
+            setattr(d, name, md)
+    head = desc_of(spec["lm_head"])
+    fn = _np(spec["final_norm"], np.float32)
+    emb = None if spec.get("embed_bf16") is None else _np(spec["embed_bf16"], np.uint16).reshape(-1)
+    words = (C.c_uint64 * 6)(*mode_words)
+    qkv_rows = (c["n_q"] + 2 * c["n_kv"]) * c["head_dim"]
+    rc = L.kronos_cuda_k2tb_save(os.fsencode(path), C.byref(words), layers, len(spec["layers"]), c["hidden"], qkv_rows, c["head_dim"], _p(fn),
+                                 C.byref(head), _p(emb), 0 if emb is None else emb.size)
+    if rc != 0:
+        raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())
