@@ -469,6 +469,29 @@ def decode_tok_s(ctx, stream, timed_region, world):
     return out
 
 
+def run_decode_only(args, local_rank):
+    """Small whole-token run for profilers: engine of the decode workload's shape, 16-token prompt, N greedy steps."""
+    import numpy as np
+    import torch
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    ctx = k2.Context(local_rank)
+    eng = k2.Engine(ctx, synth.random_model(synth.SMOLLM2_135M, "b4", seed=3))
+    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, synth.SMOLLM2_135M["vocab"], 16).astype(np.uint32)
+    l0 = ctx.launch_count
+    eng.forward_token_ids(prompt[:-1])
+    l1 = ctx.launch_count
+    t0 = time.perf_counter()
+    toks = eng.decode_greedy(int(prompt[-1]), 15, args.decode_only)
+    dt = time.perf_counter() - t0
+    print(json.dumps({"mode": "decode-only", "steps": args.decode_only, "prompt_launches": int(l1 - l0),
+                      "decode_launches": int(ctx.launch_count - l1), "wall_ms": dt * 1e3, "last_token": int(toks[-1])}))
+    eng.close()
+    ctx.close()
+
+
 def cpu_decode_baseline():
     """The oracle's dense decode step on the same model shape, all host threads: 16 prompt tokens, 16 greedy steps."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -529,6 +552,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode measurement")
+    ap.add_argument("--decode-only", type=int, default=0, metavar="N",
+                    help="profiling mode: only the whole-token engine - a 16-token prompt, then N greedy steps")
     ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")
     ap.add_argument("--tokens", type=int, default=1, help="tokens per launch in --case mode (1..4)")
     ap.add_argument("--no-graph", action="store_true", help="--case mode: skip the CUDA-graph replay timing")
@@ -536,7 +561,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.case:
+    if args.decode_only:
+        run_decode_only(args, local_rank)
+    elif args.case:
         run_case(args, local_rank)
     elif args.impl == "reference":
         run_reference(args, rank, world)

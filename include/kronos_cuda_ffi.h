@@ -199,6 +199,15 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *engine, uint32_t firs
                                          size_t n_steps, uint32_t *out_tokens, float *last_logits);
 /* kv_cache_bytes (metal_gpu.rs:1454-1617 family): bytes of KV cache held for `positions` positions. */
 size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *engine, size_t positions);
+/* KV blobs in the reference's position-major export format (export_kv_positions / import_kv_positions, real_llm.rs:6213-6291;
+ * KvSlotPtrs::export / import, src/model/kv_blob.rs:47-110): per position, per (layer, kv head): key row, key scale(s),
+ * value row, value scale(s); kv_bytes_per_pos = 2 * layers * kv_heads * (row + scale bytes) (12,240 / 6,120 B for the 135M
+ * shape with the int8 / NF4 cache).  A blob exported by the CPU engine imports here and vice versa (same kv_bits).
+ * kv_export writes positions [lo, hi) and returns the byte count (-1 on error); kv_import restores positions [0, n).
+ * Truncating a context needs no call: the host just continues at an earlier pos_start (truncate_context, 6294-6296). */
+size_t kronos_cuda_engine_kv_bytes_per_pos(const KronosCudaEngine *engine);
+int64_t kronos_cuda_engine_kv_export(KronosCudaEngine *engine, size_t lo, size_t hi, uint8_t *out, size_t cap);
+int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *engine, const uint8_t *data, size_t len, size_t n);
 /* Bytes of weights (reference file format) one decode step streams: all layer matrices + lm_head. */
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
 /* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */

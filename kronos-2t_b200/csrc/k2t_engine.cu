@@ -580,6 +580,73 @@ int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *e, uint32_t layer, uint3
     return sync_and_check(ctx, "read_kv_q4") ? 0 : -1;
 }
 
+// ---- KV blobs: the reference's position-major export format (KvSlotPtrs::export / import, src/model/kv_blob.rs:47-110):
+// for every position, for every (layer, kv head): key row, key scale(s), value row, value scale(s).
+static size_t kv_row_bytes(const KronosCudaEngine *e) { return e->cfg.kv_bits == 4 ? e->cfg.head_dim / 2 : e->cfg.head_dim; }
+static size_t kv_scale_bytes(const KronosCudaEngine *e) { return e->cfg.kv_bits == 4 ? 2 * (e->cfg.head_dim / 64) : 4; }
+
+size_t kronos_cuda_engine_kv_bytes_per_pos(const KronosCudaEngine *e) {
+    return e ? 2 * (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads * (kv_row_bytes(e) + kv_scale_bytes(e)) : 0;
+}
+
+int64_t kronos_cuda_engine_kv_export(KronosCudaEngine *e, size_t lo, size_t hi, uint8_t *out, size_t cap) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (lo > hi || hi > e->cfg.max_seq_len) return fail(ctx, "kv_export: position range out of bounds"), -1;
+    const size_t n = hi - lo, heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e);
+    const size_t total = n * kronos_cuda_engine_kv_bytes_per_pos(e);
+    if (n == 0) return 0;
+    if (!out || cap < total) return fail(ctx, "kv_export: output buffer too small"), -1;
+    if (!make_current(ctx)) return -1;
+    std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
+    const size_t S = e->cfg.max_seq_len;
+    cudaStream_t st = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpy2DAsync(kd.data(), n * db, reinterpret_cast<uint8_t *>(e->k_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(vd.data(), n * db, reinterpret_cast<uint8_t *>(e->v_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(ks.data(), n * sb, reinterpret_cast<uint8_t *>(e->k_scale) + lo * sb, S * sb, n * sb, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(vs.data(), n * sb, reinterpret_cast<uint8_t *>(e->v_scale) + lo * sb, S * sb, n * sb, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+        !sync_and_check(ctx, "kv_export"))
+        return -1;
+    uint8_t *w = out;
+    for (size_t p = 0; p < n; ++p)
+        for (size_t h = 0; h < heads; ++h) {
+            std::memcpy(w, kd.data() + (h * n + p) * db, db); w += db;
+            std::memcpy(w, ks.data() + (h * n + p) * sb, sb); w += sb;
+            std::memcpy(w, vd.data() + (h * n + p) * db, db); w += db;
+            std::memcpy(w, vs.data() + (h * n + p) * sb, sb); w += sb;
+        }
+    return (int64_t)total;
+}
+
+int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, size_t len, size_t n) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (n > e->cfg.max_seq_len) return fail(ctx, "kv_import: more positions than max_seq_len"), -1;
+    if (n == 0) return 0;
+    if (!data || len < n * kronos_cuda_engine_kv_bytes_per_pos(e)) return fail(ctx, "kv_import: blob is shorter than n positions"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->cfg.max_seq_len;
+    std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
+    const uint8_t *r = data;
+    for (size_t p = 0; p < n; ++p)
+        for (size_t h = 0; h < heads; ++h) {
+            std::memcpy(kd.data() + (h * n + p) * db, r, db); r += db;
+            std::memcpy(ks.data() + (h * n + p) * sb, r, sb); r += sb;
+            std::memcpy(vd.data() + (h * n + p) * db, r, db); r += db;
+            std::memcpy(vs.data() + (h * n + p) * sb, r, sb); r += sb;
+        }
+    cudaStream_t st = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpy2DAsync(e->k_q8, S * db, kd.data(), n * db, n * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd.data(), n * db, n * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks.data(), n * sb, n * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs.data(), n * sb, n * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+        !sync_and_check(ctx, "kv_import"))
+        return -1;
+    return 0;
+}
+
 static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const uint32_t *tokens, size_t n_tok, size_t pos_start,
                               float *all_logits, float *last_logits) {
     if (!e) return -1;

@@ -91,6 +91,9 @@ def load_library():
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
     sig("kronos_cuda_engine_read_routes", sz, vp, u32, vp, vp)
+    sig("kronos_cuda_engine_kv_bytes_per_pos", sz, vp)
+    sig("kronos_cuda_engine_kv_export", C.c_int64, vp, sz, sz, vp, sz)
+    sig("kronos_cuda_engine_kv_import", i32, vp, vp, sz, sz)
     sig("kronos_cuda_k2tb_open", vp, C.c_char_p)
     sig("kronos_cuda_k2tb_close", None, vp)
     sig("kronos_cuda_k2tb_last_error", C.c_char_p)
@@ -359,6 +362,22 @@ class Engine:
         out = np.empty(self.cfg.hidden_size, np.float32)
         self.ctx._check(self.L.kronos_cuda_engine_read_hidden(self.handle, _p(out)))
         return out
+
+    @property
+    def kv_bytes_per_pos(self):
+        return self.L.kronos_cuda_engine_kv_bytes_per_pos(self.handle)
+
+    def kv_export(self, lo, hi):
+        """Positions [lo, hi) as a blob in the reference's position-major format."""
+        out = np.empty((hi - lo) * self.kv_bytes_per_pos, np.uint8)
+        n = self.L.kronos_cuda_engine_kv_export(self.handle, lo, hi, _p(out), out.size)
+        if n < 0:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(self.ctx.handle).decode())
+        return out[:n]
+
+    def kv_import(self, blob, n):
+        b = _np(blob, np.uint8)
+        self.ctx._check(self.L.kronos_cuda_engine_kv_import(self.handle, _p(b), b.size, n))
 
     def read_routes(self, layer):
         e, w = np.zeros(32, np.uint32), np.zeros(32, np.float32)

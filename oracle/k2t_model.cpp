@@ -504,6 +504,47 @@ void k2o_model_embed(const K2oModel *m, uint32_t token, float *out) {
 
 const float *k2o_model_tap_hidden(const K2oModel *m) { return m->tap_hidden.data(); }
 const float *k2o_model_tap_attention(const K2oModel *m) { return m->tap_attn.data(); }
+size_t k2o_model_kv_export(const K2oModel *m, size_t lo, size_t hi, uint8_t *out) {
+    if (!m || lo > hi || hi > m->cfg.max_seq) return 0;
+    const bool q4 = m->cfg.kv_bits == 4;
+    const size_t hd = m->cfg.head_dim, heads = (size_t)m->cfg.layers * m->cfg.n_kv, db = q4 ? hd / 2 : hd, sb = q4 ? 2 * (hd / 64) : 4;
+    const size_t total = (hi - lo) * 2 * heads * (db + sb);
+    if (!out) return total;
+    const uint8_t *kd = q4 ? m->k_q4.data() : reinterpret_cast<const uint8_t *>(m->k_q8.data());
+    const uint8_t *vd = q4 ? m->v_q4.data() : reinterpret_cast<const uint8_t *>(m->v_q8.data());
+    const uint8_t *ks = q4 ? reinterpret_cast<const uint8_t *>(m->k_s16.data()) : reinterpret_cast<const uint8_t *>(m->k_sc.data());
+    const uint8_t *vs = q4 ? reinterpret_cast<const uint8_t *>(m->v_s16.data()) : reinterpret_cast<const uint8_t *>(m->v_sc.data());
+    for (size_t p = lo; p < hi; ++p)
+        for (size_t h = 0; h < heads; ++h) {
+            const size_t slot = h * m->cfg.max_seq + p;
+            std::memcpy(out, kd + slot * db, db); out += db;
+            std::memcpy(out, ks + slot * sb, sb); out += sb;
+            std::memcpy(out, vd + slot * db, db); out += db;
+            std::memcpy(out, vs + slot * sb, sb); out += sb;
+        }
+    return total;
+}
+
+int k2o_model_kv_import(K2oModel *m, const uint8_t *data, size_t len, size_t n) {
+    if (!m || !data || n > m->cfg.max_seq || len < k2o_model_kv_export(m, 0, n, nullptr)) return -1;
+    const bool q4 = m->cfg.kv_bits == 4;
+    const size_t hd = m->cfg.head_dim, heads = (size_t)m->cfg.layers * m->cfg.n_kv, db = q4 ? hd / 2 : hd, sb = q4 ? 2 * (hd / 64) : 4;
+    uint8_t *kd = q4 ? m->k_q4.data() : reinterpret_cast<uint8_t *>(m->k_q8.data());
+    uint8_t *vd = q4 ? m->v_q4.data() : reinterpret_cast<uint8_t *>(m->v_q8.data());
+    uint8_t *ks = q4 ? reinterpret_cast<uint8_t *>(m->k_s16.data()) : reinterpret_cast<uint8_t *>(m->k_sc.data());
+    uint8_t *vs = q4 ? reinterpret_cast<uint8_t *>(m->v_s16.data()) : reinterpret_cast<uint8_t *>(m->v_sc.data());
+    for (size_t p = 0; p < n; ++p)
+        for (size_t h = 0; h < heads; ++h) {
+            const size_t slot = h * m->cfg.max_seq + p;
+            std::memcpy(kd + slot * db, data, db); data += db;
+            std::memcpy(ks + slot * sb, data, sb); data += sb;
+            std::memcpy(vd + slot * db, data, db); data += db;
+            std::memcpy(vs + slot * sb, data, sb); data += sb;
+        }
+    m->pos = n;
+    return 0;
+}
+
 int k2o_model_read_kv_q4(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, uint8_t *k_q4, uint16_t *k_s16,
                          uint8_t *v_q4, uint16_t *v_s16) {
     if (!m || m->cfg.kv_bits != 4 || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;

@@ -185,6 +185,11 @@ int k2o_model_read_kv_q4(const K2oModel *m, uint32_t layer, uint32_t kv_head, si
 /* store_hadamard_q4_head_raw (real_llm.rs:8646-8701) on one head: packed NF4 indices and one bf16 scale per 64 values. */
 void k2o_kv_quant_head_q4(const float *src, size_t head_dim, uint8_t *q4, uint16_t *s16);
 uint8_t k2o_nf4_nearest_idx(float y);
+/* KV blob of positions [lo, hi) in the position-major export format (KvSlotPtrs::export, src/model/kv_blob.rs:63-81): per
+ * position, per (layer, kv head): key row, key scale(s), value row, value scale(s).  Returns the byte count; with out ==
+ * NULL only the count.  k2o_model_kv_import restores positions [0, n) and sets the position to n. */
+size_t k2o_model_kv_export(const K2oModel *m, size_t lo, size_t hi, uint8_t *out);
+int k2o_model_kv_import(K2oModel *m, const uint8_t *data, size_t len, size_t n);
 /* One KV cache slot (layer, kv head, position): int8 rotated values [head_dim] and fp32 scales. */
 int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, int8_t *k_q8, float *k_scale,
                       int8_t *v_q8, float *v_scale);

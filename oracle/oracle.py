@@ -419,6 +419,8 @@ def _declare_model(L):
     L.k2o_nf_expert_layout.argtypes = [C.c_size_t] * 4 + [P] * 4
     L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
     L.k2o_model_read_kv.restype, L.k2o_model_read_kv.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
+    L.k2o_model_kv_export.restype, L.k2o_model_kv_export.argtypes = C.c_size_t, [P, C.c_size_t, C.c_size_t, P]
+    L.k2o_model_kv_import.restype, L.k2o_model_kv_import.argtypes = C.c_int, [P, P, C.c_size_t, C.c_size_t]
     L.k2o_model_read_kv_q4.restype, L.k2o_model_read_kv_q4.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
     L.k2o_kv_quant_head_q4.restype, L.k2o_kv_quant_head_q4.argtypes = None, [P, C.c_size_t, P, P]
     L.k2o_nf4_nearest_idx.restype, L.k2o_nf4_nearest_idx.argtypes = C.c_uint8, [C.c_float]
@@ -577,6 +579,16 @@ class Model:
         p = self.L.k2o_model_tap_hidden(self.h)
         n = self.cfg.layers * self.cfg.hidden
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).reshape(self.cfg.layers, self.cfg.hidden).copy()
+
+    def kv_export(self, lo, hi):
+        n = self.L.k2o_model_kv_export(self.h, lo, hi, None)
+        out = np.zeros(n, np.uint8)
+        self.L.k2o_model_kv_export(self.h, lo, hi, _ptr(out))
+        return out
+
+    def kv_import(self, blob, n):
+        b = _c(blob, np.uint8)
+        assert self.L.k2o_model_kv_import(self.h, _ptr(b), b.size, n) == 0
 
     def last_routes(self, layer):
         e, w = np.zeros(32, np.uint32), np.zeros(32, np.float32)

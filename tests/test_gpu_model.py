@@ -265,6 +265,45 @@ def test_greedy_smollm2_135m_shape_128_steps(ctx, oracle, decode_path):
         eng.close(); ref.close()
 
 
+@pytest.mark.parametrize("kv_bits", [8, 4])
+def test_kv_blob_export_import_and_truncation(ctx, oracle, kv_bits):
+    """KV blobs in the reference's position-major format move between the CPU engine and the device: equal bytes for the same
+    prompt, a session restored from a CPU blob continues identically, and a truncated context is just an earlier pos_start."""
+    cfg = dict(km.TINY, kv_bits=kv_bits)
+    spec, eng, ref = make(ctx, oracle, cfg, "b5", seed=23, qkv_bias=True)
+    try:
+        rng = np.random.Generator(np.random.PCG64(4))
+        tokens = [int(t) for t in rng.integers(0, cfg["vocab"], 30)]
+        for t in tokens[:20]:
+            ref.forward_token(t, 2)
+        eng.forward_token_ids(tokens[:20])
+        per_pos = 2 * cfg["layers"] * cfg["n_kv"] * ((cfg["head_dim"] + 4) if kv_bits == 8 else (cfg["head_dim"] // 2 + 2))
+        assert eng.kv_bytes_per_pos == per_pos
+        blob_cpu, blob_gpu = ref.kv_export(0, 20), eng.kv_export(0, 20)
+        assert blob_gpu.size == 20 * per_pos and np.array_equal(blob_cpu, blob_gpu)
+        assert np.array_equal(eng.kv_export(5, 9), blob_cpu[5 * per_pos:9 * per_pos])
+        # a fresh engine restored from the CPU blob continues like the CPU engine
+        import kronos_2t_b200 as k2
+        eng2 = k2.Engine(ctx, spec)
+        try:
+            eng2.kv_import(blob_cpu, 20)
+            want = np.stack([ref.forward_token(t, 2) for t in tokens[20:]])
+            assert np.array_equal(eng2.forward_token_ids(tokens[20:], pos_start=20, want_all=True), want)
+            # truncation: go back to position 12 and replay different tokens on both sides
+            other = [int(t) for t in rng.integers(0, cfg["vocab"], 6)]
+            ref.kv_import(blob_gpu[:12 * per_pos], 12)                 # the CPU engine restored from a device blob
+            want = np.stack([ref.forward_token(t, 2) for t in other])
+            assert np.array_equal(eng2.forward_token_ids(other, pos_start=12, want_all=True), want)
+            with pytest.raises(k2.KronosCudaError, match="shorter"):
+                eng2.kv_import(blob_cpu[:100], 20)
+            with pytest.raises(k2.KronosCudaError, match="out of bounds"):
+                eng2.kv_export(0, cfg["max_seq"] + 1)
+        finally:
+            eng2.close()
+    finally:
+        eng.close(); ref.close()
+
+
 def test_engine_argument_errors(ctx, oracle):
     import kronos_2t_b200 as k2
     spec, eng, ref = make(ctx, oracle, km.TINY, "b4", seed=1)
