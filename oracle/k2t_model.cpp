@@ -324,9 +324,10 @@ struct Act {
     std::vector<int8_t> q;
     std::vector<float> s;
     std::vector<int32_t> m;
-    void populate(const float *x, size_t cols) {   // fwht64_signed_inplace + populate (exec_hidden_proj!, 6521-6562)
+    // fwht64_signed_inplace + populate (exec_hidden_proj!, 6521-6562); chunk0 = global index of the first chunk
+    void populate(const float *x, size_t cols, uint64_t chunk0 = 0) {
         q.resize(cols); s.resize(cols / 64); m.resize(cols / 64);
-        k2o_act_populate_fwht(x, cols, nullptr, 1.0f, 0, q.data(), s.data(), m.data());
+        k2o_act_populate_fwht(x, cols, nullptr, 1.0f, chunk0, q.data(), s.data(), m.data());
     }
 };
 
@@ -570,66 +571,94 @@ int k2o_model_read_kv(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_
 }
 
 // One decode step from an embedding vector (what the device boundary receives); logits[vocab].
-int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads) {
-    if (!m || m->pos >= m->cfg.max_seq) return -1;
+int k2o_model_attn_part(K2oModel *m, uint32_t l, const float *hidden, float *out, size_t threads) {
+    if (!m || l >= m->layers.size() || m->pos >= m->cfg.max_seq) return -1;
     const K2oConfig &c = m->cfg;
-    const size_t h = c.hidden, hd = c.head_dim, q_dim = (size_t)c.n_q * hd, kv_dim = (size_t)c.n_kv * hd, inter = c.inter;
+    const size_t h = c.hidden, hd = c.head_dim, q_dim = (size_t)c.n_q * hd, kv_dim = (size_t)c.n_kv * hd;
     const size_t group = c.n_q / c.n_kv, pos = m->pos;
     const float attn_scale = 1.0f / std::sqrt((float)hd);
     const float *rope_row = m->rope.data() + pos * hd;
-    std::vector<float> hidden(embedding, embedding + h), norm(std::max(h, inter)), qkv(q_dim + 2 * kv_dim), attn(q_dim),
-        proj(h), gu(2 * inter), sw(inter), sc;
+    Layer &L = m->layers[l];
+    std::vector<float> norm(h), qkv(q_dim + 2 * kv_dim), attn(q_dim), sc;
     Act act;
-    m->tap_hidden.assign((size_t)c.layers * h, 0.0f);
-    for (size_t l = 0; l < c.layers; ++l) {
-        Layer &L = m->layers[l];
-        rms_norm(hidden.data(), L.input_norm.data(), h, c.eps, norm.data());
-        act.populate(norm.data(), h);
-        L.qkv.gemv(act.q.data(), act.s.data(), act.m.data(), qkv.data(), threads);
-        if (!L.qkv_bias.empty()) for (size_t i = 0; i < qkv.size(); ++i) qkv[i] = std::fmaf(L.qkv_bias[i], 1.0f, qkv[i]);
-        float *q = qkv.data(), *k = q + q_dim, *v = k + kv_dim;
-        // apply_qk_norm_rope (8139-8165)
-        if (c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
-        if (!L.q_norm.empty()) head_rms_norm(q, c.n_q, hd, L.q_norm.data(), c.eps);
-        if (!L.k_norm.empty()) head_rms_norm(k, c.n_kv, hd, L.k_norm.data(), c.eps);
-        if (!c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
-        for (size_t kvh = 0; kvh < c.n_kv; ++kvh) {
-            size_t slot = m->kv_slot(l, kvh, pos);
-            if (c.kv_bits == 4) {
-                quant_head_q4(k + kvh * hd, hd, m->k_q4.data() + slot * hd / 2, m->k_s16.data() + slot * (hd / 64));
-                quant_head_q4(v + kvh * hd, hd, m->v_q4.data() + slot * hd / 2, m->v_s16.data() + slot * (hd / 64));
-            } else {
-                quant_head(k + kvh * hd, hd, m->k_q8.data() + slot * hd, &m->k_sc[slot]);
-                quant_head(v + kvh * hd, hd, m->v_q8.data() + slot * hd, &m->v_sc[slot]);
-            }
+    rms_norm(hidden, L.input_norm.data(), h, c.eps, norm.data());
+    act.populate(norm.data(), h);
+    L.qkv.gemv(act.q.data(), act.s.data(), act.m.data(), qkv.data(), threads);
+    if (!L.qkv_bias.empty()) for (size_t i = 0; i < qkv.size(); ++i) qkv[i] = std::fmaf(L.qkv_bias[i], 1.0f, qkv[i]);
+    float *q = qkv.data(), *k = q + q_dim, *v = k + kv_dim;
+    // apply_qk_norm_rope (8139-8165)
+    if (c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
+    if (!L.q_norm.empty()) head_rms_norm(q, c.n_q, hd, L.q_norm.data(), c.eps);
+    if (!L.k_norm.empty()) head_rms_norm(k, c.n_kv, hd, L.k_norm.data(), c.eps);
+    if (!c.qk_norm_after_rope) { rope_heads(q, c.n_q, hd, rope_row); rope_heads(k, c.n_kv, hd, rope_row); }
+    for (size_t kvh = 0; kvh < c.n_kv; ++kvh) {
+        size_t slot = m->kv_slot(l, kvh, pos);
+        if (c.kv_bits == 4) {
+            quant_head_q4(k + kvh * hd, hd, m->k_q4.data() + slot * hd / 2, m->k_s16.data() + slot * (hd / 64));
+            quant_head_q4(v + kvh * hd, hd, m->v_q4.data() + slot * hd / 2, m->v_s16.data() + slot * (hd / 64));
+        } else {
+            quant_head(k + kvh * hd, hd, m->k_q8.data() + slot * hd, &m->k_sc[slot]);
+            quant_head(v + kvh * hd, hd, m->v_q8.data() + slot * hd, &m->v_sc[slot]);
         }
-        for (size_t qh = 0; qh < c.n_q; ++qh)
-            (c.kv_bits == 4 ? attend_head_q4 : attend_head)(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
-        if (l + 1 == c.layers) m->tap_attn = attn;
-        act.populate(attn.data(), q_dim);
-        L.o.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
-        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);   // add_inplace = axpy(1.0)
-        rms_norm(hidden.data(), L.post_norm.data(), h, c.eps, norm.data());
-        if (L.moe.on) {                                 // real_llm.rs:6709-6714
-            moe_forward(m->layers[l].moe, norm.data(), h, proj.data(), threads);
-            for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);
-            std::memcpy(m->tap_hidden.data() + l * h, hidden.data(), h * sizeof(float));
-            continue;
-        }
-        act.populate(norm.data(), h);
-        L.gate_up.gemv(act.q.data(), act.s.data(), act.m.data(), gu.data(), threads);
-        for (size_t i = 0; i < inter; ++i) {       // swiglu_activate_neon (9811-9842): inter is a multiple of 8
-            float g = gu[i], u = gu[inter + i];
-            sw[i] = (g / (1.0f + exp_poly(-g))) * u;
-        }
-        act.populate(sw.data(), inter);
-        L.down.gemv(act.q.data(), act.s.data(), act.m.data(), proj.data(), threads);
-        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);
-        std::memcpy(m->tap_hidden.data() + l * h, hidden.data(), h * sizeof(float));
     }
-    rms_norm(hidden.data(), m->final_norm.data(), h, c.eps, norm.data());
+    for (size_t qh = 0; qh < c.n_q; ++qh)
+        (c.kv_bits == 4 ? attend_head_q4 : attend_head)(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
+    if (l + 1 == c.layers) m->tap_attn = attn;
+    act.populate(attn.data(), q_dim, c.o_chunk0);
+    L.o.gemv(act.q.data(), act.s.data(), act.m.data(), out, threads);
+    return 0;
+}
+
+int k2o_model_ffn_part(K2oModel *m, uint32_t l, const float *hidden, float *out, size_t threads) {
+    if (!m || l >= m->layers.size()) return -1;
+    const K2oConfig &c = m->cfg;
+    const size_t h = c.hidden, inter = c.inter;
+    Layer &L = m->layers[l];
+    std::vector<float> norm(h);
+    rms_norm(hidden, L.post_norm.data(), h, c.eps, norm.data());
+    if (L.moe.on) {                                     // real_llm.rs:6709-6714
+        moe_forward(L.moe, norm.data(), h, out, threads);
+        return 0;
+    }
+    Act act;
+    std::vector<float> gu(2 * inter), sw(inter);
+    act.populate(norm.data(), h);
+    L.gate_up.gemv(act.q.data(), act.s.data(), act.m.data(), gu.data(), threads);
+    for (size_t i = 0; i < inter; ++i) {               // swiglu_activate_neon (9811-9842): inter is a multiple of 8
+        float g = gu[i], u = gu[inter + i];
+        sw[i] = (g / (1.0f + exp_poly(-g))) * u;
+    }
+    act.populate(sw.data(), inter, c.down_chunk0);
+    L.down.gemv(act.q.data(), act.s.data(), act.m.data(), out, threads);
+    return 0;
+}
+
+int k2o_model_head_part(K2oModel *m, const float *hidden, float *logits, size_t threads) {
+    if (!m) return -1;
+    const size_t h = m->cfg.hidden;
+    std::vector<float> norm(h);
+    Act act;
+    rms_norm(hidden, m->final_norm.data(), h, m->cfg.eps, norm.data());
     act.populate(norm.data(), h);
     m->lm_head.gemv(act.q.data(), act.s.data(), act.m.data(), logits, threads);
+    return 0;
+}
+
+void k2o_model_advance(K2oModel *m) { if (m) m->pos += 1; }
+
+int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads) {
+    if (!m || m->pos >= m->cfg.max_seq) return -1;
+    const size_t h = m->cfg.hidden;
+    std::vector<float> hidden(embedding, embedding + h), proj(h);
+    m->tap_hidden.assign((size_t)m->cfg.layers * h, 0.0f);
+    for (uint32_t l = 0; l < m->cfg.layers; ++l) {
+        if (k2o_model_attn_part(m, l, hidden.data(), proj.data(), threads) != 0) return -1;
+        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);   // add_inplace = axpy(1.0)
+        if (k2o_model_ffn_part(m, l, hidden.data(), proj.data(), threads) != 0) return -1;
+        for (size_t i = 0; i < h; ++i) hidden[i] = std::fmaf(proj[i], 1.0f, hidden[i]);
+        std::memcpy(m->tap_hidden.data() + (size_t)l * h, hidden.data(), h * sizeof(float));
+    }
+    if (k2o_model_head_part(m, hidden.data(), logits, threads) != 0) return -1;
     m->pos += 1;
     return 0;
 }

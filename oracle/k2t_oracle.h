@@ -146,6 +146,11 @@ typedef struct K2oConfig {
     float eps;
     int32_t qk_norm_after_rope;
     uint32_t kv_bits;   /* 8 = int8 Hadamard cache, 4 = NF4 Hadamard cache (set_kv_bits, real_llm.rs:1731-1735) */
+    /* Tensor-parallel rank view (no counterpart in the reference, which runs on one device): the model holds n_q / n_kv
+     * LOCAL heads, inter LOCAL MLP columns and vocab LOCAL lm_head rows; the activations of the row-parallel projections
+     * are rotated with their GLOBAL chunk index: o_proj input chunk c is global chunk o_chunk0 + c, down_proj input chunk c
+     * is down_chunk0 + c.  All zero for the whole model. */
+    uint32_t o_chunk0, down_chunk0;
 } K2oConfig;
 typedef struct K2oModel K2oModel;
 K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table);
@@ -173,6 +178,16 @@ void k2o_model_set_pos(K2oModel *m, size_t pos);
 /* embed_token_into (real_llm.rs:8063-8097). */
 void k2o_model_embed(const K2oModel *m, uint32_t token, float *out);
 /* forward_token, generic path (6485-6790), int8 Hadamard KV; advances pos by one. */
+/* The three pieces of a token's forward pass, for a tensor-parallel emulation that sums the ranks' partial outputs in
+ * rank order between them (with one rank they compose to k2o_model_forward_embedding):
+ *   attn_part: hidden[h] -> this rank's o_proj output (input norm, qkv, RoPE, KV store at the current position, attention
+ *              over the local heads, o_proj over the local columns);
+ *   ffn_part:  hidden[h] -> this rank's down_proj output (post-attention norm, local gate_up, SwiGLU, local down);
+ *   head_part: hidden[h] -> logits of this rank's lm_head rows (final norm, lm_head);  advance: position += 1. */
+int k2o_model_attn_part(K2oModel *m, uint32_t layer, const float *hidden, float *out, size_t threads);
+int k2o_model_ffn_part(K2oModel *m, uint32_t layer, const float *hidden, float *out, size_t threads);
+int k2o_model_head_part(K2oModel *m, const float *hidden, float *logits, size_t threads);
+void k2o_model_advance(K2oModel *m);
 int k2o_model_forward_embedding(K2oModel *m, const float *embedding, float *logits, size_t threads);
 int k2o_model_forward_token(K2oModel *m, uint32_t token, float *logits, size_t threads);
 /* hidden state after every layer of the last step, [layers][hidden]. */

@@ -372,7 +372,8 @@ class MatrixDesc(C.Structure):
 class Config(C.Structure):
     _fields_ = [("hidden", C.c_uint32), ("layers", C.c_uint32), ("n_q", C.c_uint32), ("n_kv", C.c_uint32),
                 ("head_dim", C.c_uint32), ("inter", C.c_uint32), ("vocab", C.c_uint32), ("max_seq", C.c_uint32),
-                ("eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)]
+                ("eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32),
+                ("o_chunk0", C.c_uint32), ("down_chunk0", C.c_uint32)]
 
 
 def desc_of(m):
@@ -419,6 +420,10 @@ def _declare_model(L):
     L.k2o_nf_expert_layout.argtypes = [C.c_size_t] * 4 + [P] * 4
     L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
     L.k2o_model_read_kv.restype, L.k2o_model_read_kv.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
+    for name in ("k2o_model_attn_part", "k2o_model_ffn_part"):
+        getattr(L, name).restype, getattr(L, name).argtypes = C.c_int, [P, C.c_uint32, P, P, C.c_size_t]
+    L.k2o_model_head_part.restype, L.k2o_model_head_part.argtypes = C.c_int, [P, P, P, C.c_size_t]
+    L.k2o_model_advance.restype, L.k2o_model_advance.argtypes = None, [P]
     L.k2o_model_kv_export.restype, L.k2o_model_kv_export.argtypes = C.c_size_t, [P, C.c_size_t, C.c_size_t, P]
     L.k2o_model_kv_import.restype, L.k2o_model_kv_import.argtypes = C.c_int, [P, P, C.c_size_t, C.c_size_t]
     L.k2o_model_read_kv_q4.restype, L.k2o_model_read_kv_q4.argtypes = C.c_int, [P, C.c_uint32, C.c_uint32, C.c_size_t, P, P, P, P]
@@ -524,7 +529,8 @@ class Model:
         self.L, self.spec = L, spec
         c = spec["cfg"]
         self.cfg = Config(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"], c["max_seq"],
-                          c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
+                          c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)),
+                          int(c.get("o_chunk0", 0)), int(c.get("down_chunk0", 0)))
         rope = _c(spec["rope"], np.float32)
         self.h = L.k2o_model_new(C.byref(self.cfg), _ptr(rope))
         assert self.h, "k2o_model_new failed"
@@ -580,6 +586,25 @@ class Model:
         n = self.cfg.layers * self.cfg.hidden
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)).reshape(self.cfg.layers, self.cfg.hidden).copy()
 
+    # ---- pieces of a forward pass (tensor-parallel emulation, see TpModel)
+    def attn_part(self, layer, hidden, threads=2):
+        out = np.zeros(self.cfg.hidden, np.float32)
+        assert self.L.k2o_model_attn_part(self.h, layer, _ptr(_c(hidden, np.float32)), _ptr(out), threads) == 0
+        return out
+
+    def ffn_part(self, layer, hidden, threads=2):
+        out = np.zeros(self.cfg.hidden, np.float32)
+        assert self.L.k2o_model_ffn_part(self.h, layer, _ptr(_c(hidden, np.float32)), _ptr(out), threads) == 0
+        return out
+
+    def head_part(self, hidden, threads=2):
+        out = np.zeros(self.cfg.vocab, np.float32)
+        assert self.L.k2o_model_head_part(self.h, _ptr(_c(hidden, np.float32)), _ptr(out), threads) == 0
+        return out
+
+    def advance(self):
+        self.L.k2o_model_advance(self.h)
+
     def kv_export(self, lo, hi):
         n = self.L.k2o_model_kv_export(self.h, lo, hi, None)
         out = np.zeros(n, np.uint8)
@@ -623,3 +648,37 @@ class Model:
             out.append(nxt)
             logits = self.forward_token(nxt, threads)
         return out, logits
+
+
+class TpModel:
+    """Tensor-parallel emulation on the CPU: one rank-local Model per rank (specs from kronos_2t_b200.tp.shard_spec); after
+    the attention block and after the MLP the ranks' partial outputs are summed in rank order, ((p0 + p1) + p2) + ..., and
+    added to the residual stream; logits are the concatenation of the ranks' lm_head slices.  `embed(token)` must be
+    given (the full model's embedding), since a rank only holds a slice of the lm_head."""
+
+    def __init__(self, rank_specs, embed):
+        self.ranks = [Model(s) for s in rank_specs]
+        self.embed = embed
+        self.layers = rank_specs[0]["cfg"]["layers"]
+
+    def close(self):
+        for m in self.ranks:
+            m.close()
+
+    @staticmethod
+    def _sum(parts):
+        acc = parts[0].copy()
+        for p in parts[1:]:
+            acc = (acc + p).astype(np.float32)
+        return acc
+
+    def forward_token(self, token, threads=2):
+        hidden = np.asarray(self.embed(token), np.float32).copy()
+        for l in range(self.layers):
+            hidden = (hidden + self._sum([m.attn_part(l, hidden, threads) for m in self.ranks])).astype(np.float32)
+            hidden = (hidden + self._sum([m.ffn_part(l, hidden, threads) for m in self.ranks])).astype(np.float32)
+        logits = np.concatenate([m.head_part(hidden, threads) for m in self.ranks])
+        for m in self.ranks:
+            m.advance()
+        self.last_hidden = hidden
+        return logits

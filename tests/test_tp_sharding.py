@@ -1,0 +1,117 @@
+"""Tensor-parallel host logic on the CPU: file-format slicing, the rank-order partial-sum semantics (oracle.TpModel), and the
+same exchange over a real process group (gloo, world size 2)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import k2t_models as km
+
+TP_CFG = dict(hidden=256, layers=2, n_q=4, n_kv=2, head_dim=64, inter=512, vocab=384, max_seq=64, eps=1e-5, theta=1e5)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def dequant_rows(oracle, m):
+    return np.stack([oracle.bipolar_dequant_row(m, r) if m.kind == 0 else oracle.nf_dequant_row(m, r) for r in range(m.rows)])
+
+
+@pytest.mark.parametrize("mode", ["b4", "b6", "nf4g128", "nf3", "nf5g128"])
+def test_file_format_slices_select_rows_and_chunks(oracle, mode):
+    from kronos_2t_b200 import tp
+    from k2t_rng import normal
+    m = km.quantize(oracle, normal(5, (192, 512), 0.02), mode)
+    full = dequant_rows(oracle, m)                       # rotated domain: a 64-column chunk is self-contained
+    assert np.array_equal(dequant_rows(oracle, tp.rows_slice(m, 64, 160)), full[64:160])
+    assert np.array_equal(dequant_rows(oracle, tp.cols_slice(m, 2, 6)), full[:, 128:384])
+    cat = tp.rows_concat([tp.rows_slice(m, 128, 192), tp.rows_slice(m, 0, 32)])
+    assert np.array_equal(dequant_rows(oracle, cat), np.concatenate([full[128:192], full[0:32]]))
+    with pytest.raises(ValueError):
+        tp.rows_slice(m, 8, 64)
+    if mode.endswith("g128"):
+        with pytest.raises(ValueError):
+            tp.cols_slice(m, 1, 4)                       # not on a scale-group boundary
+
+
+@pytest.mark.parametrize("mode,kw", [("b5", dict(qkv_bias=True)), ("nf4g128", dict(qk_norm=True, tied=False))])
+def test_tp_emulation_matches_the_whole_model(oracle, mode, kw):
+    from kronos_2t_b200 import tp
+    spec = km.build(oracle, TP_CFG, mode, seed=3, **kw)
+    whole = oracle.Model(spec)
+    tokens = [5, 17, 300, 42, 7, 199, 63, 250]
+    want = np.stack([whole.forward_token(t, 2) for t in tokens])
+    embed = lambda t: whole.embed(t)
+    one = oracle.TpModel([tp.shard_spec(spec, 1, 0)], embed)
+    assert np.array_equal(np.stack([one.forward_token(t) for t in tokens]), want)        # one rank: the same arithmetic, bit for bit
+    two = oracle.TpModel([tp.shard_spec(spec, 2, r) for r in range(2)], embed)
+    got = np.stack([two.forward_token(t) for t in tokens])
+    # two ranks: every row-parallel output is (partial over rank 0's chunks) + (partial over rank 1's chunks) instead of one
+    # chain over all chunks: rounding-level differences that the int8 re-quantization of later layers can amplify slightly
+    assert np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
+    cos = [np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)) for a, b in zip(got, want)]
+    assert min(cos) > 0.99999
+    for m in (one, two):
+        m.close()
+    whole.close()
+    # shapes of a rank
+    s0 = tp.shard_spec(spec, 2, 1)
+    c = s0["cfg"]
+    assert (c["n_q"], c["n_kv"], c["inter"], c["vocab"], c["o_chunk0"], c["down_chunk0"]) == (2, 1, 256, 192, 2, 4)
+    assert s0["layers"][0]["qkv"].rows == (2 + 2 * 1) * 64 and s0["layers"][0]["o"].cols == 128 and s0["layers"][0]["down"].cols == 256
+    with pytest.raises(ValueError):
+        tp.shard_spec(spec, 4, 0)                        # 2 kv heads do not split four ways
+
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, os.path.join(ROOT, "tests")); sys.path.insert(0, os.path.join(ROOT, "oracle")); sys.path.insert(0, ROOT)
+import numpy as np, torch, torch.distributed as dist
+import oracle as o, k2t_models as km
+from kronos_2t_b200 import tp
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % os.environ["PORT"], rank=int(os.environ["RANK"]), world_size=2)
+rank = dist.get_rank()
+cfg = dict(hidden=256, layers=2, n_q=4, n_kv=2, head_dim=64, inter=512, vocab=384, max_seq=64, eps=1e-5, theta=1e5)
+spec = km.build(o, cfg, "b5", seed=3, qkv_bias=True)
+whole = o.Model(spec)                                    # only for the embedding lookup
+local = o.Model(tp.shard_spec(spec, 2, rank))
+
+def all_sum(part):                                       # every rank's partial, summed in rank order on every rank
+    parts = [torch.zeros(part.size) for _ in range(2)]
+    dist.all_gather(parts, torch.from_numpy(part.copy()))
+    acc = parts[0].numpy().copy()
+    for p in parts[1:]:
+        acc = (acc + p.numpy()).astype(np.float32)
+    return acc
+
+out = []
+for t in [5, 17, 300, 42, 7]:
+    hidden = whole.embed(t)
+    for l in range(cfg["layers"]):
+        hidden = (hidden + all_sum(local.attn_part(l, hidden))).astype(np.float32)
+        hidden = (hidden + all_sum(local.ffn_part(l, hidden))).astype(np.float32)
+    sl = torch.from_numpy(local.head_part(hidden))
+    parts = [torch.zeros(sl.numel()) for _ in range(2)]
+    dist.all_gather(parts, sl)
+    out.append(torch.cat(parts).numpy())
+    local.advance()
+np.save(os.environ["OUT"] + ".%d.npy" % rank, np.stack(out))
+dist.destroy_process_group()
+'''
+
+
+def test_two_gloo_ranks_reproduce_the_emulation(oracle, tmp_path):
+    from kronos_2t_b200 import tp
+    port = str(29000 + os.getpid() % 2000)
+    env = dict(os.environ, PORT=port, OUT=str(tmp_path / "logits"))
+    procs = [subprocess.Popen([sys.executable, "-c", "ROOT = %r\n" % ROOT + WORKER], env=dict(env, RANK=str(r))) for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=240) == 0
+    a, b = np.load(str(tmp_path / "logits.0.npy")), np.load(str(tmp_path / "logits.1.npy"))
+    assert np.array_equal(a, b)                          # both ranks hold the same logits
+    spec = km.build(oracle, TP_CFG, "b5", seed=3, qkv_bias=True)
+    whole = oracle.Model(spec)
+    emu = oracle.TpModel([tp.shard_spec(spec, 2, r) for r in range(2)], lambda t: whole.embed(t))
+    want = np.stack([emu.forward_token(t) for t in [5, 17, 300, 42, 7]])
+    assert np.array_equal(a, want)
+    emu.close(); whole.close()
