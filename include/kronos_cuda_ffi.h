@@ -152,6 +152,13 @@ typedef struct KronosCudaEngineConfig {
      * (MoeRouterScoring::Softmax); shared experts are not accepted. */
     uint32_t moe_num_experts, moe_top_k, moe_norm_topk, moe_d_ff, moe_bits, moe_scale_group_chunks;
     uint64_t moe_expert_bytes;
+    /* Tensor parallelism over the GPUs of one node, one process (and one engine) per rank; all zero / tp_size <= 1 for a
+     * single device.  No counterpart in the reference.  The sizes above are then the rank's LOCAL ones: its query / kv
+     * heads, its MLP columns (intermediate_size) and its lm_head rows (vocab_size); vocab_total is the whole vocabulary;
+     * o_chunk0 / down_chunk0 are the global indices of the first 64-column chunk of this rank's slice of o_proj's and
+     * down_proj's input, so that the activations are rotated with their global block index.  The matrices passed to
+     * kronos_cuda_engine_create are the rank's slices in the ordinary file formats (kronos_2t_b200/tp.py cuts them). */
+    uint32_t tp_size, tp_rank, o_chunk0, down_chunk0, vocab_total;
 } KronosCudaEngineConfig;
 
 /* One decoder layer as borrowed from the host engine: counterpart of LayerBorrow
@@ -212,6 +219,16 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *engine, const uint8_t *da
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
 /* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */
 int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
+/* Tensor parallel set-up (after create, before the first forward call; every rank in the same order):
+ *   tp_handle: writes this rank's 64-byte inter-process handle (cudaIpcMemHandle_t) of its exchange buffer;
+ *   tp_attach: takes the handles of all tp_size ranks (this rank's own entry is ignored), maps the peers' buffers and
+ *              enables the exchanges: the partial outputs of o_proj and down_proj are summed over the ranks in rank
+ *              order, the logits slices are concatenated, every rank ends a step with the same logits and next token.
+ * The caller makes sure (a process-group barrier) that all ranks have attached before any of them runs a step.
+ * With tied embeddings every rank also needs the whole lm_head for the token lookup: set_embedding_matrix uploads it. */
+int32_t kronos_cuda_engine_tp_handle(KronosCudaEngine *engine, uint8_t handle[64]);
+int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *engine, const uint8_t *handles /* [tp_size][64] */, size_t n_handles);
+int32_t kronos_cuda_engine_set_embedding_matrix(KronosCudaEngine *engine, const KronosCudaMatrixDesc *whole_lm_head);
 /* Diagnostic: routes of the last forwarded token through MoE layer `layer` (route_sorted, sparse_moe.rs:86-182):
  * up to 32 (expert id, weight) pairs in ascending expert order; returns their number (0 for a dense layer). */
 size_t kronos_cuda_engine_read_routes(KronosCudaEngine *engine, uint32_t layer, uint32_t *experts, float *weights);

@@ -12,6 +12,7 @@
 #include "k2t_context.h"
 #include "k2t_decode_mega.h"
 #include "k2t_model_kernels.h"
+#include "k2t_tp.h"
 
 using namespace k2t;
 
@@ -50,6 +51,13 @@ struct KronosCudaEngine {
     float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr;
     int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
     bool has_moe = false;
+    // tensor parallel: exchange buffer (data[2][tp][slot] floats + flags[tp]) and the peers' mappings
+    k2t::TpLink tp{};
+    float *tp_buf = nullptr;
+    std::vector<void *> tp_peers;            // mappings opened with cudaIpcOpenMemHandle
+    bool tp_ready = false;
+    float *logits_local = nullptr;            // this rank's logits slice [MAX_BATCH][vocab_size]
+    KronosCudaMatrix *embed_matrix = nullptr; // whole lm_head for the token lookup (tied embeddings under tp)
     uint32_t last_row = 0;                    // row of `hidden` that holds the last forwarded token (prompt batches)
     bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
     size_t weight_bytes = 0;
@@ -98,6 +106,17 @@ bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 
 
 void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a);
 
+// tensor parallel: x <- sum over ranks of x (rank order), and the concatenation of the ranks' slices; no-ops on one device
+bool tp_sum(KronosCudaEngine *e, float *x, uint32_t n) {
+    if (e->cfg.tp_size <= 1) return true;
+    if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
+    return count(e, launch_tp_exchange(e->ctx->stream, e->tp, x, x, n, 0, e->pdl), "tp sum");
+}
+bool tp_gather(KronosCudaEngine *e, const float *slice, float *all, uint32_t n) {
+    if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
+    return count(e, launch_tp_exchange(e->ctx->stream, e->tp, slice, all, n, n, e->pdl), "tp gather");
+}
+
 constexpr uint32_t MAX_BATCH = 4;      // tokens per weight pass in prompt processing (the reference's 4-token tiles)
 
 enum class Tail { Greedy, LastLogits, AllLogits, None };
@@ -137,7 +156,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 fa.out_q = oq; fa.out_scales = os; fa.out_sums = om; fa.err_flag = e->ctx->d_err;
                 fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
                 fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
-                fa.kv_bits = c.kv_bits;
+                fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
                 if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
             } else {
                 QkvPostArgs qa{};
@@ -151,13 +170,14 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
                 aa.pos = e->d_pos; aa.pos_offset = t;
                 aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
-                aa.out_q = oq; aa.out_scales = os; aa.out_sums = om;
+                aa.out_q = oq; aa.out_scales = os; aa.out_sums = om; aa.out_chunk0 = c.o_chunk0;
                 aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
                 aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
                 if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
             }
         }
         if (!gemv(e, L.o, e->proj, T)) return false;
+        if (!tp_sum(e, e->proj, T * h)) return false;
         if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
             if (!count(e, launch_rmsnorm_quant_x(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->x_norm, T, e->pdl), "rmsnorm")) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
@@ -178,14 +198,23 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
         }
         if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
         if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
-        if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, T, e->pdl), "swiglu")) return false;
+        if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, c.down_chunk0, T, e->pdl), "swiglu")) return false;
         if (!gemv(e, L.down, e->proj, T)) return false;
+        if (!tp_sum(e, e->proj, T * h)) return false;
     }
     // the last residual is folded into `hidden` by the final norm even when no logits are wanted
     if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
-    if (tail == Tail::AllLogits || tail == Tail::Greedy) { if (!gemv(e, e->lm_head, e->logits, T)) return false; }
-    else if (tail == Tail::LastLogits) { if (!gemv(e, e->lm_head, e->logits, 1, T - 1)) return false; }
-    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
+    const uint32_t vocab_all = c.tp_size > 1 ? c.vocab_total : c.vocab_size;
+    float *lg = c.tp_size > 1 ? e->logits_local : e->logits;        // under tp: this rank's slice, then gathered into `logits`
+    if (tail == Tail::AllLogits || tail == Tail::Greedy) {
+        if (!gemv(e, e->lm_head, lg, T)) return false;
+        for (uint32_t t = 0; t < T && c.tp_size > 1; ++t)
+            if (!tp_gather(e, lg + (size_t)t * c.vocab_size, e->logits + (size_t)t * vocab_all, c.vocab_size)) return false;
+    } else if (tail == Tail::LastLogits) {
+        if (!gemv(e, e->lm_head, lg, 1, T - 1)) return false;
+        if (c.tp_size > 1 && !tp_gather(e, lg, e->logits, c.vocab_size)) return false;
+    }
+    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, vocab_all, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
     return count(e, launch_advance_pos(s, e->d_pos, T, e->pdl), "advance");
 }
 
@@ -232,8 +261,8 @@ cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
     return e->graphs[(greedy ? 0 : 2) + (pos + 1 > ATTN_EXACT_CTX ? 1 : 0)];
 }
 uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
-    uint32_t n = 1 + 2 + 1;
-    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4
+    uint32_t n = 1 + 2 + 1 + (e->cfg.tp_size > 1 ? 1 : 0);
+    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0) + (e->cfg.tp_size > 1 ? 2 : 0);     // MoE FFN: 6 kernels for 4
     return n;
 }
 
@@ -251,6 +280,7 @@ bool setup_mega(KronosCudaEngine *e) {
     if (!want || want[0] != '1') { e->mega_why = "not requested (KRONOS_CUDA_MEGA=1 enables it)"; return true; }
     if (c.num_attention_heads > (uint32_t)ctx->sm_count) { e->mega_why = "more query heads than SMs"; return true; }
     if (e->has_moe) { e->mega_why = "sparse-MoE layers are served by the per-operator path"; return true; }
+    if (c.tp_size > 1) { e->mega_why = "tensor-parallel ranks are served by the per-operator path"; return true; }
     uint32_t warp_smem = 0;
     auto fill = [&](const KronosCudaMatrix *m, MegaMatrix &mm) {
         const int fmt = fill_gemv_args(m->dm, true, mm.g);
@@ -289,9 +319,10 @@ bool setup_mega(KronosCudaEngine *e) {
 }
 
 void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a) {
-    const MatrixGeom &g = e->lm_head->dm.geom;
-    for (int k = 0; k < 3; ++k) { a.plane[k] = e->lm_head->dm.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; a.cell[k] = g.cell[k]; }
-    a.scales = reinterpret_cast<const uint16_t *>(e->lm_head->dm.d_base + g.scale_off);
+    const KronosCudaMatrix *src = e->embed_matrix ? e->embed_matrix : e->lm_head;
+    const MatrixGeom &g = src->dm.geom;
+    for (int k = 0; k < 3; ++k) { a.plane[k] = src->dm.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; a.cell[k] = g.cell[k]; }
+    a.scales = reinterpret_cast<const uint16_t *>(src->dm.d_base + g.scale_off);
     a.embed_bf16 = e->embed_bf16; a.token = e->d_token; a.hidden = e->hidden;
     a.fmt = g.fmt; a.nc = g.nc; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.max_odd = g.max_odd;
     a.sgc_shift = 32;
@@ -391,6 +422,8 @@ void kronos_cuda_engine_destroy(KronosCudaEngine *e) {
         for (KronosCudaMatrix *m : L.expert_dn) if (m) kronos_cuda_matrix_free(e->ctx, m);
     }
     if (e->lm_head) kronos_cuda_matrix_free(e->ctx, e->lm_head);
+    if (e->embed_matrix) kronos_cuda_matrix_free(e->ctx, e->embed_matrix);
+    for (void *p : e->tp_peers) cudaIpcCloseMemHandle(p);
     for (void *p : e->allocs) cudaFree(p);
     delete e;
 }
@@ -409,6 +442,10 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         fail(ctx, "engine_create: query heads must be a multiple (at most 8x) of the kv heads"); return nullptr; }
     if (c.kv_bits != 8 && c.kv_bits != 4) { fail(ctx, "engine_create: kv_bits must be 8 (int8 Hadamard cache) or 4 (NF4 Hadamard cache)"); return nullptr; }
     if (c.max_seq_len == 0) { fail(ctx, "engine_create: max_seq_len is 0"); return nullptr; }
+    if (c.tp_size > 1) {
+        if (c.tp_size > TP_MAX || c.tp_rank >= c.tp_size) { fail(ctx, "engine_create: tp_size up to 8 and tp_rank below it"); return nullptr; }
+        if (c.vocab_total != c.vocab_size * c.tp_size || c.vocab_size % 4) { fail(ctx, "engine_create: vocab_total must be tp_size equal lm_head slices"); return nullptr; }
+    }
     if (!make_current(ctx)) return nullptr;
     const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd, kv_dim = c.num_key_value_heads * hd;
     const uint32_t qkv_rows = q_dim + 2 * kv_dim, inter = c.intermediate_size;
@@ -456,7 +493,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               // per-token vectors hold MAX_BATCH tokens (prompt batches), [token][n]
               dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
               dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
-              dev_alloc(e, e->logits, (size_t)MAX_BATCH * c.vocab_size) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
+              dev_alloc(e, e->logits, (size_t)MAX_BATCH * (c.tp_size > 1 ? c.vocab_total : c.vocab_size)) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
               dev_alloc(e, e->act_s, (size_t)MAX_BATCH * act_n / 64) && dev_alloc(e, e->act_m, (size_t)MAX_BATCH * act_n / 64) &&
               dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
@@ -466,6 +503,21 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
+    if (ok && c.tp_size > 1) {
+        if (e->has_moe) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
+        const size_t slot = std::max<size_t>((size_t)MAX_BATCH * h, c.vocab_size), floats = 2 * (size_t)c.tp_size * slot;
+        void *raw = nullptr;
+        ok = cuda_ok(ctx, cudaMalloc(&raw, floats * 4 + 256), "cudaMalloc(tp exchange)");
+        if (ok) {
+            e->allocs.push_back(raw);
+            e->tp_buf = static_cast<float *>(raw);
+            ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, floats * 4 + 256, ctx->stream), "clear tp exchange") &&
+                 dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
+            e->tp.tp = c.tp_size; e->tp.rank = c.tp_rank; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
+            e->tp.peer_data[c.tp_rank] = e->tp_buf;
+            e->tp.peer_flags[c.tp_rank] = reinterpret_cast<uint32_t *>(e->tp_buf + floats);
+        }
+    }
     if (ok && e->has_moe) {
         const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
         ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->moe_gu, (size_t)k * 2 * dff) &&
@@ -497,6 +549,54 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *e, float *hidden) {
         !sync_and_check(ctx, "read hidden"))
         return -1;
     return 0;
+}
+
+int32_t kronos_cuda_engine_tp_handle(KronosCudaEngine *e, uint8_t handle[64]) {
+    if (!e || !handle) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (e->cfg.tp_size <= 1 || !e->tp_buf) return fail(ctx, "tp_handle: the engine was created with tp_size <= 1"), -1;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t hnd;
+    if (!make_current(ctx) || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "tp_handle") ||      // the buffer is cleared by now
+        !cuda_ok(ctx, cudaIpcGetMemHandle(&hnd, e->tp_buf), "cudaIpcGetMemHandle"))
+        return -1;
+    std::memcpy(handle, &hnd, 64);
+    return 0;
+}
+
+int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *e, const uint8_t *handles, size_t n_handles) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (e->cfg.tp_size <= 1 || !e->tp_buf) return fail(ctx, "tp_attach: the engine was created with tp_size <= 1"), -1;
+    if (!handles || n_handles != e->cfg.tp_size) return fail(ctx, "tp_attach: one handle per rank is needed"), -1;
+    if (e->tp_ready) return fail(ctx, "tp_attach: already attached"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t floats = 2 * (size_t)e->cfg.tp_size * e->tp.slot;
+    for (uint32_t r = 0; r < e->cfg.tp_size; ++r) {
+        if (r == e->cfg.tp_rank) continue;
+        cudaIpcMemHandle_t hnd;
+        std::memcpy(&hnd, handles + (size_t)r * 64, 64);
+        void *p = nullptr;
+        if (!cuda_ok(ctx, cudaIpcOpenMemHandle(&p, hnd, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return -1;
+        e->tp_peers.push_back(p);
+        e->tp.peer_data[r] = static_cast<float *>(p);
+        e->tp.peer_flags[r] = reinterpret_cast<uint32_t *>(static_cast<float *>(p) + floats);
+    }
+    e->tp_ready = true;
+    return 0;
+}
+
+int32_t kronos_cuda_engine_set_embedding_matrix(KronosCudaEngine *e, const KronosCudaMatrixDesc *whole) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!whole || whole->cols != e->cfg.hidden_size) return fail(ctx, "set_embedding_matrix: the matrix must have hidden_size columns"), -1;
+    if (e->embed_matrix) { kronos_cuda_matrix_free(ctx, e->embed_matrix); e->embed_matrix = nullptr; }
+    e->embed_matrix = kronos_cuda_matrix_upload(ctx, whole, 0);
+    for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }      // captured embed arguments are stale
+    return e->embed_matrix ? 0 : -1;
 }
 
 size_t kronos_cuda_engine_read_routes(KronosCudaEngine *e, uint32_t layer, uint32_t *experts, float *weights) {
@@ -660,8 +760,8 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     if (!make_current(ctx)) return -1;
     if (tokens)
         for (size_t t = 0; t < n_tok; ++t)
-            if (tokens[t] >= e->cfg.vocab_size) return fail(ctx, "forward: token id out of range"), -1;
-    const size_t h = e->cfg.hidden_size, v = e->cfg.vocab_size;
+            if (tokens[t] >= (e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size)) return fail(ctx, "forward: token id out of range"), -1;
+    const size_t h = e->cfg.hidden_size, v = e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size;
     if (tokens && n_tok == 1) {         // one decode step: the captured graph
         if (!ensure_graphs(e) || !set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
         if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens, 4, cudaMemcpyHostToDevice, ctx->stream), "copy token") ||
@@ -714,7 +814,8 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     KronosCudaContext *ctx = e->ctx;
     ctx->err.clear();
     if (!out_tokens) return fail(ctx, "decode_greedy: out_tokens is NULL"), -1;
-    if (first_token >= e->cfg.vocab_size) return fail(ctx, "decode_greedy: token id out of range"), -1;
+    const size_t vocab_all = e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size;
+    if (first_token >= vocab_all) return fail(ctx, "decode_greedy: token id out of range"), -1;
     if (pos_start + n_steps > e->cfg.max_seq_len) return fail(ctx, "decode_greedy: sequence would exceed max_seq_len"), -1;
     if (e->cfg.kv_bits == 4 && pos_start + n_steps > ATTN_EXACT_CTX)
         return fail(ctx, "decode_greedy: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
@@ -724,7 +825,7 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     if (e->mega_ok && pos_start + n_steps <= ATTN_EXACT_CTX) {
         if (!decode_mega(e, first_token, (uint32_t)pos_start, (uint32_t)n_steps)) return -1;
         if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
-        if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
+        if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, vocab_all * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
         return sync_and_check(ctx, "decode_greedy") ? 0 : -1;
     }
     if (!ensure_graphs(e)) return -1;
@@ -739,7 +840,7 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
         ctx->launches += step_launches(e, pos_start + i);
     }
     if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
-    if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
+    if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, vocab_all * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
     return sync_and_check(ctx, "decode_greedy") ? 0 : -1;
 }
 

@@ -542,7 +542,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         warp_ifwht64(x0, x1, b, lane);
         if (A.attn_tap != nullptr) reinterpret_cast<float2 *>(A.attn_tap + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
         const uint32_t c = qh * NB + b;
-        warp_fwht64(x0, x1, c, lane);
+        warp_fwht64(x0, x1, A.out_chunk0 + c, lane);
         int q0, q1, sum;
         float sc;
         warp_quant64(x0, x1, q0, q1, sc, sum);

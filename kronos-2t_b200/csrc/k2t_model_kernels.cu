@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
         warp_ifwht64(x0, x1, b, lane);
         if (a.attn_out != nullptr) reinterpret_cast<float2 *>(a.attn_out + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
         const uint32_t c = qh * NB + b;
-        warp_fwht64(x0, x1, c, lane);
+        warp_fwht64(x0, x1, a.out_chunk0 + c, lane);
         int q0, q1, sum;
         float sc;
         warp_quant64(x0, x1, q0, q1, sc, sum);
@@ -543,7 +543,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAtt
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restrict__ gate_up, uint32_t inter,
                                                            int8_t *__restrict__ q, float *__restrict__ scales,
-                                                           int32_t *__restrict__ sums, float *__restrict__ dbg) {
+                                                           int32_t *__restrict__ sums, float *__restrict__ dbg, uint32_t chunk0) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
     pdl_wait();
     pdl_trigger();
@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
     float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_poly(-g.x))), u.x);
     float x1 = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, exp_poly(-g.y))), u.y);
     if (dbg != nullptr) reinterpret_cast<float2 *>(dbg + (size_t)c * 64)[lane] = make_float2(x0, x1);
-    warp_fwht64(x0, x1, c, lane);
+    warp_fwht64(x0, x1, chunk0 + c, lane);
     int q0, q1, sum;
     float sc;
     warp_quant64(x0, x1, q0, q1, sc, sum);
@@ -674,8 +674,8 @@ cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool 
     return launch_kernel(attn_fused_kernel, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
 }
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg, uint32_t n_tok, bool pdl) {
-    return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8, n_tok), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg);
+                                float *dbg, uint32_t chunk0, uint32_t n_tok, bool pdl) {
+    return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8, n_tok), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg, chunk0);
 }
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl) {

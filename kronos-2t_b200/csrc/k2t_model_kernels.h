@@ -44,6 +44,7 @@ struct AttnArgs {
     float *part_m, *part_l, *part_o;         // [n_q][n_split], [n_q][n_split], [n_q][n_split][head_dim]
     float *attn_out;             // optional fp32 attention output [n_q][head_dim] (tests), may be null
     int8_t *out_q; float *out_scales; int32_t *out_sums;   // activation of o_proj
+    uint32_t out_chunk0;         // global index of the first o_proj input chunk of this rank (tensor parallel), else 0
     uint32_t n_kv, group, head_dim, max_seq, layer, n_split;
     float attn_scale;
 };
@@ -57,6 +58,7 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     int8_t *k_q8, *v_q8; float *k_scale, *v_scale;
     float *attn_tap;             // optional fp32 attention output [n_q][head_dim]
     int8_t *out_q; float *out_scales; int32_t *out_sums;
+    uint32_t out_chunk0;         // global index of the first o_proj input chunk of this rank (tensor parallel), else 0
     uint32_t *err_flag;          // set when the bounded wait for the value rows gives up
     uint32_t n_q, n_kv, head_dim, max_seq, layer;
     uint32_t kv_bits;            // 8: int8 rows [head_dim] + fp32 scale per slot; 4: NF4 rows [head_dim / 2] + bf16 scale per 64 values
@@ -82,8 +84,9 @@ cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl);
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl);     // two kernels
 // contexts of up to ATTN_EXACT_CTX positions: qkv_post + attention in one kernel (leaves longer contexts untouched)
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl);
+// chunk0: global index of the first down_proj input chunk of this rank (tensor parallel), else 0
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
-                                float *dbg, uint32_t n_tok, bool pdl);
+                                float *dbg, uint32_t chunk0, uint32_t n_tok, bool pdl);
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl);
 // x_norm (optional): also write the normalised fp32 vector (the MoE router reads it)

@@ -37,7 +37,8 @@ class EngineConfig(C.Structure):
                                           "head_dim", "intermediate_size", "vocab_size", "max_seq_len")] + \
                [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)] + \
                [(n, C.c_uint32) for n in ("moe_num_experts", "moe_top_k", "moe_norm_topk", "moe_d_ff", "moe_bits",
-                                          "moe_scale_group_chunks")] + [("moe_expert_bytes", C.c_uint64)]
+                                          "moe_scale_group_chunks")] + [("moe_expert_bytes", C.c_uint64)] + \
+               [(n, C.c_uint32) for n in ("tp_size", "tp_rank", "o_chunk0", "down_chunk0", "vocab_total")]
 
 
 class LayerDesc(C.Structure):
@@ -91,6 +92,9 @@ def load_library():
     sig("kronos_cuda_engine_read_hidden", i32, vp, vp)
     sig("kronos_cuda_engine_read_attention", i32, vp, vp)
     sig("kronos_cuda_engine_read_routes", sz, vp, u32, vp, vp)
+    sig("kronos_cuda_engine_tp_handle", i32, vp, vp)
+    sig("kronos_cuda_engine_tp_attach", i32, vp, vp, sz)
+    sig("kronos_cuda_engine_set_embedding_matrix", i32, vp, C.POINTER(MatrixDesc))
     sig("kronos_cuda_engine_kv_bytes_per_pos", sz, vp)
     sig("kronos_cuda_engine_kv_export", C.c_int64, vp, sz, sz, vp, sz)
     sig("kronos_cuda_engine_kv_import", i32, vp, vp, sz, sz)
@@ -284,6 +288,9 @@ class Engine:
         c = spec["cfg"]
         self.cfg = EngineConfig(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
                                 c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
+        if int(c.get("tp_size", 1)) > 1:      # a rank of a tensor-parallel group (spec from kronos_2t_b200.tp.shard_spec)
+            self.cfg.tp_size, self.cfg.tp_rank, self.cfg.vocab_total = c["tp_size"], c["tp_rank"], c["vocab_total"]
+            self.cfg.o_chunk0, self.cfg.down_chunk0 = c["o_chunk0"], c["down_chunk0"]
         moes = [ly["moe"] for ly in spec["layers"] if ly.get("moe")]
         if moes:        # one geometry for every MoE layer of a model (MoeGeometry)
             m0 = moes[0]
@@ -322,6 +329,21 @@ class Engine:
                                                        _p(fn), C.byref(head), _p(emb))
         if not self.handle:
             raise KronosCudaError(self.L.kronos_cuda_last_error(ctx.handle).decode())
+        self.vocab = self.cfg.vocab_total if self.cfg.tp_size > 1 else self.cfg.vocab_size
+        if spec.get("embed_matrix") is not None:
+            md = desc_of(spec["embed_matrix"])
+            self.ctx._check(self.L.kronos_cuda_engine_set_embedding_matrix(self.handle, C.byref(md)))
+
+    def tp_handle(self):
+        """This rank's 64-byte inter-process handle of its exchange buffer."""
+        buf = np.zeros(64, np.uint8)
+        self.ctx._check(self.L.kronos_cuda_engine_tp_handle(self.handle, _p(buf)))
+        return buf.tobytes()
+
+    def tp_attach(self, handles):
+        """handles: the tp_handle() bytes of every rank, in rank order.  Barrier across the ranks afterwards."""
+        blob = np.frombuffer(b"".join(handles), np.uint8).copy()
+        self.ctx._check(self.L.kronos_cuda_engine_tp_attach(self.handle, _p(blob), len(handles)))
 
     def close(self):
         if self.handle:
@@ -330,7 +352,7 @@ class Engine:
 
     def forward_tokens(self, embeds, pos_start=0, want_all=False):
         e = _np(embeds, np.float32).reshape(-1, self.cfg.hidden_size)
-        n, v = e.shape[0], self.cfg.vocab_size
+        n, v = e.shape[0], self.vocab
         last = np.empty(v, np.float32)
         allv = np.empty((n, v), np.float32) if want_all else None
         self.ctx._check(self.L.kronos_cuda_engine_forward_tokens(self.handle, _p(e), n, pos_start, _p(allv), _p(last)))
@@ -338,7 +360,7 @@ class Engine:
 
     def forward_token_ids(self, tokens, pos_start=0, want_all=False):
         t = _np(tokens, np.uint32).reshape(-1)
-        n, v = t.size, self.cfg.vocab_size
+        n, v = t.size, self.vocab
         last = np.empty(v, np.float32)
         allv = np.empty((n, v), np.float32) if want_all else None
         self.ctx._check(self.L.kronos_cuda_engine_forward_token_ids(self.handle, _p(t), n, pos_start, _p(allv), _p(last)))
@@ -346,7 +368,7 @@ class Engine:
 
     def decode_greedy(self, first_token, pos_start, n_steps, want_logits=False):
         out = np.empty(n_steps, np.uint32)
-        logits = np.empty(self.cfg.vocab_size, np.float32) if want_logits else None
+        logits = np.empty(self.vocab, np.float32) if want_logits else None
         self.ctx._check(self.L.kronos_cuda_engine_decode_greedy(self.handle, int(first_token), pos_start, n_steps, _p(out),
                                                                 _p(logits)))
         return (out, logits) if want_logits else out

@@ -1,0 +1,73 @@
+"""Tensor-parallel engine on two GPUs of one node (skipped where fewer are visible): one child process per rank, the ranks'
+exchange-buffer handles swapped over a gloo process group, results compared with the CPU emulation that sums the ranks'
+partial outputs in the same (rank) order - so logits and greedy tokens must be identical, bit for bit."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import k2t_models as km
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TP_CFG = dict(hidden=256, layers=2, n_q=4, n_kv=2, head_dim=64, inter=512, vocab=384, max_seq=64, eps=1e-5, theta=1e5)
+TOKENS = [5, 17, 300, 42, 7, 199, 63, 250, 11]
+
+WORKER = r"""
+import os, sys
+sys.path.insert(0, os.path.join(ROOT, "tests")); sys.path.insert(0, os.path.join(ROOT, "oracle")); sys.path.insert(0, ROOT)
+import numpy as np, torch.distributed as dist
+import oracle as o, k2t_models as km, kronos_2t_b200 as k2
+from kronos_2t_b200 import tp
+rank, world = int(os.environ["RANK"]), 2
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % os.environ["PORT"], rank=rank, world_size=world)
+cfg = eval(os.environ["CFG"]); mode = os.environ["MODE"]; kw = eval(os.environ["KW"]); tokens = eval(os.environ["TOKENS"])
+spec = km.build(o, cfg, mode, seed=3, **kw)
+ctx = k2.Context(rank)
+eng = k2.Engine(ctx, tp.shard_spec(spec, world, rank))
+handles = [None] * world
+dist.all_gather_object(handles, eng.tp_handle())
+eng.tp_attach(handles)
+dist.barrier()
+logits = eng.forward_token_ids(tokens, want_all=True)
+greedy = eng.decode_greedy(int(np.argmax(logits[-1])), len(tokens), 12)
+np.save(os.environ["OUT"] + ".%d.npy" % rank, logits)
+np.save(os.environ["OUT"] + ".g%d.npy" % rank, greedy)
+dist.barrier()
+eng.close(); ctx.close()
+dist.destroy_process_group()
+"""
+
+
+def gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode,kw", [("b5", dict(qkv_bias=True)), ("nf4g128", dict(qk_norm=True, tied=False))])
+def test_two_rank_engine_matches_rank_order_emulation(oracle, tmp_path, mode, kw):
+    from kronos_2t_b200 import tp
+    port = str(31000 + os.getpid() % 2000)
+    env = dict(os.environ, PORT=port, OUT=str(tmp_path / "tp"), CFG=repr(TP_CFG), MODE=mode, KW=repr(kw), TOKENS=repr(TOKENS))
+    procs = [subprocess.Popen([sys.executable, "-c", "ROOT = %r\n" % ROOT + WORKER], env=dict(env, RANK=str(r))) for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    got = [np.load(str(tmp_path / f"tp.{r}.npy")) for r in range(2)]
+    greedy = [np.load(str(tmp_path / f"tp.g{r}.npy")) for r in range(2)]
+    assert np.array_equal(got[0], got[1]) and np.array_equal(greedy[0], greedy[1])       # every rank ends with the same logits and tokens
+    spec = km.build(oracle, TP_CFG, mode, seed=3, **kw)
+    whole = oracle.Model(spec)
+    emu = oracle.TpModel([tp.shard_spec(spec, 2, r) for r in range(2)], lambda t: whole.embed(t))
+    want = np.stack([emu.forward_token(t) for t in TOKENS])
+    assert np.array_equal(got[0], want)
+    nxt, out = int(np.argmax(want[-1])), []
+    for _ in range(12):
+        logits = emu.forward_token(nxt); nxt = oracle.argmax(logits); out.append(nxt)
+    assert list(greedy[0]) == out
+    emu.close(); whole.close()
