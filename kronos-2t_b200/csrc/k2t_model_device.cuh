@@ -225,7 +225,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     // mbarrier; then this lane's head inputs, and the key rows and scales of this thread's (at most two)
     // cached positions.
     const uint32_t vbar = (uint32_t)__cvta_generic_to_shared(s.bar);
-    if (tid == 0 && pos > 0) {
+    if (tid == NT - 32 && pos > 0) {       // a warp that has nothing to do during the head preparation: its fences delay nobody
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vbar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async;" ::: "memory");       // barrier init, and the cache rows other CTAs / kernels stored
@@ -491,45 +491,62 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             const uint32_t byte_off = g * 32 + (e / 32) * 16 + (r % 16), shift = r < 16 ? 0u : 4u;
             const float *wp = s.wg + g * ATTN_EXACT_CTX;
             const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + byte_off;
+            // plain fma for every position (a zero weight adds +-0: same bits as the CPU's skip), next eight positions
+            // loaded while the current eight run
             uint32_t j = 0;
-            for (; j + 8 <= pos; j += 8) {
-                float w[8], c[8];
+            float w[8], c[8], wn[8], cn[8];
+            if (pos >= 8) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; c[u] = s.cbf[(vp[(j + u) * ROW] >> shift) & 15u]; }
+                for (int u = 0; u < 8; ++u) { w[u] = wp[u]; c[u] = s.cbf[(vp[u * ROW] >> shift) & 15u]; }
+            }
+            for (; j + 16 <= pos; j += 8) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(c[u], w[u], o); o = w[u] != 0.0f ? nv : o; }
+                for (int u = 0; u < 8; ++u) { wn[u] = wp[j + 8 + u]; cn[u] = s.cbf[(vp[(j + 8 + u) * ROW] >> shift) & 15u]; }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) o = __fmaf_rn(c[u], w[u], o);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { w[u] = wn[u]; c[u] = cn[u]; }
             }
-            for (; j < pos; ++j) {
-                const float w = wp[j];
-                const float nv = __fmaf_rn(s.cbf[(vp[j * ROW] >> shift) & 15u], w, o);
-                o = w != 0.0f ? nv : o;
+            if (j + 8 <= pos) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) o = __fmaf_rn(c[u], w[u], o);
+                j += 8;
             }
-            const float w = wp[pos];       // the current position: its value row is still in shared memory
-            const float nv = __fmaf_rn(s.cbf[(s.hq4[64 + byte_off] >> shift) & 15u], w, o);
-            o = w != 0.0f ? nv : o;
+            for (; j < pos; ++j) o = __fmaf_rn(s.cbf[(vp[j * ROW] >> shift) & 15u], wp[j], o);
+            // the current position: its value row is still in shared memory
+            o = __fmaf_rn(s.cbf[(s.hq4[64 + byte_off] >> shift) & 15u], wp[pos], o);
         } else {
             // int8 -> fp32 without the conversion unit (a quarter-rate pipe that would bound this loop): for a byte b,
             // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
             const float *wp = s.sc;
             const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + tid;
             auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
+            // The CPU loop skips positions whose weight is zero; the plain fma gives the same bits (w >= 0 and the values
+            // are finite: o + (+-0) = o, and +0 + (-0) = +0), so the chain is one fma per position.  The next eight
+            // positions are loaded while the current eight run.
             uint32_t j = 0;
-            for (; j + 8 <= pos; j += 8) {
-                float w[8];
-                uint32_t v[8];
+            float w[8], wn[8];
+            uint32_t v[8], vn[8];
+            if (pos >= 8) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { w[u] = wp[j + u]; v[u] = vp[(j + u) * HD]; }
+                for (int u = 0; u < 8; ++u) { w[u] = wp[u]; v[u] = vp[u * HD]; }
+            }
+            for (; j + 16 <= pos; j += 8) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { const float nv = __fmaf_rn(to_f32(v[u]), w[u], o); o = w[u] != 0.0f ? nv : o; }
+                for (int u = 0; u < 8; ++u) { wn[u] = wp[j + 8 + u]; vn[u] = vp[(j + 8 + u) * HD]; }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) o = __fmaf_rn(to_f32(v[u]), w[u], o);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { w[u] = wn[u]; v[u] = vn[u]; }
             }
-            for (; j < pos; ++j) {
-                const float w = wp[j];
-                const float nv = __fmaf_rn(to_f32(vp[j * HD]), w, o);
-                o = w != 0.0f ? nv : o;
+            if (j + 8 <= pos) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) o = __fmaf_rn(to_f32(v[u]), w[u], o);
+                j += 8;
             }
-            const float w = wp[pos];       // the current position: its value row is still in shared memory
-            const float nv = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), w, o);
-            o = w != 0.0f ? nv : o;
+            for (; j < pos; ++j) o = __fmaf_rn(to_f32(vp[j * HD]), wp[j], o);
+            // the current position: its value row is still in shared memory
+            o = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), wp[pos], o);
         }
     }
     if (__syncthreads_or(copy_failed) && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);

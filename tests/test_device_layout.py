@@ -76,12 +76,51 @@ def decode_cell(fmt, ca, cb, cb_words):
             s |= (W[3 * hh + 2] >> 1) & 0x44444444
             u[12 + 2 * hh], u[13 + 2 * hh] = prmt(cb_words[0], cb_words[1], s), prmt(cb_words[0], cb_words[1], s >> 16)
         dt = np.int8
+    elif fmt == "nf5":
+        sel = lambda lo, hi, m: (lo & ~m & M) | (hi & m)
+        for i in range(8):
+            x = a[i]
+            lo3, hb = x & 0x77777777, x & 0x88888888
+            hs = (hb << 4) & M
+            m0, m1 = prmt(hs, hb, 0xD9C8), prmt(hs, hb, 0xFBEA)
+            hw = h[i // 4]
+            for half, (l3, m) in enumerate(((lo3, m0), (lo3 >> 16, m1))):
+                j = 2 * (i % 4) + half
+                t = (((hw << (4 - j)) & M if j <= 4 else hw >> (j - 4)) & 0x10101010) >> 4
+                bmask = (t * 0xFF) & M
+                lo16 = sel(prmt(cb_words[0], cb_words[1], l3), prmt(cb_words[2], cb_words[3], l3), m)
+                hi16 = sel(prmt(cb_words[4], cb_words[5], l3), prmt(cb_words[6], cb_words[7], l3), m)
+                u[2 * i + half] = sel(lo16, hi16, bmask)
+        dt = np.int8
+    elif fmt == "e8q2":
+        spread4 = lambda b: ((((b * 0x00204081) & M) & 0x01010101) * 0xFF) & M
+        tab = cb_words                                     # the 28 even-coset template words
+        for b in range(8):
+            pair = (a[b // 2] >> (16 * (b % 2))) & 0xFFFF
+            tpl, sgn = pair & 0xFF, pair >> 8
+            tu, tv = tpl & 15, tpl >> 4
+            if bin(tpl ^ sgn).count("1") & 1:
+                ui = 16 + tu if tu < 12 <= tv else tu
+                vi = 16 + tv if tv < 12 <= tu else tv
+                mu, mv = tab[ui], tab[vi]
+            else:
+                mu, mv = (spread4(tu) & 0x20202020) + 0x10101010, (spread4(tv) & 0x20202020) + 0x10101010
+            for k, (mag, bits4) in enumerate(((mu, sgn & 15), (mv, sgn >> 4))):
+                sm = spread4(bits4)
+                pos_b, neg_b = mag & ~sm & M, mag & sm
+                u[2 * b + k] = sum((((pos_b >> (8 * q)) & 0xFF) - ((neg_b >> (8 * q)) & 0xFF)) % 256 << (8 * q) for q in range(4))   # __vsub4
+        dt = np.int8
     else:
         raise ValueError(fmt)
     return np.array(u, dtype="<u4").view(np.uint8).view(dt)
 
 
-CELL_BYTES = {"bp4": (16, 16, 0), "bp5": (16, 16, 8), "bp6": (16, 16, 16), "nf4": (16, 16, 0), "nf3": (16, 8, 0)}
+CELL_BYTES = {"bp4": (16, 16, 0), "bp5": (16, 16, 8), "bp6": (16, 16, 16), "nf4": (16, 16, 0), "nf3": (16, 8, 0), "nf5": (16, 16, 8),
+              "e8q2": (16, 0, 0)}
+E8Q2_TEMPLATES = [(0, 0, 0, 0), (32, 32, 0, 0), (32, 0, 32, 0), (32, 0, 0, 32), (0, 32, 32, 0), (0, 32, 0, 32), (0, 0, 32, 32), (64, 0, 0, 0),
+                  (0, 64, 0, 0), (0, 0, 64, 0), (0, 0, 0, 64), (32, 32, 32, 32), (32, 0, 0, 0), (0, 32, 0, 0), (0, 0, 32, 0), (0, 0, 0, 32),
+                  (32, 32, 32, 0), (32, 32, 0, 32), (32, 0, 32, 32), (0, 32, 32, 32), (96, 0, 0, 0), (0, 96, 0, 0), (0, 0, 96, 0), (0, 0, 0, 96),
+                  (64, 32, 32, 32), (32, 64, 32, 32), (32, 32, 64, 32), (32, 32, 32, 64)]
 
 
 def up16(x):
@@ -102,7 +141,7 @@ def split_image(fmt, image, rows, cols, nsg):
     scales = image[off: off + rows * nsg_pad * 2].view("<u2").reshape(rows, nsg_pad)
     assert not scales[:, nsg:].any()
     assert image.size == off + rows * nsg_pad * 2 + 16
-    if fmt == "nf3":
+    if fmt in ("nf3", "e8q2"):
         return planes[0], planes[1], scales[:, :nsg]
     return np.concatenate([planes[0], planes[1]], axis=2), planes[2], scales[:, :nsg]
 
@@ -149,6 +188,40 @@ def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
     sc_file = sc.reshape(-1, nsg, 16)
     for r in range(rows):
         assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
+
+
+@pytest.mark.parametrize("rows,sgc", [(71, 1), (128, 2)])
+def test_nf5_image_decodes_to_centroids(oracle, rows, sgc):
+    cols = 192
+    rng = np.random.Generator(np.random.PCG64(rows))
+    idx = rng.integers(0, 32, (rows, cols), dtype=np.uint8)
+    nsg = -(-(cols // 64) // sgc)
+    sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, sgc)).astype(np.uint16)
+    cb = np.array([1, -2, 5, 9, 17, 21, 33, 40, 41, 59, 70, 77, 90, 100, 120, 127], np.int8)      # 16 magnitudes, one of them negative
+    m = oracle.nf_pack(idx, sc, 5, sgc, cb)
+    cb32 = oracle.nf_expand_codebook32(5, cb)                  # [15 - m] = -cb[m], [16 + m] = cb[m]
+    image = k2.matrix_image(k2.nf_desc(rows, cols, 5, sgc, cb, m.pair, m.tail))
+    vals, scales = image_rows("nf5", image, rows, cols, nsg, _words(cb32.tobytes()))
+    assert np.array_equal(vals[:rows], cb32.astype(np.int16)[idx])
+    sc_file = sc.reshape(-1, nsg, 16)
+    for r in range(rows):
+        assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
+
+
+def test_e8q2_image_decodes_to_lattice_points(oracle):
+    rows, cols, sgc = 71, 128, 2
+    rng = np.random.Generator(np.random.PCG64(3))
+    tpl = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+    sgn = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+    tpl[0, 0], sgn[0, 0] = 0, 1                                # the padding codeword
+    sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, sgc)).astype(np.uint16)
+    m = oracle.e8q2_pack(tpl, sgn, sc, sgc)
+    words = [t[0] | t[1] << 8 | t[2] << 16 | t[3] << 24 for t in E8Q2_TEMPLATES]
+    image = k2.matrix_image(k2.nf_desc(rows, cols, 2, sgc, np.zeros(16, np.int8), m.pair, m.tail))
+    vals, _ = image_rows("e8q2", image, rows, cols, 1, words)
+    for r in range(rows):
+        want = np.concatenate([oracle.e8q2_decode_8d(tpl[r, b], sgn[r, b]) for b in range(cols // 8)])
+        assert np.array_equal(vals[r], want.astype(np.int16)), r
 
 
 def nf4_two_table_values(cell, cb_sorted):
