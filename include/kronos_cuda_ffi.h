@@ -148,8 +148,9 @@ typedef struct KronosCudaEngineConfig {
     uint32_t kv_bits;
     /* MoeGeometry (metal_gpu.rs:443-456), all zero for a dense model: experts per MoE layer, routes per token,
      * renormalise the top-k weights, expert MLP width, NF bits (2..5) and scale group of the expert matrices, bytes of
-     * one .k2tm expert record (nf_expert_byte_layout, moe_800b.rs:1330-1383).  Router scoring is the full softmax
-     * (MoeRouterScoring::Softmax); shared experts are not accepted. */
+     * one .k2tm expert record (nf_expert_byte_layout, moe_800b.rs:1330-1383).  moe_norm_topk: bit 0 = renormalise the
+     * top-k weights, bits 8.. = MoeRouterScoring tag (sparse_moe.rs:28-53: 0 softmax over all experts, 1 top-k softmax,
+     * 2 sigmoid).  Shared experts are not accepted. */
     uint32_t moe_num_experts, moe_top_k, moe_norm_topk, moe_d_ff, moe_bits, moe_scale_group_chunks;
     uint64_t moe_expert_bytes;
     /* Tensor parallelism over the GPUs of one node, one process (and one engine) per rank; all zero / tp_size <= 1 for a

@@ -184,7 +184,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             for (uint32_t t = 0; t < T; ++t) {
                 RouterArgs ra{};
                 ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm + (size_t)t * h;
-                ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)c.moe_norm_topk;
+                ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
                 ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32;
                 if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
                 if (!count(e, launch_gemv_experts(s, L.expert_gu[0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),

@@ -131,18 +131,25 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
         if (lane == 0) s_max = m;
     }
     __syncthreads();
-    for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = exp_cr(__fsub_rn(s_z[e], s_max));
+    // scores: softmax numerators (normalised below), sigmoid values, or the raw logits (top-k softmax)
+    for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) {
+        if (a.scoring == 0) s_z[e] = exp_cr(__fsub_rn(s_z[e], s_max));
+        else if (a.scoring == 2) s_z[e] = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_cr(-s_z[e])));
+    }
     __syncthreads();
     if (tid == 0) {
-        float sum = 0.0f;
-        for (uint32_t e = 0; e < a.n_experts; ++e) sum = __fadd_rn(sum, s_z[e]);
-        const float inv_all = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)a.n_experts);
+        float inv_all = 1.0f;
+        if (a.scoring == 0) {
+            float sum = 0.0f;
+            for (uint32_t e = 0; e < a.n_experts; ++e) sum = __fadd_rn(sum, s_z[e]);
+            inv_all = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)a.n_experts);
+        }
         const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
         uint32_t ids[ROUTER_MAX_TOPK];
         float w[ROUTER_MAX_TOPK];
         uint32_t len = 0;
         for (uint32_t e = 0; e < a.n_experts; ++e) {
-            const float sc = __fmul_rn(s_z[e], inv_all);
+            const float sc = a.scoring == 0 ? __fmul_rn(s_z[e], inv_all) : s_z[e];
             if (len < k) {
                 uint32_t pos = len;
                 while (pos > 0 && sc > w[pos - 1]) { ids[pos] = ids[pos - 1]; w[pos] = w[pos - 1]; --pos; }
@@ -153,7 +160,13 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
                 ids[pos] = e; w[pos] = sc;
             }
         }
-        if (a.norm_topk) {
+        if (a.scoring == 1) {                 // k-way softmax over the selected logits, in selection order
+            float max_z = -INFINITY, sum = 0.0f;
+            for (uint32_t i = 0; i < k; ++i) max_z = fmaxf(max_z, w[i]);
+            for (uint32_t i = 0; i < k; ++i) { w[i] = exp_cr(__fsub_rn(w[i], max_z)); sum = __fadd_rn(sum, w[i]); }
+            const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)k);
+            for (uint32_t i = 0; i < k; ++i) w[i] = __fmul_rn(w[i], inv);
+        } else if (a.norm_topk) {
             float top_sum = 0.0f;
             for (uint32_t i = 0; i < k; ++i) top_sum = __fadd_rn(top_sum, w[i]);
             if (top_sum > 0.0f) { const float inv_top = __fdiv_rn(1.0f, top_sum); for (uint32_t i = 0; i < k; ++i) w[i] = __fmul_rn(w[i], inv_top); }

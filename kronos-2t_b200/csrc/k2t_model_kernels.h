@@ -71,6 +71,7 @@ struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scorin
     const float *x;              // normalised hidden state (fp32, not rotated)
     uint32_t n_experts, hidden, top_k;
     int32_t norm_topk;
+    uint32_t scoring;            // MoeRouterScoring tag: 0 softmax over all experts, 1 top-k softmax, 2 sigmoid
     uint32_t *route_ids;         // out: [top_k] expert ids, ascending
     float *route_w;              // out: [top_k]
 };

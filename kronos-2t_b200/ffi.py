@@ -295,7 +295,9 @@ class Engine:
         if moes:        # one geometry for every MoE layer of a model (MoeGeometry)
             m0 = moes[0]
             assert all(all(m[k] == m0[k] for k in ("n_experts", "top_k", "norm_topk", "d_ff", "bits", "sgc", "expert_bytes")) for m in moes)
-            self.cfg.moe_num_experts, self.cfg.moe_top_k, self.cfg.moe_norm_topk = m0["n_experts"], m0["top_k"], int(m0["norm_topk"])
+            assert all(m.get("scoring", 0) == m0.get("scoring", 0) for m in moes)
+            self.cfg.moe_num_experts, self.cfg.moe_top_k = m0["n_experts"], m0["top_k"]
+            self.cfg.moe_norm_topk = int(m0["norm_topk"]) | (int(m0.get("scoring", 0)) << 8)
             self.cfg.moe_d_ff, self.cfg.moe_bits, self.cfg.moe_scale_group_chunks = m0["d_ff"], m0["bits"], m0["sgc"]
             self.cfg.moe_expert_bytes = m0["expert_bytes"]
         keep = []

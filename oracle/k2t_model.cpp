@@ -75,6 +75,7 @@ struct Moe {
     bool on = false;
     uint32_t n_experts = 0, top_k = 0, d_ff = 0;
     bool norm_topk = false;
+    uint32_t scoring = 0;               // MoeRouterScoring tag: 0 softmax, 1 top-k softmax, 2 sigmoid (sparse_moe.rs:28-53)
     std::vector<float> router_w, router_bias;
     std::vector<Expert> experts;
     uint32_t last_k = 0;                 // routes of the last token (tests)
@@ -340,19 +341,31 @@ void moe_forward(Moe &M, const float *x_norm, size_t h, float *out, size_t threa
         if (!M.router_bias.empty()) v += M.router_bias[e];
         logits[e] = v;
     }
-    float max_z = -INFINITY;
-    for (size_t e = 0; e < E; ++e) max_z = std::max(max_z, logits[e]);
-    float sum = 0.0f;
-    for (size_t e = 0; e < E; ++e) { logits[e] = exp_cr(logits[e] - max_z); sum += logits[e]; }
-    const float inv_all = sum > 0.0f ? 1.0f / sum : 1.0f / (float)E;
-    for (size_t e = 0; e < E; ++e) logits[e] *= inv_all;
     uint32_t ids[32];
     float w[32];
-    select_topk(logits.data(), E, k, ids, w);
-    if (M.norm_topk) {
-        float top_sum = 0.0f;
-        for (size_t i = 0; i < k; ++i) top_sum += w[i];
-        if (top_sum > 0.0f) { const float inv_top = 1.0f / top_sum; for (size_t i = 0; i < k; ++i) w[i] *= inv_top; }
+    if (M.scoring == 1) {                              // TopkSoftmax: top-k raw logits, then a k-way softmax
+        select_topk(logits.data(), E, k, ids, w);
+        float max_z = -INFINITY, sum = 0.0f;
+        for (size_t i = 0; i < k; ++i) max_z = std::max(max_z, w[i]);
+        for (size_t i = 0; i < k; ++i) { w[i] = exp_cr(w[i] - max_z); sum += w[i]; }
+        const float inv = sum > 0.0f ? 1.0f / sum : 1.0f / (float)k;
+        for (size_t i = 0; i < k; ++i) w[i] *= inv;
+    } else {
+        if (M.scoring == 2) {                          // Sigmoid
+            for (size_t e = 0; e < E; ++e) logits[e] = 1.0f / (1.0f + exp_cr(-logits[e]));
+        } else {                                       // Softmax over all experts
+            float max_z = -INFINITY, sum = 0.0f;
+            for (size_t e = 0; e < E; ++e) max_z = std::max(max_z, logits[e]);
+            for (size_t e = 0; e < E; ++e) { logits[e] = exp_cr(logits[e] - max_z); sum += logits[e]; }
+            const float inv_all = sum > 0.0f ? 1.0f / sum : 1.0f / (float)E;
+            for (size_t e = 0; e < E; ++e) logits[e] *= inv_all;
+        }
+        select_topk(logits.data(), E, k, ids, w);
+        if (M.norm_topk) {
+            float top_sum = 0.0f;
+            for (size_t i = 0; i < k; ++i) top_sum += w[i];
+            if (top_sum > 0.0f) { const float inv_top = 1.0f / top_sum; for (size_t i = 0; i < k; ++i) w[i] *= inv_top; }
+        }
     }
     for (size_t i = 1; i < k; ++i) {                  // insertion sort by ascending expert id
         const uint32_t ce = ids[i]; const float cw = w[i];
@@ -409,7 +422,8 @@ int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const floa
     size_t gu_off, gub, dn_off, dnb;
     if (k2o_nf_expert_layout(h, d_ff, bits, sgc, &gu_off, &gub, &dn_off, &dnb) != expert_bytes) return -1;
     Moe &M = m->layers[l].moe;
-    M.on = true; M.n_experts = n_experts; M.top_k = top_k; M.d_ff = d_ff; M.norm_topk = norm_topk != 0;
+    M.on = true; M.n_experts = n_experts; M.top_k = top_k; M.d_ff = d_ff; M.norm_topk = (norm_topk & 1) != 0;
+    M.scoring = (uint32_t)norm_topk >> 8;             // bits 8.. of the flag word carry the scoring tag
     M.router_w.assign(router_w, router_w + (size_t)n_experts * h);
     if (router_bias) M.router_bias.assign(router_bias, router_bias + n_experts); else M.router_bias.clear();
     M.experts.resize(n_experts);

@@ -159,7 +159,8 @@ int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const 
                         const float *q_norm, const float *k_norm, const K2oMatrixDesc *qkv, const K2oMatrixDesc *o,
                         const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down);
 /* Makes layer l a sparse-MoE layer (its dense gate_up / down are ignored): router [n_experts][hidden] fp32 (+ optional
- * bias), softmax scoring, top_k with optional renormalisation (DenseMoeRouter::route_sorted, sparse_moe.rs:86-206), experts
+ * bias), top_k with optional renormalisation (DenseMoeRouter::route_sorted, sparse_moe.rs:86-206; norm_topk bit 0 = renormalise,
+ * bits 8.. = MoeRouterScoring tag: 0 softmax over all experts, 1 top-k softmax, 2 sigmoid), experts
  * as .k2tm records (nf_expert_byte_layout / pack_nf_expert_record, moe_800b.rs:1330-1407): record e of `shard` starts at
  * e * expert_bytes.  Forward = SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084) with the zero-copy NF
  * expert (MmapNfExpertView::forward_swiglu_zero_copy, moe_800b.rs:1440-1563). */

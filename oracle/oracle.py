@@ -545,7 +545,7 @@ class Model:
                 rw = _c(moe["router_w"], np.float32)
                 rb = None if moe.get("router_bias") is None else _c(moe["router_bias"], np.float32)
                 shard = _c(moe["shard"], np.uint8)
-                rc = L.k2o_model_set_moe(self.h, l, _ptr(rw), _ptr(rb), moe["n_experts"], moe["top_k"], int(moe["norm_topk"]), moe["d_ff"],
+                rc = L.k2o_model_set_moe(self.h, l, _ptr(rw), _ptr(rb), moe["n_experts"], moe["top_k"], int(moe["norm_topk"]) | (int(moe.get("scoring", 0)) << 8), moe["d_ff"],
                                          moe["bits"], moe["sgc"], _ptr(shard), moe["expert_bytes"])
                 assert rc == 0, f"set_moe {l} failed"
         emb = None if spec.get("embed_bf16") is None else _c(spec["embed_bf16"], np.uint16)

@@ -153,3 +153,35 @@ def test_oracle_q4_cache_tracks_int8_cache_and_byte_count(oracle):
     c = km.SMOL_135M
     assert 2 * c["layers"] * c["n_kv"] * (c["head_dim"] + 4) == 12240
     assert 2 * c["layers"] * c["n_kv"] * (c["head_dim"] // 2 + 2 * (c["head_dim"] // 64)) == 6120
+
+
+# ----------------------------------------------------------------------------- sparse-MoE router
+@pytest.mark.parametrize("scoring,norm", [(0, True), (0, False), (1, True), (2, True), (2, False)])
+def test_moe_router_scoring_modes(oracle, scoring, norm):
+    """Routes of the oracle against a direct numpy evaluation of DenseMoeRouter::route_sorted (float64 scores: the expert
+    SET and order must agree, the weights to fp32 rounding)."""
+    moe = dict(layers=[0], n_experts=8, top_k=3, d_ff=64, bits=4, sgc=1, norm_topk=norm, scoring=scoring, bias=True)
+    spec = km.build(oracle, km.MOE_TINY, "b4", seed=5, moe=moe)
+    m = oracle.Model(spec)
+    m.forward_token(11, 2)
+    ids, w = m.last_routes(0)
+    assert list(ids) == sorted(ids) and len(ids) == 3
+    # recompute from the post-attention hidden state of layer 0: run the attention block by hand
+    ly = spec["layers"][0]
+    m2 = oracle.Model(spec)
+    hidden = m2.embed(11)
+    hidden = (hidden + m2.attn_part(0, hidden)).astype(np.float32)
+    x = hidden.astype(np.float64)
+    xn = x / np.sqrt(np.mean(x * x) + km.MOE_TINY["eps"]) * ly["post_norm"]
+    logits = ly["moe"]["router_w"].astype(np.float64) @ xn + ly["moe"]["router_bias"]
+    if scoring == 1:
+        top = np.argsort(-logits, kind="stable")[:3]
+        p = np.exp(logits[top] - logits[top].max()); p /= p.sum()
+    else:
+        sc = np.exp(logits - logits.max()) / np.exp(logits - logits.max()).sum() if scoring == 0 else 1 / (1 + np.exp(-logits))
+        top = np.argsort(-sc, kind="stable")[:3]
+        p = sc[top] / (sc[top].sum() if norm else 1.0)
+    order = np.argsort(top)
+    assert list(ids) == list(top[order])
+    assert np.allclose(w, p[order], rtol=1e-4, atol=1e-6)
+    m.close(); m2.close()
