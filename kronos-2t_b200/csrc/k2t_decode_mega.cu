@@ -91,7 +91,13 @@ struct GridSync {
 // per-CTA prologues: fill s.xq / s.xs / s.xm with the activation of the next GEMV
 // ------------------------------------------------------------------------------------------------
 // s.x holds n fp32 values: RMSNorm (CPU accumulator order, see rmsnorm_quant_kernel) + rotation + int8.
+#define MEGA_SMEM_HINTS(s)                                                                                                   \
+    __builtin_assume(__isShared((s).x)); __builtin_assume(__isShared((s).xq)); __builtin_assume(__isShared((s).xs));          \
+    __builtin_assume(__isShared((s).xm)); __builtin_assume(__isShared((s).warp0)); __builtin_assume(__isShared((s).s_f));     \
+    __builtin_assume(__isShared((s).at.inv)); __builtin_assume(__isShared((s).at.red));
+
 __device__ __noinline__ void cta_norm_quant(const MegaSmem &s, const float *__restrict__ w, uint32_t n, float eps) {
+    MEGA_SMEM_HINTS(s)
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
     if (warp == 0) {
         float acc = 0.0f;
@@ -125,6 +131,7 @@ __device__ __noinline__ void cta_norm_quant(const MegaSmem &s, const float *__re
 // x = in + delta (delta may be null); CTA 0 also writes x to `out`.  Then norm + quant.
 __device__ __noinline__ void cta_residual_norm_quant(const MegaSmem &s, const float *in, const float *delta, float *out,
                                                         const float *w, uint32_t n, float eps) {
+    MEGA_SMEM_HINTS(s)
     for (uint32_t i = threadIdx.x; i < n / 4; i += MEGA_THREADS) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(in) + i);
         if (delta != nullptr) {
@@ -141,6 +148,7 @@ __device__ __noinline__ void cta_residual_norm_quant(const MegaSmem &s, const fl
 // x = embedding of `tok` (embed_kernel); CTA 0 writes it to `out`.  Then norm + quant.
 __device__ __noinline__ void cta_embed_norm_quant(const MegaSmem &s, const EmbedArgs &e, uint32_t tok, float *out, const float *w,
                                                      uint32_t n, float eps) {
+    MEGA_SMEM_HINTS(s)
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t c = warp; c < e.nc; c += MEGA_WARPS) {
         float v0, v1;
@@ -162,6 +170,7 @@ __device__ __noinline__ void cta_embed_norm_quant(const MegaSmem &s, const Embed
 
 // SwiGLU of gate_up[2 * inter] + rotation + int8 (swiglu_quant_kernel)
 __device__ __noinline__ void cta_swiglu_quant(const MegaSmem &s, const float *gate_up, uint32_t inter) {
+    MEGA_SMEM_HINTS(s)
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (uint32_t c = warp; c < inter / 64; c += MEGA_WARPS) {
         const float2 g = __ldcg(reinterpret_cast<const float2 *>(gate_up + (size_t)c * 64) + lane);
@@ -180,6 +189,7 @@ __device__ __noinline__ void cta_swiglu_quant(const MegaSmem &s, const float *ga
 
 // copies an activation another phase left in global memory
 __device__ __noinline__ void cta_load_act(const MegaSmem &s, const int8_t *q, const float *sc, const int32_t *sm, uint32_t n) {
+    MEGA_SMEM_HINTS(s)
     for (uint32_t i = threadIdx.x; i < n / 16; i += MEGA_THREADS)
         reinterpret_cast<int4 *>(s.xq)[i] = __ldcg(reinterpret_cast<const int4 *>(q) + i);
     for (uint32_t i = threadIdx.x; i < n / 64; i += MEGA_THREADS) { s.xs[i] = __ldcg(sc + i); s.xm[i] = __ldcg(sm + i); }
@@ -194,6 +204,8 @@ struct TeamSlot { uint8_t *wsm; float *s_f; uint32_t gw, nw, wid, wk, bar; };
 template <int FMT>
 __device__ __noinline__ void mega_gemv_fmt(const MegaMatrix *mm, const int8_t *xq, const float *xs, const int32_t *xm, float *out,
                                            const TeamSlot t, PipeState &ps) {
+    __builtin_assume(__isShared(xq)); __builtin_assume(__isShared(xs)); __builtin_assume(__isShared(xm));
+    __builtin_assume(__isShared(t.wsm)); __builtin_assume(__isShared(t.s_f));
     const GemvArgs a = mm->g;
     gemv_body<FMT, 1, false, true>(a, xq, xs, xm, out, t.wsm, t.s_f, t.gw, t.nw, t.wid, t.wk, t.bar, ps);
 }
@@ -220,6 +232,7 @@ __device__ __noinline__ void mega_gemv(const MegaMatrix *mm, float *out, const M
 
 // first maximum of logits[n] (argmax_scalar, real_llm.rs:9914-9924), by one CTA
 __device__ __noinline__ uint32_t cta_argmax(const float *logits, uint32_t n, const MegaSmem &s) {
+    MEGA_SMEM_HINTS(s)
     float bv = -INFINITY;
     uint32_t bi = 0xffffffffu;
     for (uint32_t i = threadIdx.x; i < n; i += MEGA_THREADS) {

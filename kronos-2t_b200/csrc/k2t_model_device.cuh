@@ -212,6 +212,15 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     constexpr int QW = HD / 4, NB = HD / 64;
     constexpr uint32_t NT = ATTN_THREADS, NW = ATTN_THREADS / 32;
     constexpr uint32_t ROW = KV4 ? HD / 2 : HD;            // bytes of one cached key / value row
+    // The work areas arrive as generic pointers; telling the compiler that they are shared memory turns every access into
+    // a shared-memory instruction (generic loads of shared memory cost several times the latency: the value chain below
+    // ran at 40 cycles per position with them).
+    __builtin_assume(__isShared(s.sc)); __builtin_assume(__isShared(s.vbuf)); __builtin_assume(__isShared(s.head));
+    __builtin_assume(__isShared(s.hq)); __builtin_assume(__isShared(s.hs)); __builtin_assume(__isShared(s.o));
+    __builtin_assume(__isShared(s.red)); __builtin_assume(__isShared(s.inv)); __builtin_assume(__isShared(s.bar));
+    __builtin_assume(__isShared(s.wg)); __builtin_assume(__isShared(s.cbf)); __builtin_assume(__isShared(s.qs_val));
+    __builtin_assume(__isShared(s.qs_c)); __builtin_assume(__isShared(s.qs_idx)); __builtin_assume(__isShared(s.hq4));
+    __builtin_assume(__isShared(s.hs16));
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t group = A.n_q / A.n_kv, kvh = qh / group, ctx = pos + 1, layer = A.layer;
     const size_t slot0 = ((size_t)layer * A.n_kv + kvh) * A.max_seq;
@@ -483,6 +492,8 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
                          : "=r"(ok) : "r"(vbar) : "memory");
         copy_failed = !ok;
     }
+    copy_failed = __syncthreads_or(copy_failed) != 0;      // the same verdict in every thread (there are barriers below)
+    if (copy_failed && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
     if (tid < HD && !copy_failed) {
         // a zero weight skips the position (as the CPU loop does): select, not branch.  Eight positions are
         // loaded before their fma chain starts, so the chain runs at fma latency, not shared-memory latency.
@@ -518,38 +529,42 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         } else {
             // int8 -> fp32 without the conversion unit (a quarter-rate pipe that would bound this loop): for a byte b,
             // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
-            const float *wp = s.sc;
-            const uint8_t *vp = reinterpret_cast<const uint8_t *>(s.vbuf) + tid;
-            auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
             // The CPU loop skips positions whose weight is zero; the plain fma gives the same bits (w >= 0 and the values
-            // are finite: o + (+-0) = o, and +0 + (-0) = +0), so the chain is one fma per position.  The next eight
-            // positions are loaded while the current eight run.
+            // are finite: o + (+-0) = o, and +0 + (-0) = +0), so the chain is one fma per position.
+            // A warp owns 32 dimensions = 8 words of a row: one 32-bit load per lane fetches those words for FOUR positions
+            // (lane l: word l % 8 of position 4g + l / 8); every lane then takes the word holding its dimension by shuffle.
+            // Byte loads of one's own dimension ran at 40 cycles per position (one shared-memory round trip each).
+            const float *wp = s.sc;
+            const uint8_t *vb = reinterpret_cast<const uint8_t *>(s.vbuf);
+            auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
+            const uint32_t wbase = tid & ~31u, my_word = lane >> 2, my_sel = 0x7650u + (lane & 3u);
+            const uint8_t *src = vb + (size_t)(lane >> 3) * HD + wbase + 4 * (lane & 7u);
             uint32_t j = 0;
-            float w[8], wn[8];
-            uint32_t v[8], vn[8];
-            if (pos >= 8) {
+            for (; j + 16 <= pos; j += 16) {
+                uint32_t wd[4];
+                float4 wt[4];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) { w[u] = wp[u]; v[u] = vp[u * HD]; }
+                for (int g = 0; g < 4; ++g) {
+                    wd[g] = *reinterpret_cast<const uint32_t *>(src + (size_t)(j + 4 * g) * HD) ^ 0x80808080u;
+                    wt[g] = *reinterpret_cast<const float4 *>(wp + j + 4 * g);
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const float wr[4] = {wt[g].x, wt[g].y, wt[g].z, wt[g].w};
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const uint32_t word = __shfl_sync(0xffffffffu, wd[g], r * 8 + my_word);
+                        const float val = __fsub_rn(__uint_as_float(prmt(word, 0x4B000000u, my_sel)), 8388736.0f);
+                        o = __fmaf_rn(val, wr[r], o);
+                    }
+                }
             }
-            for (; j + 16 <= pos; j += 8) {
-#pragma unroll
-                for (int u = 0; u < 8; ++u) { wn[u] = wp[j + 8 + u]; vn[u] = vp[(j + 8 + u) * HD]; }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) o = __fmaf_rn(to_f32(v[u]), w[u], o);
-#pragma unroll
-                for (int u = 0; u < 8; ++u) { w[u] = wn[u]; v[u] = vn[u]; }
-            }
-            if (j + 8 <= pos) {
-#pragma unroll
-                for (int u = 0; u < 8; ++u) o = __fmaf_rn(to_f32(v[u]), w[u], o);
-                j += 8;
-            }
-            for (; j < pos; ++j) o = __fmaf_rn(to_f32(vp[j * HD]), wp[j], o);
+            for (; j < pos; ++j) o = __fmaf_rn(to_f32(vb[(size_t)j * HD + tid]), wp[j], o);
             // the current position: its value row is still in shared memory
             o = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), wp[pos], o);
         }
     }
-    if (__syncthreads_or(copy_failed) && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
+    __syncthreads();
     if (tid == 0 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
     if (tid < HD) s.o[tid] = o;
     __syncthreads();
