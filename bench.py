@@ -34,6 +34,11 @@ FORMATS = ["b4", "b5", "b6", "nf4g128"]
 WORKLOAD = "gemv_sweep_batch1: K x N in 2048x2048, 2048x8192, 8192x2048, 2048x49152; b4, b5, b6, nf4g128"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one 2048x49152 launch from the ncu --set full captures summarised under
+# profiles/ (gemv_b4_2048x49152.md, gemv_nf4g128_2048x49152.md)
+NCU_DRAM_BYTES_PER_LAUNCH = {"b4": 53507328 + 69120, "nf4g128": 51939072 + 62720}
+
+
 def fmt_spec(fmt):
     if fmt.startswith("b"):
         return ("bipolar", int(fmt[1]), 1)
@@ -330,7 +335,9 @@ def run_b200(args, rank, world, local_rank):
     achieved = big_b / big_us / 1e3
     roofline = {"bound": "hbm", "kernel": "gemv_kernel, the four 2048x49152 launches of a sweep pass (78% of its bytes)",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "traffic_note": "ncu dram bytes per launch = algorithmic bytes within 0.1% (profiles/)",
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH["b4"], "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, b4 2048x49152)",
+                "traffic_note": "ncu captures of the b4 and nf4g128 launches: 53.58 / 52.00 MB against 53.68 / 52.10 MB algorithmic (profiles/)",
+                "traffic_per_format": NCU_DRAM_BYTES_PER_LAUNCH,
                 "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak},
                 "per_launch": kernels}
 

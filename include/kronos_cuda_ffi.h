@@ -138,8 +138,7 @@ typedef struct KronosCudaEngine KronosCudaEngine;
 
 /* LlamaConfig scalars the device forward needs (src/model/real_llm.rs:91-457), as MetalLlamaEngine::try_new
  * receives them through `cfg`, plus the KV format (kv_bits: 8 = int8 Hadamard cache, 4 = NF4 Hadamard cache as
- * selected by RealLlamaEngine::set_kv_bits, real_llm.rs:1731-1735; the NF4 cache serves contexts of up to 512
- * positions in this version). */
+ * selected by RealLlamaEngine::set_kv_bits, real_llm.rs:1731-1735). */
 typedef struct KronosCudaEngineConfig {
     uint32_t hidden_size, num_layers, num_attention_heads, num_key_value_heads, head_dim,
              intermediate_size, vocab_size, max_seq_len;

@@ -164,7 +164,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 qa.pos = e->d_pos; qa.pos_offset = t;
                 qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
                 qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
-                qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope;
+                qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
                 if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
                 AttnArgs aa{};
                 aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
@@ -172,7 +172,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
                 aa.out_q = oq; aa.out_scales = os; aa.out_sums = om; aa.out_chunk0 = c.o_chunk0;
                 aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
-                aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd);
+                aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd); aa.kv_bits = c.kv_bits;
                 if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
             }
         }
@@ -232,7 +232,9 @@ bool ensure_graphs(KronosCudaEngine *e) {
     // easier to attribute.  They run token 0 at the LAST position of the cache: that slot is only ever read after a
     // real token has been written to it, so a prompt already in the cache is not disturbed (callers set position
     // and token before every replay).
-    const int variants = e->cfg.kv_bits == 8 ? 2 : 1;       // the split-KV (long context) kernels read the int8 cache only
+    // the split-KV variant is warmed up at the last cache position; with an NF4 cache of at most 512 positions that would be
+    // a short context, which those kernels leave to the fused kernel - and such an engine never needs the variant
+    const int variants = (e->cfg.kv_bits == 8 || e->cfg.max_seq_len > ATTN_EXACT_CTX) ? 2 : 1;
     for (int long_ctx = 0; long_ctx < variants; ++long_ctx)
         if (!set_u32(e, e->d_pos, e->cfg.max_seq_len - 1) || !set_u32(e, e->d_token, 0) || !enqueue_batch(e, 1, true, Tail::Greedy, long_ctx != 0) ||
             !sync_and_check(ctx, "engine warm-up step"))
@@ -755,8 +757,6 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     if ((!embeds && !tokens) || !last_logits) return fail(ctx, "forward: NULL buffer"), -1;
     if (n_tok == 0) return fail(ctx, "forward: n_tok is 0"), -1;
     if (pos_start + n_tok > e->cfg.max_seq_len) return fail(ctx, "forward: sequence would exceed max_seq_len"), -1;
-    if (e->cfg.kv_bits == 4 && pos_start + n_tok > ATTN_EXACT_CTX)
-        return fail(ctx, "forward: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (!make_current(ctx)) return -1;
     if (tokens)
         for (size_t t = 0; t < n_tok; ++t)
@@ -778,8 +778,10 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
     // prompt: batches of up to MAX_BATCH tokens per weight pass (forward_prompt / forward_batch_sdot_impl,
     // real_llm.rs:7407-7448, 7450-7860)
     if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
-    for (size_t t0 = 0; t0 < n_tok; t0 += MAX_BATCH) {
-        const uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
+    for (size_t t0 = 0, T_done = 0; t0 < n_tok; t0 += T_done) {
+        uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
+        const size_t p0 = pos_start + t0;
+        if (p0 < ATTN_EXACT_CTX && p0 + T > ATTN_EXACT_CTX) T = (uint32_t)(ATTN_EXACT_CTX - p0);    // a batch stays on one side of the attention switch
         const bool last = t0 + T == n_tok;
         if (tokens) {
             if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens + t0, T * 4, cudaMemcpyHostToDevice, ctx->stream), "copy tokens")) return -1;
@@ -789,6 +791,7 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
         const Tail tail = all_logits ? Tail::AllLogits : (last ? Tail::LastLogits : Tail::None);
         if (!enqueue_batch(e, T, tokens != nullptr, tail, pos_start + t0 + T > ATTN_EXACT_CTX)) return -1;
         e->last_row = T - 1;
+        T_done = T;
         if (all_logits && !cuda_ok(ctx, cudaMemcpyAsync(all_logits + t0 * v, e->logits, (size_t)T * v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
         if (!all_logits && last && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
         // the token / embedding staging buffers are reused by the next batch: the copies above are stream-ordered
@@ -817,8 +820,6 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     const size_t vocab_all = e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size;
     if (first_token >= vocab_all) return fail(ctx, "decode_greedy: token id out of range"), -1;
     if (pos_start + n_steps > e->cfg.max_seq_len) return fail(ctx, "decode_greedy: sequence would exceed max_seq_len"), -1;
-    if (e->cfg.kv_bits == 4 && pos_start + n_steps > ATTN_EXACT_CTX)
-        return fail(ctx, "decode_greedy: the NF4 KV cache is implemented for contexts of up to 512 positions"), -1;
     if (n_steps == 0) return 0;
     if (!make_current(ctx)) return -1;
     e->last_row = 0;

@@ -224,6 +224,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
 // (one scale per head) for the attention kernel.
 __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     __shared__ float s_head[4][128];
+    __shared__ float s_qv[4][64], s_qc[4][64];     // NF4 quantizer scratch per warp
+    __shared__ uint8_t s_qi[4][64];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t head = blockIdx.x * 4 + warp, hd = a.head_dim, half = hd / 2;
     pdl_wait();
@@ -277,6 +279,19 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
         warp_fwht64(v0[b], v1[b], b, lane);
         mx = fmaxf(mx, fmaxf(fabsf(v0[b]), fabsf(v1[b])));
     }
+    if (!is_q && a.kv_bits == 4) {       // NF4 cache entry: packed indices + one bf16 scale per 64 values (store_hadamard_q4_head_raw)
+        const uint32_t kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
+        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + pos;
+        uint8_t *row = reinterpret_cast<uint8_t *>(is_k ? a.k_q8 : a.v_q8) + slot * (hd / 2);
+        uint16_t *sc = reinterpret_cast<uint16_t *>(is_k ? a.k_scale : a.v_scale) + slot * nb;
+        for (uint32_t b = 0; b < nb; ++b) {
+            uint16_t sb;
+            const uint32_t byte = warp_quant64_q4(v0[b], v1[b], lane, s_qv[warp], s_qc[warp], s_qi[warp], &sb);
+            row[b * 32 + lane] = (uint8_t)byte;
+            if (lane == 0) sc[b] = sb;
+        }
+        return;
+    }
     mx = warp_max(mx);
     int8_t *dst_q;
     float *dst_s;
@@ -305,12 +320,14 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
 // for bit.  Softmax is the online form; partial (max, sum, out) per split are merged by attn_finish_kernel.  Sums run in a different order than the CPU's
 // position-ascending chains: the output agrees to fp32 rounding, not bit for bit.
 
-template <int HD>
+template <int HD, bool KV4>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
-    constexpr int QW = HD / 4;            // int32 words per query / key row
+    constexpr int QW = HD / 4;            // int32 words per query row
     constexpr int NB = HD / 64;
-    __shared__ int s_q[4][8][QW];         // [warp][query in group][words]
-    __shared__ float s_p[4][8][32];       // probabilities of the current 32 positions
+    constexpr int ROW = KV4 ? HD / 2 : HD;            // bytes of a cached key / value row
+    __shared__ int s_q[4][8][QW];         // [warp][query in group][words] (NF4 cache: gathered in the packed column order)
+    __shared__ float s_p[4][8][KV4 ? NB : 1][32];     // value weights of the current 32 positions (per 64-value group for NF4)
+    __shared__ float s_cb[16];            // NF4 centroids
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t split = blockIdx.x * 4 + warp, kvh = blockIdx.y;
     pdl_wait();
@@ -321,10 +338,22 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     const uint32_t per = split_span(ctx, a.n_split);
     const uint32_t t_lo = min(ctx, split * per), t_hi = min(ctx, t_lo + per);
     const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
-    const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
+    const uint8_t *K = reinterpret_cast<const uint8_t *>(a.k_q8) + slot0 * ROW, *V = reinterpret_cast<const uint8_t *>(a.v_q8) + slot0 * ROW;
     const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
-    for (uint32_t i = lane; i < G * QW; i += 32)
-        s_q[warp][i / QW][i % QW] = __ldcg(reinterpret_cast<const int *>(a.q_i8 + (size_t)(kvh * G) * HD) + i);
+    const uint16_t *ks16 = reinterpret_cast<const uint16_t *>(a.k_scale) + slot0 * NB, *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
+    if (KV4 && lane < 16) s_cb[lane] = NF4_KV_CENTROIDS[lane];      // every warp writes the same values
+    for (uint32_t i = lane; i < G * QW; i += 32) {
+        const int8_t *qb = a.q_i8 + (size_t)(kvh * G + i / QW) * HD;
+        const uint32_t wi = i % QW;
+        if (KV4) {        // packed word w of a 64-value group holds columns (c, 16+c, c+1, 16+c+1 | c+2, ...) of a 32-column half
+            const uint32_t g = wi / 16, w = (wi % 16) / 2, u = wi % 2;
+            const int8_t *p = qb + g * 64 + (w / 4) * 32 + 4 * (w % 4);
+            s_q[warp][i / QW][wi] = (int)((uint32_t)(uint8_t)__ldcg(p + 2 * u) | ((uint32_t)(uint8_t)__ldcg(p + 16 + 2 * u) << 8) |
+                                          ((uint32_t)(uint8_t)__ldcg(p + 2 * u + 1) << 16) | ((uint32_t)(uint8_t)__ldcg(p + 16 + 2 * u + 1) << 24));
+        } else {
+            s_q[warp][i / QW][wi] = __ldcg(reinterpret_cast<const int *>(qb) + wi);
+        }
+    }
     __syncwarp();
     float qas[8], m[8], l[8], o[8][HD / 16];   // lane owns dims d0..d0+3 of (HD/16 ... ) see below
     // value phase mapping: 16 lanes x 4 dims cover 64 dims; for HD = 128 each lane owns two such groups
@@ -340,30 +369,60 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         const uint32_t t = t0 + lane;
         const bool on = t < t_hi;
         // scores of position t for every query of the group
-        int kw[QW];
+        int kw[ROW / 4];
         if (on) {
 #pragma unroll
-            for (int i = 0; i < QW / 4; ++i) {
-                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
+            for (int i = 0; i < ROW / 16; ++i) {
+                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * ROW) + i);
                 kw[4 * i] = v.x; kw[4 * i + 1] = v.y; kw[4 * i + 2] = v.z; kw[4 * i + 3] = v.w;
             }
         }
         const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
         const bool grouped = t - tile0 < (tile_n & ~7u);
-        const float kst = on ? __ldcg(ks + t) : 0.0f;
-        const float vst = on ? __ldcg(vs + t) : 0.0f;
+        float kst[KV4 ? NB : 1], vst[KV4 ? NB : 1];
+        if (KV4) {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                kst[b] = on ? bf16_bits_to_f32(__ldcg(ks16 + (size_t)t * NB + b)) : 0.0f;
+                vst[b] = on ? bf16_bits_to_f32(__ldcg(vs16 + (size_t)t * NB + b)) : 0.0f;
+            }
+        } else {
+            kst[0] = on ? __ldcg(ks + t) : 0.0f;
+            vst[0] = on ? __ldcg(vs + t) : 0.0f;
+        }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             if (g >= (int)G) break;
-            int dot = 0;
-            if (on) {
+            float s = -INFINITY;
+            if (KV4) {        // causal_gqa_group_q4_or_window: total += ((dot_b * ks_b) * q_s) per 64-value group
+                if (on) {
+                    s = 0.0f;
 #pragma unroll
-                for (int i = 0; i < QW; ++i) dot = __dp4a(kw[i], s_q[warp][g][i], dot);
+                    for (int b = 0; b < NB; ++b) {
+                        int up = 0, dn = 0;
+#pragma unroll
+                        for (int w = 0; w < 8; ++w) {
+                            const uint32_t x = (uint32_t)kw[b * 8 + w], y = x ^ 0x88888888u;
+                            const int q0 = s_q[warp][g][b * 16 + 2 * w], q1 = s_q[warp][g][b * 16 + 2 * w + 1];
+                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y), q0, up);
+                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x), q0, dn);
+                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y >> 16), q1, up);
+                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x >> 16), q1, dn);
+                        }
+                        s = __fadd_rn(s, __fmul_rn(__fmul_rn((float)(up - dn), kst[b]), qas[g]));
+                    }
+                }
+            } else {
+                int dot = 0;
+                if (on) {
+#pragma unroll
+                    for (int i = 0; i < QW; ++i) dot = __dp4a(kw[i], s_q[warp][g][i], dot);
+                }
+                // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+                s = !on ? -INFINITY
+                  : grouped ? __fmul_rn((float)dot, __fmul_rn(kst[0], qas[g]))
+                            : __fmul_rn(__fmul_rn((float)dot, kst[0]), qas[g]);
             }
-            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
-            const float s = !on ? -INFINITY
-                          : grouped ? __fmul_rn((float)dot, __fmul_rn(kst, qas[g]))
-                                    : __fmul_rn(__fmul_rn((float)dot, kst), qas[g]);
             const float m_new = fmaxf(m[g], warp_max(s));
             const float corr = m[g] == -INFINITY ? 0.0f : exp_poly(m[g] - m_new);
             const float p = on ? exp_poly(s - m_new) : 0.0f;
@@ -371,7 +430,8 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
 #pragma unroll
             for (int d = 0; d < HD / 16; ++d) o[g][d] *= corr;
             m[g] = m_new;
-            s_p[warp][g][lane] = __fmul_rn(p, vst);     // weight of V row t
+#pragma unroll
+            for (int b = 0; b < (KV4 ? NB : 1); ++b) s_p[warp][g][b][lane] = __fmul_rn(p, vst[b]);     // weight of V row t
         }
         __syncwarp();
         // values: half-warp hw takes positions t0 + hw, t0 + hw + 2, ...
@@ -379,15 +439,23 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         for (uint32_t j = hw; j < n_here; j += 2) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-                const char4 v = __ldcg(reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * HD + b * 64 + dl * 4));
+                float c0, c1, c2, c3;
+                if (KV4) {    // dims 4 dl .. 4 dl + 3 of the group sit in one packed word: low nibbles for columns 0..15 of a half, high for 16..31
+                    const uint32_t e = dl * 4, r = e % 32, shift = r < 16 ? 0u : 4u;
+                    const uint32_t word = __ldcg(reinterpret_cast<const uint32_t *>(V + (size_t)(t0 + j) * ROW + b * 32 + (e / 32) * 16 + (r % 16))) >> shift;
+                    c0 = s_cb[word & 15u]; c1 = s_cb[(word >> 8) & 15u]; c2 = s_cb[(word >> 16) & 15u]; c3 = s_cb[(word >> 24) & 15u];
+                } else {
+                    const char4 v = __ldcg(reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * ROW + b * 64 + dl * 4));
+                    c0 = (float)v.x; c1 = (float)v.y; c2 = (float)v.z; c3 = (float)v.w;
+                }
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     if (g >= (int)G) break;
-                    const float w = s_p[warp][g][j];
-                    o[g][4 * b + 0] = __fmaf_rn((float)v.x, w, o[g][4 * b + 0]);
-                    o[g][4 * b + 1] = __fmaf_rn((float)v.y, w, o[g][4 * b + 1]);
-                    o[g][4 * b + 2] = __fmaf_rn((float)v.z, w, o[g][4 * b + 2]);
-                    o[g][4 * b + 3] = __fmaf_rn((float)v.w, w, o[g][4 * b + 3]);
+                    const float w = s_p[warp][g][KV4 ? b : 0][j];
+                    o[g][4 * b + 0] = __fmaf_rn(c0, w, o[g][4 * b + 0]);
+                    o[g][4 * b + 1] = __fmaf_rn(c1, w, o[g][4 * b + 1]);
+                    o[g][4 * b + 2] = __fmaf_rn(c2, w, o[g][4 * b + 2]);
+                    o[g][4 * b + 3] = __fmaf_rn(c3, w, o[g][4 * b + 3]);
                 }
             }
         }
@@ -430,6 +498,7 @@ __global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
     pdl_trigger();
     const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + a.pos_offset + 1;
     float o = 0.0f;
+    if (ctx <= ATTN_EXACT_CTX && a.kv_bits == 4) return;      // the NF4 cache at these lengths belongs to attn_fused_kernel
     if (ctx <= ATTN_EXACT_CTX) {
         const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
         const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
@@ -672,8 +741,10 @@ cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
     dim3 grid((a.n_split + 3) / 4, a.n_kv);
     cudaError_t e;
-    if (a.head_dim == 64) e = launch_kernel(attn_partial_kernel<64>, grid, dim3(128), 0, s, pdl, a);
-    else if (a.head_dim == 128) e = launch_kernel(attn_partial_kernel<128>, grid, dim3(128), 0, s, pdl, a);
+    if (a.head_dim == 64) e = a.kv_bits == 4 ? launch_kernel(attn_partial_kernel<64, true>, grid, dim3(128), 0, s, pdl, a)
+                                             : launch_kernel(attn_partial_kernel<64, false>, grid, dim3(128), 0, s, pdl, a);
+    else if (a.head_dim == 128) e = a.kv_bits == 4 ? launch_kernel(attn_partial_kernel<128, true>, grid, dim3(128), 0, s, pdl, a)
+                                                   : launch_kernel(attn_partial_kernel<128, false>, grid, dim3(128), 0, s, pdl, a);
     else return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
     if (a.head_dim == 64) return launch_kernel(attn_finish_kernel<64>, dim3(a.n_kv * a.group), dim3(64), 0, s, pdl, a);

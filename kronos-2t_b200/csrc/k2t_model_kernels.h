@@ -28,6 +28,7 @@ struct QkvPostArgs {
     int8_t *q_i8; float *q_scale;            // rotated int8 queries, one scale per head
     int8_t *k_q8, *v_q8; float *k_scale, *v_scale;   // cache: [layer][kv head][max_seq][head_dim] / [..][max_seq]
     uint32_t n_q, n_kv, head_dim, max_seq, layer;
+    uint32_t kv_bits;            // 8: int8 rows + fp32 scale; 4: packed NF4 rows + bf16 scale per 64 values
     float eps;
     int32_t qk_norm_after_rope;
 };
@@ -46,6 +47,7 @@ struct AttnArgs {
     int8_t *out_q; float *out_scales; int32_t *out_sums;   // activation of o_proj
     uint32_t out_chunk0;         // global index of the first o_proj input chunk of this rank (tensor parallel), else 0
     uint32_t n_kv, group, head_dim, max_seq, layer, n_split;
+    uint32_t kv_bits;            // 8 or 4 (see QkvPostArgs)
     float attn_scale;
 };
 

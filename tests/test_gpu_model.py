@@ -200,8 +200,9 @@ def test_head_dim_128_and_wide_groups(ctx, oracle, cfg, mode, kw):
         eng.close(); ref.close()
 
 
-@pytest.mark.parametrize("cfg,mode", [(LONG, "b4"), (LONG128, "nf4g128")])
-def test_split_attention_beyond_512_positions(ctx, oracle, cfg, mode):
+@pytest.mark.parametrize("cfg,mode,kv_bits", [(LONG, "b4", 8), (LONG128, "nf4g128", 8), (LONG, "b5", 4), (LONG128, "b4", 4)])
+def test_split_attention_beyond_512_positions(ctx, oracle, cfg, mode, kv_bits):
+    cfg = dict(cfg, kv_bits=kv_bits)
     spec, eng, ref = make(ctx, oracle, cfg, mode, seed=8)
     try:
         n = cfg["max_seq"] - 1
@@ -220,9 +221,7 @@ def test_split_attention_beyond_512_positions(ctx, oracle, cfg, mode):
         assert np.mean(err <= TOL) >= 0.9 and err.max() <= 1e-2, (float(np.mean(err <= TOL)), float(err.max()))
         for pos in (0, 511, 512, n - 1):                   # a one-layer model: KV entries never depend on attention
             for kvh in range(cfg["n_kv"]):
-                gk, gks, gv, gvs = eng.read_kv(0, kvh, pos)
-                wk, wks, wv, wvs = ref.read_kv(0, kvh, pos)
-                assert np.array_equal(gk, wk) and np.array_equal(gv, wv) and gks == wks and gvs == wvs
+                assert all(np.array_equal(a, b) for a, b in zip(eng.read_kv(0, kvh, pos), ref.read_kv(0, kvh, pos)))
     finally:
         eng.close(); ref.close()
 
