@@ -181,8 +181,8 @@ typedef struct KronosCudaLayerDesc {
 /* MetalLlamaEngine::try_new (metal_gpu.rs:1196-1206): copies every tensor to HBM, allocates the KV cache
  * for max_seq_len positions and the per-token workspace.  rope_cos_sin = build_rope_table()'s
  * [max_seq_len][head_dim] rows (cos half, sin half; real_llm.rs:9212-9236).  embed_bf16 = untied
- * embedding table [vocab][hidden] or NULL for tied embeddings (the lm_head row, rotated back:
- * embed_token_into, real_llm.rs:8063-8097).  Returns NULL on error (kronos_cuda_last_error(ctx)). */
+ * embedding table [vocab][hidden] (all vocab_total rows on every rank under tensor parallelism) or NULL for
+ * tied embeddings (the lm_head row, rotated back: embed_token_into, real_llm.rs:8063-8097).  Returns NULL on error (kronos_cuda_last_error(ctx)). */
 KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const KronosCudaEngineConfig *cfg,
                                             const float *rope_cos_sin, const KronosCudaLayerDesc *layers,
                                             size_t n_layers, const float *final_norm,

@@ -491,7 +491,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * c.max_seq_len;
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
-              (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)c.vocab_size * h, embed_bf16)) &&
+              (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)(c.tp_size > 1 ? c.vocab_total : c.vocab_size) * h, embed_bf16)) &&   // every rank keeps the whole table
               // per-token vectors hold MAX_BATCH tokens (prompt batches), [token][n]
               dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
               dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
