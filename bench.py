@@ -345,6 +345,9 @@ def run_b200(args, rank, world, local_rank):
     if not args.no_decode:
         decode = decode_tok_s(ctx, stream, timed_region=lambda fn: timed(fn, 1)[0], world=world)
 
+        if not args.no_decode_models:
+            decode["models"] = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(mats)
@@ -476,8 +479,82 @@ def decode_tok_s(ctx, stream, timed_region, world):
     return out
 
 
+def _prefill(eng, rng, vocab, lo, hi, timed_region=None):
+    """Prompt positions [lo, hi) of random token ids in 4-token weight passes; returns tok/s when timed."""
+    toks = rng.integers(0, vocab, hi - lo).astype("uint32")
+    if timed_region is None:
+        eng.forward_token_ids(toks, pos_start=lo)
+        return None
+    ms = timed_region(lambda: eng.forward_token_ids(toks, pos_start=lo))
+    return (hi - lo) / (ms / 1e3)
+
+
+def decode_models(ctx, timed_region, rank, world, dist):
+    """Whole-token decode of the larger model shapes (random codes; time does not depend on the values).
+
+    One GPU: the SmolLM2-1.7B shape in nf4g128 at contexts 512 and 8192 with the int8 and the NF4 KV cache, and the
+    Qwen2-7B shape in the p55454 plane tier at context 4096.  2 or 4 GPUs: the Qwen2-7B shape tensor-parallel over all
+    ranks (8 GPUs: two groups of four, since 28 query heads do not split eight ways); the sum / gather steps run
+    inside the engine over peer memory."""
+    import numpy as np
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(23))
+    out = []
+    steps = 64
+    if world == 1:
+        for kv_bits in (8, 4):
+            cfg = dict(synth.SMOLLM2_1_7B, kv_bits=kv_bits)
+            eng = k2.Engine(ctx, synth.random_model(cfg, "nf4g128", seed=5, share_layers=True))
+            _prefill(eng, rng, cfg["vocab"], 0, 64)                                   # warm-up
+            prefill = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region)
+            res = {"model": "SmolLM2-1.7B-shaped (hidden 2048, 24 layers, 32q/32kv heads of 64, MLP 8192, vocab 49152), nf4g128",
+                   "kv": "int8" if kv_bits == 8 else "nf4", "prefill_tok_s_1024": prefill, "weight_bytes_per_token": eng.weight_bytes,
+                   "kv_bytes_per_pos": eng.kv_bytes_per_pos}
+            for name, pos in (("ctx_512", 512 - steps), ("ctx_8192", 8192)):
+                if pos > 1024:
+                    _prefill(eng, rng, cfg["vocab"], 1024, pos)
+                eng.decode_greedy(1, pos, 8)                                          # warm-up (graph capture)
+                ms = min(timed_region(lambda: eng.decode_greedy(1, pos, steps)) for _ in range(2))
+                res[name] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps],
+                             "weight_gbs": eng.weight_bytes * steps / (ms / 1e3) / 1e9}
+            eng.close()
+            out.append(res)
+    tp = world if world in (1, 2, 4) else 4
+    group, tp_rank = rank // tp, rank % tp
+    cfg = dict(synth.QWEN2_7B)
+    eng = k2.Engine(ctx, synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, tp=(tp, tp_rank), share_layers=True))
+    if tp > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.tp_handle())
+        eng.tp_attach(handles[group * tp:(group + 1) * tp])
+        dist.barrier()
+    _prefill(eng, rng, cfg["vocab"], 0, 64)
+    prefill = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region)
+    _prefill(eng, rng, cfg["vocab"], 1024, 4096)
+    eng.decode_greedy(1, 4096, 8)
+    ms = min(timed_region(lambda: eng.decode_greedy(1, 4096, steps)) for _ in range(2))
+    groups = world // tp
+    wb = eng.weight_bytes
+    if dist:
+        import torch
+        t = torch.tensor([float(wb)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        wb = int(t.item()) // groups
+    out.append({"model": "Qwen2-7B-shaped (hidden 3584, 28 layers, 28q/4kv heads of 128, MLP 18944, vocab 152064, qkv bias, untied), "
+                         "p55454 planes (qkv 5, o 5, gate_up 4, down 5, head 4)", "kv": "int8", "tp": tp, "groups": groups,
+                "prefill_tok_s_1024": prefill * groups,
+                "ctx_4096": {"tok_s": groups * steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [4096, 4096 + steps],
+                             "weight_gbs": groups * wb * steps / (ms / 1e3) / 1e9},
+                "weight_bytes_per_token": wb,
+                "exchange": None if tp == 1 else "2 partial-sum exchanges per layer + 1 logits gather per token, one kernel each over peer memory (no NCCL on the data path)"})
+    eng.close()
+    return out
+
+
 def run_decode_only(args, local_rank):
-    """Small whole-token run for profilers: engine of the decode workload's shape, 16-token prompt, N greedy steps."""
+    """Small whole-token run for profilers: engine of the chosen shape, 16-token prompt, then N greedy steps starting at
+    position --decode-ctx (positions in between stay zero: kernel time does not depend on the cached values)."""
     import numpy as np
     import torch
     import kronos_2t_b200 as k2
@@ -485,16 +562,30 @@ def run_decode_only(args, local_rank):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     ctx = k2.Context(local_rank)
-    eng = k2.Engine(ctx, synth.random_model(synth.SMOLLM2_135M, "b4", seed=3))
-    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, synth.SMOLLM2_135M["vocab"], 16).astype(np.uint32)
+    pos = max(args.decode_ctx, 15)
+    if args.decode_model == "1.7b":
+        cfg = dict(synth.SMOLLM2_1_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
+        spec = synth.random_model(cfg, "nf4g128", seed=5, share_layers=True)
+    elif args.decode_model == "7b":
+        cfg = dict(synth.QWEN2_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
+        spec = synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, share_layers=True)
+    else:
+        cfg = dict(synth.SMOLLM2_135M, kv_bits=args.kv_bits, max_seq=max(512, pos + args.decode_only + 1))
+        spec = synth.random_model(cfg, "b4", seed=3)
+    eng = k2.Engine(ctx, spec)
+    prompt = np.random.Generator(np.random.PCG64(11)).integers(0, cfg["vocab"], 16).astype(np.uint32)
     l0 = ctx.launch_count
     eng.forward_token_ids(prompt[:-1])
     l1 = ctx.launch_count
+    eng.decode_greedy(int(prompt[-1]), pos, 2)          # graph capture and warm-up
+    l2 = ctx.launch_count
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    toks = eng.decode_greedy(int(prompt[-1]), 15, args.decode_only)
+    toks = eng.decode_greedy(int(prompt[-1]), pos, args.decode_only)
     dt = time.perf_counter() - t0
-    print(json.dumps({"mode": "decode-only", "steps": args.decode_only, "prompt_launches": int(l1 - l0),
-                      "decode_launches": int(ctx.launch_count - l1), "wall_ms": dt * 1e3, "last_token": int(toks[-1])}))
+    print(json.dumps({"mode": "decode-only", "model": args.decode_model, "kv_bits": args.kv_bits, "pos_start": pos, "steps": args.decode_only,
+                      "prompt_launches": int(l1 - l0), "warmup_launches": int(l2 - l1), "decode_launches": int(ctx.launch_count - l2),
+                      "wall_ms": dt * 1e3, "ms_per_token": dt * 1e3 / args.decode_only, "last_token": int(toks[-1])}))
     eng.close()
     ctx.close()
 
@@ -559,8 +650,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode measurement")
+    ap.add_argument("--no-decode-models", action="store_true", help="skip the 1.7B / 7B-shaped decode measurements")
     ap.add_argument("--decode-only", type=int, default=0, metavar="N",
                     help="profiling mode: only the whole-token engine - a 16-token prompt, then N greedy steps")
+    ap.add_argument("--decode-model", default="135m", choices=["135m", "1.7b", "7b"], help="--decode-only: model shape")
+    ap.add_argument("--decode-ctx", type=int, default=15, help="--decode-only: position of the first greedy step")
+    ap.add_argument("--kv-bits", type=int, default=8, choices=[4, 8], help="--decode-only: KV cache format")
     ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")
     ap.add_argument("--tokens", type=int, default=1, help="tokens per launch in --case mode (1..4)")
     ap.add_argument("--no-graph", action="store_true", help="--case mode: skip the CUDA-graph replay timing")

@@ -47,6 +47,7 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    uint32_t kv_stride = 0;                   // cache positions per (layer, kv head): max_seq_len rounded up to 32, so every 32-position tile of rows and scales starts on 16 bytes
     // sparse-MoE workspace: normalised hidden state, per-route expert buffers
     float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr;
     int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
@@ -154,7 +155,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
                 fa.attn_tap = tap;
                 fa.out_q = oq; fa.out_scales = os; fa.out_sums = om; fa.err_flag = e->ctx->d_err;
-                fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = c.max_seq_len; fa.layer = l;
+                fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = e->kv_stride; fa.layer = l;
                 fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
                 fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
                 if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
@@ -163,7 +164,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 qa.qkv = qkv_t; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope;
                 qa.pos = e->d_pos; qa.pos_offset = t;
                 qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
-                qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = c.max_seq_len; qa.layer = l;
+                qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
                 qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
                 if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
                 AttnArgs aa{};
@@ -172,7 +173,8 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
                 aa.out_q = oq; aa.out_scales = os; aa.out_sums = om; aa.out_chunk0 = c.o_chunk0;
                 aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
-                aa.max_seq = c.max_seq_len; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd); aa.kv_bits = c.kv_bits;
+                aa.max_seq = e->kv_stride; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd); aa.kv_bits = c.kv_bits;
+                aa.err_flag = e->ctx->d_err;
                 if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
             }
         }
@@ -232,8 +234,8 @@ bool ensure_graphs(KronosCudaEngine *e) {
     // easier to attribute.  They run token 0 at the LAST position of the cache: that slot is only ever read after a
     // real token has been written to it, so a prompt already in the cache is not disturbed (callers set position
     // and token before every replay).
-    // the split-KV variant is warmed up at the last cache position; with an NF4 cache of at most 512 positions that would be
-    // a short context, which those kernels leave to the fused kernel - and such an engine never needs the variant
+    // The split-KV variant is warmed up at the last cache position too; an NF4 cache of at most ATTN_EXACT_CTX
+    // positions never needs that variant.
     const int variants = (e->cfg.kv_bits == 8 || e->cfg.max_seq_len > ATTN_EXACT_CTX) ? 2 : 1;
     for (int long_ctx = 0; long_ctx < variants; ++long_ctx)
         if (!set_u32(e, e->d_pos, e->cfg.max_seq_len - 1) || !set_u32(e, e->d_token, 0) || !enqueue_batch(e, 1, true, Tail::Greedy, long_ctx != 0) ||
@@ -339,7 +341,7 @@ bool decode_mega(KronosCudaEngine *e, uint32_t first_token, uint32_t pos_start, 
     MegaArgs a{};
     a.layers = e->d_mega_layers; a.head = e->d_mega_head;
     a.n_layers = c.num_layers; a.hidden = c.hidden_size; a.n_q = c.num_attention_heads; a.n_kv = c.num_key_value_heads;
-    a.head_dim = c.head_dim; a.inter = c.intermediate_size; a.vocab = c.vocab_size; a.max_seq = c.max_seq_len; a.kv_bits = c.kv_bits;
+    a.head_dim = c.head_dim; a.inter = c.intermediate_size; a.vocab = c.vocab_size; a.max_seq = e->kv_stride; a.kv_bits = c.kv_bits;
     a.eps = c.rms_norm_eps; a.attn_scale = 1.0f / sqrtf((float)c.head_dim); a.qk_norm_after_rope = c.qk_norm_after_rope;
     a.final_norm = e->final_norm; a.rope = e->rope;
     fill_embed_args(e, a.embed);
@@ -454,6 +456,12 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     KronosCudaEngine *e = new (std::nothrow) KronosCudaEngine();
     if (!e) { fail(ctx, "engine_create: out of host memory"); return nullptr; }
     e->ctx = ctx; e->cfg = c;
+    e->kv_stride = (c.max_seq_len + 31u) & ~31u;
+    {   // split-KV attention runs one warp per (kv head, split): enough splits to put about eight warps on every SM,
+        // at most 128 (a split is at least one 32-position tile of a context above ATTN_EXACT_CTX)
+        const uint32_t want = (8u * (uint32_t)ctx->sm_count + c.num_key_value_heads - 1) / c.num_key_value_heads;
+        e->n_split = std::min(128u, std::max(32u, (want + 3u) & ~3u));
+    }
     if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
     e->layers.resize(c.num_layers);
     auto bad = [&](const std::string &why) { std::string keep = why; kronos_cuda_engine_destroy(e); fail(ctx, keep); return (KronosCudaEngine *)nullptr; };
@@ -488,7 +496,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     e->lm_head = kronos_cuda_matrix_upload(ctx, lm_head, 0);
     if (!e->lm_head) return bad("engine_create: lm_head: " + ctx->err);
     e->weight_bytes += e->lm_head->dm.geom.file_bytes;
-    const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * c.max_seq_len;
+    const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * e->kv_stride;
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
               (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)(c.tp_size > 1 ? c.vocab_total : c.vocab_size) * h, embed_bf16)) &&   // every rank keeps the whole table
@@ -651,7 +659,7 @@ int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *e, uint32_t layer, uint32_t
         return fail(ctx, "read_kv: index out of range"), -1;
     if (e->cfg.kv_bits != 8) return fail(ctx, "read_kv: the engine holds an NF4 cache (use read_kv_q4)"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->cfg.max_seq_len + position, hd = e->cfg.head_dim;
+    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + position, hd = e->cfg.head_dim;
     cudaStream_t s = ctx->stream;
     if (!cuda_ok(ctx, cudaMemcpyAsync(k_q8, e->k_q8 + slot * hd, hd, cudaMemcpyDeviceToHost, s), "read_kv") ||
         !cuda_ok(ctx, cudaMemcpyAsync(v_q8, e->v_q8 + slot * hd, hd, cudaMemcpyDeviceToHost, s), "read_kv") ||
@@ -671,7 +679,7 @@ int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *e, uint32_t layer, uint3
         return fail(ctx, "read_kv_q4: index out of range"), -1;
     if (e->cfg.kv_bits != 4) return fail(ctx, "read_kv_q4: the engine holds an int8 cache (use read_kv)"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->cfg.max_seq_len + position, hd = e->cfg.head_dim;
+    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + position, hd = e->cfg.head_dim;
     const size_t nb = hd / 64;
     cudaStream_t s = ctx->stream;
     if (!cuda_ok(ctx, cudaMemcpyAsync(k_q4, reinterpret_cast<uint8_t *>(e->k_q8) + slot * hd / 2, hd / 2, cudaMemcpyDeviceToHost, s), "read_kv_q4") ||
@@ -702,7 +710,7 @@ int64_t kronos_cuda_engine_kv_export(KronosCudaEngine *e, size_t lo, size_t hi, 
     if (!out || cap < total) return fail(ctx, "kv_export: output buffer too small"), -1;
     if (!make_current(ctx)) return -1;
     std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
-    const size_t S = e->cfg.max_seq_len;
+    const size_t S = e->kv_stride;
     cudaStream_t st = ctx->stream;
     if (!cuda_ok(ctx, cudaMemcpy2DAsync(kd.data(), n * db, reinterpret_cast<uint8_t *>(e->k_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(vd.data(), n * db, reinterpret_cast<uint8_t *>(e->v_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
@@ -729,7 +737,7 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, s
     if (n == 0) return 0;
     if (!data || len < n * kronos_cuda_engine_kv_bytes_per_pos(e)) return fail(ctx, "kv_import: blob is shorter than n positions"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->cfg.max_seq_len;
+    const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->kv_stride;
     std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
     const uint8_t *r = data;
     for (size_t p = 0; p < n; ++p)

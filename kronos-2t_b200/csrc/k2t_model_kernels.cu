@@ -3,6 +3,8 @@
 // RoPE / KV store / query quantization, split-KV decode attention over the int8 Hadamard cache,
 // SwiGLU + rotation + quantization, argmax.  Everything position dependent reads the position from
 // device memory so that one captured CUDA graph serves every decode step.
+#include <algorithm>
+
 #include "k2t_model_device.cuh"
 
 namespace k2t {
@@ -30,11 +32,11 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 // ------------------------------------------------------------------------------------------------
 // residual add + RMSNorm + FWHT-64 + int8  (rms_norm 9858-9898 + exec_hidden_proj!)
 // ------------------------------------------------------------------------------------------------
-// One CTA of 256 threads (8 warps).  hidden += delta (if given, written back), then the activation of
+// One CTA per token, 256 to 1024 threads (a warp per 64-value chunk where that fits).  hidden += delta (if given, written back), then the activation of
 // the next projection.  The sum of squares follows dot_f32_neon (real_llm.rs:9736-9800) exactly: 16 fma
 // accumulators over 16-element strides (lanes 0..15 of warp 0 run the 16 chains over the staged vector),
 // combined (a0+a1)+(a2+a3) lane-wise and then pairwise - so inv_rms is the CPU value bit for bit.
-__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
+__global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
                                                             const float *__restrict__ w, uint32_t n, float eps,
                                                             int8_t *__restrict__ q, float *__restrict__ scales,
                                                             int32_t *__restrict__ sums, float *__restrict__ x_norm) {
@@ -49,7 +51,8 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     }
     pdl_wait();
     pdl_trigger();
-    for (uint32_t i = tid; i < n / 4; i += 256) {
+    const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
+    for (uint32_t i = tid; i < n / 4; i += nthr) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
             const float4 d = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
@@ -62,7 +65,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     if (warp == 0) {
         float acc = 0.0f;
         if (lane < 16) {
-#pragma unroll 8
+#pragma unroll 16
             for (uint32_t i = lane; i < n; i += 16) { const float v = s_x[i]; acc = __fmaf_rn(v, v, acc); }
         }
         float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));      // lanes 0..3: a0+a1, lanes 8..11: a2+a3
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(float *__restrict__ 
     }
     __syncthreads();
     const float inv = s_inv;
-    for (uint32_t c = warp; c < nc; c += 8) {
+    for (uint32_t c = warp; c < nc; c += nwarp) {
         float2 v = reinterpret_cast<const float2 *>(s_x + (size_t)c * 64)[lane];
         const float2 ww = reinterpret_cast<const float2 *>(w + (size_t)c * 64)[lane];
         v.x = __fmul_rn(__fmul_rn(v.x, inv), ww.x);
@@ -312,20 +315,38 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// split-KV decode attention over the int8 Hadamard cache (causal_gqa_group_q8, 8471-8594)
+// split-KV decode attention over the Hadamard cache (causal_gqa_group_q8, 8471-8594; NF4: causal_gqa_group_q4_or_window)
 // ------------------------------------------------------------------------------------------------
-// One warp per (kv head, split).  Scores: lane = position (K row of hd bytes, dp4a against the
-// group's int8 queries); values: lane = four dimensions (two half-warps take alternate positions).
-// Used for contexts longer than ATTN_EXACT_CTX positions.  Scores (and so the maximum) are the CPU's bit
-// for bit.  Softmax is the online form; partial (max, sum, out) per split are merged by attn_finish_kernel.  Sums run in a different order than the CPU's
-// position-ascending chains: the output agrees to fp32 rounding, not bit for bit.
+// One warp per (kv head, split).  The warp streams its positions through a ring of 32-position tiles in shared
+// memory: lane 0 issues four bulk copies per tile (key rows, value rows and their scales are contiguous runs of the
+// cache) that complete on the tile's mbarrier, several tiles ahead of the arithmetic, so the kernel is bound by the
+// copy engine's bandwidth and not by one load latency per position.  A ragged last tile, or scale rows that do not
+// start on 16 bytes, are copied by the lanes with plain loads instead.
+// Scores: lane = position (its key row against the group's int8 queries with dp4a; the 16-byte vectors of a row are
+// visited in a lane-dependent rotation so that a quarter-warp reads eight different bank groups - integer sums do
+// not depend on the order); values: lane = four dimensions, the two half-warps take alternate positions.
+// Used for contexts longer than ATTN_EXACT_CTX positions.  Scores (and so the maximum) are the CPU's bit for bit.
+// Softmax is the online form; partial (max, sum, out) per split are merged by attn_finish_kernel.  Sums run in a
+// different order than the CPU's position-ascending chains: the output agrees to fp32 rounding, not bit for bit.
+template <int HD, bool KV4>
+struct SplitTile {
+    static constexpr uint32_t ROW = KV4 ? HD / 2 : HD;             // bytes of a cached key / value row
+    static constexpr uint32_t SC = KV4 ? (HD / 64) * 2 : 4;        // scale bytes per position (bf16 per 64 values / fp32)
+    static constexpr uint32_t K_OFF = 0, V_OFF = 32 * ROW, KS_OFF = 64 * ROW, VS_OFF = 64 * ROW + 32 * SC;
+    static constexpr uint32_t BYTES = 64 * ROW + 64 * SC;
+    static constexpr uint32_t NST = BYTES > 8000 ? 3 : 4;          // tiles in flight per warp
+    static constexpr uint32_t WARP_BYTES = 64 + NST * BYTES;       // mbarriers first
+};
+template <int HD, bool KV4> constexpr size_t attn_partial_smem() { return 4 * SplitTile<HD, KV4>::WARP_BYTES; }
 
 template <int HD, bool KV4>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
+    using Tile = SplitTile<HD, KV4>;
     constexpr int QW = HD / 4;            // int32 words per query row
     constexpr int NB = HD / 64;
-    constexpr int ROW = KV4 ? HD / 2 : HD;            // bytes of a cached key / value row
-    __shared__ int s_q[4][8][QW];         // [warp][query in group][words] (NF4 cache: gathered in the packed column order)
+    constexpr uint32_t ROW = Tile::ROW, SC = Tile::SC, NST = Tile::NST, NV = ROW / 16;
+    extern __shared__ __align__(128) uint8_t dyn_smem[];
+    __shared__ __align__(16) int s_q[4][8][QW];       // [warp][query in group][words] (NF4 cache: gathered in the packed column order)
     __shared__ float s_p[4][8][KV4 ? NB : 1][32];     // value weights of the current 32 positions (per 64-value group for NF4)
     __shared__ float s_cb[16];            // NF4 centroids
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -337,10 +358,47 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
     if (ctx <= ATTN_EXACT_CTX) return;     // short contexts are computed in the CPU's order by attn_finish_kernel
     const uint32_t per = split_span(ctx, a.n_split);
     const uint32_t t_lo = min(ctx, split * per), t_hi = min(ctx, t_lo + per);
+    const uint32_t n_tiles = (t_hi - t_lo + 31) / 32;
     const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
     const uint8_t *K = reinterpret_cast<const uint8_t *>(a.k_q8) + slot0 * ROW, *V = reinterpret_cast<const uint8_t *>(a.v_q8) + slot0 * ROW;
-    const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
-    const uint16_t *ks16 = reinterpret_cast<const uint16_t *>(a.k_scale) + slot0 * NB, *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
+    const uint8_t *KS = reinterpret_cast<const uint8_t *>(a.k_scale) + slot0 * SC, *VS = reinterpret_cast<const uint8_t *>(a.v_scale) + slot0 * SC;
+    uint8_t *wsm = dyn_smem + (size_t)warp * Tile::WARP_BYTES;
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(wsm);
+    uint8_t *stages = wsm + 64;
+    if (lane == 0) {
+        for (uint32_t st = 0; st < NST; ++st) mbar_init(bar0 + 8 * st, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    // bulk copies want 16-byte aligned sources: rows always are, the scale runs only for some cache lengths
+    const bool sc_aligned = ((reinterpret_cast<uintptr_t>(KS + (size_t)t_lo * SC) | reinterpret_cast<uintptr_t>(VS + (size_t)t_lo * SC)) & 15u) == 0;
+    auto tile_is_bulk = [&](uint32_t i) { return sc_aligned && t_lo + 32 * i + 32 <= t_hi; };
+    auto fill = [&](uint32_t i) {         // tile i of the split into stage i % NST (every earlier read of that stage is done)
+        const uint32_t t0 = t_lo + 32 * i, n = min(32u, t_hi - t0);
+        uint8_t *st = stages + (i % NST) * Tile::BYTES;
+        if (tile_is_bulk(i)) {
+            if (lane == 0) {
+                const uint32_t bar = bar0 + 8 * (i % NST), dst = (uint32_t)__cvta_generic_to_shared(st);
+                fence_proxy_async();
+                mbar_expect_tx(bar, Tile::BYTES);
+                bulk_g2s(dst + Tile::K_OFF, K + (size_t)t0 * ROW, 32 * ROW, bar);
+                bulk_g2s(dst + Tile::V_OFF, V + (size_t)t0 * ROW, 32 * ROW, bar);
+                bulk_g2s(dst + Tile::KS_OFF, KS + (size_t)t0 * SC, 32 * SC, bar);
+                bulk_g2s(dst + Tile::VS_OFF, VS + (size_t)t0 * SC, 32 * SC, bar);
+            }
+        } else {
+            for (uint32_t v = lane; v < n * NV; v += 32) {
+                reinterpret_cast<uint4 *>(st + Tile::K_OFF)[v] = __ldcg(reinterpret_cast<const uint4 *>(K + (size_t)t0 * ROW) + v);
+                reinterpret_cast<uint4 *>(st + Tile::V_OFF)[v] = __ldcg(reinterpret_cast<const uint4 *>(V + (size_t)t0 * ROW) + v);
+            }
+            for (uint32_t v = lane; v < n * (SC / 2); v += 32) {
+                reinterpret_cast<uint16_t *>(st + Tile::KS_OFF)[v] = __ldcg(reinterpret_cast<const uint16_t *>(KS + (size_t)t0 * SC) + v);
+                reinterpret_cast<uint16_t *>(st + Tile::VS_OFF)[v] = __ldcg(reinterpret_cast<const uint16_t *>(VS + (size_t)t0 * SC) + v);
+            }
+        }
+    };
+    for (uint32_t i = 0; i < NST && i < n_tiles; ++i) fill(i);
+
     if (KV4 && lane < 16) s_cb[lane] = NF4_KV_CENTROIDS[lane];      // every warp writes the same values
     for (uint32_t i = lane; i < G * QW; i += 32) {
         const int8_t *qb = a.q_i8 + (size_t)(kvh * G + i / QW) * HD;
@@ -355,7 +413,7 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         }
     }
     __syncwarp();
-    float qas[8], m[8], l[8], o[8][HD / 16];   // lane owns dims d0..d0+3 of (HD/16 ... ) see below
+    float qas[8], m[8], l[8], o[8][HD / 16];
     // value phase mapping: 16 lanes x 4 dims cover 64 dims; for HD = 128 each lane owns two such groups
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
@@ -365,30 +423,84 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         for (int d = 0; d < HD / 16; ++d) o[g][d] = 0.0f;
     }
     const uint32_t hw = lane >> 4, dl = lane & 15;   // half-warp, dim group
-    for (uint32_t t0 = t_lo; t0 < t_hi; t0 += 32) {
+    const uint32_t rot = (lane * NV / 8) % NV;       // vector rotation of this lane's key row
+    uint32_t phase = 0;                              // parity bit per stage
+    bool failed = false;
+    for (uint32_t i = 0; i < n_tiles && !failed; ++i) {
+        const uint32_t t0 = t_lo + 32 * i, stage = i % NST;
+        const uint8_t *st = stages + stage * Tile::BYTES;
+        if (tile_is_bulk(i)) {             // bounded wait for the tile
+            uint32_t ok = 0;
+            for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) ok = mbar_try_wait(bar0 + 8 * stage, (phase >> stage) & 1u);
+            phase ^= 1u << stage;
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
+                failed = true;
+                break;
+            }
+        } else {
+            __syncwarp();                  // the lanes' own stores
+        }
         const uint32_t t = t0 + lane;
         const bool on = t < t_hi;
-        // scores of position t for every query of the group
-        int kw[ROW / 4];
-        if (on) {
-#pragma unroll
-            for (int i = 0; i < ROW / 16; ++i) {
-                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * ROW) + i);
-                kw[4 * i] = v.x; kw[4 * i + 1] = v.y; kw[4 * i + 2] = v.z; kw[4 * i + 3] = v.w;
-            }
-        }
         const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
         const bool grouped = t - tile0 < (tile_n & ~7u);
         float kst[KV4 ? NB : 1], vst[KV4 ? NB : 1];
         if (KV4) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
-                kst[b] = on ? bf16_bits_to_f32(__ldcg(ks16 + (size_t)t * NB + b)) : 0.0f;
-                vst[b] = on ? bf16_bits_to_f32(__ldcg(vs16 + (size_t)t * NB + b)) : 0.0f;
+                kst[b] = on ? bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(st + Tile::KS_OFF)[lane * NB + b]) : 0.0f;
+                vst[b] = on ? bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(st + Tile::VS_OFF)[lane * NB + b]) : 0.0f;
             }
         } else {
-            kst[0] = on ? __ldcg(ks + t) : 0.0f;
-            vst[0] = on ? __ldcg(vs + t) : 0.0f;
+            kst[0] = on ? reinterpret_cast<const float *>(st + Tile::KS_OFF)[lane] : 0.0f;
+            vst[0] = on ? reinterpret_cast<const float *>(st + Tile::VS_OFF)[lane] : 0.0f;
+        }
+        // integer dots of position t with every query of the group
+        int up[8][KV4 ? NB : 1], dn[8][KV4 ? NB : 1];
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+#pragma unroll
+            for (int b = 0; b < (KV4 ? NB : 1); ++b) { up[g][b] = 0; dn[g][b] = 0; }
+        const uint4 *krow = reinterpret_cast<const uint4 *>(st + Tile::K_OFF + lane * ROW);
+#pragma unroll
+        for (uint32_t v = 0; v < NV; ++v) {
+            const uint32_t vv = (v + rot) & (NV - 1);
+            const uint4 kk = krow[vv];
+            if (KV4) {
+                const bool second = NB == 2 && vv >= NV / 2;      // the 64-value group this vector belongs to
+                const uint32_t x[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if (g >= (int)G) break;
+                    const int4 qa = *reinterpret_cast<const int4 *>(&s_q[warp][g][8 * vv]), qb = *reinterpret_cast<const int4 *>(&s_q[warp][g][8 * vv + 4]);
+                    const int q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                    int tu = 0, td = 0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t y = x[c] ^ 0x88888888u;
+                        tu = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y), q[2 * c], tu);
+                        td = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x[c]), q[2 * c], td);
+                        tu = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y >> 16), q[2 * c + 1], tu);
+                        td = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x[c] >> 16), q[2 * c + 1], td);
+                    }
+                    if (NB == 2) {
+                        up[g][0] += second ? 0 : tu; dn[g][0] += second ? 0 : td;
+                        up[g][NB - 1] += second ? tu : 0; dn[g][NB - 1] += second ? td : 0;
+                    } else {
+                        up[g][0] += tu; dn[g][0] += td;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if (g >= (int)G) break;
+                    const int4 qq = *reinterpret_cast<const int4 *>(&s_q[warp][g][4 * vv]);
+                    int d = up[g][0];
+                    d = __dp4a((int)kk.x, qq.x, d); d = __dp4a((int)kk.y, qq.y, d); d = __dp4a((int)kk.z, qq.z, d); d = __dp4a((int)kk.w, qq.w, d);
+                    up[g][0] = d;
+                }
+            }
         }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -398,27 +510,11 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
                 if (on) {
                     s = 0.0f;
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        int up = 0, dn = 0;
-#pragma unroll
-                        for (int w = 0; w < 8; ++w) {
-                            const uint32_t x = (uint32_t)kw[b * 8 + w], y = x ^ 0x88888888u;
-                            const int q0 = s_q[warp][g][b * 16 + 2 * w], q1 = s_q[warp][g][b * 16 + 2 * w + 1];
-                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y), q0, up);
-                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x), q0, dn);
-                            up = dp4a_us(prmt(NF4_KV_HI0, NF4_KV_HI1, y >> 16), q1, up);
-                            dn = dp4a_us(prmt(NF4_KV_LO0, NF4_KV_LO1, x >> 16), q1, dn);
-                        }
-                        s = __fadd_rn(s, __fmul_rn(__fmul_rn((float)(up - dn), kst[b]), qas[g]));
-                    }
+                    for (int b = 0; b < NB; ++b) s = __fadd_rn(s, __fmul_rn(__fmul_rn((float)(up[g][b] - dn[g][b]), kst[b]), qas[g]));
                 }
             } else {
-                int dot = 0;
-                if (on) {
-#pragma unroll
-                    for (int i = 0; i < QW; ++i) dot = __dp4a(kw[i], s_q[warp][g][i], dot);
-                }
                 // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
+                const int dot = up[g][0];
                 s = !on ? -INFINITY
                   : grouped ? __fmul_rn((float)dot, __fmul_rn(kst[0], qas[g]))
                             : __fmul_rn(__fmul_rn((float)dot, kst[0]), qas[g]);
@@ -436,16 +532,17 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         __syncwarp();
         // values: half-warp hw takes positions t0 + hw, t0 + hw + 2, ...
         const uint32_t n_here = min(32u, t_hi - t0);
+        const uint8_t *vt = st + Tile::V_OFF;
         for (uint32_t j = hw; j < n_here; j += 2) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 float c0, c1, c2, c3;
                 if (KV4) {    // dims 4 dl .. 4 dl + 3 of the group sit in one packed word: low nibbles for columns 0..15 of a half, high for 16..31
                     const uint32_t e = dl * 4, r = e % 32, shift = r < 16 ? 0u : 4u;
-                    const uint32_t word = __ldcg(reinterpret_cast<const uint32_t *>(V + (size_t)(t0 + j) * ROW + b * 32 + (e / 32) * 16 + (r % 16))) >> shift;
+                    const uint32_t word = *reinterpret_cast<const uint32_t *>(vt + j * ROW + b * 32 + (e / 32) * 16 + (r % 16)) >> shift;
                     c0 = s_cb[word & 15u]; c1 = s_cb[(word >> 8) & 15u]; c2 = s_cb[(word >> 16) & 15u]; c3 = s_cb[(word >> 24) & 15u];
                 } else {
-                    const char4 v = __ldcg(reinterpret_cast<const char4 *>(V + (size_t)(t0 + j) * ROW + b * 64 + dl * 4));
+                    const char4 v = *reinterpret_cast<const char4 *>(vt + j * ROW + b * 64 + dl * 4);
                     c0 = (float)v.x; c1 = (float)v.y; c2 = (float)v.z; c3 = (float)v.w;
                 }
 #pragma unroll
@@ -459,8 +556,10 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
                 }
             }
         }
-        __syncwarp();
+        __syncwarp();                      // the stage and the weights are free again
+        if (i + NST < n_tiles) fill(i + NST);
     }
+    if (failed) return;
     // combine the two half-warps and write the partial result
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
@@ -485,117 +584,51 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
 //   longer contexts: merges the split partials (sums in split order; fp32-rounding agreement).
 // Then: inverse rotation (block index 0/1), forward rotation with the global chunk index
 // qh*(hd/64)+b and quantization for o_proj (7059-7084).
+constexpr uint32_t FINISH_THREADS = 256;     // also the largest split count the merge handles
 template <int HD>
-__global__ void __launch_bounds__(HD) attn_finish_kernel(const AttnArgs a) {
-    constexpr int QW = HD / 4, NB = HD / 64, VT = 64;      // VT positions per staged value tile
-    __shared__ float s_sc[ATTN_EXACT_CTX];
-    __shared__ __align__(16) int8_t s_v[VT * HD];
-    __shared__ float s_o[HD];
-    __shared__ float s_red[HD / 32];
-    __shared__ float s_inv;
+__global__ void __launch_bounds__(FINISH_THREADS) attn_finish_kernel(const AttnArgs a) {
+    constexpr int NB = HD / 64, NG = FINISH_THREADS / HD;      // NG thread groups share the splits of a dimension
+    __shared__ float s_w[FINISH_THREADS];
+    __shared__ float s_part[NG][HD];
+    __shared__ float s_red[FINISH_THREADS / 32], s_redl[FINISH_THREADS / 32];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_wait();
     pdl_trigger();
-    const uint32_t qh = blockIdx.x, kvh = qh / a.group, ctx = __ldcg(a.pos) + a.pos_offset + 1;
+    const uint32_t qh = blockIdx.x, ctx = __ldcg(a.pos) + a.pos_offset + 1;
+    if (ctx <= ATTN_EXACT_CTX) return;         // those lengths belong to attn_fused_kernel
+    const uint32_t per = split_span(ctx, a.n_split);
+    const uint32_t used = (ctx + per - 1) / per;               // splits that hold positions (at most FINISH_THREADS)
+    // thread s: weight of split s against the global maximum, and its share of the softmax denominator
+    const float ms = tid < used ? __ldcg(a.part_m + (size_t)qh * a.n_split + tid) : -INFINITY;
+    const float ls = tid < used ? __ldcg(a.part_l + (size_t)qh * a.n_split + tid) : 0.0f;
+    float M = warp_max(ms);
+    if (lane == 0) s_red[warp] = M;
+    __syncthreads();
+#pragma unroll
+    for (uint32_t i = 0; i < FINISH_THREADS / 32; ++i) M = fmaxf(M, s_red[i]);
+    const float wgt = tid < used ? exp_poly(ms - M) : 0.0f;
+    s_w[tid] = wgt;
+    const float lw = warp_sum(__fmul_rn(ls, wgt));
+    if (lane == 0) s_redl[warp] = lw;
+    __syncthreads();
+    float L = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < FINISH_THREADS / 32; ++i) L = __fadd_rn(L, s_redl[i]);
+    // group g of dimension d sums splits g, g + NG, ... (independent loads, one fma chain); the groups are added in order
+    const uint32_t d = tid % HD, grp = tid / HD;
     float o = 0.0f;
-    if (ctx <= ATTN_EXACT_CTX && a.kv_bits == 4) return;      // the NF4 cache at these lengths belongs to attn_fused_kernel
-    if (ctx <= ATTN_EXACT_CTX) {
-        const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
-        const int8_t *K = a.k_q8 + slot0 * HD, *V = a.v_q8 + slot0 * HD;
-        const float *ks = a.k_scale + slot0, *vs = a.v_scale + slot0;
-        const float qas = __fmul_rn(__ldcg(a.q_scale + qh), a.attn_scale);
-        int qw[QW];
-#pragma unroll
-        for (int i = 0; i < QW / 4; ++i) {
-            const int4 v = __ldcg(reinterpret_cast<const int4 *>(a.q_i8 + (size_t)qh * HD) + i);
-            qw[4 * i] = v.x; qw[4 * i + 1] = v.y; qw[4 * i + 2] = v.z; qw[4 * i + 3] = v.w;
-        }
-        float mx = -INFINITY;
-        for (uint32_t t = tid; t < ctx; t += HD) {
-            int dot = 0;
-#pragma unroll
-            for (int i = 0; i < QW / 4; ++i) {
-                const int4 v = __ldcg(reinterpret_cast<const int4 *>(K + (size_t)t * HD) + i);
-                dot = __dp4a(v.x, qw[4 * i], dot); dot = __dp4a(v.y, qw[4 * i + 1], dot);
-                dot = __dp4a(v.z, qw[4 * i + 2], dot); dot = __dp4a(v.w, qw[4 * i + 3], dot);
-            }
-            // 256-position tiles: whole groups of 8 use dot*(ks*qas), the tile remainder (dot*ks)*qas (8992-9057)
-            const uint32_t tile0 = t & ~255u, tile_n = min(ctx, tile0 + 256u) - tile0;
-            const float kst = __ldcg(ks + t);
-            const float sc = (t - tile0 < (tile_n & ~7u)) ? __fmul_rn((float)dot, __fmul_rn(kst, qas))
-                                                           : __fmul_rn(__fmul_rn((float)dot, kst), qas);
-            s_sc[t] = sc;
-            mx = fmaxf(mx, sc);
-        }
-        mx = warp_max(mx);
-        if (lane == 0) s_red[warp] = mx;
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < HD / 32; ++i) mx = fmaxf(mx, s_red[i]);
-        // softmax_unnorm (9603-9632): polynomial exp for whole groups of 4 positions, libm exp for the rest
-        const uint32_t n4 = ctx & ~3u;
-        for (uint32_t t = tid; t < ctx; t += HD) {
-            const float x = __fsub_rn(s_sc[t], mx);
-            s_sc[t] = t < n4 ? exp_poly(x) : (float)exp((double)x);
-        }
-        __syncthreads();
-        if (warp == 0) {
-            float acc = 0.0f;
-            if (lane < 4)
-                for (uint32_t t = lane; t < n4; t += 4) acc = __fadd_rn(acc, s_sc[t]);
-            acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0+a1, lane 2: a2+a3
-            acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
-            if (lane == 0) {
-                for (uint32_t t = n4; t < ctx; ++t) acc = __fadd_rn(acc, s_sc[t]);
-                s_inv = __fdiv_rn(1.0f, acc);
-            }
-        }
-        __syncthreads();
-        const float inv = s_inv;
-        for (uint32_t t = tid; t < ctx; t += HD) s_sc[t] = __fmul_rn(__fmul_rn(s_sc[t], inv), __ldcg(vs + t));
-        // values: tiles of VT positions staged in shared memory (next tile prefetched into registers)
-        constexpr int LD = VT / 16;            // int4 loads per thread and tile: VT*HD/16 over HD threads
-        int4 nxt[LD];
-        auto fetch = [&](uint32_t t0) {
-#pragma unroll
-            for (int j = 0; j < LD; ++j) {
-                const uint32_t e = (uint32_t)j * HD + tid;             // int4 index within the tile
-                const uint32_t t = t0 + e / (HD / 16);
-                nxt[j] = t < ctx ? __ldcg(reinterpret_cast<const int4 *>(V + (size_t)t0 * HD) + e) : make_int4(0, 0, 0, 0);
-            }
-        };
-        fetch(0);
-        for (uint32_t t0 = 0; t0 < ctx; t0 += VT) {
-            __syncthreads();                   // weights written / previous tile consumed
-#pragma unroll
-            for (int j = 0; j < LD; ++j) reinterpret_cast<int4 *>(s_v)[(uint32_t)j * HD + tid] = nxt[j];
-            __syncthreads();
-            if (t0 + VT < ctx) fetch(t0 + VT);
-            const uint32_t n_here = min((uint32_t)VT, ctx - t0);
-#pragma unroll 8
-            for (uint32_t j = 0; j < n_here; ++j) {
-                const float w = s_sc[t0 + j];
-                if (w != 0.0f) o = __fmaf_rn((float)s_v[j * HD + tid], w, o);
-            }
-        }
-    } else {
-        const uint32_t per = split_span(ctx, a.n_split);
-        const uint32_t used = (ctx + per - 1) / per;           // splits that hold positions
-        const float *pm = a.part_m + (size_t)qh * a.n_split, *pl = a.part_l + (size_t)qh * a.n_split;
-        float M = -INFINITY, L = 0.0f;
-        for (uint32_t s = 0; s < used; ++s) M = fmaxf(M, __ldcg(pm + s));
-        for (uint32_t s = 0; s < used; ++s) {
-            const float wgt = exp_poly(__ldcg(pm + s) - M);
-            L = __fmaf_rn(__ldcg(pl + s), wgt, L);
-            o = __fmaf_rn(__ldcg(a.part_o + ((size_t)qh * a.n_split + s) * HD + tid), wgt, o);
-        }
-        o = __fmul_rn(o, __fdiv_rn(1.0f, L));
-    }
-    s_o[tid] = o;
+    const float *po = a.part_o + (size_t)qh * a.n_split * HD + d;
+#pragma unroll 16
+    for (uint32_t sp = grp; sp < used; sp += NG) o = __fmaf_rn(__ldcg(po + (size_t)sp * HD), s_w[sp], o);
+    s_part[grp][d] = o;
     __syncthreads();
     if (warp < NB) {
         const uint32_t b = warp;
-        float x0 = s_o[b * 64 + 2 * lane], x1 = s_o[b * 64 + 2 * lane + 1];
+        const float invL = __fdiv_rn(1.0f, L);
+        float x0 = 0.0f, x1 = 0.0f;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) { x0 = __fadd_rn(x0, s_part[g][b * 64 + 2 * lane]); x1 = __fadd_rn(x1, s_part[g][b * 64 + 2 * lane + 1]); }
+        x0 = __fmul_rn(x0, invL); x1 = __fmul_rn(x1, invL);
         warp_ifwht64(x0, x1, b, lane);
         if (a.attn_out != nullptr) reinterpret_cast<float2 *>(a.attn_out + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
         const uint32_t c = qh * NB + b;
@@ -732,23 +765,33 @@ cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *d
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(256), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm);
+    // one warp per 64-value chunk where that fits: the load and the rotation each take one round
+    const uint32_t threads = std::min(1024u, std::max(256u, (n / 64) * 32u));
+    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm);
 }
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;
     return launch_kernel(qkv_post_kernel, dim3((heads + 3) / 4), dim3(128), 0, s, pdl, a);
 }
+template <int HD, bool KV4>
+static cudaError_t launch_partial(cudaStream_t s, dim3 grid, bool pdl, const AttnArgs &a) {
+    constexpr size_t smem = attn_partial_smem<HD, KV4>();
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, KV4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_kernel(attn_partial_kernel<HD, KV4>, grid, dim3(128), smem, s, pdl, a);
+}
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
     dim3 grid((a.n_split + 3) / 4, a.n_kv);
     cudaError_t e;
-    if (a.head_dim == 64) e = a.kv_bits == 4 ? launch_kernel(attn_partial_kernel<64, true>, grid, dim3(128), 0, s, pdl, a)
-                                             : launch_kernel(attn_partial_kernel<64, false>, grid, dim3(128), 0, s, pdl, a);
-    else if (a.head_dim == 128) e = a.kv_bits == 4 ? launch_kernel(attn_partial_kernel<128, true>, grid, dim3(128), 0, s, pdl, a)
-                                                   : launch_kernel(attn_partial_kernel<128, false>, grid, dim3(128), 0, s, pdl, a);
+    if (a.head_dim == 64) e = a.kv_bits == 4 ? launch_partial<64, true>(s, grid, pdl, a) : launch_partial<64, false>(s, grid, pdl, a);
+    else if (a.head_dim == 128) e = a.kv_bits == 4 ? launch_partial<128, true>(s, grid, pdl, a) : launch_partial<128, false>(s, grid, pdl, a);
     else return cudaErrorInvalidValue;
     if (e != cudaSuccess) return e;
-    if (a.head_dim == 64) return launch_kernel(attn_finish_kernel<64>, dim3(a.n_kv * a.group), dim3(64), 0, s, pdl, a);
-    return launch_kernel(attn_finish_kernel<128>, dim3(a.n_kv * a.group), dim3(128), 0, s, pdl, a);
+    if (a.n_split > FINISH_THREADS) return cudaErrorInvalidValue;
+    if (a.head_dim == 64) return launch_kernel(attn_finish_kernel<64>, dim3(a.n_kv * a.group), dim3(FINISH_THREADS), 0, s, pdl, a);
+    return launch_kernel(attn_finish_kernel<128>, dim3(a.n_kv * a.group), dim3(FINISH_THREADS), 0, s, pdl, a);
 }
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl) {
     const size_t smem = attn_smem_bytes();

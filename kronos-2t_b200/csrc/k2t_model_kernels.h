@@ -49,6 +49,7 @@ struct AttnArgs {
     uint32_t n_kv, group, head_dim, max_seq, layer, n_split;
     uint32_t kv_bits;            // 8 or 4 (see QkvPostArgs)
     float attn_scale;
+    uint32_t *err_flag;          // set to 1 when a bounded wait for a staged tile gives up
 };
 
 struct FusedAttnArgs {           // one layer's attention from the fused qkv vector to the o_proj activation

@@ -80,16 +80,54 @@ def rope_table(max_seq, head_dim, theta):
 SMOLLM2_135M = dict(hidden=576, layers=30, n_q=9, n_kv=3, head_dim=64, inter=1536, vocab=49152, max_seq=512, eps=1e-5, theta=1e5)
 
 
-def random_model(cfg, mode, seed=0):
-    """Engine spec of a dense Llama-shaped model with random codes (decode time does not depend on the values)."""
+SMOLLM2_1_7B = dict(hidden=2048, layers=24, n_q=32, n_kv=32, head_dim=64, inter=8192, vocab=49152, max_seq=8192 + 64, eps=1e-5, theta=1.3e5)
+QWEN2_7B = dict(hidden=3584, layers=28, n_q=28, n_kv=4, head_dim=128, inter=18944, vocab=152064, max_seq=4096 + 64, eps=1e-6, theta=1e6)
+P55454 = dict(qkv="b5", o="b5", gate_up="b4", down="b5", head="b4")     # the reference's mixed-plane tier pQOGDH
+
+
+def random_bf16(seed, n, lo=0x3800, hi=0x3C00):
+    """n bf16 values of random sign with magnitudes in [2^-15, 2^-7)."""
+    rng = _rng(seed)
+    return (rng.integers(lo, hi, n, dtype=np.uint16) | (rng.integers(0, 2, n, dtype=np.uint16) << 15)).astype(np.uint16)
+
+
+def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp=(1, 0), share_layers=False):
+    """Engine spec of a dense Llama-shaped model with random codes (decode time does not depend on the values).
+
+    modes: per-matrix formats {qkv, o, gate_up, down, head} overriding `mode`.  tp = (size, rank): the rank-local
+    spec of a tensor-parallel group, generated directly in the rank's shapes (what kronos_2t_b200.tp.shard_spec cuts
+    out of a whole model); tensor-parallel specs use an untied embedding table.  share_layers: every layer points at
+    layer 0's host arrays (each still becomes its own device copy), which keeps multi-billion-parameter specs quick to make."""
     c = dict(cfg)
-    h, hd, inter = c["hidden"], c["head_dim"], c["inter"]
+    tp_size, tp_rank = tp
+    md = dict(qkv=mode, o=mode, gate_up=mode, down=mode, head=mode)
+    md.update(modes or {})
+    h, hd = c["hidden"], c["head_dim"]
+    vocab_total = c["vocab"]
+    if tp_size > 1:
+        assert c["n_q"] % tp_size == 0 and c["n_kv"] % tp_size == 0 and c["inter"] % (64 * tp_size) == 0 and c["vocab"] % (32 * tp_size) == 0
+        c.update(n_q=c["n_q"] // tp_size, n_kv=c["n_kv"] // tp_size, inter=c["inter"] // tp_size, vocab=c["vocab"] // tp_size)
+        c.update(tp_size=tp_size, tp_rank=tp_rank, vocab_total=vocab_total, o_chunk0=tp_rank * c["n_q"] * hd // 64,
+                 down_chunk0=tp_rank * c["inter"] // 64)
+        untied = True
+    inter = c["inter"]
     q_dim, kv_dim = c["n_q"] * hd, c["n_kv"] * hd
     layers = []
     for l in range(c["layers"]):
-        s = seed * 100003 + 10 * l
-        layers.append(dict(input_norm=np.ones(h, np.float32), post_norm=np.ones(h, np.float32), qkv_bias=None, q_norm=None, k_norm=None,
-                           qkv=random_matrix(s + 1, q_dim + 2 * kv_dim, h, mode), o=random_matrix(s + 2, h, q_dim, mode),
-                           gate_up=random_matrix(s + 3, 2 * inter, h, mode), down=random_matrix(s + 4, h, inter, mode)))
-    return dict(cfg=c, layers=layers, final_norm=np.ones(h, np.float32), lm_head=random_matrix(seed * 100003 + 7, c["vocab"], h, mode),
-                rope=rope_table(c["max_seq"], hd, c["theta"]), embed_bf16=None)
+        if share_layers and l > 0:
+            layers.append(dict(layers[0]))
+            continue
+        s = seed * 100003 + 10 * l + 1000003 * tp_rank
+        bias = None
+        if qkv_bias:
+            bias = (_rng(s + 5).standard_normal(q_dim + 2 * kv_dim) * 0.02).astype(np.float32)
+        layers.append(dict(input_norm=np.ones(h, np.float32), post_norm=np.ones(h, np.float32), qkv_bias=bias, q_norm=None, k_norm=None,
+                           qkv=random_matrix(s + 1, q_dim + 2 * kv_dim, h, md["qkv"]), o=random_matrix(s + 2, h, q_dim, md["o"]),
+                           gate_up=random_matrix(s + 3, 2 * inter, h, md["gate_up"]), down=random_matrix(s + 4, h, inter, md["down"])))
+    embed = None
+    if untied:       # a 4096-row random block, repeated
+        blk = random_bf16(seed * 100003 + 8, min(vocab_total, 4096) * h)
+        embed = np.tile(blk, -(-vocab_total // 4096))[:vocab_total * h]
+    return dict(cfg=c, layers=layers, final_norm=np.ones(h, np.float32),
+                lm_head=random_matrix(seed * 100003 + 7 + 1000003 * tp_rank, c["vocab"], h, md["head"]),
+                rope=rope_table(c["max_seq"], hd, c["theta"]), embed_bf16=embed)
