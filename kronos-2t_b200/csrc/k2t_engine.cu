@@ -325,10 +325,10 @@ bool setup_mega(KronosCudaEngine *e) {
 void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a) {
     const KronosCudaMatrix *src = e->embed_matrix ? e->embed_matrix : e->lm_head;
     const MatrixGeom &g = src->dm.geom;
-    for (int k = 0; k < 3; ++k) { a.plane[k] = src->dm.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; a.cell[k] = g.cell[k]; }
+    for (int k = 0; k < 3; ++k) { a.plane[k] = src->dm.d_base + g.plane_off[k]; a.cell[k] = g.cell[k]; }
     a.scales = reinterpret_cast<const uint16_t *>(src->dm.d_base + g.scale_off);
     a.embed_bf16 = e->embed_bf16; a.token = e->d_token; a.hidden = e->hidden;
-    a.fmt = g.fmt; a.nc = g.nc; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.max_odd = g.max_odd;
+    a.fmt = g.fmt; a.nc = g.nc; a.rows_pad = g.rows_pad; a.sgc = g.sgc; a.max_odd = g.max_odd;
     a.sgc_shift = 32;
     for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
     for (int i = 0; i < 32; ++i) a.codebook[i] = g.codebook32[i];

@@ -141,15 +141,15 @@ cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int
     }
 }
 
-// Fills the matrix part of GemvArgs (planes, pitches, codebooks) and returns the kernel format index
+// Fills the matrix part of GemvArgs (planes, codebooks) and returns the kernel format index
 // (FMT_NF4G for an NF4 codebook the two-table decode cannot represent), or -1 when unsupported.
 int fill_gemv_args(const DeviceMatrix &m, bool has_xsum, GemvArgs &a) {
     const MatrixGeom &g = m.geom;
-    for (int k = 0; k < 3; ++k) { a.plane[k] = m.d_base + g.plane_off[k]; a.pitch[k] = g.pitch[k]; }
+    for (int k = 0; k < 3; ++k) a.plane[k] = m.d_base + g.plane_off[k];
     a.scales = reinterpret_cast<const uint16_t *>(m.d_base + g.scale_off);
     a.xq = nullptr; a.xs = nullptr; a.xsum = nullptr; a.out = nullptr; a.int_dots = nullptr; a.err_flag = nullptr;
     a.out_stride = g.rows; a.pdl = 0;
-    a.rows = g.rows; a.cols = g.cols; a.nc = g.nc; a.nsg = g.nsg; a.nsg_pad = g.nsg_pad; a.sgc = g.sgc; a.n_tok = 1;
+    a.rows = g.rows; a.rows_pad = g.rows_pad; a.cols = g.cols; a.nc = g.nc; a.nsg = g.nsg; a.sgc = g.sgc; a.n_tok = 1;
     a.sgc_shift = 32;
     for (uint32_t sh = 0; sh < 4; ++sh) if ((1u << sh) == g.sgc) a.sgc_shift = sh;
     a.max_odd = g.max_odd; a.nf4_offset = g.nf4_offset;

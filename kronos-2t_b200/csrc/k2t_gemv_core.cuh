@@ -18,8 +18,8 @@
 //
 // Weight streaming.  Each warp runs its own bulk-copy pipeline: a stage receives the cells of one
 // 4-row block for one pass (16-byte half cells of columns 0..31 and 32..63, the extra-bit plane and
-// the bf16 scales, one `cp.async.bulk` per contiguous run) and signals an mbarrier with the byte
-// count.  NSTAGE stages per warp keep 9..13 KiB per warp in flight without holding a register; the
+// the bf16 scales; the pass-tiled image makes each of them ONE contiguous run, so a stage is three or
+// four `cp.async.bulk` copies) and signals an mbarrier with the byte count.  NSTAGE stages per warp keep 9..13 KiB per warp in flight without holding a register; the
 // stage is refilled right after its four rows have been reduced.  Cells are 16 bytes apart in a
 // stage, so the 128-bit shared-memory reads of a warp are conflict-free.
 //
@@ -33,8 +33,8 @@
 namespace k2t {
 
 struct GemvArgs {
-    const uint8_t *plane[3];  // code planes, [rows][pitch] bytes
-    const uint16_t *scales;   // [rows][nsg_pad] bf16
+    const uint8_t *plane[3];  // code planes in pass tiles (k2t_layout.h)
+    const uint16_t *scales;   // scale plane in pass tiles
     const int8_t *xq;
     const float *xs;
     const int32_t *xsum;
@@ -42,8 +42,7 @@ struct GemvArgs {
     int32_t *int_dots;
     uint32_t *err_flag;       // set to 1 when a bounded mbarrier wait gives up
     size_t out_stride;
-    uint32_t rows, cols, nc, nsg, nsg_pad, sgc, sgc_shift, n_tok;   // sgc_shift: log2(sgc) or 32
-    uint32_t pitch[3];
+    uint32_t rows, rows_pad, cols, nc, nsg, sgc, sgc_shift, n_tok;  // sgc_shift: log2(sgc) or 32
     int32_t max_odd;
     int32_t nf4_offset;
     uint32_t cb[8];    // expanded codebook, 4 centroids per word (NF4: sorted ascending)
@@ -305,8 +304,6 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     const uint32_t np = (a.nc + 31) / 32;
     const uint32_t my_np = wid < np ? (np - wid + WK - 1) / WK : 0; // passes of this warp: wid, wid + WK, ...
     const uint32_t rounds = (np + WK - 1) / WK;
-    const bool merged = np == 1;                               // a block's rows are contiguous in every plane
-
     // warp region: mbarriers (first 128 B, so that the stages keep their 128-byte alignment and a quarter-warp's
     // 128-bit reads stay within one 128-byte line), stages, v tile, w_scale tile
     uint8_t *stages = wsm + 128;
@@ -315,46 +312,27 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(wsm);
     const uint32_t stage_sa = (uint32_t)__cvta_generic_to_shared(stages);
 
-    // ---- producer role of this lane: which run of bytes it copies for every unit.
-    // merged: lane k < NPL copies plane k (or the scales) of the whole block; otherwise lane
-    // rr*NPL + k copies row rr of plane k.  Everything that does not depend on the unit is fixed here.
-    const uint32_t my_k = lane % St::NPL, my_rr = lane / St::NPL;
-    const bool my_scale = my_k == St::NPL - 1;
+    // ---- producer role of this lane: lane k < NPL copies plane k (the last one: the scales) of every unit - the
+    // four rows of a block are one contiguous run in a pass tile.  What does not depend on the unit is fixed here.
+    const uint32_t my_k = lane;
+    const bool my_role = lane < St::NPL, my_scale = my_k == St::NPL - 1;
     const uint32_t my_cell = my_scale ? 0u : (my_k == 0 ? (uint32_t)Cell<FMT>::B0 : my_k == 1 ? (uint32_t)Cell<FMT>::B1 : (uint32_t)Cell<FMT>::B2);
-    const uint32_t my_pitch = my_scale ? a.nsg_pad * 2 : a.pitch[my_scale ? 0 : my_k];
-    const uint8_t *my_base = my_scale ? reinterpret_cast<const uint8_t *>(a.scales) : a.plane[my_scale ? 0 : my_k];
+    const uint8_t *my_base = my_scale ? reinterpret_cast<const uint8_t *>(a.scales) : a.plane[my_role ? my_k : 0];
     const uint32_t my_soff = my_scale ? St::OFFS : (my_k == 0 ? St::OFF0 : my_k == 1 ? St::OFF1 : St::OFF2);
-    const uint32_t my_spitch = my_scale ? (uint32_t)SCALE_PITCH : 32u * my_cell;       // stage pitch when not merged
-    const bool my_role = merged ? my_rr == 0 : my_rr < RS;
-    uint32_t sum_pitch = a.nsg_pad * 2;                         // bytes of one row over all planes (merged case)
-#pragma unroll
-    for (int k = 0; k < 3; ++k) sum_pitch += (k == 0 || (k == 1 && Cell<FMT>::B1) || (k == 2 && Cell<FMT>::B2)) ? a.pitch[k] : 0u;
+    constexpr uint32_t CELL_SUM = Cell<FMT>::B0 + Cell<FMT>::B1 + Cell<FMT>::B2;
 
     // producer cursor: 32-row group, own pass index, block in group
     uint32_t pj0 = 0, ppi = 0, pjj = 0;
     auto issue = [&](uint32_t stage) {
         if (pj0 >= J || my_np == 0) return;                     // nothing left: the stage stays idle
         const uint32_t row0 = (gw + (pj0 + pjj) * nw) * RS;
-        const uint32_t nrows = min((uint32_t)RS, a.rows - row0);
         const uint32_t bar = bar0 + 8 * stage;
-        uint32_t bytes, total, dst = stage_sa + stage * St::BYTES + my_soff;
-        const uint8_t *src;
-        if (merged) {
-            bytes = nrows * my_pitch;
-            total = nrows * sum_pitch;
-            src = my_base + (size_t)row0 * my_pitch;
-        } else {
-            const uint32_t c0 = (wid + ppi * WK) * 32, n = min(32u, a.nc - c0);
-            const uint32_t sga = scale_group_of(a, c0) & ~7u;
-            const uint32_t sbytes = up16((scale_group_of(a, c0 + n - 1) - sga + 1) * 2);
-            bytes = my_scale ? sbytes : up16(n * my_cell);
-            total = nrows * (sbytes + up16(n * Cell<FMT>::B0) + up16(n * Cell<FMT>::B1) + up16(n * Cell<FMT>::B2));
-            src = my_base + (size_t)(row0 + my_rr) * my_pitch + (my_scale ? sga * 2 : c0 * my_cell);
-            dst += my_rr * my_spitch;
-        }
-        if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, total); }
+        const uint32_t p = wid + ppi * WK, n = tile_chunks(a.nc, p), sp = tile_scale_pitch(a.nc, a.sgc, p);
+        const uint32_t pitch = my_scale ? sp : n * my_cell;     // bytes of one row of this lane's plane in tile p
+        const uint8_t *src = my_base + (my_scale ? tile_scale_off(a.rows_pad, p) : tile_code_off(a.rows_pad, my_cell, p)) + (size_t)row0 * pitch;
+        if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, RS * (sp + n * CELL_SUM)); }
         __syncwarp();
-        if (my_role && my_rr < nrows) bulk_g2s(dst, src, bytes, bar);
+        if (my_role) bulk_g2s(stage_sa + stage * St::BYTES + my_soff, src, RS * pitch, bar);
         const uint32_t in_group = min(8u, J - pj0);
         if (++pjj == in_group) { pjj = 0; if (++ppi == my_np) { ppi = 0; pj0 += 8; } }
     };
@@ -396,10 +374,9 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
                     }
                 }
                 // stage geometry of this pass
-                const uint32_t sga = merged ? 0 : (scale_group_of(a, p * 32) & ~7u);
-                const uint32_t p0 = merged ? a.pitch[0] : 32 * Cell<FMT>::B0, p1 = merged ? a.pitch[1] : 32 * Cell<FMT>::B1;
-                const uint32_t p2 = merged ? a.pitch[2] : 32 * Cell<FMT>::B2, ps = merged ? a.nsg_pad * 2 : SCALE_PITCH;
-                const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - sga) * 2;
+                const uint32_t p0 = n * Cell<FMT>::B0, p1 = n * Cell<FMT>::B1, p2 = n * Cell<FMT>::B2;
+                const uint32_t ps = tile_scale_pitch(a.nc, a.sgc, p);
+                const uint32_t ws_off = (scale_group_of(a, act ? c : p * 32) - scale_group_of(a, p * 32)) * 2;
 
                 for (uint32_t jj = 0; jj < in_group; ++jj) {
                     const uint32_t row0 = (gw + (j0 + jj) * nw) * RS;

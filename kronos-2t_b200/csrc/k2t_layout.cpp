@@ -158,16 +158,15 @@ bool matrix_geometry(const KronosCudaMatrixDesc &d, MatrixGeom &g, std::string &
         err = "matrix: unsupported kind (only bipolar=0 and NF=2)";
         return false;
     }
-    auto up16 = [](size_t x) { return (x + 15) & ~(size_t)15; };
+    g.rows_pad = (g.rows + 3u) & ~3u;
+    g.np = (g.nc + 31u) / 32u;
     size_t off = 0;
     for (int k = 0; k < 3; ++k) {
-        g.pitch[k] = (uint32_t)up16((size_t)g.nc * g.cell[k]);
         g.plane_off[k] = off;
-        off += (size_t)g.rows * g.pitch[k];
+        off += (size_t)g.rows_pad * g.nc * g.cell[k];      // a multiple of 16: rows_pad is a multiple of 4, cells are 8 or 16 bytes
     }
-    g.nsg_pad = (g.nsg + 7) & ~7u;
     g.scale_off = off;
-    off += (size_t)g.rows * g.nsg_pad * 2;
+    off += (size_t)g.np * g.rows_pad * 64;
     g.image_total = off + 16;
     return true;
 }
@@ -183,20 +182,16 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
         uint32_t blk = r / 128, w = r % 128;
         return w < 64 ? blk * 64 + w : inter + blk * 64 + (w - 64);
     };
-    uint8_t *scales = out + g.scale_off;
 
     auto do_rows = [&](uint32_t r_lo, uint32_t r_hi) {
         for (uint32_t r_dst = r_lo; r_dst < r_hi; ++r_dst) {
             const uint32_t r = src_row(r_dst), lane = r % STRIPE;
-            uint8_t *row_k[3];
-            for (int k = 0; k < 3; ++k) row_k[k] = out + g.plane_off[k] + (size_t)r_dst * g.pitch[k];
-            uint8_t *row_s = scales + (size_t)r_dst * g.nsg_pad * 2;
             for (uint32_t c = 0; c < g.nc; ++c) {
-                uint8_t *c0 = row_k[0] + (size_t)c * g.cell[0];
-                uint8_t *c1 = row_k[1] + (size_t)c * g.cell[1];
-                uint8_t *c2 = row_k[2] + (size_t)c * g.cell[2];
+                uint8_t *c0 = out + g.cell_off(0, r_dst, c);
+                uint8_t *c1 = out + g.cell_off(1, r_dst, c);
+                uint8_t *c2 = out + g.cell_off(2, r_dst, c);
                 if (d.kind == KRONOS_CUDA_MATRIX_BIPOLAR) {
-                    put_u16(row_s + (size_t)c * 2, fv.bp_scale(r, c));
+                    put_u16(out + g.scale_off_of(r_dst, c), fv.bp_scale(r, c));
                     for (uint32_t col = 0; col < 64; ++col) {
                         uint32_t u = fv.bp_code(r, c * 64 + col);
                         uint32_t k = col % 8, cc = col % 32;
@@ -214,7 +209,7 @@ void repack_matrix(const KronosCudaMatrixDesc &d, const MatrixGeom &g, bool inte
                 }
                 const uint8_t *blk, *sc;
                 fv.nf_ptrs(r / STRIPE, c, blk, sc);
-                if (c % g.sgc == 0) put_u16(row_s + (size_t)(c / g.sgc) * 2, fv.nf_scale(r, c));
+                put_u16(out + g.scale_off_of(r_dst, c), fv.nf_scale(r, c));     // every chunk of a group writes the group's scale (a group may sit in two tiles)
                 if (d.bits == 2) {
                     for (uint32_t eb8 = 0; eb8 < 8; ++eb8) {
                         uint8_t tpl, sgn;

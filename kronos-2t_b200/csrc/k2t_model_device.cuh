@@ -38,12 +38,15 @@ __device__ __forceinline__ float warp_max(float v) {
 // ------------------------------------------------------------------------------------------------
 // weight value (rotated domain) of element `col` (0..63) of cell (row, c)
 __device__ __forceinline__ float cell_value(const EmbedArgs &a, uint32_t row, uint32_t c, uint32_t col) {
-    const size_t cell = c;
-    const uint8_t *p0 = a.plane[0] + (size_t)row * a.pitch[0] + cell * a.cell[0];
-    const uint8_t *p1 = a.plane[1] + (size_t)row * a.pitch[1] + cell * a.cell[1];
-    const uint8_t *p2 = a.plane[2] + (size_t)row * a.pitch[2] + cell * a.cell[2];
-    const uint32_t sg = a.sgc_shift < 32 ? c >> a.sgc_shift : c / a.sgc;
-    const float delta = bf16_bits_to_f32(a.scales[(size_t)row * a.nsg_pad + sg]);
+    // pass-tile addressing (k2t_layout.h): tile p = c / 32 holds n cells per row
+    const uint32_t p = c / 32, n = tile_chunks(a.nc, p);
+    const size_t cell = (size_t)row * n + c % 32;
+    const uint8_t *p0 = a.plane[0] + tile_code_off(a.rows_pad, a.cell[0], p) + cell * a.cell[0];
+    const uint8_t *p1 = a.plane[1] + tile_code_off(a.rows_pad, a.cell[1], p) + cell * a.cell[1];
+    const uint8_t *p2 = a.plane[2] + tile_code_off(a.rows_pad, a.cell[2], p) + cell * a.cell[2];
+    const uint8_t *sp = reinterpret_cast<const uint8_t *>(a.scales) + tile_scale_off(a.rows_pad, p) + (size_t)row * tile_scale_pitch(a.nc, a.sgc, p) +
+                        (size_t)(c / a.sgc - (32u * p) / a.sgc) * 2;
+    const float delta = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(sp));
     if (a.fmt == FMT_BP4 || a.fmt == FMT_BP5 || a.fmt == FMT_BP6) {
         const uint8_t *half = col < 32 ? p0 : p1;
         const uint32_t cc = col % 32, k = col % 8;

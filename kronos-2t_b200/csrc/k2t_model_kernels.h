@@ -13,8 +13,8 @@ struct EmbedArgs {               // tied embedding = row of the lm_head matrix (
     const uint16_t *embed_bf16;  // [vocab][hidden] or null
     const uint32_t *token;       // device, [n_tok]
     float *hidden;
-    uint32_t fmt, nc, nsg_pad, sgc, sgc_shift;
-    uint32_t pitch[3], cell[3];
+    uint32_t fmt, nc, rows_pad, sgc, sgc_shift;
+    uint32_t cell[3];
     int32_t max_odd;
     int8_t codebook[32];
 };

@@ -123,27 +123,49 @@ E8Q2_TEMPLATES = [(0, 0, 0, 0), (32, 32, 0, 0), (32, 0, 32, 0), (32, 0, 0, 32), 
                   (64, 32, 32, 32), (32, 64, 32, 32), (32, 32, 64, 32), (32, 32, 32, 64)]
 
 
-def up16(x):
-    return (x + 15) & ~15
-
-
 def split_image(fmt, image, rows, cols, nsg):
     """-> (plane A bytes [rows, nc, a], plane B bytes [rows, nc, b], scales [rows, nsg]) where A is what
-    decode<FMT> sees first (32 B: planes 0+1 for 4-bit formats, 16 B for NF3) and B the rest."""
+    decode<FMT> sees first (32 B: planes 0+1 for 4-bit formats, 16 B for NF3) and B the rest.
+
+    The image keeps every plane in pass tiles: tile p = chunks 32p.. of all rows (rows padded to 4 with zero cells),
+    [row][n_p cells]; the scale plane likewise, 64 bytes x rows_pad per tile, row pitch = the tile's scale groups x 2
+    bytes rounded up to 4 (a group that straddles two tiles is stored in both)."""
     nc = cols // 64
-    cells = CELL_BYTES[fmt]
+    sgc = -(-nc // nsg)
+    assert -(-nc // sgc) == nsg
+    rows_pad, n_pass = (rows + 3) & ~3, -(-nc // 32)
     off, planes = 0, []
-    for cb in cells:
-        pitch = up16(nc * cb)
-        planes.append(image[off: off + rows * pitch].reshape(rows, pitch)[:, : nc * cb].reshape(rows, nc, cb))
-        off += rows * pitch
-    nsg_pad = (nsg + 7) & ~7
-    scales = image[off: off + rows * nsg_pad * 2].view("<u2").reshape(rows, nsg_pad)
-    assert not scales[:, nsg:].any()
-    assert image.size == off + rows * nsg_pad * 2 + 16
+    for cb in CELL_BYTES[fmt]:
+        plane = np.zeros((rows, nc, cb), np.uint8)
+        for p in range(n_pass):
+            n = min(32, nc - 32 * p)
+            t0 = off + p * rows_pad * 32 * cb
+            tile = image[t0: t0 + rows_pad * n * cb].reshape(rows_pad, n, cb)
+            assert not tile[rows:].any()
+            plane[:, 32 * p: 32 * p + n] = tile[:rows]
+        planes.append(plane)
+        off += rows_pad * nc * cb
+    scales = np.zeros((rows, nsg), np.uint16)
+    seen = np.zeros(nsg, bool)
+    for p in range(n_pass):
+        n = min(32, nc - 32 * p)
+        g_lo, g_hi = (32 * p) // sgc, (32 * p + n - 1) // sgc
+        cnt = g_hi - g_lo + 1
+        pitch = (cnt * 2 + 3) & ~3
+        t0 = off + p * rows_pad * 64
+        tile = image[t0: t0 + rows_pad * pitch].reshape(rows_pad, pitch)
+        assert not tile[rows:].any() and not tile[:, cnt * 2:].any()
+        vals = np.ascontiguousarray(tile[:rows, : cnt * 2]).view("<u2")
+        for g in range(g_lo, g_hi + 1):
+            if seen[g]:
+                assert np.array_equal(scales[:, g], vals[:, g - g_lo])
+            scales[:, g] = vals[:, g - g_lo]
+            seen[g] = True
+    assert seen.all()
+    assert image.size == off + n_pass * rows_pad * 64 + 16
     if fmt in ("nf3", "e8q2"):
-        return planes[0], planes[1], scales[:, :nsg]
-    return np.concatenate([planes[0], planes[1]], axis=2), planes[2], scales[:, :nsg]
+        return planes[0], planes[1], scales
+    return np.concatenate([planes[0], planes[1]], axis=2), planes[2], scales
 
 
 def image_rows(fmt, image, rows, cols, nsg, cb_words=None):
@@ -169,10 +191,21 @@ def test_bitplane_image_decodes_to_file_codes(oracle, planes, rows):
         assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
 
 
+def test_wide_bitplane_image_spans_pass_tiles(oracle):
+    """40 chunks = a full pass tile and a ragged one (8 chunks); 22 rows = padding rows in every tile."""
+    rows, cols, planes = 22, 2560, 5
+    m = oracle.bipolar_quantize_rtn(normal(77, (rows, cols), 0.02), planes, threads=2)
+    image = k2.matrix_image(k2.bipolar_desc(rows, cols, planes, m.data, m.scales))
+    codes, scales = image_rows("bp5", image, rows, cols, cols // 64)
+    sc_file = m.scales.reshape(-1, cols // 64, 16)
+    for r in range(rows):
+        assert np.array_equal(codes[r], oracle.bipolar_unpack_row(m, r))
+        assert np.array_equal(scales[r], sc_file[r // 16, :, r % 16])
+
+
 @pytest.mark.parametrize("bits", [3, 4])
-@pytest.mark.parametrize("rows,sgc", [(71, 1), (71, 2), (128, 2)])
-def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc):
-    cols = 192
+@pytest.mark.parametrize("rows,sgc,cols", [(71, 1, 192), (71, 2, 192), (128, 2, 192), (32, 3, 2560), (32, 2, 2304)])
+def test_nf_image_decodes_to_centroids(oracle, bits, rows, sgc, cols):
     m, idx, sc = oracle.nf_quantize_rtn(normal(40 + bits, (rows, cols), 0.02), bits, sgc, threads=2, return_indices=True)
     # an asymmetric codebook exercises the general 16-entry lookup, not just the fitted symmetric one
     cb = m.codebook.copy()
@@ -288,7 +321,7 @@ def test_malformed_descriptors_are_rejected(oracle):
     m = oracle.bipolar_quantize_rtn(normal(1, (16, 64), 0.02), 4)
     L = k2.load_library()
     good = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
-    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 2 * 16 * 16 + 16 * 8 * 2 + 16
+    assert L.kronos_cuda_matrix_image(C.byref(good), 0, None, 0) == 2 * 16 * 16 + 16 * 64 + 16
     for kw in ({"cols": 65}, {"bits": 7}, {"rows": 0}, {"kind": 1}, {"len0": 5}):
         bad = k2.bipolar_desc(16, 64, 4, m.data, m.scales)
         for key, val in kw.items():
