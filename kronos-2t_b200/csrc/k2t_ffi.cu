@@ -36,7 +36,7 @@ bool run_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, const int8_t *d
         uint32_t n = (uint32_t)std::min<size_t>(max_t, n_tok - t0), launched = 0;
         cudaError_t e = launch_gemv(ctx->stream, m->dm, d_xq + t0 * g.cols, d_xs + t0 * g.nc,
                                     d_xsum ? d_xsum + t0 * g.nc : nullptr, n, d_out + t0 * out_stride, out_stride,
-                                    d_dots ? d_dots + t0 * (size_t)g.rows * g.nc : nullptr, ctx->sm_count, ctx->d_err, &launched);
+                                    d_dots ? d_dots + t0 * (size_t)g.rows * g.nc : nullptr, ctx->sm_count, ctx->d_err, &launched, true);
         ctx->launches += launched;
         if (!cuda_ok(ctx, e, "gemv launch")) return false;
     }

@@ -13,6 +13,10 @@ fwht_quant_kernel(const float *__restrict__ x, const float *__restrict__ norm_w,
                   int8_t *__restrict__ q, float *__restrict__ scales, int32_t *__restrict__ sums) {
     const uint32_t lane = threadIdx.x & 31;
     const uint64_t item = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    // launched as a programmatic dependent: wait for the producer of x, then let the next kernel (a GEMV that
+    // starts streaming its weights before it needs these activations) begin
+    pdl_wait();
+    pdl_trigger();
     if (item >= (uint64_t)n_tok * nc) return;   // whole warp leaves together
     const uint32_t t = (uint32_t)(item / nc), c = (uint32_t)(item % nc);
     const size_t base = (size_t)t * nc * 64 + (size_t)c * 64;
@@ -40,9 +44,8 @@ cudaError_t launch_fwht_quant(cudaStream_t stream, const float *x, const float *
     const uint32_t nc = cols / 64;
     const uint64_t items = (uint64_t)n_tok * nc;
     if (items == 0) return cudaSuccess;
-    fwht_quant_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(x, norm_w, inv_rms, n_tok, nc, chunk0, q,
-                                                                      scales, sums);
-    return cudaGetLastError();
+    return launch_kernel(fwht_quant_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, stream, true, x, norm_w, inv_rms, n_tok, nc, chunk0, q,
+                         scales, sums);
 }
 
 }  // namespace k2t

@@ -1,5 +1,6 @@
 // Stand-alone quantized GEMV / small-N GEMM kernel and its host launcher (body: k2t_gemv_core.cuh).
 #include <algorithm>
+#include <cstdlib>
 
 #include "k2t_gemv_core.cuh"
 
@@ -21,26 +22,42 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
+// Team shape for a launch: WK warps per team (they split the passes of their row blocks) and the number of teams.
+// A team works through its J row blocks in groups of 8; each group costs one ROUND per WK passes, and a round pays a
+// fixed latency (activation loads, first stage in flight, the hand-off of the fp32 chain) before its stages stream.
+// So few fat rounds beat many thin ones: among the shapes that fit the SMs, take the one with the smallest
+// groups x rounds x (latency + stages per round), with every team given the same number of blocks (no tail).
+struct TeamShape { uint32_t wk, teams, smem; };
+static TeamShape choose_team(uint32_t n_rb, uint32_t np, uint32_t warp_bytes, uint32_t extra_bytes, uint32_t n_slot, int sm_count) {
+    TeamShape best{1, 1, warp_bytes + extra_bytes};
+    float best_cost = 1e30f;
+    static const uint32_t force_wk = [] { const char *v = std::getenv("KRONOS_CUDA_GEMV_WK"); return v ? (uint32_t)std::atoi(v) : 0u; }();   // measurement switch
+    for (uint32_t wk = 1; wk <= 8 && (wk == 1 || wk <= np); wk *= 2) {
+        if (force_wk && wk != force_wk && !(wk < force_wk && wk * 2 > std::min(8u, np))) continue;     // the forced size, or the largest one the passes allow
+        const uint32_t smem = wk * warp_bytes + extra_bytes;
+        uint32_t per_sm = (227u * 1024u) / (smem + 1024u);      // CTAs per SM by shared memory (1 KiB reserved per CTA)
+        if (per_sm == 0) continue;
+        per_sm = std::min(per_sm, 32u);
+        if (per_sm * wk > 48) per_sm = 48 / wk;
+        // warps per SM a multiple of 4, so that the four schedulers of an SM get the same number of warps
+        if (per_sm * wk >= 4) per_sm = ((per_sm * wk) & ~3u) / wk;
+        const uint32_t cap = std::max(1u, per_sm * (uint32_t)sm_count / n_slot);
+        const uint32_t J = (n_rb + cap - 1) / cap, teams = (n_rb + J - 1) / J;
+        const uint32_t groups = (J + 7) / 8, in_group = std::min(8u, J), rounds = (np + wk - 1) / wk;
+        const float cost = (float)(groups * rounds) * (1.5f + 0.25f * (float)in_group);
+        if (cost < 0.9f * best_cost) { best_cost = cost; best = TeamShape{wk, teams, smem}; }      // a larger team has to win clearly: its chain hand-offs are serial
+    }
+    return best;
+}
+
 template <int FMT, int NT, bool DOTS>
 static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_count) {
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
-    // warps per CTA: split the passes when rows alone give fewer than ~12 warps per SM
-    uint32_t wk = 1;
-    while (wk < 8 && wk * 2 <= np && n_rb * wk < 12u * (uint32_t)sm_count) wk *= 2;
-    const uint32_t smem = wk * warp_smem<FMT>(NT) + NT * 32 * 4;
+    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(NT), NT * 32 * 4, 1, sm_count);
     cudaError_t e = cudaSuccess;
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (t.smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem);
     if (e != cudaSuccess) return e;
-    // persistent grid: as many CTAs as fit per SM (shared memory, 1 KiB reserved per CTA), with the warps
-    // per SM a multiple of 4 so that the four schedulers of an SM get the same number of warps
-    uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
-    per_sm = per_sm < 1 ? 1 : per_sm;
-    if (per_sm > 32) per_sm = 32;
-    if (per_sm * wk > 48) per_sm = 48 / wk;
-    if (per_sm * wk >= 4) per_sm = ((per_sm * wk) & ~3u) / wk;
-    uint32_t grid = per_sm * (uint32_t)sm_count;
-    if (grid > n_rb) grid = n_rb;
-    return launch_kernel(gemv_kernel<FMT, NT, DOTS>, dim3(grid), dim3(32 * wk), smem, stream, a.pdl != 0, a);
+    return launch_kernel(gemv_kernel<FMT, NT, DOTS>, dim3(t.teams), dim3(32 * t.wk), t.smem, stream, a.pdl != 0, a);
 }
 
 template <int FMT>
@@ -98,19 +115,12 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
 template <int FMT>
 static cudaError_t launch_expert_fmt(cudaStream_t stream, const GemvArgs &a, const ExpertBatch &b, uint32_t n_slot, int sm_count) {
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
-    uint32_t wk = 1;
-    while (wk < 8 && wk * 2 <= np && n_rb * n_slot * wk < 12u * (uint32_t)sm_count) wk *= 2;
-    const uint32_t smem = wk * warp_smem<FMT>(1) + 32 * 4;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_expert_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(1), 32 * 4, n_slot, sm_count);
+    if (t.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_expert_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem);
         if (e != cudaSuccess) return e;
     }
-    uint32_t per_sm = (227u * 1024u) / (smem + 1024u);
-    per_sm = per_sm < 1 ? 1 : per_sm > 32 ? 32 : per_sm;
-    if (per_sm * wk > 48) per_sm = 48 / wk;
-    uint32_t grid = std::max(1u, per_sm * (uint32_t)sm_count / n_slot);
-    if (grid > n_rb) grid = n_rb;
-    return launch_kernel(gemv_expert_kernel<FMT>, dim3(grid, n_slot), dim3(32 * wk), smem, stream, a.pdl != 0, a, b);
+    return launch_kernel(gemv_expert_kernel<FMT>, dim3(t.teams, n_slot), dim3(32 * t.wk), t.smem, stream, a.pdl != 0, a, b);
 }
 
 int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out) {

@@ -321,18 +321,26 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     const uint32_t my_soff = my_scale ? St::OFFS : (my_k == 0 ? St::OFF0 : my_k == 1 ? St::OFF1 : St::OFF2);
     constexpr uint32_t CELL_SUM = Cell<FMT>::B0 + Cell<FMT>::B1 + Cell<FMT>::B2;
 
-    // producer cursor: 32-row group, own pass index, block in group
+    // producer cursor: 32-row group, own pass index, block in group; the tile geometry is recomputed only when the
+    // pass changes (never, for a matrix of one pass)
     uint32_t pj0 = 0, ppi = 0, pjj = 0;
+    uint32_t c_pass = 0xffffffffu, c_pitch = 0, c_total = 0;
+    const uint8_t *c_src = my_base;
     auto issue = [&](uint32_t stage) {
         if (pj0 >= J || my_np == 0) return;                     // nothing left: the stage stays idle
+        const uint32_t p = wid + ppi * WK;
+        if (p != c_pass) {
+            const uint32_t n = tile_chunks(a.nc, p), sp = tile_scale_pitch(a.nc, a.sgc, p);
+            c_pass = p;
+            c_pitch = my_scale ? sp : n * my_cell;              // bytes of one row of this lane's plane in tile p
+            c_total = RS * (sp + n * CELL_SUM);
+            c_src = my_base + (my_scale ? tile_scale_off(a.rows_pad, p) : tile_code_off(a.rows_pad, my_cell, p));
+        }
         const uint32_t row0 = (gw + (pj0 + pjj) * nw) * RS;
         const uint32_t bar = bar0 + 8 * stage;
-        const uint32_t p = wid + ppi * WK, n = tile_chunks(a.nc, p), sp = tile_scale_pitch(a.nc, a.sgc, p);
-        const uint32_t pitch = my_scale ? sp : n * my_cell;     // bytes of one row of this lane's plane in tile p
-        const uint8_t *src = my_base + (my_scale ? tile_scale_off(a.rows_pad, p) : tile_code_off(a.rows_pad, my_cell, p)) + (size_t)row0 * pitch;
-        if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, RS * (sp + n * CELL_SUM)); }
+        if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, c_total); }
         __syncwarp();
-        if (my_role) bulk_g2s(stage_sa + stage * St::BYTES + my_soff, src, RS * pitch, bar);
+        if (my_role) bulk_g2s(stage_sa + stage * St::BYTES + my_soff, c_src + (size_t)row0 * c_pitch, RS * c_pitch, bar);
         const uint32_t in_group = min(8u, J - pj0);
         if (++pjj == in_group) { pjj = 0; if (++ppi == my_np) { ppi = 0; pj0 += 8; } }
     };

@@ -77,7 +77,7 @@ extern "C" int32_t kronos_cuda_linear_noalloc(KronosCudaContext *ctx, const Kron
         ctx->launches += 1;
         if (!cuda_ok(ctx, e, "linear_noalloc: fwht_quant launch")) return -1;
         uint32_t launched = 0;
-        e = launch_gemv(ctx->stream, m->dm, q, xs, xsum, n, d_out + t0 * g.rows, g.rows, nullptr, ctx->sm_count, ctx->d_err, &launched);
+        e = launch_gemv(ctx->stream, m->dm, q, xs, xsum, n, d_out + t0 * g.rows, g.rows, nullptr, ctx->sm_count, ctx->d_err, &launched, true);
         ctx->launches += launched;
         if (!cuda_ok(ctx, e, "linear_noalloc: gemv launch")) return -1;
     }
