@@ -39,8 +39,9 @@ static TeamShape choose_team(uint32_t n_rb, uint32_t np, uint32_t warp_bytes, ui
         if (per_sm == 0) continue;
         per_sm = std::min(per_sm, 32u);
         if (per_sm * wk > 48) per_sm = 48 / wk;
-        // warps per SM a multiple of 4, so that the four schedulers of an SM get the same number of warps
-        if (per_sm * wk >= 4) per_sm = ((per_sm * wk) & ~3u) / wk;
+        // warps per SM a multiple of 4, so that the four schedulers of an SM get the same number of warps - where that
+        // costs at most one warp in seven (14 -> 12, not 11 -> 8)
+        if (per_sm * wk >= 4 && 7 * ((per_sm * wk) & 3u) <= per_sm * wk) per_sm = ((per_sm * wk) & ~3u) / wk;
         const uint32_t cap = std::max(1u, per_sm * (uint32_t)sm_count / n_slot);
         const uint32_t J = (n_rb + cap - 1) / cap, teams = (n_rb + J - 1) / J;
         const uint32_t groups = (J + 7) / 8, in_group = std::min(8u, J), rounds = (np + wk - 1) / wk;
