@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
 // host side
 // ------------------------------------------------------------------------------------------------
 // Team shape for a launch: WK warps per team (they split the passes of their row blocks) and the number of teams.
-// A team works through its J row blocks in groups of 8; each group costs one ROUND per WK passes, and a round pays a
+// A team works through its J row blocks in groups of GB; each group costs one ROUND per WK passes, and a round pays a
 // fixed latency (activation loads, first stage in flight, the hand-off of the fp32 chain) before its stages stream.
 // So few fat rounds beat many thin ones: among the shapes that fit the SMs, take the one with the smallest
 // groups x rounds x (latency + stages per round), with every team given the same number of blocks (no tail).
@@ -39,12 +39,11 @@ static TeamShape choose_team(uint32_t n_rb, uint32_t np, uint32_t warp_bytes, ui
         if (per_sm == 0) continue;
         per_sm = std::min(per_sm, 32u);
         if (per_sm * wk > 48) per_sm = 48 / wk;
-        // warps per SM a multiple of 4, so that the four schedulers of an SM get the same number of warps - where that
-        // costs at most one warp in seven (14 -> 12, not 11 -> 8)
-        if (per_sm * wk >= 4 && 7 * ((per_sm * wk) & 3u) <= per_sm * wk) per_sm = ((per_sm * wk) & ~3u) / wk;
+        static const uint32_t force_per_sm = [] { const char *v = std::getenv("KRONOS_CUDA_GEMV_WARPS"); return v ? (uint32_t)std::atoi(v) : 0u; }();   // measurement switch
+        if (force_per_sm && force_per_sm / wk >= 1 && force_per_sm / wk <= per_sm + 4) per_sm = force_per_sm / wk;
         const uint32_t cap = std::max(1u, per_sm * (uint32_t)sm_count / n_slot);
         const uint32_t J = (n_rb + cap - 1) / cap, teams = (n_rb + J - 1) / J;
-        const uint32_t groups = (J + 7) / 8, in_group = std::min(8u, J), rounds = (np + wk - 1) / wk;
+        const uint32_t groups = (J + GB - 1) / GB, in_group = std::min(GB, J), rounds = (np + wk - 1) / wk;
         const float cost = (float)(groups * rounds) * (1.5f + 0.25f * (float)in_group);
         if (cost < 0.9f * best_cost) { best_cost = cost; best = TeamShape{wk, teams, smem}; }      // a larger team has to win clearly: its chain hand-offs are serial
     }

@@ -235,7 +235,12 @@ template <int FMT> struct Stage {
 };
 
 // shared memory of one warp: stages, v tile float [NT][32][33], w_scale tile bf16 [32][34], mbarriers
-constexpr uint32_t TILE_V = 32 * 33 * 4, TILE_WS = 32 * 34 * 2;
+// GB row blocks (GB x RS = 32 rows) share one fp32-chain step: lane i runs row i.  The kernel is latency-bound and its
+// throughput follows the warps an SM can hold (measured on a 2048 x 49152 b4 launch: 14.2 / 12.6 / 10.1 / 9.6 us with
+// 8 / 10 / 12 / 14 warps per SM), which shared memory per warp decides; halving the group (a smaller tile, 17 warps)
+// was measured slower all the same (10.1 us; NF4 17.8 instead of 12.5 us): the chain steps double.
+constexpr uint32_t GB = 8, GROUP_ROWS = GB * RS;
+constexpr uint32_t TILE_V = GROUP_ROWS * 33 * 4, TILE_WS = GROUP_ROWS * 34 * 2;
 template <int FMT> __host__ __device__ constexpr uint32_t warp_smem(uint32_t nt) {
     return ((NSTAGE * Stage<FMT>::BYTES + nt * TILE_V + TILE_WS + 128) + 127u) & ~127u;
 }
@@ -341,8 +346,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
         if (lane == 0) { fence_proxy_async(); mbar_expect_tx(bar, c_total); }
         __syncwarp();
         if (my_role) bulk_g2s(stage_sa + stage * St::BYTES + my_soff, c_src + (size_t)row0 * c_pitch, RS * c_pitch, bar);
-        const uint32_t in_group = min(8u, J - pj0);
-        if (++pjj == in_group) { pjj = 0; if (++ppi == my_np) { ppi = 0; pj0 += 8; } }
+        const uint32_t in_group = min(GB, J - pj0);
+        if (++pjj == in_group) { pjj = 0; if (++ppi == my_np) { ppi = 0; pj0 += GB; } }
     };
     // the first unit goes to the stage the consumer reads first (the cursor persists across calls)
 #pragma unroll
@@ -358,8 +363,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     uint32_t stage = ps.stage, phase = ps.phase;
     bool failed = false;                                         // a wait gave up: keep the barriers in step, skip waiting
     const uint32_t slot_j = lane / RS, slot_r = lane % RS;       // chain: lane -> (block in group, row in block)
-    for (uint32_t j0 = 0; j0 < J; j0 += 8) {
-        const uint32_t in_group = min(8u, J - j0);
+    for (uint32_t j0 = 0; j0 < J; j0 += GB) {
+        const uint32_t in_group = min(GB, J - j0);
         for (uint32_t r = 0; r < rounds; ++r) {
             const uint32_t p = r * WK + wid;
             const bool has = p < np;
@@ -434,7 +439,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
                                 const int acc = dot16<FMT>(ub, q[t]);
                                 const int dot = is_bitplane<FMT>() ? 2 * acc - a.max_odd * xsum[t] : acc;
                                 if (act && rr < nrows) {
-                                    s_v[t * (32 * 33) + (jj * RS + rr) * 33 + lane] = __fmul_rn(__int2float_rn(dot), sx[t]);
+                                    s_v[t * (GROUP_ROWS * 33) + (jj * RS + rr) * 33 + lane] = __fmul_rn(__int2float_rn(dot), sx[t]);
                                     if (DOTS && (uint32_t)t < a.n_tok) a.int_dots[((size_t)t * a.rows + row0 + rr) * a.nc + c] = dot;
                                 }
                             }
@@ -453,7 +458,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
                     const uint32_t row = (gw + (j0 + slot_j) * nw) * RS + slot_r;
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
-                        const float *vv = s_v + t * (32 * 33) + lane * 33;
+                        const float *vv = s_v + t * (GROUP_ROWS * 33) + lane * 33;
                         const uint16_t *wv = s_ws + lane * 34;
                         float ft = p == 0 ? 0.0f : s_f[t * 32 + lane];
                         if (nz[t] == (n == 32 ? 0xffffffffu : (1u << n) - 1u)) {
