@@ -533,7 +533,8 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
         // values: half-warp hw takes positions t0 + hw, t0 + hw + 2, ...
         const uint32_t n_here = min(32u, t_hi - t0);
         const uint8_t *vt = st + Tile::V_OFF;
-        for (uint32_t j = hw; j < n_here; j += 2) {
+#pragma unroll 4
+        for (uint32_t j = hw; j < n_here; j += 2) {      // unrolled: the loads of four positions are in flight together
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 float c0, c1, c2, c3;
@@ -542,8 +543,12 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnArgs a) {
                     const uint32_t word = *reinterpret_cast<const uint32_t *>(vt + j * ROW + b * 32 + (e / 32) * 16 + (r % 16)) >> shift;
                     c0 = s_cb[word & 15u]; c1 = s_cb[(word >> 8) & 15u]; c2 = s_cb[(word >> 16) & 15u]; c3 = s_cb[(word >> 24) & 15u];
                 } else {
-                    const char4 v = *reinterpret_cast<const char4 *>(vt + j * ROW + b * 64 + dl * 4);
-                    c0 = (float)v.x; c1 = (float)v.y; c2 = (float)v.z; c3 = (float)v.w;
+                    // int8 -> fp32 without the conversion unit: 0x4B000000 | (b ^ 0x80) is the float 2^23 + 128 + (int8)b
+                    const uint32_t v = *reinterpret_cast<const uint32_t *>(vt + j * ROW + b * 64 + dl * 4) ^ 0x80808080u;
+                    c0 = __fsub_rn(__uint_as_float(prmt(v, 0x4B000000u, 0x7650u)), 8388736.0f);
+                    c1 = __fsub_rn(__uint_as_float(prmt(v, 0x4B000000u, 0x7651u)), 8388736.0f);
+                    c2 = __fsub_rn(__uint_as_float(prmt(v, 0x4B000000u, 0x7652u)), 8388736.0f);
+                    c3 = __fsub_rn(__uint_as_float(prmt(v, 0x4B000000u, 0x7653u)), 8388736.0f);
                 }
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
