@@ -36,7 +36,7 @@ WORKLOAD = "gemv_sweep_batch1: K x N in 2048x2048, 2048x8192, 8192x2048, 2048x49
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one 2048x49152 launch from the ncu --set full captures summarised under
 # profiles/ (gemv_b4_2048x49152.md, gemv_nf4g128_2048x49152.md)
-NCU_DRAM_BYTES_PER_LAUNCH = {"b4": 53507328 + 69120, "nf4g128": 51939072 + 62720}
+NCU_DRAM_BYTES_PER_LAUNCH = {"b4": 53507072 + 124672, "nf4g128": 51937536 + 20224}
 
 
 def fmt_spec(fmt):
@@ -337,8 +337,11 @@ def run_b200(args, rank, world, local_rank):
     achieved = big_b / big_us / 1e3
     roofline = {"bound": "hbm", "kernel": "gemv_kernel, the four 2048x49152 launches of a sweep pass (78% of its bytes)",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "launch_form": "each case timed alone: a CUDA graph of back-to-back launches over distinct HBM copies of the matrix, "
+                               "programmatic dependents of one another as in the decode engine (a launch streams its first weight stages "
+                               "while the previous one drains); CUDA events around three replays",
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH["b4"], "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, b4 2048x49152)",
-                "traffic_note": "ncu captures of the b4 and nf4g128 launches: 53.58 / 52.00 MB against 53.68 / 52.10 MB algorithmic (profiles/)",
+                "traffic_note": "ncu captures of the b4 and nf4g128 launches: 53.63 / 51.96 MB against 53.68 / 52.10 MB algorithmic (profiles/)",
                 "traffic_per_format": NCU_DRAM_BYTES_PER_LAUNCH,
                 "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak},
                 "per_launch": kernels}

@@ -55,6 +55,7 @@ struct KronosCudaEngine {
     // tensor parallel: exchange buffer (data[2][tp][slot] floats + flags[tp]) and the peers' mappings
     k2t::TpLink tp{};
     float *tp_buf = nullptr;
+    uint32_t *tp_done = nullptr;              // CTAs of the current fused exchange that have finished (device word)
     std::vector<void *> tp_peers;            // mappings opened with cudaIpcOpenMemHandle
     bool tp_ready = false;
     float *logits_local = nullptr;            // this rank's logits slice [MAX_BATCH][vocab_size]
@@ -108,17 +109,24 @@ bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 
 void fill_embed_args(const KronosCudaEngine *e, EmbedArgs &a);
 
 // tensor parallel: x <- sum over ranks of x (rank order), and the concatenation of the ranks' slices; no-ops on one device
-bool tp_sum(KronosCudaEngine *e, float *x, uint32_t n) {
-    if (e->cfg.tp_size <= 1) return true;
-    if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
-    return count(e, launch_tp_exchange(e->ctx->stream, e->tp, x, x, n, 0, e->pdl), "tp sum");
-}
 bool tp_gather(KronosCudaEngine *e, const float *slice, float *all, uint32_t n) {
     if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
     return count(e, launch_tp_exchange(e->ctx->stream, e->tp, slice, all, n, n, e->pdl), "tp gather");
 }
 
 constexpr uint32_t MAX_BATCH = 4;      // tokens per weight pass in prompt processing (the reference's 4-token tiles)
+
+// Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
+// output of a row-parallel projection: the kernel exchanges and sums the ranks' partials itself.
+bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *x_norm, uint32_t T, bool pdl) {
+    const KronosCudaEngineConfig &c = e->cfg;
+    if (c.tp_size > 1 && delta != nullptr) {
+        if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
+        return count(e, launch_rmsnorm_quant_tp(e->ctx->stream, e->hidden, delta, w, c.hidden_size, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, x_norm, T, pdl,
+                                                e->tp, e->tp_done), "rmsnorm");
+    }
+    return count(e, launch_rmsnorm_quant_x(e->ctx->stream, e->hidden, delta, w, c.hidden_size, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, x_norm, T, pdl), "rmsnorm");
+}
 
 enum class Tail { Greedy, LastLogits, AllLogits, None };
 
@@ -140,7 +148,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
     }
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const EngineLayer &L = e->layers[l];
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, l == 0 ? nullptr : e->proj, L.input_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl && (embed || l > 0)), "rmsnorm")) return false;
+        if (!norm_quant(e, l == 0 ? nullptr : e->proj, L.input_norm, nullptr, T, e->pdl && (embed || l > 0))) return false;
         if (!gemv(e, L.qkv, e->qkv, T)) return false;
         for (uint32_t t = 0; t < T; ++t) {      // the attention output of token t becomes row t of the o_proj activation
             float *qkv_t = e->qkv + (size_t)t * qkv_rows;
@@ -178,10 +186,9 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
             }
         }
-        if (!gemv(e, L.o, e->proj, T)) return false;
-        if (!tp_sum(e, e->proj, T * h)) return false;
+        if (!gemv(e, L.o, e->proj, T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
         if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
-            if (!count(e, launch_rmsnorm_quant_x(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->x_norm, T, e->pdl), "rmsnorm")) return false;
+            if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl)) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
             for (uint32_t t = 0; t < T; ++t) {
                 RouterArgs ra{};
@@ -198,14 +205,13 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             }
             continue;
         }
-        if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
+        if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl)) return false;
         if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
         if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, c.down_chunk0, T, e->pdl), "swiglu")) return false;
         if (!gemv(e, L.down, e->proj, T)) return false;
-        if (!tp_sum(e, e->proj, T * h)) return false;
     }
     // the last residual is folded into `hidden` by the final norm even when no logits are wanted
-    if (!count(e, launch_rmsnorm_quant(s, e->hidden, e->proj, e->final_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, T, e->pdl), "rmsnorm")) return false;
+    if (!norm_quant(e, e->proj, e->final_norm, nullptr, T, e->pdl)) return false;
     const uint32_t vocab_all = c.tp_size > 1 ? c.vocab_total : c.vocab_size;
     float *lg = c.tp_size > 1 ? e->logits_local : e->logits;        // under tp: this rank's slice, then gathered into `logits`
     if (tail == Tail::AllLogits || tail == Tail::Greedy) {
@@ -266,7 +272,7 @@ cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
 }
 uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
     uint32_t n = 1 + 2 + 1 + (e->cfg.tp_size > 1 ? 1 : 0);
-    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0) + (e->cfg.tp_size > 1 ? 2 : 0);     // MoE FFN: 6 kernels for 4
+    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4; the tensor-parallel sums ride in the norm kernels
     return n;
 }
 
@@ -522,7 +528,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
             e->allocs.push_back(raw);
             e->tp_buf = static_cast<float *>(raw);
             ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, floats * 4 + 256, ctx->stream), "clear tp exchange") &&
-                 dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
+                 dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
             e->tp.tp = c.tp_size; e->tp.rank = c.tp_rank; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
             e->tp.peer_data[c.tp_rank] = e->tp_buf;
             e->tp.peer_flags[c.tp_rank] = reinterpret_cast<uint32_t *>(e->tp_buf + floats);

@@ -36,13 +36,21 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 // the next projection.  The sum of squares follows dot_f32_neon (real_llm.rs:9736-9800) exactly: 16 fma
 // accumulators over 16-element strides (lanes 0..15 of warp 0 run the 16 chains over the staged vector),
 // combined (a0+a1)+(a2+a3) lane-wise and then pairwise - so inv_rms is the CPU value bit for bit.
+//
+// Tensor parallel (tp.tp > 1, delta given): delta is this rank's PARTIAL projection output; the ranks' partials are
+// exchanged here - the protocol of tp_exchange_kernel (k2t_tp.cu), one exchange per token with its own flag row: store
+// the partial into every rank's buffer, fence, raise the flags, wait (bounded) for everybody's, then add the slots in
+// rank order - so the residual update needs no launch of its own.  The call counter is advanced by the last CTA to finish.
 __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
                                                             const float *__restrict__ w, uint32_t n, float eps,
                                                             int8_t *__restrict__ q, float *__restrict__ scales,
-                                                            int32_t *__restrict__ sums, float *__restrict__ x_norm) {
+                                                            int32_t *__restrict__ sums, float *__restrict__ x_norm,
+                                                            const TpLink tp, uint32_t *__restrict__ tp_done) {
     extern __shared__ float s_x[];           // n floats
     __shared__ float s_inv;
+    __shared__ uint32_t s_epoch;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nc = n / 64;
+    const uint32_t tok = blockIdx.x;
     {   // blockIdx.x = token of the batch: every per-token vector is contiguous
         const size_t t = blockIdx.x;
         hidden += t * n; q += t * n; scales += t * nc; sums += t * nc;
@@ -52,10 +60,42 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
     pdl_wait();
     pdl_trigger();
     const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
+    const bool exchange = tp.tp > 1 && delta != nullptr;
+    uint32_t epoch = 0;
+    if (exchange) {
+        if (tid == 0) s_epoch = *tp.epoch + 1;
+        __syncthreads();
+        epoch = s_epoch;
+        const size_t off = ((size_t)(epoch & 1u) * tp.tp + tp.rank) * tp.slot + (size_t)tok * n;
+        for (uint32_t p = 0; p < tp.tp; ++p) {
+            float4 *to = reinterpret_cast<float4 *>(tp.peer_data[p] + off);
+            for (uint32_t i = tid; i < n / 4; i += nthr) to[i] = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
+        }
+        __threadfence_system();
+        __syncthreads();
+        int failed = 0;
+        if (tid < tp.tp) {
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tp.peer_flags[tid] + tok * TP_MAX + tp.rank), "r"(epoch) : "memory");
+            uint32_t seen = 0, polls = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(tp.peer_flags[tp.rank] + tok * TP_MAX + tid) : "memory");
+                if (seen >= epoch) break;
+                if (++polls > (1u << 22)) { failed = 1; break; }
+            }
+        }
+        if (__syncthreads_or(failed) && tid == 0) atomicExch(tp.err, 3u);
+        delta = tp.peer_data[tp.rank] + (size_t)(epoch & 1u) * tp.tp * tp.slot + (size_t)tok * n;      // slot of rank 0; rank r is r * slot further
+    }
     for (uint32_t i = tid; i < n / 4; i += nthr) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
-            const float4 d = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
+            float4 d = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
+            if (exchange) {
+                for (uint32_t r = 1; r < tp.tp; ++r) {     // ((v0 + v1) + v2) + ...: the same bits on every rank
+                    const float4 u = __ldcg(reinterpret_cast<const float4 *>(delta + (size_t)r * tp.slot) + i);
+                    d.x = __fadd_rn(d.x, u.x); d.y = __fadd_rn(d.y, u.y); d.z = __fadd_rn(d.z, u.z); d.w = __fadd_rn(d.w, u.w);
+                }
+            }
             v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
             reinterpret_cast<float4 *>(hidden)[i] = v;
         }
@@ -88,6 +128,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
         warp_quant64(v.x, v.y, q0, q1, sc, sum);
         reinterpret_cast<char2 *>(q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
         if (lane == 0) { scales[c] = sc; sums[c] = sum; }
+    }
+    if (exchange && tid == 0 && atomicAdd(tp_done, 1u) + 1u == gridDim.x) {       // every CTA of the launch has read the counter
+        *tp_done = 0;
+        *tp.epoch = epoch;
     }
 }
 
@@ -764,6 +808,13 @@ cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const fl
 }
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {
+    TpLink none{};
+    return launch_rmsnorm_quant_tp(s, hidden, delta, w, n, eps, q, scales, sums, x_norm, n_tok, pdl, none, nullptr);
+}
+cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl,
+                                    const TpLink &tp, uint32_t *tp_done) {
+    if (tp.tp > 1 && ((size_t)n_tok * n > tp.slot || n_tok * TP_MAX > 64 || tp_done == nullptr)) return cudaErrorInvalidValue;
     const size_t smem = (size_t)n * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
@@ -772,7 +823,7 @@ cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *d
     }
     // one warp per 64-value chunk where that fits: the load and the rotation each take one round
     const uint32_t threads = std::min(1024u, std::max(256u, (n / 64) * 32u));
-    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm);
+    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm, tp, tp_done);
 }
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;

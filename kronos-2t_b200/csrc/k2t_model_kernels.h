@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include "k2t_layout.h"
+#include "k2t_tp.h"
 
 namespace k2t {
 
@@ -96,6 +97,11 @@ cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, 
 // x_norm (optional): also write the normalised fp32 vector (the MoE router reads it)
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl);
+// the same with the tensor-parallel exchange of `delta` (each rank's partial projection output) folded in: tp.tp > 1,
+// tp_done = a zeroed device word; n_tok * n floats must fit a slot of the exchange buffer
+cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
+                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl,
+                                    const TpLink &tp, uint32_t *tp_done);
 cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl);
 // SwiGLU of n_slot expert outputs [n_slot][2 * d_ff] with the scalar-path exp (moe_800b.rs:1498-1517), then rotation + int8
 cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
