@@ -523,11 +523,15 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         if (e->has_moe) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
         const size_t slot = std::max<size_t>((size_t)MAX_BATCH * h, c.vocab_size), floats = 2 * (size_t)c.tp_size * slot;
         void *raw = nullptr;
-        ok = cuda_ok(ctx, cudaMalloc(&raw, floats * 4 + 256), "cudaMalloc(tp exchange)");
+        // floats | 256 bytes of flags | (value, call number) words of the fused sums: [2][tp][MAX_BATCH * hidden] x 8 bytes
+        const size_t ll_slot = (size_t)MAX_BATCH * h, total = floats * 4 + 256 + 2 * (size_t)c.tp_size * ll_slot * 8;
+        ok = cuda_ok(ctx, cudaMalloc(&raw, total), "cudaMalloc(tp exchange)");
         if (ok) {
             e->allocs.push_back(raw);
             e->tp_buf = static_cast<float *>(raw);
-            ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, floats * 4 + 256, ctx->stream), "clear tp exchange") &&
+            e->tp.ll_slot = (uint32_t)ll_slot;
+            e->tp.peer_ll[c.tp_rank] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(raw) + floats * 4 + 256);
+            ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, total, ctx->stream), "clear tp exchange") &&
                  dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
             e->tp.tp = c.tp_size; e->tp.rank = c.tp_rank; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
             e->tp.peer_data[c.tp_rank] = e->tp_buf;
@@ -599,6 +603,7 @@ int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *e, const uint8_t *handles
         e->tp_peers.push_back(p);
         e->tp.peer_data[r] = static_cast<float *>(p);
         e->tp.peer_flags[r] = reinterpret_cast<uint32_t *>(static_cast<float *>(p) + floats);
+        e->tp.peer_ll[r] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(p) + floats * 4 + 256);
     }
     e->tp_ready = true;
     return 0;

@@ -38,9 +38,11 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 // combined (a0+a1)+(a2+a3) lane-wise and then pairwise - so inv_rms is the CPU value bit for bit.
 //
 // Tensor parallel (tp.tp > 1, delta given): delta is this rank's PARTIAL projection output; the ranks' partials are
-// exchanged here - the protocol of tp_exchange_kernel (k2t_tp.cu), one exchange per token with its own flag row: store
-// the partial into every rank's buffer, fence, raise the flags, wait (bounded) for everybody's, then add the slots in
-// rank order - so the residual update needs no launch of its own.  The call counter is advanced by the last CTA to finish.
+// exchanged here, so the residual update needs no launch of its own.  Every element is stored into each peer's buffer
+// as an 8-byte (value, call number) word; the receiver polls (bounded) the words of call e in the half e & 1 of its own
+// buffer and adds the ranks' values in rank order.  A rank cannot be two calls ahead of another (it needs the others'
+// words of call e + 1, sent after they finished call e), so two halves suffice; the call counter is shared with
+// tp_exchange_kernel (k2t_tp.cu) and advanced by the last CTA of the launch to finish.
 __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
                                                             const float *__restrict__ w, uint32_t n, float eps,
                                                             int8_t *__restrict__ q, float *__restrict__ scales,
@@ -62,40 +64,49 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
     const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
     const bool exchange = tp.tp > 1 && delta != nullptr;
     uint32_t epoch = 0;
+    float *s_d = s_x + n;                    // exchange: the summed delta (the launcher doubles the shared memory)
     if (exchange) {
         if (tid == 0) s_epoch = *tp.epoch + 1;
         __syncthreads();
         epoch = s_epoch;
-        const size_t off = ((size_t)(epoch & 1u) * tp.tp + tp.rank) * tp.slot + (size_t)tok * n;
-        for (uint32_t p = 0; p < tp.tp; ++p) {
-            float4 *to = reinterpret_cast<float4 *>(tp.peer_data[p] + off);
-            for (uint32_t i = tid; i < n / 4; i += nthr) to[i] = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
-        }
-        __threadfence_system();
-        __syncthreads();
-        int failed = 0;
-        if (tid < tp.tp) {
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tp.peer_flags[tid] + tok * TP_MAX + tp.rank), "r"(epoch) : "memory");
-            uint32_t seen = 0, polls = 0;
-            for (;;) {
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(tp.peer_flags[tp.rank] + tok * TP_MAX + tid) : "memory");
-                if (seen >= epoch) break;
-                if (++polls > (1u << 22)) { failed = 1; break; }
+        const size_t half_off = (size_t)(epoch & 1u) * tp.tp * tp.ll_slot + (size_t)tok * n;
+        // send: every element travels with the call number in one 8-byte store, so the receiver needs no fence and
+        // no flag round trip - it polls the words themselves
+        for (uint32_t i = tid; i < n; i += nthr) {
+            const uint32_t bits = __float_as_uint(__ldcg(delta + i));
+            for (uint32_t p = 0; p < tp.tp; ++p) {
+                if (p == tp.rank) continue;
+                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(tp.peer_ll[p] + half_off + (size_t)tp.rank * tp.ll_slot + i), "r"(bits), "r"(epoch) : "memory");
             }
         }
+        // receive and add in rank order, ((v0 + v1) + v2) + ...: the same bits on every rank
+        int failed = 0;
+        const uint2 *mine = tp.peer_ll[tp.rank] + half_off;
+        for (uint32_t i = tid; i < n; i += nthr) {
+            float acc = 0.0f;
+            for (uint32_t r = 0; r < tp.tp; ++r) {
+                float v;
+                if (r == tp.rank) {
+                    v = __ldcg(delta + i);
+                } else {
+                    uint32_t bits = 0, seen = 0, polls = 0;
+                    for (;;) {
+                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(mine + (size_t)r * tp.ll_slot + i) : "memory");
+                        if (seen == epoch) break;
+                        if (++polls > (1u << 22)) { failed = 1; break; }
+                    }
+                    v = __uint_as_float(bits);
+                }
+                acc = r == 0 ? v : __fadd_rn(acc, v);
+            }
+            s_d[i] = acc;
+        }
         if (__syncthreads_or(failed) && tid == 0) atomicExch(tp.err, 3u);
-        delta = tp.peer_data[tp.rank] + (size_t)(epoch & 1u) * tp.tp * tp.slot + (size_t)tok * n;      // slot of rank 0; rank r is r * slot further
     }
     for (uint32_t i = tid; i < n / 4; i += nthr) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
-            float4 d = __ldcg(reinterpret_cast<const float4 *>(delta) + i);
-            if (exchange) {
-                for (uint32_t r = 1; r < tp.tp; ++r) {     // ((v0 + v1) + v2) + ...: the same bits on every rank
-                    const float4 u = __ldcg(reinterpret_cast<const float4 *>(delta + (size_t)r * tp.slot) + i);
-                    d.x = __fadd_rn(d.x, u.x); d.y = __fadd_rn(d.y, u.y); d.z = __fadd_rn(d.z, u.z); d.w = __fadd_rn(d.w, u.w);
-                }
-            }
+            const float4 d = exchange ? reinterpret_cast<const float4 *>(s_d)[i] : __ldcg(reinterpret_cast<const float4 *>(delta) + i);
             v.x = __fadd_rn(v.x, d.x); v.y = __fadd_rn(v.y, d.y); v.z = __fadd_rn(v.z, d.z); v.w = __fadd_rn(v.w, d.w);
             reinterpret_cast<float4 *>(hidden)[i] = v;
         }
@@ -814,8 +825,8 @@ cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *d
 cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                     int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl,
                                     const TpLink &tp, uint32_t *tp_done) {
-    if (tp.tp > 1 && ((size_t)n_tok * n > tp.slot || n_tok * TP_MAX > 64 || tp_done == nullptr)) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)n * sizeof(float);
+    if (tp.tp > 1 && ((size_t)n_tok * n > tp.ll_slot || tp_done == nullptr)) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)n * sizeof(float) * (tp.tp > 1 ? 2 : 1);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -10,8 +10,10 @@ constexpr uint32_t TP_MAX = 8;
 struct TpLink {
     float *peer_data[TP_MAX];       // exchange buffer of every rank (own buffer at index `rank`), mapped into this process
     uint32_t *peer_flags[TP_MAX];   // their flag words
+    uint2 *peer_ll[TP_MAX];         // their (value, call number) words for the sums fused into the norm kernel: [2][tp][ll_slot]
     uint32_t tp, rank;
     uint32_t slot;                  // floats per (half, rank) slot
+    uint32_t ll_slot;               // words per (half, rank) slot of the (value, call number) region
     uint32_t *epoch;                // this rank's call counter (device memory)
     uint32_t *err;                  // error word of the context
 };
