@@ -159,6 +159,12 @@ typedef struct KronosCudaEngineConfig {
      * down_proj's input, so that the activations are rotated with their global block index.  The matrices passed to
      * kronos_cuda_engine_create are the rank's slices in the ordinary file formats (kronos_2t_b200/tp.py cuts them). */
     uint32_t tp_size, tp_rank, o_chunk0, down_chunk0, vocab_total;
+    /* Expert parallelism for sparse-MoE models (no counterpart in the reference): ep_size ranks, one engine each; every
+     * rank keeps the dense tensors (attention, norms, lm_head, router) whole and only the experts e with
+     * e % ep_size == ep_rank.  A token's routed experts run on their owners; the ranks' partial weighted sums are added
+     * in rank order inside the norm kernel that follows the MoE block (the exchange of kronos_cuda_engine_tp_handle /
+     * _tp_attach, with ep_size handles).  Zero / ep_size <= 1 for one device; not combined with tp_size > 1. */
+    uint32_t ep_size, ep_rank;
 } KronosCudaEngineConfig;
 
 /* One decoder layer as borrowed from the host engine: counterpart of LayerBorrow

@@ -26,6 +26,7 @@ struct EngineLayer {
     const uint8_t **d_gu_bases = nullptr, **d_dn_bases = nullptr;     // device tables: image base of every expert
     k2t::ExpertCodebook *d_gu_books = nullptr, *d_dn_books = nullptr; // device tables: decode tables of every expert
     int gu_fmt = -1, dn_fmt = -1;                                     // kernel format of the layer's experts
+    uint32_t expert0 = 0;                                             // first expert held by this rank (expert parallelism)
     uint32_t *d_route_ids = nullptr;                                  // [MAX_BATCH][32] routes of the last batch
     float *d_route_w = nullptr;
 };
@@ -118,9 +119,11 @@ constexpr uint32_t MAX_BATCH = 4;      // tokens per weight pass in prompt proce
 
 // Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
 // output of a row-parallel projection: the kernel exchanges and sums the ranks' partials itself.
-bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *x_norm, uint32_t T, bool pdl) {
+// `partial`: delta holds this rank's share only (row-parallel projection under tensor parallelism, routed experts under
+// expert parallelism).
+bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *x_norm, uint32_t T, bool pdl, bool partial) {
     const KronosCudaEngineConfig &c = e->cfg;
-    if (c.tp_size > 1 && delta != nullptr) {
+    if (partial && delta != nullptr) {
         if (!e->tp_ready) return fail(e->ctx, "tensor-parallel engine used before kronos_cuda_engine_tp_attach");
         return count(e, launch_rmsnorm_quant_tp(e->ctx->stream, e->hidden, delta, w, c.hidden_size, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, x_norm, T, pdl,
                                                 e->tp, e->tp_done), "rmsnorm");
@@ -148,7 +151,9 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
     }
     for (uint32_t l = 0; l < c.num_layers; ++l) {
         const EngineLayer &L = e->layers[l];
-        if (!norm_quant(e, l == 0 ? nullptr : e->proj, L.input_norm, nullptr, T, e->pdl && (embed || l > 0))) return false;
+        // the FFN output of the layer before: partial sums under tensor parallelism, and after a MoE block under expert parallelism
+        const bool ffn_partial = c.tp_size > 1 || (c.ep_size > 1 && l > 0 && e->layers[l - 1].moe);
+        if (!norm_quant(e, l == 0 ? nullptr : e->proj, L.input_norm, nullptr, T, e->pdl && (embed || l > 0), ffn_partial)) return false;
         if (!gemv(e, L.qkv, e->qkv, T)) return false;
         for (uint32_t t = 0; t < T; ++t) {      // the attention output of token t becomes row t of the o_proj activation
             float *qkv_t = e->qkv + (size_t)t * qkv_rows;
@@ -188,7 +193,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
         }
         if (!gemv(e, L.o, e->proj, T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
         if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
-            if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl)) return false;
+            if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl, c.tp_size > 1)) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
             for (uint32_t t = 0; t < T; ++t) {
                 RouterArgs ra{};
@@ -196,22 +201,22 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
                 ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32;
                 if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
-                if (!count(e, launch_gemv_experts(s, L.expert_gu[0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
+                if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
                                                   e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert gate_up")) return false;
                 if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
-                if (!count(e, launch_gemv_experts(s, L.expert_dn[0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
+                if (!count(e, launch_gemv_experts(s, L.expert_dn[L.expert0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
                                                   e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert down")) return false;
-                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl), "moe combine")) return false;
+                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl, ra.route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr), "moe combine")) return false;
             }
             continue;
         }
-        if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl)) return false;
+        if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl, c.tp_size > 1)) return false;
         if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
         if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, c.down_chunk0, T, e->pdl), "swiglu")) return false;
         if (!gemv(e, L.down, e->proj, T)) return false;
     }
     // the last residual is folded into `hidden` by the final norm even when no logits are wanted
-    if (!norm_quant(e, e->proj, e->final_norm, nullptr, T, e->pdl)) return false;
+    if (!norm_quant(e, e->proj, e->final_norm, nullptr, T, e->pdl, c.tp_size > 1 || (c.ep_size > 1 && e->layers.back().moe))) return false;
     const uint32_t vocab_all = c.tp_size > 1 ? c.vocab_total : c.vocab_size;
     float *lg = c.tp_size > 1 ? e->logits_local : e->logits;        // under tp: this rank's slice, then gathered into `logits`
     if (tail == Tail::AllLogits || tail == Tail::Greedy) {
@@ -290,7 +295,7 @@ bool setup_mega(KronosCudaEngine *e) {
     if (!want || want[0] != '1') { e->mega_why = "not requested (KRONOS_CUDA_MEGA=1 enables it)"; return true; }
     if (c.num_attention_heads > (uint32_t)ctx->sm_count) { e->mega_why = "more query heads than SMs"; return true; }
     if (e->has_moe) { e->mega_why = "sparse-MoE layers are served by the per-operator path"; return true; }
-    if (c.tp_size > 1) { e->mega_why = "tensor-parallel ranks are served by the per-operator path"; return true; }
+    if (c.tp_size > 1 || c.ep_size > 1) { e->mega_why = "tensor- and expert-parallel ranks are served by the per-operator path"; return true; }
     uint32_t warp_smem = 0;
     auto fill = [&](const KronosCudaMatrix *m, MegaMatrix &mm) {
         const int fmt = fill_gemv_args(m->dm, true, mm.g);
@@ -384,24 +389,30 @@ std::string setup_moe_layer(KronosCudaEngine *e, EngineLayer &L, const KronosCud
     if (d.moe_router_bias && !dev_alloc(e, L.router_bias, E, d.moe_router_bias)) return ctx->err;
     std::vector<const uint8_t *> gu_bases(E), dn_bases(E);
     std::vector<ExpertCodebook> gu_books(E), dn_books(E);
+    L.expert_gu.assign(E, nullptr);
+    L.expert_dn.assign(E, nullptr);
+    L.expert0 = c.ep_size > 1 ? c.ep_rank : 0;         // the first expert this rank holds: geometry template of the expert kernels
+    bool first = true;
     for (uint32_t x = 0; x < E; ++x) {
+        if (c.ep_size > 1 && x % c.ep_size != c.ep_rank) { gu_bases[x] = nullptr; dn_bases[x] = nullptr; gu_books[x] = ExpertCodebook{}; dn_books[x] = ExpertCodebook{}; continue; }
         const uint8_t *r = d.moe_shard + (size_t)x * rec;
         KronosCudaMatrixDesc m{};
         m.kind = KRONOS_CUDA_MATRIX_NF; m.bits = bits; m.scale_group_chunks = sgc;
         m.rows = 2 * dff; m.cols = h; std::memcpy(m.codebook, r, 16); m.data0 = r + gu_off; m.len0 = gu_bytes;
         KronosCudaMatrix *gu = kronos_cuda_matrix_upload(ctx, &m, 0);
         if (!gu) return "expert " + std::to_string(x) + " gate_up: " + ctx->err;
-        L.expert_gu.push_back(gu);
+        L.expert_gu[x] = gu;
         m.rows = h; m.cols = dff; std::memcpy(m.codebook, r + 16, 16); m.data0 = r + dn_off; m.len0 = dn_bytes;
         KronosCudaMatrix *dn = kronos_cuda_matrix_upload(ctx, &m, 0);
         if (!dn) return "expert " + std::to_string(x) + " down: " + ctx->err;
-        L.expert_dn.push_back(dn);
+        L.expert_dn[x] = dn;
         // every expert of a layer decodes with one kernel: NF4 falls back to the general decode for all of them as soon
         // as one codebook does not fit the two-table form
         const int fg = expert_codebook(gu->dm, gu_books[x]), fd = expert_codebook(dn->dm, dn_books[x]);
         if (fg < 0 || fd < 0) return "expert matrices in an unsupported format";
-        L.gu_fmt = x == 0 ? fg : (L.gu_fmt == fg ? fg : (int)FMT_COUNT);
-        L.dn_fmt = x == 0 ? fd : (L.dn_fmt == fd ? fd : (int)FMT_COUNT);
+        L.gu_fmt = first ? fg : (L.gu_fmt == fg ? fg : (int)FMT_COUNT);
+        L.dn_fmt = first ? fd : (L.dn_fmt == fd ? fd : (int)FMT_COUNT);
+        first = false;
         gu_bases[x] = gu->dm.d_base; dn_bases[x] = dn->dm.d_base;
     }
     if (!dev_alloc(e, L.d_gu_books, E, gu_books.data()) || !dev_alloc(e, L.d_dn_books, E, dn_books.data()) ||
@@ -455,6 +466,10 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     if (c.tp_size > 1) {
         if (c.tp_size > TP_MAX || c.tp_rank >= c.tp_size) { fail(ctx, "engine_create: tp_size up to 8 and tp_rank below it"); return nullptr; }
         if (c.vocab_total != c.vocab_size * c.tp_size || c.vocab_size % 4) { fail(ctx, "engine_create: vocab_total must be tp_size equal lm_head slices"); return nullptr; }
+    }
+    if (c.ep_size > 1) {
+        if (c.tp_size > 1) { fail(ctx, "engine_create: expert parallelism is not combined with tensor parallelism"); return nullptr; }
+        if (c.ep_size > TP_MAX || c.ep_rank >= c.ep_size || c.ep_size > c.moe_num_experts) { fail(ctx, "engine_create: ep_size up to 8 (and at most the experts), ep_rank below it"); return nullptr; }
     }
     if (!make_current(ctx)) return nullptr;
     const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd, kv_dim = c.num_key_value_heads * hd;
@@ -519,23 +534,24 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len);
-    if (ok && c.tp_size > 1) {
-        if (e->has_moe) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
-        const size_t slot = std::max<size_t>((size_t)MAX_BATCH * h, c.vocab_size), floats = 2 * (size_t)c.tp_size * slot;
+    const uint32_t xg = c.tp_size > 1 ? c.tp_size : c.ep_size, xr = c.tp_size > 1 ? c.tp_rank : c.ep_rank;     // exchange group
+    if (ok && xg > 1) {
+        if (e->has_moe && c.tp_size > 1) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
+        const size_t slot = std::max<size_t>((size_t)MAX_BATCH * h, c.vocab_size), floats = 2 * (size_t)xg * slot;
         void *raw = nullptr;
         // floats | 256 bytes of flags | (value, call number) words of the fused sums: [2][tp][MAX_BATCH * hidden] x 8 bytes
-        const size_t ll_slot = (size_t)MAX_BATCH * h, total = floats * 4 + 256 + 2 * (size_t)c.tp_size * ll_slot * 8;
+        const size_t ll_slot = (size_t)MAX_BATCH * h, total = floats * 4 + 256 + 2 * (size_t)xg * ll_slot * 8;
         ok = cuda_ok(ctx, cudaMalloc(&raw, total), "cudaMalloc(tp exchange)");
         if (ok) {
             e->allocs.push_back(raw);
             e->tp_buf = static_cast<float *>(raw);
             e->tp.ll_slot = (uint32_t)ll_slot;
-            e->tp.peer_ll[c.tp_rank] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(raw) + floats * 4 + 256);
+            e->tp.peer_ll[xr] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(raw) + floats * 4 + 256);
             ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, total, ctx->stream), "clear tp exchange") &&
                  dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
-            e->tp.tp = c.tp_size; e->tp.rank = c.tp_rank; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
-            e->tp.peer_data[c.tp_rank] = e->tp_buf;
-            e->tp.peer_flags[c.tp_rank] = reinterpret_cast<uint32_t *>(e->tp_buf + floats);
+            e->tp.tp = xg; e->tp.rank = xr; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
+            e->tp.peer_data[xr] = e->tp_buf;
+            e->tp.peer_flags[xr] = reinterpret_cast<uint32_t *>(e->tp_buf + floats);
         }
     }
     if (ok && e->has_moe) {
@@ -575,7 +591,7 @@ int32_t kronos_cuda_engine_tp_handle(KronosCudaEngine *e, uint8_t handle[64]) {
     if (!e || !handle) return -1;
     KronosCudaContext *ctx = e->ctx;
     ctx->err.clear();
-    if (e->cfg.tp_size <= 1 || !e->tp_buf) return fail(ctx, "tp_handle: the engine was created with tp_size <= 1"), -1;
+    if (!e->tp_buf) return fail(ctx, "tp_handle: the engine was created with tp_size <= 1 and ep_size <= 1"), -1;
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
     cudaIpcMemHandle_t hnd;
     if (!make_current(ctx) || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "tp_handle") ||      // the buffer is cleared by now
@@ -589,13 +605,13 @@ int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *e, const uint8_t *handles
     if (!e) return -1;
     KronosCudaContext *ctx = e->ctx;
     ctx->err.clear();
-    if (e->cfg.tp_size <= 1 || !e->tp_buf) return fail(ctx, "tp_attach: the engine was created with tp_size <= 1"), -1;
-    if (!handles || n_handles != e->cfg.tp_size) return fail(ctx, "tp_attach: one handle per rank is needed"), -1;
+    if (!e->tp_buf) return fail(ctx, "tp_attach: the engine was created with tp_size <= 1 and ep_size <= 1"), -1;
+    if (!handles || n_handles != e->tp.tp) return fail(ctx, "tp_attach: one handle per rank is needed"), -1;
     if (e->tp_ready) return fail(ctx, "tp_attach: already attached"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t floats = 2 * (size_t)e->cfg.tp_size * e->tp.slot;
-    for (uint32_t r = 0; r < e->cfg.tp_size; ++r) {
-        if (r == e->cfg.tp_rank) continue;
+    const size_t floats = 2 * (size_t)e->tp.tp * e->tp.slot;
+    for (uint32_t r = 0; r < e->tp.tp; ++r) {
+        if (r == e->tp.rank) continue;
         cudaIpcMemHandle_t hnd;
         std::memcpy(&hnd, handles + (size_t)r * 64, 64);
         void *p = nullptr;

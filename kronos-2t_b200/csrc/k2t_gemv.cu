@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
     pdl_wait();
     const uint32_t slot = blockIdx.y, e = __ldcg(b.route_ids + slot);
     const uint8_t *base = b.bases[e];
+    if (base == nullptr) return;       // expert parallelism: another rank owns this expert (the whole CTA leaves, no copy is in flight)
     {
         const uint4 *bk = reinterpret_cast<const uint4 *>(b.books + e);
         const uint4 c0 = __ldg(bk), c1 = __ldg(bk + 1), t = __ldg(bk + 2), o = __ldg(bk + 3);

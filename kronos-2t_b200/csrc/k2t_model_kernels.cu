@@ -262,15 +262,20 @@ __global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *_
     if (lane == 0) { scales[c] = sc; sums[c] = sum; }
 }
 
-// out[i] = 0; for every route in ascending expert order: out[i] += w * expert_out[slot][i]   (separate multiply and add)
+// out[i] = 0; for every route in ascending expert order: out[i] += w * expert_out[slot][i]   (separate multiply and add).
+// Expert parallelism (owned != null): only the routes whose expert this rank holds (owned[e] != null) - a partial sum.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ expert_out, const float *__restrict__ route_w,
-                                                          uint32_t n_slot, uint32_t n, float *__restrict__ out) {
+                                                          uint32_t n_slot, uint32_t n, float *__restrict__ out,
+                                                          const uint32_t *__restrict__ route_ids, const uint8_t *const *__restrict__ owned) {
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
     pdl_wait();
     pdl_trigger();
     if (i >= n) return;
     float acc = 0.0f;
-    for (uint32_t s = 0; s < n_slot; ++s) acc = __fadd_rn(acc, __fmul_rn(__ldcg(route_w + s), __ldcg(expert_out + (size_t)s * n + i)));
+    for (uint32_t s = 0; s < n_slot; ++s) {
+        if (owned != nullptr && owned[__ldcg(route_ids + s)] == nullptr) continue;
+        acc = __fadd_rn(acc, __fmul_rn(__ldcg(route_w + s), __ldcg(expert_out + (size_t)s * n + i)));
+    }
     out[i] = acc;
 }
 
@@ -814,8 +819,8 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
     return launch_kernel(expert_swiglu_quant_kernel, dim3((d_ff / 64 + 7) / 8, n_slot), dim3(256), 0, s, pdl, gate_up, d_ff, q, scales, sums);
 }
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl) {
-    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out);
+                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned) {
+    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned);
 }
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {

@@ -108,7 +108,7 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
                                        int32_t *sums, bool pdl);
 // out[i] = sum over slots, in slot order, of route_w[s] * expert_out[s][i]   (sparse_moe.rs:1046-1048)
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl);
+                               bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
 
 }  // namespace k2t

@@ -38,7 +38,7 @@ class EngineConfig(C.Structure):
                [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)] + \
                [(n, C.c_uint32) for n in ("moe_num_experts", "moe_top_k", "moe_norm_topk", "moe_d_ff", "moe_bits",
                                           "moe_scale_group_chunks")] + [("moe_expert_bytes", C.c_uint64)] + \
-               [(n, C.c_uint32) for n in ("tp_size", "tp_rank", "o_chunk0", "down_chunk0", "vocab_total")]
+               [(n, C.c_uint32) for n in ("tp_size", "tp_rank", "o_chunk0", "down_chunk0", "vocab_total", "ep_size", "ep_rank")]
 
 
 class LayerDesc(C.Structure):
@@ -291,6 +291,8 @@ class Engine:
         if int(c.get("tp_size", 1)) > 1:      # a rank of a tensor-parallel group (spec from kronos_2t_b200.tp.shard_spec)
             self.cfg.tp_size, self.cfg.tp_rank, self.cfg.vocab_total = c["tp_size"], c["tp_rank"], c["vocab_total"]
             self.cfg.o_chunk0, self.cfg.down_chunk0 = c["o_chunk0"], c["down_chunk0"]
+        if int(c.get("ep_size", 1)) > 1:      # a rank of an expert-parallel group: the whole spec, experts e % ep_size == ep_rank are used
+            self.cfg.ep_size, self.cfg.ep_rank = c["ep_size"], c["ep_rank"]
         moes = [ly["moe"] for ly in spec["layers"] if ly.get("moe")]
         if moes:        # one geometry for every MoE layer of a model (MoeGeometry)
             m0 = moes[0]

@@ -78,6 +78,7 @@ struct Moe {
     uint32_t scoring = 0;               // MoeRouterScoring tag: 0 softmax, 1 top-k softmax, 2 sigmoid (sparse_moe.rs:28-53)
     std::vector<float> router_w, router_bias;
     std::vector<Expert> experts;
+    uint32_t ep_size = 1, ep_rank = 0;   // expert-parallel emulation: only experts e % ep_size == ep_rank contribute (tests)
     uint32_t last_k = 0;                 // routes of the last token (tests)
     uint32_t last_e[32] = {0};
     float last_w[32] = {0};
@@ -380,6 +381,7 @@ void moe_forward(Moe &M, const float *x_norm, size_t h, float *out, size_t threa
     std::vector<float> gu(2 * (size_t)M.d_ff), sw(M.d_ff), eo(h);
     std::fill(out, out + h, 0.0f);
     for (size_t i = 0; i < k; ++i) {
+        if (M.ep_size > 1 && ids[i] % M.ep_size != M.ep_rank) continue;      // another rank's expert
         const Expert &X = M.experts[ids[i]];
         X.gu.gemv(act_in.q.data(), act_in.s.data(), act_in.m.data(), gu.data(), threads);
         for (size_t j = 0; j < M.d_ff; ++j) {          // moe_800b.rs:1498-1505: scalar libm exp, gate = rows [0, d_ff), up = the rest
@@ -439,6 +441,11 @@ int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const floa
         if (!load_mat(M.experts[e].dn, &d)) return -1;
     }
     return 0;
+}
+
+void k2o_model_set_ep(K2oModel *m, uint32_t ep_size, uint32_t ep_rank) {
+    if (!m) return;
+    for (Layer &L : m->layers) { L.moe.ep_size = ep_size ? ep_size : 1; L.moe.ep_rank = ep_rank; }
 }
 
 uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts, float *weights) {

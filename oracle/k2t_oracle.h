@@ -168,6 +168,9 @@ int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const floa
                       uint32_t top_k, int norm_topk, uint32_t d_ff, uint32_t bits, uint32_t scale_group_chunks,
                       const uint8_t *shard, size_t expert_bytes);
 /* Routes of the last token through MoE layer l: up to 32 (expert, weight) pairs sorted by expert id; returns k. */
+/* Expert-parallel emulation (the reference runs on one device): from now on the MoE blocks of `m` add only the routed
+ * experts e with e % ep_size == ep_rank, so k2o_model_ffn_part returns one rank's partial sum. */
+void k2o_model_set_ep(K2oModel *m, uint32_t ep_size, uint32_t ep_rank);
 uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts, float *weights);
 /* .k2tm record geometry (NfExpertByteLayout): returns aligned_expert_bytes, fills the pair-stream offsets / sizes. */
 size_t k2o_nf_expert_layout(size_t d_model, size_t d_ff, size_t bits, size_t sgc, size_t *gu_pair_off, size_t *gu_pair_bytes,

@@ -416,6 +416,7 @@ def _declare_model(L):
     L.k2o_model_set_moe.restype = C.c_int
     L.k2o_model_set_moe.argtypes = [P, C.c_uint32, P, P, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, P, C.c_size_t]
     L.k2o_model_last_routes.restype, L.k2o_model_last_routes.argtypes = C.c_uint32, [P, C.c_uint32, P, P]
+    L.k2o_model_set_ep.restype, L.k2o_model_set_ep.argtypes = None, [P, C.c_uint32, C.c_uint32]
     L.k2o_nf_expert_layout.restype = C.c_size_t
     L.k2o_nf_expert_layout.argtypes = [C.c_size_t] * 4 + [P] * 4
     L.k2o_model_tap_attention.restype, L.k2o_model_tap_attention.argtypes = P, [P]
@@ -682,3 +683,34 @@ class TpModel:
             m.advance()
         self.last_hidden = hidden
         return logits
+
+
+class EpModel:
+    """Expert-parallel emulation on the CPU: every rank holds the whole model and runs the dense parts (identically);
+    in a sparse-MoE block rank r adds only the routed experts e with e % ep == r, and the ranks' partial sums are added
+    in rank order, ((p0 + p1) + p2) + ..., before they join the residual stream."""
+
+    def __init__(self, spec, ep):
+        self.ranks = [Model(spec) for _ in range(ep)]
+        for r, m in enumerate(self.ranks):
+            m.L.k2o_model_set_ep(m.h, ep, r)
+        self.layers = spec["cfg"]["layers"]
+        self.moe = [bool(ly.get("moe")) for ly in spec["layers"]]
+
+    def close(self):
+        for m in self.ranks:
+            m.close()
+
+    def forward_token(self, token, threads=2):
+        hidden = np.asarray(self.ranks[0].embed(token), np.float32).copy()
+        for l in range(self.layers):
+            attn = [m.attn_part(l, hidden, threads) for m in self.ranks]          # every rank keeps its own KV cache
+            hidden = (hidden + attn[0]).astype(np.float32)
+            parts = [m.ffn_part(l, hidden, threads) for m in self.ranks]
+            hidden = (hidden + (TpModel._sum(parts) if self.moe[l] else parts[0])).astype(np.float32)
+        logits = self.ranks[0].head_part(hidden, threads)
+        for m in self.ranks:
+            m.advance()
+        self.last_hidden = hidden
+        return logits
+

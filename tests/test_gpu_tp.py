@@ -71,3 +71,54 @@ def test_two_rank_engine_matches_rank_order_emulation(oracle, tmp_path, mode, kw
         logits = emu.forward_token(nxt); nxt = oracle.argmax(logits); out.append(nxt)
     assert list(greedy[0]) == out
     emu.close(); whole.close()
+
+
+EP_WORKER = r"""
+import os, sys
+sys.path.insert(0, os.path.join(ROOT, "tests")); sys.path.insert(0, os.path.join(ROOT, "oracle")); sys.path.insert(0, ROOT)
+import numpy as np, torch.distributed as dist
+import oracle as o, k2t_models as km, kronos_2t_b200 as k2
+rank, world = int(os.environ["RANK"]), 2
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%s" % os.environ["PORT"], rank=rank, world_size=world)
+moe = eval(os.environ["MOE"]); mode = os.environ["MODE"]; tokens = eval(os.environ["TOKENS"])
+spec = km.build(o, km.MOE_TINY, mode, seed=21, moe=moe)
+spec["cfg"] = dict(spec["cfg"], ep_size=world, ep_rank=rank)
+ctx = k2.Context(rank)
+eng = k2.Engine(ctx, spec)
+handles = [None] * world
+dist.all_gather_object(handles, eng.tp_handle())
+eng.tp_attach(handles)
+dist.barrier()
+logits = eng.forward_token_ids(tokens, want_all=True)
+greedy = eng.decode_greedy(int(np.argmax(logits[-1])), len(tokens), 12)
+np.save(os.environ["OUT"] + ".%d.npy" % rank, logits)
+np.save(os.environ["OUT"] + ".g%d.npy" % rank, greedy)
+dist.barrier()
+eng.close(); ctx.close()
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode,moe", [("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=3, d_ff=64, bits=3, sgc=2)),
+                                      ("b5", dict(layers=[1, 2], n_experts=6, top_k=6, d_ff=64, bits=4, sgc=1, norm_topk=False, bias=True))])
+def test_two_rank_expert_parallel_engine_matches_rank_order_emulation(oracle, tmp_path, mode, moe):
+    tokens = [t % km.MOE_TINY["vocab"] for t in TOKENS]
+    port = str(33000 + os.getpid() % 2000)
+    env = dict(os.environ, PORT=port, OUT=str(tmp_path / "ep"), MODE=mode, MOE=repr(moe), TOKENS=repr(tokens))
+    procs = [subprocess.Popen([sys.executable, "-c", "ROOT = %r\n" % ROOT + EP_WORKER], env=dict(env, RANK=str(r))) for r in range(2)]
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    got = [np.load(str(tmp_path / f"ep.{r}.npy")) for r in range(2)]
+    greedy = [np.load(str(tmp_path / f"ep.g{r}.npy")) for r in range(2)]
+    assert np.array_equal(got[0], got[1]) and np.array_equal(greedy[0], greedy[1])
+    spec = km.build(oracle, km.MOE_TINY, mode, seed=21, moe=moe)
+    emu = oracle.EpModel(spec, 2)
+    want = np.stack([emu.forward_token(t) for t in tokens])
+    assert np.array_equal(got[0], want)
+    nxt, out = int(np.argmax(want[-1])), []
+    for _ in range(12):
+        logits = emu.forward_token(nxt); nxt = oracle.argmax(logits); out.append(nxt)
+    assert list(greedy[0]) == out
+    emu.close()
+

@@ -115,3 +115,25 @@ def test_two_gloo_ranks_reproduce_the_emulation(oracle, tmp_path):
     want = np.stack([emu.forward_token(t) for t in [5, 17, 300, 42, 7]])
     assert np.array_equal(a, want)
     emu.close(); whole.close()
+
+
+@pytest.mark.parametrize("moe,ep", [(dict(layers=[0, 2], n_experts=8, top_k=3, d_ff=64, bits=3, sgc=2), 2),
+                                    (dict(layers=[1], n_experts=6, top_k=6, d_ff=64, bits=4, sgc=1, norm_topk=False), 3)])
+def test_expert_parallel_emulation_matches_the_whole_model(oracle, moe, ep):
+    """Experts e % ep == r on rank r: one rank reproduces the model bit for bit; more ranks differ only by the order of
+    the weighted sum (partial sums per rank, added in rank order); routes are the single-device routes on every rank."""
+    spec = km.build(oracle, km.MOE_TINY, "b4", seed=21, moe=moe)
+    whole = oracle.Model(spec)
+    tokens = [5, 17, 300, 42, 7, 199, 63, 250, 11]
+    want = np.stack([whole.forward_token(t, 2) for t in tokens])
+    one = oracle.EpModel(spec, 1)
+    assert np.array_equal(np.stack([one.forward_token(t) for t in tokens]), want)
+    many = oracle.EpModel(spec, ep)
+    got = np.stack([many.forward_token(t) for t in tokens])
+    assert np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
+    cos = [np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)) for a, b in zip(got, want)]
+    assert min(cos) > 0.99999
+    for m in (one, many):
+        m.close()
+    whole.close()
+
