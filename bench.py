@@ -351,7 +351,10 @@ def run_b200(args, rank, world, local_rank):
         decode = decode_tok_s(ctx, stream, timed_region=lambda fn: timed(fn, 1)[0], world=world)
 
         if not args.no_decode_models:
-            decode["models"] = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+            try:
+                decode["models"] = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+            except Exception as exc:      # the headline line must still come out; the failure is reported in it
+                decode["models_error"] = f"{type(exc).__name__}: {exc}"
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
