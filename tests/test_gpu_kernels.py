@@ -174,6 +174,31 @@ def test_linear_end_to_end(ctx, oracle):
 
 
 # ----------------------------------------------------------------------------- sweep shapes (random codes)
+@pytest.mark.parametrize("fmt,sgc", [("b4", 1), ("b5", 1), ("b6", 1), ("nf4", 2), ("nf4", 1), ("nf3", 2), ("nf5", 2)])
+@pytest.mark.parametrize("cols,rows", [(3584, 70), (2560, 130), (18944, 36), (4736, 513)])
+def test_wide_ragged_matrices_bit_exact(ctx, oracle, fmt, sgc, cols, rows):
+    """Several pass tiles with a ragged last one (56 = 32 + 24 chunks, 40 = 32 + 8, 296 = 9 x 32 + 8, 74 = 64 + 10),
+    rows that are no multiple of 4, scale groups of two chunks: 1 and 4 tokens per launch against the oracle."""
+    if fmt[0] == "b":
+        m = random_bipolar(oracle, rows + cols, rows, cols, int(fmt[1]))
+    elif fmt == "nf5":
+        m = random_nf(oracle, rows + cols, rows, cols, 5, sgc, np.array(NF5_POS, np.int8))
+    else:
+        m = random_nf(oracle, rows + cols, rows, cols, int(fmt[2]), sgc)
+    x = normal(rows, (4, cols))
+    x[2, 64 * 33:64 * 34] = 0.0                      # a zero chunk in the second pass (skipped by the chain)
+    act = oracle.act_populate_fwht(x)
+    dm = upload(ctx, m)
+    try:
+        one = ctx.gemv(dm, act.q[0], act.scales[0], act.sums[0])
+        four, dots = ctx.gemv(dm, act.q, act.scales, act.sums, want_dots=True)
+    finally:
+        dm.free()
+    want, want_dots = oracle.gemv(m, act, want_dots=True, threads=8)
+    assert np.array_equal(dots, want_dots)
+    assert np.array_equal(four, want) and np.array_equal(one[0], want[0])
+
+
 @pytest.mark.parametrize("fmt", ["b4", "b5", "b6", "nf4g128", "nf3g128"])
 @pytest.mark.parametrize("cols,rows", [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)])
 def test_sweep_shapes_bit_exact(ctx, oracle, fmt, cols, rows):
