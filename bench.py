@@ -355,6 +355,11 @@ def run_b200(args, rank, world, local_rank):
                 decode["models"] = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
             except Exception as exc:      # the headline line must still come out; the failure is reported in it
                 decode["models_error"] = f"{type(exc).__name__}: {exc}"
+        if not args.no_decode_moe:
+            try:
+                decode["moe"] = decode_moe(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+            except Exception as exc:
+                decode["moe_error"] = f"{type(exc).__name__}: {exc}"
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -560,6 +565,41 @@ def decode_models(ctx, timed_region, rank, world, dist):
     return out
 
 
+def decode_moe(ctx, timed_region, rank, world, dist):
+    """Whole-token decode of the Qwen3-30B-A3B shape (48 layers, 128 experts of 768, top-8, nf3 experts, nf4g128 attention;
+    random codes), expert-parallel over all ranks: rank r holds the experts e % world == r, the partial weighted sums are
+    exchanged inside the norm kernel after every MoE block."""
+    import numpy as np
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(29))
+    cfg = dict(synth.QWEN3_30B_A3B)
+    t0 = time.perf_counter()
+    spec = synth.random_model(cfg, "nf4g128", seed=9, untied=True, share_layers=True, ep=(world, rank),
+                              moe=dict(n_experts=128, top_k=8, d_ff=768, bits=3, sgc=1))
+    eng = k2.Engine(ctx, spec)
+    build_s = time.perf_counter() - t0
+    if world > 1:
+        handles = [None] * world
+        dist.all_gather_object(handles, eng.tp_handle())
+        eng.tp_attach(handles)
+        dist.barrier()
+    steps = 32
+    _prefill(eng, rng, cfg["vocab"], 0, 16)
+    prefill = _prefill(eng, rng, cfg["vocab"], 0, 512 - steps, timed_region)
+    out = {"model": "Qwen3-30B-A3B-shaped (hidden 2048, 48 layers, 32q/4kv heads of 128, 128 experts of 768, top-8, vocab 151936), "
+                    "nf3 experts, nf4g128 attention", "kv": "int8", "ep": world, "build_s": round(build_s, 1),
+           "prefill_tok_s_480": prefill, "weight_bytes_per_token": eng.weight_bytes,
+           "exchange": None if world == 1 else "1 partial-sum exchange per MoE block inside the norm kernel (peer memory, no NCCL on the data path)"}
+    for name, pos in (("ctx_512", 512 - steps), ("ctx_6600", 6600)):
+        eng.decode_greedy(1, pos, 4)
+        ms = min(timed_region(lambda: eng.decode_greedy(1, pos, steps)) for _ in range(2))
+        out[name] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps]}
+    out["ctx_6600"]["note"] = "cache rows 480..6599 are zero: kernel time does not depend on the cached values"
+    eng.close()
+    return out
+
+
 def run_decode_only(args, local_rank):
     """Small whole-token run for profilers: engine of the chosen shape, 16-token prompt, then N greedy steps starting at
     position --decode-ctx (positions in between stay zero: kernel time does not depend on the cached values)."""
@@ -574,6 +614,9 @@ def run_decode_only(args, local_rank):
     if args.decode_model == "1.7b":
         cfg = dict(synth.SMOLLM2_1_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
         spec = synth.random_model(cfg, "nf4g128", seed=5, share_layers=True)
+    elif args.decode_model == "moe":
+        cfg = dict(synth.QWEN3_30B_A3B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1, layers=args.decode_layers or 48)
+        spec = synth.random_model(cfg, "nf4g128", seed=9, untied=True, share_layers=True, moe=dict(n_experts=128, top_k=8, d_ff=768, bits=3, sgc=1))
     elif args.decode_model == "7b":
         cfg = dict(synth.QWEN2_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
         spec = synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, share_layers=True)
@@ -658,10 +701,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode measurement")
+    ap.add_argument("--no-decode-moe", action="store_true", help="skip the sparse-MoE (30B-A3B-shaped) decode measurement")
     ap.add_argument("--no-decode-models", action="store_true", help="skip the 1.7B / 7B-shaped decode measurements")
     ap.add_argument("--decode-only", type=int, default=0, metavar="N",
                     help="profiling mode: only the whole-token engine - a 16-token prompt, then N greedy steps")
-    ap.add_argument("--decode-model", default="135m", choices=["135m", "1.7b", "7b"], help="--decode-only: model shape")
+    ap.add_argument("--decode-model", default="135m", choices=["135m", "1.7b", "7b", "moe"], help="--decode-only: model shape")
+    ap.add_argument("--decode-layers", type=int, default=0, help="--decode-only, moe: fewer layers than the shape's 48 (profiling)")
     ap.add_argument("--decode-ctx", type=int, default=15, help="--decode-only: position of the first greedy step")
     ap.add_argument("--kv-bits", type=int, default=8, choices=[4, 8], help="--decode-only: KV cache format")
     ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")

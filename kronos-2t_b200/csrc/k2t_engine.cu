@@ -50,7 +50,8 @@ struct KronosCudaEngine {
     uint32_t n_split = 32;
     uint32_t kv_stride = 0;                   // cache positions per (layer, kv head): max_seq_len rounded up to 32, so every 32-position tile of rows and scales starts on 16 bytes
     // sparse-MoE workspace: normalised hidden state, per-route expert buffers
-    float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr;
+    float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr, *router_logits = nullptr;
+    uint32_t *router_done = nullptr;
     int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
     bool has_moe = false;
     // tensor parallel: exchange buffer (data[2][tp][slot] floats + flags[tp]) and the peers' mappings
@@ -199,7 +200,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 RouterArgs ra{};
                 ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm + (size_t)t * h;
                 ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
-                ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32;
+                ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32; ra.logits = e->router_logits; ra.done = e->router_done;
                 if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
                 if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
                                                   e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert gate_up")) return false;
@@ -556,7 +557,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     }
     if (ok && e->has_moe) {
         const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
-        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->moe_gu, (size_t)k * 2 * dff) &&
+        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->router_logits, 256) && dev_alloc(e, e->router_done, 1) && dev_alloc(e, e->moe_gu, (size_t)k * 2 * dff) &&
              dev_alloc(e, e->moe_out, (size_t)k * h) && dev_alloc(e, e->moe_q, (size_t)k * dff) &&
              dev_alloc(e, e->moe_s, (size_t)k * dff / 64) && dev_alloc(e, e->moe_m, (size_t)k * dff / 64);
     }

@@ -153,34 +153,47 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
 // as in the CPU restatement these kernels are compared with.
 __device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x); }
 
-// Router: one CTA.  Logits in the accumulator order of dot_f32_moe_neon (16 fma lanes over 16-element strides,
-// (a0+a1)+(a2+a3), pairwise): half a warp per expert.  Softmax over all experts with a sequential sum, top-k by
-// insertion with strict '>' (select_topk_by_score), optional renormalisation, sort by expert id: one thread,
-// a few thousand operations.
-constexpr uint32_t ROUTER_THREADS = 512, ROUTER_MAX_EXPERTS = 256, ROUTER_MAX_TOPK = 32;
+// Router.  Logits in the accumulator order of dot_f32_moe_neon (16 fma lanes over 16-element strides, (a0+a1)+(a2+a3),
+// pairwise): half a warp per expert, eight experts per CTA, so the router matrix streams through many SMs at once (one
+// CTA took 65 us for 128 experts of 2048).  The CTA that finishes last (device counter) does the small sequential part:
+// softmax over all experts with the sum in expert order, top-k by rank (score descending, the earlier expert first among
+// equals - what select_topk_by_score's strict '>' insertion produces), optional renormalisation in that order, sort by id.
+constexpr uint32_t ROUTER_THREADS = 128, ROUTER_MAX_EXPERTS = 256, ROUTER_MAX_TOPK = 32;
+constexpr uint32_t ROUTER_EXPERTS_PER_CTA = ROUTER_THREADS / 16;
 __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const RouterArgs a) {
     extern __shared__ float s_xr[];          // hidden floats
     __shared__ float s_z[ROUTER_MAX_EXPERTS];
+    __shared__ float s_sel_w[ROUTER_MAX_TOPK];
+    __shared__ uint32_t s_sel_e[ROUTER_MAX_TOPK];
     __shared__ float s_max;
+    __shared__ uint32_t s_last;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = lane >> 4, l16 = lane & 15;
     pdl_wait();
     pdl_trigger();
     for (uint32_t i = tid; i < a.hidden; i += ROUTER_THREADS) s_xr[i] = __ldcg(a.x + i);
     __syncthreads();
-    for (uint32_t e0 = warp * 2; e0 < a.n_experts; e0 += (ROUTER_THREADS / 32) * 2) {
-        const uint32_t e = e0 + half;
+    {
+        const uint32_t e = blockIdx.x * ROUTER_EXPERTS_PER_CTA + warp * 2 + half;
         float acc = 0.0f;
         if (e < a.n_experts) {
             const float *row = a.w + (size_t)e * a.hidden;
-#pragma unroll 8
+#pragma unroll 16
             for (uint32_t i = l16; i < a.hidden; i += 16) acc = __fmaf_rn(__ldg(row + i), s_xr[i], acc);
         }
         float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));      // within each half: lanes 0..3 and 8..11
         t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 8));
         t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 1));
         t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2));
-        if (l16 == 0 && e < a.n_experts) s_z[e] = a.bias != nullptr ? __fadd_rn(t, __ldg(a.bias + e)) : t;
+        if (l16 == 0 && e < a.n_experts) a.logits[e] = a.bias != nullptr ? __fadd_rn(t, __ldg(a.bias + e)) : t;
     }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.done, 1u) + 1u == gridDim.x ? 1u : 0u;
+    __syncthreads();
+    if (s_last == 0) return;
+    __threadfence();
+    if (tid == 0) *a.done = 0;               // ready for the next launch (launches of a stream do not overlap here)
+    for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __ldcg(a.logits + e);
     __syncthreads();
     if (warp == 0) {
         float m = -INFINITY;
@@ -195,29 +208,32 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
         else if (a.scoring == 2) s_z[e] = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_cr(-s_z[e])));
     }
     __syncthreads();
-    if (tid == 0) {
-        float inv_all = 1.0f;
-        if (a.scoring == 0) {
+    if (a.scoring == 0) {
+        if (tid == 0) {
             float sum = 0.0f;
             for (uint32_t e = 0; e < a.n_experts; ++e) sum = __fadd_rn(sum, s_z[e]);
-            inv_all = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)a.n_experts);
+            s_max = sum > 0.0f ? __fdiv_rn(1.0f, sum) : __fdiv_rn(1.0f, (float)a.n_experts);
         }
-        const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
+        __syncthreads();
+        const float inv_all = s_max;
+        for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __fmul_rn(s_z[e], inv_all);
+        __syncthreads();
+    }
+    const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
+    for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) {       // rank of expert e in the descending order
+        const float sc = s_z[e];
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < a.n_experts; ++j) {
+            const float sj = s_z[j];
+            rank += (sj > sc || (sj == sc && j < e)) ? 1u : 0u;
+        }
+        if (rank < k) { s_sel_e[rank] = e; s_sel_w[rank] = sc; }
+    }
+    __syncthreads();
+    if (tid == 0) {
         uint32_t ids[ROUTER_MAX_TOPK];
         float w[ROUTER_MAX_TOPK];
-        uint32_t len = 0;
-        for (uint32_t e = 0; e < a.n_experts; ++e) {
-            const float sc = a.scoring == 0 ? __fmul_rn(s_z[e], inv_all) : s_z[e];
-            if (len < k) {
-                uint32_t pos = len;
-                while (pos > 0 && sc > w[pos - 1]) { ids[pos] = ids[pos - 1]; w[pos] = w[pos - 1]; --pos; }
-                ids[pos] = e; w[pos] = sc; ++len;
-            } else if (sc > w[k - 1]) {
-                uint32_t pos = k - 1;
-                while (pos > 0 && sc > w[pos - 1]) { ids[pos] = ids[pos - 1]; w[pos] = w[pos - 1]; --pos; }
-                ids[pos] = e; w[pos] = sc;
-            }
-        }
+        for (uint32_t i = 0; i < k; ++i) { ids[i] = s_sel_e[i]; w[i] = s_sel_w[i]; }
         if (a.scoring == 1) {                 // k-way softmax over the selected logits, in selection order
             float max_z = -INFINITY, sum = 0.0f;
             for (uint32_t i = 0; i < k; ++i) max_z = fmaxf(max_z, w[i]);
@@ -812,7 +828,8 @@ cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl) {
         cudaError_t e = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_kernel(moe_router_kernel, dim3(1), dim3(ROUTER_THREADS), smem, s, pdl, a);
+    if (a.logits == nullptr || a.done == nullptr) return cudaErrorInvalidValue;
+    return launch_kernel(moe_router_kernel, dim3((a.n_experts + ROUTER_EXPERTS_PER_CTA - 1) / ROUTER_EXPERTS_PER_CTA), dim3(ROUTER_THREADS), smem, s, pdl, a);
 }
 cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
                                        int32_t *sums, bool pdl) {

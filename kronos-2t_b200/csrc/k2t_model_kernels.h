@@ -78,6 +78,8 @@ struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scorin
     uint32_t scoring;            // MoeRouterScoring tag: 0 softmax over all experts, 1 top-k softmax, 2 sigmoid
     uint32_t *route_ids;         // out: [top_k] expert ids, ascending
     float *route_w;              // out: [top_k]
+    float *logits;               // scratch: [n_experts] router logits (device)
+    uint32_t *done;              // scratch: CTAs that have written their logits (zero between launches)
 };
 
 // pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).

@@ -91,13 +91,41 @@ def random_bf16(seed, n, lo=0x3800, hi=0x3C00):
     return (rng.integers(lo, hi, n, dtype=np.uint16) | (rng.integers(0, 2, n, dtype=np.uint16) << 15)).astype(np.uint16)
 
 
-def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp=(1, 0), share_layers=False):
+QWEN3_30B_A3B = dict(hidden=2048, layers=48, n_q=32, n_kv=4, head_dim=128, inter=768, vocab=151936, max_seq=6600 + 64, eps=1e-6, theta=1e6)
+
+
+def random_moe(seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk=True):
+    """One sparse-MoE FFN with random expert codes in the reference's .k2tm record form (nf_expert_byte_layout,
+    src/model/moe_800b.rs): codebooks at bytes 0 / 16, the gate_up pair stream at 64, the down pair stream at the next
+    multiple of 64, records padded to 16 KiB; router weights N(0, 0.02) (near-uniform routing)."""
+    cb = _NF_CHUNK[bits]
+    gu_chunks, dn_chunks = hidden // 64, d_ff // 64
+    gu_bytes = (2 * d_ff // 32) * (-(-gu_chunks // sgc) * 64 + gu_chunks * 2 * cb)
+    dn_bytes = (hidden // 32) * (-(-dn_chunks // sgc) * 64 + dn_chunks * 2 * cb)
+    gu_off, dn_off = 64, (64 + gu_bytes + 63) // 64 * 64
+    rec = (dn_off + dn_bytes + 16383) // 16384 * 16384
+    shard = np.zeros(n_experts * rec, np.uint8)
+    book = (NF4_DEFAULT if bits == 4 else NF3_DEFAULT).view(np.uint8)
+    for e in range(n_experts):
+        r = shard[e * rec:(e + 1) * rec]
+        r[0:16] = book
+        r[16:32] = book
+        r[gu_off:gu_off + gu_bytes] = random_nf_bytes(seed * 1009 + 2 * e, 2 * d_ff, hidden, bits, sgc)[0]
+        r[dn_off:dn_off + dn_bytes] = random_nf_bytes(seed * 1009 + 2 * e + 1, hidden, d_ff, bits, sgc)[0]
+    router = (_rng(seed * 1009 + 7).standard_normal((n_experts, hidden)) * 0.02).astype(np.float32)
+    return dict(router_w=router, router_bias=None, n_experts=n_experts, top_k=top_k, norm_topk=norm_topk, d_ff=d_ff, bits=bits, sgc=sgc,
+                shard=shard, expert_bytes=rec, scoring=0)
+
+
+def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp=(1, 0), share_layers=False, moe=None, ep=(1, 0)):
     """Engine spec of a dense Llama-shaped model with random codes (decode time does not depend on the values).
 
     modes: per-matrix formats {qkv, o, gate_up, down, head} overriding `mode`.  tp = (size, rank): the rank-local
     spec of a tensor-parallel group, generated directly in the rank's shapes (what kronos_2t_b200.tp.shard_spec cuts
     out of a whole model); tensor-parallel specs use an untied embedding table.  share_layers: every layer points at
-    layer 0's host arrays (each still becomes its own device copy), which keeps multi-billion-parameter specs quick to make."""
+    layer 0's host arrays (each still becomes its own device copy), which keeps multi-billion-parameter specs quick to make.
+    moe: dict(n_experts, top_k, d_ff, bits, sgc) - every layer gets a sparse-MoE FFN (random_moe) instead of the dense MLP;
+    ep = (size, rank): expert-parallel rank (the whole spec; the engine keeps the experts e % size == rank)."""
     c = dict(cfg)
     tp_size, tp_rank = tp
     md = dict(qkv=mode, o=mode, gate_up=mode, down=mode, head=mode)
@@ -110,6 +138,8 @@ def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp
         c.update(tp_size=tp_size, tp_rank=tp_rank, vocab_total=vocab_total, o_chunk0=tp_rank * c["n_q"] * hd // 64,
                  down_chunk0=tp_rank * c["inter"] // 64)
         untied = True
+    if ep[0] > 1:
+        c.update(ep_size=ep[0], ep_rank=ep[1])
     inter = c["inter"]
     q_dim, kv_dim = c["n_q"] * hd, c["n_kv"] * hd
     layers = []
@@ -121,9 +151,13 @@ def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp
         bias = None
         if qkv_bias:
             bias = (_rng(s + 5).standard_normal(q_dim + 2 * kv_dim) * 0.02).astype(np.float32)
-        layers.append(dict(input_norm=np.ones(h, np.float32), post_norm=np.ones(h, np.float32), qkv_bias=bias, q_norm=None, k_norm=None,
-                           qkv=random_matrix(s + 1, q_dim + 2 * kv_dim, h, md["qkv"]), o=random_matrix(s + 2, h, q_dim, md["o"]),
-                           gate_up=random_matrix(s + 3, 2 * inter, h, md["gate_up"]), down=random_matrix(s + 4, h, inter, md["down"])))
+        ly = dict(input_norm=np.ones(h, np.float32), post_norm=np.ones(h, np.float32), qkv_bias=bias, q_norm=None, k_norm=None,
+                  qkv=random_matrix(s + 1, q_dim + 2 * kv_dim, h, md["qkv"]), o=random_matrix(s + 2, h, q_dim, md["o"]))
+        if moe:
+            ly["moe"] = random_moe(s + 6, h, moe["n_experts"], moe["top_k"], moe["d_ff"], moe["bits"], moe["sgc"])
+        else:
+            ly.update(gate_up=random_matrix(s + 3, 2 * inter, h, md["gate_up"]), down=random_matrix(s + 4, h, inter, md["down"]))
+        layers.append(ly)
     embed = None
     if untied:       # a 4096-row random block, repeated
         blk = random_bf16(seed * 100003 + 8, min(vocab_total, 4096) * h)
