@@ -9,8 +9,9 @@ A step = one pass over the sweep at batch 1: for every K x N shape (2048x2048, 2
   value     GB/s of algorithmic bytes (reference file-format weight bytes + activations + outputs)
             with inputs resident in HBM; whole-job aggregate over all ranks (each rank runs its own
             independent sweep: weak scaling, no collective on the data path).
-  e2e       same metric through the host-buffer C-ABI call kronos_cuda_linear (pinned host vectors,
-            H2D + kernels + D2H inside the timed region).
+  e2e       same metric through the host-buffer C-ABI calls (pinned host vectors; H2D + kernels + D2H inside the timed
+            region): the sixteen independent projections of a pass queued with kronos_cuda_linear_async and waited for
+            once; `sync_per_call` is the same pass with the blocking kronos_cuda_linear.
   roofline  GEMV kernels of the sweep timed one by one with CUDA events (aggregate and per case).
   cpu_baseline  the CPU oracle (a C++ port of the reference CPU path) on one pass, all host threads.
 
@@ -244,8 +245,11 @@ def run_b200(args, rank, world, local_rank):
             ctx.gemv_dev(c["dm"], pq, ps, pm, 1, po)
 
     def step_e2e():
+        # host buffers in, host buffers out: the sixteen projections of a pass are independent, so they are queued with
+        # kronos_cuda_linear_async (copy in, rotate + quantize, GEMV, copy out, each) and waited for once
         for c in cases:
-            ctx.linear_ptr(c["dm"], c["x_host"].data_ptr(), 1, c["out_host"].data_ptr())
+            ctx.linear_async_ptr(c["dm"], c["x_host"].data_ptr(), 1, c["out_host"].data_ptr())
+        ctx.synchronize()
 
     def barrier():
         torch.cuda.synchronize()
@@ -291,11 +295,18 @@ def run_b200(args, rank, world, local_rank):
     gpu_launches = launches_per_step * args.steps
     value = bytes_per_step * world * args.steps / (ms / 1e3) / 1e9
 
+    def step_e2e_sync():
+        for c in cases:
+            ctx.linear_ptr(c["dm"], c["x_host"].data_ptr(), 1, c["out_host"].data_ptr())
+
     for _ in range(3):
         step_e2e()
+        step_e2e_sync()
     e2e_steps = min(args.steps, 50)
     ms_e2e, _ = timed(step_e2e, e2e_steps)
     e2e_value = bytes_per_step * world * e2e_steps / (ms_e2e / 1e3) / 1e9
+    ms_e2e_sync, _ = timed(step_e2e_sync, e2e_steps)
+    e2e_sync_value = bytes_per_step * world * e2e_steps / (ms_e2e_sync / 1e3) / 1e9
     h2d = sum(c["m"]["cols"] * 4 for c in cases)
     d2h = sum(c["m"]["rows"] * 4 for c in cases)
 
@@ -376,7 +387,10 @@ def run_b200(args, rank, world, local_rank):
                        "per_rank": "each rank runs its own sweep (replicas, no collective)"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "form": "16 x kronos_cuda_linear_async + 1 x kronos_cuda_synchronize per step",
+                    "sync_per_call": {"value": e2e_sync_value, "unit": "GB/s", "ms_per_step": ms_e2e_sync / e2e_steps,
+                                      "form": "16 x kronos_cuda_linear (each call waits for its result)"}},
             "gpu_launches": int(gpu_launches),
             "roofline": roofline, "cpu_baseline": cpu, "decode": decode,
         }))

@@ -122,6 +122,13 @@ int32_t kronos_cuda_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, cons
  * out[n_tok][rows] fp32.  This is the host-buffer call the benchmark's end-to-end number uses. */
 int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x,
                            size_t n_tok, float *out);
+/* The same call without the final wait: copies and kernels are queued on the context's stream and the call returns.
+ * x and out must stay valid (and should be page-locked, or the copies are staged synchronously) until
+ * kronos_cuda_synchronize(ctx), which also reports a device-side failure of any queued call.  Calls queue in order,
+ * so independent projections (a host that evaluates several matrices before it needs any result) overlap their
+ * copies with one another's kernels.  No counterpart in the reference (its CPU LinearBackend::forward is synchronous). */
+int32_t kronos_cuda_linear_async(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x,
+                                 size_t n_tok, float *out);
 
 /* ---- kernels, device buffers (no copies; pointers are device addresses on ctx's device) ---- */
 

@@ -283,7 +283,7 @@ int32_t kronos_cuda_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, cons
     return sync_and_check(ctx, "gemv") ? 0 : -1;
 }
 
-int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out) {
+static int32_t linear_impl(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out, bool wait) {
     if (!ctx) return -1;
     ctx->err.clear();
     if (!m) return fail(ctx, "linear: matrix is NULL"), -1;
@@ -305,7 +305,16 @@ int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, co
                   (float *)ctx->out.p, g.rows, nullptr))
         return -1;
     if (!cuda_ok(ctx, cudaMemcpyAsync(out, ctx->out.p, n_out * 4, cudaMemcpyDeviceToHost, s), "copy out")) return -1;
+    if (!wait) return 0;
     return sync_and_check(ctx, "linear") ? 0 : -1;
+}
+
+int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out) {
+    return linear_impl(ctx, m, x, n_tok, out, true);
+}
+
+int32_t kronos_cuda_linear_async(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out) {
+    return linear_impl(ctx, m, x, n_tok, out, false);
 }
 
 }  // extern "C"

@@ -78,6 +78,7 @@ def load_library():
     sig("kronos_cuda_fwht_quant", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
     sig("kronos_cuda_gemv", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
     sig("kronos_cuda_linear", i32, vp, vp, vp, sz, vp)
+    sig("kronos_cuda_linear_async", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_fwht_quant_dev", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
     sig("kronos_cuda_linear_noalloc", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_gemv_dev", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
@@ -255,6 +256,10 @@ class Context:
     def linear_ptr(self, mat, x_ptr, n_tok, out_ptr):
         """kronos_cuda_linear on raw host addresses (e.g. pinned torch tensors)."""
         self._check(self.L.kronos_cuda_linear(self.handle, mat.handle, x_ptr, n_tok, out_ptr))
+
+    def linear_async_ptr(self, mat, x_ptr, n_tok, out_ptr):
+        """kronos_cuda_linear_async: queued, no wait; call synchronize() before reading the output."""
+        self._check(self.L.kronos_cuda_linear_async(self.handle, mat.handle, x_ptr, n_tok, out_ptr))
 
     # ---- device-buffer kernels
     def fwht_quant_dev(self, d_x, n_tok, cols, d_q, d_scales, d_sums, d_norm_w=None, d_inv_rms=None, chunk0=0):

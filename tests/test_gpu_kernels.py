@@ -239,3 +239,24 @@ def test_errors_are_reported_not_swallowed(ctx, oracle):
     before = ctx.launch_count
     ctx.fwht_quant(normal(2, 64))
     assert ctx.launch_count == before + 1
+
+
+def test_linear_async_equals_linear(ctx, oracle):
+    """Queued host-buffer calls (one wait at the end) give the bits of the synchronous call, in any interleaving of matrices."""
+    import torch
+    mats = [random_bipolar(oracle, 5, 130, 576, 5), random_nf(oracle, 6, 96, 2560, 4, 2), random_bipolar(oracle, 7, 64, 192, 4)]
+    dms = [upload(ctx, m) for m in mats]
+    try:
+        xs = [torch.from_numpy(normal(10 + i, m.cols).astype(np.float32)).pin_memory() for i, m in enumerate(mats)]
+        want = [ctx.linear(dm, x.numpy()) for dm, x in zip(dms, xs)]
+        outs = [torch.empty(m.rows, dtype=torch.float32).pin_memory() for m in mats]
+        for _ in range(3):
+            for dm, x, out in zip(dms, xs, outs):
+                ctx.linear_async_ptr(dm, x.data_ptr(), 1, out.data_ptr())
+        ctx.synchronize()
+        for w, out in zip(want, outs):
+            assert np.array_equal(w.reshape(-1), out.numpy())
+    finally:
+        for dm in dms:
+            dm.free()
+
