@@ -137,3 +137,21 @@ def test_expert_parallel_emulation_matches_the_whole_model(oracle, moe, ep):
         m.close()
     whole.close()
 
+
+def test_synthetic_moe_records_follow_the_reference_layout(oracle):
+    """kronos_2t_b200.synth.random_moe writes .k2tm expert records the oracle parses: record size and offsets equal
+    nf_expert_byte_layout, and a model built from them runs (finite logits, top-k routes in ascending expert order)."""
+    from kronos_2t_b200 import synth
+    for hidden, d_ff, bits, sgc in [(2048, 768, 3, 1), (256, 128, 4, 2), (128, 64, 3, 2)]:
+        lay = oracle.nf_expert_layout(hidden, d_ff, bits, sgc)
+        m = synth.random_moe(3, hidden, 2, 1, d_ff, bits, sgc)
+        assert m["expert_bytes"] == lay["expert_bytes"] and m["shard"].size == 2 * lay["expert_bytes"]
+    cfg = dict(hidden=128, layers=2, n_q=4, n_kv=2, head_dim=64, inter=64, vocab=320, max_seq=32, eps=1e-6, theta=1e6)
+    spec = synth.random_model(cfg, "nf4g128", seed=2, moe=dict(n_experts=8, top_k=3, d_ff=64, bits=3, sgc=1), ep=(2, 1))
+    assert spec["cfg"]["ep_size"] == 2 and spec["cfg"]["ep_rank"] == 1
+    ref = oracle.Model(spec)
+    logits = ref.forward_token(5)
+    ids, w = ref.last_routes(0)
+    assert np.isfinite(logits).all() and len(ids) == 3 and list(ids) == sorted(ids) and abs(float(w.sum()) - 1.0) < 1e-5
+    ref.close()
+
