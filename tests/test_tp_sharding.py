@@ -142,7 +142,7 @@ def test_synthetic_moe_records_follow_the_reference_layout(oracle):
     """kronos_2t_b200.synth.random_moe writes .k2tm expert records the oracle parses: record size and offsets equal
     nf_expert_byte_layout, and a model built from them runs (finite logits, top-k routes in ascending expert order)."""
     from kronos_2t_b200 import synth
-    for hidden, d_ff, bits, sgc in [(2048, 768, 3, 1), (256, 128, 4, 2), (128, 64, 3, 2)]:
+    for hidden, d_ff, bits, sgc in [(2048, 768, 3, 1), (256, 128, 4, 2), (256, 128, 3, 2)]:
         lay = oracle.nf_expert_layout(hidden, d_ff, bits, sgc)
         m = synth.random_moe(3, hidden, 2, 1, d_ff, bits, sgc)
         assert m["expert_bytes"] == lay["expert_bytes"] and m["shard"].size == 2 * lay["expert_bytes"]
