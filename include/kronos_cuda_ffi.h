@@ -109,7 +109,8 @@ int32_t kronos_cuda_fwht_quant(KronosCudaContext *ctx, const float *x, size_t n_
                                int8_t *q, float *scales, int32_t *sums);
 
 /* nibble4_sdot_stripe_range_raw (simd_lut.rs:3536-3582) / nf_sdot_stripe_range_raw (5687-5760) for
- * n_tok = 1 and the batch forms (4101-4331, 6689-7029) for n_tok <= 8, over all rows:
+ * n_tok = 1 and the batch forms (4101-4331, 6689-7029) for any n_tok >= 1 (one weight pass serves up to 4 tokens;
+ * longer batches are split into such passes inside the call), over all rows:
  * out[t*out_stride + r] = sum over chunks of fmaf((float)dot*xs, w_scale, acc), ascending chunks,
  * chunks with xs == 0 skipped.  int_dots (optional, [n_tok][rows][cols/64]) receives the exact
  * int32 chunk dots (bipolar: 2*sum(u*q) - (2^B-1)*xsum; NF: sum(cb[idx]*q)). xsum may be NULL for NF. */
@@ -147,6 +148,9 @@ typedef struct KronosCudaEngine KronosCudaEngine;
  * receives them through `cfg`, plus the KV format (kv_bits: 8 = int8 Hadamard cache, 4 = NF4 Hadamard cache as
  * selected by RealLlamaEngine::set_kv_bits, real_llm.rs:1731-1735). */
 typedef struct KronosCudaEngineConfig {
+    /* sizeof(KronosCudaEngineConfig) as the caller compiled it: kronos_cuda_engine_create refuses any other value, so
+     * a binding written against an older or shorter layout fails with a message instead of being read past its end. */
+    uint32_t struct_size;
     uint32_t hidden_size, num_layers, num_attention_heads, num_key_value_heads, head_dim,
              intermediate_size, vocab_size, max_seq_len;
     float rms_norm_eps;
@@ -172,7 +176,20 @@ typedef struct KronosCudaEngineConfig {
      * in rank order inside the norm kernel that follows the MoE block (the exchange of kronos_cuda_engine_tp_handle /
      * _tp_attach, with ep_size handles).  Zero / ep_size <= 1 for one device; not combined with tp_size > 1. */
     uint32_t ep_size, ep_rank;
+    /* Sliding-window + attention-sink KV ring (RealLlamaEngine::set_kv_sliding_window, real_llm.rs:1764-1790, as try_new
+     * receives kv_window / kv_sinks, metal_gpu.rs:1196-1206): kv_window = 0 keeps the full causal context; otherwise
+     * (>= 8) a token attends to the first kv_sinks positions and the last kv_window - kv_sinks ones, and cache rows live
+     * in a ring (QuantKvRawPtrs::slot_of_pos, real_llm.rs:1116-1122).  kronos_cuda_engine_reconfigure_kv changes both. */
+    uint32_t kv_window, kv_sinks;
+    /* KRONOS_CUDA_ENGINE_* bits */
+    uint32_t flags;
 } KronosCudaEngineConfig;
+
+/* flags: contexts longer than 512 positions are attended in the reference's summation order by default (logits and
+ * greedy streams identical to the CPU path at any length).  With this bit the split-KV kernel serves them instead:
+ * exact scores, partial sums merged in split order, so outputs agree with the CPU path to fp32 rounding only - faster
+ * at long contexts, not bit-identical.  No counterpart in the reference. */
+#define KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION 1u
 
 /* One decoder layer as borrowed from the host engine: counterpart of LayerBorrow
  * (src/backend/metal_gpu.rs:428-439).  Optional vectors are NULL when absent.  qkv_proj is the row
@@ -258,6 +275,17 @@ int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *engine, uint32_t layer, 
  * (activation prologue done / GEMV done / grid barrier passed; the attention phase has two marks).  Returns
  * the number of marks written (0 when that kernel is not in use).  No counterpart in the reference. */
 size_t kronos_cuda_engine_decode_trace(KronosCudaEngine *engine, uint64_t *marks_ns, size_t cap);
+/* Per-kernel-class timing of one greedy decode step (the CUDA counterpart of the Metal backend's KRONOS_DECODE_PROF
+ * table, src/backend/metal_gpu.rs:963-1027): the step for `token` is launched kernel by kernel with a timing event after
+ * every kernel, `reps` times (positions pos, pos + 1, ...), without programmatic overlap, so each kernel is timed alone on
+ * a warm device.  Writes a text table (kernel class | launches per step | us per step | avg us | share) into table[cap]
+ * (NUL-terminated, truncated to cap) and returns its full length, -1 on error.  The KV cache rows at pos .. pos + reps - 1
+ * are overwritten.  With KRONOS_CUDA_DECODE_PROF=1 in the environment kronos_cuda_engine_decode_greedy prints this
+ * table for its last position to stderr. */
+int64_t kronos_cuda_engine_profile_step(KronosCudaEngine *engine, uint32_t token, size_t pos, uint32_t reps, char *table, size_t cap);
+/* Diagnostic: 32 words the kernels of layer 0 leave when KRONOS_CUDA_ATTN_TRACE=1 was set at engine creation (SM clock
+ * readings of query head 0 at the phase boundaries of the attention kernel).  No counterpart in the reference. */
+size_t kronos_cuda_engine_debug_words(KronosCudaEngine *engine, uint64_t *out, size_t cap);
 /* Diagnostic: one KV cache entry (layer, kv head, position): k_q8/v_q8[head_dim] rotated int8 values and
  * their fp32 scales - the contents of the reference's k_q8 / k_scales / v_q8 / v_scales slot
  * (KvCache, real_llm.rs:8303-8365). */

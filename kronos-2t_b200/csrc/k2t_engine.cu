@@ -5,13 +5,18 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
+#include <map>
 #include <new>
+#include <string>
 #include <vector>
 
 #include "k2t_context.h"
 #include "k2t_decode_mega.h"
+#include "k2t_gemv_fused.h"
 #include "k2t_model_kernels.h"
+#include "k2t_prologue.cuh"
 #include "k2t_tp.h"
 
 using namespace k2t;
@@ -64,6 +69,8 @@ struct KronosCudaEngine {
     KronosCudaMatrix *embed_matrix = nullptr; // whole lm_head for the token lookup (tied embeddings under tp)
     uint32_t last_row = 0;                    // row of `hidden` that holds the last forwarded token (prompt batches)
     bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
+    bool fused = false;                       // single-token steps: norm / SwiGLU / embedding run as prologues of the GEMV that consumes them (KRONOS_CUDA_FUSED=1)
+    const float *final_hidden = nullptr;      // where the last step left the residual stream of its last token
     size_t weight_bytes = 0;
     std::vector<void *> allocs;
     // whole-token decode kernel (contexts up to ATTN_EXACT_CTX positions)
@@ -78,6 +85,12 @@ struct KronosCudaEngine {
     size_t mega_smem = 0;
     cudaGraphExec_t graphs[4] = {nullptr, nullptr, nullptr, nullptr};      // [greedy ? 0 : 1][long context ? 1 : 0] -> 2 * ids + long
     cudaStream_t graph_stream = nullptr;      // the stream the graphs were captured on
+    // per-kernel-class timing of one step (kronos_cuda_engine_profile_step): while prof_on, every launch is followed
+    // by an event record, so a captured step carries one event node per kernel
+    bool prof_on = false;
+    std::vector<std::pair<const char *, cudaEvent_t>> prof_marks;
+    unsigned long long *d_dbg = nullptr;      // 32 diagnostic words (phase clocks of the attention kernel, layer 0)
+    bool attn_trace = false;
 };
 
 namespace {
@@ -94,17 +107,24 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
 }
 
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
-bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, uint32_t n_tok = 1, size_t act_tok0 = 0) {
+bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 1);
+
+bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char *what, uint32_t n_tok = 1, size_t act_tok0 = 0) {
     uint32_t launched = 0;
     const size_t cols = m->dm.geom.cols, nc = cols / 64;
     cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q + act_tok0 * cols, e->act_s + act_tok0 * nc, e->act_m + act_tok0 * nc, n_tok, out,
                                   m->dm.geom.rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
-    e->ctx->launches += launched;
-    return cuda_ok(e->ctx, err, "engine gemv");
+    return count(e, err, what, launched);
 }
 
-bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 1) {
+bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n) {
     e->ctx->launches += n;
+    if (e->prof_on && err == cudaSuccess) {
+        cudaEvent_t ev = nullptr;
+        if (!cuda_ok(e->ctx, cudaEventCreate(&ev), "profile event") || !cuda_ok(e->ctx, cudaEventRecord(ev, e->ctx->stream), "profile event"))
+            return false;
+        e->prof_marks.emplace_back(what, ev);
+    }
     return cuda_ok(e->ctx, err, what);
 }
 
@@ -134,6 +154,126 @@ bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *
 
 enum class Tail { Greedy, LastLogits, AllLogits, None };
 
+bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, bool long_ctx);
+
+// One token with the small operators folded into the GEMVs (k2t_gemv_fused.cu): per dense layer
+//   [residual + norm -> qkv]  [attention]  [o]  [residual + norm -> gate_up]  [SwiGLU -> down]
+// five kernels instead of eight; per sparse-MoE layer norm, router, expert gate_up, [SwiGLU -> expert down], the weighted
+// sum of the experts riding in the next residual prologue.  The residual stream alternates between two buffers (every
+// CTA of a fused GEMV reads the old one while CTA 0 writes the new one).
+bool enqueue_fused_step(KronosCudaEngine *e, bool embed, Tail tail, bool long_ctx) {
+    const KronosCudaEngineConfig &c = e->cfg;
+    cudaStream_t s = e->ctx->stream;
+    const uint32_t h = c.hidden_size, inter = c.intermediate_size;
+    float *cur = e->hidden, *other = e->hidden2;
+    const float *pend = nullptr;              // projection output not yet added to the residual stream
+    const EngineLayer *pend_moe = nullptr;    // ... or the routed experts' outputs of that layer
+    auto residual_norm = [&](FusedPro &p, const float *w, bool first) {
+        p = FusedPro{};
+        p.n = h; p.chunk0 = 0; p.eps = c.rms_norm_eps; p.norm_w = w;
+        if (first && embed) {
+            p.mode = PRO_EMBED_NORM;
+            fill_embed_args(e, p.embed);
+            p.x_out = cur;
+            return;
+        }
+        p.mode = PRO_NORM;
+        p.x_in = cur;
+        if (pend_moe != nullptr) {
+            p.moe_out = e->moe_out; p.route_w = pend_moe->d_route_w; p.n_slot = std::min(c.moe_top_k, c.moe_num_experts);
+        } else {
+            p.delta = pend;
+        }
+        if (p.delta != nullptr || p.n_slot > 0) { p.x_out = other; std::swap(cur, other); }
+        pend = nullptr; pend_moe = nullptr;
+    };
+    const bool pdl = e->pdl;
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        const EngineLayer &L = e->layers[l];
+        FusedPro p;
+        residual_norm(p, L.input_norm, l == 0);
+        if (!count(e, launch_gemv_fused(s, L.qkv->dm, p, e->qkv, e->ctx->sm_count, e->ctx->d_err, pdl && (l > 0)), "gemv qkv (+norm)")) return false;
+        if (!enqueue_attention(e, l, 0, 1, long_ctx)) return false;
+        if (!gemv(e, L.o, e->proj, "gemv o")) return false;
+        pend = e->proj;
+        if (L.moe) {
+            // norm kernel (x_norm for the router + the experts' activation), router, expert gate_up, [SwiGLU -> expert down]
+            if (!count(e, launch_rmsnorm_quant_x(s, cur, pend, L.post_norm, h, c.rms_norm_eps, e->act_q, e->act_s, e->act_m, e->x_norm, 1, pdl), "rmsnorm")) return false;
+            pend = nullptr;        // added in place by the norm kernel
+            const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
+            RouterArgs ra{};
+            ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm;
+            ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
+            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done;
+            if (!count(e, launch_moe_router(s, ra, pdl), "router")) return false;
+            if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q, e->act_s, e->act_m, 0, 0,
+                                              e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, pdl, c.moe_num_experts), "expert gate_up")) return false;
+            FusedPro ps{};
+            ps.mode = PRO_SWIGLU; ps.n = dff; ps.chunk0 = 0; ps.swiglu_exp_cr = 1; ps.gate_up = e->moe_gu;
+            if (!count(e, launch_gemv_fused_experts(s, L.expert_dn[L.expert0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, c.moe_num_experts, ps,
+                                                    (size_t)2 * dff, e->moe_out, h, e->ctx->sm_count, e->ctx->d_err, pdl), "expert down (+swiglu)")) return false;
+            pend_moe = &L;
+            continue;
+        }
+        residual_norm(p, L.post_norm, false);
+        if (!count(e, launch_gemv_fused(s, L.gate_up->dm, p, e->gate_up, e->ctx->sm_count, e->ctx->d_err, pdl), "gemv gate_up (+norm)")) return false;
+        FusedPro ps{};
+        ps.mode = PRO_SWIGLU; ps.n = inter; ps.chunk0 = c.down_chunk0; ps.gate_up = e->gate_up;
+        if (!count(e, launch_gemv_fused(s, L.down->dm, ps, e->proj, e->ctx->sm_count, e->ctx->d_err, pdl), "gemv down (+swiglu)")) return false;
+        pend = e->proj;
+    }
+    FusedPro p;
+    residual_norm(p, e->final_norm, false);
+    e->final_hidden = cur;
+    if (!count(e, launch_gemv_fused(s, e->lm_head->dm, p, e->logits, e->ctx->sm_count, e->ctx->d_err, pdl), "gemv lm_head (+norm)")) return false;
+    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, pdl), "argmax");
+    return count(e, launch_advance_pos(s, e->d_pos, 1, pdl), "advance");
+}
+
+// Attention of token t of a batch of T for layer l: the output becomes row t of the o_proj activation.
+bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, bool long_ctx) {
+    const KronosCudaEngineConfig &c = e->cfg;
+    cudaStream_t s = e->ctx->stream;
+    const EngineLayer &L = e->layers[l];
+    const uint32_t hd = c.head_dim, q_dim = c.num_attention_heads * hd, qkv_rows = q_dim + 2 * c.num_key_value_heads * hd;
+        float *qkv_t = e->qkv + (size_t)t * qkv_rows;
+        int8_t *oq = e->act_q + (size_t)t * q_dim;
+        float *os = e->act_s + (size_t)t * (q_dim / 64);
+        int32_t *om = e->act_m + (size_t)t * (q_dim / 64);
+        float *tap = (l + 1 == c.num_layers && t + 1 == T) ? e->attn_tap : nullptr;
+        if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
+            FusedAttnArgs fa{};
+            fa.qkv = qkv_t; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope;
+            fa.pos = e->d_pos; fa.pos_offset = t;
+            fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
+            fa.attn_tap = tap;
+            fa.out_q = oq; fa.out_scales = os; fa.out_sums = om; fa.err_flag = e->ctx->d_err;
+            fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = e->kv_stride; fa.layer = l;
+            fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
+            fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
+            fa.trace = (e->attn_trace && l == 0) ? e->d_dbg : nullptr;
+            if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
+        } else {
+            QkvPostArgs qa{};
+            qa.qkv = qkv_t; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope;
+            qa.pos = e->d_pos; qa.pos_offset = t;
+            qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
+            qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
+            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
+            if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
+            AttnArgs aa{};
+            aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
+            aa.pos = e->d_pos; aa.pos_offset = t;
+            aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
+            aa.out_q = oq; aa.out_scales = os; aa.out_sums = om; aa.out_chunk0 = c.o_chunk0;
+            aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
+            aa.max_seq = e->kv_stride; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd); aa.kv_bits = c.kv_bits;
+            aa.err_flag = e->ctx->d_err;
+            if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
+        }
+    return true;
+}
+
 // Queues the kernels of a batch of T <= 4 consecutive tokens on the context's stream (T = 1: one decode step).
 // `embed`: look the T tokens of d_token up first (otherwise `hidden` already holds the T embeddings).  Every
 // projection reads its weights once for the whole batch (small-N GEMM); attention runs token by token because
@@ -145,6 +285,9 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
     cudaStream_t s = e->ctx->stream;
     const uint32_t h = c.hidden_size, hd = c.head_dim, q_dim = c.num_attention_heads * hd, inter = c.intermediate_size;
     const uint32_t qkv_rows = q_dim + 2 * c.num_key_value_heads * hd;
+    (void)qkv_rows; (void)hd;
+    if (T == 1 && e->fused && tail != Tail::None) return enqueue_fused_step(e, embed, tail, long_ctx);
+    e->final_hidden = nullptr;
     if (embed) {
         EmbedArgs a{};
         fill_embed_args(e, a);
@@ -155,44 +298,10 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
         // the FFN output of the layer before: partial sums under tensor parallelism, and after a MoE block under expert parallelism
         const bool ffn_partial = c.tp_size > 1 || (c.ep_size > 1 && l > 0 && e->layers[l - 1].moe);
         if (!norm_quant(e, l == 0 ? nullptr : e->proj, L.input_norm, nullptr, T, e->pdl && (embed || l > 0), ffn_partial)) return false;
-        if (!gemv(e, L.qkv, e->qkv, T)) return false;
-        for (uint32_t t = 0; t < T; ++t) {      // the attention output of token t becomes row t of the o_proj activation
-            float *qkv_t = e->qkv + (size_t)t * qkv_rows;
-            int8_t *oq = e->act_q + (size_t)t * q_dim;
-            float *os = e->act_s + (size_t)t * (q_dim / 64);
-            int32_t *om = e->act_m + (size_t)t * (q_dim / 64);
-            float *tap = (l + 1 == c.num_layers && t + 1 == T) ? e->attn_tap : nullptr;
-            if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
-                FusedAttnArgs fa{};
-                fa.qkv = qkv_t; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope;
-                fa.pos = e->d_pos; fa.pos_offset = t;
-                fa.k_q8 = e->k_q8; fa.v_q8 = e->v_q8; fa.k_scale = e->k_scale; fa.v_scale = e->v_scale;
-                fa.attn_tap = tap;
-                fa.out_q = oq; fa.out_scales = os; fa.out_sums = om; fa.err_flag = e->ctx->d_err;
-                fa.n_q = c.num_attention_heads; fa.n_kv = c.num_key_value_heads; fa.head_dim = hd; fa.max_seq = e->kv_stride; fa.layer = l;
-                fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
-                fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
-                if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
-            } else {
-                QkvPostArgs qa{};
-                qa.qkv = qkv_t; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope;
-                qa.pos = e->d_pos; qa.pos_offset = t;
-                qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
-                qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
-                qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
-                if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
-                AttnArgs aa{};
-                aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
-                aa.pos = e->d_pos; aa.pos_offset = t;
-                aa.part_m = e->part_m; aa.part_l = e->part_l; aa.part_o = e->part_o; aa.attn_out = tap;
-                aa.out_q = oq; aa.out_scales = os; aa.out_sums = om; aa.out_chunk0 = c.o_chunk0;
-                aa.n_kv = c.num_key_value_heads; aa.group = c.num_attention_heads / c.num_key_value_heads; aa.head_dim = hd;
-                aa.max_seq = e->kv_stride; aa.layer = l; aa.n_split = e->n_split; aa.attn_scale = 1.0f / sqrtf((float)hd); aa.kv_bits = c.kv_bits;
-                aa.err_flag = e->ctx->d_err;
-                if (!count(e, launch_attention(s, aa, e->pdl), "attention", 2)) return false;
-            }
-        }
-        if (!gemv(e, L.o, e->proj, T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
+        if (!gemv(e, L.qkv, e->qkv, "gemv qkv", T)) return false;
+        for (uint32_t t = 0; t < T; ++t)
+            if (!enqueue_attention(e, l, t, T, long_ctx)) return false;
+        if (!gemv(e, L.o, e->proj, "gemv o", T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
         if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
             if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl, c.tp_size > 1)) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
@@ -203,29 +312,29 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32; ra.logits = e->router_logits; ra.done = e->router_done;
                 if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
                 if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
-                                                  e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert gate_up")) return false;
+                                                  e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert gate_up")) return false;
                 if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
                 if (!count(e, launch_gemv_experts(s, L.expert_dn[L.expert0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
-                                                  e->ctx->sm_count, e->ctx->d_err, e->pdl), "expert down")) return false;
-                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl, ra.route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr), "moe combine")) return false;
+                                                  e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert down")) return false;
+                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl, ra.route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr, c.moe_num_experts), "moe combine")) return false;
             }
             continue;
         }
         if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl, c.tp_size > 1)) return false;
-        if (!gemv(e, L.gate_up, e->gate_up, T)) return false;
+        if (!gemv(e, L.gate_up, e->gate_up, "gemv gate_up", T)) return false;
         if (!count(e, launch_swiglu_quant(s, e->gate_up, inter, e->act_q, e->act_s, e->act_m, nullptr, c.down_chunk0, T, e->pdl), "swiglu")) return false;
-        if (!gemv(e, L.down, e->proj, T)) return false;
+        if (!gemv(e, L.down, e->proj, "gemv down", T)) return false;
     }
     // the last residual is folded into `hidden` by the final norm even when no logits are wanted
     if (!norm_quant(e, e->proj, e->final_norm, nullptr, T, e->pdl, c.tp_size > 1 || (c.ep_size > 1 && e->layers.back().moe))) return false;
     const uint32_t vocab_all = c.tp_size > 1 ? c.vocab_total : c.vocab_size;
     float *lg = c.tp_size > 1 ? e->logits_local : e->logits;        // under tp: this rank's slice, then gathered into `logits`
     if (tail == Tail::AllLogits || tail == Tail::Greedy) {
-        if (!gemv(e, e->lm_head, lg, T)) return false;
+        if (!gemv(e, e->lm_head, lg, "gemv lm_head", T)) return false;
         for (uint32_t t = 0; t < T && c.tp_size > 1; ++t)
             if (!tp_gather(e, lg + (size_t)t * c.vocab_size, e->logits + (size_t)t * vocab_all, c.vocab_size)) return false;
     } else if (tail == Tail::LastLogits) {
-        if (!gemv(e, e->lm_head, lg, 1, T - 1)) return false;
+        if (!gemv(e, e->lm_head, lg, "gemv lm_head", 1, T - 1)) return false;
         if (c.tp_size > 1 && !tp_gather(e, lg, e->logits, c.vocab_size)) return false;
     }
     if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, vocab_all, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
@@ -277,6 +386,11 @@ cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
     return e->graphs[(greedy ? 0 : 2) + (pos + 1 > ATTN_EXACT_CTX ? 1 : 0)];
 }
 uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
+    if (e->fused) {      // lm_head + argmax; per layer qkv, attention (1 or 3 kernels), o, and gate_up / down or norm / router / two expert GEMVs
+        uint32_t n = 2;
+        for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 3 : 1) + (L.moe ? 6 : 4);
+        return n;
+    }
     uint32_t n = 1 + 2 + 1 + (e->cfg.tp_size > 1 ? 1 : 0);
     for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4; the tensor-parallel sums ride in the norm kernels
     return n;
@@ -326,7 +440,7 @@ bool setup_mega(KronosCudaEngine *e) {
         e->mega_why = std::string("kernel does not fit one CTA per SM: ") + cudaGetErrorString(chk);
         return true;
     }
-    if (!dev_alloc(e, e->hidden2, c.hidden_size) || !dev_alloc(e, e->d_barrier, 1) || !dev_alloc(e, e->d_trace, TRACE_CAP + 1) ||
+    if (!dev_alloc(e, e->d_barrier, 1) || !dev_alloc(e, e->d_trace, TRACE_CAP + 1) ||
         !dev_alloc(e, e->d_mega_layers, layers.size(), layers.data()) || !dev_alloc(e, e->d_mega_head, 1, &head) ||
         !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "decode kernel tables"))      // the host vectors go out of scope
         return false;
@@ -457,6 +571,11 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     ctx->err.clear();
     if (!cfg || !rope || !layers || !final_norm || !lm_head) { fail(ctx, "engine_create: NULL argument"); return nullptr; }
     const KronosCudaEngineConfig &c = *cfg;
+    if (c.struct_size != sizeof(KronosCudaEngineConfig)) {
+        fail(ctx, "engine_create: config.struct_size is " + std::to_string(c.struct_size) + ", this library's KronosCudaEngineConfig has " +
+                      std::to_string(sizeof(KronosCudaEngineConfig)) + " bytes (binding out of date?)");
+        return nullptr;
+    }
     if (n_layers != c.num_layers || c.num_layers == 0) { fail(ctx, "engine_create: n_layers does not match the config"); return nullptr; }
     if (c.head_dim != 64 && c.head_dim != 128) { fail(ctx, "engine_create: head_dim must be 64 or 128"); return nullptr; }
     if (c.hidden_size % 64 || c.intermediate_size % 64 || c.hidden_size == 0) { fail(ctx, "engine_create: hidden and intermediate sizes must be multiples of 64"); return nullptr; }
@@ -485,6 +604,9 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         e->n_split = std::min(128u, std::max(32u, (want + 3u) & ~3u));
     }
     if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
+    if (const char *v = std::getenv("KRONOS_CUDA_ATTN_TRACE")) e->attn_trace = v[0] == '1';
+    if (const char *v = std::getenv("KRONOS_CUDA_FUSED")) e->fused = v[0] == '1';     // measurement switch
+    if (c.tp_size > 1 || c.ep_size > 1) e->fused = false;       // the exchanges of the parallel modes live in the norm kernel
     e->layers.resize(c.num_layers);
     auto bad = [&](const std::string &why) { std::string keep = why; kronos_cuda_engine_destroy(e); fail(ctx, keep); return (KronosCudaEngine *)nullptr; };
     auto shape_ok = [](const KronosCudaMatrixDesc &d, uint32_t rows, uint32_t cols) { return d.rows == rows && d.cols == cols; };
@@ -523,7 +645,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
               (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)(c.tp_size > 1 ? c.vocab_total : c.vocab_size) * h, embed_bf16)) &&   // every rank keeps the whole table
               // per-token vectors hold MAX_BATCH tokens (prompt batches), [token][n]
-              dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
+              dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->hidden2, h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
               dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
               dev_alloc(e, e->logits, (size_t)MAX_BATCH * (c.tp_size > 1 ? c.vocab_total : c.vocab_size)) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
               dev_alloc(e, e->act_s, (size_t)MAX_BATCH * act_n / 64) && dev_alloc(e, e->act_m, (size_t)MAX_BATCH * act_n / 64) &&
@@ -534,7 +656,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->k_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
-              dev_alloc(e, e->d_history, c.max_seq_len);
+              dev_alloc(e, e->d_history, c.max_seq_len) && dev_alloc(e, e->d_dbg, 32);
     const uint32_t xg = c.tp_size > 1 ? c.tp_size : c.ep_size, xr = c.tp_size > 1 ? c.tp_rank : c.ep_rank;     // exchange group
     if (ok && xg > 1) {
         if (e->has_moe && c.tp_size > 1) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
@@ -574,6 +696,7 @@ size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *e, size_t positions) 
     return positions * 2 * (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads * per_head;
 }
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *e) { return e ? e->weight_bytes : 0; }
+int64_t kronos_cuda_engine_profile_step(KronosCudaEngine *e, uint32_t token, size_t pos, uint32_t reps, char *table, size_t cap);
 
 int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *e, float *hidden) {
     if (!e || !hidden) return -1;
@@ -581,7 +704,8 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *e, float *hidden) {
     ctx->err.clear();
     if (!make_current(ctx)) return -1;
     // the final norm kernel has already folded the last down_proj into the residual stream
-    if (!cuda_ok(ctx, cudaMemcpyAsync(hidden, e->hidden + (size_t)e->last_row * e->cfg.hidden_size, (size_t)e->cfg.hidden_size * 4,
+    const float *src = e->final_hidden ? e->final_hidden : e->hidden + (size_t)e->last_row * e->cfg.hidden_size;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(hidden, src, (size_t)e->cfg.hidden_size * 4,
                                       cudaMemcpyDeviceToHost, ctx->stream), "read hidden") ||
         !sync_and_check(ctx, "read hidden"))
         return -1;
@@ -878,7 +1002,100 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     }
     if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
     if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, vocab_all * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
-    return sync_and_check(ctx, "decode_greedy") ? 0 : -1;
+    if (!sync_and_check(ctx, "decode_greedy")) return -1;
+    if (const char *v = std::getenv("KRONOS_CUDA_DECODE_PROF")) {
+        if (v[0] == '1') {              // the step that produced the last token, once more, kernel by kernel (same cache row, same result)
+            std::vector<char> table(1 << 14);
+            const uint32_t tok = n_steps >= 2 ? out_tokens[n_steps - 2] : first_token;
+            if (kronos_cuda_engine_profile_step(e, tok, pos_start + n_steps - 1, 1, table.data(), table.size()) >= 0)
+                std::fprintf(stderr, "[kronos_cuda decode profile, position %zu]\n%s", pos_start + n_steps - 1, table.data());
+        }
+    }
+    return 0;
+}
+
+int64_t kronos_cuda_engine_profile_step(KronosCudaEngine *e, uint32_t token, size_t pos, uint32_t reps, char *table, size_t cap) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!table || cap == 0) return fail(ctx, "profile_step: no output buffer"), -1;
+    reps = std::max(1u, reps);
+    if (pos + reps > e->cfg.max_seq_len) return fail(ctx, "profile_step: positions beyond max_seq_len"), -1;
+    if (!make_current(ctx) || !ensure_graphs(e)) return -1;          // warm: every kernel loaded, attributes set
+    // The step is launched kernel by kernel with a timing event after each one (and one in front), without programmatic
+    // overlap, so the time between two events is the kernel between them, run alone on a warm device.  A bounded delay
+    // kernel keeps the stream busy while the host queues the step, so the gaps between events hold no launch latency.
+    const bool pdl_was = e->pdl;
+    const bool long_ctx = pos + reps > ATTN_EXACT_CTX;
+    std::map<std::string, std::pair<double, uint32_t>> acc;
+    std::vector<std::string> order;
+    double total = 0.0;
+    cudaEvent_t first = nullptr;
+    bool ok = cuda_ok(ctx, cudaEventCreate(&first), "profile event");
+    const uint32_t init[3] = {token, (uint32_t)pos, 0u};
+    ok = ok && cuda_ok(ctx, cudaMemcpyAsync(e->d_token, &init[0], 4, cudaMemcpyHostToDevice, ctx->stream), "set token") &&
+         cuda_ok(ctx, cudaMemcpyAsync(e->d_pos, &init[1], 4, cudaMemcpyHostToDevice, ctx->stream), "set pos") &&
+         cuda_ok(ctx, cudaMemcpyAsync(e->d_step, &init[2], 4, cudaMemcpyHostToDevice, ctx->stream), "set step") &&
+         cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "profile setup");
+    for (uint32_t r = 0; ok && r < reps; ++r) {
+        e->pdl = false;
+        e->prof_on = true;
+        e->prof_marks.clear();
+        const uint64_t delay_ns = 1000000ull + 8000ull * step_launches(e, pos + r);
+        ok = cuda_ok(ctx, launch_delay(ctx->stream, delay_ns), "delay kernel") && cuda_ok(ctx, cudaEventRecord(first, ctx->stream), "profile event") &&
+             enqueue_batch(e, 1, true, Tail::Greedy, long_ctx);
+        e->pdl = pdl_was;
+        e->prof_on = false;
+        ok = ok && sync_and_check(ctx, "profile step");
+        cudaEvent_t prev = first;
+        for (auto &mk : e->prof_marks) {
+            float ms = 0.0f;
+            if (ok && !cuda_ok(ctx, cudaEventElapsedTime(&ms, prev, mk.second), "event time")) ok = false;
+            if (ok) {
+                auto it = acc.find(mk.first);
+                if (it == acc.end()) { acc[mk.first] = {0.0, 0u}; order.push_back(mk.first); it = acc.find(mk.first); }
+                it->second.first += ms * 1e3; it->second.second += 1;
+                total += ms * 1e3;
+            }
+            prev = mk.second;
+        }
+        for (auto &mk : e->prof_marks) cudaEventDestroy(mk.second);
+        e->prof_marks.clear();
+    }
+    e->pdl = pdl_was;
+    e->prof_on = false;
+    for (auto &mk : e->prof_marks) cudaEventDestroy(mk.second);
+    e->prof_marks.clear();
+    if (first) cudaEventDestroy(first);
+    if (!ok) return -1;
+    std::string out = "kernel class | launches per step | us per step | avg us | share\n";
+    char line[256];
+    for (const std::string &k : order) {
+        const auto &v = acc[k];
+        std::snprintf(line, sizeof line, "%s | %.1f | %.1f | %.2f | %.1f%%\n", k.c_str(), (double)v.second / reps, v.first / reps, v.first / v.second,
+                      100.0 * v.first / std::max(total, 1e-9));
+        out += line;
+    }
+    std::snprintf(line, sizeof line, "total | | %.1f | |\n", total / reps);
+    out += line;
+    const size_t n = std::min(out.size(), cap - 1);
+    std::memcpy(table, out.data(), n);
+    table[n] = 0;
+    return (int64_t)out.size();
+}
+
+size_t kronos_cuda_engine_debug_words(KronosCudaEngine *e, uint64_t *out, size_t cap) {
+    if (!e || !out) return 0;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!make_current(ctx)) return 0;
+    unsigned long long buf[32];
+    if (!cuda_ok(ctx, cudaMemcpyAsync(buf, e->d_dbg, sizeof buf, cudaMemcpyDeviceToHost, ctx->stream), "read debug words") ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "read debug words"))
+        return 0;
+    const size_t n = std::min<size_t>(32, cap);
+    for (size_t i = 0; i < n; ++i) out[i] = buf[i];
+    return n;
 }
 
 }  // extern "C"

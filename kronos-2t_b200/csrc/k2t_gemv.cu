@@ -84,6 +84,7 @@ struct ExpertBatch {
     const uint32_t *route_ids;     // device [n_slot]
     size_t xq_stride, xs_stride;   // per-slot strides of the activation
     size_t out_stride;             // per-slot stride of the output
+    uint32_t n_experts;            // entries of books / bases: a route id outside is refused (error word 4)
 };
 
 template <int FMT>
@@ -95,6 +96,10 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
     __syncwarp();
     pdl_wait();
     const uint32_t slot = blockIdx.y, e = __ldcg(b.route_ids + slot);
+    if (e >= b.n_experts) {            // never produced by the router kernel; a foreign id must not index the tables
+        if (threadIdx.x == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 4u);
+        return;
+    }
     const uint8_t *base = b.bases[e];
     if (base == nullptr) return;       // expert parallelism: another rank owns this expert (the whole CTA leaves, no copy is in flight)
     {
@@ -136,12 +141,12 @@ int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out) {
 
 cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases, const uint32_t *route_ids,
                                 uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum, size_t xq_stride,
-                                size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl) {
+                                size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl, uint32_t n_experts) {
     if (n_slot == 0) return cudaSuccess;
     GemvArgs a;
     if (fill_gemv_args(m0, xsum != nullptr, a) < 0) return cudaErrorNotSupported;
     a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.err_flag = err_flag; a.out_stride = m0.geom.rows; a.pdl = pdl ? 1u : 0u; a.n_tok = 1;
-    ExpertBatch b{books, bases, m0.d_base, route_ids, xq_stride, xs_stride, out_stride};
+    ExpertBatch b{books, bases, m0.d_base, route_ids, xq_stride, xs_stride, out_stride, n_experts};
     switch (fmt) {
         case FMT_NF4: return launch_expert_fmt<FMT_NF4>(stream, a, b, n_slot, sm_count);
         case FMT_NF4G: return launch_expert_fmt<FMT_NF4G>(stream, a, b, n_slot, sm_count);

@@ -293,10 +293,15 @@ __device__ __forceinline__ void gemv_init_barriers(uint8_t *wsm) {     // one la
     fence_proxy_async();
 }
 
-template <int FMT, int NT, bool DOTS, bool MEGA>
+struct NoHook { __device__ __forceinline__ void operator()() const {} };
+
+// `hook` runs once per warp right after the first weight stages have been requested and before any activation is read:
+// a kernel that builds its activation itself (k2t_gemv_fused.cu) waits for its predecessor and fills the shared-memory
+// activation there, CTA-wide, while its weights are already on their way.
+template <int FMT, int NT, bool DOTS, bool MEGA, typename Hook>
 __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, const float *xs, const int32_t *xsum_p, float *out,
                                           uint8_t *wsm, float *s_f, uint32_t gw, uint32_t nw, uint32_t wid, uint32_t WK,
-                                          uint32_t bar_id, PipeState &ps) {
+                                          uint32_t bar_id, PipeState &ps, Hook hook) {
     using St = Stage<FMT>;
     const uint32_t lane = threadIdx.x & 31;
     if (FMT == FMT_E8Q2) {          // every warp fills the (same) table itself, so no CTA-wide barrier is needed
@@ -354,6 +359,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     for (int s = 0; s < NSTAGE; ++s) issue((ps.stage + s) % NSTAGE);
     // weights are on their way; the activations (and the output buffer) belong to the preceding kernels
     if (!MEGA) { pdl_wait(); pdl_trigger(); }
+    hook();
 
     // ---- consumer
     int q[NT][16];
@@ -478,6 +484,13 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
         }
     }
     ps.stage = stage; ps.phase = phase;
+}
+
+template <int FMT, int NT, bool DOTS, bool MEGA>
+__device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, const float *xs, const int32_t *xsum_p, float *out,
+                                          uint8_t *wsm, float *s_f, uint32_t gw, uint32_t nw, uint32_t wid, uint32_t WK,
+                                          uint32_t bar_id, PipeState &ps) {
+    gemv_body<FMT, NT, DOTS, MEGA>(a, xq, xs, xsum_p, out, wsm, s_f, gw, nw, wid, WK, bar_id, ps, NoHook{});
 }
 
 }  // namespace k2t

@@ -18,7 +18,7 @@ cudaError_t launch_fwht_quant(cudaStream_t stream, const float *x, const float *
                               uint32_t n_tok, uint32_t cols, uint64_t chunk0, int8_t *q, float *scales,
                               int32_t *sums);
 
-// Quantized GEMV / small-N GEMM over all rows. n_tok in 1..8. Returns the number of kernel launches
+// Quantized GEMV / small-N GEMM over all rows. n_tok in 1..4 (callers split longer batches). Returns the number of kernel launches
 // in *launches. xsum may be null for NF formats.  pdl: launch as a programmatic dependent of the previous
 // kernel in the stream (the weight pipeline starts before that kernel has finished).
 cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs,
@@ -40,9 +40,10 @@ int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out);
 // expert e) with activation row s (strides 0 = shared) into out + s * out_stride.
 cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases,
                                 const uint32_t *route_ids, uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum,
-                                size_t xq_stride, size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl);
+                                size_t xq_stride, size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl,
+                                uint32_t n_experts);
 
-// Largest n_tok one launch_gemv call accepts for this matrix (shared-memory bound), at most 8.
+// Largest n_tok one launch_gemv call accepts for this matrix (4: the reference's tokens per weight tile in prompt batches).
 uint32_t gemv_max_tokens(const DeviceMatrix &m);
 
 }  // namespace k2t

@@ -210,6 +210,8 @@ __device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
     return s;
 }
 
+#define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); } while (0)
+
 template <int HD, bool KV4>
 __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
     constexpr int QW = HD / 4, NB = HD / 64;
@@ -237,6 +239,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     // mbarrier; then this lane's head inputs, and the key rows and scales of this thread's (at most two)
     // cached positions.
     const uint32_t vbar = (uint32_t)__cvta_generic_to_shared(s.bar);
+    ATTN_MARK(0);
     if (tid == NT - 32 && pos > 0) {       // a warp that has nothing to do during the head preparation: its fences delay nobody
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(vbar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -281,6 +284,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             vsr[k][0] = cached ? __ldcg(vs + t) : 0.0f;
         }
     }
+    ATTN_MARK(1);
     // ---- the three heads of this CTA: warp 0 = query qh, warp 1 = key kvh, warp 2 = value kvh
     if (warp < 3) {
         float *sh = s.head + warp * 128;
@@ -361,7 +365,9 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             }
         }
     }
+    ATTN_MARK(2);
     __syncthreads();
+    ATTN_MARK(3);
     // ---- scores (positions < pos from the prefetched cache rows, position pos from shared memory)
     const float qas = __fmul_rn(s.hs[0], A.attn_scale);
     int qw[QW];
@@ -431,6 +437,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     mx = warp_max(mx);
     if (lane == 0) s.red[warp] = mx;
     __syncthreads();
+    ATTN_MARK(4);
 #pragma unroll
     for (int i = 0; i < (int)NW; ++i) mx = fmaxf(mx, s.red[i]);
     // softmax_unnorm (9603-9632): polynomial exp for whole groups of 4 positions, libm exp for the rest
@@ -442,6 +449,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         if (t < n4) s.sc[t] = exp_poly(__fsub_rn(scr[k], mx));
     }
     __syncthreads();
+    ATTN_MARK(5);
     float acc = 0.0f;
     if (warp == 0) {
         if (lane < 4) {
@@ -458,17 +466,20 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0+a1, lane 2: a2+a3
         acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
     }
+    ATTN_MARK(6);
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
         const uint32_t t = tid + k * NT;
         if (t >= n4 && t < ctx) s.sc[t] = (float)exp((double)__fsub_rn(scr[k], mx));
     }
     __syncthreads();
+    ATTN_MARK(7);
     if (tid == 0) {
         for (uint32_t t = n4; t < ctx; ++t) acc = __fadd_rn(acc, s.sc[t]);
         *s.inv = __fdiv_rn(1.0f, acc);
     }
     __syncthreads();
+    ATTN_MARK(8);
     const float inv = *s.inv;
 #pragma unroll
     for (int k = 0; k < PT; ++k) {
@@ -486,6 +497,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     // ---- values: thread i < HD = dimension i runs the position-ascending chain over the staged rows
     __syncthreads();                       // weights complete
+    ATTN_MARK(9);
     float o = 0.0f;
     bool copy_failed = false;
     if (pos > 0) {                         // bounded wait for the bulk copy
@@ -497,6 +509,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     copy_failed = __syncthreads_or(copy_failed) != 0;      // the same verdict in every thread (there are barriers below)
     if (copy_failed && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
+    ATTN_MARK(10);
     if (tid < HD && !copy_failed) {
         // a zero weight skips the position (as the CPU loop does): select, not branch.  Eight positions are
         // loaded before their fma chain starts, so the chain runs at fma latency, not shared-memory latency.
@@ -567,7 +580,9 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             o = __fmaf_rn(to_f32(reinterpret_cast<const uint8_t *>(s.hq)[256 + tid]), wp[pos], o);
         }
     }
+    ATTN_MARK(11);
     __syncthreads();
+    ATTN_MARK(12);
     if (tid == 0 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
     if (tid < HD) s.o[tid] = o;
     __syncthreads();
@@ -584,6 +599,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         reinterpret_cast<char2 *>(A.out_q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
         if (lane == 0) { A.out_scales[c] = sc; A.out_sums[c] = sum; }
     }
+    ATTN_MARK(13);
 }
 
 // runtime dispatch on head_dim / cache format

@@ -220,6 +220,10 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
         __syncthreads();
     }
     const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
+    // Non-finite scores (a NaN ranks before nothing and after nothing) can leave ranks unassigned: every slot starts as
+    // a valid route (expert i, weight 0), so the expert kernels never see an id outside [0, n_experts).
+    if (tid < k) { s_sel_e[tid] = tid; s_sel_w[tid] = 0.0f; }
+    __syncthreads();
     for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) {       // rank of expert e in the descending order
         const float sc = s_z[e];
         uint32_t rank = 0;
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
             while (j > 0 && ids[j - 1] > ce) { ids[j] = ids[j - 1]; w[j] = w[j - 1]; --j; }
             ids[j] = ce; w[j] = cw;
         }
-        for (uint32_t i = 0; i < k; ++i) { a.route_ids[i] = ids[i]; a.route_w[i] = w[i]; }
+        for (uint32_t i = 0; i < k; ++i) { a.route_ids[i] = min(ids[i], a.n_experts - 1u); a.route_w[i] = w[i]; }
     }
 }
 
@@ -282,14 +286,15 @@ __global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *_
 // Expert parallelism (owned != null): only the routes whose expert this rank holds (owned[e] != null) - a partial sum.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ expert_out, const float *__restrict__ route_w,
                                                           uint32_t n_slot, uint32_t n, float *__restrict__ out,
-                                                          const uint32_t *__restrict__ route_ids, const uint8_t *const *__restrict__ owned) {
+                                                          const uint32_t *__restrict__ route_ids, const uint8_t *const *__restrict__ owned,
+                                                          uint32_t n_experts) {
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
     pdl_wait();
     pdl_trigger();
     if (i >= n) return;
     float acc = 0.0f;
     for (uint32_t s = 0; s < n_slot; ++s) {
-        if (owned != nullptr && owned[__ldcg(route_ids + s)] == nullptr) continue;
+        if (owned != nullptr && (__ldcg(route_ids + s) >= n_experts || owned[__ldcg(route_ids + s)] == nullptr)) continue;
         acc = __fadd_rn(acc, __fmul_rn(__ldcg(route_w + s), __ldcg(expert_out + (size_t)s * n + i)));
     }
     out[i] = acc;
@@ -806,6 +811,17 @@ __global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restri
     }
 }
 
+// Keeps the stream busy for about `ns` nanoseconds of the global timer (bounded a second time by a poll count).
+__global__ void delay_kernel(unsigned long long ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t i = 0; i < (1u << 24); ++i) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 >= ns) break;
+        __nanosleep(200);
+    }
+}
+
 __global__ void advance_pos_kernel(uint32_t *pos, uint32_t by) {
     pdl_wait();
     *pos = __ldcg(pos) + by;
@@ -836,8 +852,8 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
     return launch_kernel(expert_swiglu_quant_kernel, dim3((d_ff / 64 + 7) / 8, n_slot), dim3(256), 0, s, pdl, gate_up, d_ff, q, scales, sums);
 }
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned) {
-    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned);
+                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned, uint32_t n_experts) {
+    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned, n_experts);
 }
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {
@@ -896,6 +912,9 @@ cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t i
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
                                uint32_t *history, uint32_t *step, bool pdl) {
     return launch_kernel(argmax_step_kernel, dim3(1), dim3(1024), 0, s, pdl, logits, n, token, pos, history, step);
+}
+cudaError_t launch_delay(cudaStream_t s, uint64_t ns) {
+    return launch_kernel(delay_kernel, dim3(1), dim3(1), 0, s, false, (unsigned long long)ns);
 }
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl) {
     return launch_kernel(advance_pos_kernel, dim3(1), dim3(1), 0, s, pdl, pos, by);

@@ -68,6 +68,7 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     uint32_t kv_bits;            // 8: int8 rows [head_dim] + fp32 scale per slot; 4: NF4 rows [head_dim / 2] + bf16 scale per 64 values
     float eps, attn_scale;
     int32_t qk_norm_after_rope;
+    unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (16 words)
 };
 
 struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scoring (sparse_moe.rs:86-182)
@@ -110,7 +111,9 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
                                        int32_t *sums, bool pdl);
 // out[i] = sum over slots, in slot order, of route_w[s] * expert_out[s][i]   (sparse_moe.rs:1046-1048)
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr);
+                               bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr, uint32_t n_experts = 0);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
+// one thread that waits about `ns` nanoseconds (bounded): lets a host queue work behind it (measurement only)
+cudaError_t launch_delay(cudaStream_t s, uint64_t ns);
 
 }  // namespace k2t

@@ -33,12 +33,15 @@ class MatrixDesc(C.Structure):
 
 
 class EngineConfig(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("hidden_size", "num_layers", "num_attention_heads", "num_key_value_heads",
+    _fields_ = [(n, C.c_uint32) for n in ("struct_size", "hidden_size", "num_layers", "num_attention_heads", "num_key_value_heads",
                                           "head_dim", "intermediate_size", "vocab_size", "max_seq_len")] + \
                [("rms_norm_eps", C.c_float), ("qk_norm_after_rope", C.c_int32), ("kv_bits", C.c_uint32)] + \
                [(n, C.c_uint32) for n in ("moe_num_experts", "moe_top_k", "moe_norm_topk", "moe_d_ff", "moe_bits",
                                           "moe_scale_group_chunks")] + [("moe_expert_bytes", C.c_uint64)] + \
-               [(n, C.c_uint32) for n in ("tp_size", "tp_rank", "o_chunk0", "down_chunk0", "vocab_total", "ep_size", "ep_rank")]
+               [(n, C.c_uint32) for n in ("tp_size", "tp_rank", "o_chunk0", "down_chunk0", "vocab_total", "ep_size", "ep_rank",
+                                          "kv_window", "kv_sinks", "flags")]
+
+ENGINE_SPLIT_KV_ATTENTION = 1
 
 
 class LayerDesc(C.Structure):
@@ -109,6 +112,8 @@ def load_library():
     sig("kronos_cuda_k2tb_save", i32, C.c_char_p, C.POINTER(u64 * 6), C.POINTER(LayerDesc), sz, sz, sz, sz, vp,
         C.POINTER(MatrixDesc), vp, sz)
     sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
+    sig("kronos_cuda_engine_profile_step", C.c_int64, vp, u32, sz, u32, C.c_char_p, sz)
+    sig("kronos_cuda_engine_debug_words", sz, vp, vp, sz)
     sig("kronos_cuda_engine_read_kv_q4", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     sig("kronos_cuda_engine_read_kv", i32, vp, u32, u32, sz, vp, vp, vp, vp)
     _LIB = L
@@ -291,8 +296,10 @@ class Engine:
     def __init__(self, ctx, spec):
         self.ctx, self.L = ctx, ctx.L
         c = spec["cfg"]
-        self.cfg = EngineConfig(c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
+        self.cfg = EngineConfig(C.sizeof(EngineConfig), c["hidden"], c["layers"], c["n_q"], c["n_kv"], c["head_dim"], c["inter"], c["vocab"],
                                 c["max_seq"], c["eps"], int(c.get("qk_norm_after_rope", 0)), int(c.get("kv_bits", 8)))
+        self.cfg.kv_window, self.cfg.kv_sinks = int(c.get("kv_window", 0)), int(c.get("kv_sinks", 0))
+        self.cfg.flags = ENGINE_SPLIT_KV_ATTENTION if c.get("split_kv_attention") else 0
         if int(c.get("tp_size", 1)) > 1:      # a rank of a tensor-parallel group (spec from kronos_2t_b200.tp.shard_spec)
             self.cfg.tp_size, self.cfg.tp_rank, self.cfg.vocab_total = c["tp_size"], c["tp_rank"], c["vocab_total"]
             self.cfg.o_chunk0, self.cfg.down_chunk0 = c["o_chunk0"], c["down_chunk0"]
@@ -424,6 +431,19 @@ class Engine:
         """Global-timer marks (ns) of the last step of the last whole-token-kernel decode call."""
         buf = np.zeros(4096, np.uint64)
         n = self.L.kronos_cuda_engine_decode_trace(self.handle, _p(buf), buf.size)
+        return buf[:n].copy()
+
+    def profile_step(self, token, pos, reps=16):
+        """Per-kernel-class timing table (text) of one greedy step at position `pos`, averaged over `reps` replays."""
+        buf = C.create_string_buffer(1 << 14)
+        n = self.L.kronos_cuda_engine_profile_step(self.handle, int(token), pos, reps, buf, len(buf))
+        if n < 0:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(self.ctx.handle).decode())
+        return buf.value.decode()
+
+    def debug_words(self):
+        buf = np.zeros(32, np.uint64)
+        n = self.L.kronos_cuda_engine_debug_words(self.handle, _p(buf), buf.size)
         return buf[:n].copy()
 
     def read_kv(self, layer, kv_head, position):

@@ -159,10 +159,12 @@ def _greedy_check(eng, ref, prompt, steps):
     assert np.array_equal(got_logits, want_logits)
 
 
-@pytest.fixture(params=["decode-kernel", "per-operator"])
+@pytest.fixture(params=["fused", "per-operator", "decode-kernel"])
 def decode_path(request, monkeypatch):
-    """Greedy decoding runs as a CUDA graph of the per-operator kernels (default) or, with KRONOS_CUDA_MEGA=1 at
-    engine creation, in the whole-token cooperative kernel (contexts <= 512)."""
+    """Single-token steps run as a CUDA graph of GEMVs that build their own activations (norm / SwiGLU / embedding
+    prologues; the default), as a graph of per-operator kernels (KRONOS_CUDA_FUSED=0 at engine creation), or - greedy
+    decoding up to 512 positions, KRONOS_CUDA_MEGA=1 - in the whole-token cooperative kernel."""
+    monkeypatch.setenv("KRONOS_CUDA_FUSED", "0" if request.param == "per-operator" else "1")
     monkeypatch.setenv("KRONOS_CUDA_MEGA", "1" if request.param == "decode-kernel" else "0")
     return request.param
 
