@@ -48,6 +48,8 @@ struct KronosCudaEngine {
     int8_t *act_q = nullptr, *q_i8 = nullptr;
     float *attn_tap = nullptr;                // attention output of the last layer (diagnostic)
     float *act_s = nullptr, *q_scale = nullptr, *part_m = nullptr, *part_l = nullptr, *part_o = nullptr;
+    float *attn_sc = nullptr, *attn_bmax = nullptr;      // long contexts in CPU order: scores [n_q][kv_stride], block maxima [n_q][kv_stride / 128]
+    bool split_kv = false;                    // long contexts by the split-KV kernels instead (config flag, or the cache is too long for the exact path)
     int32_t *act_m = nullptr;
     int8_t *k_q8 = nullptr, *v_q8 = nullptr;
     float *k_scale = nullptr, *v_scale = nullptr;
@@ -261,6 +263,18 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
             qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
             qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
             if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
+            if (!e->split_kv) {
+                ExactAttnArgs xa{};
+                xa.q_i8 = e->q_i8; xa.q_scale = e->q_scale; xa.k_q8 = e->k_q8; xa.v_q8 = e->v_q8; xa.k_scale = e->k_scale; xa.v_scale = e->v_scale;
+                xa.pos = e->d_pos; xa.pos_offset = t;
+                xa.sc = e->attn_sc; xa.bmax = e->attn_bmax; xa.attn_out = tap;
+                xa.out_q = oq; xa.out_scales = os; xa.out_sums = om; xa.out_chunk0 = c.o_chunk0;
+                xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
+                xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128; xa.ctx_cap = e->kv_stride;
+                xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err;
+                xa.trace = (e->attn_trace && l == 0) ? e->d_dbg + 16 : nullptr;
+                return count(e, launch_attention_exact(s, xa, e->pdl), "attention", 2);
+            }
             AttnArgs aa{};
             aa.q_i8 = e->q_i8; aa.q_scale = e->q_scale; aa.k_q8 = e->k_q8; aa.v_q8 = e->v_q8; aa.k_scale = e->k_scale; aa.v_scale = e->v_scale;
             aa.pos = e->d_pos; aa.pos_offset = t;
@@ -605,6 +619,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     }
     if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
     if (const char *v = std::getenv("KRONOS_CUDA_ATTN_TRACE")) e->attn_trace = v[0] == '1';
+    e->split_kv = (c.flags & KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION) != 0 || e->kv_stride > attention_exact_max_ctx(c.head_dim, c.kv_bits);
     if (const char *v = std::getenv("KRONOS_CUDA_FUSED")) e->fused = v[0] == '1';     // measurement switch
     if (c.tp_size > 1 || c.ep_size > 1) e->fused = false;       // the exchanges of the parallel modes live in the norm kernel
     e->layers.resize(c.num_layers);
@@ -652,6 +667,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
+              dev_alloc(e, e->attn_sc, (size_t)n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)n_q * ((e->kv_stride + 127) / 128)) &&
               dev_alloc(e, e->k_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) &&
               dev_alloc(e, e->k_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
               dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&

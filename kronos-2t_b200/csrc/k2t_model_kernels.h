@@ -34,8 +34,8 @@ struct QkvPostArgs {
     int32_t qk_norm_after_rope;
 };
 
-// Contexts up to this many positions are attended in the CPU's summation order (bit-identical output);
-// longer ones by the split-KV kernel (fp32-rounding agreement).
+// Contexts up to this many positions are attended by the single fused kernel; longer ones by the three-kernel path in
+// the same (CPU) summation order, or - on request - by the split-KV kernels (fp32-rounding agreement).
 #define ATTN_EXACT_CTX 512u
 
 struct AttnArgs {
@@ -51,6 +51,25 @@ struct AttnArgs {
     uint32_t kv_bits;            // 8 or 4 (see QkvPostArgs)
     float attn_scale;
     uint32_t *err_flag;          // set to 1 when a bounded wait for a staged tile gives up
+};
+
+struct ExactAttnArgs {           // attention in the reference's summation order at any context length (k2t_attn_exact.cu)
+    const int8_t *q_i8; const float *q_scale;              // rotated int8 queries of qkv_post_kernel
+    const int8_t *k_q8, *v_q8; const float *k_scale, *v_scale;
+    const uint32_t *pos;         // device: position of the current token (context = pos + 1)
+    uint32_t pos_offset;
+    float *sc;                   // scratch: scores [n_q][sc_stride]
+    float *bmax;                 // scratch: maximum of every 128-position block [n_q][blk_stride]
+    float *attn_out;             // optional fp32 attention output [n_q][head_dim], may be null
+    int8_t *out_q; float *out_scales; int32_t *out_sums;   // activation of o_proj
+    uint32_t out_chunk0;
+    uint32_t n_kv, group, head_dim, max_seq, layer;
+    uint32_t sc_stride, blk_stride;
+    uint32_t ctx_cap;            // longest context the launch is sized for (a multiple of 4, at most sc_stride)
+    uint32_t kv_bits;
+    float attn_scale;
+    uint32_t *err_flag;
+    unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (8 words)
 };
 
 struct FusedAttnArgs {           // one layer's attention from the fused qkv vector to the o_proj activation
@@ -90,6 +109,10 @@ cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *del
                                  int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl);
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl);
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl);     // two kernels
+// any context length in the reference's summation order: two kernels (after launch_qkv_post)
+cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl);
+// longest context launch_attention_exact can serve (its value weights live in shared memory)
+size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits);
 // contexts of up to ATTN_EXACT_CTX positions: qkv_post + attention in one kernel (leaves longer contexts untouched)
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl);
 // chunk0: global index of the first down_proj input chunk of this rank (tensor parallel), else 0
