@@ -259,6 +259,13 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
 int32_t kronos_cuda_engine_tp_handle(KronosCudaEngine *engine, uint8_t handle[64]);
 int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *engine, const uint8_t *handles /* [tp_size][64] */, size_t n_handles);
 int32_t kronos_cuda_engine_set_embedding_matrix(KronosCudaEngine *engine, const KronosCudaMatrixDesc *whole_lm_head);
+/* tp_attach for a host that drives every rank from ONE process (one engine per GPU, the single-caller contract of
+ * MetalLlamaEngine kept): `engines` = the tp_size (or ep_size) engines in rank order, this engine's own entry included;
+ * peer access between their devices is enabled as needed.  Every engine of the group makes this call.
+ * Waits for a peer are bounded: a rank whose peers never write (a peer was destroyed, or never ran the matching call)
+ * gives up after KRONOS_CUDA_PEER_WAIT_POLLS polls per kernel (environment, default 4194304), its calls return -1
+ * ("gave up waiting for a peer rank") and the context stays in that state: destroy and recreate the group. */
+int32_t kronos_cuda_engine_tp_attach_local(KronosCudaEngine *engine, KronosCudaEngine *const *engines, size_t n_engines);
 /* Diagnostic: routes of the last forwarded token through MoE layer `layer` (route_sorted, sparse_moe.rs:86-182):
  * up to 32 (expert id, weight) pairs in ascending expert order; returns their number (0 for a dense layer). */
 size_t kronos_cuda_engine_read_routes(KronosCudaEngine *engine, uint32_t layer, uint32_t *experts, float *weights);

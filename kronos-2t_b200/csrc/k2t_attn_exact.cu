@@ -346,19 +346,20 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
             t_wait += clock64() - tw0;
             const uint8_t *vt = stages + (size_t)st * Sm::STAGE + byte_off;
             const float *wt = wp + tl;
+            const uint32_t va = (uint32_t)__cvta_generic_to_shared(vt), wa = (uint32_t)__cvta_generic_to_shared(wt);
             uint32_t j = 0;
             if (n >= 16) {
                 uint32_t cur[16], nxt[16];
                 float4 wc[4], wn[4];
 #pragma unroll
-                for (int u = 0; u < 16; ++u) cur[u] = vt[(size_t)u * ROW];
+                for (int u = 0; u < 16; ++u) cur[u] = lds_u8(va + u * ROW);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) wc[u] = *reinterpret_cast<const float4 *>(wt + 4 * u);
+                for (int u = 0; u < 4; ++u) wc[u] = lds_f32x4(wa + 16 * u);
                 for (; j + 32 <= n; j += 16) {
 #pragma unroll
-                    for (int u = 0; u < 16; ++u) nxt[u] = vt[(size_t)(j + 16 + u) * ROW];
+                    for (int u = 0; u < 16; ++u) nxt[u] = lds_u8(va + (j + 16 + u) * ROW);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) wn[u] = *reinterpret_cast<const float4 *>(wt + j + 16 + 4 * u);
+                    for (int u = 0; u < 4; ++u) wn[u] = lds_f32x4(wa + 4 * (j + 16) + 16 * u);
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         o = __fmaf_rn(value(cur[4 * u + 0]), wc[u].x, o);

@@ -55,8 +55,14 @@ inline bool sync_and_check(KronosCudaContext *ctx, const char *what) {
         !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), what))
         return false;
     if (flag != 0) {
-        cudaMemsetAsync(ctx->d_err, 0, 4, ctx->stream);
-        return fail(ctx, std::string(what) + ": a kernel gave up waiting for its weight pipeline (results invalid)");
+        // 3 stays set: a peer that did not answer once is not waited for again (the engine must be rebuilt)
+        if (flag != 3) cudaMemsetAsync(ctx->d_err, 0, 4, ctx->stream);
+        const char *why = flag == 2 ? "the grid barrier of the whole-token kernel gave up waiting"
+                        : flag == 3 ? "a tensor- / expert-parallel exchange gave up waiting for a peer rank (the peer has left or never attached; recreate the engines)"
+                        : flag == 4 ? "an expert kernel was handed a route id outside the layer's experts"
+                        : flag == 5 ? "the attention kernel was launched for a context longer than it was sized for"
+                        : "a kernel gave up waiting for its weight pipeline";
+        return fail(ctx, std::string(what) + ": " + why + " (results invalid)");
     }
     return true;
 }

@@ -88,6 +88,19 @@ __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
 
+// Shared-memory loads by shared-window address (from __cvta_generic_to_shared): where a pointer reaches a loop through a
+// struct or a reference the compiler may fall back to generic loads, which cost about twice as much per access.
+__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ float4 lds_f32x4(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+
 // Streaming 128-bit load that does not allocate in L1 (weights are read exactly once).
 __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     uint4 v;

@@ -685,7 +685,9 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
             e->allocs.push_back(raw);
             e->tp_buf = static_cast<float *>(raw);
             e->tp.ll_slot = (uint32_t)ll_slot;
-            e->tp.peer_ll[xr] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(raw) + floats * 4 + 256);
+            e->tp.peer_ll[xr] = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(raw) + floats * 4 + 256);
+            e->tp.wait_polls = TP_WAIT_POLLS_DEFAULT;
+            if (const char *v = std::getenv("KRONOS_CUDA_PEER_WAIT_POLLS")) e->tp.wait_polls = (uint32_t)std::strtoul(v, nullptr, 10);
             ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, total, ctx->stream), "clear tp exchange") &&
                  dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
             e->tp.tp = xg; e->tp.rank = xr; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
@@ -760,7 +762,34 @@ int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *e, const uint8_t *handles
         e->tp_peers.push_back(p);
         e->tp.peer_data[r] = static_cast<float *>(p);
         e->tp.peer_flags[r] = reinterpret_cast<uint32_t *>(static_cast<float *>(p) + floats);
-        e->tp.peer_ll[r] = reinterpret_cast<uint2 *>(static_cast<uint8_t *>(p) + floats * 4 + 256);
+        e->tp.peer_ll[r] = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(p) + floats * 4 + 256);
+    }
+    e->tp_ready = true;
+    return 0;
+}
+
+int32_t kronos_cuda_engine_tp_attach_local(KronosCudaEngine *e, KronosCudaEngine *const *engines, size_t n_engines) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!e->tp_buf) return fail(ctx, "tp_attach_local: the engine was created with tp_size <= 1 and ep_size <= 1"), -1;
+    if (!engines || n_engines != e->tp.tp) return fail(ctx, "tp_attach_local: one engine per rank is needed"), -1;
+    if (e->tp_ready) return fail(ctx, "tp_attach_local: already attached"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t floats = 2 * (size_t)e->tp.tp * e->tp.slot;
+    for (uint32_t r = 0; r < e->tp.tp; ++r) {
+        if (r == e->tp.rank) continue;
+        const KronosCudaEngine *o = engines[r];
+        if (!o || !o->tp_buf || o->tp.tp != e->tp.tp || o->tp.rank != r || o->tp.slot != e->tp.slot || o->tp.ll_slot != e->tp.ll_slot)
+            return fail(ctx, "tp_attach_local: engine " + std::to_string(r) + " is not rank " + std::to_string(r) + " of the same group"), -1;
+        if (o->ctx->device != ctx->device) {
+            cudaError_t pe = cudaDeviceEnablePeerAccess(o->ctx->device, 0);
+            if (pe == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (!cuda_ok(ctx, pe, "cudaDeviceEnablePeerAccess")) return -1;
+        }
+        e->tp.peer_data[r] = o->tp_buf;
+        e->tp.peer_flags[r] = reinterpret_cast<uint32_t *>(o->tp_buf + floats);
+        e->tp.peer_ll[r] = reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(o->tp_buf) + floats * 4 + 256);
     }
     e->tp_ready = true;
     return 0;

@@ -547,33 +547,47 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             // 0x4B000000 | (b ^ 0x80) is the float 2^23 + (int8)b + 128, so subtracting 2^23 + 128 gives (float)(int8)b exactly.
             // The CPU loop skips positions whose weight is zero; the plain fma gives the same bits (w >= 0 and the values
             // are finite: o + (+-0) = o, and +0 + (-0) = +0), so the chain is one fma per position.
-            // A warp owns 32 dimensions = 8 words of a row: one 32-bit load per lane fetches those words for FOUR positions
-            // (lane l: word l % 8 of position 4g + l / 8); every lane then takes the word holding its dimension by shuffle.
-            // Byte loads of one's own dimension ran at 40 cycles per position (one shared-memory round trip each).
+            // Every thread reads the byte of its own dimension; sixteen positions (and their weights) are loaded while the
+            // sixteen before them run through the chain, so the chain never waits for shared memory (measured 8.3 cycles
+            // per position against 4.5 for the bare fma chain; a variant that fetched words for four positions and
+            // handed them round by shuffle ran at 18 or more).
             const float *wp = s.sc;
             const uint8_t *vb = reinterpret_cast<const uint8_t *>(s.vbuf);
             auto to_f32 = [](uint32_t b) { return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f); };
-            const uint32_t wbase = tid & ~31u, my_word = lane >> 2, my_sel = 0x7650u + (lane & 3u);
-            const uint8_t *src = vb + (size_t)(lane >> 3) * HD + wbase + 4 * (lane & 7u);
+            const uint32_t vt = (uint32_t)__cvta_generic_to_shared(vb) + tid, wa = (uint32_t)__cvta_generic_to_shared(wp);
             uint32_t j = 0;
-            for (; j + 16 <= pos; j += 16) {
-                uint32_t wd[4];
-                float4 wt[4];
+            if (pos >= 16) {
+                uint32_t cur[16], nxt[16];
+                float4 wc[4], wn[4];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    wd[g] = *reinterpret_cast<const uint32_t *>(src + (size_t)(j + 4 * g) * HD) ^ 0x80808080u;
-                    wt[g] = *reinterpret_cast<const float4 *>(wp + j + 4 * g);
-                }
+                for (int u = 0; u < 16; ++u) cur[u] = lds_u8(vt + u * HD);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const float wr[4] = {wt[g].x, wt[g].y, wt[g].z, wt[g].w};
+                for (int u = 0; u < 4; ++u) wc[u] = lds_f32x4(wa + 16 * u);
+                for (; j + 32 <= pos; j += 16) {
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t word = __shfl_sync(0xffffffffu, wd[g], r * 8 + my_word);
-                        const float val = __fsub_rn(__uint_as_float(prmt(word, 0x4B000000u, my_sel)), 8388736.0f);
-                        o = __fmaf_rn(val, wr[r], o);
+                    for (int u = 0; u < 16; ++u) nxt[u] = lds_u8(vt + (j + 16 + u) * HD);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) wn[u] = lds_f32x4(wa + 4 * (j + 16) + 16 * u);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        o = __fmaf_rn(to_f32(cur[4 * u + 0]), wc[u].x, o);
+                        o = __fmaf_rn(to_f32(cur[4 * u + 1]), wc[u].y, o);
+                        o = __fmaf_rn(to_f32(cur[4 * u + 2]), wc[u].z, o);
+                        o = __fmaf_rn(to_f32(cur[4 * u + 3]), wc[u].w, o);
                     }
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) wc[u] = wn[u];
                 }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    o = __fmaf_rn(to_f32(cur[4 * u + 0]), wc[u].x, o);
+                    o = __fmaf_rn(to_f32(cur[4 * u + 1]), wc[u].y, o);
+                    o = __fmaf_rn(to_f32(cur[4 * u + 2]), wc[u].z, o);
+                    o = __fmaf_rn(to_f32(cur[4 * u + 3]), wc[u].w, o);
+                }
+                j += 16;
             }
             for (; j < pos; ++j) o = __fmaf_rn(to_f32(vb[(size_t)j * HD + tid]), wp[j], o);
             // the current position: its value row is still in shared memory

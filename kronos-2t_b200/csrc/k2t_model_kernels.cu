@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 //
 // Tensor parallel (tp.tp > 1, delta given): delta is this rank's PARTIAL projection output; the ranks' partials are
 // exchanged here, so the residual update needs no launch of its own.  Every element is stored into each peer's buffer
-// as an 8-byte (value, call number) word; the receiver polls (bounded) the words of call e in the half e & 1 of its own
+// as one 64-bit (call number, value) word; the receiver polls (bounded) the words of call e in the half e & 1 of its own
 // buffer and adds the ranks' values in rank order.  A rank cannot be two calls ahead of another (it needs the others'
 // words of call e + 1, sent after they finished call e), so two halves suffice; the call counter is shared with
 // tp_exchange_kernel (k2t_tp.cu) and advanced by the last CTA of the launch to finish.
@@ -66,22 +66,28 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
     uint32_t epoch = 0;
     float *s_d = s_x + n;                    // exchange: the summed delta (the launcher doubles the shared memory)
     if (exchange) {
-        if (tid == 0) s_epoch = *tp.epoch + 1;
+        __shared__ int s_budget;             // polls the CTA may still spend on words that have not arrived (signed: concurrent settlements may overdraw it)
+        if (tid == 0) {
+            s_epoch = *tp.epoch + 1;
+            // a context whose error word is already set (an earlier exchange gave up: a peer has left) does not wait again
+            s_budget = __ldcg(tp.err) != 0 ? 0 : (int)min(tp.wait_polls, 0x40000000u);
+        }
         __syncthreads();
         epoch = s_epoch;
         const size_t half_off = (size_t)(epoch & 1u) * tp.tp * tp.ll_slot + (size_t)tok * n;
-        // send: every element travels with the call number in one 8-byte store, so the receiver needs no fence and
-        // no flag round trip - it polls the words themselves
+        // send: every element travels with the call number in ONE 64-bit store (value in the low half), so the receiver
+        // needs no fence and no flag round trip - it polls the words themselves, and a 64-bit access is single-copy atomic
         for (uint32_t i = tid; i < n; i += nthr) {
-            const uint32_t bits = __float_as_uint(__ldcg(delta + i));
+            const unsigned long long word = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(__ldcg(delta + i));
             for (uint32_t p = 0; p < tp.tp; ++p) {
                 if (p == tp.rank) continue;
-                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(tp.peer_ll[p] + half_off + (size_t)tp.rank * tp.ll_slot + i), "r"(bits), "r"(epoch) : "memory");
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(tp.peer_ll[p] + half_off + (size_t)tp.rank * tp.ll_slot + i), "l"(word) : "memory");
             }
         }
-        // receive and add in rank order, ((v0 + v1) + v2) + ...: the same bits on every rank
-        int failed = 0;
-        const uint2 *mine = tp.peer_ll[tp.rank] + half_off;
+        // receive and add in rank order, ((v0 + v1) + v2) + ...: the same bits on every rank.  The wait is bounded per
+        // kernel, not per word: every miss is charged to the CTA's budget, and once that is spent nobody polls again.
+        int failed = s_budget <= 0 ? 1 : 0;
+        const unsigned long long *mine = tp.peer_ll[tp.rank] + half_off;
         for (uint32_t i = tid; i < n; i += nthr) {
             float acc = 0.0f;
             for (uint32_t r = 0; r < tp.tp; ++r) {
@@ -89,13 +95,16 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
                 if (r == tp.rank) {
                     v = __ldcg(delta + i);
                 } else {
-                    uint32_t bits = 0, seen = 0, polls = 0;
+                    unsigned long long word = 0;
+                    uint32_t misses = 0;
                     for (;;) {
-                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(seen) : "l"(mine + (size_t)r * tp.ll_slot + i) : "memory");
-                        if (seen == epoch) break;
-                        if (++polls > (1u << 22)) { failed = 1; break; }
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(mine + (size_t)r * tp.ll_slot + i) : "memory");
+                        if ((uint32_t)(word >> 32) == epoch || failed) break;
+                        if ((++misses & 63u) == 0) {          // settle the bill every 64 misses; the old balance decides
+                            if (atomicSub(&s_budget, 64) < 64 || misses > tp.wait_polls) { failed = 1; break; }
+                        }
                     }
-                    v = __uint_as_float(bits);
+                    v = __uint_as_float((uint32_t)word);
                 }
                 acc = r == 0 ? v : __fadd_rn(acc, v);
             }

@@ -6,7 +6,7 @@
 // parity picks the data half) does, on every rank r:
 //   1. store its vector into data[e & 1][r] of EVERY rank's buffer (plain peer stores), then a system-scope fence;
 //   2. store e into flags[r] of every rank's buffer (release, system scope);
-//   3. wait until its own flags[0 .. tp) are all >= e (acquire, system scope; bounded: after WAIT_POLLS polls the error word
+//   3. wait until its own flags[0 .. tp) are all >= e (acquire, system scope; bounded: after L.wait_polls polls the error word
 //      is set to 3 and the kernel carries on with whatever is there, so nothing hangs and the host sees the failure);
 //   4. read data[e & 1][0 .. tp) of its OWN buffer through L2 and sum them in rank order, ((v0 + v1) + v2) + ... - every
 //      rank gets the same bits - or copy them side by side (gather).
@@ -18,7 +18,7 @@
 
 namespace k2t {
 
-constexpr uint32_t TP_THREADS = 1024, WAIT_POLLS = 1u << 22;
+constexpr uint32_t TP_THREADS = 1024;
 
 __global__ void __launch_bounds__(TP_THREADS) tp_exchange_kernel(const TpLink L, const float *__restrict__ src, float *__restrict__ dst,
                                                                  uint32_t n, uint32_t gather_stride) {
@@ -38,11 +38,13 @@ __global__ void __launch_bounds__(TP_THREADS) tp_exchange_kernel(const TpLink L,
     int failed = 0;
     if (tid < L.tp) {
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.peer_flags[tid] + L.rank), "r"(e) : "memory");
+        // a context whose error word is already set (an earlier exchange gave up: a peer has left) does not wait again
         uint32_t seen = 0, polls = 0;
+        const uint32_t limit = __ldcg(L.err) != 0 ? 0u : L.wait_polls;
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(L.peer_flags[L.rank] + tid) : "memory");
             if (seen >= e) break;
-            if (++polls > WAIT_POLLS) { failed = 1; break; }
+            if (++polls > limit) { failed = 1; break; }
         }
     }
     if (__syncthreads_or(failed) && tid == 0) atomicExch(L.err, 3u);

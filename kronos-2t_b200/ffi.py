@@ -99,6 +99,7 @@ def load_library():
     sig("kronos_cuda_engine_tp_handle", i32, vp, vp)
     sig("kronos_cuda_engine_tp_attach", i32, vp, vp, sz)
     sig("kronos_cuda_engine_set_embedding_matrix", i32, vp, C.POINTER(MatrixDesc))
+    sig("kronos_cuda_engine_tp_attach_local", i32, vp, C.POINTER(vp), sz)
     sig("kronos_cuda_engine_kv_bytes_per_pos", sz, vp)
     sig("kronos_cuda_engine_kv_export", C.c_int64, vp, sz, sz, vp, sz)
     sig("kronos_cuda_engine_kv_import", i32, vp, vp, sz, sz)
@@ -360,6 +361,11 @@ class Engine:
         """handles: the tp_handle() bytes of every rank, in rank order.  Barrier across the ranks afterwards."""
         blob = np.frombuffer(b"".join(handles), np.uint8).copy()
         self.ctx._check(self.L.kronos_cuda_engine_tp_attach(self.handle, _p(blob), len(handles)))
+
+    def tp_attach_local(self, engines):
+        """engines: every rank's Engine (same process), in rank order."""
+        arr = (C.c_void_p * len(engines))(*[e.handle for e in engines])
+        self.ctx._check(self.L.kronos_cuda_engine_tp_attach_local(self.handle, arr, len(engines)))
 
     def close(self):
         if self.handle:

@@ -41,6 +41,19 @@ dist.destroy_process_group()
 """
 
 
+def _wait_all(procs, timeout=600):
+    """Every child must exit 0; whatever happens, none is left running (a rank whose peer died would otherwise sit in its
+    bounded waits for the rest of the session)."""
+    try:
+        for p in procs:
+            assert p.wait(timeout=timeout) == 0
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+                p.wait()
+
+
 def gpu_count():
     try:
         import torch
@@ -56,8 +69,7 @@ def test_two_rank_engine_matches_rank_order_emulation(oracle, tmp_path, mode, kw
     port = str(31000 + os.getpid() % 2000)
     env = dict(os.environ, PORT=port, OUT=str(tmp_path / "tp"), CFG=repr(TP_CFG), MODE=mode, KW=repr(kw), TOKENS=repr(TOKENS))
     procs = [subprocess.Popen([sys.executable, "-c", "ROOT = %r\n" % ROOT + WORKER], env=dict(env, RANK=str(r))) for r in range(2)]
-    for p in procs:
-        assert p.wait(timeout=600) == 0
+    _wait_all(procs)
     got = [np.load(str(tmp_path / f"tp.{r}.npy")) for r in range(2)]
     greedy = [np.load(str(tmp_path / f"tp.g{r}.npy")) for r in range(2)]
     assert np.array_equal(got[0], got[1]) and np.array_equal(greedy[0], greedy[1])       # every rank ends with the same logits and tokens
@@ -107,8 +119,7 @@ def test_two_rank_expert_parallel_engine_matches_rank_order_emulation(oracle, tm
     port = str(33000 + os.getpid() % 2000)
     env = dict(os.environ, PORT=port, OUT=str(tmp_path / "ep"), MODE=mode, MOE=repr(moe), TOKENS=repr(tokens))
     procs = [subprocess.Popen([sys.executable, "-c", "ROOT = %r\n" % ROOT + EP_WORKER], env=dict(env, RANK=str(r))) for r in range(2)]
-    for p in procs:
-        assert p.wait(timeout=600) == 0
+    _wait_all(procs)
     got = [np.load(str(tmp_path / f"ep.{r}.npy")) for r in range(2)]
     greedy = [np.load(str(tmp_path / f"ep.g{r}.npy")) for r in range(2)]
     assert np.array_equal(got[0], got[1]) and np.array_equal(greedy[0], greedy[1])
@@ -122,3 +133,33 @@ def test_two_rank_expert_parallel_engine_matches_rank_order_emulation(oracle, tm
     assert list(greedy[0]) == out
     emu.close()
 
+
+
+def test_absent_peer_is_reported_not_waited_for(oracle, monkeypatch):
+    """One GPU is enough: rank 0 of a two-rank group is attached to a rank-1 engine that never runs, so the words rank 0
+    polls for are never written.  Its bounded waits run out (a short limit here), the call returns the peer error within
+    seconds and the context remembers it: later calls fail at once instead of waiting again."""
+    import time
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import tp
+    monkeypatch.setenv("KRONOS_CUDA_PEER_WAIT_POLLS", "20000")
+    spec = km.build(oracle, TP_CFG, "b5", seed=3, tied=False)
+    ctxs = [k2.Context(0), k2.Context(0)]
+    engs = [k2.Engine(ctxs[r], tp.shard_spec(spec, 2, r)) for r in range(2)]
+    try:
+        for e in engs:
+            e.tp_attach_local(engs)
+        t0 = time.perf_counter()
+        with pytest.raises(k2.KronosCudaError, match="peer rank"):
+            engs[0].forward_token_ids(TOKENS[:3])
+        first = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        with pytest.raises(k2.KronosCudaError, match="peer rank"):
+            engs[0].forward_token_ids(TOKENS[:1])
+        again = time.perf_counter() - t0
+        assert first < 20.0 and again < 5.0, (first, again)
+    finally:
+        for e in engs:
+            e.close()
+        for c in ctxs:
+            c.close()
