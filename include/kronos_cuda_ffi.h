@@ -245,6 +245,21 @@ size_t kronos_cuda_engine_kv_bytes(const KronosCudaEngine *engine, size_t positi
 size_t kronos_cuda_engine_kv_bytes_per_pos(const KronosCudaEngine *engine);
 int64_t kronos_cuda_engine_kv_export(KronosCudaEngine *engine, size_t lo, size_t hi, uint8_t *out, size_t cap);
 int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *engine, const uint8_t *data, size_t len, size_t n);
+/* RealLlamaEngine::set_kv_bits / set_kv_sliding_window (real_llm.rs:1731-1790) as they reach a device backend
+ * (MetalLlamaEngine::reconfigure_kv, metal_gpu.rs:1561): rebuilds the cache in format kv_bits (8 / 4) and geometry -
+ * window = 0: the full causal context; otherwise the sliding-window + sink ring of QuantizedKvCache::new_with_opts
+ * (real_llm.rs:1235-1257), taken only when 8 <= window and window + 512 < max_seq_len (else the full context is kept, as
+ * in the reference), sinks capped at window / 2, sinks + (window - sinks + 512) cache rows per (layer, kv head).  With a
+ * window every token is attended by causal_gqa_group_q4_or_window's arithmetic (real_llm.rs:8794-8988), bit for bit.
+ * The cache contents are lost; the host continues at position 0.  Not combined with tensor / expert parallelism. */
+int32_t kronos_cuda_engine_reconfigure_kv(KronosCudaEngine *engine, uint32_t kv_bits, size_t window, size_t sinks);
+/* kv_sliding_window (real_llm.rs:1793-1803): returns 1 and the effective (window, sinks) when a ring is active, else 0. */
+int32_t kronos_cuda_engine_kv_sliding_window(const KronosCudaEngine *engine, size_t *window, size_t *sinks);
+/* Cache rows per (layer, kv head): max_seq_len, or sinks + ring length. */
+size_t kronos_cuda_engine_kv_rows(const KronosCudaEngine *engine);
+/* can_truncate_kv_to (real_llm.rs:1806-1821): may a host that stands at cur_pos continue at the earlier target_len
+ * (speculative rollback, truncate_context) without reading ring rows that later positions have overwritten? */
+int32_t kronos_cuda_engine_can_truncate_kv_to(const KronosCudaEngine *engine, size_t cur_pos, size_t target_len);
 /* Bytes of weights (reference file format) one decode step streams: all layer matrices + lm_head. */
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
 /* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */

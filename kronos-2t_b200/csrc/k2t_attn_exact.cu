@@ -49,13 +49,15 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     const uint32_t blk = blockIdx.x, kvh = blockIdx.y, G = a.group;
     pdl_wait();
     pdl_trigger();
-    const uint32_t ctx = __ldcg(a.pos) + a.pos_offset + 1, t0 = blk * SCORE_TILE;
+    // sliding window: ctx = the active positions (sinks + the last window - sinks); index t -> position -> ring row
+    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + 1, ctx = a.ring.active_len(seq_len), t0 = blk * SCORE_TILE;
+    const bool windowed = a.ring.window > 0;
     if (t0 >= ctx) return;
     const uint32_t n = min(SCORE_TILE, ctx - t0);
     const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
     const uint8_t *K = reinterpret_cast<const uint8_t *>(a.k_q8) + (slot0 + t0) * ROW;
     const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&s_bar);
-    if (tid == 0) {
+    if (tid == 0 && !windowed) {
         mbar_init(bar, 1);
         fence_mbar_init();
         asm volatile("fence.proxy.async;" ::: "memory");      // the row qkv_post_kernel stored for this position is read by the copy engine
@@ -77,31 +79,36 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     }
     const uint32_t t = t0 + tid;
     const bool on = tid < n;
+    const uint32_t row = on ? a.ring.slot_of_pos(a.ring.active_pos(t, seq_len)) : 0u;      // cache row of this lane's position
     float kst[KV4 ? NB : 1];
     if (KV4) {
-        const uint16_t *ks16 = reinterpret_cast<const uint16_t *>(a.k_scale) + (slot0 + t) * NB;
+        const uint16_t *ks16 = reinterpret_cast<const uint16_t *>(a.k_scale) + (slot0 + row) * NB;
 #pragma unroll
         for (int b = 0; b < NB; ++b) kst[b] = on ? bf16_bits_to_f32(__ldcg(ks16 + b)) : 0.0f;
     } else {
-        kst[0] = on ? __ldcg(a.k_scale + slot0 + t) : 0.0f;
+        kst[0] = on ? __ldcg(a.k_scale + slot0 + row) : 0.0f;
     }
     float qas[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) qas[g] = g < (int)G ? __fmul_rn(__ldcg(a.q_scale + kvh * G + g), a.attn_scale) : 0.0f;
     __syncthreads();                               // queries staged, barrier initialised
-    const bool arrived = mbar_wait_bounded(bar, 0);
-    if (__syncthreads_or(!arrived)) {
-        if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
-        return;
+    if (!windowed) {
+        const bool arrived = mbar_wait_bounded(bar, 0);
+        if (__syncthreads_or(!arrived)) {
+            if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
+            return;
+        }
     }
-    int up[8][KV4 ? NB : 1], dn[8][KV4 ? NB : 1];
+    int up[8][NB], dn[8][KV4 ? NB : 1];           // integer dots per 64-value group
 #pragma unroll
     for (int g = 0; g < 8; ++g)
 #pragma unroll
-        for (int b = 0; b < (KV4 ? NB : 1); ++b) { up[g][b] = 0; dn[g][b] = 0; }
+        for (int b = 0; b < NB; ++b) { up[g][b] = 0; if (KV4) dn[g][b] = 0; }
     // the 16-byte vectors of a row are visited in a lane-dependent rotation, so that a quarter-warp reads eight different
-    // bank groups (integer sums do not depend on the order); rows beyond n hold stale bytes and their scores are dropped
-    const uint4 *krow = reinterpret_cast<const uint4 *>(s_k + (size_t)tid * ROW);
+    // bank groups (integer sums do not depend on the order); rows beyond n hold stale bytes and their scores are dropped.
+    // With a window the rows are not contiguous in the ring: every lane reads its own row from the cache (L2) instead.
+    const uint4 *krow = windowed ? reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(a.k_q8) + (slot0 + row) * ROW)
+                                 : reinterpret_cast<const uint4 *>(s_k + (size_t)tid * ROW);
     const uint32_t rot = (lane * NV / 8) % NV;
 #pragma unroll
     for (uint32_t v = 0; v < NV; ++v) {
@@ -136,9 +143,10 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
             for (int g = 0; g < 8; ++g) {
                 if (g >= (int)G) break;
                 const int4 qq = *reinterpret_cast<const int4 *>(&s_q[g][4 * vv]);
-                int d = up[g][0];
+                int d = 0;
                 d = __dp4a((int)kk.x, qq.x, d); d = __dp4a((int)kk.y, qq.y, d); d = __dp4a((int)kk.z, qq.z, d); d = __dp4a((int)kk.w, qq.w, d);
-                up[g][0] = d;
+                if (NB == 2 && vv >= NV / 2) up[g][NB - 1] += d;        // vector vv covers dimensions 16 vv .. 16 vv + 15
+                else up[g][0] += d;
             }
         }
     }
@@ -154,8 +162,12 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
                 s = 0.0f;
 #pragma unroll
                 for (int b = 0; b < NB; ++b) s = __fadd_rn(s, __fmul_rn(__fmul_rn((float)(up[g][b] - dn[g][b]), kst[b]), qas[g]));
+            } else if (windowed) {       // causal_gqa_group_q4_or_window with the int8 cache: one scale per slot, still a term per 64-value group
+                s = 0.0f;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) s = __fadd_rn(s, __fmul_rn(__fmul_rn((float)up[g][b], kst[0]), qas[g]));
             } else {
-                const int dot = up[g][0];
+                const int dot = NB == 2 ? up[g][0] + up[g][NB - 1] : up[g][0];
                 s = grouped ? __fmul_rn((float)dot, __fmul_rn(kst[0], qas[g])) : __fmul_rn(__fmul_rn((float)dot, kst[0]), qas[g]);
             }
             a.sc[(size_t)(kvh * G + g) * a.sc_stride + t] = s;
@@ -170,7 +182,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
         for (uint32_t w = 1; w < SCORE_TILE / 32; ++w) m = fmaxf(m, s_red[tid][w]);
         a.bmax[(size_t)(kvh * G + tid) * a.blk_stride + blk] = m;
     }
-    if (tid == 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+    if (tid == 0 && !windowed) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -210,7 +222,8 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     if (KV4 && tid < 16) s_cb[tid] = NF4_KV_CENTROIDS[tid];
     pdl_wait();
     pdl_trigger();
-    const uint32_t ctx = __ldcg(a.pos) + a.pos_offset + 1, cap = a.ctx_cap;
+    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + 1, ctx = a.ring.active_len(seq_len), cap = a.ctx_cap;
+    const KvRing ring = a.ring;
     if (ctx > cap) {                       // the launcher sizes shared memory for the cache length: cannot happen
         if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 5u);
         return;
@@ -223,9 +236,20 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     // ---- producer: lane 0 of warp CW keeps the ring full; the first VAL_NST tiles go out at once
     auto fill = [&](uint32_t i) {
         const uint32_t st = i % VAL_NST, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE);
         fence_proxy_async();
         mbar_expect_tx(bar0 + 8 * st, n * ROW);
-        bulk_g2s((uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE), V + (size_t)tl * ROW, n * ROW, bar0 + 8 * st);
+        // the rows of consecutive active positions are consecutive cache rows except where the sinks end and where the ring
+        // wraps: one bulk copy per run (one run without a window)
+        uint32_t cur = tl;
+        while (cur < tl + n) {
+            const uint32_t p = ring.active_pos(cur, seq_len), row = ring.slot_of_pos(p);
+            uint32_t run = tl + n - cur;
+            if (ring.window > 0 && seq_len > ring.window && cur < ring.sinks) run = min(run, ring.sinks - cur);
+            else if (ring.ring_len > 0 && p >= ring.sinks) run = min(run, ring.sinks + ring.ring_len - row);
+            bulk_g2s(dst + (cur - tl) * ROW, V + (size_t)row * ROW, run * ROW, bar0 + 8 * st);
+            cur += run;
+        }
     };
     if (warp == CW && lane == 0)
         for (uint32_t i = 0; i < VAL_NST && i < n_tiles; ++i) fill(i);
@@ -303,8 +327,9 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
         const uint16_t *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
         for (uint32_t t = tid; t < ctx; t += VAL_THREADS) {
             const float p_norm = __fmul_rn(W[t], inv);
-            if (NB == 2) W[cap + t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + (size_t)t * NB + 1)));
-            W[t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + (size_t)t * NB)));
+            const size_t row = ring.slot_of_pos(ring.active_pos(t, seq_len));
+            if (NB == 2) W[cap + t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + row * NB + 1)));
+            W[t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + row * NB)));
         }
     } else {
         const float *vs = a.v_scale + slot0;
@@ -312,11 +337,11 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
         for (; t + 7 * VAL_THREADS < ctx; t += 8 * VAL_THREADS) {
             float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(vs + t + u * VAL_THREADS);
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(vs + ring.slot_of_pos(ring.active_pos(t + u * VAL_THREADS, seq_len)));
 #pragma unroll
             for (int u = 0; u < 8; ++u) W[t + u * VAL_THREADS] = __fmul_rn(__fmul_rn(W[t + u * VAL_THREADS], inv), v[u]);
         }
-        for (; t < ctx; t += VAL_THREADS) W[t] = __fmul_rn(__fmul_rn(W[t], inv), __ldcg(vs + t));
+        for (; t < ctx; t += VAL_THREADS) W[t] = __fmul_rn(__fmul_rn(W[t], inv), __ldcg(vs + ring.slot_of_pos(ring.active_pos(t, seq_len))));
     }
     __syncthreads();
     VAL_MARK(4);

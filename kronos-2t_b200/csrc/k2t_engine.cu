@@ -55,7 +55,9 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
-    uint32_t kv_stride = 0;                   // cache positions per (layer, kv head): max_seq_len rounded up to 32, so every 32-position tile of rows and scales starts on 16 bytes
+    uint32_t kv_stride = 0;                   // cache rows per (layer, kv head): the rows the geometry needs (max_seq_len, or sinks + ring) rounded up to 32, so every 32-row tile of rows and scales starts on 16 bytes
+    k2t::KvRing ring{};                       // sliding-window + sink ring (all zero: row = position)
+    uint32_t kv_rows = 0;                     // rows in use per (layer, kv head)
     // sparse-MoE workspace: normalised hidden state, per-route expert buffers
     float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr, *router_logits = nullptr;
     uint32_t *router_done = nullptr;
@@ -106,6 +108,49 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
     p = static_cast<T *>(raw);
     if (host) return cuda_ok(e->ctx, cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, e->ctx->stream), "upload");
     return cuda_ok(e->ctx, cudaMemsetAsync(p, 0, bytes, e->ctx->stream), "clear");
+}
+
+void dev_free(KronosCudaEngine *e, void *p) {
+    if (!p) return;
+    for (size_t i = 0; i < e->allocs.size(); ++i)
+        if (e->allocs[i] == p) { e->allocs.erase(e->allocs.begin() + i); break; }
+    cudaFree(p);
+}
+
+// (Re)builds the KV cache: format `bits` (8 / 4) and geometry - the full causal context, or the sliding-window ring of
+// QuantizedKvCache::new_with_opts (real_llm.rs:1235-1257): taken only when 8 <= window and window + 512 < max_seq_len, sinks
+// capped at window / 2, ring = window - sinks + 512 rows of slack for batches.  Also the scratch sized by the cache rows.
+bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sinks) {
+    KronosCudaContext *ctx = e->ctx;
+    KronosCudaEngineConfig &c = e->cfg;
+    if (bits != 8 && bits != 4) return fail(ctx, "kv_bits must be 8 (int8 Hadamard cache) or 4 (NF4 Hadamard cache)");
+    for (void *p : {(void *)e->k_q8, (void *)e->v_q8, (void *)e->k_scale, (void *)e->v_scale, (void *)e->attn_sc, (void *)e->attn_bmax}) dev_free(e, p);
+    e->k_q8 = e->v_q8 = nullptr; e->k_scale = e->v_scale = e->attn_sc = e->attn_bmax = nullptr;
+    c.kv_bits = bits;
+    if (window >= 8 && (uint64_t)window + 512u < c.max_seq_len) {
+        e->ring.window = window;
+        e->ring.sinks = std::min(sinks, window / 2);
+        e->ring.ring_len = (window - e->ring.sinks) + 512u;
+        e->kv_rows = e->ring.sinks + e->ring.ring_len;
+    } else {
+        e->ring = KvRing{};
+        e->kv_rows = c.max_seq_len;
+    }
+    c.kv_window = e->ring.window; c.kv_sinks = e->ring.sinks;
+    e->kv_stride = (e->kv_rows + 31u) & ~31u;
+    const uint32_t hd = c.head_dim, n_q = c.num_attention_heads;
+    // contexts beyond 512 positions: in the CPU's order unless the split-KV kernels were asked for (they know no window) or
+    // the value weights of the longest context would not fit the values kernel's shared memory
+    const uint32_t longest = e->ring.window ? e->ring.window : e->kv_stride;
+    e->split_kv = e->ring.window == 0 && ((c.flags & KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION) != 0 || longest > attention_exact_max_ctx(hd, bits));
+    if (e->ring.window && longest > attention_exact_max_ctx(hd, bits)) return fail(ctx, "kv_window is longer than the attention kernel can hold");
+    const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * e->kv_stride;
+    const bool ok = dev_alloc(e, e->attn_sc, (size_t)n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)n_q * ((e->kv_stride + 127) / 128)) &&
+                    dev_alloc(e, e->k_q8, bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, bits == 4 ? slots * hd / 2 : slots * hd) &&
+                    dev_alloc(e, e->k_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
+                    dev_alloc(e, e->v_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots);
+    for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }      // captured cache pointers are stale
+    return ok;
 }
 
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
@@ -243,7 +288,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
         float *os = e->act_s + (size_t)t * (q_dim / 64);
         int32_t *om = e->act_m + (size_t)t * (q_dim / 64);
         float *tap = (l + 1 == c.num_layers && t + 1 == T) ? e->attn_tap : nullptr;
-        if (!long_ctx) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
+        if (!long_ctx && e->ring.window == 0) {       // contexts of up to ATTN_EXACT_CTX positions: one kernel, CPU summation order
             FusedAttnArgs fa{};
             fa.qkv = qkv_t; fa.bias = L.qkv_bias; fa.q_norm = L.q_norm; fa.k_norm = L.k_norm; fa.rope = e->rope;
             fa.pos = e->d_pos; fa.pos_offset = t;
@@ -261,7 +306,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
             qa.pos = e->d_pos; qa.pos_offset = t;
             qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
             qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
-            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits;
+            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring;
             if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
             if (!e->split_kv) {
                 ExactAttnArgs xa{};
@@ -270,7 +315,8 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
                 xa.sc = e->attn_sc; xa.bmax = e->attn_bmax; xa.attn_out = tap;
                 xa.out_q = oq; xa.out_scales = os; xa.out_sums = om; xa.out_chunk0 = c.o_chunk0;
                 xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
-                xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128; xa.ctx_cap = e->kv_stride;
+                xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
+                xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
                 xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err;
                 xa.trace = (e->attn_trace && l == 0) ? e->d_dbg + 16 : nullptr;
                 return count(e, launch_attention_exact(s, xa, e->pdl), "attention", 2);
@@ -361,24 +407,23 @@ bool set_u32(KronosCudaEngine *e, uint32_t *dst, uint32_t v) {
 }
 
 // Captures one step into an executable graph (first use on the current stream).
-bool ensure_graphs(KronosCudaEngine *e) {
+bool ensure_graphs(KronosCudaEngine *e, size_t warm_pos) {
     KronosCudaContext *ctx = e->ctx;
     if (e->graphs[0] && e->graph_stream == ctx->stream) return true;
     for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
     // eager steps first: loads every kernel and sets its attributes outside a capture, where an error is also
-    // easier to attribute.  They run token 0 at the LAST position of the cache: that slot is only ever read after a
-    // real token has been written to it, so a prompt already in the cache is not disturbed (callers set position
-    // and token before every replay).
-    // The split-KV variant is warmed up at the last cache position too; an NF4 cache of at most ATTN_EXACT_CTX
-    // positions never needs that variant.
-    const int variants = (e->cfg.kv_bits == 8 || e->cfg.max_seq_len > ATTN_EXACT_CTX) ? 2 : 1;
+    // easier to attribute.  They run token 0 at the position the caller is about to run for real: the only cache row
+    // they touch is that position's, which the real step rewrites before anything attends to it, so a prompt already
+    // in the cache (and, with a sliding window, every live row of the ring) stays as it is.  Callers set position and
+    // token before every replay.
+    const int variants = 2;
+    const uint32_t wp = (uint32_t)std::min<size_t>(warm_pos, e->cfg.max_seq_len - 1);
     for (int long_ctx = 0; long_ctx < variants; ++long_ctx)
-        if (!set_u32(e, e->d_pos, e->cfg.max_seq_len - 1) || !set_u32(e, e->d_token, 0) || !enqueue_batch(e, 1, true, Tail::Greedy, long_ctx != 0) ||
+        if (!set_u32(e, e->d_pos, wp) || !set_u32(e, e->d_token, 0) || !enqueue_batch(e, 1, true, Tail::Greedy, long_ctx != 0) ||
             !sync_and_check(ctx, "engine warm-up step"))
             return false;
     const uint64_t launches_before = ctx->launches;
     for (int which = 0; which < 4; ++which) {
-        if ((which & 1) && variants == 1) continue;
         cudaGraph_t graph = nullptr;
         if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return false;
         const bool ok = enqueue_batch(e, 1, true, which < 2 ? Tail::Greedy : Tail::LastLogits, (which & 1) != 0);
@@ -397,16 +442,16 @@ bool ensure_graphs(KronosCudaEngine *e) {
 
 // the graph of one step: greedy (argmax on the device) or logits only, for the context length this position gives
 cudaGraphExec_t step_graph(const KronosCudaEngine *e, bool greedy, size_t pos) {
-    return e->graphs[(greedy ? 0 : 2) + (pos + 1 > ATTN_EXACT_CTX ? 1 : 0)];
+    return e->graphs[(greedy ? 0 : 2) + ((pos + 1 > ATTN_EXACT_CTX || e->ring.window) ? 1 : 0)];
 }
 uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
     if (e->fused) {      // lm_head + argmax; per layer qkv, attention (1 or 3 kernels), o, and gate_up / down or norm / router / two expert GEMVs
         uint32_t n = 2;
-        for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 3 : 1) + (L.moe ? 6 : 4);
+        for (const EngineLayer &L : e->layers) n += ((pos + 1 > ATTN_EXACT_CTX || e->ring.window) ? 3 : 1) + (L.moe ? 6 : 4);
         return n;
     }
     uint32_t n = 1 + 2 + 1 + (e->cfg.tp_size > 1 ? 1 : 0);
-    for (const EngineLayer &L : e->layers) n += (pos + 1 > ATTN_EXACT_CTX ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4; the tensor-parallel sums ride in the norm kernels
+    for (const EngineLayer &L : e->layers) n += ((pos + 1 > ATTN_EXACT_CTX || e->ring.window) ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4; the tensor-parallel sums ride in the norm kernels
     return n;
 }
 
@@ -424,6 +469,7 @@ bool setup_mega(KronosCudaEngine *e) {
     if (!want || want[0] != '1') { e->mega_why = "not requested (KRONOS_CUDA_MEGA=1 enables it)"; return true; }
     if (c.num_attention_heads > (uint32_t)ctx->sm_count) { e->mega_why = "more query heads than SMs"; return true; }
     if (e->has_moe) { e->mega_why = "sparse-MoE layers are served by the per-operator path"; return true; }
+    if (e->ring.window) { e->mega_why = "a sliding KV window is served by the per-operator path"; return true; }
     if (c.tp_size > 1 || c.ep_size > 1) { e->mega_why = "tensor- and expert-parallel ranks are served by the per-operator path"; return true; }
     uint32_t warp_smem = 0;
     auto fill = [&](const KronosCudaMatrix *m, MegaMatrix &mm) {
@@ -611,7 +657,6 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     KronosCudaEngine *e = new (std::nothrow) KronosCudaEngine();
     if (!e) { fail(ctx, "engine_create: out of host memory"); return nullptr; }
     e->ctx = ctx; e->cfg = c;
-    e->kv_stride = (c.max_seq_len + 31u) & ~31u;
     {   // split-KV attention runs one warp per (kv head, split): enough splits to put about eight warps on every SM,
         // at most 128 (a split is at least one 32-position tile of a context above ATTN_EXACT_CTX)
         const uint32_t want = (8u * (uint32_t)ctx->sm_count + c.num_key_value_heads - 1) / c.num_key_value_heads;
@@ -619,7 +664,6 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     }
     if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
     if (const char *v = std::getenv("KRONOS_CUDA_ATTN_TRACE")) e->attn_trace = v[0] == '1';
-    e->split_kv = (c.flags & KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION) != 0 || e->kv_stride > attention_exact_max_ctx(c.head_dim, c.kv_bits);
     if (const char *v = std::getenv("KRONOS_CUDA_FUSED")) e->fused = v[0] == '1';     // measurement switch
     if (c.tp_size > 1 || c.ep_size > 1) e->fused = false;       // the exchanges of the parallel modes live in the norm kernel
     e->layers.resize(c.num_layers);
@@ -655,7 +699,6 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     e->lm_head = kronos_cuda_matrix_upload(ctx, lm_head, 0);
     if (!e->lm_head) return bad("engine_create: lm_head: " + ctx->err);
     e->weight_bytes += e->lm_head->dm.geom.file_bytes;
-    const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * e->kv_stride;
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
               (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)(c.tp_size > 1 ? c.vocab_total : c.vocab_size) * h, embed_bf16)) &&   // every rank keeps the whole table
@@ -667,10 +710,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
-              dev_alloc(e, e->attn_sc, (size_t)n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)n_q * ((e->kv_stride + 127) / 128)) &&
-              dev_alloc(e, e->k_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, c.kv_bits == 4 ? slots * hd / 2 : slots * hd) &&
-              dev_alloc(e, e->k_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
-              dev_alloc(e, e->v_scale, c.kv_bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&
+              alloc_kv(e, c.kv_bits, c.kv_window, c.kv_sinks) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len) && dev_alloc(e, e->d_dbg, 32);
     const uint32_t xg = c.tp_size > 1 ? c.tp_size : c.ep_size, xr = c.tp_size > 1 ? c.tp_rank : c.ep_rank;     // exchange group
@@ -856,7 +896,7 @@ int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *e, uint32_t layer, uint32_t
         return fail(ctx, "read_kv: index out of range"), -1;
     if (e->cfg.kv_bits != 8) return fail(ctx, "read_kv: the engine holds an NF4 cache (use read_kv_q4)"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + position, hd = e->cfg.head_dim;
+    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + e->ring.slot_of_pos((uint32_t)position), hd = e->cfg.head_dim;
     cudaStream_t s = ctx->stream;
     if (!cuda_ok(ctx, cudaMemcpyAsync(k_q8, e->k_q8 + slot * hd, hd, cudaMemcpyDeviceToHost, s), "read_kv") ||
         !cuda_ok(ctx, cudaMemcpyAsync(v_q8, e->v_q8 + slot * hd, hd, cudaMemcpyDeviceToHost, s), "read_kv") ||
@@ -876,7 +916,7 @@ int32_t kronos_cuda_engine_read_kv_q4(KronosCudaEngine *e, uint32_t layer, uint3
         return fail(ctx, "read_kv_q4: index out of range"), -1;
     if (e->cfg.kv_bits != 4) return fail(ctx, "read_kv_q4: the engine holds an int8 cache (use read_kv)"), -1;
     if (!make_current(ctx)) return -1;
-    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + position, hd = e->cfg.head_dim;
+    const size_t slot = ((size_t)layer * e->cfg.num_key_value_heads + kv_head) * e->kv_stride + e->ring.slot_of_pos((uint32_t)position), hd = e->cfg.head_dim;
     const size_t nb = hd / 64;
     cudaStream_t s = ctx->stream;
     if (!cuda_ok(ctx, cudaMemcpyAsync(k_q4, reinterpret_cast<uint8_t *>(e->k_q8) + slot * hd / 2, hd / 2, cudaMemcpyDeviceToHost, s), "read_kv_q4") ||
@@ -906,9 +946,30 @@ int64_t kronos_cuda_engine_kv_export(KronosCudaEngine *e, size_t lo, size_t hi, 
     if (n == 0) return 0;
     if (!out || cap < total) return fail(ctx, "kv_export: output buffer too small"), -1;
     if (!make_current(ctx)) return -1;
-    std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
     const size_t S = e->kv_stride;
     cudaStream_t st = ctx->stream;
+    if (e->ring.ring_len > 0) {           // ring: fetch every row of the (small) cache and pick each position's row
+        const size_t R = e->kv_rows;
+        std::vector<uint8_t> kd(heads * R * db), vd(heads * R * db), ks(heads * R * sb), vs(heads * R * sb);
+        if (!cuda_ok(ctx, cudaMemcpy2DAsync(kd.data(), R * db, e->k_q8, S * db, R * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(vd.data(), R * db, e->v_q8, S * db, R * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(ks.data(), R * sb, e->k_scale, S * sb, R * sb, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(vs.data(), R * sb, e->v_scale, S * sb, R * sb, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
+            !sync_and_check(ctx, "kv_export"))
+            return -1;
+        uint8_t *w = out;
+        for (size_t p = lo; p < hi; ++p) {
+            const size_t r = e->ring.slot_of_pos((uint32_t)p);
+            for (size_t h = 0; h < heads; ++h) {
+                std::memcpy(w, kd.data() + (h * R + r) * db, db); w += db;
+                std::memcpy(w, ks.data() + (h * R + r) * sb, sb); w += sb;
+                std::memcpy(w, vd.data() + (h * R + r) * db, db); w += db;
+                std::memcpy(w, vs.data() + (h * R + r) * sb, sb); w += sb;
+            }
+        }
+        return (int64_t)total;
+    }
+    std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
     if (!cuda_ok(ctx, cudaMemcpy2DAsync(kd.data(), n * db, reinterpret_cast<uint8_t *>(e->k_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(vd.data(), n * db, reinterpret_cast<uint8_t *>(e->v_q8) + lo * db, S * db, n * db, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(ks.data(), n * sb, reinterpret_cast<uint8_t *>(e->k_scale) + lo * sb, S * sb, n * sb, heads, cudaMemcpyDeviceToHost, st), "kv_export") ||
@@ -935,6 +996,28 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, s
     if (!data || len < n * kronos_cuda_engine_kv_bytes_per_pos(e)) return fail(ctx, "kv_import: blob is shorter than n positions"), -1;
     if (!make_current(ctx)) return -1;
     const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->kv_stride;
+    if (e->ring.ring_len > 0) {           // ring: positions go to their rows in order (a later position overwrites the row it shares)
+        const size_t R = e->kv_rows;
+        std::vector<uint8_t> kd(heads * R * db), vd(heads * R * db), ks(heads * R * sb), vs(heads * R * sb);
+        const uint8_t *rd = data;
+        for (size_t p = 0; p < n; ++p) {
+            const size_t row = e->ring.slot_of_pos((uint32_t)p);
+            for (size_t h = 0; h < heads; ++h) {
+                std::memcpy(kd.data() + (h * R + row) * db, rd, db); rd += db;
+                std::memcpy(ks.data() + (h * R + row) * sb, rd, sb); rd += sb;
+                std::memcpy(vd.data() + (h * R + row) * db, rd, db); rd += db;
+                std::memcpy(vs.data() + (h * R + row) * sb, rd, sb); rd += sb;
+            }
+        }
+        cudaStream_t st = ctx->stream;
+        if (!cuda_ok(ctx, cudaMemcpy2DAsync(e->k_q8, S * db, kd.data(), R * db, R * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd.data(), R * db, R * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks.data(), R * sb, R * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+            !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs.data(), R * sb, R * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
+            !sync_and_check(ctx, "kv_import"))
+            return -1;
+        return 0;
+    }
     std::vector<uint8_t> kd(heads * n * db), vd(heads * n * db), ks(heads * n * sb), vs(heads * n * sb);
     const uint8_t *r = data;
     for (size_t p = 0; p < n; ++p)
@@ -954,6 +1037,40 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, s
     return 0;
 }
 
+int32_t kronos_cuda_engine_reconfigure_kv(KronosCudaEngine *e, uint32_t kv_bits, size_t window, size_t sinks) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!make_current(ctx) || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "reconfigure_kv")) return -1;
+    if (e->cfg.tp_size > 1 || e->cfg.ep_size > 1) {
+        if (window != 0) return fail(ctx, "reconfigure_kv: a sliding window is not combined with tensor / expert parallelism"), -1;
+    }
+    if (!alloc_kv(e, kv_bits, (uint32_t)std::min<size_t>(window, 0xffffffffu), (uint32_t)std::min<size_t>(sinks, 0xffffffffu)) ||
+        !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "reconfigure_kv"))
+        return -1;
+    if (e->ring.window) e->mega_ok = false;
+    return 0;
+}
+
+int32_t kronos_cuda_engine_kv_sliding_window(const KronosCudaEngine *e, size_t *window, size_t *sinks) {
+    if (!e) return -1;
+    if (window) *window = e->ring.window;
+    if (sinks) *sinks = e->ring.sinks;
+    return e->ring.window ? 1 : 0;
+}
+
+size_t kronos_cuda_engine_kv_rows(const KronosCudaEngine *e) { return e ? e->kv_rows : 0; }
+
+int32_t kronos_cuda_engine_can_truncate_kv_to(const KronosCudaEngine *e, size_t cur_pos, size_t target_len) {
+    if (!e) return 0;
+    if (target_len >= cur_pos) return 1;
+    if (e->ring.ring_len > 0) {
+        const size_t live = e->ring.window - e->ring.sinks, slack = e->ring.ring_len > live ? e->ring.ring_len - live : 0;
+        return (target_len <= e->ring.sinks || cur_pos - target_len <= slack) ? 1 : 0;
+    }
+    return 1;
+}
+
 static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const uint32_t *tokens, size_t n_tok, size_t pos_start,
                               float *all_logits, float *last_logits) {
     if (!e) return -1;
@@ -968,7 +1085,7 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
             if (tokens[t] >= (e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size)) return fail(ctx, "forward: token id out of range"), -1;
     const size_t h = e->cfg.hidden_size, v = e->cfg.tp_size > 1 ? e->cfg.vocab_total : e->cfg.vocab_size;
     if (tokens && n_tok == 1) {         // one decode step: the captured graph
-        if (!ensure_graphs(e) || !set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
+        if (!ensure_graphs(e, pos_start) || !set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
         if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens, 4, cudaMemcpyHostToDevice, ctx->stream), "copy token") ||
             !cuda_ok(ctx, cudaGraphLaunch(step_graph(e, false, pos_start), ctx->stream), "graph launch"))
             return -1;
@@ -1034,7 +1151,7 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
         if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, vocab_all * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
         return sync_and_check(ctx, "decode_greedy") ? 0 : -1;
     }
-    if (!ensure_graphs(e)) return -1;
+    if (!ensure_graphs(e, pos_start)) return -1;
     const uint32_t init[3] = {first_token, (uint32_t)pos_start, 0u};
     if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, &init[0], 4, cudaMemcpyHostToDevice, ctx->stream), "set token") ||
         !cuda_ok(ctx, cudaMemcpyAsync(e->d_pos, &init[1], 4, cudaMemcpyHostToDevice, ctx->stream), "set pos") ||
@@ -1066,7 +1183,7 @@ int64_t kronos_cuda_engine_profile_step(KronosCudaEngine *e, uint32_t token, siz
     if (!table || cap == 0) return fail(ctx, "profile_step: no output buffer"), -1;
     reps = std::max(1u, reps);
     if (pos + reps > e->cfg.max_seq_len) return fail(ctx, "profile_step: positions beyond max_seq_len"), -1;
-    if (!make_current(ctx) || !ensure_graphs(e)) return -1;          // warm: every kernel loaded, attributes set
+    if (!make_current(ctx) || !ensure_graphs(e, pos)) return -1;          // warm: every kernel loaded, attributes set
     // The step is launched kernel by kernel with a timing event after each one (and one in front), without programmatic
     // overlap, so the time between two events is the kernel between them, run alone on a warm device.  A bounded delay
     // kernel keeps the stream busy while the host queues the step, so the gaps between events hold no launch latency.

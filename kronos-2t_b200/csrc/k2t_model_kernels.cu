@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     }
     if (!is_q && a.kv_bits == 4) {       // NF4 cache entry: packed indices + one bf16 scale per 64 values (store_hadamard_q4_head_raw)
         const uint32_t kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + pos;
+        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + a.ring.slot_of_pos(pos);
         uint8_t *row = reinterpret_cast<uint8_t *>(is_k ? a.k_q8 : a.v_q8) + slot * (hd / 2);
         uint16_t *sc = reinterpret_cast<uint16_t *>(is_k ? a.k_scale : a.v_scale) + slot * nb;
         for (uint32_t b = 0; b < nb; ++b) {
@@ -391,7 +391,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     if (is_q) { dst_q = a.q_i8 + (size_t)head * hd; dst_s = a.q_scale + head; }
     else {
         const uint32_t kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
-        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + pos;
+        const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + a.ring.slot_of_pos(pos);
         dst_q = (is_k ? a.k_q8 : a.v_q8) + slot * hd;
         dst_s = (is_k ? a.k_scale : a.v_scale) + slot;
     }

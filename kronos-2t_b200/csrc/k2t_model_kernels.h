@@ -20,6 +20,27 @@ struct EmbedArgs {               // tied embedding = row of the lm_head matrix (
     int8_t codebook[32];
 };
 
+// Sliding-window + attention-sink KV ring (QuantizedKvCache::new_with_opts, src/model/real_llm.rs:1235-1257): all zero =
+// full causal context, cache row = position.  Otherwise a token attends to positions [0, sinks) and the last
+// window - sinks ones, and position p >= sinks lives in row sinks + (p - sinks) % ring_len.
+struct KvRing {
+    uint32_t window, sinks, ring_len;
+#ifdef __CUDACC__
+    __host__ __device__
+#endif
+    uint32_t slot_of_pos(uint32_t p) const { return (ring_len == 0 || p < sinks) ? p : sinks + (p - sinks) % ring_len; }      // slot_of_pos, 1116-1122
+#ifdef __CUDACC__
+    __host__ __device__
+#endif
+    uint32_t active_len(uint32_t seq_len) const { return (window > 0 && seq_len > window) ? window : seq_len; }              // active_kv_len, 8597-8603
+#ifdef __CUDACC__
+    __host__ __device__
+#endif
+    uint32_t active_pos(uint32_t idx, uint32_t seq_len) const {                                                              // active_kv_pos, 8605-8612
+        return (window > 0 && seq_len > window && idx >= sinks) ? (seq_len - (window - sinks)) + (idx - sinks) : idx;
+    }
+};
+
 struct QkvPostArgs {
     const float *qkv;            // [n_q + 2 n_kv][head_dim]
     const float *bias, *q_norm, *k_norm;     // null when absent
@@ -32,6 +53,7 @@ struct QkvPostArgs {
     uint32_t kv_bits;            // 8: int8 rows + fp32 scale; 4: packed NF4 rows + bf16 scale per 64 values
     float eps;
     int32_t qk_norm_after_rope;
+    KvRing ring;                 // where the position's cache row lives
 };
 
 // Contexts up to this many positions are attended by the single fused kernel; longer ones by the three-kernel path in
@@ -70,6 +92,7 @@ struct ExactAttnArgs {           // attention in the reference's summation order
     float attn_scale;
     uint32_t *err_flag;
     unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (8 words)
+    KvRing ring;                 // sliding window: active positions and their cache rows; scores then follow causal_gqa_group_q4_or_window for both cache formats
 };
 
 struct FusedAttnArgs {           // one layer's attention from the fused qkv vector to the o_proj activation

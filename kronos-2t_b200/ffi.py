@@ -100,6 +100,10 @@ def load_library():
     sig("kronos_cuda_engine_tp_attach", i32, vp, vp, sz)
     sig("kronos_cuda_engine_set_embedding_matrix", i32, vp, C.POINTER(MatrixDesc))
     sig("kronos_cuda_engine_tp_attach_local", i32, vp, C.POINTER(vp), sz)
+    sig("kronos_cuda_engine_reconfigure_kv", i32, vp, u32, sz, sz)
+    sig("kronos_cuda_engine_kv_sliding_window", i32, vp, C.POINTER(sz), C.POINTER(sz))
+    sig("kronos_cuda_engine_kv_rows", sz, vp)
+    sig("kronos_cuda_engine_can_truncate_kv_to", i32, vp, sz, sz)
     sig("kronos_cuda_engine_kv_bytes_per_pos", sz, vp)
     sig("kronos_cuda_engine_kv_export", C.c_int64, vp, sz, sz, vp, sz)
     sig("kronos_cuda_engine_kv_import", i32, vp, vp, sz, sz)
@@ -361,6 +365,25 @@ class Engine:
         """handles: the tp_handle() bytes of every rank, in rank order.  Barrier across the ranks afterwards."""
         blob = np.frombuffer(b"".join(handles), np.uint8).copy()
         self.ctx._check(self.L.kronos_cuda_engine_tp_attach(self.handle, _p(blob), len(handles)))
+
+    def reconfigure_kv(self, kv_bits, window=0, sinks=0):
+        """set_kv_bits + set_kv_sliding_window: a fresh cache in the given format / geometry (continue at position 0)."""
+        self.ctx._check(self.L.kronos_cuda_engine_reconfigure_kv(self.handle, kv_bits, window, sinks))
+        self.cfg.kv_bits = kv_bits
+
+    @property
+    def kv_sliding_window(self):
+        """(window, sinks) of the active ring, or None."""
+        w, s = C.c_size_t(0), C.c_size_t(0)
+        on = self.L.kronos_cuda_engine_kv_sliding_window(self.handle, C.byref(w), C.byref(s))
+        return (w.value, s.value) if on == 1 else None
+
+    @property
+    def kv_rows(self):
+        return self.L.kronos_cuda_engine_kv_rows(self.handle)
+
+    def can_truncate_kv_to(self, cur_pos, target_len):
+        return bool(self.L.kronos_cuda_engine_can_truncate_kv_to(self.handle, cur_pos, target_len))
 
     def tp_attach_local(self, engines):
         """engines: every rank's Engine (same process), in rank order."""

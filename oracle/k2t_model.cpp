@@ -109,7 +109,27 @@ struct K2oModel {
     std::vector<float> tap_hidden;    // hidden state after every layer [layers][hidden]
     std::vector<float> tap_attn;      // attention output of the last layer, last token [n_q * head_dim]
 
-    size_t kv_slot(size_t l, size_t h, size_t p) const { return (l * cfg.n_kv + h) * cfg.max_seq + p; }
+    // sliding-window + sink ring (QuantizedKvCache::new_with_opts, real_llm.rs:1235-1257; zero = full causal context)
+    size_t window = 0, sinks = 0, ring_len = 0;
+    size_t cap = 0;                   // cache rows per (layer, kv head): max_seq, or sinks + ring_len
+
+    // QuantKvRawPtrs::slot_of_pos (real_llm.rs:1116-1122)
+    size_t slot_of_pos(size_t p) const { return (ring_len == 0 || p < sinks) ? p : sinks + ((p - sinks) % ring_len); }
+    size_t kv_slot(size_t l, size_t h, size_t p) const { return (l * cfg.n_kv + h) * cap + slot_of_pos(p); }
+    // active_kv_len / active_kv_pos (real_llm.rs:8597-8612)
+    size_t active_len(size_t seq_len) const { return (window > 0 && seq_len > window) ? window : seq_len; }
+    size_t active_pos(size_t idx, size_t seq_len) const {
+        return (window > 0 && seq_len > window && idx >= sinks) ? (seq_len - (window - sinks)) + (idx - sinks) : idx;
+    }
+    void alloc_cache() {
+        const size_t slots = (size_t)cfg.layers * cfg.n_kv * cap, hd = cfg.head_dim;
+        k_q8.clear(); v_q8.clear(); k_sc.clear(); v_sc.clear(); k_q4.clear(); v_q4.clear(); k_s16.clear(); v_s16.clear();
+        if (cfg.kv_bits == 8) {
+            k_q8.assign(slots * hd, 0); v_q8.assign(slots * hd, 0); k_sc.assign(slots, 0.0f); v_sc.assign(slots, 0.0f);
+        } else {
+            k_q4.assign(slots * hd / 2, 0x88); v_q4.assign(slots * hd / 2, 0x88); k_s16.assign(slots * hd / 64, 0); v_s16.assign(slots * hd / 64, 0);
+        }
+    }
 };
 
 namespace {
@@ -302,6 +322,80 @@ void attend_head_q4(const K2oModel &m, size_t l, size_t kvh, const float *q_head
     std::memcpy(out, o, hd * sizeof(float));
 }
 
+// causal_gqa_group_q4_or_window (8794-8988) with a sliding window configured, either cache format: the active positions
+// are the sinks and the last window - sinks positions (all positions while the context is shorter than the window), rows
+// come from their ring slots; scores add ((dot_g * ks) * q_s) per 64-value group for BOTH formats (the int8 cache uses the
+// slot's one scale for every group), values accumulate one fma per element in active-index order.
+void attend_head_window(const K2oModel &m, size_t l, size_t kvh, const float *q_head, size_t seq_len, float attn_scale,
+                        std::vector<float> &sc, float *out) {
+    const size_t hd = m.cfg.head_dim, gph = hd / 64, half = hd / 2, act = m.active_len(seq_len);
+    const bool q4 = m.cfg.kv_bits == 4;
+    int8_t qi[128];
+    float qs;
+    quant_head(q_head, hd, qi, &qs);
+    const float q_s = qs * attn_scale;
+    sc.resize(act);
+    for (size_t idx = 0; idx < act; ++idx) {
+        const size_t slot = m.kv_slot(l, kvh, m.active_pos(idx, seq_len));
+        float total = 0.0f;
+        for (size_t g = 0; g < gph; ++g) {
+            int32_t dot = 0;
+            float ks;
+            if (q4) {
+                ks = bf16_f32(m.k_s16[slot * gph + g]);
+                const uint8_t *kp = m.k_q4.data() + slot * half + g * 32;
+                for (size_t h = 0; h < 2; ++h)
+                    for (size_t i = 0; i < 16; ++i) {
+                        const uint8_t b = kp[h * 16 + i];
+                        dot += (int32_t)NF4_CB[b & 15] * qi[g * 64 + h * 32 + i] + (int32_t)NF4_CB[b >> 4] * qi[g * 64 + h * 32 + 16 + i];
+                    }
+            } else {
+                ks = m.k_sc[slot];
+                const int8_t *kp = m.k_q8.data() + slot * hd + g * 64;
+                for (size_t i = 0; i < 64; ++i) dot += (int32_t)kp[i] * (int32_t)qi[g * 64 + i];
+            }
+            total += ((float)dot * ks) * q_s;
+        }
+        sc[idx] = total;
+    }
+    float mx = -INFINITY;
+    for (size_t t = 0; t < act; ++t) mx = std::max(mx, sc[t]);
+    float acc[4] = {0, 0, 0, 0};
+    size_t t = 0;
+    for (; t + 4 <= act; t += 4)
+        for (int j = 0; j < 4; ++j) { float e = exp_poly(sc[t + j] - mx); sc[t + j] = e; acc[j] += e; }
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    for (; t < act; ++t) { float e = (float)std::exp((double)(sc[t] - mx)); sc[t] = e; sum += e; }
+    const float inv = 1.0f / sum;
+    float o[128] = {0};
+    for (size_t idx = 0; idx < act; ++idx) {
+        const float p_norm = sc[idx] * inv;
+        if (p_norm == 0.0f) continue;
+        const size_t slot = m.kv_slot(l, kvh, m.active_pos(idx, seq_len));
+        if (q4) {
+            for (size_t g = 0; g < gph; ++g) {
+                const float w = p_norm * bf16_f32(m.v_s16[slot * gph + g]);
+                if (w == 0.0f) continue;
+                const uint8_t *vp = m.v_q4.data() + slot * half + g * 32;
+                for (size_t h = 0; h < 2; ++h)
+                    for (size_t i = 0; i < 16; ++i) {
+                        const uint8_t b = vp[h * 16 + i];
+                        float &lo = o[g * 64 + h * 32 + i], &hi = o[g * 64 + h * 32 + 16 + i];
+                        lo = std::fmaf((float)NF4_CB[b & 15], w, lo);
+                        hi = std::fmaf((float)NF4_CB[b >> 4], w, hi);
+                    }
+            }
+        } else {
+            const float w = p_norm * m.v_sc[slot];
+            if (w == 0.0f) continue;
+            const int8_t *vp = m.v_q8.data() + slot * hd;
+            for (size_t i = 0; i < hd; ++i) o[i] = std::fmaf((float)vp[i], w, o[i]);
+        }
+    }
+    k2o_ifwht64(o, hd, 0);
+    std::memcpy(out, o, hd * sizeof(float));
+}
+
 // The platform expf of the reference's scalar paths, replaced by the correctly rounded value (see attend_head).
 inline float exp_cr(float x) { return (float)std::exp((double)x); }
 
@@ -462,21 +556,40 @@ K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table) {
     m->cfg = *cfg;
     m->rope.assign(rope_table, rope_table + (size_t)cfg->max_seq * cfg->head_dim);
     m->layers.resize(cfg->layers);
-    size_t slots = (size_t)cfg->layers * cfg->n_kv * cfg->max_seq;
     if (m->cfg.kv_bits == 0) m->cfg.kv_bits = 8;
     if (m->cfg.kv_bits != 8 && m->cfg.kv_bits != 4) return nullptr;
-    if (m->cfg.kv_bits == 8) {
-        m->k_q8.assign(slots * cfg->head_dim, 0);
-        m->v_q8.assign(slots * cfg->head_dim, 0);
-        m->k_sc.assign(slots, 0.0f);
-        m->v_sc.assign(slots, 0.0f);
-    } else {
-        m->k_q4.assign(slots * cfg->head_dim / 2, 0x88);
-        m->v_q4.assign(slots * cfg->head_dim / 2, 0x88);
-        m->k_s16.assign(slots * cfg->head_dim / 64, 0);
-        m->v_s16.assign(slots * cfg->head_dim / 64, 0);
-    }
+    m->cap = cfg->max_seq;
+    m->alloc_cache();
     return m.release();
+}
+
+// set_kv_sliding_window (real_llm.rs:1764-1790) + QuantizedKvCache::new_with_opts (1235-1257): a window is taken only when
+// 8 <= window and window + 512 < max_seq; sinks are capped at window / 2; the ring keeps 512 rows of slack for batches.
+int k2o_model_set_kv_window(K2oModel *m, uint32_t kv_bits, size_t window, size_t sinks) {
+    if (!m || (kv_bits != 8 && kv_bits != 4)) return -1;
+    m->cfg.kv_bits = kv_bits;
+    if (window >= 8 && window + 512 < m->cfg.max_seq) {
+        m->window = window;
+        m->sinks = std::min(sinks, window / 2);
+        m->ring_len = (window - m->sinks) + 512;
+        m->cap = m->sinks + m->ring_len;
+    } else {
+        m->window = m->sinks = m->ring_len = 0;
+        m->cap = m->cfg.max_seq;
+    }
+    m->alloc_cache();
+    m->pos = 0;
+    return m->window > 0 ? 1 : 0;
+}
+size_t k2o_model_kv_rows(const K2oModel *m) { return m ? m->cap : 0; }
+// can_truncate_kv_to (real_llm.rs:1806-1821)
+int k2o_model_can_truncate_kv_to(const K2oModel *m, size_t target_len) {
+    if (!m || target_len >= m->pos) return 1;
+    if (m->ring_len > 0) {
+        const size_t live = m->window - m->sinks, slack = m->ring_len > live ? m->ring_len - live : 0;
+        return (target_len <= m->sinks || (m->pos - target_len) <= slack) ? 1 : 0;
+    }
+    return 1;
 }
 
 void k2o_model_free(K2oModel *m) { delete m; }
@@ -538,7 +651,7 @@ size_t k2o_model_kv_export(const K2oModel *m, size_t lo, size_t hi, uint8_t *out
     const uint8_t *vs = q4 ? reinterpret_cast<const uint8_t *>(m->v_s16.data()) : reinterpret_cast<const uint8_t *>(m->v_sc.data());
     for (size_t p = lo; p < hi; ++p)
         for (size_t h = 0; h < heads; ++h) {
-            const size_t slot = h * m->cfg.max_seq + p;
+            const size_t slot = h * m->cap + m->slot_of_pos(p);
             std::memcpy(out, kd + slot * db, db); out += db;
             std::memcpy(out, ks + slot * sb, sb); out += sb;
             std::memcpy(out, vd + slot * db, db); out += db;
@@ -557,7 +670,7 @@ int k2o_model_kv_import(K2oModel *m, const uint8_t *data, size_t len, size_t n) 
     uint8_t *vs = q4 ? reinterpret_cast<uint8_t *>(m->v_s16.data()) : reinterpret_cast<uint8_t *>(m->v_sc.data());
     for (size_t p = 0; p < n; ++p)
         for (size_t h = 0; h < heads; ++h) {
-            const size_t slot = h * m->cfg.max_seq + p;
+            const size_t slot = h * m->cap + m->slot_of_pos(p);
             std::memcpy(kd + slot * db, data, db); data += db;
             std::memcpy(ks + slot * sb, data, sb); data += sb;
             std::memcpy(vd + slot * db, data, db); data += db;
@@ -623,7 +736,8 @@ int k2o_model_attn_part(K2oModel *m, uint32_t l, const float *hidden, float *out
         }
     }
     for (size_t qh = 0; qh < c.n_q; ++qh)
-        (c.kv_bits == 4 ? attend_head_q4 : attend_head)(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc, attn.data() + qh * hd);
+        (m->window > 0 ? attend_head_window : c.kv_bits == 4 ? attend_head_q4 : attend_head)(*m, l, qh / group, q + qh * hd, pos + 1, attn_scale, sc,
+                                                                                           attn.data() + qh * hd);
     if (l + 1 == c.layers) m->tap_attn = attn;
     act.populate(attn.data(), q_dim, c.o_chunk0);
     L.o.gemv(act.q.data(), act.s.data(), act.m.data(), out, threads);

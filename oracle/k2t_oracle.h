@@ -154,6 +154,14 @@ typedef struct K2oConfig {
 } K2oConfig;
 typedef struct K2oModel K2oModel;
 K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table);
+/* RealLlamaEngine::set_kv_bits / set_kv_sliding_window (real_llm.rs:1731-1790): rebuilds the cache in the given format and,
+ * when 8 <= window and window + 512 < max_seq, as a ring of sinks + (window - sinks + 512) rows per (layer, kv head);
+ * resets the position.  Returns 1 when a window is active, 0 when the full causal context is kept, -1 on error. */
+int k2o_model_set_kv_window(K2oModel *m, uint32_t kv_bits, size_t window, size_t sinks);
+/* cache rows per (layer, kv head) */
+size_t k2o_model_kv_rows(const K2oModel *m);
+/* can_truncate_kv_to (real_llm.rs:1806-1821): may the context be cut back to target_len without ring aliasing? */
+int k2o_model_can_truncate_kv_to(const K2oModel *m, size_t target_len);
 void k2o_model_free(K2oModel *m);
 int k2o_model_set_layer(K2oModel *m, uint32_t l, const float *input_norm, const float *post_norm, const float *qkv_bias,
                         const float *q_norm, const float *k_norm, const K2oMatrixDesc *qkv, const K2oMatrixDesc *o,

@@ -409,6 +409,9 @@ def _declare_model(L):
     L.k2o_model_reset.restype, L.k2o_model_reset.argtypes = None, [P]
     L.k2o_model_pos.restype, L.k2o_model_pos.argtypes = C.c_size_t, [P]
     L.k2o_model_set_pos.restype, L.k2o_model_set_pos.argtypes = None, [P, C.c_size_t]
+    L.k2o_model_set_kv_window.restype, L.k2o_model_set_kv_window.argtypes = C.c_int, [P, C.c_uint32, C.c_size_t, C.c_size_t]
+    L.k2o_model_kv_rows.restype, L.k2o_model_kv_rows.argtypes = C.c_size_t, [P]
+    L.k2o_model_can_truncate_kv_to.restype, L.k2o_model_can_truncate_kv_to.argtypes = C.c_int, [P, C.c_size_t]
     L.k2o_model_embed.restype, L.k2o_model_embed.argtypes = None, [P, C.c_uint32, P]
     L.k2o_model_forward_embedding.restype, L.k2o_model_forward_embedding.argtypes = C.c_int, [P, P, P, C.c_size_t]
     L.k2o_model_forward_token.restype, L.k2o_model_forward_token.argtypes = C.c_int, [P, C.c_uint32, P, C.c_size_t]
@@ -553,6 +556,22 @@ class Model:
         d = desc_of(spec["lm_head"])
         fn = _c(spec["final_norm"], np.float32)
         assert L.k2o_model_set_head(self.h, _ptr(fn), C.byref(d), _ptr(emb)) == 0
+        if int(c.get("kv_window", 0)) > 0:
+            self.set_kv_window(int(c.get("kv_bits", 8)), int(c["kv_window"]), int(c.get("kv_sinks", 0)))
+
+    def set_kv_window(self, kv_bits, window, sinks):
+        """set_kv_bits + set_kv_sliding_window: rebuilds the cache (position 0); True when the window is active."""
+        rc = self.L.k2o_model_set_kv_window(self.h, kv_bits, window, sinks)
+        assert rc >= 0
+        self.cfg.kv_bits = kv_bits
+        return rc == 1
+
+    @property
+    def kv_rows(self):
+        return self.L.k2o_model_kv_rows(self.h)
+
+    def can_truncate_kv_to(self, target_len):
+        return bool(self.L.k2o_model_can_truncate_kv_to(self.h, target_len))
 
     def close(self):
         if self.h:

@@ -185,3 +185,31 @@ def test_moe_router_scoring_modes(oracle, scoring, norm):
     assert list(ids) == list(top[order])
     assert np.allclose(w, p[order], rtol=1e-4, atol=1e-6)
     m.close(); m2.close()
+
+
+def test_sliding_window_ring_geometry_and_rollback_guard(oracle):
+    """QuantizedKvCache::new_with_opts (real_llm.rs:1235-1257) and can_truncate_kv_to (1806-1821) as restated in the oracle:
+    ring rows = sinks + (window - sinks) + 512, sinks capped at window / 2, a window is ignored unless window + 512 < max_seq;
+    the reference test's three rollback cases at position 640 (real_llm.rs:10630-10632); while the context is shorter than
+    the window the windowed attention agrees with the full one to rounding (it adds one score term per 64-value group)."""
+    import k2t_models as km
+    cfg = dict(hidden=128, layers=2, n_q=4, n_kv=2, head_dim=64, inter=256, vocab=192, max_seq=1024, eps=1e-5, theta=1e5)
+    spec = km.build(oracle, cfg, "b4", seed=5)
+    full, win = oracle.Model(spec), oracle.Model(dict(spec, cfg=dict(cfg, kv_bits=4, kv_window=16, kv_sinks=4)))
+    try:
+        assert win.kv_rows == 4 + 12 + 512 and full.kv_rows == 1024
+        assert not full.set_kv_window(8, 600, 4) and full.kv_rows == 1024          # 600 + 512 >= 1024: full context kept
+        assert full.set_kv_window(8, 100, 80) and full.kv_rows == 50 + 50 + 512      # sinks capped at window / 2
+        assert not full.set_kv_window(8, 0, 0)
+        tokens = [(i * 13 + 5) % 192 for i in range(640)]
+        for t in tokens:
+            win.forward_token(t, threads=2)
+        assert win.can_truncate_kv_to(0) and not win.can_truncate_kv_to(8) and win.can_truncate_kv_to(638)
+        short = oracle.Model(dict(spec, cfg=dict(cfg, kv_window=64, kv_sinks=4)))
+        full.reset()
+        for t in tokens[:60]:
+            a, b = full.forward_token(t, threads=2), short.forward_token(t, threads=2)
+            assert np.max(np.abs(a - b)) <= 1e-5 * max(1.0, float(np.max(np.abs(a))))
+        short.close()
+    finally:
+        full.close(); win.close()
