@@ -260,6 +260,15 @@ size_t kronos_cuda_engine_kv_rows(const KronosCudaEngine *engine);
 /* can_truncate_kv_to (real_llm.rs:1806-1821): may a host that stands at cur_pos continue at the earlier target_len
  * (speculative rollback, truncate_context) without reading ring rows that later positions have overwritten? */
 int32_t kronos_cuda_engine_can_truncate_kv_to(const KronosCudaEngine *engine, size_t cur_pos, size_t target_len);
+/* KV prefix snapshots (KvPrefixSnapshot::Q8 / Q4 with RealLlamaEngine::save_kv_prefix / restore_kv_prefix_slice,
+ * real_llm.rs:5821-6155; the Metal backend's twin, metal_gpu.rs:1454-1617): a head-major copy of the first min(n, cur_pos)
+ * cache rows of every (layer, kv head) - of the whole ring when a sliding window is active - for prompt caches and
+ * speculative rollback.  Blob: 32-byte header ("K2TKVPFX", kv_bits, slots_per_head, heads, head_dim, 0, 0 as u32) followed by
+ * the snapshot's four vectors in field order (key rows, value rows, key scales, value scales).  restore copies the first
+ * min(slots_per_head, copy_slots) rows back (copy_slots = SIZE_MAX: all); the host then continues at its own position. */
+size_t kronos_cuda_engine_kv_prefix_bytes(const KronosCudaEngine *engine, size_t n, size_t cur_pos);
+int64_t kronos_cuda_engine_save_kv_prefix(KronosCudaEngine *engine, size_t n, size_t cur_pos, uint8_t *out, size_t cap);
+int32_t kronos_cuda_engine_restore_kv_prefix(KronosCudaEngine *engine, const uint8_t *data, size_t len, size_t copy_slots);
 /* Bytes of weights (reference file format) one decode step streams: all layer matrices + lm_head. */
 size_t kronos_cuda_engine_weight_bytes(const KronosCudaEngine *engine);
 /* Diagnostic: hidden state [hidden] after the last forwarded token (before the final norm). */

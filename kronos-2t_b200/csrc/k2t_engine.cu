@@ -149,8 +149,12 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
                     dev_alloc(e, e->k_q8, bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, bits == 4 ? slots * hd / 2 : slots * hd) &&
                     dev_alloc(e, e->k_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
                     dev_alloc(e, e->v_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots);
+    // unwritten NF4 rows hold index 8 in both nibbles, as in the reference's fresh cache (vec![0x88; ..], real_llm.rs:1278-1279)
+    const bool filled = !ok || bits != 4 ||
+                        (cuda_ok(ctx, cudaMemsetAsync(e->k_q8, 0x88, slots * hd / 2, ctx->stream), "fill cache") &&
+                         cuda_ok(ctx, cudaMemsetAsync(e->v_q8, 0x88, slots * hd / 2, ctx->stream), "fill cache"));
     for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }      // captured cache pointers are stale
-    return ok;
+    return ok && filled;
 }
 
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
@@ -1069,6 +1073,68 @@ int32_t kronos_cuda_engine_can_truncate_kv_to(const KronosCudaEngine *e, size_t 
         return (target_len <= e->ring.sinks || cur_pos - target_len <= slack) ? 1 : 0;
     }
     return 1;
+}
+
+// ---- KV prefix snapshots (KvPrefixSnapshot::Q8 / Q4, RealLlamaEngine::save_kv_prefix / restore_kv_prefix_slice,
+// real_llm.rs:5821-6155): head-major copies of the first rows of every (layer, kv head) - the first n positions, or the
+// whole ring when a sliding window is active.  Blob = 32-byte header {"K2TKVPFX", kv_bits, slots_per_head, heads, head_dim,
+// 0, 0} + the snapshot's four vectors in field order: key rows, value rows, key scales, value scales.
+static const char KV_PREFIX_MAGIC[8] = {'K', '2', 'T', 'K', 'V', 'P', 'F', 'X'};
+
+size_t kronos_cuda_engine_kv_prefix_bytes(const KronosCudaEngine *e, size_t n, size_t cur_pos) {
+    if (!e) return 0;
+    const size_t len = std::min(n, cur_pos), slots = e->ring.ring_len > 0 ? e->kv_rows : std::min<size_t>(len, e->kv_rows);
+    const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads;
+    return 32 + 2 * heads * slots * (kv_row_bytes(e) + kv_scale_bytes(e));
+}
+
+int64_t kronos_cuda_engine_save_kv_prefix(KronosCudaEngine *e, size_t n, size_t cur_pos, uint8_t *out, size_t cap) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    const size_t total = kronos_cuda_engine_kv_prefix_bytes(e, n, cur_pos);
+    if (!out || cap < total) return fail(ctx, "save_kv_prefix: output buffer too small"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t len = std::min(n, cur_pos), slots = e->ring.ring_len > 0 ? e->kv_rows : std::min<size_t>(len, e->kv_rows);
+    const size_t heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->kv_stride;
+    std::memcpy(out, KV_PREFIX_MAGIC, 8);
+    const uint32_t hdr[6] = {e->cfg.kv_bits, (uint32_t)slots, (uint32_t)heads, e->cfg.head_dim, 0u, 0u};
+    std::memcpy(out + 8, hdr, 24);
+    if (slots == 0) return (int64_t)total;
+    uint8_t *kd = out + 32, *vd = kd + heads * slots * db, *ks = vd + heads * slots * db, *vs = ks + heads * slots * sb;
+    cudaStream_t st = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpy2DAsync(kd, slots * db, e->k_q8, S * db, slots * db, heads, cudaMemcpyDeviceToHost, st), "save_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(vd, slots * db, e->v_q8, S * db, slots * db, heads, cudaMemcpyDeviceToHost, st), "save_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(ks, slots * sb, e->k_scale, S * sb, slots * sb, heads, cudaMemcpyDeviceToHost, st), "save_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(vs, slots * sb, e->v_scale, S * sb, slots * sb, heads, cudaMemcpyDeviceToHost, st), "save_kv_prefix") ||
+        !sync_and_check(ctx, "save_kv_prefix"))
+        return -1;
+    return (int64_t)total;
+}
+
+int32_t kronos_cuda_engine_restore_kv_prefix(KronosCudaEngine *e, const uint8_t *data, size_t len, size_t copy_slots) {
+    if (!e) return -1;
+    KronosCudaContext *ctx = e->ctx;
+    ctx->err.clear();
+    if (!data || len < 32 || std::memcmp(data, KV_PREFIX_MAGIC, 8) != 0) return fail(ctx, "restore_kv_prefix: not a KV prefix snapshot"), -1;
+    uint32_t hdr[6];
+    std::memcpy(hdr, data + 8, 24);
+    const size_t slots = hdr[1], heads = (size_t)e->cfg.num_layers * e->cfg.num_key_value_heads, db = kv_row_bytes(e), sb = kv_scale_bytes(e), S = e->kv_stride;
+    if (hdr[0] != e->cfg.kv_bits || hdr[2] != heads || hdr[3] != e->cfg.head_dim) return fail(ctx, "restore_kv_prefix: the snapshot was taken from a cache of another format or shape"), -1;
+    if (len < 32 + 2 * heads * slots * (db + sb)) return fail(ctx, "restore_kv_prefix: snapshot is shorter than its header says"), -1;
+    const size_t cp = std::min(slots, copy_slots);
+    if (cp > e->kv_rows) return fail(ctx, "restore_kv_prefix: the snapshot holds more rows than the cache"), -1;
+    if (cp == 0) return 0;
+    if (!make_current(ctx)) return -1;
+    const uint8_t *kd = data + 32, *vd = kd + heads * slots * db, *ks = vd + heads * slots * db, *vs = ks + heads * slots * sb;
+    cudaStream_t st = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpy2DAsync(e->k_q8, S * db, kd, slots * db, cp * db, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd, slots * db, cp * db, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks, slots * sb, cp * sb, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
+        !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs, slots * sb, cp * sb, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
+        !sync_and_check(ctx, "restore_kv_prefix"))
+        return -1;
+    return 0;
 }
 
 static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const uint32_t *tokens, size_t n_tok, size_t pos_start,

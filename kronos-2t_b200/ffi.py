@@ -100,6 +100,9 @@ def load_library():
     sig("kronos_cuda_engine_tp_attach", i32, vp, vp, sz)
     sig("kronos_cuda_engine_set_embedding_matrix", i32, vp, C.POINTER(MatrixDesc))
     sig("kronos_cuda_engine_tp_attach_local", i32, vp, C.POINTER(vp), sz)
+    sig("kronos_cuda_engine_kv_prefix_bytes", sz, vp, sz, sz)
+    sig("kronos_cuda_engine_save_kv_prefix", C.c_int64, vp, sz, sz, vp, sz)
+    sig("kronos_cuda_engine_restore_kv_prefix", i32, vp, vp, sz, sz)
     sig("kronos_cuda_engine_reconfigure_kv", i32, vp, u32, sz, sz)
     sig("kronos_cuda_engine_kv_sliding_window", i32, vp, C.POINTER(sz), C.POINTER(sz))
     sig("kronos_cuda_engine_kv_rows", sz, vp)
@@ -365,6 +368,18 @@ class Engine:
         """handles: the tp_handle() bytes of every rank, in rank order.  Barrier across the ranks afterwards."""
         blob = np.frombuffer(b"".join(handles), np.uint8).copy()
         self.ctx._check(self.L.kronos_cuda_engine_tp_attach(self.handle, _p(blob), len(handles)))
+
+    def save_kv_prefix(self, n, cur_pos):
+        """KvPrefixSnapshot of the first min(n, cur_pos) positions (the whole ring with a sliding window), as a blob."""
+        out = np.empty(self.L.kronos_cuda_engine_kv_prefix_bytes(self.handle, n, cur_pos), np.uint8)
+        got = self.L.kronos_cuda_engine_save_kv_prefix(self.handle, n, cur_pos, _p(out), out.size)
+        if got < 0:
+            raise KronosCudaError(self.L.kronos_cuda_last_error(self.ctx.handle).decode())
+        return out[:got]
+
+    def restore_kv_prefix(self, blob, copy_slots=None):
+        b = _np(blob, np.uint8)
+        self.ctx._check(self.L.kronos_cuda_engine_restore_kv_prefix(self.handle, _p(b), b.size, (1 << 63) if copy_slots is None else copy_slots))
 
     def reconfigure_kv(self, kv_bits, window=0, sinks=0):
         """set_kv_bits + set_kv_sliding_window: a fresh cache in the given format / geometry (continue at position 0)."""

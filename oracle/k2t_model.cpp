@@ -680,6 +680,56 @@ int k2o_model_kv_import(K2oModel *m, const uint8_t *data, size_t len, size_t n) 
     return 0;
 }
 
+// KvPrefixSnapshot::Q8 / Q4 (save_kv_prefix / restore_kv_prefix_slice, real_llm.rs:5876-6155) as one blob: 32-byte header
+// ("K2TKVPFX", kv_bits, slots_per_head, heads, head_dim, 0, 0) + key rows, value rows, key scales, value scales, head-major.
+size_t k2o_model_save_kv_prefix(const K2oModel *m, size_t n, uint8_t *out) {
+    if (!m) return 0;
+    const size_t len = std::min(n, m->pos), slots = m->ring_len > 0 ? m->cap : len;
+    const size_t heads = (size_t)m->cfg.layers * m->cfg.n_kv, hd = m->cfg.head_dim;
+    const bool q4 = m->cfg.kv_bits == 4;
+    const size_t db = q4 ? hd / 2 : hd, sb = q4 ? 2 * (hd / 64) : 4, total = 32 + 2 * heads * slots * (db + sb);
+    if (!out) return total;
+    std::memcpy(out, "K2TKVPFX", 8);
+    const uint32_t hdr[6] = {m->cfg.kv_bits, (uint32_t)slots, (uint32_t)heads, (uint32_t)hd, 0u, 0u};
+    std::memcpy(out + 8, hdr, 24);
+    uint8_t *kd = out + 32, *vd = kd + heads * slots * db, *ks = vd + heads * slots * db, *vs = ks + heads * slots * sb;
+    const uint8_t *K = q4 ? m->k_q4.data() : reinterpret_cast<const uint8_t *>(m->k_q8.data());
+    const uint8_t *V = q4 ? m->v_q4.data() : reinterpret_cast<const uint8_t *>(m->v_q8.data());
+    const uint8_t *KS = q4 ? reinterpret_cast<const uint8_t *>(m->k_s16.data()) : reinterpret_cast<const uint8_t *>(m->k_sc.data());
+    const uint8_t *VS = q4 ? reinterpret_cast<const uint8_t *>(m->v_s16.data()) : reinterpret_cast<const uint8_t *>(m->v_sc.data());
+    for (size_t h = 0; h < heads; ++h) {
+        std::memcpy(kd + h * slots * db, K + h * m->cap * db, slots * db);
+        std::memcpy(vd + h * slots * db, V + h * m->cap * db, slots * db);
+        std::memcpy(ks + h * slots * sb, KS + h * m->cap * sb, slots * sb);
+        std::memcpy(vs + h * slots * sb, VS + h * m->cap * sb, slots * sb);
+    }
+    return total;
+}
+int k2o_model_restore_kv_prefix(K2oModel *m, const uint8_t *data, size_t len, size_t copy_slots, size_t total_pos) {
+    if (!m || !data || len < 32 || std::memcmp(data, "K2TKVPFX", 8) != 0) return -1;
+    uint32_t hdr[6];
+    std::memcpy(hdr, data + 8, 24);
+    const size_t slots = hdr[1], heads = (size_t)m->cfg.layers * m->cfg.n_kv, hd = m->cfg.head_dim;
+    const bool q4 = m->cfg.kv_bits == 4;
+    const size_t db = q4 ? hd / 2 : hd, sb = q4 ? 2 * (hd / 64) : 4;
+    if (hdr[0] != m->cfg.kv_bits || hdr[2] != heads || hdr[3] != hd || len < 32 + 2 * heads * slots * (db + sb)) return -1;
+    const size_t cp = std::min(slots, copy_slots);
+    if (cp > m->cap) return -1;
+    const uint8_t *kd = data + 32, *vd = kd + heads * slots * db, *ks = vd + heads * slots * db, *vs = ks + heads * slots * sb;
+    uint8_t *K = q4 ? m->k_q4.data() : reinterpret_cast<uint8_t *>(m->k_q8.data());
+    uint8_t *V = q4 ? m->v_q4.data() : reinterpret_cast<uint8_t *>(m->v_q8.data());
+    uint8_t *KS = q4 ? reinterpret_cast<uint8_t *>(m->k_s16.data()) : reinterpret_cast<uint8_t *>(m->k_sc.data());
+    uint8_t *VS = q4 ? reinterpret_cast<uint8_t *>(m->v_s16.data()) : reinterpret_cast<uint8_t *>(m->v_sc.data());
+    for (size_t h = 0; h < heads; ++h) {
+        std::memcpy(K + h * m->cap * db, kd + h * slots * db, cp * db);
+        std::memcpy(V + h * m->cap * db, vd + h * slots * db, cp * db);
+        std::memcpy(KS + h * m->cap * sb, ks + h * slots * sb, cp * sb);
+        std::memcpy(VS + h * m->cap * sb, vs + h * slots * sb, cp * sb);
+    }
+    m->pos = total_pos;
+    return 0;
+}
+
 int k2o_model_read_kv_q4(const K2oModel *m, uint32_t layer, uint32_t kv_head, size_t pos, uint8_t *k_q4, uint16_t *k_s16,
                          uint8_t *v_q4, uint16_t *v_s16) {
     if (!m || m->cfg.kv_bits != 4 || layer >= m->cfg.layers || kv_head >= m->cfg.n_kv || pos >= m->cfg.max_seq) return -1;

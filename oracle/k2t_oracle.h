@@ -158,6 +158,11 @@ K2oModel *k2o_model_new(const K2oConfig *cfg, const float *rope_table);
  * when 8 <= window and window + 512 < max_seq, as a ring of sinks + (window - sinks + 512) rows per (layer, kv head);
  * resets the position.  Returns 1 when a window is active, 0 when the full causal context is kept, -1 on error. */
 int k2o_model_set_kv_window(K2oModel *m, uint32_t kv_bits, size_t window, size_t sinks);
+/* KvPrefixSnapshot (save_kv_prefix / restore_kv_prefix_slice, real_llm.rs:5876-6155) as one blob: 32-byte header ("K2TKVPFX",
+ * kv_bits, slots_per_head, heads, head_dim, 0, 0) + key rows, value rows, key scales, value scales, head-major.  save returns
+ * the byte count (out == NULL: only the count); restore copies min(slots_per_head, copy_slots) rows and sets the position. */
+size_t k2o_model_save_kv_prefix(const K2oModel *m, size_t n, uint8_t *out);
+int k2o_model_restore_kv_prefix(K2oModel *m, const uint8_t *data, size_t len, size_t copy_slots, size_t total_pos);
 /* cache rows per (layer, kv head) */
 size_t k2o_model_kv_rows(const K2oModel *m);
 /* can_truncate_kv_to (real_llm.rs:1806-1821): may the context be cut back to target_len without ring aliasing? */

@@ -411,6 +411,8 @@ def _declare_model(L):
     L.k2o_model_set_pos.restype, L.k2o_model_set_pos.argtypes = None, [P, C.c_size_t]
     L.k2o_model_set_kv_window.restype, L.k2o_model_set_kv_window.argtypes = C.c_int, [P, C.c_uint32, C.c_size_t, C.c_size_t]
     L.k2o_model_kv_rows.restype, L.k2o_model_kv_rows.argtypes = C.c_size_t, [P]
+    L.k2o_model_save_kv_prefix.restype, L.k2o_model_save_kv_prefix.argtypes = C.c_size_t, [P, C.c_size_t, P]
+    L.k2o_model_restore_kv_prefix.restype, L.k2o_model_restore_kv_prefix.argtypes = C.c_int, [P, P, C.c_size_t, C.c_size_t, C.c_size_t]
     L.k2o_model_can_truncate_kv_to.restype, L.k2o_model_can_truncate_kv_to.argtypes = C.c_int, [P, C.c_size_t]
     L.k2o_model_embed.restype, L.k2o_model_embed.argtypes = None, [P, C.c_uint32, P]
     L.k2o_model_forward_embedding.restype, L.k2o_model_forward_embedding.argtypes = C.c_int, [P, P, P, C.c_size_t]
@@ -569,6 +571,15 @@ class Model:
     @property
     def kv_rows(self):
         return self.L.k2o_model_kv_rows(self.h)
+
+    def save_kv_prefix(self, n):
+        out = np.zeros(self.L.k2o_model_save_kv_prefix(self.h, n, None), np.uint8)
+        self.L.k2o_model_save_kv_prefix(self.h, n, _ptr(out))
+        return out
+
+    def restore_kv_prefix(self, blob, total_pos, copy_slots=None):
+        b = _c(blob, np.uint8)
+        assert self.L.k2o_model_restore_kv_prefix(self.h, _ptr(b), b.size, (1 << 63) if copy_slots is None else copy_slots, total_pos) == 0
 
     def can_truncate_kv_to(self, target_len):
         return bool(self.L.k2o_model_can_truncate_kv_to(self.h, target_len))

@@ -102,3 +102,38 @@ def test_reconfigure_kv_and_blobs_on_the_ring(ctx, oracle):
         assert np.array_equal(eng.forward_token_ids(tokens[:40], want_all=True), want)
     finally:
         eng.close(); ref.close()
+
+
+@pytest.mark.parametrize("kv_bits,window", [(4, 0), (8, 0), (4, 16)])
+def test_kv_prefix_snapshot_save_restore(ctx, oracle, kv_bits, window):
+    """save_kv_prefix / restore_kv_prefix (real_llm.rs:5876-6155), following the reference test's sequence (10597-10604):
+    snapshot after 12 of 24 prompt tokens, run something else, restore, replay the rest - the logits must be the original
+    ones.  The device snapshot equals the CPU engine's byte for byte, and each side restores from the other's."""
+    cfg = dict(REF_SHAPE, kv_bits=kv_bits, kv_window=window, kv_sinks=4 if window else 0)
+    spec, eng, ref = make(ctx, oracle, cfg, "b4")
+    try:
+        prompt = [(i * 11 + 3) % cfg["vocab"] for i in range(24)]
+        want = np.stack([ref.forward_token(t, threads=2) for t in prompt])
+        got = eng.forward_token_ids(prompt, want_all=True)
+        assert np.array_equal(got, want)
+        ref.reset()
+        for t in prompt[:12]:
+            ref.forward_token(t, threads=2)
+        eng.forward_token_ids(prompt[:12])
+        snap_cpu, snap_gpu = ref.save_kv_prefix(12), eng.save_kv_prefix(12, 12)
+        assert np.array_equal(snap_cpu, snap_gpu)
+        rows = eng.kv_rows if window else 12
+        per_row = 2 * cfg["layers"] * cfg["n_kv"] * ((cfg["head_dim"] // 2 + 2 * (cfg["head_dim"] // 64)) if kv_bits == 4 else (cfg["head_dim"] + 4))
+        assert snap_gpu.size == 32 + rows * per_row
+        eng.forward_token_ids([7], pos_start=12)                     # something else at position 12
+        eng.restore_kv_prefix(snap_cpu)                                # the CPU engine's snapshot restores on the device
+        rest = eng.forward_token_ids(prompt[12:], pos_start=12, want_all=True)
+        assert np.array_equal(rest, want[12:])
+        ref.forward_token(7, threads=2)
+        ref.restore_kv_prefix(snap_gpu, 12)                            # and the device's on the CPU engine
+        assert np.array_equal(np.stack([ref.forward_token(t, threads=2) for t in prompt[12:]]), want[12:])
+        import kronos_2t_b200 as k2
+        with pytest.raises(k2.KronosCudaError, match="not a KV prefix"):
+            eng.restore_kv_prefix(np.zeros(64, np.uint8))
+    finally:
+        eng.close(); ref.close()
