@@ -329,16 +329,33 @@ int32_t kronos_cuda_engine_read_kv(KronosCudaEngine *engine, uint32_t layer, uin
  * real_llm.rs:3705-3895, 3902-4186; magics K2TBIPOLAR1, K2TKRONOS2/3/4/6).  Host code, no GPU needed.  The descriptors
  * handed out point into storage owned by the handle and stay valid until kronos_cuda_k2tb_close; they are exactly what
  * kronos_cuda_engine_create takes, so a cached model runs with no recompile.  Shapes (heads, head_dim, ...) are not in
- * the file: they come from the model's config.json as in the reference.  VQ2 / Q2c matrices and the sparse-MoE core
- * (K2TKRONOS5) are rejected.  Errors: NULL / -1 and kronos_cuda_k2tb_last_error() (per thread). */
+ * the file: they come from the model's config.json as in the reference.  VQ2 / Q2c matrices are rejected.  The sparse-MoE
+ * core (K2TKRONOS5, RealLlamaEngine::load_moe_from_files, real_llm.rs:5166-5519) opens through the same call (version 5);
+ * its expert records live in the .k2tm shard below.  Errors: NULL / -1 and kronos_cuda_k2tb_last_error() (per thread). */
 typedef struct KronosCudaK2tb KronosCudaK2tb;
 KronosCudaK2tb *kronos_cuda_k2tb_open(const char *path);
 void kronos_cuda_k2tb_close(KronosCudaK2tb *file);
 const char *kronos_cuda_k2tb_last_error(void);
 /* version = 1, 2, 3, 4 or 6; mode_words = the six RealWeightMode words (real_llm.rs:3805-3829). */
 int32_t kronos_cuda_k2tb_info(const KronosCudaK2tb *file, uint32_t *version, uint64_t mode_words[6], size_t *n_layers);
-/* Layer l as a KronosCudaLayerDesc (MoE fields NULL); qkv_bias_len = elements of the bias (0 = none). */
+/* Layer l as a KronosCudaLayerDesc; qkv_bias_len = elements of the bias (0 = none).  A MoE layer of a K2TKRONOS5 core gets
+ * its router (moe_router_w / moe_router_bias); the caller adds moe_shard / moe_shard_len from kronos_cuda_k2tm_layer.  Fails
+ * (message in kronos_cuda_k2tb_last_error) for layers with an o_proj bias or a shared expert, which the engine does not run. */
 int32_t kronos_cuda_k2tb_layer(const KronosCudaK2tb *file, size_t l, KronosCudaLayerDesc *out, size_t *qkv_bias_len);
+/* K2TKRONOS5 only: NF bits and scale group (64-column chunks per scale) of the expert matrices. */
+int32_t kronos_cuda_k2tb_moe_info(const KronosCudaK2tb *file, uint64_t *expert_bits, uint64_t *expert_scale_group_chunks);
+/* 1 when layer l is a MoE layer (then: its slot in the expert shard, router experts and hidden), 0 for a dense layer. */
+int32_t kronos_cuda_k2tb_moe_layer(const KronosCudaK2tb *file, size_t l, uint64_t *moe_slot_idx, uint64_t *experts, uint64_t *hidden);
+
+/* The .k2tm expert shard (K2tmShardHeader, src/model/moe_800b.rs:790-854; open_k2tm, src/model/sparse_moe.rs:685): mapped
+ * read-only.  info: the header's seven words (layers, experts per layer, d_model, d_ff, scale_group_chunks, aligned expert
+ * bytes, bits).  layer: the records of MoE slot `moe_slot_idx` (experts x aligned bytes, from expert_byte_offset(slot, 0)) -
+ * what KronosCudaLayerDesc.moe_shard / moe_shard_len take; valid until kronos_cuda_k2tm_close. */
+typedef struct KronosCudaK2tm KronosCudaK2tm;
+KronosCudaK2tm *kronos_cuda_k2tm_open(const char *path);
+void kronos_cuda_k2tm_close(KronosCudaK2tm *shard);
+int32_t kronos_cuda_k2tm_info(const KronosCudaK2tm *shard, uint64_t words[7]);
+int32_t kronos_cuda_k2tm_layer(const KronosCudaK2tm *shard, size_t moe_slot_idx, const uint8_t **records, size_t *len);
 int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *file, const float **final_norm, size_t *final_norm_len,
                               KronosCudaMatrixDesc *lm_head, const uint16_t **embed_bf16, size_t *embed_bf16_len,
                               const float **embed_f32, size_t *embed_f32_len);

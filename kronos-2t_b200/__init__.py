@@ -11,6 +11,7 @@ from .ffi import (  # noqa: F401
     MatrixDesc,
     bipolar_desc,
     k2tb_load,
+    moe_load,
     k2tb_save,
     matrix_image,
     nf_desc,

@@ -9,6 +9,18 @@
 //     tag 0 bipolar: rows, cols, planes, u64 len + interleaved bytes, u64 n + bf16 scales
 //     tag 2 NF:      rows, cols, bits, scale_group_chunks, 16-byte codebook, u64 len + pair_stream, u64 len + tail_stream
 //   Tags 1 (VQ2) and 3 (Q2c) are other weight formats of the reference and are rejected here.
+// Sparse-MoE models come as two files (RealLlamaEngine::load_moe_from_files, real_llm.rs:5166-5519):
+//   the core, magic K2TKRONOS5: 6 x u64 mode words, u64 expert_bits, u64 expert_scale_group_chunks, u64 n_layers;
+//     per layer: f32s input_norm, post_attn_norm, qkv_bias, o_bias, q_norm, k_norm (empty = absent), matrices qkv, o, u64 is_moe;
+//       MoE layer: u64 moe_slot_idx, u64 experts, u64 hidden, f32s router weights, f32s router bias,
+//                  u64 has_shared [+ u64 inter, f32s gate_weight, matrices gate_up, down],
+//                  u64 has_lookahead [+ u64 future_layer, u64 d_model, u64 rank, f32s u, f32s v];
+//       dense layer: matrices gate_up, down;
+//     f32s final_norm, matrix lm_head, f32s embed_f32, u16s embed_bf16, u64 flag [+ NF matrix];
+//   the expert shard (.k2tm, K2tmShardHeader, src/model/moe_800b.rs:790-854): a 16 KiB header page - magic
+//     "K2TM800B_V1\0", at byte 16 seven u64: layers, experts per layer, d_model, d_ff, scale_group_chunks, aligned expert
+//     bytes, bits - then layers x experts records of aligned_expert_bytes each (expert_byte_offset = 16384 + (layer *
+//     experts + expert) * aligned bytes).  The shard is mapped read-only, not copied.
 // Host code only: the arrays are copied out of the file image into aligned storage owned by the handle, and the
 // descriptors handed out point into that storage.
 #include <cstdio>
@@ -16,6 +28,11 @@
 #include <memory>
 #include <string>
 #include <vector>
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #include "../../include/kronos_cuda_ffi.h"
 
@@ -27,8 +44,12 @@ struct OwnedMatrix {
     void fix() { d.data0 = a.empty() ? nullptr : a.data(); d.len0 = a.size(); d.data1 = b.empty() ? nullptr : b.data(); d.len1 = b.size(); }
 };
 struct OwnedLayer {
-    std::vector<float> input_norm, post_norm, qkv_bias, q_norm, k_norm;
+    std::vector<float> input_norm, post_norm, qkv_bias, o_bias, q_norm, k_norm;
     OwnedMatrix qkv, o, gate_up, down;
+    // sparse-MoE layer of a K2TKRONOS5 core
+    bool moe = false, has_shared = false, has_lookahead = false;
+    uint64_t moe_slot = 0, router_experts = 0, router_hidden = 0;
+    std::vector<float> router_w, router_bias;
 };
 
 struct Reader {
@@ -73,6 +94,7 @@ struct Reader {
 struct KronosCudaK2tb {
     int version = 0;
     uint64_t mode[6] = {0};
+    uint64_t expert_bits = 0, expert_sgc = 0;      // K2TKRONOS5 only
     std::vector<OwnedLayer> layers;
     std::vector<float> final_norm, embed_f32;
     std::vector<uint16_t> embed_bf16;
@@ -85,20 +107,58 @@ thread_local std::string g_k2tb_error;
 
 bool parse(const uint8_t *bytes, size_t n, KronosCudaK2tb &f, std::string &err) {
     static const struct { const char *magic; int version; } MAGICS[] = {
-        {"K2TBIPOLAR1\n", 1}, {"K2TKRONOS2\n", 2}, {"K2TKRONOS3\n", 3}, {"K2TKRONOS4\n", 4}, {"K2TKRONOS6\n", 6}};
+        {"K2TBIPOLAR1\n", 1}, {"K2TKRONOS2\n", 2}, {"K2TKRONOS3\n", 3}, {"K2TKRONOS4\n", 4}, {"K2TKRONOS5\n", 5}, {"K2TKRONOS6\n", 6}};
     size_t mlen = 0;
     for (const auto &m : MAGICS) {
         const size_t l = std::strlen(m.magic);
         if (n >= l && std::memcmp(bytes, m.magic, l) == 0) { f.version = m.version; mlen = l; }
     }
-    if (!f.version) {
-        err = (n >= 11 && std::memcmp(bytes, "K2TKRONOS5\n", 11) == 0) ? "a sparse-MoE core (K2TKRONOS5) is read by the MoE loader, not this one"
-                                                                        : "not a .k2tb file (unknown magic)";
-        return false;
-    }
+    if (!f.version) { err = "not a .k2tb file (unknown magic)"; return false; }
     Reader r{bytes, n, mlen, {}};
     uint64_t n_layers = 0;
     for (int i = 0; i < 6; ++i) if (!r.u64(f.mode[i])) { err = r.err; return false; }
+    if (f.version == 5) {          // sparse-MoE core: its own field order (load_moe_from_files, real_llm.rs:5166-5519)
+        if (!r.u64(f.expert_bits) || !r.u64(f.expert_sgc) || !r.u64(n_layers) || n_layers == 0 || n_layers > 4096) {
+            err = r.err.empty() ? "implausible layer count" : r.err;
+            return false;
+        }
+        if (f.expert_sgc == 0) f.expert_sgc = 1;
+        f.layers.resize((size_t)n_layers);
+        for (OwnedLayer &L : f.layers) {
+            uint64_t is_moe = 0;
+            bool ok = r.arr(L.input_norm, n) && r.arr(L.post_norm, n) && r.arr(L.qkv_bias, n) && r.arr(L.o_bias, n) && r.arr(L.q_norm, n) && r.arr(L.k_norm, n) &&
+                      r.matrix(L.qkv, true) && r.matrix(L.o, true) && r.u64(is_moe);
+            if (ok && is_moe) {
+                L.moe = true;
+                uint64_t flag = 0;
+                ok = r.u64(L.moe_slot) && r.u64(L.router_experts) && r.u64(L.router_hidden) && r.arr(L.router_w, n) && r.arr(L.router_bias, n) && r.u64(flag);
+                if (ok && L.router_w.size() != L.router_experts * L.router_hidden) { r.err = "router weights do not match experts x hidden"; ok = false; }
+                if (ok && flag) {          // shared expert: read past it (the engine does not run shared experts)
+                    L.has_shared = true;
+                    uint64_t inter;
+                    std::vector<float> gate_weight;
+                    OwnedMatrix gu, dn;
+                    ok = r.u64(inter) && r.arr(gate_weight, n) && r.matrix(gu, true) && r.matrix(dn, true);
+                }
+                ok = ok && r.u64(flag);
+                if (ok && flag) {          // lookahead projector (expert prefetch of the CPU pager): read past it
+                    L.has_lookahead = true;
+                    uint64_t a, b, c;
+                    std::vector<float> u, v;
+                    ok = r.u64(a) && r.u64(b) && r.u64(c) && r.arr(u, n) && r.arr(v, n);
+                }
+            } else if (ok) {
+                ok = r.matrix(L.gate_up, true) && r.matrix(L.down, true);
+            }
+            if (!ok) { err = r.err; return false; }
+        }
+        uint64_t flag = 0;
+        bool ok = r.arr(f.final_norm, n) && r.matrix(f.lm_head, true) && r.arr(f.embed_f32, n) && r.arr(f.embed_bf16, n) && r.u64(flag);
+        if (ok && flag) { f.has_embed_nf4 = true; ok = r.matrix(f.embed_nf4, true); }
+        if (!ok) { err = r.err; return false; }
+        if (r.pos != n) { err = "trailing bytes after the last field"; return false; }
+        return true;
+    }
     if (!r.u64(n_layers) || n_layers == 0 || n_layers > 4096) { err = r.err.empty() ? "implausible layer count" : r.err; return false; }
     f.layers.resize((size_t)n_layers);
     const bool tagged = f.version >= 2;
@@ -186,7 +246,31 @@ int32_t kronos_cuda_k2tb_layer(const KronosCudaK2tb *f, size_t l, KronosCudaLaye
     out->k_norm = L.k_norm.empty() ? nullptr : L.k_norm.data();
     out->qkv_proj = L.qkv.d; out->o_proj = L.o.d; out->gate_up_proj = L.gate_up.d; out->down_proj = L.down.d;
     if (qkv_bias_len) *qkv_bias_len = L.qkv_bias.size();
+    if (!L.o_bias.empty()) { g_k2tb_error = "k2tb_layer: the layer carries an o_proj bias, which the device engine does not apply"; return -1; }
+    if (L.moe) {
+        if (L.has_shared) { g_k2tb_error = "k2tb_layer: the layer has a shared expert, which the device engine does not run"; return -1; }
+        out->moe_router_w = L.router_w.data();
+        out->moe_router_bias = L.router_bias.empty() ? nullptr : L.router_bias.data();
+        // moe_shard / moe_shard_len come from the expert shard: kronos_cuda_k2tm_layer(shard, moe slot)
+    }
     return 0;
+}
+
+int32_t kronos_cuda_k2tb_moe_info(const KronosCudaK2tb *f, uint64_t *expert_bits, uint64_t *expert_scale_group_chunks) {
+    if (!f || f->version != 5) return -1;
+    if (expert_bits) *expert_bits = f->expert_bits;
+    if (expert_scale_group_chunks) *expert_scale_group_chunks = f->expert_sgc;
+    return 0;
+}
+
+int32_t kronos_cuda_k2tb_moe_layer(const KronosCudaK2tb *f, size_t l, uint64_t *moe_slot_idx, uint64_t *experts, uint64_t *hidden) {
+    if (!f || l >= f->layers.size()) return -1;
+    const OwnedLayer &L = f->layers[l];
+    if (!L.moe) return 0;
+    if (moe_slot_idx) *moe_slot_idx = L.moe_slot;
+    if (experts) *experts = L.router_experts;
+    if (hidden) *hidden = L.router_hidden;
+    return 1;
 }
 
 int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *f, const float **final_norm, size_t *final_norm_len, KronosCudaMatrixDesc *lm_head,
@@ -199,6 +283,57 @@ int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *f, const float **final_norm,
     if (embed_bf16_len) *embed_bf16_len = f->embed_bf16.size();
     if (embed_f32) *embed_f32 = f->embed_f32.empty() ? nullptr : f->embed_f32.data();
     if (embed_f32_len) *embed_f32_len = f->embed_f32.size();
+    return 0;
+}
+
+struct KronosCudaK2tm {
+    void *map = nullptr;
+    size_t len = 0;
+    uint64_t w[7] = {0};      // layers, experts per layer, d_model, d_ff, scale_group_chunks, aligned expert bytes, bits
+};
+
+KronosCudaK2tm *kronos_cuda_k2tm_open(const char *path) {
+    g_k2tb_error.clear();
+    if (!path) { g_k2tb_error = "k2tm_open: NULL path"; return nullptr; }
+    const int fd = ::open(path, O_RDONLY);
+    if (fd < 0) { g_k2tb_error = std::string("k2tm_open: cannot open ") + path; return nullptr; }
+    struct stat st;
+    if (::fstat(fd, &st) != 0 || st.st_size < 16384 || (st.st_size % 16384) != 0) {       // open_k2tm (sparse_moe.rs:685): whole 16 KiB pages
+        ::close(fd);
+        g_k2tb_error = "k2tm_open: the file is not a whole number of 16 KiB pages";
+        return nullptr;
+    }
+    void *map = ::mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    ::close(fd);
+    if (map == MAP_FAILED) { g_k2tb_error = "k2tm_open: mmap failed"; return nullptr; }
+    std::unique_ptr<KronosCudaK2tm> h(new KronosCudaK2tm());
+    h->map = map; h->len = (size_t)st.st_size;
+    const uint8_t *page = static_cast<const uint8_t *>(map);
+    auto bad = [&](const char *why) { g_k2tb_error = std::string("k2tm_open: ") + why; ::munmap(map, (size_t)st.st_size); h->map = nullptr; return (KronosCudaK2tm *)nullptr; };
+    if (std::memcmp(page, "K2TM800B_V1\0", 12) != 0) return bad("bad k2tm header magic");
+    std::memcpy(h->w, page + 16, 56);
+    const uint64_t L = h->w[0], E = h->w[1], rec = h->w[5];
+    if (L == 0 || E == 0 || rec == 0 || rec % 16384 || L > 4096 || E > 65536) return bad("implausible shard header");
+    if (16384 + L * E * rec != (uint64_t)st.st_size) return bad("file size does not match layers x experts x record bytes");
+    return h.release();
+}
+
+void kronos_cuda_k2tm_close(KronosCudaK2tm *h) {
+    if (!h) return;
+    if (h->map) ::munmap(h->map, h->len);
+    delete h;
+}
+
+int32_t kronos_cuda_k2tm_info(const KronosCudaK2tm *h, uint64_t words[7]) {
+    if (!h || !words) return -1;
+    std::memcpy(words, h->w, sizeof h->w);
+    return 0;
+}
+
+int32_t kronos_cuda_k2tm_layer(const KronosCudaK2tm *h, size_t moe_slot_idx, const uint8_t **records, size_t *len) {
+    if (!h || !records || !len || moe_slot_idx >= h->w[0]) return -1;
+    *records = static_cast<const uint8_t *>(h->map) + 16384 + moe_slot_idx * h->w[1] * h->w[5];      // expert_byte_offset(slot, 0)
+    *len = (size_t)(h->w[1] * h->w[5]);
     return 0;
 }
 

@@ -557,6 +557,77 @@ def k2tb_load(path, cfg, rope):
         L.kronos_cuda_k2tb_close(h)
 
 
+def moe_load(core_path, shard_path, cfg, rope):
+    """load_moe_from_files (real_llm.rs:5166-5519): reads a K2TKRONOS5 core and its .k2tm expert shard into an engine spec.
+    cfg = shapes and routing from the model's config.json (hidden, heads, ..., plus moe_top_k, moe_norm_topk[, moe_scoring]);
+    the shard stays mapped (the spec's `shard` arrays are views into it) until the returned `close()` is called, so build the
+    engine first.  Returns (spec, header_words, close)."""
+    L = load_library()
+    u64, sz, vp = C.c_uint64, C.c_size_t, C.c_void_p
+    for name, res, args in (("kronos_cuda_k2tb_moe_info", C.c_int32, [vp, C.POINTER(u64), C.POINTER(u64)]),
+                            ("kronos_cuda_k2tb_moe_layer", C.c_int32, [vp, sz, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)]),
+                            ("kronos_cuda_k2tm_open", vp, [C.c_char_p]), ("kronos_cuda_k2tm_close", None, [vp]),
+                            ("kronos_cuda_k2tm_info", C.c_int32, [vp, C.POINTER(u64 * 7)]),
+                            ("kronos_cuda_k2tm_layer", C.c_int32, [vp, sz, C.POINTER(vp), C.POINTER(sz)])):
+        f = getattr(L, name)
+        f.restype, f.argtypes = res, args
+    h = L.kronos_cuda_k2tb_open(os.fsencode(core_path))
+    if not h:
+        raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())
+    tm = L.kronos_cuda_k2tm_open(os.fsencode(shard_path))
+    if not tm:
+        L.kronos_cuda_k2tb_close(h)
+        raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())
+    try:
+        ver, mode, nl = C.c_uint32(), (u64 * 6)(), sz()
+        L.kronos_cuda_k2tb_info(h, C.byref(ver), C.byref(mode), C.byref(nl))
+        if ver.value != 5:
+            raise KronosCudaError("moe_load: the core file is not a K2TKRONOS5 container")
+        words = (u64 * 7)()
+        L.kronos_cuda_k2tm_info(tm, C.byref(words))
+        n_moe_layers, experts, d_model, d_ff, sgc, rec, bits = [int(w) for w in words]
+        ebits, esgc = u64(), u64()
+        L.kronos_cuda_k2tb_moe_info(h, C.byref(ebits), C.byref(esgc))
+        if d_model != cfg["hidden"] or ebits.value != bits or esgc.value != sgc:
+            raise KronosCudaError("moe_load: core and expert shard disagree (hidden size, expert bits or scale group)")
+        hd, hid = cfg["head_dim"], cfg["hidden"]
+        layers = []
+        for l in range(nl.value):
+            d, nb = LayerDesc(), sz()
+            if L.kronos_cuda_k2tb_layer(h, l, C.byref(d), C.byref(nb)) != 0:
+                raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())
+            ly = dict(input_norm=_f32(d.input_norm, hid), post_norm=_f32(d.post_attn_norm, hid), qkv_bias=_f32(d.qkv_bias, nb.value),
+                      q_norm=_f32(d.q_norm, hd), k_norm=_f32(d.k_norm, hd), qkv=_HostMatrix(d.qkv_proj), o=_HostMatrix(d.o_proj))
+            slot, n_exp, r_hid = u64(), u64(), u64()
+            if L.kronos_cuda_k2tb_moe_layer(h, l, C.byref(slot), C.byref(n_exp), C.byref(r_hid)) == 1:
+                if n_exp.value != experts or r_hid.value != hid or slot.value >= n_moe_layers:
+                    raise KronosCudaError(f"moe_load: layer {l}: router shape or shard slot does not match the expert shard")
+                ptr, ln = vp(), sz()
+                L.kronos_cuda_k2tm_layer(tm, slot.value, C.byref(ptr), C.byref(ln))
+                shard = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(ln.value,))        # a view into the mapping
+                ly["gate_up"] = ly["down"] = None
+                ly["moe"] = dict(router_w=_f32(d.moe_router_w, experts * hid), router_bias=_f32(d.moe_router_bias, experts), n_experts=experts,
+                                 top_k=cfg["moe_top_k"], norm_topk=bool(cfg.get("moe_norm_topk", True)), d_ff=d_ff, bits=bits, sgc=sgc, shard=shard,
+                                 expert_bytes=rec, scoring=int(cfg.get("moe_scoring", 0)))
+            else:
+                ly.update(gate_up=_HostMatrix(d.gate_up_proj), down=_HostMatrix(d.down_proj))
+            layers.append(ly)
+        fn, fnl, emb, embl, ef, efl = vp(), sz(), vp(), sz(), vp(), sz()
+        head = MatrixDesc()
+        L.kronos_cuda_k2tb_head(h, C.byref(fn), C.byref(fnl), C.byref(head), C.byref(emb), C.byref(embl), C.byref(ef), C.byref(efl))
+        embed = np.ctypeslib.as_array(C.cast(emb, C.POINTER(C.c_uint16)), shape=(embl.value,)).copy() if embl.value else None
+        spec = dict(cfg=dict(cfg, layers=nl.value), layers=layers, final_norm=_f32(fn, fnl.value), lm_head=_HostMatrix(head), rope=rope, embed_bf16=embed)
+        L.kronos_cuda_k2tb_close(h)
+        h = None
+        return spec, [int(w) for w in words], (lambda: L.kronos_cuda_k2tm_close(tm))
+    except Exception:
+        L.kronos_cuda_k2tm_close(tm)
+        raise
+    finally:
+        if h:
+            L.kronos_cuda_k2tb_close(h)
+
+
 def k2tb_save(path, spec, mode_words):
     """Writes an engine spec as a .k2tb dense container (version chosen as the reference's save_bipolar does)."""
     L = load_library()

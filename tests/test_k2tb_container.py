@@ -118,7 +118,7 @@ def test_k2tb_reader_rejects_malformed_files(oracle, tmp_path):
     raw = path.read_bytes()
     bad = tmp_path / "bad.k2tb"
     for data, text in ((raw[:len(raw) // 2], "truncated"), (b"K2TWHATEVER\n" + raw[12:], "magic"), (raw + b"\0", "trailing"),
-                       (b"K2TKRONOS5\n" + raw[12:], "MoE")):
+                       (b"K2TKRONOS5\n" + raw[12:], "implausible|truncated|exceeds|tag")):      # a dense body behind the MoE core magic
         bad.write_bytes(data)
         with pytest.raises(k2.KronosCudaError, match=text):
             k2.k2tb_load(bad, spec["cfg"], spec["rope"])
@@ -156,3 +156,96 @@ def test_engine_from_k2tb_file(oracle, tmp_path, mode, kw, words):
         assert list(got[:11]) == out
     finally:
         eng.close(); ref.close(); ctx.close()
+
+
+def test_moe_core_and_expert_shard_readers(oracle, tmp_path):
+    """K2TKRONOS5 core + .k2tm shard: the library's readers return what an independent writer (tests/k2t_moe_files.py) put
+    in - every vector, matrix, router and expert record, the shard header words, the skipped lookahead projector - and refuse
+    malformed files.  No GPU needed."""
+    import kronos_2t_b200 as k2
+    import k2t_moe_files as mf
+    moe = dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, bias=True)
+    spec = km.build(oracle, km.MOE_TINY, "nf4g128", seed=17, moe=moe, qk_norm=True, qkv_bias=True, tied=False)
+    core, shard = str(tmp_path / "core.k2tb"), str(tmp_path / "experts.k2tm")
+    words = mf.write_moe_files(core, shard, spec, [6, 4, 3, 2, 0, 0], lookahead_layers=(0,))
+    cfg = dict(km.MOE_TINY, moe_top_k=2, moe_norm_topk=True)
+    got, hdr, close = k2.moe_load(core, shard, cfg, spec["rope"])
+    try:
+        assert hdr == words == [2, 8, km.MOE_TINY["hidden"], 64, 2, spec["layers"][0]["moe"]["expert_bytes"], 3]
+        for l, (a, b) in enumerate(zip(got["layers"], spec["layers"])):
+            for k in ("input_norm", "post_norm", "qkv_bias", "q_norm", "k_norm"):
+                assert np.array_equal(a[k], b[k]), (l, k)
+            for k in ("qkv", "o"):
+                assert np.array_equal(a[k].pair, b[k].pair) and np.array_equal(a[k].codebook, b[k].codebook) and a[k].sgc == b[k].sgc
+            if b.get("moe"):
+                ma, mb = a["moe"], b["moe"]
+                assert np.array_equal(ma["router_w"].reshape(-1), np.asarray(mb["router_w"]).reshape(-1)) and np.array_equal(ma["router_bias"], mb["router_bias"])
+                assert np.array_equal(ma["shard"], mb["shard"]) and ma["expert_bytes"] == mb["expert_bytes"]
+                assert (ma["n_experts"], ma["d_ff"], ma["bits"], ma["sgc"], ma["top_k"]) == (8, 64, 3, 2, 2)
+            else:
+                assert np.array_equal(a["gate_up"].pair, b["gate_up"].pair) and np.array_equal(a["down"].pair, b["down"].pair)
+        assert np.array_equal(got["final_norm"], spec["final_norm"]) and np.array_equal(got["embed_bf16"], np.asarray(spec["embed_bf16"]).reshape(-1))
+        assert np.array_equal(got["lm_head"].pair, spec["lm_head"].pair)
+    finally:
+        close()
+    raw = open(shard, "rb").read()
+    bad = str(tmp_path / "bad.k2tm")
+    open(bad, "wb").write(raw[:-16384])                                   # a record page missing
+    with pytest.raises(k2.KronosCudaError, match="file size"):
+        k2.moe_load(core, bad, cfg, spec["rope"])
+    open(bad, "wb").write(b"X" + raw[1:])
+    with pytest.raises(k2.KronosCudaError, match="magic"):
+        k2.moe_load(core, bad, cfg, spec["rope"])
+    open(bad, "wb").write(raw[:100])
+    with pytest.raises(k2.KronosCudaError, match="16 KiB"):
+        k2.moe_load(core, bad, cfg, spec["rope"])
+    craw = open(core, "rb").read()
+    badc = str(tmp_path / "bad.k2tb")
+    open(badc, "wb").write(craw[:len(craw) // 2])
+    with pytest.raises(k2.KronosCudaError, match="truncated|exceeds"):
+        k2.moe_load(badc, shard, cfg, spec["rope"])
+    with pytest.raises(k2.KronosCudaError, match="top_k|K2TKRONOS5|core"):     # a dense container is not a MoE core
+        dense = km.build(oracle, km.TINY, "b4", seed=1)
+        k2.k2tb_save(str(tmp_path / "dense.k2tb"), dense, [0, 4, 0, 0, 0, 0])
+        k2.moe_load(str(tmp_path / "dense.k2tb"), shard, cfg, spec["rope"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode,moe,kw", [
+    ("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2), dict(qk_norm=True, tied=False)),     # Qwen3-MoE style
+    ("b5", dict(layers=[1], n_experts=16, top_k=4, d_ff=128, bits=4, sgc=1, norm_topk=False, bias=True), dict(qkv_bias=True)),
+])
+def test_moe_engine_from_core_and_shard_files(oracle, tmp_path, mode, moe, kw):
+    """load_moe_from_files on the device: a sparse-MoE model written as K2TKRONOS5 core + .k2tm shard, read back through the
+    library (the expert records stay in the mapped file until the engine has uploaded them) and run: logits, routes and
+    the greedy stream equal the oracle's on the in-memory model."""
+    import kronos_2t_b200 as k2
+    import k2t_moe_files as mf
+    spec = km.build(oracle, km.MOE_TINY, mode, seed=19, moe=moe, **kw)
+    core, shard = str(tmp_path / "core.k2tb"), str(tmp_path / "experts.k2tm")
+    mf.write_moe_files(core, shard, spec, [6, 4, moe["bits"], moe["sgc"], 0, 0], lookahead_layers=(moe["layers"][0],))
+    cfg = dict(km.MOE_TINY, moe_top_k=moe["top_k"], moe_norm_topk=moe.get("norm_topk", True))
+    loaded, hdr, close = k2.moe_load(core, shard, cfg, spec["rope"])
+    ctx = k2.Context(0)
+    try:
+        eng = k2.Engine(ctx, loaded)
+        close()                                   # the engine owns device copies: the mapping may go
+        ref = oracle.Model(spec)
+        try:
+            rng = np.random.Generator(np.random.PCG64(4))
+            tokens = [int(t) for t in rng.integers(0, km.MOE_TINY["vocab"], 21)]
+            want = np.stack([ref.forward_token(t, threads=2) for t in tokens])
+            assert np.array_equal(eng.forward_token_ids(tokens, want_all=True), want)
+            for l in moe["layers"]:
+                ge, gw = eng.read_routes(l)
+                we, ww = ref.last_routes(l)
+                assert np.array_equal(ge, we) and np.array_equal(gw, ww)
+            tok, out = int(np.argmax(want[-1])), []
+            got = eng.decode_greedy(tok, len(tokens), 20)
+            for _ in range(20):
+                tok = oracle.argmax(ref.forward_token(tok, threads=2)); out.append(tok)
+            assert list(got) == out
+        finally:
+            eng.close(); ref.close()
+    finally:
+        ctx.close()
