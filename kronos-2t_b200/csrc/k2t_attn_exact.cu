@@ -450,14 +450,10 @@ template <int HD, bool KV4>
 static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl) {
     const size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-        cudaError_t e = cudaFuncSetAttribute(attn_values_kernel<HD, KV4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        allowed = smem;
-    }
+    cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_values_kernel<HD, KV4>), smem);
+    if (e != cudaSuccess) return e;
     const uint32_t nblk = (a.ctx_cap + SCORE_TILE - 1) / SCORE_TILE;
-    cudaError_t e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv), dim3(SCORE_TILE), 0, s, pdl, a);
+    e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv), dim3(SCORE_TILE), 0, s, pdl, a);
     if (e != cudaSuccess) return e;
     return launch_kernel(attn_values_kernel<HD, KV4>, dim3(a.n_kv * a.group), dim3(VAL_THREADS), smem, s, pdl, a);
 }

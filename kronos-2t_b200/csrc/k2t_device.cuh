@@ -1,6 +1,7 @@
 // Small device helpers shared by the kernels (sm_100a).
 #pragma once
 #include <cstdint>
+#include <mutex>
 #include <cuda_runtime.h>
 
 namespace k2t {
@@ -55,6 +56,30 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device) instead of on every launch: the value set so
+// far is remembered per device, and cudaFuncSetAttribute is called only for a larger request.  (The attribute belongs
+// to the function on the current device, so a process that drives several GPUs sets it on each.)
+inline cudaError_t allow_dynamic_smem(const void *kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    constexpr int MAX_DEV = 16, SLOTS = 256;
+    struct Entry { const void *fn; size_t bytes[MAX_DEV]; };
+    static Entry table[SLOTS] = {};
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry *slot = nullptr;
+    for (int i = 0; i < SLOTS && dev < MAX_DEV; ++i) {
+        if (table[i].fn == kernel) { slot = &table[i]; break; }
+        if (table[i].fn == nullptr) { table[i].fn = kernel; slot = &table[i]; break; }
+    }
+    if (slot != nullptr && slot->bytes[dev] >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && slot != nullptr) slot->bytes[dev] = bytes;
+    return e;
 }
 
 // E8Q2 even-coset templates (simd_lut.rs:4354-4383): four magnitudes per entry, packed little-endian.  The decode

@@ -10,6 +10,7 @@
 #include <map>
 #include <new>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "k2t_context.h"
@@ -27,7 +28,8 @@ struct EngineLayer {
     // sparse-MoE FFN (router + expert records) instead of gate_up / down
     bool moe = false;
     float *router_w = nullptr, *router_bias = nullptr;
-    std::vector<KronosCudaMatrix *> expert_gu, expert_dn;
+    k2t::DeviceMatrix gu_dm{}, dn_dm{};                                // geometry (and image base) of the first expert this rank holds: template of the expert launches
+    uint8_t *d_experts = nullptr;                                     // ONE allocation: the device images of all experts of the layer this rank holds
     const uint8_t **d_gu_bases = nullptr, **d_dn_bases = nullptr;     // device tables: image base of every expert
     k2t::ExpertCodebook *d_gu_books = nullptr, *d_dn_books = nullptr; // device tables: decode tables of every expert
     int gu_fmt = -1, dn_fmt = -1;                                     // kernel format of the layer's experts
@@ -257,11 +259,11 @@ bool enqueue_fused_step(KronosCudaEngine *e, bool embed, Tail tail, bool long_ct
             ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
             ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done;
             if (!count(e, launch_moe_router(s, ra, pdl), "router")) return false;
-            if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q, e->act_s, e->act_m, 0, 0,
+            if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q, e->act_s, e->act_m, 0, 0,
                                               e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, pdl, c.moe_num_experts), "expert gate_up")) return false;
             FusedPro ps{};
             ps.mode = PRO_SWIGLU; ps.n = dff; ps.chunk0 = 0; ps.swiglu_exp_cr = 1; ps.gate_up = e->moe_gu;
-            if (!count(e, launch_gemv_fused_experts(s, L.expert_dn[L.expert0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, c.moe_num_experts, ps,
+            if (!count(e, launch_gemv_fused_experts(s, L.dn_dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, c.moe_num_experts, ps,
                                                     (size_t)2 * dff, e->moe_out, h, e->ctx->sm_count, e->ctx->d_err, pdl), "expert down (+swiglu)")) return false;
             pend_moe = &L;
             continue;
@@ -375,10 +377,10 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
                 ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32; ra.logits = e->router_logits; ra.done = e->router_done;
                 if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
-                if (!count(e, launch_gemv_experts(s, L.expert_gu[L.expert0]->dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
+                if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
                                                   e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert gate_up")) return false;
                 if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
-                if (!count(e, launch_gemv_experts(s, L.expert_dn[L.expert0]->dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
+                if (!count(e, launch_gemv_experts(s, L.dn_dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
                                                   e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert down")) return false;
                 if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl, ra.route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr, c.moe_num_experts), "moe combine")) return false;
             }
@@ -566,33 +568,64 @@ std::string setup_moe_layer(KronosCudaEngine *e, EngineLayer &L, const KronosCud
     if (!d.moe_shard || d.moe_shard_len < (size_t)E * rec) return "expert shard is shorter than moe_num_experts records";
     if (!dev_alloc(e, L.router_w, (size_t)E * h, d.moe_router_w)) return ctx->err;
     if (d.moe_router_bias && !dev_alloc(e, L.router_bias, E, d.moe_router_bias)) return ctx->err;
-    std::vector<const uint8_t *> gu_bases(E), dn_bases(E);
+    std::vector<const uint8_t *> gu_bases(E, nullptr), dn_bases(E, nullptr);
     std::vector<ExpertCodebook> gu_books(E), dn_books(E);
-    L.expert_gu.assign(E, nullptr);
-    L.expert_dn.assign(E, nullptr);
     L.expert0 = c.ep_size > 1 ? c.ep_rank : 0;         // the first expert this rank holds: geometry template of the expert kernels
-    bool first = true;
-    for (uint32_t x = 0; x < E; ++x) {
-        if (c.ep_size > 1 && x % c.ep_size != c.ep_rank) { gu_bases[x] = nullptr; dn_bases[x] = nullptr; gu_books[x] = ExpertCodebook{}; dn_books[x] = ExpertCodebook{}; continue; }
+    // every expert of the layer has the same shapes, so the same image sizes: one device allocation and one upload per
+    // layer (12,288 single allocations took 25 s for the 48 x 128 experts of the 30B-A3B shape), images repacked on the
+    // host by a few threads
+    std::vector<uint32_t> owned;
+    for (uint32_t x = 0; x < E; ++x)
+        if (c.ep_size <= 1 || x % c.ep_size == c.ep_rank) owned.push_back(x);
+    auto desc_of = [&](uint32_t x, bool down) {
         const uint8_t *r = d.moe_shard + (size_t)x * rec;
         KronosCudaMatrixDesc m{};
         m.kind = KRONOS_CUDA_MATRIX_NF; m.bits = bits; m.scale_group_chunks = sgc;
-        m.rows = 2 * dff; m.cols = h; std::memcpy(m.codebook, r, 16); m.data0 = r + gu_off; m.len0 = gu_bytes;
-        KronosCudaMatrix *gu = kronos_cuda_matrix_upload(ctx, &m, 0);
-        if (!gu) return "expert " + std::to_string(x) + " gate_up: " + ctx->err;
-        L.expert_gu[x] = gu;
-        m.rows = h; m.cols = dff; std::memcpy(m.codebook, r + 16, 16); m.data0 = r + dn_off; m.len0 = dn_bytes;
-        KronosCudaMatrix *dn = kronos_cuda_matrix_upload(ctx, &m, 0);
-        if (!dn) return "expert " + std::to_string(x) + " down: " + ctx->err;
-        L.expert_dn[x] = dn;
+        if (!down) { m.rows = 2 * dff; m.cols = h; std::memcpy(m.codebook, r, 16); m.data0 = r + gu_off; m.len0 = gu_bytes; }
+        else { m.rows = h; m.cols = dff; std::memcpy(m.codebook, r + 16, 16); m.data0 = r + dn_off; m.len0 = dn_bytes; }
+        return m;
+    };
+    MatrixGeom g_gu, g_dn;
+    std::string why;
+    {
+        const KronosCudaMatrixDesc m0 = desc_of(owned[0], false), m1 = desc_of(owned[0], true);
+        if (!matrix_geometry(m0, g_gu, why) || !matrix_geometry(m1, g_dn, why)) return "expert matrices: " + why;
+    }
+    const size_t img_gu = (g_gu.image_bytes() + 255) & ~(size_t)255, img_dn = (g_dn.image_bytes() + 255) & ~(size_t)255, img = img_gu + img_dn;
+    std::vector<uint8_t> host;
+    try { host.resize(owned.size() * img); } catch (...) { return "out of host memory for the expert images"; }
+    std::vector<MatrixGeom> geo_gu(owned.size()), geo_dn(owned.size());
+    std::vector<std::string> errs(owned.size());
+    {
+        const unsigned n_thr = std::max(1u, std::min(16u, std::thread::hardware_concurrency()));
+        std::vector<std::thread> pool;
+        for (unsigned t = 0; t < n_thr; ++t)
+            pool.emplace_back([&, t] {
+                for (size_t i = t; i < owned.size(); i += n_thr) {
+                    const KronosCudaMatrixDesc m0 = desc_of(owned[i], false), m1 = desc_of(owned[i], true);
+                    if (!matrix_geometry(m0, geo_gu[i], errs[i]) || !matrix_geometry(m1, geo_dn[i], errs[i])) continue;
+                    repack_matrix(m0, geo_gu[i], false, host.data() + i * img, 1);
+                    repack_matrix(m1, geo_dn[i], false, host.data() + i * img + img_gu, 1);
+                }
+            });
+        for (std::thread &th : pool) th.join();
+    }
+    for (size_t i = 0; i < owned.size(); ++i)
+        if (!errs[i].empty()) return "expert " + std::to_string(owned[i]) + ": " + errs[i];
+    if (!dev_alloc(e, L.d_experts, host.size(), host.data()) || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "expert upload")) return ctx->err;
+    bool first = true;
+    for (size_t i = 0; i < owned.size(); ++i) {
+        const uint32_t x = owned[i];
+        DeviceMatrix gu{geo_gu[i], L.d_experts + i * img, img_gu}, dn{geo_dn[i], L.d_experts + i * img + img_gu, img_dn};
         // every expert of a layer decodes with one kernel: NF4 falls back to the general decode for all of them as soon
         // as one codebook does not fit the two-table form
-        const int fg = expert_codebook(gu->dm, gu_books[x]), fd = expert_codebook(dn->dm, dn_books[x]);
+        const int fg = expert_codebook(gu, gu_books[x]), fd = expert_codebook(dn, dn_books[x]);
         if (fg < 0 || fd < 0) return "expert matrices in an unsupported format";
         L.gu_fmt = first ? fg : (L.gu_fmt == fg ? fg : (int)FMT_COUNT);
         L.dn_fmt = first ? fd : (L.dn_fmt == fd ? fd : (int)FMT_COUNT);
+        if (first) { L.gu_dm = gu; L.dn_dm = dn; }
         first = false;
-        gu_bases[x] = gu->dm.d_base; dn_bases[x] = dn->dm.d_base;
+        gu_bases[x] = gu.d_base; dn_bases[x] = dn.d_base;
     }
     if (!dev_alloc(e, L.d_gu_books, E, gu_books.data()) || !dev_alloc(e, L.d_dn_books, E, dn_books.data()) ||
         !dev_alloc(e, L.d_gu_bases, E, gu_bases.data()) || !dev_alloc(e, L.d_dn_bases, E, dn_bases.data()) ||
@@ -618,8 +651,6 @@ void kronos_cuda_engine_destroy(KronosCudaEngine *e) {
     {
         for (KronosCudaMatrix *m : {L.qkv, L.o, L.gate_up, L.down})
             if (m) kronos_cuda_matrix_free(e->ctx, m);
-        for (KronosCudaMatrix *m : L.expert_gu) if (m) kronos_cuda_matrix_free(e->ctx, m);
-        for (KronosCudaMatrix *m : L.expert_dn) if (m) kronos_cuda_matrix_free(e->ctx, m);
     }
     if (e->lm_head) kronos_cuda_matrix_free(e->ctx, e->lm_head);
     if (e->embed_matrix) kronos_cuda_matrix_free(e->ctx, e->embed_matrix);

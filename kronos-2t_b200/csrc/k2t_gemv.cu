@@ -55,7 +55,7 @@ static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_cou
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
     const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(NT), NT * 32 * 4, 1, sm_count);
     cudaError_t e = cudaSuccess;
-    if (t.smem > 48 * 1024) e = cudaFuncSetAttribute(gemv_kernel<FMT, NT, DOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem);
+    e = allow_dynamic_smem(reinterpret_cast<const void *>(gemv_kernel<FMT, NT, DOTS>), t.smem);
     if (e != cudaSuccess) return e;
     return launch_kernel(gemv_kernel<FMT, NT, DOTS>, dim3(t.teams), dim3(32 * t.wk), t.smem, stream, a.pdl != 0, a);
 }
@@ -122,10 +122,8 @@ template <int FMT>
 static cudaError_t launch_expert_fmt(cudaStream_t stream, const GemvArgs &a, const ExpertBatch &b, uint32_t n_slot, int sm_count) {
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
     const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(1), 32 * 4, n_slot, sm_count);
-    if (t.smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_expert_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t.smem);
-        if (e != cudaSuccess) return e;
-    }
+    cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(gemv_expert_kernel<FMT>), t.smem);
+    if (e != cudaSuccess) return e;
     return launch_kernel(gemv_expert_kernel<FMT>, dim3(t.teams, n_slot), dim3(32 * t.wk), t.smem, stream, a.pdl != 0, a, b);
 }
 

@@ -134,13 +134,10 @@ static bool choose_fused(uint32_t n_rb, uint32_t np, uint32_t warp_bytes, uint32
     return true;
 }
 
+// the 1 KiB every CTA reserves in choose_fused also covers the few static bytes of a kernel (the E8Q2 template table)
 template <typename K>
-static cudaError_t allow_smem(K kernel, bool &done) {
-    if (done) return cudaSuccess;
-    // the 1 KiB every CTA reserves in choose_fused also covers the few static bytes of a kernel (the E8Q2 template table)
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(FUSED_SMEM_LIMIT - 1024u));
-    if (e == cudaSuccess) done = true;
-    return e;
+static cudaError_t allow_smem(K kernel, bool &) {
+    return allow_dynamic_smem(reinterpret_cast<const void *>(kernel), FUSED_SMEM_LIMIT - 1024u);
 }
 
 template <int FMT>

@@ -849,8 +849,8 @@ cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *del
 cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl) {
     if (a.n_experts > ROUTER_MAX_EXPERTS || a.top_k > ROUTER_MAX_TOPK || a.hidden * 4 > 160 * 1024) return cudaErrorInvalidValue;
     const size_t smem = (size_t)a.hidden * 4;
-    if (smem > 40 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(moe_router_kernel), smem + 4096);      // beside 3 KiB of static shared memory
         if (e != cudaSuccess) return e;
     }
     if (a.logits == nullptr || a.done == nullptr) return cudaErrorInvalidValue;
@@ -875,8 +875,8 @@ cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *
     if (tp.tp > 1 && ((size_t)n_tok * n > tp.ll_slot || tp_done == nullptr)) return cudaErrorInvalidValue;
     const size_t smem = (size_t)n * sizeof(float) * (tp.tp > 1 ? 2 : 1);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(rmsnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(rmsnorm_quant_kernel), smem);
         if (e != cudaSuccess) return e;
     }
     // one warp per 64-value chunk where that fits: the load and the rotation each take one round
@@ -890,8 +890,8 @@ cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
 template <int HD, bool KV4>
 static cudaError_t launch_partial(cudaStream_t s, dim3 grid, bool pdl, const AttnArgs &a) {
     constexpr size_t smem = attn_partial_smem<HD, KV4>();
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, KV4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_partial_kernel<HD, KV4>), smem);
         if (e != cudaSuccess) return e;
     }
     return launch_kernel(attn_partial_kernel<HD, KV4>, grid, dim3(128), smem, s, pdl, a);
@@ -910,7 +910,7 @@ cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl) {
     const size_t smem = attn_smem_bytes();
     if (a.head_dim != 64 && a.head_dim != 128) return cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(attn_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_fused_kernel), smem);
     if (e != cudaSuccess) return e;
     return launch_kernel(attn_fused_kernel, dim3(a.n_q), dim3(ATTN_THREADS), smem, s, pdl, a);
 }
