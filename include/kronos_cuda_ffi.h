@@ -118,6 +118,15 @@ int32_t kronos_cuda_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, cons
                          const float *xs, const int32_t *xsum, size_t n_tok, float *out,
                          size_t out_stride, int32_t *int_dots);
 
+/* DenseMoeRouter::route_sorted (src/model/sparse_moe.rs:86-182): logits = W x_norm (+ bias), scoring 0 = softmax over all
+ * experts, 1 = softmax over the selected logits, 2 = sigmoid; the top_k experts by score (the earlier expert wins ties),
+ * optionally renormalised (norm_topk), returned in ascending expert order.  Host buffers: router_w[n_experts][hidden],
+ * router_bias[n_experts] or NULL, x_norm[hidden]; route_ids / route_w receive min(top_k, n_experts) entries.  Returns that
+ * count, -1 on error.  Non-finite inputs still yield ids inside [0, n_experts) (unranked slots are expert i, weight 0). */
+int32_t kronos_cuda_moe_route(KronosCudaContext *ctx, const float *router_w, const float *router_bias, const float *x_norm,
+                              uint32_t n_experts, uint32_t hidden, uint32_t top_k, int32_t norm_topk, uint32_t scoring,
+                              uint32_t *route_ids, float *route_w);
+
 /* LinearBackend::forward for the Nibble4 / NfSdot arms (real_llm.rs:825-858) fed by
  * Int8ChunkActivation::populate_fwht: y[t] = W * rotate_quantize(x[t]).  x[n_tok][cols] fp32 in,
  * out[n_tok][rows] fp32.  This is the host-buffer call the benchmark's end-to-end number uses. */

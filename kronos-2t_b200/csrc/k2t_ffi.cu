@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "k2t_context.h"
+#include "k2t_model_kernels.h"
 
 using namespace k2t;
 
@@ -307,6 +308,42 @@ static int32_t linear_impl(KronosCudaContext *ctx, const KronosCudaMatrix *m, co
     if (!cuda_ok(ctx, cudaMemcpyAsync(out, ctx->out.p, n_out * 4, cudaMemcpyDeviceToHost, s), "copy out")) return -1;
     if (!wait) return 0;
     return sync_and_check(ctx, "linear") ? 0 : -1;
+}
+
+int32_t kronos_cuda_moe_route(KronosCudaContext *ctx, const float *router_w, const float *router_bias, const float *x_norm,
+                              uint32_t n_experts, uint32_t hidden, uint32_t top_k, int32_t norm_topk, uint32_t scoring,
+                              uint32_t *route_ids, float *route_w) {
+    if (!ctx) return -1;
+    ctx->err.clear();
+    if (!router_w || !x_norm || !route_ids || !route_w) return fail(ctx, "moe_route: NULL buffer"), -1;
+    if (n_experts < 1 || n_experts > 256 || top_k < 1 || top_k > 32 || hidden == 0 || hidden % 4 || scoring > 2)
+        return fail(ctx, "moe_route: 1..256 experts, 1..32 routes, hidden a multiple of 4, scoring 0..2"), -1;
+    if (!make_current(ctx)) return -1;
+    const size_t wb = (size_t)n_experts * hidden * 4;
+    // scratch: weights | bias | x | logits[256] | done word | ids[32] | weights[32]
+    const size_t off_b = wb, off_x = off_b + (size_t)n_experts * 4, off_l = off_x + (size_t)hidden * 4, off_d = off_l + 1024, off_i = off_d + 16, off_w = off_i + 128;
+    if (!reserve(ctx, ctx->x, off_w + 128)) return -1;
+    uint8_t *base = static_cast<uint8_t *>(ctx->x.p);
+    cudaStream_t s = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(base, router_w, wb, cudaMemcpyHostToDevice, s), "copy router") ||
+        (router_bias && !cuda_ok(ctx, cudaMemcpyAsync(base + off_b, router_bias, (size_t)n_experts * 4, cudaMemcpyHostToDevice, s), "copy router bias")) ||
+        !cuda_ok(ctx, cudaMemcpyAsync(base + off_x, x_norm, (size_t)hidden * 4, cudaMemcpyHostToDevice, s), "copy x") ||
+        !cuda_ok(ctx, cudaMemsetAsync(base + off_d, 0, 16, s), "clear counter"))
+        return -1;
+    RouterArgs ra{};
+    ra.w = reinterpret_cast<const float *>(base); ra.bias = router_bias ? reinterpret_cast<const float *>(base + off_b) : nullptr;
+    ra.x = reinterpret_cast<const float *>(base + off_x);
+    ra.n_experts = n_experts; ra.hidden = hidden; ra.top_k = top_k; ra.norm_topk = norm_topk; ra.scoring = scoring;
+    ra.route_ids = reinterpret_cast<uint32_t *>(base + off_i); ra.route_w = reinterpret_cast<float *>(base + off_w);
+    ra.logits = reinterpret_cast<float *>(base + off_l); ra.done = reinterpret_cast<uint32_t *>(base + off_d);
+    const uint32_t k = std::min(top_k, n_experts);
+    ctx->launches += 1;
+    if (!cuda_ok(ctx, launch_moe_router(s, ra, false), "moe_router") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(route_ids, ra.route_ids, k * 4, cudaMemcpyDeviceToHost, s), "copy routes") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(route_w, ra.route_w, k * 4, cudaMemcpyDeviceToHost, s), "copy routes") ||
+        !sync_and_check(ctx, "moe_route"))
+        return -1;
+    return (int32_t)k;
 }
 
 int32_t kronos_cuda_linear(KronosCudaContext *ctx, const KronosCudaMatrix *m, const float *x, size_t n_tok, float *out) {

@@ -80,6 +80,7 @@ def load_library():
     sig("kronos_cuda_matrix_image", sz, C.POINTER(MatrixDesc), u32, vp, sz)
     sig("kronos_cuda_fwht_quant", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
     sig("kronos_cuda_gemv", i32, vp, vp, vp, vp, vp, sz, vp, sz, vp)
+    sig("kronos_cuda_moe_route", i32, vp, vp, vp, vp, u32, u32, u32, i32, u32, vp, vp)
     sig("kronos_cuda_linear", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_linear_async", i32, vp, vp, vp, sz, vp)
     sig("kronos_cuda_fwht_quant_dev", i32, vp, vp, sz, sz, vp, vp, u64, vp, vp, vp)
@@ -259,6 +260,18 @@ class Context:
         dots = np.empty((n, mat.rows, nc), np.int32) if want_dots else None
         self._check(self.L.kronos_cuda_gemv(self.handle, mat.handle, _p(xq), _p(xs), _p(xm), n, _p(out), mat.rows, _p(dots)))
         return (out, dots) if want_dots else out
+
+    def moe_route(self, router_w, x_norm, top_k, router_bias=None, norm_topk=True, scoring=0):
+        """(expert ids ascending, weights) of DenseMoeRouter::route_sorted for one normalised hidden vector."""
+        w = _np(router_w, np.float32)
+        n_experts, hidden = w.shape
+        x = _np(x_norm, np.float32).reshape(hidden)
+        b = None if router_bias is None else _np(router_bias, np.float32)
+        ids, wt = np.zeros(32, np.uint32), np.zeros(32, np.float32)
+        k = self.L.kronos_cuda_moe_route(self.handle, _p(w), _p(b), _p(x), n_experts, hidden, top_k, int(norm_topk), scoring, _p(ids), _p(wt))
+        if k < 0:
+            self._check(-1)
+        return ids[:k].copy(), wt[:k].copy()
 
     def linear(self, mat, x):
         x = _np(x, np.float32).reshape(-1, mat.cols)

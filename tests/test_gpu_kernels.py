@@ -260,3 +260,32 @@ def test_linear_async_equals_linear(ctx, oracle):
         for dm in dms:
             dm.free()
 
+
+
+def test_router_kernel_routes_and_survives_non_finite_inputs(ctx):
+    """kronos_cuda_moe_route alone (the router indexes nothing by route id, so hostile inputs cannot fault here): ordinary
+    inputs give distinct ascending ids whose renormalised weights sum to 1 and match a numpy softmax / top-k; NaN and Inf
+    activations or weights still give ids inside [0, n_experts) - the expert kernels index their tables with them."""
+    rng = np.random.Generator(np.random.PCG64(12))
+    n_experts, hidden, k = 64, 256, 8
+    w = (rng.standard_normal((n_experts, hidden)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(hidden).astype(np.float32)
+    ids, wt = ctx.moe_route(w, x, k)
+    logits = (w.astype(np.float64) @ x.astype(np.float64))
+    p = np.exp(logits - logits.max()); p /= p.sum()
+    want = np.sort(np.argsort(-p, kind="stable")[:k])
+    assert list(ids) == list(want) and np.all(np.diff(ids.astype(np.int64)) > 0)
+    assert abs(float(wt.sum()) - 1.0) < 1e-5 and np.allclose(wt, p[want] / p[want].sum(), rtol=1e-4)
+    for scoring in (0, 1, 2):
+        for poison in ("nan_x", "inf_x", "nan_w", "all_nan"):
+            xx, ww = x.copy(), w.copy()
+            if poison == "nan_x":
+                xx[7] = np.nan
+            elif poison == "inf_x":
+                xx[3], xx[4] = np.inf, -np.inf
+            elif poison == "nan_w":
+                ww[5, :] = np.nan
+            else:
+                xx[:] = np.nan
+            ids, wt = ctx.moe_route(ww, xx, k, scoring=scoring)
+            assert len(ids) == k and np.all(ids < n_experts), (scoring, poison, ids)
