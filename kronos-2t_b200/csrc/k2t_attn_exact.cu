@@ -46,11 +46,11 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     __shared__ float s_red[8][SCORE_TILE / 32];
     __shared__ __align__(8) uint64_t s_bar;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t blk = blockIdx.x, kvh = blockIdx.y, G = a.group;
+    const uint32_t blk = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z, G = a.group, n_q = a.n_kv * G;
     pdl_wait();
     pdl_trigger();
     // sliding window: ctx = the active positions (sinks + the last window - sinks); index t -> position -> ring row
-    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + 1, ctx = a.ring.active_len(seq_len), t0 = blk * SCORE_TILE;
+    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + tok + 1, ctx = a.ring.active_len(seq_len), t0 = blk * SCORE_TILE;
     const bool windowed = a.ring.window > 0;
     if (t0 >= ctx) return;
     const uint32_t n = min(SCORE_TILE, ctx - t0);
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     }
     // the group's int8 queries (NF4 cache: gathered in the packed column order of a cached row)
     for (uint32_t i = tid; i < G * QW; i += SCORE_TILE) {
-        const int8_t *qb = a.q_i8 + (size_t)(kvh * G + i / QW) * HD;
+        const int8_t *qb = a.q_i8 + ((size_t)tok * n_q + kvh * G + i / QW) * HD;
         const uint32_t wi = i % QW;
         if (KV4) {        // packed word w of a 64-value group holds columns (c, 16+c, c+1, 16+c+1 | c+2, ...) of a 32-column half
             const uint32_t g = wi / 16, w = (wi % 16) / 2, u = wi % 2;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     }
     float qas[8];
 #pragma unroll
-    for (int g = 0; g < 8; ++g) qas[g] = g < (int)G ? __fmul_rn(__ldcg(a.q_scale + kvh * G + g), a.attn_scale) : 0.0f;
+    for (int g = 0; g < 8; ++g) qas[g] = g < (int)G ? __fmul_rn(__ldcg(a.q_scale + (size_t)tok * n_q + kvh * G + g), a.attn_scale) : 0.0f;
     __syncthreads();                               // queries staged, barrier initialised
     if (!windowed) {
         const bool arrived = mbar_wait_bounded(bar, 0);
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
                 const int dot = NB == 2 ? up[g][0] + up[g][NB - 1] : up[g][0];
                 s = grouped ? __fmul_rn((float)dot, __fmul_rn(kst[0], qas[g])) : __fmul_rn(__fmul_rn((float)dot, kst[0]), qas[g]);
             }
-            a.sc[(size_t)(kvh * G + g) * a.sc_stride + t] = s;
+            a.sc[((size_t)tok * n_q + kvh * G + g) * a.sc_stride + t] = s;
         }
         const float m = warp_max(s);
         if (lane == 0) s_red[g][warp] = m;
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
         float m = s_red[tid][0];
 #pragma unroll
         for (uint32_t w = 1; w < SCORE_TILE / 32; ++w) m = fmaxf(m, s_red[tid][w]);
-        a.bmax[(size_t)(kvh * G + tid) * a.blk_stride + blk] = m;
+        a.bmax[((size_t)tok * n_q + kvh * G + tid) * a.blk_stride + blk] = m;
     }
     if (tid == 0 && !windowed) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -196,7 +196,7 @@ struct ValSmem {
     static __host__ __device__ size_t bytes(uint32_t ctx_cap) { return 128 + (size_t)VAL_NST * STAGE + (size_t)NW * ctx_cap * 4; }
 };
 
-#define VAL_MARK(i) do { if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) a.trace[i] = (unsigned long long)clock64(); } while (0)
+#define VAL_MARK(i) do { if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.trace[i] = (unsigned long long)clock64(); } while (0)
 
 template <int HD, bool KV4>
 __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAttnArgs a) {
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     __shared__ float s_cb[16];
     __shared__ uint32_t s_fail;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t qh = blockIdx.x, G = a.group, kvh = qh / G;
+    const uint32_t qh = blockIdx.x, tok = blockIdx.y, G = a.group, kvh = qh / G, n_q = a.n_kv * G;
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(dyn);           // full[VAL_NST], then empty[VAL_NST]
     uint8_t *stages = dyn + 128;
     float *W = reinterpret_cast<float *>(dyn + 128 + (size_t)VAL_NST * Sm::STAGE);
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     if (KV4 && tid < 16) s_cb[tid] = NF4_KV_CENTROIDS[tid];
     pdl_wait();
     pdl_trigger();
-    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + 1, ctx = a.ring.active_len(seq_len), cap = a.ctx_cap;
+    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + tok + 1, ctx = a.ring.active_len(seq_len), cap = a.ctx_cap;
     const KvRing ring = a.ring;
     if (ctx > cap) {                       // the launcher sizes shared memory for the cache length: cannot happen
         if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 5u);
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     {
         const uint32_t nblk = (ctx + SCORE_TILE - 1) / SCORE_TILE;
         float m = -INFINITY;
-        for (uint32_t i = tid; i < nblk; i += VAL_THREADS) m = fmaxf(m, __ldcg(a.bmax + (size_t)qh * a.blk_stride + i));
+        for (uint32_t i = tid; i < nblk; i += VAL_THREADS) m = fmaxf(m, __ldcg(a.bmax + ((size_t)tok * n_q + qh) * a.blk_stride + i));
         m = warp_max(m);
         if (lane == 0) s_red[warp] = m;
         __syncthreads();
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     VAL_MARK(1);
     const float mx = s_max;
     const uint32_t n4 = ctx & ~3u;
-    const float *sc = a.sc + (size_t)qh * a.sc_stride;
+    const float *sc = a.sc + ((size_t)tok * n_q + qh) * a.sc_stride;
     {   // eight loads in flight per thread (the scores come from L2)
         uint32_t t = tid;
         for (; t + 7 * VAL_THREADS < n4; t += 8 * VAL_THREADS) {
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
             if (lane == 0) mbar_arrive(bar0 + 8 * (VAL_NST + st));          // this warp is done with the stage
         }
         if (failed) atomicExch(&s_fail, 1u);
-        if (a.trace != nullptr && blockIdx.x == 0 && tid == 0) a.trace[8] = (unsigned long long)t_wait;
+        if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) a.trace[8] = (unsigned long long)t_wait;
         s_o[d] = o;
     } else if (warp == CW && lane == 0) {
         for (uint32_t i = VAL_NST; i < n_tiles; ++i) {           // tile i reuses the stage of tile i - VAL_NST once every chain warp has left it
@@ -431,14 +431,15 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
         const uint32_t b = warp;
         float x0 = s_o[b * 64 + 2 * lane], x1 = s_o[b * 64 + 2 * lane + 1];
         warp_ifwht64(x0, x1, b, lane);
-        if (a.attn_out != nullptr) reinterpret_cast<float2 *>(a.attn_out + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
+        if (a.attn_out != nullptr && tok + 1 == gridDim.y) reinterpret_cast<float2 *>(a.attn_out + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
         const uint32_t c = qh * NB + b;
         warp_fwht64(x0, x1, a.out_chunk0 + c, lane);
         int q0, q1, sum;
         float scl;
         warp_quant64(x0, x1, q0, q1, scl, sum);
-        reinterpret_cast<char2 *>(a.out_q + (size_t)c * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
-        if (lane == 0) { a.out_scales[c] = scl; a.out_sums[c] = sum; }
+        const size_t row = (size_t)tok * n_q * NB;           // o_proj activation row of this token, in chunks
+        reinterpret_cast<char2 *>(a.out_q + (row + c) * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+        if (lane == 0) { a.out_scales[row + c] = scl; a.out_sums[row + c] = sum; }
     }
     VAL_MARK(7);
 }
@@ -447,15 +448,15 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
 // launchers
 // ------------------------------------------------------------------------------------------------
 template <int HD, bool KV4>
-static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl) {
+static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok) {
     const size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_values_kernel<HD, KV4>), smem);
     if (e != cudaSuccess) return e;
     const uint32_t nblk = (a.ctx_cap + SCORE_TILE - 1) / SCORE_TILE;
-    e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv), dim3(SCORE_TILE), 0, s, pdl, a);
+    e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv, n_tok), dim3(SCORE_TILE), 0, s, pdl, a);
     if (e != cudaSuccess) return e;
-    return launch_kernel(attn_values_kernel<HD, KV4>, dim3(a.n_kv * a.group), dim3(VAL_THREADS), smem, s, pdl, a);
+    return launch_kernel(attn_values_kernel<HD, KV4>, dim3(a.n_kv * a.group, n_tok), dim3(VAL_THREADS), smem, s, pdl, a);
 }
 
 size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits) {
@@ -464,10 +465,10 @@ size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits) {
     return (200 * 1024 - ring) / (4 * nw);
 }
 
-cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl) {
-    if (a.group > 8 || a.group == 0) return cudaErrorInvalidValue;
-    if (a.head_dim == 64) return a.kv_bits == 4 ? launch_exact<64, true>(s, a, pdl) : launch_exact<64, false>(s, a, pdl);
-    if (a.head_dim == 128) return a.kv_bits == 4 ? launch_exact<128, true>(s, a, pdl) : launch_exact<128, false>(s, a, pdl);
+cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok) {
+    if (a.group > 8 || a.group == 0 || n_tok == 0) return cudaErrorInvalidValue;
+    if (a.head_dim == 64) return a.kv_bits == 4 ? launch_exact<64, true>(s, a, pdl, n_tok) : launch_exact<64, false>(s, a, pdl, n_tok);
+    if (a.head_dim == 128) return a.kv_bits == 4 ? launch_exact<128, true>(s, a, pdl, n_tok) : launch_exact<128, false>(s, a, pdl, n_tok);
     return cudaErrorInvalidValue;
 }
 

@@ -112,6 +112,8 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
     return cuda_ok(e->ctx, cudaMemsetAsync(p, 0, bytes, e->ctx->stream), "clear");
 }
 
+constexpr uint32_t ATTN_BATCH = 16;    // tokens whose attention runs side by side (= the prompt batch, MAX_BATCH below)
+
 void dev_free(KronosCudaEngine *e, void *p) {
     if (!p) return;
     for (size_t i = 0; i < e->allocs.size(); ++i)
@@ -147,7 +149,7 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
     e->split_kv = e->ring.window == 0 && ((c.flags & KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION) != 0 || longest > attention_exact_max_ctx(hd, bits));
     if (e->ring.window && longest > attention_exact_max_ctx(hd, bits)) return fail(ctx, "kv_window is longer than the attention kernel can hold");
     const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * e->kv_stride;
-    const bool ok = dev_alloc(e, e->attn_sc, (size_t)n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)n_q * ((e->kv_stride + 127) / 128)) &&
+    const bool ok = dev_alloc(e, e->attn_sc, (size_t)ATTN_BATCH * n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)ATTN_BATCH * n_q * ((e->kv_stride + 127) / 128)) &&
                     dev_alloc(e, e->k_q8, bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, bits == 4 ? slots * hd / 2 : slots * hd) &&
                     dev_alloc(e, e->k_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
                     dev_alloc(e, e->v_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots);
@@ -162,12 +164,18 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
 bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 1);
 
+constexpr uint32_t PASS_TOKENS = 4;    // tokens one weight pass serves (the reference's 4-token tiles in prompt batches)
+
 bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char *what, uint32_t n_tok = 1, size_t act_tok0 = 0) {
-    uint32_t launched = 0;
-    const size_t cols = m->dm.geom.cols, nc = cols / 64;
-    cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q + act_tok0 * cols, e->act_s + act_tok0 * nc, e->act_m + act_tok0 * nc, n_tok, out,
-                                  m->dm.geom.rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
-    return count(e, err, what, launched);
+    const size_t cols = m->dm.geom.cols, nc = cols / 64, rows = m->dm.geom.rows;
+    for (uint32_t t0 = 0; t0 < n_tok; t0 += PASS_TOKENS) {
+        uint32_t launched = 0;
+        const size_t a0 = act_tok0 + t0;
+        cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q + a0 * cols, e->act_s + a0 * nc, e->act_m + a0 * nc, std::min(PASS_TOKENS, n_tok - t0),
+                                      out + (size_t)t0 * rows, rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
+        if (!count(e, err, what, launched)) return false;
+    }
+    return true;
 }
 
 bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n) {
@@ -189,7 +197,8 @@ bool tp_gather(KronosCudaEngine *e, const float *slice, float *all, uint32_t n) 
     return count(e, launch_tp_exchange(e->ctx->stream, e->tp, slice, all, n, n, e->pdl), "tp gather");
 }
 
-constexpr uint32_t MAX_BATCH = 4;      // tokens per weight pass in prompt processing (the reference's 4-token tiles)
+constexpr uint32_t MAX_BATCH = 16;     // tokens per prompt batch: their projections run as weight passes of PASS_TOKENS tokens, their attention side by side
+static_assert(MAX_BATCH == ATTN_BATCH, "the attention scratch is sized for one prompt batch");
 
 // Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
 // output of a row-parallel projection: the kernel exchanges and sums the ranks' partials itself.
@@ -208,6 +217,7 @@ bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *
 enum class Tail { Greedy, LastLogits, AllLogits, None };
 
 bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, bool long_ctx);
+bool enqueue_attention_batch(KronosCudaEngine *e, uint32_t l, uint32_t T);
 
 // One token with the small operators folded into the GEMVs (k2t_gemv_fused.cu): per dense layer
 //   [residual + norm -> qkv]  [attention]  [o]  [residual + norm -> gate_up]  [SwiGLU -> down]
@@ -281,6 +291,33 @@ bool enqueue_fused_step(KronosCudaEngine *e, bool embed, Tail tail, bool long_ct
     if (!count(e, launch_gemv_fused(s, e->lm_head->dm, p, e->logits, e->ctx->sm_count, e->ctx->d_err, pdl), "gemv lm_head (+norm)")) return false;
     if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, pdl), "argmax");
     return count(e, launch_advance_pos(s, e->d_pos, 1, pdl), "advance");
+}
+
+// Attention of all T tokens of a batch for layer l in three launches: bias / norm / RoPE / cache rows / int8 queries of every
+// token, then scores and values of the T tokens side by side (token t sees the positions up to its own, the rows of the
+// tokens before it in the batch included: they are in the cache by then).  Same arithmetic as the single-token kernels.
+bool enqueue_attention_batch(KronosCudaEngine *e, uint32_t l, uint32_t T) {
+    const KronosCudaEngineConfig &c = e->cfg;
+    cudaStream_t s = e->ctx->stream;
+    const EngineLayer &L = e->layers[l];
+    const uint32_t hd = c.head_dim;
+    QkvPostArgs qa{};
+    qa.qkv = e->qkv; qa.bias = L.qkv_bias; qa.q_norm = L.q_norm; qa.k_norm = L.k_norm; qa.rope = e->rope;
+    qa.pos = e->d_pos; qa.pos_offset = 0;
+    qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
+    qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
+    qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring;
+    if (!count(e, launch_qkv_post(s, qa, e->pdl, T), "qkv_post")) return false;
+    ExactAttnArgs xa{};
+    xa.q_i8 = e->q_i8; xa.q_scale = e->q_scale; xa.k_q8 = e->k_q8; xa.v_q8 = e->v_q8; xa.k_scale = e->k_scale; xa.v_scale = e->v_scale;
+    xa.pos = e->d_pos; xa.pos_offset = 0;
+    xa.sc = e->attn_sc; xa.bmax = e->attn_bmax; xa.attn_out = l + 1 == c.num_layers ? e->attn_tap : nullptr;
+    xa.out_q = e->act_q; xa.out_scales = e->act_s; xa.out_sums = e->act_m; xa.out_chunk0 = c.o_chunk0;
+    xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
+    xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
+    xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
+    xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err; xa.trace = nullptr;
+    return count(e, launch_attention_exact(s, xa, e->pdl, T), "attention", 2);
 }
 
 // Attention of token t of a batch of T for layer l: the output becomes row t of the o_proj activation.
@@ -365,8 +402,12 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
         const bool ffn_partial = c.tp_size > 1 || (c.ep_size > 1 && l > 0 && e->layers[l - 1].moe);
         if (!norm_quant(e, l == 0 ? nullptr : e->proj, L.input_norm, nullptr, T, e->pdl && (embed || l > 0), ffn_partial)) return false;
         if (!gemv(e, L.qkv, e->qkv, "gemv qkv", T)) return false;
-        for (uint32_t t = 0; t < T; ++t)
-            if (!enqueue_attention(e, l, t, T, long_ctx)) return false;
+        if (T > 1 && !e->split_kv) {
+            if (!enqueue_attention_batch(e, l, T)) return false;
+        } else {
+            for (uint32_t t = 0; t < T; ++t)
+                if (!enqueue_attention(e, l, t, T, long_ctx)) return false;
+        }
         if (!gemv(e, L.o, e->proj, "gemv o", T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
         if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
             if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl, c.tp_size > 1)) return false;
@@ -742,7 +783,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
               dev_alloc(e, e->logits, (size_t)MAX_BATCH * (c.tp_size > 1 ? c.vocab_total : c.vocab_size)) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
               dev_alloc(e, e->act_s, (size_t)MAX_BATCH * act_n / 64) && dev_alloc(e, e->act_m, (size_t)MAX_BATCH * act_n / 64) &&
-              dev_alloc(e, e->q_i8, q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, n_q) &&
+              dev_alloc(e, e->q_i8, (size_t)MAX_BATCH * q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, (size_t)MAX_BATCH * n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
               alloc_kv(e, c.kv_bits, c.kv_window, c.kv_sinks) &&
@@ -1194,13 +1235,13 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
         if (all_logits) std::memcpy(all_logits, last_logits, v * 4);
         return 0;
     }
-    // prompt: batches of up to MAX_BATCH tokens per weight pass (forward_prompt / forward_batch_sdot_impl,
-    // real_llm.rs:7407-7448, 7450-7860)
+    // prompt: batches of up to MAX_BATCH tokens (forward_prompt / forward_batch_sdot_impl, real_llm.rs:7407-7448, 7450-7860):
+    // every projection as weight passes of 4 tokens, the attention of the batch's tokens side by side
     if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
     for (size_t t0 = 0, T_done = 0; t0 < n_tok; t0 += T_done) {
         uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
         const size_t p0 = pos_start + t0;
-        if (p0 < ATTN_EXACT_CTX && p0 + T > ATTN_EXACT_CTX) T = (uint32_t)(ATTN_EXACT_CTX - p0);    // a batch stays on one side of the attention switch
+        if (e->split_kv && p0 < ATTN_EXACT_CTX && p0 + T > ATTN_EXACT_CTX) T = (uint32_t)(ATTN_EXACT_CTX - p0);    // split-KV kernels: a batch stays on one side of the attention switch
         const bool last = t0 + T == n_tok;
         if (tokens) {
             if (!cuda_ok(ctx, cudaMemcpyAsync(e->d_token, tokens + t0, T * 4, cudaMemcpyHostToDevice, ctx->stream), "copy tokens")) return -1;

@@ -324,10 +324,11 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     pdl_wait();
     pdl_trigger();
     if (head >= a.n_q + 2 * a.n_kv) return;
-    const uint32_t pos = __ldcg(a.pos) + a.pos_offset;
+    const uint32_t tok = blockIdx.y;             // token of the batch: its own fused qkv vector, position and query slots
+    const uint32_t pos = __ldcg(a.pos) + a.pos_offset + tok;
     const bool is_q = head < a.n_q, is_k = !is_q && head < a.n_q + a.n_kv;
     float *sh = s_head[warp];
-    const float *src = a.qkv + (size_t)head * hd;
+    const float *src = a.qkv + (size_t)tok * (a.n_q + 2 * a.n_kv) * hd + (size_t)head * hd;
     for (uint32_t i = lane; i < hd; i += 32) {
         float v = __ldcg(src + i);
         if (a.bias != nullptr) v = __fadd_rn(v, a.bias[(size_t)head * hd + i]);
@@ -388,7 +389,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     mx = warp_max(mx);
     int8_t *dst_q;
     float *dst_s;
-    if (is_q) { dst_q = a.q_i8 + (size_t)head * hd; dst_s = a.q_scale + head; }
+    if (is_q) { dst_q = a.q_i8 + ((size_t)tok * a.n_q + head) * hd; dst_s = a.q_scale + (size_t)tok * a.n_q + head; }
     else {
         const uint32_t kvh = is_k ? head - a.n_q : head - a.n_q - a.n_kv;
         const size_t slot = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq + a.ring.slot_of_pos(pos);
@@ -883,9 +884,9 @@ cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *
     const uint32_t threads = std::min(1024u, std::max(256u, (n / 64) * 32u));
     return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm, tp, tp_done);
 }
-cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl) {
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl, uint32_t n_tok) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;
-    return launch_kernel(qkv_post_kernel, dim3((heads + 3) / 4), dim3(128), 0, s, pdl, a);
+    return launch_kernel(qkv_post_kernel, dim3((heads + 3) / 4, n_tok), dim3(128), 0, s, pdl, a);
 }
 template <int HD, bool KV4>
 static cudaError_t launch_partial(cudaStream_t s, dim3 grid, bool pdl, const AttnArgs &a) {

@@ -130,10 +130,14 @@ struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scorin
 cudaError_t launch_embed(cudaStream_t s, const EmbedArgs &a, uint32_t n_tok, bool pdl);
 cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                  int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl);
-cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl);
+// n_tok consecutive tokens (positions *pos + pos_offset + t): qkv [n_tok][n_q + 2 n_kv][head_dim], q_i8 [n_tok][n_q][head_dim], q_scale [n_tok][n_q]
+cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl, uint32_t n_tok = 1);
 cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl);     // two kernels
-// any context length in the reference's summation order: two kernels (after launch_qkv_post)
-cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl);
+// any context length in the reference's summation order: two kernels (after launch_qkv_post).  n_tok consecutive tokens of a
+// batch are attended side by side (token t sees the positions up to its own): per-token query slots as above, scores
+// [n_tok][n_q][sc_stride], block maxima [n_tok][n_q][blk_stride], o_proj activation rows [n_tok][n_q * head_dim] (scales and
+// sums [n_tok][n_q * head_dim / 64]); attn_out (optional) receives the last token's output.
+cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok = 1);
 // longest context launch_attention_exact can serve (its value weights live in shared memory)
 size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits);
 // contexts of up to ATTN_EXACT_CTX positions: qkv_post + attention in one kernel (leaves longer contexts untouched)
