@@ -33,11 +33,38 @@ sys.path.insert(0, ROOT)
 SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048), (2048, 49152)]   # (K = cols, N = rows)
 FORMATS = ["b4", "b5", "b6", "nf4g128"]
 WORKLOAD = "gemv_sweep_batch1: K x N in 2048x2048, 2048x8192, 8192x2048, 2048x49152; b4, b5, b6, nf4g128"
+SWEEP_CONFIG = {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of distinct weights per step)"}      # the same dict in both arms
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one 2048x49152 launch from the ncu --set full captures summarised under
-# profiles/ (gemv_b4_2048x49152.md, gemv_nf4g128_2048x49152.md)
-NCU_DRAM_BYTES_PER_LAUNCH = {"b4": 53507072 + 124672, "nf4g128": 51937536 + 20224}
+GEMV_SOURCES = ("k2t_gemv_core.cuh", "k2t_gemv.cu", "k2t_device.cuh", "k2t_layout.h")
+
+
+def gemv_source_hash():
+    """sha256 over the sources of the GEMV kernel: a profile summary names the hash it was captured with."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in GEMV_SOURCES:
+        with open(os.path.join(ROOT, "kronos-2t_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(fmt):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one 2048x49152 launch, read from the ncu summary under profiles/ - only
+    when that summary was captured from the kernel sources as they are now (its `kernel-source-hash:` line); otherwise
+    (None, why)."""
+    import re
+    path = os.path.join(ROOT, "profiles", f"gemv_{fmt}_2048x49152.md")
+    if not os.path.exists(path):
+        return None, "no ncu summary under profiles/ for this format"
+    text = open(path).read()
+    m_hash = re.search(r"kernel-source-hash:\s*([0-9a-f]+)", text)
+    m_bytes = re.search(r"dram-bytes-per-launch:\s*([0-9]+)", text)
+    if not m_hash or not m_bytes:
+        return None, "the ncu summary carries no kernel-source-hash / dram-bytes-per-launch lines"
+    if m_hash.group(1) != gemv_source_hash():
+        return None, "the GEMV sources changed since the ncu capture (hash %s, now %s)" % (m_hash.group(1), gemv_source_hash())
+    return int(m_bytes.group(1)), os.path.relpath(path, ROOT)
 
 
 def fmt_spec(fmt):
@@ -183,7 +210,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "quantized_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4..6 -> int32, fp32 epilogue", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of weights per pass)"},
+        "config": SWEEP_CONFIG,
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -314,7 +341,7 @@ def run_b200(args, rank, world, local_rank):
     # HBM copies of the matrix (>= 256 MB) that no launch finds its weights in L2
     peak, peak_kind = peaks()
     kernels = []
-    tot_b = tot_us = 0.0
+    tot_b = tot_us = tot_us_iso = 0.0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for c in cases:
         wbytes = c["dm"].file_bytes
@@ -336,41 +363,81 @@ def run_b200(args, rank, world, local_rank):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (3 * 2 * copies)
         gbs = c["bytes"] / us / 1e3
+        # the same launches each behind the rotation kernel of its activation (the position a GEMV has in a decode step:
+        # its weight prefetch overlaps a tiny kernel, not the tail of another large GEMV), minus the rotation kernels alone
+        def graph_us(with_gemv):
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg, stream=stream):
+                for r in range(2):
+                    for m in clones:
+                        ctx.fwht_quant_dev(px, 1, c["m"]["cols"], pq, ps, pm)
+                        if with_gemv:
+                            ctx.gemv_dev(m, pq, ps, pm, 1, po)
+            ctx.set_stream(stream.cuda_stream)
+            gg.replay()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(3):
+                gg.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (3 * 2 * copies)
+        us_iso = max(graph_us(True) - graph_us(False), 1e-3)
         kernels.append({"case": f"{c['m']['fmt']} {c['m']['cols']}x{c['m']['rows']}", "us": round(us, 2),
-                        "GBps": round(gbs, 1), "frac": round(gbs / peak, 3)})
-        tot_b += c["bytes"]; tot_us += us
+                        "GBps": round(gbs, 1), "frac": round(gbs / peak, 3),
+                        "us_isolated": round(us_iso, 2), "frac_isolated": round(c["bytes"] / us_iso / 1e3 / peak, 3)})
+        tot_b += c["bytes"]; tot_us += us; tot_us_iso += us_iso
         del g
         for m in clones[1:]:
             m.free()
     big = [k for k in kernels if k["case"].endswith("x49152")]
     big_b = sum(c["bytes"] for c in cases if c["m"]["rows"] == 49152)
     big_us = sum(k["us"] for k in big)
+    big_us_iso = sum(k["us_isolated"] for k in big)
     achieved = big_b / big_us / 1e3
+    traffic, traffic_src = ncu_traffic("b4")
+    traffic_per_format = {f: ncu_traffic(f)[0] for f in ("b4", "nf4g128")}
     roofline = {"bound": "hbm", "kernel": "gemv_kernel, the four 2048x49152 launches of a sweep pass (78% of its bytes)",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "launch_form": "each case timed alone: a CUDA graph of back-to-back launches over distinct HBM copies of the matrix, "
                                "programmatic dependents of one another as in the decode engine (a launch streams its first weight stages "
                                "while the previous one drains); CUDA events around three replays",
-                "traffic": NCU_DRAM_BYTES_PER_LAUNCH["b4"], "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, b4 2048x49152)",
-                "traffic_note": "ncu captures of the b4 and nf4g128 launches: 53.63 / 51.96 MB against 53.68 / 52.10 MB algorithmic (profiles/)",
-                "traffic_per_format": NCU_DRAM_BYTES_PER_LAUNCH,
-                "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak},
+                "isolated": {"achieved": big_b / big_us_iso / 1e3, "frac": big_b / big_us_iso / 1e3 / peak,
+                             "form": "the same four launches, each behind the rotation kernel of its activation instead of another large GEMV "
+                                     "(what a decode step gives it), rotation time subtracted"},
+                "traffic": traffic, "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, b4 2048x49152)",
+                "traffic_source": traffic_src, "traffic_per_format": traffic_per_format,
+                "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak,
+                                    "achieved_isolated": tot_b / tot_us_iso / 1e3, "frac_isolated": tot_b / tot_us_iso / 1e3 / peak},
                 "per_launch": kernels}
 
     decode = None
     if not args.no_decode:
         decode = decode_tok_s(ctx, stream, timed_region=lambda fn: timed(fn, 1)[0], world=world)
 
+        roofline["decode"] = [_decode_entry("SmolLM2-135M b4", 192, "int8", "reference order", decode["tok_s"] / world, decode["weight_bytes_per_token"],
+                                            decode["kv_bytes_at_256"] // 256, peak)]
         if not args.no_decode_models:
             try:
-                decode["models"] = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+                decode["models"], roof, attn = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+                roofline["decode"] += roof
+                roofline["attention"] = attn
             except Exception as exc:      # the headline line must still come out; the failure is reported in it
                 decode["models_error"] = f"{type(exc).__name__}: {exc}"
         if not args.no_decode_moe:
             try:
-                decode["moe"] = decode_moe(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+                decode["moe"], roof = decode_moe(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+                roofline["decode"] += roof
             except Exception as exc:
                 decode["moe_error"] = f"{type(exc).__name__}: {exc}"
+        if world > 1:
+            try:
+                roofline["sharded_parity"] = sharded_parity(ctx, rank, world, dist)
+            except Exception as exc:
+                roofline["sharded_parity"] = {"error": f"{type(exc).__name__}: {exc}"}
+        roofline["decode_note"] = ("frac = bytes_per_token * tok_s / (n_gpus * peak): weights of one step in the reference's file format + the cached "
+                                   "rows the token attends to; n_gpus > 1: the Qwen2-7B shape tensor-parallel (tp) and the Qwen3-30B-A3B shape "
+                                   "expert-parallel (ep) over all ranks - strong scaling of ONE token stream")
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -383,8 +450,7 @@ def run_b200(args, rank, world, local_rank):
             "metric": "quantized_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "step_form": "one CUDA graph of 32 kernels per step", "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x 4..6-bit codes -> int32, fp32 epilogue", "data": "synthetic (random codes)",
-            "config": {"workload": WORKLOAD, "l2_policy": "inputs larger than L2 (343 MB of distinct weights per step)",
-                       "per_rank": "each rank runs its own sweep (replicas, no collective)"},
+            "config": SWEEP_CONFIG, "per_rank": "each rank runs its own sweep (replicas, no collective)",
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -500,7 +566,7 @@ def decode_tok_s(ctx, stream, timed_region, world):
     out = {"workload": DECODE_WORKLOAD, "tok_s": 128 * world / (ms_decode / 1e3), "ms_per_token": ms_decode / 128,
            "prompt_tok_s": 127 * world / (ms_prompt / 1e3), "weight_bytes_per_token": eng.weight_bytes,
            "weight_gbs": eng.weight_bytes * 128 * world / (ms_decode / 1e3) / 1e9, "kv_bytes_at_256": eng.kv_bytes(256),
-           "form": "one CUDA graph replay per token (8 kernels per layer + 4), argmax on the device",
+           "form": "one CUDA graph replay per token (8 kernels per layer + 3), argmax on the device",
            "note": "each rank decodes its own replica; tok_s is the aggregate"}
     eng.close()
     return out
@@ -516,67 +582,195 @@ def _prefill(eng, rng, vocab, lo, hi, timed_region=None):
     return (hi - lo) / (ms / 1e3)
 
 
+def _attention_us(eng, pos, reps=4):
+    """us per layer of the attention launches of one greedy step at `pos` (kronos_cuda_engine_profile_step: every kernel alone
+    between two events, which adds a few us to each): (attention kernels, qkv_post kernel)."""
+    rows = {}
+    for line in eng.profile_step(1, pos, reps).splitlines()[1:]:
+        f = [x.strip() for x in line.split("|")]
+        if len(f) >= 4 and f[3]:
+            rows[f[0]] = float(f[3])
+    return rows.get("attention"), rows.get("qkv_post")
+
+
+def _decode_entry(name, ctx_len, kv, mode, tok_s, weight_bytes, kv_bytes_per_pos, peak, n_gpus=1, parallel=None):
+    """One roofline.decode record: bytes a token must stream (weights of one step + the cached rows it attends to)."""
+    per_token = weight_bytes + kv_bytes_per_pos * ctx_len
+    gbs = per_token * tok_s / 1e9
+    return {"model": name, "ctx": ctx_len, "kv": kv, "attention": mode, "n_gpus": n_gpus, "parallel": parallel, "tok_s": round(tok_s, 1),
+            "bytes_per_token": per_token, "GBps": round(gbs, 1), "frac": round(gbs / (peak * n_gpus), 4)}
+
+
 def decode_models(ctx, timed_region, rank, world, dist):
     """Whole-token decode of the larger model shapes (random codes; time does not depend on the values).
 
     One GPU: the SmolLM2-1.7B shape in nf4g128 at contexts 512 and 8192 with the int8 and the NF4 KV cache, and the
-    Qwen2-7B shape in the p55454 plane tier at context 4096.  2 or 4 GPUs: the Qwen2-7B shape tensor-parallel over all
-    ranks (8 GPUs: two groups of four, since 28 query heads do not split eight ways); the sum / gather steps run
-    inside the engine over peer memory."""
+    Qwen2-7B shape in the p55454 plane tier at context 4096.  Contexts beyond 512 positions run twice: in the reference's
+    summation order (the default: identical results) and with the split-KV kernels (KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION).
+    2, 4 or 8 GPUs: the Qwen2-7B shape tensor-parallel over all ranks (8 ranks: two per kv head, query heads 4 + 3); the sum
+    and gather steps run inside the engine over peer memory."""
     import numpy as np
     import kronos_2t_b200 as k2
     from kronos_2t_b200 import synth
     rng = np.random.Generator(np.random.PCG64(23))
-    out = []
+    peak, _ = peaks()
+    out, roof, attn = [], [], []
     steps = 64
+    name17 = "SmolLM2-1.7B-shaped (hidden 2048, 24 layers, 32q/32kv heads of 64, MLP 8192, vocab 49152), nf4g128"
     if world == 1:
         for kv_bits in (8, 4):
+            kv = "int8" if kv_bits == 8 else "nf4"
             cfg = dict(synth.SMOLLM2_1_7B, kv_bits=kv_bits)
             eng = k2.Engine(ctx, synth.random_model(cfg, "nf4g128", seed=5, share_layers=True))
             _prefill(eng, rng, cfg["vocab"], 0, 64)                                   # warm-up
             prefill = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region)
-            res = {"model": "SmolLM2-1.7B-shaped (hidden 2048, 24 layers, 32q/32kv heads of 64, MLP 8192, vocab 49152), nf4g128",
-                   "kv": "int8" if kv_bits == 8 else "nf4", "prefill_tok_s_1024": prefill, "weight_bytes_per_token": eng.weight_bytes,
+            res = {"model": name17, "kv": kv, "prefill_tok_s_1024": prefill, "weight_bytes_per_token": eng.weight_bytes,
                    "kv_bytes_per_pos": eng.kv_bytes_per_pos}
-            for name, pos in (("ctx_512", 512 - steps), ("ctx_8192", 8192)):
+            for key, pos in (("ctx_512", 512 - steps), ("ctx_8192", 8192)):
                 if pos > 1024:
                     _prefill(eng, rng, cfg["vocab"], 1024, pos)
                 eng.decode_greedy(1, pos, 8)                                          # warm-up (graph capture)
                 ms = min(timed_region(lambda: eng.decode_greedy(1, pos, steps)) for _ in range(2))
-                res[name] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps],
-                             "weight_gbs": eng.weight_bytes * steps / (ms / 1e3) / 1e9}
+                res[key] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps],
+                            "weight_gbs": eng.weight_bytes * steps / (ms / 1e3) / 1e9, "attention": "reference order"}
+                roof.append(_decode_entry("SmolLM2-1.7B nf4g128", pos + steps // 2, kv, "reference order", steps / (ms / 1e3), eng.weight_bytes,
+                                          eng.kv_bytes_per_pos, peak))
+            if kv_bits == 8:
+                a_us, q_us = _attention_us(eng, 8192)
+                kv_layer = 32 * 8192 * (2 * 64 + 8)
+                attn.append({"kernel": "attn_scores_kernel<64> + attn_values_kernel<64> (reference order)", "model": "SmolLM2-1.7B", "ctx": 8192,
+                             "kv_bytes_per_layer": kv_layer, "us_per_layer": a_us, "qkv_post_us": q_us, "GBps": round(kv_layer / a_us / 1e3, 1),
+                             "frac": round(kv_layer / a_us / 1e3 / peak, 3)})
             eng.close()
+            if kv_bits == 8:          # the same context with the split-KV kernels
+                eng = k2.Engine(ctx, synth.random_model(dict(cfg, split_kv_attention=True), "nf4g128", seed=5, share_layers=True))
+                eng.decode_greedy(1, 8192, 8)
+                ms = min(timed_region(lambda: eng.decode_greedy(1, 8192, steps)) for _ in range(2))
+                res["ctx_8192_split_kv"] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [8192, 8192 + steps],
+                                            "attention": "split-KV (fp32-rounding agreement)"}
+                roof.append(_decode_entry("SmolLM2-1.7B nf4g128", 8192 + steps // 2, kv, "split-KV", steps / (ms / 1e3), eng.weight_bytes, eng.kv_bytes_per_pos, peak))
+                a_us, q_us = _attention_us(eng, 8192)
+                attn.append({"kernel": "attn_partial_kernel<64> + attn_finish_kernel<64> (split-KV)", "model": "SmolLM2-1.7B", "ctx": 8192,
+                             "kv_bytes_per_layer": kv_layer, "us_per_layer": a_us, "qkv_post_us": q_us, "GBps": round(kv_layer / a_us / 1e3, 1),
+                             "frac": round(kv_layer / a_us / 1e3 / peak, 3)})
+                eng.close()
             out.append(res)
-    tp = world if world in (1, 2, 4) else 4
+    tp = world if world in (1, 2, 4, 8) else 4
     group, tp_rank = rank // tp, rank % tp
-    cfg = dict(synth.QWEN2_7B)
-    eng = k2.Engine(ctx, synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, tp=(tp, tp_rank), share_layers=True))
-    if tp > 1:
+    name7 = ("Qwen2-7B-shaped (hidden 3584, 28 layers, 28q/4kv heads of 128, MLP 18944, vocab 152064, qkv bias, untied), "
+             "p55454 planes (qkv 5, o 5, gate_up 4, down 5, head 4)")
+    res7 = {"model": name7, "kv": "int8", "tp": tp, "groups": world // tp,
+            "exchange": None if tp == 1 else "2 partial-sum exchanges per layer + 1 logits gather per token, one kernel each over peer memory (no NCCL on the data path)",
+            "head_split": None if tp <= 4 else "two ranks per kv head (own copy of its cache), query heads 4 + 3"}
+    for split in ((False, True) if world == 1 else (False,)):
+        cfg = dict(synth.QWEN2_7B, split_kv_attention=split)
+        eng = k2.Engine(ctx, synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, tp=(tp, tp_rank), share_layers=True))
+        if tp > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, eng.tp_handle())
+            eng.tp_attach(handles[group * tp:(group + 1) * tp])
+            dist.barrier()
+        if not split:
+            _prefill(eng, rng, cfg["vocab"], 0, 64)
+            res7["prefill_tok_s_1024"] = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region) * (world // tp)
+        eng.decode_greedy(1, 4096, 8)
+        ms = min(timed_region(lambda: eng.decode_greedy(1, 4096, steps)) for _ in range(2))
+        groups = world // tp
+        wb = eng.weight_bytes
+        if dist:
+            import torch
+            t = torch.tensor([float(wb)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t)
+            wb = int(t.item()) // groups
+        key = "ctx_4096_split_kv" if split else "ctx_4096"
+        res7[key] = {"tok_s": groups * steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [4096, 4096 + steps],
+                     "weight_gbs": groups * wb * steps / (ms / 1e3) / 1e9, "attention": "split-KV (fp32-rounding agreement)" if split else "reference order"}
+        res7["weight_bytes_per_token"] = wb
+        kv_pos = 2 * 28 * 4 * (128 + 4)
+        roof.append(_decode_entry("Qwen2-7B p55454", 4096 + steps // 2, "int8", "split-KV" if split else "reference order", steps / (ms / 1e3), wb,
+                                  kv_pos, peak, n_gpus=tp, parallel=None if tp == 1 else f"tp{tp}"))
+        if world == 1:
+            a_us, q_us = _attention_us(eng, 4096)
+            kv_layer = 4 * 4096 * (2 * 128 + 8)
+            attn.append({"kernel": ("attn_partial_kernel<128> + attn_finish_kernel<128> (split-KV)" if split else
+                                    "attn_scores_kernel<128> + attn_values_kernel<128> (reference order)"), "model": "Qwen2-7B", "ctx": 4096,
+                         "kv_bytes_per_layer": kv_layer, "us_per_layer": a_us, "qkv_post_us": q_us, "GBps": round(kv_layer / a_us / 1e3, 1),
+                         "frac": round(kv_layer / a_us / 1e3 / peak, 3)})
+        eng.close()
+    out.append(res7)
+    return out, roof, attn
+
+
+def sharded_parity(ctx, rank, world, dist):
+    """The two-GPU parity tests of tests/test_gpu_tp.py inside an N-rank run (N = 2, 4, 8), outside every timed region:
+    a small dense model tensor-parallel over all ranks and a small sparse-MoE model expert-parallel over all ranks, each
+    compared - logits of a short prompt and a greedy stream - with the CPU emulation that sums the ranks' partial outputs
+    in rank order (oracle.TpModel / oracle.EpModel, the checker; rank 0 only).  Returns {tp_parity_ok, ep_parity_ok}."""
+    import numpy as np
+    import torch
+    import kronos_2t_b200 as k2
+    from kronos_2t_b200 import synth
+    tokens = [5, 17, 300, 42, 7, 199, 63, 250, 11]
+    res = {}
+
+    def run(eng):
         handles = [None] * world
         dist.all_gather_object(handles, eng.tp_handle())
-        eng.tp_attach(handles[group * tp:(group + 1) * tp])
+        eng.tp_attach(handles)
         dist.barrier()
-    _prefill(eng, rng, cfg["vocab"], 0, 64)
-    prefill = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region)
-    _prefill(eng, rng, cfg["vocab"], 1024, 4096)
-    eng.decode_greedy(1, 4096, 8)
-    ms = min(timed_region(lambda: eng.decode_greedy(1, 4096, steps)) for _ in range(2))
-    groups = world // tp
-    wb = eng.weight_bytes
-    if dist:
-        import torch
-        t = torch.tensor([float(wb)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t)
-        wb = int(t.item()) // groups
-    out.append({"model": "Qwen2-7B-shaped (hidden 3584, 28 layers, 28q/4kv heads of 128, MLP 18944, vocab 152064, qkv bias, untied), "
-                         "p55454 planes (qkv 5, o 5, gate_up 4, down 5, head 4)", "kv": "int8", "tp": tp, "groups": groups,
-                "prefill_tok_s_1024": prefill * groups,
-                "ctx_4096": {"tok_s": groups * steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [4096, 4096 + steps],
-                             "weight_gbs": groups * wb * steps / (ms / 1e3) / 1e9},
-                "weight_bytes_per_token": wb,
-                "exchange": None if tp == 1 else "2 partial-sum exchanges per layer + 1 logits gather per token, one kernel each over peer memory (no NCCL on the data path)"})
+        logits = eng.forward_token_ids(tokens, want_all=True)
+        greedy = eng.decode_greedy(int(np.argmax(logits[-1])), len(tokens), 12)
+        dist.barrier()
+        return logits, greedy
+
+    def agree(mine):          # every rank holds the same bits
+        t = torch.from_numpy(np.ascontiguousarray(mine).view(np.uint8).copy()).cuda()
+        ref = t.clone()
+        dist.broadcast(ref, 0)
+        same = torch.tensor([int(torch.equal(t, ref))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        return bool(same.item())
+
+    tp_cfg = dict(hidden=512, layers=2, n_q=8, n_kv=4, head_dim=64, inter=1024, vocab=2048, max_seq=64, eps=1e-5, theta=1e5)
+    eng = k2.Engine(ctx, synth.random_model(tp_cfg, "b5", seed=41, qkv_bias=True, tp=(world, rank)))
+    logits, greedy = run(eng)
     eng.close()
-    return out
+    ok = agree(logits) and agree(greedy)
+    if rank == 0:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import oracle as o
+        specs = [synth.random_model(tp_cfg, "b5", seed=41, qkv_bias=True, tp=(world, r)) for r in range(world)]
+        table = np.asarray(specs[0]["embed_bf16"], np.uint16).reshape(-1, tp_cfg["hidden"])
+        emu = o.TpModel(specs, lambda t: (table[t].astype(np.uint32) << 16).view(np.float32))
+        want = np.stack([emu.forward_token(t) for t in tokens])
+        nxt, stream = int(np.argmax(want[-1])), []
+        for _ in range(12):
+            nxt = o.argmax(emu.forward_token(nxt)); stream.append(nxt)
+        emu.close()
+        ok = ok and np.array_equal(logits, want) and list(greedy) == stream
+    res["tp_parity_ok"] = bool(ok)
+    ep_cfg = dict(hidden=256, layers=2, n_q=4, n_kv=2, head_dim=64, inter=256, vocab=512, max_seq=64, eps=1e-6, theta=1e6)
+    moe = dict(n_experts=16, top_k=4, d_ff=128, bits=3, sgc=1)
+    spec = synth.random_model(ep_cfg, "nf4g128", seed=43, untied=True, moe=moe, ep=(world, rank))
+    eng = k2.Engine(ctx, spec)
+    logits, greedy = run(eng)
+    eng.close()
+    ok = agree(logits) and agree(greedy)
+    if rank == 0:
+        import oracle as o
+        whole = synth.random_model(ep_cfg, "nf4g128", seed=43, untied=True, moe=moe)
+        emu = o.EpModel(whole, world)
+        want = np.stack([emu.forward_token(t) for t in tokens])
+        nxt, stream = int(np.argmax(want[-1])), []
+        for _ in range(12):
+            nxt = o.argmax(emu.forward_token(nxt)); stream.append(nxt)
+        emu.close()
+        ok = ok and np.array_equal(logits, want) and list(greedy) == stream
+    res["ep_parity_ok"] = bool(ok)
+    flag = torch.tensor([int(res["tp_parity_ok"]), int(res["ep_parity_ok"])], device="cuda")
+    dist.broadcast(flag, 0)
+    return {"tp_parity_ok": bool(flag[0].item()), "ep_parity_ok": bool(flag[1].item()),
+            "what": "logits of a 9-token prompt and 12 greedy tokens, every rank bit-identical to the rank-order CPU emulation (small models, outside the timed regions)"}
 
 
 def decode_moe(ctx, timed_region, rank, world, dist):
@@ -605,13 +799,19 @@ def decode_moe(ctx, timed_region, rank, world, dist):
                     "nf3 experts, nf4g128 attention", "kv": "int8", "ep": world, "build_s": round(build_s, 1),
            "prefill_tok_s_480": prefill, "weight_bytes_per_token": eng.weight_bytes,
            "exchange": None if world == 1 else "1 partial-sum exchange per MoE block inside the norm kernel (peer memory, no NCCL on the data path)"}
+    peak, _ = peaks()
+    roof = []
+    # a token streams the dense tensors + router of every layer and the routed experts; under expert parallelism the ranks
+    # hold disjoint experts, so the experts' bytes are divided and the dense part is read by every rank
     for name, pos in (("ctx_512", 512 - steps), ("ctx_6600", 6600)):
         eng.decode_greedy(1, pos, 4)
         ms = min(timed_region(lambda: eng.decode_greedy(1, pos, steps)) for _ in range(2))
-        out[name] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps]}
+        out[name] = {"tok_s": steps / (ms / 1e3), "ms_per_token": ms / steps, "positions": [pos, pos + steps], "attention": "reference order"}
+        roof.append(_decode_entry("Qwen3-30B-A3B nf3 experts / nf4g128 attention", pos + steps // 2, "int8", "reference order", steps / (ms / 1e3),
+                                  eng.weight_bytes, eng.kv_bytes_per_pos, peak, n_gpus=world, parallel=None if world == 1 else f"ep{world}"))
     out["ctx_6600"]["note"] = "cache rows 480..6599 are zero: kernel time does not depend on the cached values"
     eng.close()
-    return out
+    return out, roof
 
 
 def run_decode_only(args, local_rank):

@@ -96,6 +96,7 @@ struct KronosCudaEngine {
     bool prof_on = false;
     std::vector<std::pair<const char *, cudaEvent_t>> prof_marks;
     unsigned long long *d_dbg = nullptr;      // 32 diagnostic words (phase clocks of the attention kernel, layer 0)
+    float *argmax_scratch = nullptr;          // candidates and arrival counter of the argmax kernel
     bool attn_trace = false;
 };
 
@@ -289,7 +290,7 @@ bool enqueue_fused_step(KronosCudaEngine *e, bool embed, Tail tail, bool long_ct
     residual_norm(p, e->final_norm, false);
     e->final_hidden = cur;
     if (!count(e, launch_gemv_fused(s, e->lm_head->dm, p, e->logits, e->ctx->sm_count, e->ctx->d_err, pdl), "gemv lm_head (+norm)")) return false;
-    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, pdl), "argmax");
+    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, c.vocab_size, e->d_token, e->d_pos, e->d_history, e->d_step, e->argmax_scratch, pdl), "argmax");
     return count(e, launch_advance_pos(s, e->d_pos, 1, pdl), "advance");
 }
 
@@ -444,7 +445,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
         if (!gemv(e, e->lm_head, lg, "gemv lm_head", 1, T - 1)) return false;
         if (c.tp_size > 1 && !tp_gather(e, lg, e->logits, c.vocab_size)) return false;
     }
-    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, vocab_all, e->d_token, e->d_pos, e->d_history, e->d_step, e->pdl), "argmax");
+    if (tail == Tail::Greedy) return count(e, launch_argmax_step(s, e->logits, vocab_all, e->d_token, e->d_pos, e->d_history, e->d_step, e->argmax_scratch, e->pdl), "argmax");
     return count(e, launch_advance_pos(s, e->d_pos, T, e->pdl), "advance");
 }
 
@@ -788,7 +789,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
               alloc_kv(e, c.kv_bits, c.kv_window, c.kv_sinks) &&
               dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
-              dev_alloc(e, e->d_history, c.max_seq_len) && dev_alloc(e, e->d_dbg, 32);
+              dev_alloc(e, e->d_history, c.max_seq_len) && dev_alloc(e, e->d_dbg, 32) && dev_alloc(e, e->argmax_scratch, ARGMAX_SCRATCH_WORDS);
     const uint32_t xg = c.tp_size > 1 ? c.tp_size : c.ep_size, xr = c.tp_size > 1 ? c.tp_rank : c.ep_rank;     // exchange group
     if (ok && xg > 1) {
         if (e->has_moe && c.tp_size > 1) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");

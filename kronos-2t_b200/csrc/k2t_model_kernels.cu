@@ -780,44 +780,64 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
 // ------------------------------------------------------------------------------------------------
 // greedy step: argmax (first maximum, argmax_scalar 9914-9924), record the token, advance the position
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) argmax_step_kernel(const float *__restrict__ logits, uint32_t n,
-                                                           uint32_t *__restrict__ token, uint32_t *__restrict__ pos,
-                                                           uint32_t *__restrict__ history, uint32_t *__restrict__ step) {
-    __shared__ float s_v[32];
-    __shared__ uint32_t s_i[32];
+// Many CTAs scan a slice of the logits each (a single CTA spent 12 - 25 us on 49K - 152K logits, one L2 round trip per
+// thread and iteration); every CTA leaves its best (value, index) in `part`, and the CTA that finishes last (device
+// counter) picks the winner among them - the first maximum, as a sequential scan would - and advances the step.
+constexpr uint32_t ARGMAX_THREADS = 256, ARGMAX_MAX_CTAS = 256;
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_step_kernel(const float *__restrict__ logits, uint32_t n,
+                                                                     uint32_t *__restrict__ token, uint32_t *__restrict__ pos,
+                                                                     uint32_t *__restrict__ history, uint32_t *__restrict__ step,
+                                                                     float *__restrict__ part_v, uint32_t *__restrict__ part_i,
+                                                                     uint32_t *__restrict__ done) {
+    __shared__ float s_v[ARGMAX_THREADS / 32];
+    __shared__ uint32_t s_i[ARGMAX_THREADS / 32];
+    __shared__ uint32_t s_last;
     float bv = -INFINITY;
     uint32_t bi = 0xffffffffu;
     pdl_wait();
     pdl_trigger();
-    for (uint32_t i = threadIdx.x; i < n; i += 1024) {
-        const float v = __ldcg(logits + i);
-        if (v > bv) { bv = v; bi = i; }         // ascending i per thread: keeps the first maximum
-    }
     auto better = [](float v, uint32_t i, float bv2, uint32_t bi2) { return v > bv2 || (v == bv2 && i < bi2); };
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
-        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, m);
-        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        bv = s_v[threadIdx.x]; bi = s_i[threadIdx.x];
+    auto block_best = [&]() {            // best of the CTA in thread 0
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, m);
             const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, m);
             if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if (threadIdx.x == 0) {
-            if (bi == 0xffffffffu) bi = 0;      // all NaN / -inf: the scalar loop also returns 0
-            *token = bi;
-            const uint32_t st = __ldcg(step);
-            if (history != nullptr) history[st] = bi;
-            *step = st + 1;
-            *pos = __ldcg(pos) + 1;
-        }
+        if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (uint32_t w = 1; w < ARGMAX_THREADS / 32; ++w)
+                if (better(s_v[w], s_i[w], bv, bi)) { bv = s_v[w]; bi = s_i[w]; }
+    };
+    // slice of this CTA: contiguous, a multiple of 4 logits
+    const uint32_t per = ((n + gridDim.x - 1) / gridDim.x + 3u) & ~3u;
+    const uint32_t lo = min(n, blockIdx.x * per), hi = min(n, lo + per);
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
+        const float v = __ldcg(logits + i);
+        if (v > bv) { bv = v; bi = i; }         // ascending i per thread: keeps the first maximum
+    }
+    block_best();
+    if (threadIdx.x == 0) {
+        part_v[blockIdx.x] = bv; part_i[blockIdx.x] = bi;
+        __threadfence();
+        s_last = atomicAdd(done, 1u) + 1u == gridDim.x ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last == 0) return;
+    __threadfence();
+    bv = -INFINITY; bi = 0xffffffffu;
+    if (threadIdx.x < gridDim.x) { bv = __ldcg(part_v + threadIdx.x); bi = __ldcg(part_i + threadIdx.x); }
+    __syncthreads();                            // s_v / s_i are reused
+    block_best();
+    if (threadIdx.x == 0) {
+        *done = 0;                              // ready for the next launch
+        if (bi == 0xffffffffu) bi = 0;          // all NaN / -inf: the scalar loop also returns 0
+        *token = bi;
+        const uint32_t st = __ldcg(step);
+        if (history != nullptr) history[st] = bi;
+        *step = st + 1;
+        *pos = __ldcg(pos) + 1;
     }
 }
 
@@ -920,8 +940,12 @@ cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t i
     return launch_kernel(swiglu_quant_kernel, dim3((inter / 64 + 7) / 8, n_tok), dim3(256), 0, s, pdl, gate_up, inter, q, scales, sums, dbg, chunk0);
 }
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
-                               uint32_t *history, uint32_t *step, bool pdl) {
-    return launch_kernel(argmax_step_kernel, dim3(1), dim3(1024), 0, s, pdl, logits, n, token, pos, history, step);
+                               uint32_t *history, uint32_t *step, float *scratch, bool pdl) {
+    // scratch: ARGMAX_SCRATCH_WORDS 32-bit words, zero before the first launch: [256] values | [256] indices | counter
+    if (scratch == nullptr) return cudaErrorInvalidValue;
+    const uint32_t ctas = std::max(1u, std::min(ARGMAX_MAX_CTAS, n / 1024u));
+    return launch_kernel(argmax_step_kernel, dim3(ctas), dim3(ARGMAX_THREADS), 0, s, pdl, logits, n, token, pos, history, step, scratch,
+                         reinterpret_cast<uint32_t *>(scratch) + ARGMAX_MAX_CTAS, reinterpret_cast<uint32_t *>(scratch) + 2 * ARGMAX_MAX_CTAS);
 }
 cudaError_t launch_delay(cudaStream_t s, uint64_t ns) {
     return launch_kernel(delay_kernel, dim3(1), dim3(1), 0, s, false, (unsigned long long)ns);

@@ -145,8 +145,10 @@ cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool 
 // chunk0: global index of the first down_proj input chunk of this rank (tensor parallel), else 0
 cudaError_t launch_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t inter, int8_t *q, float *scales, int32_t *sums,
                                 float *dbg, uint32_t chunk0, uint32_t n_tok, bool pdl);
+// scratch: ARGMAX_SCRATCH_WORDS zeroed 32-bit words of device memory (per-CTA candidates and the arrival counter)
+constexpr uint32_t ARGMAX_SCRATCH_WORDS = 2 * 256 + 4;
 cudaError_t launch_argmax_step(cudaStream_t s, const float *logits, uint32_t n, uint32_t *token, uint32_t *pos,
-                               uint32_t *history, uint32_t *step, bool pdl);
+                               uint32_t *history, uint32_t *step, float *scratch, bool pdl);
 // x_norm (optional): also write the normalised fp32 vector (the MoE router reads it)
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl);

@@ -133,9 +133,11 @@ def random_model(cfg, mode, seed=0, modes=None, qkv_bias=False, untied=False, tp
     h, hd = c["hidden"], c["head_dim"]
     vocab_total = c["vocab"]
     if tp_size > 1:
-        assert c["n_q"] % tp_size == 0 and c["n_kv"] % tp_size == 0 and c["inter"] % (64 * tp_size) == 0 and c["vocab"] % (32 * tp_size) == 0
-        c.update(n_q=c["n_q"] // tp_size, n_kv=c["n_kv"] // tp_size, inter=c["inter"] // tp_size, vocab=c["vocab"] // tp_size)
-        c.update(tp_size=tp_size, tp_rank=tp_rank, vocab_total=vocab_total, o_chunk0=tp_rank * c["n_q"] * hd // 64,
+        from .tp import head_plan
+        assert c["inter"] % (64 * tp_size) == 0 and c["vocab"] % (32 * tp_size) == 0
+        qh0, nq_l, _, nkv_l = head_plan(c["n_q"], c["n_kv"], tp_size, tp_rank)      # more ranks than kv heads: the kv head is replicated
+        c.update(n_q=nq_l, n_kv=nkv_l, inter=c["inter"] // tp_size, vocab=c["vocab"] // tp_size)
+        c.update(tp_size=tp_size, tp_rank=tp_rank, vocab_total=vocab_total, o_chunk0=qh0 * hd // 64,
                  down_chunk0=tp_rank * c["inter"] // 64)
         untied = True
     if ep[0] > 1:

@@ -78,16 +78,38 @@ def cols_slice(m, c0, c1):
                       pair=np.ascontiguousarray(pair).reshape(-1), tail=np.zeros(0, np.uint8))
 
 
+def head_plan(n_q, n_kv, tp, rank):
+    """Attention heads of `rank`: (first query head, query heads, first kv head, kv heads).
+
+    tp <= n_kv: every rank takes n_kv / tp kv heads and their query groups.  tp > n_kv (more ranks than kv heads, e.g. the
+    28 / 4 heads of Qwen2-7B eight ways): tp / n_kv ranks share one kv head - each keeps its own copy of that head's key /
+    value rows and cache - and divide the group's query heads among them as evenly as possible (7 -> 4 + 3), so the
+    o_proj columns of a rank are still one contiguous run of chunks."""
+    _check(0 <= rank < tp, "rank out of range")
+    group = n_q // n_kv
+    _check(n_q % n_kv == 0, "query heads must be a multiple of the kv heads")
+    if tp <= n_kv:
+        _check(n_kv % tp == 0, f"{n_kv} kv heads do not split {tp} ways")
+        nkv_l = n_kv // tp
+        return rank * nkv_l * group, nkv_l * group, rank * nkv_l, nkv_l
+    _check(tp % n_kv == 0, f"{tp} ranks do not divide over {n_kv} kv heads")
+    per = tp // n_kv                              # ranks that share a kv head
+    _check(group >= per, "more ranks per kv head than query heads in a group")
+    kvh, j = rank // per, rank % per
+    base, extra = group // per, group % per
+    first = j * base + min(j, extra)
+    return kvh * group + first, base + (1 if j < extra else 0), kvh, 1
+
+
 def shard_spec(spec, tp, rank):
     """The rank-local engine spec of `spec` under tp-way tensor parallelism (tp = 1 returns an equivalent spec)."""
     c = spec["cfg"]
     hd, n_q, n_kv, inter, vocab = c["head_dim"], c["n_q"], c["n_kv"], c["inter"], c["vocab"]
-    _check(0 <= rank < tp, "rank out of range")
-    _check(n_q % tp == 0 and n_kv % tp == 0, f"{n_q} query / {n_kv} kv heads do not split {tp} ways")
+    qh0, nq_l, kvh0, nkv_l = head_plan(n_q, n_kv, tp, rank)
     _check(inter % (64 * tp) == 0 and vocab % (32 * tp) == 0, "MLP width / vocabulary do not split on chunk / stripe boundaries")
-    nq_l, nkv_l, inter_l, vocab_l = n_q // tp, n_kv // tp, inter // tp, vocab // tp
+    inter_l, vocab_l = inter // tp, vocab // tp
     q_dim, kv_dim = n_q * hd, n_kv * hd
-    q0, k0, v0 = rank * nq_l * hd, q_dim + rank * nkv_l * hd, q_dim + kv_dim + rank * nkv_l * hd
+    q0, k0, v0 = qh0 * hd, q_dim + kvh0 * hd, q_dim + kv_dim + kvh0 * hd
     qkv_rows = np.concatenate([np.arange(q0, q0 + nq_l * hd), np.arange(k0, k0 + nkv_l * hd), np.arange(v0, v0 + nkv_l * hd)])
     layers = []
     for ly in spec["layers"]:
@@ -97,11 +119,11 @@ def shard_spec(spec, tp, rank):
             qkv_bias=None if ly.get("qkv_bias") is None else np.ascontiguousarray(np.asarray(ly["qkv_bias"], np.float32)[qkv_rows]),
             qkv=rows_concat([rows_slice(ly["qkv"], q0, q0 + nq_l * hd), rows_slice(ly["qkv"], k0, k0 + nkv_l * hd),
                              rows_slice(ly["qkv"], v0, v0 + nkv_l * hd)]),
-            o=cols_slice(ly["o"], rank * nq_l * hd // 64, (rank + 1) * nq_l * hd // 64),
+            o=cols_slice(ly["o"], qh0 * hd // 64, (qh0 + nq_l) * hd // 64),
             gate_up=rows_concat([rows_slice(ly["gate_up"], rank * inter_l, (rank + 1) * inter_l),
                                  rows_slice(ly["gate_up"], inter + rank * inter_l, inter + (rank + 1) * inter_l)]),
             down=cols_slice(ly["down"], rank * inter_l // 64, (rank + 1) * inter_l // 64)))
-    cfg = dict(c, n_q=nq_l, n_kv=nkv_l, inter=inter_l, vocab=vocab_l, o_chunk0=rank * nq_l * hd // 64, down_chunk0=rank * inter_l // 64,
+    cfg = dict(c, n_q=nq_l, n_kv=nkv_l, inter=inter_l, vocab=vocab_l, o_chunk0=qh0 * hd // 64, down_chunk0=rank * inter_l // 64,
                tp_size=tp, tp_rank=rank, vocab_total=vocab)
     out = dict(cfg=cfg, layers=layers, final_norm=spec["final_norm"], lm_head=rows_slice(spec["lm_head"], rank * vocab_l, (rank + 1) * vocab_l),
                rope=spec["rope"], embed_bf16=spec.get("embed_bf16"))

@@ -396,6 +396,29 @@ void attend_head_window(const K2oModel &m, size_t l, size_t kvh, const float *q_
     std::memcpy(out, o, hd * sizeof(float));
 }
 
+}  // namespace
+
+// causal_gqa_attention_q8 (real_llm.rs:8951-8988) for a stand-alone cache: n_kv heads of `seq_len` cached positions,
+// k_q8 / v_q8 [n_kv][seq_len][head_dim], scales [n_kv][seq_len]; q [n_q][head_dim] fp32 in, out [n_q][head_dim].  Lets the
+// reference's own attention accuracy test run against this restatement without a model around it.
+void k2o_attention_q8(size_t head_dim, size_t n_q, size_t n_kv, size_t seq_len, const int8_t *k_q8, const float *k_scale,
+                      const int8_t *v_q8, const float *v_scale, const float *q, float attn_scale, float *out) {
+    K2oModel m;
+    m.cfg = K2oConfig{};
+    m.cfg.head_dim = (uint32_t)head_dim; m.cfg.n_kv = (uint32_t)n_kv; m.cfg.n_q = (uint32_t)n_q; m.cfg.layers = 1; m.cfg.kv_bits = 8;
+    m.cfg.max_seq = (uint32_t)seq_len;
+    m.cap = seq_len;
+    m.k_q8.assign(k_q8, k_q8 + n_kv * seq_len * head_dim);
+    m.v_q8.assign(v_q8, v_q8 + n_kv * seq_len * head_dim);
+    m.k_sc.assign(k_scale, k_scale + n_kv * seq_len);
+    m.v_sc.assign(v_scale, v_scale + n_kv * seq_len);
+    std::vector<float> sc;
+    const size_t group = n_q / n_kv;
+    for (size_t qh = 0; qh < n_q; ++qh) attend_head(m, 0, qh / group, q + qh * head_dim, seq_len, attn_scale, sc, out + qh * head_dim);
+}
+
+namespace {
+
 // The platform expf of the reference's scalar paths, replaced by the correctly rounded value (see attend_head).
 inline float exp_cr(float x) { return (float)std::exp((double)x); }
 

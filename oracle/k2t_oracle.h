@@ -163,6 +163,10 @@ int k2o_model_set_kv_window(K2oModel *m, uint32_t kv_bits, size_t window, size_t
  * the byte count (out == NULL: only the count); restore copies min(slots_per_head, copy_slots) rows and sets the position. */
 size_t k2o_model_save_kv_prefix(const K2oModel *m, size_t n, uint8_t *out);
 int k2o_model_restore_kv_prefix(K2oModel *m, const uint8_t *data, size_t len, size_t copy_slots, size_t total_pos);
+/* causal_gqa_attention_q8 (real_llm.rs:8951-8988) over a stand-alone int8 Hadamard cache: k_q8 / v_q8 [n_kv][seq_len][head_dim],
+ * scales [n_kv][seq_len], q [n_q][head_dim] (fp32, before rotation), out [n_q][head_dim]. */
+void k2o_attention_q8(size_t head_dim, size_t n_q, size_t n_kv, size_t seq_len, const int8_t *k_q8, const float *k_scale,
+                      const int8_t *v_q8, const float *v_scale, const float *q, float attn_scale, float *out);
 /* cache rows per (layer, kv head) */
 size_t k2o_model_kv_rows(const K2oModel *m);
 /* can_truncate_kv_to (real_llm.rs:1806-1821): may the context be cut back to target_len without ring aliasing? */

@@ -521,6 +521,25 @@ def kv_quant_head(src):
     return q, sc[0]
 
 
+def attention_q8(q, k_heads, v_heads, attn_scale):
+    """causal_gqa_attention_q8 over keys / values given per kv head as fp32 [n_kv][seq][head_dim]: they are stored through the
+    int8 Hadamard quantizer (store_hadamard_q8_head*_raw), then every query head [n_q][head_dim] attends to all of them."""
+    L = lib(); _declare_model(L)
+    k_heads, v_heads, q = _c(k_heads, np.float32), _c(v_heads, np.float32), _c(q, np.float32)
+    n_kv, seq, hd = k_heads.shape
+    n_q = q.shape[0]
+    kq, vq = np.zeros((n_kv, seq, hd), np.int8), np.zeros((n_kv, seq, hd), np.int8)
+    ks, vs = np.zeros((n_kv, seq), np.float32), np.zeros((n_kv, seq), np.float32)
+    for h in range(n_kv):
+        for t in range(seq):
+            kq[h, t], ks[h, t] = kv_quant_head(k_heads[h, t])
+            vq[h, t], vs[h, t] = kv_quant_head(v_heads[h, t])
+    out = np.zeros((n_q, hd), np.float32)
+    L.k2o_attention_q8.restype, L.k2o_attention_q8.argtypes = None, [C.c_size_t] * 4 + [C.c_void_p] * 5 + [C.c_float, C.c_void_p]
+    L.k2o_attention_q8(hd, n_q, n_kv, seq, _ptr(kq), _ptr(ks), _ptr(vq), _ptr(vs), _ptr(q), attn_scale, _ptr(out))
+    return out
+
+
 def argmax(v):
     L = lib(); _declare_model(L)
     v = _c(v, np.float32)

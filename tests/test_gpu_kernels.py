@@ -156,6 +156,27 @@ def test_batch_gemv_matches_oracle(ctx, oracle, n_tok):
         _check_gemv(ctx, oracle, m, x)
 
 
+@pytest.mark.parametrize("rows", [71, 128])
+@pytest.mark.parametrize("bits,sgc", [(3, 1), (3, 2), (4, 1), (4, 2), (5, 1), (5, 2)])
+def test_reference_nf_sdot_case(ctx, oracle, rows, bits, sgc):
+    """The reference's NF kernel test case (test_nf3_nf4_sdot_neon_scalar_parity_and_quality, src/kernels/simd_lut.rs:9137-9319:
+    its LCG weights and activations, 256 columns, 71 / 128 rows, bits 3-5, scale groups of 1 and 2 chunks) and its batch leg
+    (15 tokens against the single-token kernel), bit for bit on the device."""
+    import k2t_refgen as rg
+    m = oracle.nf_quantize_rtn(rg.sample_weights(rows, 256), bits, sgc)
+    one = _check_gemv(ctx, oracle, m, rg.sample_x(4242 + bits * 10 + sgc, 256))
+    xs = np.stack([rg.sample_x(9000 + t, 256) for t in range(15)])
+    batch = _check_gemv(ctx, oracle, m, xs)
+    dm = upload(ctx, m)
+    try:
+        for t in (0, 7, 14):
+            act = oracle.act_populate_fwht(xs[t])
+            assert np.array_equal(ctx.gemv(dm, act.q, act.scales, act.sums).reshape(-1), batch[t])
+    finally:
+        dm.free()
+    assert one.shape[-1] == rows
+
+
 def test_gate_up_interleave_upload(ctx, oracle):
     rows, cols = 256, 576
     _check_gemv(ctx, oracle, oracle.bipolar_quantize_rtn(normal(3, (rows, cols), 0.02), 4), normal(4, cols), interleave=True)

@@ -288,12 +288,24 @@ def test_greedy_crosses_512_positions(ctx, oracle, decode_path):
         eng.close(); ref.close()
 
 
+_SMOL_WANT = {}
+
+
 def test_greedy_smollm2_135m_shape_128_steps(ctx, oracle, decode_path):
-    """BASELINE configs[0] shape (SmolLM2-135M: 30 layers, hidden 576, 9/3 heads, vocab 49152), synthetic weights."""
+    """BASELINE configs[0]: the SmolLM2-135M shape (30 layers, hidden 576, 9/3 heads, vocab 49152, tied), b4 planes with b5 for
+    qkv / o / down here, int8 KV: a 128-token seeded prompt, then 128 greedy steps - the token stream and the last logits are
+    the oracle's.  (Synthetic N(0, 0.02) weights through the oracle's RTN quantizer.)"""
     spec, eng, ref = make(ctx, oracle, km.SMOL_135M, "b4", seed=2, modes=dict(qkv="b5", o="b5", down="b5"))
     try:
-        _greedy_check(eng, ref, [11, 4242, 31000, 7, 48000, 123, 999, 20000], 128)
-        assert eng.kv_bytes(136) == 136 * 2 * 30 * 3 * (64 + 4)
+        prompt = [int(t) for t in np.random.Generator(np.random.PCG64(128)).integers(0, km.SMOL_135M["vocab"], 128)]
+        if "want" not in _SMOL_WANT:                        # the oracle's 256 tokens once for all decode paths
+            _SMOL_WANT["want"] = ref.greedy(prompt, 128, threads=16)
+        want, want_logits = _SMOL_WANT["want"]
+        eng.forward_token_ids(prompt[:-1])
+        got, got_logits = eng.decode_greedy(prompt[-1], 127, 129, want_logits=True)
+        assert list(got[:128]) == want
+        assert np.array_equal(got_logits, want_logits)
+        assert eng.kv_bytes(256) == 256 * 2 * 30 * 3 * (64 + 4)
         files = sum(ly[k].file_bytes() for ly in spec["layers"] for k in ("qkv", "o", "gate_up", "down")) + spec["lm_head"].file_bytes()
         assert eng.weight_bytes == files
     finally:

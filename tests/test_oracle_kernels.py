@@ -337,3 +337,37 @@ def test_published_byte_counts(oracle):
     assert bip(49152, 2048, 4) == 53_477_376 and nf(49152, 2048, 4, 2) == 51_904_528
     # Nibble4 records carry the same bytes as the file layout
     assert L.k2o_nibble4_pair_bytes(2048, 2048, 5) == bip(2048, 2048, 5)
+
+
+@pytest.mark.parametrize("rows", [71, 128])
+@pytest.mark.parametrize("bits,sgc", [(3, 1), (3, 2), (4, 1), (4, 2), (5, 1), (5, 2)])
+def test_reference_nf_sdot_case_scalar_parity(oracle, rows, bits, sgc):
+    """The shapes, generators and tolerance of the reference's NF kernel test (test_nf3_nf4_sdot_neon_scalar_parity_and_quality,
+    src/kernels/simd_lut.rs:9137-9319): 256 columns, 71 (odd stripe count) and 128 rows, bits 3 / 4 / 5, scale groups of 1 and 2
+    chunks; the oracle's GEMV (NEON semantics: exact int32 chunk dots, fused multiply-add epilogue) against a scalar
+    restatement of nf_sdot_stripe_range_scalar_raw (6459-6539: integer dot, (dot * xs) * ws accumulated with separate multiply and
+    add) within 1e-4 * max(|y|, 1), for any thread split.  Weights are quantized round-to-nearest (the reference test compiles
+    them with a calibration Hessian, which changes the codes, not the kernel arithmetic)."""
+    import k2t_refgen as rg
+    cols = 256
+    w = rg.sample_weights(rows, cols)
+    nf, idx, sc = oracle.nf_quantize_rtn(w, bits, sgc, return_indices=True)
+    x = rg.sample_x(4242 + bits * 10 + sgc, cols)
+    act = oracle.act_populate_fwht(x)
+    y, dots = oracle.gemv(nf, act, want_dots=True)
+    y, dots = y.reshape(rows), dots.reshape(rows, cols // 64)
+    for threads in (2, 3, 5):
+        assert np.array_equal(oracle.gemv(nf, act, threads=threads).reshape(rows), y)
+    cb = oracle.nf_expand_codebook32(bits, nf.codebook).astype(np.int64)
+    q, xs = act.q.reshape(-1).astype(np.int64), act.scales.reshape(-1)
+    nsg = (cols // 64 + sgc - 1) // sgc
+    want = np.zeros(rows, np.float32)
+    for r in range(rows):
+        f = np.float32(0.0)
+        for c in range(cols // 64):
+            dot = int(np.dot(cb[idx[r, c * 64:(c + 1) * 64]], q[c * 64:(c + 1) * 64]))
+            assert dot == dots[r, c]
+            ws = oracle.bf16_to_f32(sc[((r // 16) * nsg + c // sgc) * 16 + r % 16])
+            f = np.float32(f + np.float32(np.float32(np.float32(dot) * xs[c]) * ws))
+        want[r] = f
+    assert np.all(np.abs(y - want) <= 1e-4 * np.maximum(np.abs(want), 1.0)), float(np.max(np.abs(y - want)))

@@ -213,3 +213,36 @@ def test_sliding_window_ring_geometry_and_rollback_guard(oracle):
         short.close()
     finally:
         full.close(); win.close()
+
+
+def test_reference_hadamard_q8_kv_attention_accuracy_case(oracle):
+    """The reference's own accuracy test for the int8 Hadamard cache, run against this restatement with its generator and
+    threshold (test_hadamard_q8_kv_cache_attention_accuracy, src/model/real_llm.rs:10189-10284): 6 query / 2 kv heads, head_dim
+    64 and 128, 37 positions with 12x outliers on two channels per head, queries at positions 0, 7, 15, 36 - the attention
+    over the quantized cache must keep a cosine above 0.9998 against the unquantized float attention; and the cache costs
+    2 * (head_dim + 4) bytes per (layer, kv head, position), the byte identity that test asserts."""
+    for hd in (64, 128):
+        heads, kv_heads, n_max = 6, 2, 37
+        kv_dim = kv_heads * hd
+        attn_scale = np.float32(1.0 / np.sqrt(np.float32(hd)))
+        assert 2 * 2 * 64 * (2 * hd + 8) == 64 * 2 * 2 * kv_heads * (hd + 4)       # physical_bytes() of 2 layers x 2 kv heads x 64 positions
+
+        def f(i, m):
+            base = (np.float32((i * m) % 101) / np.float32(101.0) - np.float32(0.5)) * np.float32(1.6)
+            return base * np.float32(12.0) if (i % hd) in (7, hd // 2 + 7) else base
+
+        k_all = np.array([f(i, 19) for i in range(n_max * kv_dim)], np.float32).reshape(n_max, kv_heads, hd)
+        v_all = np.array([f(i, 29) for i in range(n_max * kv_dim)], np.float32).reshape(n_max, kv_heads, hd)
+        for pos in (0, 7, 15, 36):
+            q = np.array([f(i + pos * 13, 37) for i in range(heads * hd)], np.float32).reshape(heads, hd)
+            n = pos + 1
+            got = oracle.attention_q8(q, k_all[:n].transpose(1, 0, 2), v_all[:n].transpose(1, 0, 2), float(attn_scale))
+            want = np.zeros((heads, hd))
+            for h in range(heads):
+                kvh = h // (heads // kv_heads)
+                sc = (k_all[:n, kvh].astype(np.float64) @ q[h].astype(np.float64)) * float(attn_scale)
+                e = np.exp(sc - sc.max())
+                want[h] = (e / e.sum()) @ v_all[:n, kvh].astype(np.float64)
+            a, b = got.astype(np.float64).reshape(-1), want.reshape(-1)
+            cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+            assert cos > 0.99980, (hd, pos, cos)

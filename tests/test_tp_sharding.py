@@ -60,7 +60,33 @@ def test_tp_emulation_matches_the_whole_model(oracle, mode, kw):
     assert (c["n_q"], c["n_kv"], c["inter"], c["vocab"], c["o_chunk0"], c["down_chunk0"]) == (2, 1, 256, 192, 2, 4)
     assert s0["layers"][0]["qkv"].rows == (2 + 2 * 1) * 64 and s0["layers"][0]["o"].cols == 128 and s0["layers"][0]["down"].cols == 256
     with pytest.raises(ValueError):
-        tp.shard_spec(spec, 4, 0)                        # 2 kv heads do not split four ways
+        tp.shard_spec(spec, 3, 0)                        # 2 kv heads do not split three ways
+
+
+def test_more_ranks_than_kv_heads_replicate_the_kv_head(oracle):
+    """Eight-way tensor parallelism of a 28 / 4-head model (Qwen2-7B): two ranks share each kv head, keep their own copy of
+    its key / value rows and split its seven query heads 4 + 3; the o_proj chunks of the ranks tile the matrix in order.
+    On a small model the four-rank emulation (2 kv heads, 2 ranks each) tracks the whole model like the two-rank one."""
+    from kronos_2t_b200 import tp
+    plan = [tp.head_plan(28, 4, 8, r) for r in range(8)]
+    assert [p[1] for p in plan] == [4, 3, 4, 3, 4, 3, 4, 3] and [p[2] for p in plan] == [0, 0, 1, 1, 2, 2, 3, 3] and all(p[3] == 1 for p in plan)
+    assert [p[0] for p in plan] == [0, 4, 7, 11, 14, 18, 21, 25]                      # contiguous query heads, in rank order
+    assert tp.head_plan(28, 4, 4, 2) == (14, 7, 2, 1) and tp.head_plan(28, 4, 2, 1) == (14, 14, 2, 2)
+    cfg = dict(TP_CFG, n_q=6, n_kv=2, hidden=384)                                     # groups of three query heads: 2 + 1 per rank pair
+    spec = km.build(oracle, cfg, "b5", seed=3, qkv_bias=True, tied=False)
+    whole = oracle.Model(spec)
+    tokens = [5, 17, 300, 42, 7, 199, 63, 250]
+    want = np.stack([whole.forward_token(t, 2) for t in tokens])
+    shards = [tp.shard_spec(spec, 4, r) for r in range(4)]
+    assert [s["cfg"]["n_q"] for s in shards] == [2, 1, 2, 1] and all(s["cfg"]["n_kv"] == 1 for s in shards)
+    assert [s["cfg"]["o_chunk0"] for s in shards] == [0, 2, 3, 5]
+    assert sum(s["layers"][0]["o"].cols for s in shards) == 6 * 64
+    four = oracle.TpModel(shards, lambda t: whole.embed(t))
+    got = np.stack([four.forward_token(t) for t in tokens])
+    assert np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
+    cos = [np.dot(a, b) / (np.linalg.norm(a) * np.linalg.norm(b)) for a, b in zip(got, want)]
+    assert min(cos) > 0.99999
+    four.close(); whole.close()
 
 
 WORKER = r'''
