@@ -45,7 +45,7 @@ def build(force=False, verbose=False):
             os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC)
         ):
             continue
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + os.environ.get("KRONOS_CUDA_NVCC_FLAGS", "").split() + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, p in procs:
         out, _ = p.communicate()

@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
                 fa.n_q = A.n_q; fa.n_kv = A.n_kv; fa.head_dim = A.head_dim; fa.max_seq = A.max_seq; fa.layer = l;
                 fa.eps = A.eps; fa.attn_scale = A.attn_scale; fa.qk_norm_after_rope = A.qk_norm_after_rope;
                 fa.kv_bits = A.kv_bits; fa.out_chunk0 = 0; fa.pos_offset = 0; fa.trace = nullptr;
-                attention_head_dispatch(fa, blockIdx.x, pos, s.at);
+                attention_head_dispatch<false>(fa, blockIdx.x, pos, s.at);
             }
             tr.mark();
             if (!grid.sync()) return;

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstdint>
 #include <mutex>
+#include <vector>
 #include <cuda_runtime.h>
 
 namespace k2t {
@@ -42,7 +43,31 @@ __device__ __forceinline__ uint32_t lop3_select(uint32_t lo, uint32_t hi, uint32
 // successor start launching; kernels call it AFTER their own pdl_wait(), so that at most two consecutive
 // kernels are ever resident together (a kernel two steps back can then no longer refill an SM's L1 with
 // lines its successor is about to overwrite).  Both are no-ops for a kernel launched the ordinary way.
+#ifndef K2T_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#else
+// Build-time diagnostic (-DK2T_TIMELINE): thread 0 of block (0,0,0) of every kernel stamps %globaltimer when its dependency
+// wait returns, i.e. when its predecessor has drained.  Consecutive stamps of a chained step are the in-chain durations
+// of its kernels (launch gap included), which events around isolated launches cannot show.  The buffer is
+// [count, capacity, stamps...]; each translation unit holds its own copy of the pointer, set through the registry below.
+// The stamp costs the stamping thread one atomic round trip (well under a microsecond per kernel).
+static __device__ unsigned long long *g_timeline;
+inline std::vector<void (*)(unsigned long long *)> &timeline_setters() {
+    static std::vector<void (*)(unsigned long long *)> v;
+    return v;
+}
+static void timeline_set_here(unsigned long long *p) { cudaMemcpyToSymbol(g_timeline, &p, sizeof p); }
+static const int timeline_registered = (timeline_setters().push_back(&timeline_set_here), 0);
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if ((threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && g_timeline != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const unsigned long long i = atomicAdd(g_timeline, 1ull);
+        if (i < g_timeline[1]) g_timeline[2 + i] = t;
+    }
+}
+#endif
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Launches `kernel` on `stream`, optionally as a programmatic dependent of the previous kernel in the stream.

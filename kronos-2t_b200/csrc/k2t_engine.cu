@@ -95,6 +95,10 @@ struct KronosCudaEngine {
     // by an event record, so a captured step carries one event node per kernel
     bool prof_on = false;
     std::vector<std::pair<const char *, cudaEvent_t>> prof_marks;
+#ifdef K2T_TIMELINE
+    std::vector<const char *> tl_labels[4];     // launch labels of the four captured step graphs, in launch order
+    std::vector<const char *> *tl_cur = nullptr;
+#endif
     unsigned long long *d_dbg = nullptr;      // 32 diagnostic words (phase clocks of the attention kernel, layer 0)
     float *argmax_scratch = nullptr;          // candidates and arrival counter of the argmax kernel
     bool attn_trace = false;
@@ -181,6 +185,9 @@ bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char
 
 bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n) {
     e->ctx->launches += n;
+#ifdef K2T_TIMELINE
+    if (e->tl_cur) for (uint32_t i = 0; i < n; ++i) e->tl_cur->push_back(what);
+#endif
     if (e->prof_on && err == cudaSuccess) {
         cudaEvent_t ev = nullptr;
         if (!cuda_ok(e->ctx, cudaEventCreate(&ev), "profile event") || !cuda_ok(e->ctx, cudaEventRecord(ev, e->ctx->stream), "profile event"))
@@ -343,6 +350,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
             fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
             fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
             fa.trace = (e->attn_trace && l == 0) ? e->d_dbg : nullptr;
+            fa.early = T == 1 ? 1u : 0u;        // in a batch the launch before is the attention of the token before: it wrote a row this one reads
             if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
         } else {
             QkvPostArgs qa{};
@@ -474,7 +482,14 @@ bool ensure_graphs(KronosCudaEngine *e, size_t warm_pos) {
     for (int which = 0; which < 4; ++which) {
         cudaGraph_t graph = nullptr;
         if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return false;
+#ifdef K2T_TIMELINE
+        e->tl_labels[which].clear();
+        e->tl_cur = &e->tl_labels[which];
+#endif
         const bool ok = enqueue_batch(e, 1, true, which < 2 ? Tail::Greedy : Tail::LastLogits, (which & 1) != 0);
+#ifdef K2T_TIMELINE
+        e->tl_cur = nullptr;
+#endif
         cudaError_t err = cudaStreamEndCapture(ctx->stream, &graph);
         if (!ok || !cuda_ok(ctx, err, "end capture")) { if (graph) cudaGraphDestroy(graph); return false; }
         cudaGraphExec_t exec = nullptr;
@@ -1297,6 +1312,19 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
         !cuda_ok(ctx, cudaMemcpyAsync(e->d_step, &init[2], 4, cudaMemcpyHostToDevice, ctx->stream), "set step") ||
         !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "decode_greedy setup"))
         return -1;
+#ifdef K2T_TIMELINE
+    // KRONOS_CUDA_TIMELINE=<file>: stamps of every kernel of these steps (see pdl_wait), one line of labels, then one line
+    // of nanosecond stamps per step.  All steps must use the same graph variant.
+    const char *tl_path = std::getenv("KRONOS_CUDA_TIMELINE");
+    unsigned long long *tl_dev = nullptr;
+    const size_t tl_cap = 1 << 18;
+    if (tl_path) {
+        if (!cuda_ok(ctx, cudaMalloc(&tl_dev, (tl_cap + 2) * 8), "timeline buffer")) return -1;
+        const unsigned long long head[2] = {0, tl_cap};
+        cudaMemcpy(tl_dev, head, 16, cudaMemcpyHostToDevice);
+        for (auto set : timeline_setters()) set(tl_dev);
+    }
+#endif
     for (size_t i = 0; i < n_steps; ++i) {
         if (!cuda_ok(ctx, cudaGraphLaunch(step_graph(e, true, pos_start + i), ctx->stream), "graph launch")) return -1;
         ctx->launches += step_launches(e, pos_start + i);
@@ -1304,6 +1332,26 @@ int32_t kronos_cuda_engine_decode_greedy(KronosCudaEngine *e, uint32_t first_tok
     if (!cuda_ok(ctx, cudaMemcpyAsync(out_tokens, e->d_history, n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy tokens")) return -1;
     if (last_logits && !cuda_ok(ctx, cudaMemcpyAsync(last_logits, e->logits, vocab_all * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
     if (!sync_and_check(ctx, "decode_greedy")) return -1;
+#ifdef K2T_TIMELINE
+    if (tl_path) {
+        for (auto set : timeline_setters()) set(nullptr);
+        std::vector<unsigned long long> h(tl_cap + 2);
+        cudaMemcpy(h.data(), tl_dev, h.size() * 8, cudaMemcpyDeviceToHost);
+        cudaFree(tl_dev);
+        const int which = (pos_start + 1 > ATTN_EXACT_CTX || e->ring.window) ? 1 : 0;
+        const std::vector<const char *> &lab = e->tl_labels[which];
+        const size_t n = std::min<size_t>(h[0], tl_cap);
+        std::sort(h.begin() + 2, h.begin() + 2 + n);
+        if (FILE *f = std::fopen(tl_path, "a")) {
+            std::fprintf(f, "steps %zu stamps %zu labels %zu\n", n_steps, n, lab.size());
+            for (const char *l : lab) std::fprintf(f, "%s|", l);
+            std::fprintf(f, "\n");
+            for (size_t i = 0; i < n; ++i) std::fprintf(f, "%llu%c", h[2 + i] - h[2], (i + 1) % std::max<size_t>(1, lab.size()) == 0 ? '\n' : ' ');
+            std::fprintf(f, "\n");
+            std::fclose(f);
+        }
+    }
+#endif
     if (const char *v = std::getenv("KRONOS_CUDA_DECODE_PROF")) {
         if (v[0] == '1') {              // the step that produced the last token, once more, kernel by kernel (same cache row, same result)
             std::vector<char> table(1 << 14);

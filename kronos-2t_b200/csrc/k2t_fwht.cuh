@@ -11,11 +11,18 @@
 
 namespace k2t {
 
+// The two sign words of a lane (elements 2l, 2l+1 of `block`).  They depend on nothing a kernel computes, so kernels on a
+// latency chain fetch them before they wait for their predecessor (the SplitMix64 rounds cost about a hundred cycles).
+struct FwhtSigns { uint32_t s0, s1; };
+__device__ __forceinline__ FwhtSigns fwht_signs(uint64_t block, uint32_t lane) {
+    return FwhtSigns{rademacher_sign(block, 2 * lane), rademacher_sign(block, 2 * lane + 1)};
+}
+
 // In: v0/v1 = elements 2l, 2l+1 of the block (already RMS-normalised if wanted).
 // Out: rotated values  (1/8) * H64 * D_block * x.
-__device__ __forceinline__ void warp_fwht64(float &v0, float &v1, uint64_t block, uint32_t lane) {
-    v0 = __fmul_rn(__uint_as_float(__float_as_uint(v0) ^ rademacher_sign(block, 2 * lane)), 0.125f);
-    v1 = __fmul_rn(__uint_as_float(__float_as_uint(v1) ^ rademacher_sign(block, 2 * lane + 1)), 0.125f);
+__device__ __forceinline__ void warp_fwht64(float &v0, float &v1, const FwhtSigns sg, uint32_t lane) {
+    v0 = __fmul_rn(__uint_as_float(__float_as_uint(v0) ^ sg.s0), 0.125f);
+    v1 = __fmul_rn(__uint_as_float(__float_as_uint(v1) ^ sg.s1), 0.125f);
     float a = __fadd_rn(v0, v1), b = __fsub_rn(v0, v1);
     v0 = a; v1 = b;
 #pragma unroll
@@ -28,8 +35,12 @@ __device__ __forceinline__ void warp_fwht64(float &v0, float &v1, uint64_t block
     }
 }
 
+__device__ __forceinline__ void warp_fwht64(float &v0, float &v1, uint64_t block, uint32_t lane) {
+    warp_fwht64(v0, v1, fwht_signs(block, lane), lane);
+}
+
 // Inverse: butterflies, then *0.125, then sign (ifwht64_signed_inplace_scalar, hadamard.rs:200-228).
-__device__ __forceinline__ void warp_ifwht64(float &v0, float &v1, uint64_t block, uint32_t lane) {
+__device__ __forceinline__ void warp_ifwht64(float &v0, float &v1, const FwhtSigns sg, uint32_t lane) {
     float a = __fadd_rn(v0, v1), b = __fsub_rn(v0, v1);
     v0 = a; v1 = b;
 #pragma unroll
@@ -40,8 +51,11 @@ __device__ __forceinline__ void warp_ifwht64(float &v0, float &v1, uint64_t bloc
         v0 = hi ? __fsub_rn(o0, v0) : __fadd_rn(v0, o0);
         v1 = hi ? __fsub_rn(o1, v1) : __fadd_rn(v1, o1);
     }
-    v0 = __uint_as_float(__float_as_uint(__fmul_rn(v0, 0.125f)) ^ rademacher_sign(block, 2 * lane));
-    v1 = __uint_as_float(__float_as_uint(__fmul_rn(v1, 0.125f)) ^ rademacher_sign(block, 2 * lane + 1));
+    v0 = __uint_as_float(__float_as_uint(__fmul_rn(v0, 0.125f)) ^ sg.s0);
+    v1 = __uint_as_float(__float_as_uint(__fmul_rn(v1, 0.125f)) ^ sg.s1);
+}
+__device__ __forceinline__ void warp_ifwht64(float &v0, float &v1, uint64_t block, uint32_t lane) {
+    warp_ifwht64(v0, v1, fwht_signs(block, lane), lane);
 }
 
 // Per-chunk int8 quantization of one rotated block held by a warp

@@ -167,6 +167,7 @@ constexpr uint32_t ATTN_THREADS = 256;
 struct AttnSmem {
     float *sc;                 // [ATTN_EXACT_CTX]
     int8_t *vbuf;              // [ATTN_EXACT_CTX][head_dim <= 128] cached value rows (one bulk copy)
+    uint8_t *vt;               // [head_dim][ATTN_EXACT_CTX] the same rows transposed (value_rows_transpose); null: the chain reads vbuf bytes
     uint64_t *bar;             // mbarrier of that copy
     // kv_bits = 4 only
     float *wg;                 // [2][ATTN_EXACT_CTX] value weights per 64-value group
@@ -183,14 +184,17 @@ struct AttnSmem {
     float *inv;                // [1]
 };
 __host__ __device__ inline size_t attn_round(size_t v) { return (v + 127) & ~(size_t)127; }
-__host__ __device__ inline size_t attn_smem_bytes() {
-    return attn_round(2 * ATTN_EXACT_CTX * 4) + 128 + 2 * attn_round(3 * 64 * 4) + attn_round(3 * 64) + 128 + 128 +
+constexpr uint32_t ATTN_VT_BYTES = 128 * ATTN_EXACT_CTX;
+__host__ __device__ inline size_t attn_smem_bytes(bool staged = false) {
+    return (staged ? ATTN_VT_BYTES : 0) + attn_round(2 * ATTN_EXACT_CTX * 4) + 128 + 2 * attn_round(3 * 64 * 4) + attn_round(3 * 64) + 128 + 128 +
            attn_round(ATTN_EXACT_CTX * 4) + attn_round(ATTN_EXACT_CTX * 128) + 128 + attn_round(3 * 128 * 4) + attn_round(3 * 128) + 128 +
            attn_round(128 * 4) + 128 + 128;
 }
-__device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
+__device__ __forceinline__ AttnSmem attn_carve(uint8_t *base, bool staged = false) {
     AttnSmem s;
     size_t off = 0;
+    s.vt = staged ? base : nullptr;
+    if (staged) off += ATTN_VT_BYTES;
     s.sc = reinterpret_cast<float *>(base + off); off += attn_round(ATTN_EXACT_CTX * 4);
     s.vbuf = reinterpret_cast<int8_t *>(base + off); off += attn_round(ATTN_EXACT_CTX * 128);
     s.bar = reinterpret_cast<uint64_t *>(base + off); off += 128;
@@ -210,10 +214,124 @@ __device__ __forceinline__ AttnSmem attn_carve(uint8_t *base) {
     return s;
 }
 
-#define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); } while (0)
 
+// ------------------------------------------------------------------------------------------------
+// Transposed value tile.  The position-ascending fma chain of a dimension wants that dimension's bytes of consecutive
+// positions side by side: one 16-byte shared-memory load then feeds sixteen chain steps (byte -> float by prmt + one
+// subtraction), where the row-major cache rows cost a byte load per step.  Warps that are not on the chain transpose
+// 16-position blocks in registers (4x4 byte transposes, eight prmt each).  Layout: row d (dimension) holds `stride`
+// bytes; the 16-byte chunk of positions 16b..16b+15 sits at chunk index b ^ swz(d), swz(d) = (d ^ (d >> 3)) & 7, which
+// keeps both sides free of bank conflicts (eight consecutive dimensions read eight different chunks; the eight lanes
+// of a store phase, dimensions 4 apart, also do).  int8 rows are stored with the sign bit flipped (b ^ 0x80), NF4 rows as
+// one byte per value holding 4 * index (the byte offset of its centroid in the fp32 table).
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t vt_swz(uint32_t d) { return (d ^ (d >> 3)) & 7u; }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u32x4(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ void sts_u32x4(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// w[0..3] = four positions x four dimensions (byte i of w[j] = dimension i of position j)  ->  t[i] = dimension i, positions 0..3
+__device__ __forceinline__ void transpose4x4_bytes(const uint32_t w[4], uint32_t t[4]) {
+    const uint32_t a = prmt(w[0], w[1], 0x5140u), b = prmt(w[2], w[3], 0x5140u);
+    const uint32_t c = prmt(w[0], w[1], 0x7362u), d = prmt(w[2], w[3], 0x7362u);
+    t[0] = prmt(a, b, 0x5410u); t[1] = prmt(a, b, 0x7632u);
+    t[2] = prmt(c, d, 0x5410u); t[3] = prmt(c, d, 0x7632u);
+}
+// One warp transposes 16-position blocks blk0, blk0 + blk_step, ... < n_blk of the row-major rows at shared address
+// `rows` (ROW bytes each: head_dim int8, or head_dim / 2 packed NF4 pairs) into the tile at `tile` (see above; block b of
+// the source becomes chunk (b + chunk0) of the tile rows).  A lane takes one word column of the rows: head_dim / 4 lanes
+// per block for int8, head_dim / 8 for NF4, so a warp works on 32 / that many blocks at a time.
 template <int HD, bool KV4>
-__device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
+__device__ __forceinline__ void value_rows_transpose(uint32_t rows, uint32_t tile, uint32_t stride, uint32_t n_blk, uint32_t unit0,
+                                                     uint32_t unit_step, uint32_t lane, uint32_t chunk0 = 0) {
+    constexpr uint32_t ROW = KV4 ? HD / 2 : HD, LPB = ROW / 4, BPU = 32 / LPB;
+    const uint32_t col = lane % LPB;
+    for (uint32_t u = unit0; u * BPU < n_blk; u += unit_step) {
+        const uint32_t b = u * BPU + lane / LPB;
+        if (b >= n_blk) continue;
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = lds_u32(rows + (16 * b + j) * ROW + 4 * col);
+        const uint32_t chunk = b + chunk0;
+        if (KV4) {
+            // bytes 4 col .. 4 col + 3 of a row: low nibbles = dimensions D .. D + 3, high nibbles = D + 16 .. D + 19
+            const uint32_t B0 = 4 * col, D = (B0 / 32) * 64 + ((B0 / 16) % 2) * 32 + B0 % 16;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t t[4][4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t x[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) x[j] = half ? (w[4 * q + j] >> 2) & 0x3C3C3C3Cu : (w[4 * q + j] << 2) & 0x3C3C3C3Cu;
+                    uint32_t r[4];
+                    transpose4x4_bytes(x, r);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) t[i][q] = r[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t d = D + 16 * half + i;
+                    sts_u32x4(tile + d * stride + (((chunk & ~7u) | ((chunk ^ vt_swz(d)) & 7u)) << 4), t[i][0], t[i][1], t[i][2], t[i][3]);
+                }
+            }
+        } else {
+            uint32_t t[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t x[4], r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = w[4 * q + j] ^ 0x80808080u;
+                transpose4x4_bytes(x, r);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) t[i][q] = r[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t d = 4 * col + i;
+                sts_u32x4(tile + d * stride + (((chunk & ~7u) | ((chunk ^ vt_swz(d)) & 7u)) << 4), t[i][0], t[i][1], t[i][2], t[i][3]);
+            }
+        }
+    }
+}
+// Sixteen chain steps of dimension d from one 16-byte chunk of its tile row: o = fma(value, weight, o), positions ascending.
+// `n` < 16 stops after n steps (selects, no branches).  KV4: `cbfa` = shared address of the 16 fp32 centroids.
+template <bool KV4>
+__device__ __forceinline__ float value_chain16(float o, const uint4 x, const float4 w0, const float4 w1, const float4 w2, const float4 w3,
+                                               uint32_t cbfa, uint32_t n = 16) {
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+    const float ws[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w, w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        float v;
+        if (KV4) {
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(cbfa + prmt(xs[k / 4], 0u, 0x4440u + (k % 4))));
+        } else {
+            // 0x4B000000 | (b ^ 0x80) is the float 2^23 + 128 + (int8)b: subtracting 2^23 + 128 converts without the conversion unit
+            v = __fsub_rn(__uint_as_float(prmt(xs[k / 4], 0x4B000000u, 0x7440u + (k % 4))), 8388736.0f);
+        }
+        const float r = __fmaf_rn(v, ws[k], o);
+        o = (uint32_t)k < n ? r : o;
+    }
+    return o;
+}
+
+#ifndef K2T_CUT_AT
+#define K2T_CUT_AT 99
+#endif
+#define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); if (K2T_CUT_AT == (i)) return; } while (0)
+
+template <int HD, bool KV4, bool STAGED>
+__device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, bool wait_here) {
     constexpr int QW = HD / 4, NB = HD / 64;
     constexpr uint32_t NT = ATTN_THREADS, NW = ATTN_THREADS / 32;
     constexpr uint32_t ROW = KV4 ? HD / 2 : HD;            // bytes of one cached key / value row
@@ -226,6 +344,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     __builtin_assume(__isShared(s.wg)); __builtin_assume(__isShared(s.cbf)); __builtin_assume(__isShared(s.qs_val));
     __builtin_assume(__isShared(s.qs_c)); __builtin_assume(__isShared(s.qs_idx)); __builtin_assume(__isShared(s.hq4));
     __builtin_assume(__isShared(s.hs16));
+    if (STAGED) __builtin_assume(__isShared(s.vt));
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t group = A.n_q / A.n_kv, kvh = qh / group, ctx = pos + 1, layer = A.layer;
     const size_t slot0 = ((size_t)layer * A.n_kv + kvh) * A.max_seq;
@@ -251,13 +370,17 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     if (KV4 && tid < 16) s.cbf[tid] = NF4_KV_CENTROIDS[tid];
     constexpr int HV = HD / 32;                            // head elements per lane (warps 0..2)
     const uint32_t my_head = warp == 0 ? qh : warp == 1 ? A.n_q + kvh : A.n_q + A.n_kv + kvh;
-    float hv[HV], rc[HV], rs[HV];                          // head values (+bias), rope cos / sin of the lane's pair
+    float hv[HV], hb[HV], rc[HV], rs[HV];                  // head values, their bias, rope cos / sin of the lane's pair
+    FwhtSigns sg_head[NB], sg_out_inv, sg_out_fwd;         // rotation signs: of the head's blocks (warps 0..2), of the output chunk (warps < NB)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) sg_head[b] = fwht_signs(b, lane);
+    sg_out_inv = fwht_signs(warp, lane);
+    sg_out_fwd = fwht_signs(A.out_chunk0 + qh * NB + warp, lane);
     if (warp < 3) {
 #pragma unroll
         for (int k = 0; k < HV; ++k) {
             const uint32_t i = lane + 32 * k;
-            hv[k] = __ldcg(A.qkv + (size_t)my_head * HD + i);
-            if (A.bias != nullptr) hv[k] = __fadd_rn(hv[k], __ldg(A.bias + (size_t)my_head * HD + i));
+            hb[k] = A.bias != nullptr ? __ldg(A.bias + (size_t)my_head * HD + i) : 0.0f;
             rc[k] = __ldg(A.rope + (size_t)pos * HD + (i % (HD / 2)));
             rs[k] = __ldg(A.rope + (size_t)pos * HD + HD / 2 + (i % (HD / 2)));
         }
@@ -284,7 +407,17 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             vsr[k][0] = cached ? __ldcg(vs + t) : 0.0f;
         }
     }
+    // Everything above reads what earlier steps (or a launch at least two back) wrote; the projection output below is the
+    // predecessor's.
+    if (wait_here) { pdl_wait(); pdl_trigger(); }
     ATTN_MARK(1);
+    if (warp < 3) {
+#pragma unroll
+        for (int k = 0; k < HV; ++k) {
+            hv[k] = __ldcg(A.qkv + (size_t)my_head * HD + lane + 32 * k);
+            if (A.bias != nullptr) hv[k] = __fadd_rn(hv[k], hb[k]);
+        }
+    }
     // ---- the three heads of this CTA: warp 0 = query qh, warp 1 = key kvh, warp 2 = value kvh
     if (warp < 3) {
         float *sh = s.head + warp * 128;
@@ -320,16 +453,18 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             __syncwarp();
         };
         if (warp < 2) {
-            if (A.qk_norm_after_rope) do_rope();
-            if (norm_w != nullptr) do_norm();
-            if (!A.qk_norm_after_rope) do_rope();
+#pragma unroll 1
+            for (int step = 0; step < 2; ++step) {       // rolled: one copy of each in the code
+                if ((step == 0) == (A.qk_norm_after_rope != 0)) do_rope();
+                else if (norm_w != nullptr) do_norm();
+            }
         }
         float v0[NB], v1[NB], mx = 0.0f;
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
             v0[b] = sh[b * 64 + 2 * lane];
             v1[b] = sh[b * 64 + 2 * lane + 1];
-            warp_fwht64(v0[b], v1[b], b, lane);
+            warp_fwht64(v0[b], v1[b], sg_head[b], lane);
             mx = fmaxf(mx, fmaxf(fabsf(v0[b]), fabsf(v1[b])));
         }
         const bool store = warp > 0 && qh % group == 0;     // one CTA of the group writes the cache entry
@@ -450,27 +585,48 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     __syncthreads();
     ATTN_MARK(5);
+    // thread 0 sums the body (four accumulators = four independent chains, 16-byte loads four groups ahead) while three
+    // other threads evaluate the remainder's exps and warps 1.. transpose the cached value rows for the chain below
     float acc = 0.0f;
-    if (warp == 0) {
-        if (lane < 4) {
-            uint32_t t = lane;
-            for (; t + 28 < n4; t += 32) {
-                float v[8];
+    bool copy_failed = false;
+    if (tid == 0) {
+        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(s.sc);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        uint32_t t = 0;
+        for (; t + 16 <= n4; t += 16) {
+            float4 v[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = s.sc[t + 4 * j];
+            for (int j = 0; j < 4; ++j) v[j] = lds_f32x4(sa + 4 * t + 16 * j);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc = __fadd_rn(acc, v[j]);
+            for (int j = 0; j < 4; ++j) {
+                a0 = __fadd_rn(a0, v[j].x); a1 = __fadd_rn(a1, v[j].y); a2 = __fadd_rn(a2, v[j].z); a3 = __fadd_rn(a3, v[j].w);
             }
-            for (; t < n4; t += 4) acc = __fadd_rn(acc, s.sc[t]);
         }
-        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0+a1, lane 2: a2+a3
-        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
+        for (; t < n4; t += 4) {
+            const float4 v = lds_f32x4(sa + 4 * t);
+            a0 = __fadd_rn(a0, v.x); a1 = __fadd_rn(a1, v.y); a2 = __fadd_rn(a2, v.z); a3 = __fadd_rn(a3, v.w);
+        }
+        acc = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
     }
     ATTN_MARK(6);
+    {
+        // the remainder's exps (at most three positions; thread 0 gets to its own, if any, after the sum)
+        float tail_x = 0.0f;
+        uint32_t tail_t = 0xffffffffu;
 #pragma unroll
-    for (int k = 0; k < PT; ++k) {
-        const uint32_t t = tid + k * NT;
-        if (t >= n4 && t < ctx) s.sc[t] = (float)exp((double)__fsub_rn(scr[k], mx));
+        for (int k = 0; k < PT; ++k) {
+            const uint32_t t = tid + k * NT;
+            if (t >= n4 && t < ctx) { tail_t = t; tail_x = __fsub_rn(scr[k], mx); }
+        }
+        if (tail_t != 0xffffffffu) s.sc[tail_t] = (float)exp((double)tail_x);
+    }
+    if (STAGED && warp > 0 && pos > 0) {           // bounded wait for the bulk copy of the value rows, then the transposition
+        uint32_t ok = 0;
+        for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) ok = mbar_try_wait(vbar, 0);
+        copy_failed = !ok;
+        if (ok)
+            value_rows_transpose<HD, KV4>((uint32_t)__cvta_generic_to_shared(s.vbuf), (uint32_t)__cvta_generic_to_shared(s.vt), ATTN_EXACT_CTX,
+                                          (pos + 15) / 16, warp - 1, NW - 1, lane);
     }
     __syncthreads();
     ATTN_MARK(7);
@@ -499,8 +655,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     __syncthreads();                       // weights complete
     ATTN_MARK(9);
     float o = 0.0f;
-    bool copy_failed = false;
-    if (pos > 0) {                         // bounded wait for the bulk copy
+    if (pos > 0 && !STAGED) {              // bounded wait for the bulk copy (the transposers have waited already where there is a tile)
         uint32_t ok = 0;
         for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin)
             asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -510,7 +665,40 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     copy_failed = __syncthreads_or(copy_failed) != 0;      // the same verdict in every thread (there are barriers below)
     if (copy_failed && tid == 0 && A.err_flag != nullptr) atomicExch(A.err_flag, 1u);
     ATTN_MARK(10);
-    if (tid < HD && !copy_failed) {
+    if (STAGED) {
+        if (tid < HD && !copy_failed) {
+            const uint32_t row = (uint32_t)__cvta_generic_to_shared(s.vt) + tid * ATTN_EXACT_CTX, fd = vt_swz(tid);
+            const uint32_t wa = (uint32_t)__cvta_generic_to_shared(KV4 ? s.wg + (tid / 64) * ATTN_EXACT_CTX : s.sc);
+            const uint32_t cbfa = (uint32_t)__cvta_generic_to_shared(s.cbf);
+            const uint32_t n_full = pos / 16, rem = pos % 16;
+            auto chunk_at = [&](uint32_t b) { return row + (((b & ~7u) | ((b ^ fd) & 7u)) << 4); };
+            uint4 x = make_uint4(0, 0, 0, 0);
+            float4 w0 = make_float4(0, 0, 0, 0), w1 = w0, w2 = w0, w3 = w0;
+            if (pos > 0) {
+                x = lds_u32x4(chunk_at(0));
+                w0 = lds_f32x4(wa); w1 = lds_f32x4(wa + 16); w2 = lds_f32x4(wa + 32); w3 = lds_f32x4(wa + 48);
+            }
+            for (uint32_t b = 0; b < n_full; ++b) {
+                // the next block's bytes and weights are requested before this block's sixteen steps (the last request may
+                // read the partial block or, at pos = 512, one chunk of the next row: in bounds, unused)
+                const uint32_t nb = b + 1 < ATTN_EXACT_CTX / 16 ? b + 1 : b;
+                const uint4 xn = lds_u32x4(chunk_at(nb));
+                const float4 n0 = lds_f32x4(wa + 64 * nb), n1 = lds_f32x4(wa + 64 * nb + 16), n2 = lds_f32x4(wa + 64 * nb + 32), n3 = lds_f32x4(wa + 64 * nb + 48);
+                o = value_chain16<KV4>(o, x, w0, w1, w2, w3, cbfa);
+                x = xn; w0 = n0; w1 = n1; w2 = n2; w3 = n3;
+            }
+            if (rem != 0) o = value_chain16<KV4>(o, x, w0, w1, w2, w3, cbfa, rem);
+            // the current position: its value row is still in the head area
+            if (KV4) {
+                const uint32_t g = tid / 64, e = tid % 64, r = e % 32;
+                const uint32_t byte_off = g * 32 + (e / 32) * 16 + (r % 16), shift = r < 16 ? 0u : 4u;
+                o = __fmaf_rn(s.cbf[(s.hq4[64 + byte_off] >> shift) & 15u], s.wg[g * ATTN_EXACT_CTX + pos], o);
+            } else {
+                const uint32_t b = reinterpret_cast<const uint8_t *>(s.hq)[256 + tid];
+                o = __fmaf_rn(__fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f), s.sc[pos], o);
+            }
+        }
+    } else if (tid < HD && !copy_failed) {
         // a zero weight skips the position (as the CPU loop does): select, not branch.  Eight positions are
         // loaded before their fma chain starts, so the chain runs at fma latency, not shared-memory latency.
         if (KV4) {
@@ -597,16 +785,15 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     ATTN_MARK(11);
     __syncthreads();
     ATTN_MARK(12);
-    if (tid == 0 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
     if (tid < HD) s.o[tid] = o;
     __syncthreads();
     if (warp < NB) {
         const uint32_t b = warp;
         float x0 = s.o[b * 64 + 2 * lane], x1 = s.o[b * 64 + 2 * lane + 1];
-        warp_ifwht64(x0, x1, b, lane);
+        warp_ifwht64(x0, x1, sg_out_inv, lane);
         if (A.attn_tap != nullptr) reinterpret_cast<float2 *>(A.attn_tap + (size_t)qh * HD + b * 64)[lane] = make_float2(x0, x1);
         const uint32_t c = qh * NB + b;
-        warp_fwht64(x0, x1, A.out_chunk0 + c, lane);
+        warp_fwht64(x0, x1, sg_out_fwd, lane);
         int q0, q1, sum;
         float sc;
         warp_quant64(x0, x1, q0, q1, sc, sum);
@@ -614,16 +801,23 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
         if (lane == 0) { A.out_scales[c] = sc; A.out_sums[c] = sum; }
     }
     ATTN_MARK(13);
+    // the barrier's memory is initialised again by the next call on this shared memory (the whole-token kernel)
+    if (tid == NT - 32 && pos > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(vbar) : "memory");
 }
 
 // runtime dispatch on head_dim / cache format
-__device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s) {
+template <bool STAGED>
+__device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, bool wait_here = false) {
+#ifdef K2T_PROBE_HD
+    attention_head_cta<K2T_PROBE_HD, K2T_PROBE_KV4 != 0, STAGED>(A, qh, pos, s, wait_here);
+    return;
+#endif
     if (A.kv_bits == 4) {
-        if (A.head_dim == 64) attention_head_cta<64, true>(A, qh, pos, s);
-        else attention_head_cta<128, true>(A, qh, pos, s);
+        if (A.head_dim == 64) attention_head_cta<64, true, STAGED>(A, qh, pos, s, wait_here);
+        else attention_head_cta<128, true, STAGED>(A, qh, pos, s, wait_here);
     } else {
-        if (A.head_dim == 64) attention_head_cta<64, false>(A, qh, pos, s);
-        else attention_head_cta<128, false>(A, qh, pos, s);
+        if (A.head_dim == 64) attention_head_cta<64, false, STAGED>(A, qh, pos, s, wait_here);
+        else attention_head_cta<128, false, STAGED>(A, qh, pos, s, wait_here);
     }
 }
 

@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const EmbedArgs a) {
 // buffer and adds the ranks' values in rank order.  A rank cannot be two calls ahead of another (it needs the others'
 // words of call e + 1, sent after they finished call e), so two halves suffice; the call counter is shared with
 // tp_exchange_kernel (k2t_tp.cu) and advanced by the last CTA of the launch to finish.
+template <bool TP>
 __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__ hidden, const float *__restrict__ delta,
                                                             const float *__restrict__ w, uint32_t n, float eps,
                                                             int8_t *__restrict__ q, float *__restrict__ scales,
@@ -59,13 +60,19 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
         if (delta != nullptr) delta += t * n;
         if (x_norm != nullptr) x_norm += t * n;
     }
+    const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
+    // The norm weights do not depend on the predecessor: they are staged in shared memory before the wait (the weights of a
+    // layer are read once per token, so this load goes all the way to HBM).  The loops of this kernel stay rolled: its code
+    // runs once per launch, and instruction fetch, not issue, is what a long straight-line kernel waits for.
+    float *s_w = s_x + (TP ? 2 : 1) * n;
+#pragma unroll 1
+    for (uint32_t i = tid; i < n / 4; i += nthr) reinterpret_cast<float4 *>(s_w)[i] = __ldg(reinterpret_cast<const float4 *>(w) + i);
     pdl_wait();
     pdl_trigger();
-    const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
-    const bool exchange = tp.tp > 1 && delta != nullptr;
+    const bool exchange = TP && tp.tp > 1 && delta != nullptr;
     uint32_t epoch = 0;
     float *s_d = s_x + n;                    // exchange: the summed delta (the launcher doubles the shared memory)
-    if (exchange) {
+    if (TP && exchange) {
         __shared__ int s_budget;             // polls the CTA may still spend on words that have not arrived (signed: concurrent settlements may overdraw it)
         if (tid == 0) {
             s_epoch = *tp.epoch + 1;
@@ -112,6 +119,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
         }
         if (__syncthreads_or(failed) && tid == 0) atomicExch(tp.err, 3u);
     }
+#pragma unroll 1
     for (uint32_t i = tid; i < n / 4; i += nthr) {
         float4 v = __ldcg(reinterpret_cast<const float4 *>(hidden) + i);
         if (delta != nullptr) {
@@ -136,9 +144,10 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
     }
     __syncthreads();
     const float inv = s_inv;
+#pragma unroll 1
     for (uint32_t c = warp; c < nc; c += nwarp) {
         float2 v = reinterpret_cast<const float2 *>(s_x + (size_t)c * 64)[lane];
-        const float2 ww = reinterpret_cast<const float2 *>(w + (size_t)c * 64)[lane];
+        const float2 ww = reinterpret_cast<const float2 *>(s_w + (size_t)c * 64)[lane];
         v.x = __fmul_rn(__fmul_rn(v.x, inv), ww.x);
         v.y = __fmul_rn(__fmul_rn(v.y, inv), ww.y);
         if (x_norm != nullptr) reinterpret_cast<float2 *>(x_norm + (size_t)c * 64)[lane] = v;
@@ -742,11 +751,14 @@ __global__ void __launch_bounds__(FINISH_THREADS) attn_finish_kernel(const AttnA
 // kernels serve them.
 __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    pdl_wait();
-    pdl_trigger();
+    const bool early = a.early != 0;
+    if (!early) { pdl_wait(); pdl_trigger(); }
     const uint32_t pos = __ldcg(a.pos) + a.pos_offset;
-    if (pos + 1 > ATTN_EXACT_CTX) return;
-    attention_head_dispatch(a, blockIdx.x, pos, attn_carve(smem));
+    if (pos + 1 > ATTN_EXACT_CTX) {
+        if (early) { pdl_wait(); pdl_trigger(); }       // every kernel of the chain waits: completion of this one implies its predecessors'
+        return;
+    }
+    attention_head_dispatch<true>(a, blockIdx.x, pos, attn_carve(smem, true), early);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -756,6 +768,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
                                                            int8_t *__restrict__ q, float *__restrict__ scales,
                                                            int32_t *__restrict__ sums, float *__restrict__ dbg, uint32_t chunk0) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const FwhtSigns sg = fwht_signs(chunk0 + c, lane);
     pdl_wait();
     pdl_trigger();
     if (c >= inter / 64) return;
@@ -769,7 +782,7 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const float *__restri
     float x0 = __fmul_rn(__fdiv_rn(g.x, __fadd_rn(1.0f, exp_poly(-g.x))), u.x);
     float x1 = __fmul_rn(__fdiv_rn(g.y, __fadd_rn(1.0f, exp_poly(-g.y))), u.y);
     if (dbg != nullptr) reinterpret_cast<float2 *>(dbg + (size_t)c * 64)[lane] = make_float2(x0, x1);
-    warp_fwht64(x0, x1, chunk0 + c, lane);
+    warp_fwht64(x0, x1, sg, lane);
     int q0, q1, sum;
     float sc;
     warp_quant64(x0, x1, q0, q1, sc, sum);
@@ -894,15 +907,17 @@ cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *
                                     int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl,
                                     const TpLink &tp, uint32_t *tp_done) {
     if (tp.tp > 1 && ((size_t)n_tok * n > tp.ll_slot || tp_done == nullptr)) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)n * sizeof(float) * (tp.tp > 1 ? 2 : 1);
+    const bool with_tp = tp.tp > 1;
+    const size_t smem = (size_t)n * sizeof(float) * (with_tp ? 3 : 2);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     {
-        cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(rmsnorm_quant_kernel), smem);
+        cudaError_t e = allow_dynamic_smem(with_tp ? reinterpret_cast<const void *>(rmsnorm_quant_kernel<true>) : reinterpret_cast<const void *>(rmsnorm_quant_kernel<false>), smem);
         if (e != cudaSuccess) return e;
     }
     // one warp per 64-value chunk where that fits: the load and the rotation each take one round
     const uint32_t threads = std::min(1024u, std::max(256u, (n / 64) * 32u));
-    return launch_kernel(rmsnorm_quant_kernel, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm, tp, tp_done);
+    if (with_tp) return launch_kernel(rmsnorm_quant_kernel<true>, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm, tp, tp_done);
+    return launch_kernel(rmsnorm_quant_kernel<false>, dim3(n_tok), dim3(threads), smem, s, pdl, hidden, delta, w, n, eps, q, scales, sums, x_norm, tp, tp_done);
 }
 cudaError_t launch_qkv_post(cudaStream_t s, const QkvPostArgs &a, bool pdl, uint32_t n_tok) {
     const uint32_t heads = a.n_q + 2 * a.n_kv;
@@ -929,7 +944,7 @@ cudaError_t launch_attention(cudaStream_t s, const AttnArgs &a, bool pdl) {
     return launch_kernel(attn_finish_kernel<128>, dim3(a.n_kv * a.group), dim3(FINISH_THREADS), 0, s, pdl, a);
 }
 cudaError_t launch_attention_fused(cudaStream_t s, const FusedAttnArgs &a, bool pdl) {
-    const size_t smem = attn_smem_bytes();
+    const size_t smem = attn_smem_bytes(true);
     if (a.head_dim != 64 && a.head_dim != 128) return cudaErrorInvalidValue;
     cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_fused_kernel), smem);
     if (e != cudaSuccess) return e;

@@ -111,6 +111,8 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     float eps, attn_scale;
     int32_t qk_norm_after_rope;
     unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (16 words)
+    uint32_t early;              // 1: the launch before this one wrote nothing this kernel prefetches (position word, cache rows of
+                                 // earlier positions), so those loads are issued before the dependency wait
 };
 
 struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scoring (sparse_moe.rs:86-182)
