@@ -8,11 +8,13 @@
 // denominator and ctx dependent fmas per dimension (about 4.5 cycles per position).  Two kernels after qkv_post_kernel:
 //   attn_scores_kernel  - CTA = (128 positions, kv head): key rows staged by one bulk copy, lane = position, dp4a against
 //                         the group's int8 queries; writes the scores and the maximum of every 128-position block;
-//   attn_values_kernel  - CTA = query head: maximum, exp, denominator, value weights for all positions in shared memory,
-//                         then the chains: thread = dimension, value rows streamed through a ring of 256-position tiles
-//                         (bulk copies issued by a producer warp, full / empty mbarriers), sixteen positions loaded
-//                         ahead of the chain; finally the inverse rotation, the forward rotation with the global chunk
-//                         index and the int8 activation of o_proj (real_llm.rs:7059-7084).
+//   attn_values_kernel  - CTA = query head: maximum, exp and denominator for all positions in shared memory, then a
+//                         three-stage pipeline over 256-position tiles: bulk copies of the value rows into a ring
+//                         (producer lane), the other non-chain warps transpose each tile (dimension-major, see
+//                         value_rows_transpose) and turn its softmax terms into value weights, and the chain warps
+//                         (thread = dimension) run sixteen positions per 16-byte load; full / free mbarriers between
+//                         the stages.  Finally the inverse rotation, the forward rotation with the global chunk index
+//                         and the int8 activation of o_proj (real_llm.rs:7059-7084).
 #include <algorithm>
 
 #include "k2t_model_device.cuh"
@@ -20,9 +22,9 @@
 namespace k2t {
 
 constexpr uint32_t SCORE_TILE = 128;          // positions per CTA of the scores kernel (= its threads)
-constexpr uint32_t VAL_THREADS = 256;
+constexpr uint32_t VAL_THREADS = 288;        // chain warps, transposing warps, one producer warp (the ninth)
 constexpr uint32_t VAL_TILE = 256;            // positions per ring stage of the values kernel
-constexpr uint32_t VAL_NST = 4;
+constexpr uint32_t VAL_TBUF = 2;              // transposed tiles in flight between the transposing warps and the chain warps
 constexpr uint32_t EXACT_WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -31,6 +33,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
     uint32_t ok = 0;
     for (uint32_t spin = 0; spin < EXACT_WAIT_LIMIT && !ok; ++spin) ok = mbar_try_wait(bar, parity);
+    return ok != 0;
+}
+// The same for warps that are ahead of the chain warps and share their schedulers: the hardware may park the thread for
+// up to a microsecond per attempt and the loop sleeps between attempts, so waiting costs the running warps no issue slots.
+__device__ __forceinline__ bool mbar_wait_bounded_idle(uint32_t bar, uint32_t parity) {
+    uint32_t ok = 0;
+    for (uint32_t spin = 0; spin < EXACT_WAIT_LIMIT && !ok; ++spin) {
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (!ok) __nanosleep(200);
+    }
     return ok != 0;
 }
 
@@ -192,8 +205,12 @@ template <int HD, bool KV4>
 struct ValSmem {
     static constexpr uint32_t ROW = KV4 ? HD / 2 : HD;
     static constexpr uint32_t NW = KV4 ? HD / 64 : 1;             // weight vectors (one per 64-value group for NF4)
-    static constexpr uint32_t STAGE = VAL_TILE * ROW;
-    static __host__ __device__ size_t bytes(uint32_t ctx_cap) { return 128 + (size_t)VAL_NST * STAGE + (size_t)NW * ctx_cap * 4; }
+    static constexpr uint32_t STAGE = VAL_TILE * ROW;             // one tile of cache rows as stored
+    static constexpr uint32_t NST = STAGE > 16 * 1024 ? 2 : 4;    // ring depth: 64 KB of rows in flight at most
+    static constexpr uint32_t TILE_T = VAL_TILE * HD;             // one transposed tile: a byte per value, row = dimension
+    static constexpr uint32_t W_OFF = 128 + NST * STAGE + VAL_TBUF * TILE_T;
+    // barriers, row ring, transposed tiles, weights (16 floats of slack: the chain requests the next block's weights ahead)
+    static __host__ __device__ size_t bytes(uint32_t ctx_cap) { return W_OFF + (size_t)NW * (ctx_cap + 16) * 4; }
 };
 
 #define VAL_MARK(i) do { if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.trace[i] = (unsigned long long)clock64(); } while (0)
@@ -211,17 +228,29 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     __shared__ uint32_t s_fail;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t qh = blockIdx.x, tok = blockIdx.y, G = a.group, kvh = qh / G, n_q = a.n_kv * G;
-    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(dyn);           // full[VAL_NST], then empty[VAL_NST]
+    // ring depth; transposing warps: the four that do not share a warp scheduler with a chain warp where that is possible
+    // (head_dim 64: chain warps 0 and 1, transposing warps 2, 3, 6, 7, warps 4 and 5 idle during the chains; head_dim 128:
+    // chain warps 0..3, transposing warps 4..7)
+    constexpr uint32_t NST = Sm::NST, NTW = 4;
+    // barriers: full[NST] (rows of a tile have landed), rows_free[NST] (every transposing warp has read them),
+    // t_full[VAL_TBUF] (tile transposed and its weights written), t_free[VAL_TBUF] (every chain warp has left it)
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(dyn);
+    const uint32_t bar_full = bar0, bar_rows_free = bar0 + 8 * NST, bar_t_full = bar0 + 16 * NST, bar_t_free = bar0 + 16 * NST + 8 * VAL_TBUF;
     uint8_t *stages = dyn + 128;
-    float *W = reinterpret_cast<float *>(dyn + 128 + (size_t)VAL_NST * Sm::STAGE);
+    const uint32_t tiles_t = (uint32_t)__cvta_generic_to_shared(dyn + 128 + (size_t)NST * Sm::STAGE);
+    float *W = reinterpret_cast<float *>(dyn + Sm::W_OFF);
+    const uint32_t w_stride = a.ctx_cap + 16;                                // floats between the weight vectors of the NF4 groups
     if (tid == 0) {
-        for (uint32_t s = 0; s < VAL_NST; ++s) { mbar_init(bar0 + 8 * s, 1); mbar_init(bar0 + 8 * (VAL_NST + s), CW); }
+        for (uint32_t s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_rows_free + 8 * s, NTW); }
+        for (uint32_t s = 0; s < VAL_TBUF; ++s) { mbar_init(bar_t_full + 8 * s, NTW); mbar_init(bar_t_free + 8 * s, CW); }
         fence_mbar_init();
         s_fail = 0;
     }
     if (KV4 && tid < 16) s_cb[tid] = NF4_KV_CENTROIDS[tid];
+    // The successor (the o_proj GEMV) is released when the chains reach their last two tiles, not here: its CTAs would sit
+    // on this SM for the whole chain, and warps waiting for a predecessor slow the ones that run (the tail of this kernel
+    // took eight times longer with them resident).
     pdl_wait();
-    pdl_trigger();
     const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + tok + 1, ctx = a.ring.active_len(seq_len), cap = a.ctx_cap;
     const KvRing ring = a.ring;
     if (ctx > cap) {                       // the launcher sizes shared memory for the cache length: cannot happen
@@ -235,10 +264,10 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     VAL_MARK(0);
     // ---- producer: lane 0 of warp CW keeps the ring full; the first VAL_NST tiles go out at once
     auto fill = [&](uint32_t i) {
-        const uint32_t st = i % VAL_NST, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
+        const uint32_t st = i % NST, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
         const uint32_t dst = (uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE);
         fence_proxy_async();
-        mbar_expect_tx(bar0 + 8 * st, n * ROW);
+        mbar_expect_tx(bar_full + 8 * st, n * ROW);
         // the rows of consecutive active positions are consecutive cache rows except where the sinks end and where the ring
         // wraps: one bulk copy per run (one run without a window)
         uint32_t cur = tl;
@@ -247,12 +276,12 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
             uint32_t run = tl + n - cur;
             if (ring.window > 0 && seq_len > ring.window && cur < ring.sinks) run = min(run, ring.sinks - cur);
             else if (ring.ring_len > 0 && p >= ring.sinks) run = min(run, ring.sinks + ring.ring_len - row);
-            bulk_g2s(dst + (cur - tl) * ROW, V + (size_t)row * ROW, run * ROW, bar0 + 8 * st);
+            bulk_g2s(dst + (cur - tl) * ROW, V + (size_t)row * ROW, run * ROW, bar_full + 8 * st);
             cur += run;
         }
     };
-    if (warp == CW && lane == 0)
-        for (uint32_t i = 0; i < VAL_NST && i < n_tiles; ++i) fill(i);
+    if (warp == VAL_THREADS / 32 - 1 && lane == 0)
+        for (uint32_t i = 0; i < NST && i < n_tiles; ++i) fill(i);
     // ---- maximum over the blocks of the scores kernel
     {
         const uint32_t nblk = (ctx + SCORE_TILE - 1) / SCORE_TILE;
@@ -289,135 +318,131 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     }
     __syncthreads();
     VAL_MARK(2);
-    // ---- denominator: lanes 0..3 of warp 0 = the four accumulators (positions 4k + lane), sixteen loads ahead of the adds
+    // ---- denominator (softmax_body_sum in warp 0).  Meanwhile the transposing warps take the first VAL_TBUF tiles (rows only:
+    // the weights need the denominator).
+    const bool is_tw = CW == 4 ? (warp >= 4 && warp < 8) : (warp == 2 || warp == 3 || warp == 6 || warp == 7);
+    const uint32_t tw = CW == 4 ? warp - 4 : (warp < 4 ? warp - 2 : warp - 4);          // transposing warp index 0..3 (0 = warp CW, the producer's)
+    // tile i: rows of stage i % NST -> transposed tile i % VAL_TBUF; the producer lane refills the stage once all have read it
+    auto transpose_tile = [&](uint32_t i) -> bool {
+        const uint32_t st = i % NST, tb = i % VAL_TBUF, n = min(VAL_TILE, ctx - i * VAL_TILE);
+        if (!mbar_wait_bounded(bar_full + 8 * st, (i / NST) & 1u)) return false;
+        if (i >= VAL_TBUF && !mbar_wait_bounded(bar_t_free + 8 * tb, ((i / VAL_TBUF) - 1u) & 1u)) return false;
+        value_rows_transpose<HD, KV4>((uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE), tiles_t + tb * Sm::TILE_T, VAL_TILE,
+                                      (n + 15) / 16, tw, NTW, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_rows_free + 8 * st);
+        return true;
+    };
+    // producer (lane 0 of the ninth warp): tile i + NST goes into the stage of tile i once every transposing warp has read it
+    auto refill_after = [&](uint32_t i) -> bool {
+        if (i + NST >= n_tiles) return true;
+        if (!mbar_wait_bounded_idle(bar_rows_free + 8 * (i % NST), (i / NST) & 1u)) return false;
+        fill(i + NST);
+        return true;
+    };
+    constexpr uint32_t PRODUCER_WARP = VAL_THREADS / 32 - 1;
+    bool failed = false;
     if (warp == 0) {
-        float acc = 0.0f;
-        if (lane < 4) {
-            uint32_t t = lane;
-            float cur[16], nxt[16];
-            if (t + 60 < n4) {
-#pragma unroll
-                for (int u = 0; u < 16; ++u) cur[u] = W[t + 4 * u];
-                for (; t + 124 < n4; t += 64) {
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) nxt[u] = W[t + 64 + 4 * u];
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, cur[u]);
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
-                }
-#pragma unroll
-                for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, cur[u]);
-                t += 64;
-            }
-            for (; t < n4; t += 4) acc = __fadd_rn(acc, W[t]);
-        }
-        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0 + a1, lane 2: a2 + a3
-        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
+        float acc = softmax_body_sum((uint32_t)__cvta_generic_to_shared(W), n4, lane);
         if (lane == 0) {
-            for (uint32_t t = n4; t < ctx; ++t) acc = __fadd_rn(acc, W[t]);
+            for (uint32_t t2 = n4; t2 < ctx; ++t2) acc = __fadd_rn(acc, W[t2]);
             s_inv = __fdiv_rn(1.0f, acc);
         }
+    } else if (is_tw) {
+        for (uint32_t i = 0; i < VAL_TBUF && i < n_tiles && !failed; ++i) failed = !transpose_tile(i);
+    } else if (warp == PRODUCER_WARP && lane == 0) {
+        for (uint32_t i = 0; i < VAL_TBUF && i < n_tiles && !failed; ++i) failed = !refill_after(i);
     }
     __syncthreads();
     VAL_MARK(3);
-    // ---- value weights: (p * inv) * v_scale   (per 64-value group for the NF4 cache)
     const float inv = s_inv;
-    if (KV4) {
-        const uint16_t *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
-        for (uint32_t t = tid; t < ctx; t += VAL_THREADS) {
-            const float p_norm = __fmul_rn(W[t], inv);
-            const size_t row = ring.slot_of_pos(ring.active_pos(t, seq_len));
-            if (NB == 2) W[cap + t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + row * NB + 1)));
-            W[t] = __fmul_rn(p_norm, bf16_bits_to_f32(__ldcg(vs16 + row * NB)));
-        }
-    } else {
-        const float *vs = a.v_scale + slot0;
-        uint32_t t = tid;
-        for (; t + 7 * VAL_THREADS < ctx; t += 8 * VAL_THREADS) {
-            float v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldcg(vs + ring.slot_of_pos(ring.active_pos(t + u * VAL_THREADS, seq_len)));
-#pragma unroll
-            for (int u = 0; u < 8; ++u) W[t + u * VAL_THREADS] = __fmul_rn(__fmul_rn(W[t + u * VAL_THREADS], inv), v[u]);
-        }
-        for (; t < ctx; t += VAL_THREADS) W[t] = __fmul_rn(__fmul_rn(W[t], inv), __ldcg(vs + ring.slot_of_pos(ring.active_pos(t, seq_len))));
-    }
-    __syncthreads();
     VAL_MARK(4);
-    // ---- chains
     if (warp < CW) {
-        // a zero weight adds +-0 (the CPU loop skips such positions: same bits, the values are finite and the sum starts at +0)
+        // ---- chains: a zero weight adds +-0 (the CPU loop skips such positions: same bits, the values are finite and the sum
+        // starts at +0)
         float o = 0.0f;
-        bool failed = false;
         long long t_wait = 0;
-        const uint32_t d = tid;                                    // this thread's dimension
-        uint32_t byte_off = d, shift = 0;
-        const float *wp = W;
-        if (KV4) {        // byte 16h + i of a 64-value group packs columns 32h + i (low nibble) and 32h + 16 + i (high)
-            const uint32_t g = d / 64, e = d % 64, r = e % 32;
-            byte_off = g * 32 + (e / 32) * 16 + (r % 16);
-            shift = r < 16 ? 0u : 4u;
-            wp = W + (size_t)g * cap;
-        }
-        auto value = [&](uint32_t b) -> float {
-            if (KV4) return s_cb[(b >> shift) & 15u];
-            return __fsub_rn(__uint_as_float(b ^ 0x4B000080u), 8388736.0f);      // int8 -> fp32 without the conversion unit
-        };
+        const uint32_t d = tid, fd = vt_swz(d);                    // this thread's dimension
+        const uint32_t cbfa = (uint32_t)__cvta_generic_to_shared(s_cb);
+        const uint32_t wa0 = (uint32_t)__cvta_generic_to_shared(W + (KV4 ? (size_t)(d / 64) * w_stride : 0));
         for (uint32_t i = 0; i < n_tiles; ++i) {
-            const uint32_t st = i % VAL_NST, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
+            const uint32_t tb = i % VAL_TBUF, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
+            if (i + 2 >= n_tiles) pdl_trigger();       // one thread's call releases the CTA: only the chain warps call it
             const long long tw0 = clock64();
-            if (!mbar_wait_bounded(bar0 + 8 * st, (i / VAL_NST) & 1u)) { failed = true; break; }
+            if (!mbar_wait_bounded(bar_t_full + 8 * tb, (i / VAL_TBUF) & 1u)) { failed = true; break; }
             t_wait += clock64() - tw0;
-            const uint8_t *vt = stages + (size_t)st * Sm::STAGE + byte_off;
-            const float *wt = wp + tl;
-            const uint32_t va = (uint32_t)__cvta_generic_to_shared(vt), wa = (uint32_t)__cvta_generic_to_shared(wt);
-            uint32_t j = 0;
-            if (n >= 16) {
-                uint32_t cur[16], nxt[16];
-                float4 wc[4], wn[4];
-#pragma unroll
-                for (int u = 0; u < 16; ++u) cur[u] = lds_u8(va + u * ROW);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) wc[u] = lds_f32x4(wa + 16 * u);
-                for (; j + 32 <= n; j += 16) {
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) nxt[u] = lds_u8(va + (j + 16 + u) * ROW);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) wn[u] = lds_f32x4(wa + 4 * (j + 16) + 16 * u);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        o = __fmaf_rn(value(cur[4 * u + 0]), wc[u].x, o);
-                        o = __fmaf_rn(value(cur[4 * u + 1]), wc[u].y, o);
-                        o = __fmaf_rn(value(cur[4 * u + 2]), wc[u].z, o);
-                        o = __fmaf_rn(value(cur[4 * u + 3]), wc[u].w, o);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 16; ++u) cur[u] = nxt[u];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) wc[u] = wn[u];
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    o = __fmaf_rn(value(cur[4 * u + 0]), wc[u].x, o);
-                    o = __fmaf_rn(value(cur[4 * u + 1]), wc[u].y, o);
-                    o = __fmaf_rn(value(cur[4 * u + 2]), wc[u].z, o);
-                    o = __fmaf_rn(value(cur[4 * u + 3]), wc[u].w, o);
-                }
-                j += 16;
+            const uint32_t row = tiles_t + tb * Sm::TILE_T + d * VAL_TILE, wa = wa0 + 4 * tl;
+            auto chunk_at = [&](uint32_t b) { return row + (((b & ~7u) | ((b ^ fd) & 7u)) << 4); };
+            const uint32_t n_full = n / 16, rem = n % 16;
+            uint4 x = lds_u32x4(chunk_at(0));
+            float4 w0 = lds_f32x4(wa), w1 = lds_f32x4(wa + 16), w2 = lds_f32x4(wa + 32), w3 = lds_f32x4(wa + 48);
+            for (uint32_t b = 0; b < n_full; ++b) {
+                // the next block's bytes and weights are requested before this block's sixteen steps (past the end of the
+                // tile they are in bounds and unused)
+                const uint32_t nb = b + 1 < VAL_TILE / 16 ? b + 1 : b;
+                const uint4 xn = lds_u32x4(chunk_at(nb));
+                const float4 n0 = lds_f32x4(wa + 64 * nb), n1 = lds_f32x4(wa + 64 * nb + 16), n2 = lds_f32x4(wa + 64 * nb + 32), n3 = lds_f32x4(wa + 64 * nb + 48);
+                o = value_chain16<KV4>(o, x, w0, w1, w2, w3, cbfa);
+                x = xn; w0 = n0; w1 = n1; w2 = n2; w3 = n3;
             }
-            for (; j < n; ++j) o = __fmaf_rn(value(vt[(size_t)j * ROW]), wt[j], o);
+            if (rem != 0) o = value_chain16<KV4>(o, x, w0, w1, w2, w3, cbfa, rem);
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar0 + 8 * (VAL_NST + st));          // this warp is done with the stage
+            if (lane == 0) mbar_arrive(bar_t_free + 8 * tb);               // this warp is done with the tile
         }
         if (failed) atomicExch(&s_fail, 1u);
         if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) a.trace[8] = (unsigned long long)t_wait;
         s_o[d] = o;
-    } else if (warp == CW && lane == 0) {
-        for (uint32_t i = VAL_NST; i < n_tiles; ++i) {           // tile i reuses the stage of tile i - VAL_NST once every chain warp has left it
-            if (!mbar_wait_bounded(bar0 + 8 * (VAL_NST + i % VAL_NST), ((i / VAL_NST) - 1u) & 1u)) { atomicExch(&s_fail, 1u); break; }
-            fill(i);
+    } else if (is_tw) {
+        // ---- transposing warps: tile by tile, the value weights (p * inv) * v_scale of its positions (per 64-value group for
+        // the NF4 cache), then - from the third tile on - the transposition; the scales of the next tile are requested first
+        const uint32_t li = tw * 32 + lane;                        // this lane's position within a tile (and li + NTW * 32)
+        constexpr uint32_t PER = (VAL_TILE + NTW * 32 - 1) / (NTW * 32);
+        const float *vs = a.v_scale + slot0;
+        const uint16_t *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
+        float sc_next[PER][KV4 ? NB : 1];
+        auto load_scales = [&](uint32_t i) {
+#pragma unroll
+            for (uint32_t k = 0; k < PER; ++k) {
+                const uint32_t t = i * VAL_TILE + li + k * NTW * 32;
+                const bool on = li + k * NTW * 32 < VAL_TILE && t < ctx;
+                const size_t row = on ? ring.slot_of_pos(ring.active_pos(t, seq_len)) : 0;
+                if (KV4) {
+#pragma unroll
+                    for (int g = 0; g < NB; ++g) sc_next[k][g] = on ? bf16_bits_to_f32(__ldcg(vs16 + row * NB + g)) : 0.0f;
+                } else {
+                    sc_next[k][0] = on ? __ldcg(vs + row) : 0.0f;
+                }
+            }
+        };
+        if (n_tiles > 0) load_scales(0);
+        for (uint32_t i = 0; i < n_tiles && !failed; ++i) {
+            float sc_cur[PER][KV4 ? NB : 1];
+#pragma unroll
+            for (uint32_t k = 0; k < PER; ++k)
+#pragma unroll
+                for (int g = 0; g < (KV4 ? NB : 1); ++g) sc_cur[k][g] = sc_next[k][g];
+            if (i + 1 < n_tiles) load_scales(i + 1);
+            if (i >= VAL_TBUF) failed = !transpose_tile(i);
+#pragma unroll
+            for (uint32_t k = 0; k < PER; ++k) {
+                const uint32_t t = i * VAL_TILE + li + k * NTW * 32;
+                if (li + k * NTW * 32 < VAL_TILE && t < ctx) {
+                    const float p_norm = __fmul_rn(W[t], inv);
+                    if (KV4) {
+#pragma unroll
+                        for (int g = NB - 1; g >= 0; --g) W[(size_t)g * w_stride + t] = __fmul_rn(p_norm, sc_cur[k][g]);
+                    } else {
+                        W[t] = __fmul_rn(p_norm, sc_cur[k][0]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_t_full + 8 * (i % VAL_TBUF));
         }
+        if (failed) atomicExch(&s_fail, 1u);
+    } else if (warp == PRODUCER_WARP && lane == 0) {
+        for (uint32_t i = VAL_TBUF; i < n_tiles && !failed; ++i) failed = !refill_after(i);
+        if (failed) atomicExch(&s_fail, 1u);
     }
     VAL_MARK(5);
     __syncthreads();
@@ -449,8 +474,12 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
 // ------------------------------------------------------------------------------------------------
 template <int HD, bool KV4>
 static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok) {
-    const size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap);
+    size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    // One token: few CTAs, each a latency chain.  Asking for more than half an SM's shared memory keeps two of them off the
+    // same SM (the block scheduler otherwise puts them wherever the scores kernel frees room first, and chain warps that
+    // share a scheduler take turns: 103k against 86k cycles for 8192 positions).  Batches fill the SMs anyway.
+    if (a.n_kv * a.group * n_tok <= 148) smem = std::max<size_t>(smem, 116 * 1024);
     cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_values_kernel<HD, KV4>), smem);
     if (e != cudaSuccess) return e;
     const uint32_t nblk = (a.ctx_cap + SCORE_TILE - 1) / SCORE_TILE;
@@ -460,9 +489,10 @@ static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl
 }
 
 size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits) {
-    const size_t ring = 128 + (size_t)VAL_NST * VAL_TILE * (kv_bits == 4 ? head_dim / 2 : head_dim);
+    const size_t stage = (size_t)VAL_TILE * (kv_bits == 4 ? head_dim / 2 : head_dim);
+    const size_t fixed = 128 + (stage > 16 * 1024 ? 2 : 4) * stage + (size_t)VAL_TBUF * VAL_TILE * head_dim;
     const size_t nw = kv_bits == 4 ? head_dim / 64 : 1;
-    return (200 * 1024 - ring) / (4 * nw);
+    return (200 * 1024 - fixed) / (4 * nw) - 16;
 }
 
 cudaError_t launch_attention_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok) {

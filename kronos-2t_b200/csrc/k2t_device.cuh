@@ -68,7 +68,11 @@ __device__ __forceinline__ void pdl_wait() {
     }
 }
 #endif
+#ifndef K2T_TRIGGER_AT_EXIT
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#else
+__device__ __forceinline__ void pdl_trigger() {}       // measurement build: dependents launch when the CTAs exit
+#endif
 
 // Launches `kernel` on `stream`, optionally as a programmatic dependent of the previous kernel in the stream.
 template <typename... KArgs, typename... Args>

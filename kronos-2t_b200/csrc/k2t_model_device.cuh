@@ -253,56 +253,102 @@ __device__ __forceinline__ void transpose4x4_bytes(const uint32_t w[4], uint32_t
 template <int HD, bool KV4>
 __device__ __forceinline__ void value_rows_transpose(uint32_t rows, uint32_t tile, uint32_t stride, uint32_t n_blk, uint32_t unit0,
                                                      uint32_t unit_step, uint32_t lane, uint32_t chunk0 = 0) {
-    constexpr uint32_t ROW = KV4 ? HD / 2 : HD, LPB = ROW / 4, BPU = 32 / LPB;
+    constexpr uint32_t ROW = KV4 ? HD / 2 : HD, LPB = ROW / 4, BPU = 32 / LPB, NOUT = KV4 ? 8 : 4;
     const uint32_t col = lane % LPB;
-    for (uint32_t u = unit0; u * BPU < n_blk; u += unit_step) {
-        const uint32_t b = u * BPU + lane / LPB;
-        if (b >= n_blk) continue;
-        uint32_t w[16];
+    // the NOUT tile rows this lane writes (dimension, swizzle) do not change from block to block
+    uint32_t out_row[NOUT], out_swz[NOUT];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = lds_u32(rows + (16 * b + j) * ROW + 4 * col);
-        const uint32_t chunk = b + chunk0;
-        if (KV4) {
-            // bytes 4 col .. 4 col + 3 of a row: low nibbles = dimensions D .. D + 3, high nibbles = D + 16 .. D + 19
+    for (uint32_t k = 0; k < NOUT; ++k) {
+        uint32_t d;
+        if (KV4) {      // bytes 4 col .. 4 col + 3 of a row: low nibbles = dimensions D .. D + 3, high nibbles = D + 16 .. D + 19
             const uint32_t B0 = 4 * col, D = (B0 / 32) * 64 + ((B0 / 16) % 2) * 32 + B0 % 16;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t t[4][4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint32_t x[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) x[j] = half ? (w[4 * q + j] >> 2) & 0x3C3C3C3Cu : (w[4 * q + j] << 2) & 0x3C3C3C3Cu;
-                    uint32_t r[4];
-                    transpose4x4_bytes(x, r);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) t[i][q] = r[i];
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t d = D + 16 * half + i;
-                    sts_u32x4(tile + d * stride + (((chunk & ~7u) | ((chunk ^ vt_swz(d)) & 7u)) << 4), t[i][0], t[i][1], t[i][2], t[i][3]);
-                }
-            }
+            d = D + 16 * (k / 4) + k % 4;
         } else {
+            d = 4 * col + k;
+        }
+        out_row[k] = tile + d * stride;
+        out_swz[k] = vt_swz(d);
+    }
+    // two units per round, the loads of both ahead of the byte shuffles of either: one unit alone is a chain of latencies
+    // (sixteen loads, three levels of prmt, four stores: about 330 cycles for 90 instructions)
+    auto load = [&](uint32_t b, uint32_t (&w)[16]) {
+        const uint32_t src = rows + 16 * b * ROW + 4 * col;
+#define K2T_LD_ROW(j) asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(w[j]) : "r"(src), "n"((j) * ROW))
+        K2T_LD_ROW(0); K2T_LD_ROW(1); K2T_LD_ROW(2); K2T_LD_ROW(3); K2T_LD_ROW(4); K2T_LD_ROW(5); K2T_LD_ROW(6); K2T_LD_ROW(7);
+        K2T_LD_ROW(8); K2T_LD_ROW(9); K2T_LD_ROW(10); K2T_LD_ROW(11); K2T_LD_ROW(12); K2T_LD_ROW(13); K2T_LD_ROW(14); K2T_LD_ROW(15);
+#undef K2T_LD_ROW
+    };
+    auto emit = [&](uint32_t b, const uint32_t (&w)[16]) {
+        const uint32_t chunk = b + chunk0, hi = (chunk & ~7u) << 4, lo = chunk & 7u;
+#pragma unroll
+        for (uint32_t half = 0; half < (KV4 ? 2u : 1u); ++half) {
             uint32_t t[4][4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t x[4], r[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) x[j] = w[4 * q + j] ^ 0x80808080u;
+                for (int j = 0; j < 4; ++j)
+                    x[j] = KV4 ? (half ? (w[4 * q + j] >> 2) & 0x3C3C3C3Cu : (w[4 * q + j] << 2) & 0x3C3C3C3Cu) : w[4 * q + j] ^ 0x80808080u;
                 transpose4x4_bytes(x, r);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) t[i][q] = r[i];
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t d = 4 * col + i;
-                sts_u32x4(tile + d * stride + (((chunk & ~7u) | ((chunk ^ vt_swz(d)) & 7u)) << 4), t[i][0], t[i][1], t[i][2], t[i][3]);
-            }
+            for (int i = 0; i < 4; ++i)
+                sts_u32x4(out_row[4 * half + i] + hi + ((lo ^ out_swz[4 * half + i]) << 4), t[i][0], t[i][1], t[i][2], t[i][3]);
         }
+    };
+    for (uint32_t u = unit0; u * BPU < n_blk; u += 2 * unit_step) {
+        const uint32_t b0 = u * BPU + lane / LPB, b1 = (u + unit_step) * BPU + lane / LPB;
+        const bool on0 = b0 < n_blk, on1 = b1 < n_blk;
+        uint32_t w0[16], w1[16];
+        if (on0) load(b0, w0);
+        if (on1) load(b1, w1);
+        if (on0) emit(b0, w0);
+        if (on1) emit(b1, w1);
     }
 }
+// The softmax denominator's body (softmax_unnorm_neon's four-lane accumulator): lane i < 4 of the calling warp adds the
+// terms 4k + i, k ascending - four chains that share one instruction stream, sixty-four positions requested ahead, so
+// the loop runs at the latency of a dependent add - then (a0 + a1) + (a2 + a3).  `sa` = shared address of the terms,
+// n4 = their count (a multiple of 4).  The result is valid in lane 0.
+__device__ __forceinline__ float softmax_body_sum(uint32_t sa, uint32_t n4, uint32_t lane) {
+    float acc = 0.0f;
+    if (lane < 4) {
+        const uint32_t base = sa + 4 * lane;
+        uint32_t t = 0;
+        float A[16], B[16];
+#define K2T_LD_TERM(u) asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v[u]) : "r"(at), "n"(16 * (u)))
+        auto load16 = [&](float (&v)[16], uint32_t t0) {
+            const uint32_t at = base + 4 * t0;
+            K2T_LD_TERM(0); K2T_LD_TERM(1); K2T_LD_TERM(2); K2T_LD_TERM(3); K2T_LD_TERM(4); K2T_LD_TERM(5); K2T_LD_TERM(6); K2T_LD_TERM(7);
+            K2T_LD_TERM(8); K2T_LD_TERM(9); K2T_LD_TERM(10); K2T_LD_TERM(11); K2T_LD_TERM(12); K2T_LD_TERM(13); K2T_LD_TERM(14); K2T_LD_TERM(15);
+        };
+#undef K2T_LD_TERM
+        auto add16 = [&](const float (&v)[16]) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, v[u]);
+        };
+        if (n4 >= 64) {
+            load16(A, 0);
+            for (;;) {          // A holds positions t .. t + 63
+                if (t + 128 > n4) { add16(A); t += 64; break; }
+                load16(B, t + 64); add16(A); t += 64;
+                if (t + 128 > n4) { add16(B); t += 64; break; }
+                load16(A, t + 64); add16(B); t += 64;
+            }
+        }
+        for (; t < n4; t += 4) {
+            float v;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(base + 4 * t));
+            acc = __fadd_rn(acc, v);
+        }
+    }
+    acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 1));          // lane 0: a0 + a1, lane 2: a2 + a3
+    acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 2));
+    return acc;
+}
+
 // Sixteen chain steps of dimension d from one 16-byte chunk of its tile row: o = fma(value, weight, o), positions ascending.
 // `n` < 16 stops after n steps (selects, no branches).  KV4: `cbfa` = shared address of the 16 fp32 centroids.
 template <bool KV4>
@@ -331,7 +377,12 @@ __device__ __forceinline__ float value_chain16(float o, const uint4 x, const flo
 #define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); if (K2T_CUT_AT == (i)) return; } while (0)
 
 template <int HD, bool KV4, bool STAGED>
-__device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, bool wait_here) {
+__device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, int pdl_mode) {
+    // pdl_mode: 0 = not a programmatic dependent (whole-token kernel), 1 = the caller has waited for the predecessor,
+    // 2 = the wait is in here, after the prefetch of everything older launches wrote.  In modes 1 and 2 the successor
+    // is released before the value chain, not at the start: CTAs that sit on an SM waiting for their predecessor slow
+    // the warps running there (this kernel's phases took a third longer with the next projection's CTAs resident from
+    // the start), and the successor needs only a microsecond or two of lead for its first weight stages.
     constexpr int QW = HD / 4, NB = HD / 64;
     constexpr uint32_t NT = ATTN_THREADS, NW = ATTN_THREADS / 32;
     constexpr uint32_t ROW = KV4 ? HD / 2 : HD;            // bytes of one cached key / value row
@@ -409,7 +460,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     // Everything above reads what earlier steps (or a launch at least two back) wrote; the projection output below is the
     // predecessor's.
-    if (wait_here) { pdl_wait(); pdl_trigger(); }
+    if (pdl_mode == 2) pdl_wait();
     ATTN_MARK(1);
     if (warp < 3) {
 #pragma unroll
@@ -585,29 +636,11 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     __syncthreads();
     ATTN_MARK(5);
-    // thread 0 sums the body (four accumulators = four independent chains, 16-byte loads four groups ahead) while three
-    // other threads evaluate the remainder's exps and warps 1.. transpose the cached value rows for the chain below
+    // warp 0 sums the body while at most three other threads evaluate the remainder's exps and warps 1.. transpose the
+    // cached value rows for the chain below
     float acc = 0.0f;
     bool copy_failed = false;
-    if (tid == 0) {
-        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(s.sc);
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-        uint32_t t = 0;
-        for (; t + 16 <= n4; t += 16) {
-            float4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = lds_f32x4(sa + 4 * t + 16 * j);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                a0 = __fadd_rn(a0, v[j].x); a1 = __fadd_rn(a1, v[j].y); a2 = __fadd_rn(a2, v[j].z); a3 = __fadd_rn(a3, v[j].w);
-            }
-        }
-        for (; t < n4; t += 4) {
-            const float4 v = lds_f32x4(sa + 4 * t);
-            a0 = __fadd_rn(a0, v.x); a1 = __fadd_rn(a1, v.y); a2 = __fadd_rn(a2, v.z); a3 = __fadd_rn(a3, v.w);
-        }
-        acc = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
-    }
+    if (warp == 0) acc = softmax_body_sum((uint32_t)__cvta_generic_to_shared(s.sc), n4, lane);
     ATTN_MARK(6);
     {
         // the remainder's exps (at most three positions; thread 0 gets to its own, if any, after the sum)
@@ -653,6 +686,7 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
     }
     // ---- values: thread i < HD = dimension i runs the position-ascending chain over the staged rows
     __syncthreads();                       // weights complete
+    if (pdl_mode != 0) pdl_trigger();
     ATTN_MARK(9);
     float o = 0.0f;
     if (pos > 0 && !STAGED) {              // bounded wait for the bulk copy (the transposers have waited already where there is a tile)
@@ -807,17 +841,17 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
 
 // runtime dispatch on head_dim / cache format
 template <bool STAGED>
-__device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, bool wait_here = false) {
+__device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, int pdl_mode = 0) {
 #ifdef K2T_PROBE_HD
-    attention_head_cta<K2T_PROBE_HD, K2T_PROBE_KV4 != 0, STAGED>(A, qh, pos, s, wait_here);
+    attention_head_cta<K2T_PROBE_HD, K2T_PROBE_KV4 != 0, STAGED>(A, qh, pos, s, pdl_mode);
     return;
 #endif
     if (A.kv_bits == 4) {
-        if (A.head_dim == 64) attention_head_cta<64, true, STAGED>(A, qh, pos, s, wait_here);
-        else attention_head_cta<128, true, STAGED>(A, qh, pos, s, wait_here);
+        if (A.head_dim == 64) attention_head_cta<64, true, STAGED>(A, qh, pos, s, pdl_mode);
+        else attention_head_cta<128, true, STAGED>(A, qh, pos, s, pdl_mode);
     } else {
-        if (A.head_dim == 64) attention_head_cta<64, false, STAGED>(A, qh, pos, s, wait_here);
-        else attention_head_cta<128, false, STAGED>(A, qh, pos, s, wait_here);
+        if (A.head_dim == 64) attention_head_cta<64, false, STAGED>(A, qh, pos, s, pdl_mode);
+        else attention_head_cta<128, false, STAGED>(A, qh, pos, s, pdl_mode);
     }
 }
 

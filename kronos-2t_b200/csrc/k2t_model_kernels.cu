@@ -752,13 +752,13 @@ __global__ void __launch_bounds__(FINISH_THREADS) attn_finish_kernel(const AttnA
 __global__ void __launch_bounds__(ATTN_THREADS) attn_fused_kernel(const FusedAttnArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const bool early = a.early != 0;
-    if (!early) { pdl_wait(); pdl_trigger(); }
+    if (!early) pdl_wait();
     const uint32_t pos = __ldcg(a.pos) + a.pos_offset;
     if (pos + 1 > ATTN_EXACT_CTX) {
-        if (early) { pdl_wait(); pdl_trigger(); }       // every kernel of the chain waits: completion of this one implies its predecessors'
+        if (early) pdl_wait();          // every kernel of the chain waits: completion of this one implies its predecessors'
         return;
     }
-    attention_head_dispatch<true>(a, blockIdx.x, pos, attn_carve(smem, true), early);
+    attention_head_dispatch<true>(a, blockIdx.x, pos, attn_carve(smem, true), early ? 2 : 1);
 }
 
 // ------------------------------------------------------------------------------------------------
