@@ -291,7 +291,8 @@ int32_t kronos_cuda_engine_read_hidden(KronosCudaEngine *engine, float *hidden);
  * With tied embeddings every rank also needs the whole lm_head for the token lookup: set_embedding_matrix uploads it. */
 int32_t kronos_cuda_engine_tp_handle(KronosCudaEngine *engine, uint8_t handle[64]);
 int32_t kronos_cuda_engine_tp_attach(KronosCudaEngine *engine, const uint8_t *handles /* [tp_size][64] */, size_t n_handles);
-int32_t kronos_cuda_engine_set_embedding_matrix(KronosCudaEngine *engine, const KronosCudaMatrixDesc *whole_lm_head);
+/* Also the route for an untied embedding table stored as an NF4 matrix (embed_nf4, real_llm.rs:1553, 8084-8087). */
+int32_t kronos_cuda_engine_set_embedding_matrix(KronosCudaEngine *engine, const KronosCudaMatrixDesc *table);
 /* tp_attach for a host that drives every rank from ONE process (one engine per GPU, the single-caller contract of
  * MetalLlamaEngine kept): `engines` = the tp_size (or ep_size) engines in rank order, this engine's own entry included;
  * peer access between their devices is enabled as needed.  Every engine of the group makes this call.
@@ -368,12 +369,17 @@ int32_t kronos_cuda_k2tm_layer(const KronosCudaK2tm *shard, size_t moe_slot_idx,
 int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *file, const float **final_norm, size_t *final_norm_len,
                               KronosCudaMatrixDesc *lm_head, const uint16_t **embed_bf16, size_t *embed_bf16_len,
                               const float **embed_f32, size_t *embed_f32_len);
-/* Writes a container the reference's load_bipolar reads: the version follows save_bipolar's rule (6 with q/k norms, 3 with
- * a qkv bias or a bf16 embedding table, 2 with NF matrices, else 1).  hidden / qkv_rows / head_dim give the lengths of the
- * per-layer vectors. */
+/* The untied embedding table quantized to NF4 (embed_nf4, real_llm.rs:1553; containers of version >= 4): 1 and the matrix
+ * when the file holds one, 0 when it does not.  Hand it to kronos_cuda_engine_set_embedding_matrix (embed_bf16 = NULL at
+ * engine creation): the engine then embeds a token as embed_token_into does (8084-8087), row decode + inverse rotation. */
+int32_t kronos_cuda_k2tb_embed_nf4(const KronosCudaK2tb *file, KronosCudaMatrixDesc *table);
+/* Writes a container the reference's load_bipolar reads: the version follows save_bipolar's rule (6 with q/k norms, 4 with
+ * an NF4 embedding table, 3 with a qkv bias or a bf16 embedding table, 2 with NF matrices, else 1).  hidden / qkv_rows /
+ * head_dim give the lengths of the per-layer vectors; embed_nf4 may be NULL. */
 int32_t kronos_cuda_k2tb_save(const char *path, const uint64_t mode_words[6], const KronosCudaLayerDesc *layers, size_t n_layers,
                               size_t hidden, size_t qkv_rows, size_t head_dim, const float *final_norm,
-                              const KronosCudaMatrixDesc *lm_head, const uint16_t *embed_bf16, size_t embed_bf16_len);
+                              const KronosCudaMatrixDesc *lm_head, const uint16_t *embed_bf16, size_t embed_bf16_len,
+                              const KronosCudaMatrixDesc *embed_nf4);
 
 /* ---- no-allocation variant ------------------------------------------------------------------- */
 

@@ -286,6 +286,13 @@ int32_t kronos_cuda_k2tb_head(const KronosCudaK2tb *f, const float **final_norm,
     return 0;
 }
 
+int32_t kronos_cuda_k2tb_embed_nf4(const KronosCudaK2tb *f, KronosCudaMatrixDesc *table) {
+    if (!f) return -1;
+    if (!f->has_embed_nf4) return 0;
+    if (table) *table = f->embed_nf4.d;
+    return 1;
+}
+
 struct KronosCudaK2tm {
     void *map = nullptr;
     size_t len = 0;
@@ -339,8 +346,9 @@ int32_t kronos_cuda_k2tm_layer(const KronosCudaK2tm *h, size_t moe_slot_idx, con
 
 int32_t kronos_cuda_k2tb_save(const char *path, const uint64_t mode_words[6], const KronosCudaLayerDesc *layers, size_t n_layers,
                               size_t hidden, size_t qkv_rows, size_t head_dim, const float *final_norm, const KronosCudaMatrixDesc *lm_head,
-                              const uint16_t *embed_bf16, size_t embed_bf16_len) {
+                              const uint16_t *embed_bf16, size_t embed_bf16_len, const KronosCudaMatrixDesc *embed_nf4) {
     g_k2tb_error.clear();
+    if (embed_nf4 && (embed_nf4->kind != KRONOS_CUDA_MATRIX_NF || embed_nf4->bits != 4)) { g_k2tb_error = "k2tb_save: the embedding table must be an NF4 matrix"; return -1; }
     if (!path || !mode_words || !layers || !n_layers || !final_norm || !lm_head) { g_k2tb_error = "k2tb_save: NULL argument"; return -1; }
     bool any_nf = lm_head->kind == KRONOS_CUDA_MATRIX_NF, any_bias = false, any_qk = false;
     for (size_t l = 0; l < n_layers; ++l) {
@@ -351,11 +359,11 @@ int32_t kronos_cuda_k2tb_save(const char *path, const uint64_t mode_words[6], co
         any_qk |= d.q_norm != nullptr || d.k_norm != nullptr;
     }
     // version choice of save_bipolar (real_llm.rs:3831-3846)
-    const int version = any_qk ? 6 : (any_bias || embed_bf16_len) ? 3 : any_nf ? 2 : 1;
+    const int version = any_qk ? 6 : embed_nf4 ? 4 : (any_bias || embed_bf16_len) ? 3 : any_nf ? 2 : 1;
     FILE *fp = std::fopen(path, "wb");
     if (!fp) { g_k2tb_error = std::string("k2tb_save: cannot create ") + path; return -1; }
     Writer w{fp};
-    const char *magic = version == 6 ? "K2TKRONOS6\n" : version == 3 ? "K2TKRONOS3\n" : version == 2 ? "K2TKRONOS2\n" : "K2TBIPOLAR1\n";
+    const char *magic = version == 6 ? "K2TKRONOS6\n" : version == 4 ? "K2TKRONOS4\n" : version == 3 ? "K2TKRONOS3\n" : version == 2 ? "K2TKRONOS2\n" : "K2TBIPOLAR1\n";
     w.raw(magic, std::strlen(magic));
     for (int i = 0; i < 6; ++i) w.u64(mode_words[i]);
     w.u64(n_layers);
@@ -373,7 +381,10 @@ int32_t kronos_cuda_k2tb_save(const char *path, const uint64_t mode_words[6], co
         ok = w.matrix(*lm_head, version >= 2, err);
         w.f32s(nullptr, 0);                                      // embed_f32 (empty: tied or bf16 table)
         if (version >= 3) { w.u64(embed_bf16 ? embed_bf16_len : 0); if (embed_bf16) w.raw(embed_bf16, embed_bf16_len * 2); }
-        if (version >= 4) w.u64(0);                              // no NF4-quantized embedding table
+        if (version >= 4) {                                      // the NF4-quantized untied embedding table, if any
+            w.u64(embed_nf4 ? 1 : 0);
+            if (embed_nf4) ok = ok && w.matrix(*embed_nf4, true, err);
+        }
     }
     const bool closed = std::fclose(fp) == 0;
     if (!ok || !w.ok || !closed) { g_k2tb_error = "k2tb_save: " + (err.empty() ? std::string("write failed") : err); return -1; }

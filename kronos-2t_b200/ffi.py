@@ -118,8 +118,9 @@ def load_library():
     sig("kronos_cuda_k2tb_layer", i32, vp, sz, C.POINTER(LayerDesc), C.POINTER(sz))
     sig("kronos_cuda_k2tb_head", i32, vp, C.POINTER(vp), C.POINTER(sz), C.POINTER(MatrixDesc), C.POINTER(vp), C.POINTER(sz),
         C.POINTER(vp), C.POINTER(sz))
+    sig("kronos_cuda_k2tb_embed_nf4", i32, vp, C.POINTER(MatrixDesc))
     sig("kronos_cuda_k2tb_save", i32, C.c_char_p, C.POINTER(u64 * 6), C.POINTER(LayerDesc), sz, sz, sz, sz, vp,
-        C.POINTER(MatrixDesc), vp, sz)
+        C.POINTER(MatrixDesc), vp, sz, C.POINTER(MatrixDesc))
     sig("kronos_cuda_engine_decode_trace", sz, vp, vp, sz)
     sig("kronos_cuda_engine_profile_step", C.c_int64, vp, u32, sz, u32, C.c_char_p, sz)
     sig("kronos_cuda_engine_debug_words", sz, vp, vp, sz)
@@ -565,6 +566,9 @@ def k2tb_load(path, cfg, rope):
             embed = np.ctypeslib.as_array(C.cast(emb, C.POINTER(C.c_uint16)), shape=(embl.value,)).copy()
         spec = dict(cfg=dict(cfg, layers=nl.value), layers=layers, final_norm=_f32(fn, fnl.value), lm_head=_HostMatrix(head), rope=rope,
                     embed_bf16=embed)
+        table = MatrixDesc()
+        if L.kronos_cuda_k2tb_embed_nf4(h, C.byref(table)) == 1:      # the untied table as an NF4 matrix: the engine embeds from it
+            spec["embed_matrix"] = _HostMatrix(table)
         return spec, ver.value, [int(x) for x in mode]
     finally:
         L.kronos_cuda_k2tb_close(h)
@@ -668,7 +672,8 @@ def k2tb_save(path, spec, mode_words):
     emb = None if spec.get("embed_bf16") is None else _np(spec["embed_bf16"], np.uint16).reshape(-1)
     words = (C.c_uint64 * 6)(*mode_words)
     qkv_rows = (c["n_q"] + 2 * c["n_kv"]) * c["head_dim"]
+    table = None if spec.get("embed_matrix") is None else desc_of(spec["embed_matrix"])
     rc = L.kronos_cuda_k2tb_save(os.fsencode(path), C.byref(words), layers, len(spec["layers"]), c["hidden"], qkv_rows, c["head_dim"], _p(fn),
-                                 C.byref(head), _p(emb), 0 if emb is None else emb.size)
+                                 C.byref(head), _p(emb), 0 if emb is None else emb.size, None if table is None else C.byref(table))
     if rc != 0:
         raise KronosCudaError(L.kronos_cuda_k2tb_last_error().decode())

@@ -98,6 +98,8 @@ struct K2oModel {
     std::vector<float> final_norm;
     Mat lm_head;
     std::vector<uint16_t> embed_bf16; // empty = tied (row of lm_head, inverse rotated)
+    Mat embed_nf;                     // untied table quantized to NF4 (embed_nf4, real_llm.rs:1553): its rows, inverse rotated
+    bool has_embed_nf = false;
     // int8 Hadamard KV cache (QuantizedKvCache, real_llm.rs:1093-1412): [layer][kv head][pos][hd] + scale per (head,pos)
     std::vector<int8_t> k_q8, v_q8;
     std::vector<float> k_sc, v_sc;
@@ -656,8 +658,18 @@ void k2o_model_embed(const K2oModel *m, uint32_t token, float *out) {
         for (size_t i = 0; i < h; ++i) out[i] = k2o_bf16_to_f32(m->embed_bf16[(size_t)token * h + i]);
         return;
     }
-    m->lm_head.dequant_row(token, out);
+    if (m->has_embed_nf) m->embed_nf.dequant_row(token, out);
+    else m->lm_head.dequant_row(token, out);
     k2o_ifwht64(out, h, 0);
+}
+
+// the NF4-compressed untied table (compress_untied_embeddings_nf4, real_llm.rs:1825-1844): replaces the bf16 rows
+int k2o_model_set_embedding_matrix(K2oModel *m, const K2oMatrixDesc *table) {
+    if (!m || !table || !load_mat(m->embed_nf, table)) return -1;
+    if (m->embed_nf.cols != m->cfg.hidden) return -1;
+    m->has_embed_nf = true;
+    m->embed_bf16.clear();
+    return 0;
 }
 
 const float *k2o_model_tap_hidden(const K2oModel *m) { return m->tap_hidden.data(); }

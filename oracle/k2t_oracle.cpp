@@ -830,6 +830,56 @@ void k2o_nf_pack(const uint8_t *flat_idx, const uint16_t *sc, size_t rows, size_
                     [&](size_t stripe, size_t c, uint8_t *dst) { nf_pack_chunk(flat_idx, rows, cols, bits, stripe, c, dst); });
 }
 
+// NfSdotMatrix::build_nf4_from_bf16_getter (simd_lut.rs:5262-5495): the untied bf16 embedding table as 4-bit rows in the
+// rotated domain, default NF4 codebook.  Per row and scale group: scale0 = max|v| / top, indices at scale0, the least-squares
+// scale of those indices (bf16), indices again at that scale.  Lanes past the last row hold index 8 and scale 0.
+void k2o_nf4_embed_from_bf16(const uint16_t *bf16, size_t rows, size_t cols, size_t sgc, size_t threads,
+                             uint8_t *pair_stream, uint8_t *tail_stream) {
+    if (sgc == 0) sgc = 1;
+    const size_t nc = cols / BLK, nsg = (nc + sgc - 1) / sgc, rows_pad = (rows + STRIPE - 1) / STRIPE * STRIPE;
+    int8_t cb32[32];
+    k2o_nf_expand_codebook32(4, K2O_NF4_DEFAULT, cb32);
+    float pos_th[7];
+    for (size_t m = 0; m < 7; ++m) pos_th[m] = 0.5f * ((float)cb32[8 + m] + (float)cb32[9 + m]);
+    const float cb_top = std::max((float)cb32[15], 1.0f);
+    auto quant4 = [&](float w, float inv_delta) -> uint8_t {           // the reference's fixed comparison tree (5277-5293)
+        const float aw = std::fabs(w) * inv_delta;
+        size_t mag;
+        if (aw < pos_th[3]) mag = aw < pos_th[1] ? (aw >= pos_th[0] ? 1 : 0) : 2 + (aw >= pos_th[2] ? 1 : 0);
+        else if (aw < pos_th[5]) mag = 4 + (aw >= pos_th[4] ? 1 : 0);
+        else mag = 6 + (aw >= pos_th[6] ? 1 : 0);
+        return (uint8_t)(w >= 0.0f ? 8 + mag : 7 - mag);
+    };
+    std::vector<uint8_t> idx(rows_pad * cols, (uint8_t)8);
+    std::vector<uint16_t> sc(k2o_nf_scale_count(rows_pad, cols, sgc), (uint16_t)0);
+    parallel_ranges(rows, threads, [&](size_t lo, size_t hi) {
+        std::vector<float> buf(cols);
+        for (size_t r = lo; r < hi; ++r) {
+            for (size_t c = 0; c < cols; ++c) buf[c] = from_bf16(bf16[r * cols + c]);
+            k2o_fwht64(buf.data(), cols, 0);
+            for (size_t sg = 0; sg < nsg; ++sg) {
+                const size_t col0 = sg * sgc * BLK, col1 = std::min(col0 + sgc * BLK, cols);
+                const size_t sc_i = ((r / STRIPE) * nsg + sg) * STRIPE + r % STRIPE;
+                float max_abs = 0.0f;
+                for (size_t c = col0; c < col1; ++c) if (std::fabs(buf[c]) > max_abs) max_abs = std::fabs(buf[c]);
+                if (max_abs <= 1e-12f) { sc[sc_i] = 0; continue; }      // indices stay 8
+                const float inv0 = cb_top / max_abs;
+                float dot_wq = 0.0f, dot_qq = 0.0f;
+                for (size_t c = col0; c < col1; ++c) {
+                    const float qf = (float)cb32[quant4(buf[c], inv0)];
+                    dot_wq += buf[c] * qf;
+                    dot_qq += qf * qf;
+                }
+                const uint16_t d16 = k2o_f32_to_bf16(dot_qq > 0.0f ? std::max(dot_wq / dot_qq, 0.0f) : max_abs / cb_top);
+                const float delta = from_bf16(d16), inv = delta > 1e-12f ? 1.0f / delta : 0.0f;
+                for (size_t c = col0; c < col1; ++c) idx[r * cols + c] = quant4(buf[c], inv);
+                sc[sc_i] = d16;
+            }
+        }
+    });
+    k2o_nf_pack(idx.data(), sc.data(), rows_pad, cols, 4, sgc, pair_stream, tail_stream);
+}
+
 void k2o_e8q2_pack(const uint8_t *tpl, const uint8_t *sgn, const uint16_t *sc, size_t rows, size_t cols,
                    size_t sgc, uint8_t *pair_stream, uint8_t *tail_stream) {
     nf_pack_streams(sc, rows, cols, 2, sgc, pair_stream, tail_stream,

@@ -111,6 +111,9 @@ float k2o_nf_fit_codebook(const float *weights, size_t rows, size_t cols, size_t
                           int8_t codebook[16]);
 /* compile_hadamard_gptq_nf with hessian=None, bits 3..5 (compiler.rs:1530-1860):
  * writes row-major indices and stripe-major bf16 scales [stripes][nsg][16]. */
+/* NfSdotMatrix::from_bf16_u16_embeddings_nf4 (simd_lut.rs:5230-5495): bf16 table [rows][cols] -> NF4 streams (default codebook) */
+void k2o_nf4_embed_from_bf16(const uint16_t *bf16, size_t rows, size_t cols, size_t sgc, size_t threads,
+                             uint8_t *pair_stream, uint8_t *tail_stream);
 void k2o_nf_quantize_rtn(const float *weights, size_t rows, size_t cols, size_t bits, size_t sgc,
                          size_t threads, int8_t codebook[16], uint8_t *flat_idx, uint16_t *bf16_scales);
 /* NfSdotMatrix::from_indices (simd_lut.rs:4850-5023). */
@@ -193,6 +196,7 @@ uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts,
 size_t k2o_nf_expert_layout(size_t d_model, size_t d_ff, size_t bits, size_t sgc, size_t *gu_pair_off, size_t *gu_pair_bytes,
                             size_t *dn_pair_off, size_t *dn_pair_bytes);
 int k2o_model_set_head(K2oModel *m, const float *final_norm, const K2oMatrixDesc *lm_head, const uint16_t *embed_bf16);
+int k2o_model_set_embedding_matrix(K2oModel *m, const K2oMatrixDesc *table);   /* embed_nf4: NF rows instead of bf16 */
 void k2o_model_reset(K2oModel *m);
 size_t k2o_model_pos(const K2oModel *m);
 void k2o_model_set_pos(K2oModel *m, size_t pos);

@@ -77,6 +77,7 @@ def _declare(L):
     sig("k2o_nf_scale_count", _sz, _sz, _sz, _sz)
     sig("k2o_nf_fit_codebook", _f32, _p, _sz, _sz, _sz, _sz, _p)
     sig("k2o_nf_quantize_rtn", None, _p, _sz, _sz, _sz, _sz, _sz, _p, _p, _p)
+    sig("k2o_nf4_embed_from_bf16", None, _p, _sz, _sz, _sz, _sz, _p, _p)
     sig("k2o_nf_pack", None, _p, _p, _sz, _sz, _sz, _sz, _p, _p)
     sig("k2o_e8q2_pack", None, _p, _p, _p, _sz, _sz, _sz, _p, _p)
     sig("k2o_nf_gate_up_interleave", None, _p, _sz, _sz, _sz, _sz, _p)
@@ -319,6 +320,18 @@ def nf_quantize_rtn(w, bits, sgc, threads=8, return_indices=False):
     return (m, idx, sc) if return_indices else m
 
 
+def nf4_embed_from_bf16(table_bf16, sgc=2, threads=8):
+    """NfSdotMatrix::from_bf16_u16_embeddings_nf4: bf16 table [rows, cols] (uint16) -> Nf matrix, default NF4 codebook."""
+    t = _c(table_bf16, np.uint16)
+    rows, cols = t.shape
+    pair, tail = _nf_alloc(rows, cols, 4, sgc)
+    lib().k2o_nf4_embed_from_bf16(_ptr(t), rows, cols, sgc, threads, _ptr(pair), _ptr(tail))
+    pair = pair[: lib().k2o_nf_pair_stream_bytes(rows, cols, 4, sgc)]
+    tail = tail[: lib().k2o_nf_tail_stream_bytes(rows, cols, 4, sgc)]
+    cb = np.array([-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127], np.int8)
+    return Nf(rows, cols, 4, sgc, cb, pair, tail)
+
+
 def e8q2_pack(tpl, sgn, scales, sgc):
     tpl, sgn = _c(tpl, np.uint8), _c(sgn, np.uint8)
     rows, cols = tpl.shape[0], tpl.shape[1] * 8
@@ -406,6 +419,7 @@ def _declare_model(L):
     L.k2o_model_free.restype, L.k2o_model_free.argtypes = None, [P]
     L.k2o_model_set_layer.restype, L.k2o_model_set_layer.argtypes = C.c_int, [P, C.c_uint32, P, P, P, P, P, D, D, D, D]
     L.k2o_model_set_head.restype, L.k2o_model_set_head.argtypes = C.c_int, [P, P, D, P]
+    L.k2o_model_set_embedding_matrix.restype, L.k2o_model_set_embedding_matrix.argtypes = C.c_int, [P, D]
     L.k2o_model_reset.restype, L.k2o_model_reset.argtypes = None, [P]
     L.k2o_model_pos.restype, L.k2o_model_pos.argtypes = C.c_size_t, [P]
     L.k2o_model_set_pos.restype, L.k2o_model_set_pos.argtypes = None, [P, C.c_size_t]
@@ -577,6 +591,9 @@ class Model:
         d = desc_of(spec["lm_head"])
         fn = _c(spec["final_norm"], np.float32)
         assert L.k2o_model_set_head(self.h, _ptr(fn), C.byref(d), _ptr(emb)) == 0
+        if spec.get("embed_matrix") is not None:       # the untied table compressed to NF4 (or the whole tied lm_head of a sharded model)
+            self._embed_desc = desc_of(spec["embed_matrix"])
+            assert L.k2o_model_set_embedding_matrix(self.h, C.byref(self._embed_desc)) == 0
         if int(c.get("kv_window", 0)) > 0:
             self.set_kv_window(int(c.get("kv_bits", 8)), int(c["kv_window"]), int(c.get("kv_sinks", 0)))
 

@@ -43,7 +43,7 @@ def build_moe(oracle, seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk
                 expert_bytes=lay["expert_bytes"], scoring=scoring)
 
 
-def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=True, head_mode=None, modes=None, moe=None):
+def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=True, head_mode=None, modes=None, moe=None, embed_nf4=False):
     """modes: optional dict {qkv, o, gate_up, down, head} overriding `mode` per matrix (e.g. p55454).
     moe: optional dict(layers=[...], n_experts, top_k, d_ff, bits, sgc[, norm_topk, bias]): those layers get a sparse-MoE FFN."""
     c = dict(cfg)
@@ -77,4 +77,7 @@ def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=Tr
     if not tied:
         e = normal(s + 997, (c["vocab"], h), 0.02)
         spec["embed_bf16"] = (e.view(np.uint32) >> 16).astype(np.uint16)     # truncation is fine for synthetic tables
+        if embed_nf4:       # compress_untied_embeddings_nf4 (real_llm.rs:1825-1844): the bf16 rows become an NF4 matrix
+            spec["embed_matrix"] = oracle.nf4_embed_from_bf16(spec["embed_bf16"], 2)
+            spec["embed_bf16"] = None
     return spec

@@ -54,8 +54,8 @@ def parse_independent(raw):
     tail = dict(final_norm=arr(np.float32), lm_head=matrix(), embed_f32=arr(np.float32))
     if version >= 3:
         tail["embed_bf16"] = arr(np.uint16)
-    if version >= 4:
-        assert u64() == 0                   # flag: no NF4-quantized embedding table follows
+    if version >= 4 and u64() == 1:         # flag: an NF4-quantized embedding table follows
+        tail["embed_nf4"] = matrix()
     assert pos == len(raw)
     return version, mode, layers, tail
 
@@ -69,7 +69,8 @@ def same_matrix(m, rec):
 
 
 CASES = [("b4", {}, 1, [0, 4, 0, 0, 0, 0]), ("nf4g128", {}, 2, [5, 4, 2, 0, 0, 0]), ("b5", dict(qkv_bias=True), 3, [0, 5, 0, 0, 0, 0]),
-         ("nf3g128", dict(tied=False), 3, [5, 3, 2, 0, 0, 0]), ("b6", dict(qk_norm=True, qkv_bias=True, tied=False), 6, [0, 6, 0, 0, 0, 0])]
+         ("nf3g128", dict(tied=False), 3, [5, 3, 2, 0, 0, 0]), ("b6", dict(qk_norm=True, qkv_bias=True, tied=False), 6, [0, 6, 0, 0, 0, 0]),
+         ("nf4g128", dict(tied=False, embed_nf4=True), 4, [5, 4, 2, 0, 0, 0]), ("b5", dict(qk_norm=True, tied=False, embed_nf4=True), 6, [0, 5, 0, 0, 0, 0])]
 
 
 @pytest.mark.parametrize("mode,kw,version,words", CASES)
@@ -103,6 +104,10 @@ def test_k2tb_write_read_round_trip(oracle, tmp_path, mode, kw, version, words):
             assert np.array_equal(ma.data, mb.data) and np.array_equal(ma.scales, mb.scales) if ma.kind == 0 else \
                 np.array_equal(ma.pair, mb.pair) and np.array_equal(ma.tail, mb.tail) and np.array_equal(ma.codebook, mb.codebook)
     assert (got["embed_bf16"] is None) == (spec["embed_bf16"] is None)
+    assert ("embed_nf4" in tail) == (spec.get("embed_matrix") is not None) == (got.get("embed_matrix") is not None)
+    if "embed_nf4" in tail:
+        assert same_matrix(spec["embed_matrix"], tail["embed_nf4"])
+        assert np.array_equal(got["embed_matrix"].pair, spec["embed_matrix"].pair) and np.array_equal(got["embed_matrix"].tail, spec["embed_matrix"].tail)
     # the CPU oracle fed from the file reproduces the in-memory model
     a, b = oracle.Model(got), oracle.Model(spec)
     for t in (3, 200, 17):
@@ -134,7 +139,8 @@ def test_k2tb_reader_rejects_malformed_files(oracle, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode,kw,words", [("b4", {}, [0, 4, 0, 0, 0, 0]), ("nf4g128", dict(qk_norm=True, tied=False), [5, 4, 2, 0, 0, 0])])
+@pytest.mark.parametrize("mode,kw,words", [("b4", {}, [0, 4, 0, 0, 0, 0]), ("nf4g128", dict(qk_norm=True, tied=False), [5, 4, 2, 0, 0, 0]),
+                                           ("nf4g128", dict(tied=False, embed_nf4=True), [5, 4, 2, 0, 0, 0])])
 def test_engine_from_k2tb_file(oracle, tmp_path, mode, kw, words):
     """Oracle and device load the same file: identical logits and greedy tokens."""
     import kronos_2t_b200 as k2

@@ -371,3 +371,44 @@ def test_reference_nf_sdot_case_scalar_parity(oracle, rows, bits, sgc):
             f = np.float32(f + np.float32(np.float32(np.float32(dot) * xs[c]) * ws))
         want[r] = f
     assert np.all(np.abs(y - want) <= 1e-4 * np.maximum(np.abs(want), 1.0)), float(np.max(np.abs(y - want)))
+
+
+@pytest.mark.parametrize("rows,cols,sgc", [(37, 128, 1), (64, 192, 2), (96, 576, 2)])
+def test_nf4_embedding_table_quantizer(oracle, rows, cols, sgc):
+    """NfSdotMatrix::from_bf16_u16_embeddings_nf4 (simd_lut.rs:5230-5495) against a numpy restatement of its per-group steps:
+    scale0 = max|v| / 127, indices by the midpoint thresholds, least-squares scale rounded to bf16, indices again; then the
+    decoded rows (row dequantization + inverse rotation, embed_token_into 8084-8087) track the bf16 table."""
+    rng = np.random.Generator(np.random.PCG64(rows + cols))
+    u = (rng.standard_normal((rows, cols)).astype(np.float32) * np.float32(0.05)).view(np.uint32)
+    table = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)                    # bf16, round to nearest even
+    table[3, :64] = 0                                     # an all-zero scale group: indices 8, scale 0
+    to_f32 = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
+    m = oracle.nf4_embed_from_bf16(table, sgc, threads=3)
+    cb = np.array([-127, -96, -75, -58, -44, -31, -18, -6, 6, 18, 31, 44, 58, 75, 96, 127], np.float32)
+    th = 0.5 * (cb[8:15] + cb[9:16])
+    def quant4(v, inv):
+        mag = np.searchsorted(th, np.abs(v) * np.float32(inv), side="right")
+        return np.where(v >= 0, 8 + mag, 7 - mag)
+    worst = 1.0
+    for r in range(rows):
+        x = oracle.fwht64(to_f32(table[r]))
+        want = np.zeros(cols, np.float32)
+        for c0 in range(0, cols, sgc * 64):
+            g = x[c0:c0 + sgc * 64]
+            mx = np.float32(np.max(np.abs(g)))
+            if mx <= 1e-12:
+                continue
+            q = cb[quant4(g, np.float32(127.0) / mx)]
+            wq, qq = np.float32(0), np.float32(0)
+            for v, qf in zip(g, q):                       # sequential fp32 sums, as the reference loop
+                wq = np.float32(wq + v * qf); qq = np.float32(qq + qf * qf)
+            delta = oracle.bf16_to_f32(oracle.f32_to_bf16(np.float32(max(wq / qq, 0.0)) if qq > 0 else mx / np.float32(127.0)))
+            inv = np.float32(1.0) / delta if delta > 1e-12 else np.float32(0)
+            want[c0:c0 + sgc * 64] = cb[quant4(g, inv)] * delta
+        got = oracle.nf_dequant_row(m, r)
+        assert np.array_equal(got, want), r
+        back = oracle.ifwht64(got)
+        src = to_f32(table[r])
+        if np.linalg.norm(src) > 0:
+            worst = min(worst, float(np.dot(back, src) / (np.linalg.norm(back) * np.linalg.norm(src))))
+    assert worst > 0.99
