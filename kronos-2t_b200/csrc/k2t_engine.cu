@@ -418,22 +418,25 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
                 if (!enqueue_attention(e, l, t, T, long_ctx)) return false;
         }
         if (!gemv(e, L.o, e->proj, "gemv o", T)) return false;        // under tp: partial sums, exchanged by the norm kernel that follows
-        if (L.moe) {          // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), token by token
+        if (L.moe) {
+            // SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084) for every token of the batch in five launches
+            // (forward_layer_coalesced_batch, 1090-1352, gives each token the same sums: its routes are visited in ascending
+            // expert order either way): routes of all tokens, then the expert projections over the (token, route) pairs -
+            // slot = token * k + route; two tokens that picked the same expert read its image twice, the second time from L2.
             if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl, c.tp_size > 1)) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
-            for (uint32_t t = 0; t < T; ++t) {
-                RouterArgs ra{};
-                ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm + (size_t)t * h;
-                ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
-                ra.route_ids = L.d_route_ids + t * 32; ra.route_w = L.d_route_w + t * 32; ra.logits = e->router_logits; ra.done = e->router_done;
-                if (!count(e, launch_moe_router(s, ra, e->pdl), "router")) return false;
-                if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q + (size_t)t * h, e->act_s + (size_t)t * (h / 64),
-                                                  e->act_m + (size_t)t * (h / 64), 0, 0, e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert gate_up")) return false;
-                if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
-                if (!count(e, launch_gemv_experts(s, L.dn_dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, ra.route_ids, k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64, e->moe_out, h,
-                                                  e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts), "expert down")) return false;
-                if (!count(e, launch_moe_combine(s, e->moe_out, ra.route_w, k, h, e->proj + (size_t)t * h, e->pdl, ra.route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr, c.moe_num_experts), "moe combine")) return false;
-            }
+            RouterArgs ra{};
+            ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm;
+            ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
+            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done; ra.route_stride = 32;
+            if (!count(e, launch_moe_router(s, ra, e->pdl, T), "router")) return false;
+            if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, L.d_route_ids, T * k, e->act_q, e->act_s, e->act_m, h, h / 64,
+                                              e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts, k, 32, k), "expert gate_up")) return false;
+            if (!count(e, launch_expert_swiglu_quant(s, e->moe_gu, dff, T * k, e->moe_q, e->moe_s, e->moe_m, e->pdl), "expert swiglu")) return false;
+            if (!count(e, launch_gemv_experts(s, L.dn_dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, L.d_route_ids, T * k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64,
+                                              e->moe_out, h, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts, k, 32, 1), "expert down")) return false;
+            if (!count(e, launch_moe_combine(s, e->moe_out, L.d_route_w, k, h, e->proj, e->pdl, L.d_route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr,
+                                             c.moe_num_experts, T, 32), "moe combine")) return false;
             continue;
         }
         if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl, c.tp_size > 1)) return false;
@@ -829,9 +832,10 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     }
     if (ok && e->has_moe) {
         const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
-        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->router_logits, 256) && dev_alloc(e, e->router_done, 1) && dev_alloc(e, e->moe_gu, (size_t)k * 2 * dff) &&
-             dev_alloc(e, e->moe_out, (size_t)k * h) && dev_alloc(e, e->moe_q, (size_t)k * dff) &&
-             dev_alloc(e, e->moe_s, (size_t)k * dff / 64) && dev_alloc(e, e->moe_m, (size_t)k * dff / 64);
+        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->router_logits, (size_t)MAX_BATCH * 256) && dev_alloc(e, e->router_done, MAX_BATCH) &&
+             dev_alloc(e, e->moe_gu, (size_t)MAX_BATCH * k * 2 * dff) && dev_alloc(e, e->moe_out, (size_t)MAX_BATCH * k * h) &&
+             dev_alloc(e, e->moe_q, (size_t)MAX_BATCH * k * dff) && dev_alloc(e, e->moe_s, (size_t)MAX_BATCH * k * dff / 64) &&
+             dev_alloc(e, e->moe_m, (size_t)MAX_BATCH * k * dff / 64);
     }
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
     if (!setup_mega(e)) return bad(ctx->err);

@@ -85,6 +85,9 @@ struct ExpertBatch {
     size_t xq_stride, xs_stride;   // per-slot strides of the activation
     size_t out_stride;             // per-slot stride of the output
     uint32_t n_experts;            // entries of books / bases: a route id outside is refused (error word 4)
+    // batches of tokens: slot = token * route_group + route; the token's routes start at route_ids + token * route_stride,
+    // and act_group consecutive slots share one activation (the token's, for the gate_up projection)
+    uint32_t route_group, route_stride, act_group;
 };
 
 template <int FMT>
@@ -95,7 +98,8 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
     if ((threadIdx.x & 31) == 0) gemv_init_barriers(wsm);
     __syncwarp();
     pdl_wait();
-    const uint32_t slot = blockIdx.y, e = __ldcg(b.route_ids + slot);
+    const uint32_t slot = blockIdx.y, e = __ldcg(b.route_ids + (size_t)(slot / b.route_group) * b.route_stride + slot % b.route_group);
+    const size_t ai = slot / b.act_group;
     if (e >= b.n_experts) {            // never produced by the router kernel; a foreign id must not index the tables
         if (threadIdx.x == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 4u);
         return;
@@ -113,8 +117,8 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
     for (int k = 0; k < 3; ++k) a.plane[k] = base + (a.plane[k] - b.base0);
     a.scales = reinterpret_cast<const uint16_t *>(base + (reinterpret_cast<const uint8_t *>(a.scales) - b.base0));
     PipeState ps;
-    gemv_body<FMT, 1, false, false>(a, a.xq + slot * b.xq_stride, a.xs + slot * b.xs_stride,
-                                    a.xsum != nullptr ? a.xsum + slot * b.xs_stride : nullptr, a.out + slot * b.out_stride, wsm,
+    gemv_body<FMT, 1, false, false>(a, a.xq + ai * b.xq_stride, a.xs + ai * b.xs_stride,
+                                    a.xsum != nullptr ? a.xsum + ai * b.xs_stride : nullptr, a.out + slot * b.out_stride, wsm,
                                     reinterpret_cast<float *>(smem + (size_t)WK * warp_smem<FMT>(1)), blockIdx.x, gridDim.x, wid, WK, 0, ps);
 }
 
@@ -139,12 +143,15 @@ int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out) {
 
 cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases, const uint32_t *route_ids,
                                 uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum, size_t xq_stride,
-                                size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl, uint32_t n_experts) {
+                                size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl, uint32_t n_experts,
+                                uint32_t route_group, uint32_t route_stride, uint32_t act_group) {
     if (n_slot == 0) return cudaSuccess;
+    if (route_group == 0) { route_group = n_slot; route_stride = 0; }
+    if (act_group == 0) act_group = 1;
     GemvArgs a;
     if (fill_gemv_args(m0, xsum != nullptr, a) < 0) return cudaErrorNotSupported;
     a.xq = xq; a.xs = xs; a.xsum = xsum; a.out = out; a.err_flag = err_flag; a.out_stride = m0.geom.rows; a.pdl = pdl ? 1u : 0u; a.n_tok = 1;
-    ExpertBatch b{books, bases, m0.d_base, route_ids, xq_stride, xs_stride, out_stride, n_experts};
+    ExpertBatch b{books, bases, m0.d_base, route_ids, xq_stride, xs_stride, out_stride, n_experts, route_group, route_stride, act_group};
     switch (fmt) {
         case FMT_NF4: return launch_expert_fmt<FMT_NF4>(stream, a, b, n_slot, sm_count);
         case FMT_NF4G: return launch_expert_fmt<FMT_NF4G>(stream, a, b, n_slot, sm_count);

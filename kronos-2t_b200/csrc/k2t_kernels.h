@@ -41,7 +41,8 @@ int expert_codebook(const DeviceMatrix &m, ExpertCodebook &out);
 cudaError_t launch_gemv_experts(cudaStream_t stream, const DeviceMatrix &m0, int fmt, const ExpertCodebook *books, const uint8_t *const *bases,
                                 const uint32_t *route_ids, uint32_t n_slot, const int8_t *xq, const float *xs, const int32_t *xsum,
                                 size_t xq_stride, size_t xs_stride, float *out, size_t out_stride, int sm_count, uint32_t *err_flag, bool pdl,
-                                uint32_t n_experts);
+                                uint32_t n_experts,
+                                uint32_t route_group = 0, uint32_t route_stride = 0, uint32_t act_group = 1);
 
 // Largest n_tok one launch_gemv call accepts for this matrix (4: the reference's tokens per weight tile in prompt batches).
 uint32_t gemv_max_tokens(const DeviceMatrix &m);

@@ -178,8 +178,12 @@ __device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x);
 // equals - what select_topk_by_score's strict '>' insertion produces), optional renormalisation in that order, sort by id.
 constexpr uint32_t ROUTER_THREADS = 128, ROUTER_MAX_EXPERTS = 256, ROUTER_MAX_TOPK = 32;
 constexpr uint32_t ROUTER_EXPERTS_PER_CTA = ROUTER_THREADS / 16;
-__global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const RouterArgs a) {
+__global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a) {
     extern __shared__ float s_xr[];          // hidden floats
+    {   // blockIdx.y = token of the batch
+        const size_t t = blockIdx.y;
+        a.x += t * a.hidden; a.logits += t * a.n_experts; a.done += t; a.route_ids += t * a.route_stride; a.route_w += t * a.route_stride;
+    }
     __shared__ float s_z[ROUTER_MAX_EXPERTS];
     __shared__ float s_sel_w[ROUTER_MAX_TOPK];
     __shared__ uint32_t s_sel_e[ROUTER_MAX_TOPK];
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(const Router
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = atomicAdd(a.done, 1u) + 1u == gridDim.x ? 1u : 0u;
+    if (tid == 0) s_last = atomicAdd(a.done, 1u) + 1u == gridDim.x ? 1u : 0u;       // per token: its own counter
     __syncthreads();
     if (s_last == 0) return;
     __threadfence();
@@ -305,8 +309,12 @@ __global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *_
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ expert_out, const float *__restrict__ route_w,
                                                           uint32_t n_slot, uint32_t n, float *__restrict__ out,
                                                           const uint32_t *__restrict__ route_ids, const uint8_t *const *__restrict__ owned,
-                                                          uint32_t n_experts) {
+                                                          uint32_t n_experts, uint32_t route_stride) {
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    {   // blockIdx.y = token of the batch: its n_slot expert outputs, its routes, its output row
+        const size_t t = blockIdx.y;
+        expert_out += t * n_slot * n; route_w += t * route_stride; route_ids += t * route_stride; out += t * n;
+    }
     pdl_wait();
     pdl_trigger();
     if (i >= n) return;
@@ -880,7 +888,7 @@ cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *del
                                  int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl) {
     return launch_rmsnorm_quant_x(s, hidden, delta, w, n, eps, q, scales, sums, nullptr, n_tok, pdl);
 }
-cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl) {
+cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl, uint32_t n_tok) {
     if (a.n_experts > ROUTER_MAX_EXPERTS || a.top_k > ROUTER_MAX_TOPK || a.hidden * 4 > 160 * 1024) return cudaErrorInvalidValue;
     const size_t smem = (size_t)a.hidden * 4;
     {
@@ -888,15 +896,16 @@ cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl) {
         if (e != cudaSuccess) return e;
     }
     if (a.logits == nullptr || a.done == nullptr) return cudaErrorInvalidValue;
-    return launch_kernel(moe_router_kernel, dim3((a.n_experts + ROUTER_EXPERTS_PER_CTA - 1) / ROUTER_EXPERTS_PER_CTA), dim3(ROUTER_THREADS), smem, s, pdl, a);
+    return launch_kernel(moe_router_kernel, dim3((a.n_experts + ROUTER_EXPERTS_PER_CTA - 1) / ROUTER_EXPERTS_PER_CTA, n_tok), dim3(ROUTER_THREADS), smem, s, pdl, a);
 }
 cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
                                        int32_t *sums, bool pdl) {
     return launch_kernel(expert_swiglu_quant_kernel, dim3((d_ff / 64 + 7) / 8, n_slot), dim3(256), 0, s, pdl, gate_up, d_ff, q, scales, sums);
 }
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned, uint32_t n_experts) {
-    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned, n_experts);
+                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned, uint32_t n_experts, uint32_t n_tok, uint32_t route_stride) {
+    return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256, n_tok), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned, n_experts,
+                         route_stride);
 }
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {

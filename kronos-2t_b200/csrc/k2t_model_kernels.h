@@ -125,6 +125,8 @@ struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scorin
     float *route_w;              // out: [top_k]
     float *logits;               // scratch: [n_experts] router logits (device)
     uint32_t *done;              // scratch: CTAs that have written their logits (zero between launches)
+    // batches (grid.y = token t): x + t * hidden, route_ids / route_w + t * route_stride, logits + t * n_experts, done + t
+    uint32_t route_stride;
 };
 
 // pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).
@@ -159,13 +161,14 @@ cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *d
 cudaError_t launch_rmsnorm_quant_tp(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                     int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl,
                                     const TpLink &tp, uint32_t *tp_done);
-cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl);
+cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl, uint32_t n_tok = 1);
 // SwiGLU of n_slot expert outputs [n_slot][2 * d_ff] with the scalar-path exp (moe_800b.rs:1498-1517), then rotation + int8
 cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uint32_t d_ff, uint32_t n_slot, int8_t *q, float *scales,
                                        int32_t *sums, bool pdl);
 // out[i] = sum over slots, in slot order, of route_w[s] * expert_out[s][i]   (sparse_moe.rs:1046-1048)
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr, uint32_t n_experts = 0);
+                               bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr, uint32_t n_experts = 0,
+                               uint32_t n_tok = 1, uint32_t route_stride = 0);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
 // one thread that waits about `ns` nanoseconds (bounded): lets a host queue work behind it (measurement only)
 cudaError_t launch_delay(cudaStream_t s, uint64_t ns);
