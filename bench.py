@@ -837,6 +837,8 @@ def run_decode_only(args, local_rank):
     else:
         cfg = dict(synth.SMOLLM2_135M, kv_bits=args.kv_bits, max_seq=max(512, pos + args.decode_only + 1))
         spec = synth.random_model(cfg, "b4", seed=3)
+    if args.split_kv:
+        spec["cfg"]["split_kv_attention"] = True
     eng = k2.Engine(ctx, spec)
     prompt = np.random.Generator(np.random.PCG64(11)).integers(0, cfg["vocab"], 16).astype(np.uint32)
     l0 = ctx.launch_count
@@ -923,6 +925,7 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=0, help="--decode-only, moe: fewer layers than the shape's 48 (profiling)")
     ap.add_argument("--decode-ctx", type=int, default=15, help="--decode-only: position of the first greedy step")
     ap.add_argument("--kv-bits", type=int, default=8, choices=[4, 8], help="--decode-only: KV cache format")
+    ap.add_argument("--split-kv", action="store_true", help="--decode-only: split-KV attention beyond 512 positions (the engine's opt-in flag)")
     ap.add_argument("--case", default=None, help="profile one case, e.g. b4:2048x49152 (fmt:KxN)")
     ap.add_argument("--tokens", type=int, default=1, help="tokens per launch in --case mode (1..4)")
     ap.add_argument("--no-graph", action="store_true", help="--case mode: skip the CUDA-graph replay timing")
