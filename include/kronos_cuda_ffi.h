@@ -208,13 +208,16 @@ typedef struct KronosCudaLayerDesc {
     const float *qkv_bias;                         /* [q_dim + 2 kv_dim] or NULL */
     const float *q_norm, *k_norm;                  /* [head_dim] or NULL */
     KronosCudaMatrixDesc qkv_proj, o_proj, gate_up_proj, down_proj;
-    /* MoeLayerBorrow (metal_gpu.rs:418-426); moe_router_w == NULL for a dense layer.  On a MoE layer gate_up_proj and
-     * down_proj are ignored (rows = 0): the FFN is the router [moe_num_experts][hidden] fp32 (+ optional bias) and
-     * moe_num_experts expert records (.k2tm record layout: codebooks at 0 / 16, gate_up pair_stream at 64, down
-     * pair_stream at the next multiple of 64) stored back to back in moe_shard. */
+    /* MoeLayerBorrow (metal_gpu.rs:418-426); moe_router_w == NULL for a dense layer.  On a MoE layer the FFN is the
+     * router [moe_num_experts][hidden] fp32 (+ optional bias) and moe_num_experts expert records (.k2tm record layout:
+     * codebooks at 0 / 16, gate_up pair_stream at 64, down pair_stream at the next multiple of 64) stored back to back
+     * in moe_shard; gate_up_proj / down_proj then describe the layer's SHARED expert (SharedMoeExpert with NF matrices,
+     * sparse_moe.rs:223-315: gate_up [2 inter][hidden], gate rows first, down [hidden][inter]) or have rows = 0 when
+     * the layer has none, and moe_shared_gate_w is its sigmoid gate weight [hidden] or NULL. */
     const float *moe_router_w, *moe_router_bias;
     const uint8_t *moe_shard;
     size_t moe_shard_len;
+    const float *moe_shared_gate_w;
 } KronosCudaLayerDesc;
 
 /* MetalLlamaEngine::try_new (metal_gpu.rs:1196-1206): copies every tensor to HBM, allocates the KV cache

@@ -50,6 +50,7 @@ struct OwnedLayer {
     bool moe = false, has_shared = false, has_lookahead = false;
     uint64_t moe_slot = 0, router_experts = 0, router_hidden = 0;
     std::vector<float> router_w, router_bias;
+    std::vector<float> shared_gate_w;          // shared expert: its matrices are kept in gate_up / down
 };
 
 struct Reader {
@@ -133,12 +134,12 @@ bool parse(const uint8_t *bytes, size_t n, KronosCudaK2tb &f, std::string &err) 
                 uint64_t flag = 0;
                 ok = r.u64(L.moe_slot) && r.u64(L.router_experts) && r.u64(L.router_hidden) && r.arr(L.router_w, n) && r.arr(L.router_bias, n) && r.u64(flag);
                 if (ok && L.router_w.size() != L.router_experts * L.router_hidden) { r.err = "router weights do not match experts x hidden"; ok = false; }
-                if (ok && flag) {          // shared expert: read past it (the engine does not run shared experts)
+                if (ok && flag) {          // shared expert: inter, optional gate weight, gate_up and down as NF matrices (5097-5114)
                     L.has_shared = true;
                     uint64_t inter;
-                    std::vector<float> gate_weight;
-                    OwnedMatrix gu, dn;
-                    ok = r.u64(inter) && r.arr(gate_weight, n) && r.matrix(gu, true) && r.matrix(dn, true);
+                    ok = r.u64(inter) && r.arr(L.shared_gate_w, n) && r.matrix(L.gate_up, true) && r.matrix(L.down, true);
+                    if (ok && (L.gate_up.d.kind != KRONOS_CUDA_MATRIX_NF || L.down.d.kind != KRONOS_CUDA_MATRIX_NF || L.down.d.cols != inter ||
+                               L.gate_up.d.rows != 2 * inter)) { r.err = "the shared expert must be two NF matrices of its intermediate size"; ok = false; }
                 }
                 ok = ok && r.u64(flag);
                 if (ok && flag) {          // lookahead projector (expert prefetch of the CPU pager): read past it
@@ -248,7 +249,8 @@ int32_t kronos_cuda_k2tb_layer(const KronosCudaK2tb *f, size_t l, KronosCudaLaye
     if (qkv_bias_len) *qkv_bias_len = L.qkv_bias.size();
     if (!L.o_bias.empty()) { g_k2tb_error = "k2tb_layer: the layer carries an o_proj bias, which the device engine does not apply"; return -1; }
     if (L.moe) {
-        if (L.has_shared) { g_k2tb_error = "k2tb_layer: the layer has a shared expert, which the device engine does not run"; return -1; }
+        // a shared expert rides in gate_up_proj / down_proj (filled above; rows = 0 without one)
+        out->moe_shared_gate_w = L.has_shared && !L.shared_gate_w.empty() ? L.shared_gate_w.data() : nullptr;
         out->moe_router_w = L.router_w.data();
         out->moe_router_bias = L.router_bias.empty() ? nullptr : L.router_bias.data();
         // moe_shard / moe_shard_len come from the expert shard: kronos_cuda_k2tm_layer(shard, moe slot)

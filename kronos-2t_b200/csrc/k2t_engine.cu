@@ -36,6 +36,9 @@ struct EngineLayer {
     uint32_t expert0 = 0;                                             // first expert held by this rank (expert parallelism)
     uint32_t *d_route_ids = nullptr;                                  // [MAX_BATCH][32] routes of the last batch
     float *d_route_w = nullptr;
+    // shared expert of a MoE layer (SharedMoeExpert, sparse_moe.rs:223-315): its matrices live in gate_up / down above
+    uint32_t sh_inter = 0;
+    float *sh_gate_w = nullptr;
 };
 
 struct KronosCudaEngine {
@@ -64,6 +67,10 @@ struct KronosCudaEngine {
     float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr, *router_logits = nullptr;
     uint32_t *router_done = nullptr;
     int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
+    // shared-expert workspace, [MAX_BATCH] rows each: gate_up outputs, the down projection's activation, outputs, gate values
+    uint32_t sh_inter_max = 0;
+    float *sh_gu = nullptr, *sh_out = nullptr, *sh_scale = nullptr;
+    int8_t *sh_q = nullptr; float *sh_s = nullptr; int32_t *sh_m = nullptr;
     bool has_moe = false;
     // tensor parallel: exchange buffer (data[2][tp][slot] floats + flags[tp]) and the peers' mappings
     k2t::TpLink tp{};
@@ -171,16 +178,20 @@ bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 
 
 constexpr uint32_t PASS_TOKENS = 4;    // tokens one weight pass serves (the reference's 4-token tiles in prompt batches)
 
-bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char *what, uint32_t n_tok = 1, size_t act_tok0 = 0) {
+bool gemv_from(KronosCudaEngine *e, const KronosCudaMatrix *m, const int8_t *q, const float *sc, const int32_t *sums, float *out, const char *what,
+               uint32_t n_tok) {
     const size_t cols = m->dm.geom.cols, nc = cols / 64, rows = m->dm.geom.rows;
     for (uint32_t t0 = 0; t0 < n_tok; t0 += PASS_TOKENS) {
         uint32_t launched = 0;
-        const size_t a0 = act_tok0 + t0;
-        cudaError_t err = launch_gemv(e->ctx->stream, m->dm, e->act_q + a0 * cols, e->act_s + a0 * nc, e->act_m + a0 * nc, std::min(PASS_TOKENS, n_tok - t0),
+        cudaError_t err = launch_gemv(e->ctx->stream, m->dm, q + (size_t)t0 * cols, sc + (size_t)t0 * nc, sums + (size_t)t0 * nc, std::min(PASS_TOKENS, n_tok - t0),
                                       out + (size_t)t0 * rows, rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
         if (!count(e, err, what, launched)) return false;
     }
     return true;
+}
+bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char *what, uint32_t n_tok = 1, size_t act_tok0 = 0) {
+    const size_t cols = m->dm.geom.cols, nc = cols / 64;
+    return gemv_from(e, m, e->act_q + act_tok0 * cols, e->act_s + act_tok0 * nc, e->act_m + act_tok0 * nc, out, what, n_tok);
 }
 
 bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n) {
@@ -425,6 +436,15 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             // slot = token * k + route; two tokens that picked the same expert read its image twice, the second time from L2.
             if (!norm_quant(e, e->proj, L.post_norm, e->x_norm, T, e->pdl, c.tp_size > 1)) return false;
             const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
+            // shared expert (every token; under expert parallelism rank 0's partial sum carries it): two plain projections
+            // around the experts' SwiGLU kernel, and its sigmoid gate
+            const bool shared = L.gate_up != nullptr && (c.ep_size <= 1 || c.ep_rank == 0);
+            if (shared) {
+                if (!gemv(e, L.gate_up, e->sh_gu, "shared gate_up", T)) return false;
+                if (!count(e, launch_expert_swiglu_quant(s, e->sh_gu, L.sh_inter, T, e->sh_q, e->sh_s, e->sh_m, e->pdl), "shared swiglu")) return false;
+                if (!gemv_from(e, L.down, e->sh_q, e->sh_s, e->sh_m, e->sh_out, "shared down", T)) return false;
+                if (L.sh_gate_w && !count(e, launch_shared_gate(s, L.sh_gate_w, e->x_norm, h, T, e->sh_scale, e->pdl), "shared gate")) return false;
+            }
             RouterArgs ra{};
             ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm;
             ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
@@ -436,7 +456,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             if (!count(e, launch_gemv_experts(s, L.dn_dm, L.dn_fmt, L.d_dn_books, L.d_dn_bases, L.d_route_ids, T * k, e->moe_q, e->moe_s, e->moe_m, dff, dff / 64,
                                               e->moe_out, h, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts, k, 32, 1), "expert down")) return false;
             if (!count(e, launch_moe_combine(s, e->moe_out, L.d_route_w, k, h, e->proj, e->pdl, L.d_route_ids, c.ep_size > 1 ? L.d_dn_bases : nullptr,
-                                             c.moe_num_experts, T, 32), "moe combine")) return false;
+                                             c.moe_num_experts, T, 32, shared ? e->sh_out : nullptr, shared && L.sh_gate_w ? e->sh_scale : nullptr), "moe combine")) return false;
             continue;
         }
         if (!norm_quant(e, e->proj, L.post_norm, nullptr, T, e->pdl, c.tp_size > 1)) return false;
@@ -517,7 +537,10 @@ uint32_t step_launches(const KronosCudaEngine *e, size_t pos) {
         return n;
     }
     uint32_t n = 1 + 2 + 1 + (e->cfg.tp_size > 1 ? 1 : 0);
-    for (const EngineLayer &L : e->layers) n += ((pos + 1 > ATTN_EXACT_CTX || e->ring.window) ? 10 : 8) + (L.moe ? 2 : 0);     // MoE FFN: 6 kernels for 4; the tensor-parallel sums ride in the norm kernels
+    for (const EngineLayer &L : e->layers) {     // MoE FFN: 6 kernels for 4 (+ 3 or 4 of a shared expert); the tensor-parallel sums ride in the norm kernels
+        n += ((pos + 1 > ATTN_EXACT_CTX || e->ring.window) ? 10 : 8) + (L.moe ? 2 : 0);
+        if (L.moe && L.gate_up && (e->cfg.ep_size <= 1 || e->cfg.ep_rank == 0)) n += 3 + (L.sh_gate_w ? 1 : 0);
+    }
     return n;
 }
 
@@ -783,6 +806,20 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         if (L.moe) {
             const std::string why = setup_moe_layer(e, L, d);
             if (!why.empty()) return bad("engine_create: layer " + std::to_string(l) + ": " + why);
+            if (d.gate_up_proj.rows > 0 || d.down_proj.rows > 0) {         // the layer's shared expert
+                const uint32_t sh = d.down_proj.cols;
+                if (d.gate_up_proj.kind != KRONOS_CUDA_MATRIX_NF || d.down_proj.kind != KRONOS_CUDA_MATRIX_NF || sh == 0 || sh % 64 != 0 ||
+                    !shape_ok(d.gate_up_proj, 2 * sh, h) || !shape_ok(d.down_proj, h, sh))
+                    return bad("engine_create: layer " + std::to_string(l) + ": the shared expert must be two NF matrices [2 inter][hidden] and [hidden][inter]");
+                L.gate_up = kronos_cuda_matrix_upload(ctx, &d.gate_up_proj, 0);
+                L.down = L.gate_up ? kronos_cuda_matrix_upload(ctx, &d.down_proj, 0) : nullptr;
+                if (!L.down) return bad("engine_create: layer " + std::to_string(l) + ": shared expert: " + ctx->err);
+                if (d.moe_shared_gate_w && !dev_alloc(e, L.sh_gate_w, h, d.moe_shared_gate_w)) return bad(ctx->err);
+                L.sh_inter = sh;
+                e->sh_inter_max = std::max(e->sh_inter_max, sh);
+                e->weight_bytes += L.gate_up->dm.geom.file_bytes + L.down->dm.geom.file_bytes;
+                e->fused = false;               // the fused-prologue path has no shared-expert form
+            }
             continue;
         }
         L.gate_up = kronos_cuda_matrix_upload(ctx, &d.gate_up_proj, 0);
@@ -836,6 +873,11 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
              dev_alloc(e, e->moe_gu, (size_t)MAX_BATCH * k * 2 * dff) && dev_alloc(e, e->moe_out, (size_t)MAX_BATCH * k * h) &&
              dev_alloc(e, e->moe_q, (size_t)MAX_BATCH * k * dff) && dev_alloc(e, e->moe_s, (size_t)MAX_BATCH * k * dff / 64) &&
              dev_alloc(e, e->moe_m, (size_t)MAX_BATCH * k * dff / 64);
+        if (ok && e->sh_inter_max > 0) {
+            const size_t si = e->sh_inter_max;
+            ok = dev_alloc(e, e->sh_gu, (size_t)MAX_BATCH * 2 * si) && dev_alloc(e, e->sh_out, (size_t)MAX_BATCH * h) && dev_alloc(e, e->sh_scale, MAX_BATCH) &&
+                 dev_alloc(e, e->sh_q, (size_t)MAX_BATCH * si) && dev_alloc(e, e->sh_s, (size_t)MAX_BATCH * si / 64) && dev_alloc(e, e->sh_m, (size_t)MAX_BATCH * si / 64);
+        }
     }
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
     if (!setup_mega(e)) return bad(ctx->err);

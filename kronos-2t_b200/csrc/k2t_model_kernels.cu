@@ -309,16 +309,28 @@ __global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *_
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restrict__ expert_out, const float *__restrict__ route_w,
                                                           uint32_t n_slot, uint32_t n, float *__restrict__ out,
                                                           const uint32_t *__restrict__ route_ids, const uint8_t *const *__restrict__ owned,
-                                                          uint32_t n_experts, uint32_t route_stride) {
+                                                          uint32_t n_experts, uint32_t route_stride,
+                                                          const float *__restrict__ base, const float *__restrict__ base_scale) {
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
     {   // blockIdx.y = token of the batch: its n_slot expert outputs, its routes, its output row
         const size_t t = blockIdx.y;
         expert_out += t * n_slot * n; route_w += t * route_stride; route_ids += t * route_stride; out += t * n;
+        if (base != nullptr) base += t * n;
+        if (base_scale != nullptr) base_scale += t;
     }
     pdl_wait();
     pdl_trigger();
     if (i >= n) return;
+    // the shared expert's output comes first (SharedMoeExpert::forward_single writes `out`, the routed experts add to it),
+    // scaled by its gate unless that is 1 within f32::EPSILON (sparse_moe.rs:307-311)
     float acc = 0.0f;
+    if (base != nullptr) {
+        acc = __ldcg(base + i);
+        if (base_scale != nullptr) {
+            const float sc = __ldcg(base_scale);
+            if (fabsf(__fsub_rn(sc, 1.0f)) > 1.1920929e-07f) acc = __fmul_rn(acc, sc);
+        }
+    }
     for (uint32_t s = 0; s < n_slot; ++s) {
         if (owned != nullptr && (__ldcg(route_ids + s) >= n_experts || owned[__ldcg(route_ids + s)] == nullptr)) continue;
         acc = __fadd_rn(acc, __fmul_rn(__ldcg(route_w + s), __ldcg(expert_out + (size_t)s * n + i)));
@@ -903,9 +915,31 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
     return launch_kernel(expert_swiglu_quant_kernel, dim3((d_ff / 64 + 7) / 8, n_slot), dim3(256), 0, s, pdl, gate_up, d_ff, q, scales, sums);
 }
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
-                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned, uint32_t n_experts, uint32_t n_tok, uint32_t route_stride) {
+                               bool pdl, const uint32_t *route_ids, const uint8_t *const *owned, uint32_t n_experts, uint32_t n_tok, uint32_t route_stride,
+                               const float *base, const float *base_scale) {
     return launch_kernel(moe_combine_kernel, dim3((n + 255) / 256, n_tok), dim3(256), 0, s, pdl, expert_out, route_w, n_slot, n, out, route_ids, owned, n_experts,
-                         route_stride);
+                         route_stride, base, base_scale);
+}
+
+// Gate of a shared expert (SharedMoeExpert::gate_scale, sparse_moe.rs:241-249): sigmoid of dot_f32_moe(gate_w, x_norm), the
+// dot in the 16-accumulator order of the router logits, the exp as in the scalar paths.  One warp per token.
+__global__ void __launch_bounds__(32) shared_gate_kernel(const float *__restrict__ gate_w, const float *__restrict__ x_norm, uint32_t n,
+                                                         float *__restrict__ scale) {
+    const uint32_t lane = threadIdx.x, l16 = lane & 15;
+    pdl_wait();
+    pdl_trigger();
+    const float *x = x_norm + (size_t)blockIdx.x * n;
+    float acc = 0.0f;
+    if (lane < 16)
+        for (uint32_t i = l16; i < n; i += 16) acc = __fmaf_rn(__ldg(gate_w + i), __ldcg(x + i), acc);
+    float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));
+    t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 8));
+    t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 1));
+    t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2));
+    if (lane == 0) scale[blockIdx.x] = __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_cr(-t)));
+}
+cudaError_t launch_shared_gate(cudaStream_t s, const float *gate_w, const float *x_norm, uint32_t n, uint32_t n_tok, float *scale, bool pdl) {
+    return launch_kernel(shared_gate_kernel, dim3(n_tok), dim3(32), 0, s, pdl, gate_w, x_norm, n, scale);
 }
 cudaError_t launch_rmsnorm_quant_x(cudaStream_t s, float *hidden, const float *delta, const float *w, uint32_t n, float eps,
                                    int8_t *q, float *scales, int32_t *sums, float *x_norm, uint32_t n_tok, bool pdl) {

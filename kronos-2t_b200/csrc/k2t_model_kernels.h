@@ -168,7 +168,9 @@ cudaError_t launch_expert_swiglu_quant(cudaStream_t s, const float *gate_up, uin
 // out[i] = sum over slots, in slot order, of route_w[s] * expert_out[s][i]   (sparse_moe.rs:1046-1048)
 cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const float *route_w, uint32_t n_slot, uint32_t n, float *out,
                                bool pdl, const uint32_t *route_ids = nullptr, const uint8_t *const *owned = nullptr, uint32_t n_experts = 0,
-                               uint32_t n_tok = 1, uint32_t route_stride = 0);
+                               uint32_t n_tok = 1, uint32_t route_stride = 0, const float *base = nullptr, const float *base_scale = nullptr);
+// sigmoid gate of a shared expert, one value per token of the batch
+cudaError_t launch_shared_gate(cudaStream_t s, const float *gate_w, const float *x_norm, uint32_t n, uint32_t n_tok, float *scale, bool pdl);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
 // one thread that waits about `ns` nanoseconds (bounded): lets a host queue work behind it (measurement only)
 cudaError_t launch_delay(cudaStream_t s, uint64_t ns);

@@ -48,7 +48,8 @@ class LayerDesc(C.Structure):
     _fields_ = [("input_norm", C.c_void_p), ("post_attn_norm", C.c_void_p), ("qkv_bias", C.c_void_p),
                 ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("qkv_proj", MatrixDesc), ("o_proj", MatrixDesc), ("gate_up_proj", MatrixDesc), ("down_proj", MatrixDesc),
-                ("moe_router_w", C.c_void_p), ("moe_router_bias", C.c_void_p), ("moe_shard", C.c_void_p), ("moe_shard_len", C.c_size_t)]
+                ("moe_router_w", C.c_void_p), ("moe_router_bias", C.c_void_p), ("moe_shard", C.c_void_p), ("moe_shard_len", C.c_size_t),
+                ("moe_shared_gate_w", C.c_void_p)]
 
 
 def load_library():
@@ -360,6 +361,12 @@ class Engine:
                 md = desc_of(ly[key])
                 keep.append(md._keep)
                 setattr(d, name, md)
+            if moe and moe.get("shared") is not None:           # the layer's shared expert rides in the dense FFN fields
+                for name, key in (("gate_up_proj", "gate_up"), ("down_proj", "down")):
+                    md = desc_of(moe["shared"][key])
+                    keep.append(md._keep)
+                    setattr(d, name, md)
+                d.moe_shared_gate_w = vec(moe["shared"].get("gate_w"))
         head = desc_of(spec["lm_head"])
         rope, fn = _np(spec["rope"], np.float32), _np(spec["final_norm"], np.float32)
         emb = None if spec.get("embed_bf16") is None else _np(spec["embed_bf16"], np.uint16)
@@ -626,6 +633,8 @@ def moe_load(core_path, shard_path, cfg, rope):
                 ly["moe"] = dict(router_w=_f32(d.moe_router_w, experts * hid), router_bias=_f32(d.moe_router_bias, experts), n_experts=experts,
                                  top_k=cfg["moe_top_k"], norm_topk=bool(cfg.get("moe_norm_topk", True)), d_ff=d_ff, bits=bits, sgc=sgc, shard=shard,
                                  expert_bytes=rec, scoring=int(cfg.get("moe_scoring", 0)))
+                if d.gate_up_proj.rows:         # the layer's shared expert
+                    ly["moe"]["shared"] = dict(gate_up=_HostMatrix(d.gate_up_proj), down=_HostMatrix(d.down_proj), gate_w=_f32(d.moe_shared_gate_w, hid))
             else:
                 ly.update(gate_up=_HostMatrix(d.gate_up_proj), down=_HostMatrix(d.down_proj))
             layers.append(ly)

@@ -78,6 +78,10 @@ struct Moe {
     uint32_t scoring = 0;               // MoeRouterScoring tag: 0 softmax, 1 top-k softmax, 2 sigmoid (sparse_moe.rs:28-53)
     std::vector<float> router_w, router_bias;
     std::vector<Expert> experts;
+    // shared expert (SharedMoeExpert, Nf backend, sparse_moe.rs:223-315): runs for every token, optional sigmoid gate
+    bool has_shared = false;
+    Mat sh_gu, sh_dn;
+    std::vector<float> sh_gate;
     uint32_t ep_size = 1, ep_rank = 0;   // expert-parallel emulation: only experts e % ep_size == ep_rank contribute (tests)
     uint32_t last_k = 0;                 // routes of the last token (tests)
     uint32_t last_e[32] = {0};
@@ -452,7 +456,7 @@ struct Act {
     }
 };
 
-// SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), zero-copy NF experts, softmax router, no shared expert.
+// SparseMoeRuntime::forward_layer_single (sparse_moe.rs:961-1084), zero-copy NF experts, optional NF shared expert.
 void moe_forward(Moe &M, const float *x_norm, size_t h, float *out, size_t threads) {
     const size_t E = M.n_experts, k = std::min<size_t>(std::min<size_t>(M.top_k, E), 32);
     std::vector<float> logits(E);
@@ -499,6 +503,22 @@ void moe_forward(Moe &M, const float *x_norm, size_t h, float *out, size_t threa
     act_in.populate(x_norm, h);
     std::vector<float> gu(2 * (size_t)M.d_ff), sw(M.d_ff), eo(h);
     std::fill(out, out + h, 0.0f);
+    if (M.has_shared && (M.ep_size <= 1 || M.ep_rank == 0)) {      // SharedMoeExpert::forward_single (254-314); under the expert-parallel emulation rank 0 holds it
+        const size_t inter = M.sh_dn.cols;
+        float scale = 1.0f;
+        if (!M.sh_gate.empty()) scale = 1.0f / (1.0f + exp_cr(-k2o_dot_f32(M.sh_gate.data(), x_norm, h)));      // gate_scale (241-249)
+        std::vector<float> sgu(2 * inter), ssw(inter);
+        M.sh_gu.gemv(act_in.q.data(), act_in.s.data(), act_in.m.data(), sgu.data(), threads);
+        for (size_t j = 0; j < inter; ++j) {
+            const float g = sgu[j], u = sgu[inter + j];
+            ssw[j] = (g / (1.0f + exp_cr(-g))) * u;
+        }
+        Act sh_mid;
+        sh_mid.populate(ssw.data(), inter);
+        M.sh_dn.gemv(sh_mid.q.data(), sh_mid.s.data(), sh_mid.m.data(), out, threads);
+        if (std::fabs(scale - 1.0f) > 1.1920929e-07f)
+            for (size_t j = 0; j < h; ++j) out[j] *= scale;
+    }
     for (size_t i = 0; i < k; ++i) {
         if (M.ep_size > 1 && ids[i] % M.ep_size != M.ep_rank) continue;      // another rank's expert
         const Expert &X = M.experts[ids[i]];
@@ -559,6 +579,17 @@ int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const floa
         d.data0 = rec + dn_off; d.len0 = dnb;
         if (!load_mat(M.experts[e].dn, &d)) return -1;
     }
+    return 0;
+}
+
+int k2o_model_set_moe_shared(K2oModel *m, uint32_t l, const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down, const float *gate_w) {
+    if (!m || l >= m->layers.size() || !m->layers[l].moe.on || !gate_up || !down) return -1;
+    Moe &M = m->layers[l].moe;
+    if (!load_mat(M.sh_gu, gate_up) || !load_mat(M.sh_dn, down)) return -1;
+    const size_t h = m->cfg.hidden;
+    if (M.sh_gu.cols != h || M.sh_dn.rows != h || M.sh_gu.rows != 2 * M.sh_dn.cols) return -1;
+    if (gate_w) M.sh_gate.assign(gate_w, gate_w + h); else M.sh_gate.clear();
+    M.has_shared = true;
     return 0;
 }
 

@@ -190,6 +190,9 @@ int k2o_model_set_moe(K2oModel *m, uint32_t l, const float *router_w, const floa
 /* Routes of the last token through MoE layer l: up to 32 (expert, weight) pairs sorted by expert id; returns k. */
 /* Expert-parallel emulation (the reference runs on one device): from now on the MoE blocks of `m` add only the routed
  * experts e with e % ep_size == ep_rank, so k2o_model_ffn_part returns one rank's partial sum. */
+/* shared expert of a sparse-MoE layer (SharedMoeExpert, Nf backend, sparse_moe.rs:223-315): gate_up [2 inter][hidden] (gate
+ * rows first), down [hidden][inter], optional sigmoid gate weight [hidden] */
+int k2o_model_set_moe_shared(K2oModel *m, uint32_t l, const K2oMatrixDesc *gate_up, const K2oMatrixDesc *down, const float *gate_w);
 void k2o_model_set_ep(K2oModel *m, uint32_t ep_size, uint32_t ep_rank);
 uint32_t k2o_model_last_routes(const K2oModel *m, uint32_t l, uint32_t *experts, float *weights);
 /* .k2tm record geometry (NfExpertByteLayout): returns aligned_expert_bytes, fills the pair-stream offsets / sizes. */

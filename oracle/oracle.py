@@ -434,6 +434,7 @@ def _declare_model(L):
     L.k2o_model_tap_hidden.restype, L.k2o_model_tap_hidden.argtypes = P, [P]
     L.k2o_model_set_moe.restype = C.c_int
     L.k2o_model_set_moe.argtypes = [P, C.c_uint32, P, P, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, P, C.c_size_t]
+    L.k2o_model_set_moe_shared.restype, L.k2o_model_set_moe_shared.argtypes = C.c_int, [P, C.c_uint32, D, D, P]
     L.k2o_model_last_routes.restype, L.k2o_model_last_routes.argtypes = C.c_uint32, [P, C.c_uint32, P, P]
     L.k2o_model_set_ep.restype, L.k2o_model_set_ep.argtypes = None, [P, C.c_uint32, C.c_uint32]
     L.k2o_nf_expert_layout.restype = C.c_size_t
@@ -587,6 +588,11 @@ class Model:
                 rc = L.k2o_model_set_moe(self.h, l, _ptr(rw), _ptr(rb), moe["n_experts"], moe["top_k"], int(moe["norm_topk"]) | (int(moe.get("scoring", 0)) << 8), moe["d_ff"],
                                          moe["bits"], moe["sgc"], _ptr(shard), moe["expert_bytes"])
                 assert rc == 0, f"set_moe {l} failed"
+                sh = moe.get("shared")              # dict(gate_up=Nf, down=Nf, gate_w=array or None)
+                if sh is not None:
+                    dg, dd = desc_of(sh["gate_up"]), desc_of(sh["down"])
+                    gw = None if sh.get("gate_w") is None else _c(sh["gate_w"], np.float32)
+                    assert L.k2o_model_set_moe_shared(self.h, l, C.byref(dg), C.byref(dd), _ptr(gw)) == 0, f"set_moe_shared {l} failed"
         emb = None if spec.get("embed_bf16") is None else _c(spec["embed_bf16"], np.uint16)
         d = desc_of(spec["lm_head"])
         fn = _c(spec["final_norm"], np.float32)

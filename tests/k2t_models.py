@@ -28,7 +28,7 @@ def quantize(oracle, w, mode):
 MOE_TINY = dict(hidden=128, layers=3, n_q=4, n_kv=2, head_dim=64, inter=256, vocab=320, max_seq=96, eps=1e-6, theta=1e6)
 
 
-def build_moe(oracle, seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk=True, bias=False, scoring=0):
+def build_moe(oracle, seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk=True, bias=False, scoring=0, shared=0, shared_gate=True):
     """One sparse-MoE FFN: router N(0, 0.02) (near-uniform routing) and NF experts in .k2tm record form."""
     experts = []
     mode = ("e8q2" if bits == 2 else f"nf{bits}") + ("g128" if sgc == 2 else "")     # bits = 2: E8 lattice codewords
@@ -38,7 +38,12 @@ def build_moe(oracle, seed, hidden, n_experts, top_k, d_ff, bits, sgc, norm_topk
         assert gu.sgc == sgc and dn.sgc == sgc
         experts.append((gu, dn))
     shard, lay = oracle.pack_expert_shard(experts, hidden, d_ff, bits, sgc)
-    return dict(router_w=normal(seed + 999, (n_experts, hidden), 0.02), router_bias=normal(seed + 998, n_experts, 0.01) if bias else None,
+    sh = None
+    if shared:              # shared expert of `shared` intermediate columns (SharedMoeExpert, NF matrices), optional sigmoid gate
+        sh = dict(gate_up=quantize(oracle, normal(seed + 5000, (2 * shared, hidden), 0.02), "nf4g128"),
+                  down=quantize(oracle, normal(seed + 5001, (hidden, shared), 0.02), "nf4g128"),
+                  gate_w=normal(seed + 5002, hidden, 0.3) if shared_gate else None)
+    return dict(shared=sh, router_w=normal(seed + 999, (n_experts, hidden), 0.02), router_bias=normal(seed + 998, n_experts, 0.01) if bias else None,
                 n_experts=n_experts, top_k=top_k, norm_topk=norm_topk, d_ff=d_ff, bits=bits, sgc=sgc, shard=shard,
                 expert_bytes=lay["expert_bytes"], scoring=scoring)
 
@@ -68,7 +73,8 @@ def build(oracle, cfg, mode="b4", seed=0, qkv_bias=False, qk_norm=False, tied=Tr
         if moe and l in moe["layers"]:
             ly["gate_up"] = ly["down"] = None
             ly["moe"] = build_moe(oracle, s + 100 * l + 50, h, moe["n_experts"], moe["top_k"], moe["d_ff"], moe["bits"], moe["sgc"],
-                                  moe.get("norm_topk", True), moe.get("bias", False), moe.get("scoring", 0))
+                                  moe.get("norm_topk", True), moe.get("bias", False), moe.get("scoring", 0), moe.get("shared", 0),
+                                  moe.get("shared_gate", True))
         layers.append(ly)
     head_w = normal(s + 999, (c["vocab"], h), 0.02)
     spec = dict(cfg=c, layers=layers, final_norm=(1.0 + 0.1 * normal(s + 998, h)).astype(np.float32),

@@ -38,7 +38,12 @@ def write_moe_files(core_path, shard_path, spec, mode_words, lookahead_layers=()
                 _matrix(ly["qkv"]), _matrix(ly["o"])]
         moe = ly.get("moe")
         if moe:
-            out += [_u64(1), _u64(slot), _u64(moe["n_experts"]), _u64(hidden), _f32s(moe["router_w"]), _f32s(moe.get("router_bias")), _u64(0)]
+            out += [_u64(1), _u64(slot), _u64(moe["n_experts"]), _u64(hidden), _f32s(moe["router_w"]), _f32s(moe.get("router_bias"))]
+            sh = moe.get("shared")
+            if sh is None:
+                out += [_u64(0)]
+            else:           # shared expert: inter, gate weight (may be empty), gate_up and down as NF matrices (real_llm.rs:5097-5114)
+                out += [_u64(1), _u64(sh["down"].cols), _f32s(sh.get("gate_w")), _matrix(sh["gate_up"]), _matrix(sh["down"])]
             if l in lookahead_layers:
                 out += [_u64(1), _u64(l + 1), _u64(hidden), _u64(2), _f32s(np.zeros(2 * hidden)), _f32s(np.zeros(2 * hidden))]
             else:

@@ -106,6 +106,8 @@ def test_nf4_kv_cache_logits_and_entries(ctx, oracle, cfg, mode, kw, decode_path
     ("b4", dict(layers=[2], n_experts=4, top_k=2, d_ff=128, bits=2, sgc=2), {}),                                # E8Q2 experts
     ("nf4g128", dict(layers=[1, 2], n_experts=8, top_k=3, d_ff=64, bits=4, sgc=1, scoring=1), {}),               # top-k softmax router (GptOss)
     ("b5", dict(layers=[0], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=1, scoring=2, bias=True), {}),             # sigmoid router
+    ("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, shared=128), {}),                # shared expert with a sigmoid gate (Qwen2-MoE)
+    ("b5", dict(layers=[1], n_experts=8, top_k=3, d_ff=64, bits=4, sgc=1, shared=64, shared_gate=False), dict(qkv_bias=True)),   # ungated shared expert
 ])
 def test_sparse_moe_layers_match_oracle(ctx, oracle, mode, moe, kw):
     """Router (softmax, top-k, renormalisation, expert order), .k2tm expert records, expert SwiGLU and the weighted sum."""

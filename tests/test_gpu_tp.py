@@ -113,7 +113,8 @@ dist.destroy_process_group()
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("mode,moe", [("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=3, d_ff=64, bits=3, sgc=2)),
-                                      ("b5", dict(layers=[1, 2], n_experts=6, top_k=6, d_ff=64, bits=4, sgc=1, norm_topk=False, bias=True))])
+                                      ("b5", dict(layers=[1, 2], n_experts=6, top_k=6, d_ff=64, bits=4, sgc=1, norm_topk=False, bias=True)),
+                                      ("nf4g128", dict(layers=[0, 1], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, shared=64))])    # rank 0's partial sum carries the shared expert
 def test_two_rank_expert_parallel_engine_matches_rank_order_emulation(oracle, tmp_path, mode, moe):
     tokens = [t % km.MOE_TINY["vocab"] for t in TOKENS]
     port = str(33000 + os.getpid() % 2000)

@@ -170,7 +170,7 @@ def test_moe_core_and_expert_shard_readers(oracle, tmp_path):
     malformed files.  No GPU needed."""
     import kronos_2t_b200 as k2
     import k2t_moe_files as mf
-    moe = dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, bias=True)
+    moe = dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, bias=True, shared=128)
     spec = km.build(oracle, km.MOE_TINY, "nf4g128", seed=17, moe=moe, qk_norm=True, qkv_bias=True, tied=False)
     core, shard = str(tmp_path / "core.k2tb"), str(tmp_path / "experts.k2tm")
     words = mf.write_moe_files(core, shard, spec, [6, 4, 3, 2, 0, 0], lookahead_layers=(0,))
@@ -188,6 +188,9 @@ def test_moe_core_and_expert_shard_readers(oracle, tmp_path):
                 assert np.array_equal(ma["router_w"].reshape(-1), np.asarray(mb["router_w"]).reshape(-1)) and np.array_equal(ma["router_bias"], mb["router_bias"])
                 assert np.array_equal(ma["shard"], mb["shard"]) and ma["expert_bytes"] == mb["expert_bytes"]
                 assert (ma["n_experts"], ma["d_ff"], ma["bits"], ma["sgc"], ma["top_k"]) == (8, 64, 3, 2, 2)
+                sa, sb = ma["shared"], mb["shared"]             # the shared expert: two NF matrices and the gate weight
+                assert np.array_equal(sa["gate_up"].pair, sb["gate_up"].pair) and np.array_equal(sa["down"].pair, sb["down"].pair)
+                assert (sa["gate_up"].rows, sa["down"].cols) == (256, 128) and np.array_equal(sa["gate_w"], sb["gate_w"])
             else:
                 assert np.array_equal(a["gate_up"].pair, b["gate_up"].pair) and np.array_equal(a["down"].pair, b["down"].pair)
         assert np.array_equal(got["final_norm"], spec["final_norm"]) and np.array_equal(got["embed_bf16"], np.asarray(spec["embed_bf16"]).reshape(-1))
@@ -220,6 +223,7 @@ def test_moe_core_and_expert_shard_readers(oracle, tmp_path):
 @pytest.mark.parametrize("mode,moe,kw", [
     ("nf4g128", dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2), dict(qk_norm=True, tied=False)),     # Qwen3-MoE style
     ("b5", dict(layers=[1], n_experts=16, top_k=4, d_ff=128, bits=4, sgc=1, norm_topk=False, bias=True), dict(qkv_bias=True)),
+    ("nf4g128", dict(layers=[0, 1], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, shared=64), {}),                      # with a gated shared expert
 ])
 def test_moe_engine_from_core_and_shard_files(oracle, tmp_path, mode, moe, kw):
     """load_moe_from_files on the device: a sparse-MoE model written as K2TKRONOS5 core + .k2tm shard, read back through the

@@ -246,3 +246,41 @@ def test_reference_hadamard_q8_kv_attention_accuracy_case(oracle):
             a, b = got.astype(np.float64).reshape(-1), want.reshape(-1)
             cos = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
             assert cos > 0.99980, (hd, pos, cos)
+
+
+@pytest.mark.parametrize("gate", [True, False])
+def test_shared_expert_adds_its_output_before_the_routed_experts(oracle, gate):
+    """SharedMoeExpert::forward_single (sparse_moe.rs:254-314) in the oracle's MoE block against a composition of the oracle's
+    own primitives: the shared output (two NF projections around the scalar-exp SwiGLU, times the sigmoid gate) is what the
+    block starts from; a model without routed contribution (top-1 expert whose down scales are zero is not constructible
+    from files, so the routed part is compared through the model without a shared expert)."""
+    moe = dict(layers=[1], n_experts=4, top_k=2, d_ff=64, bits=4, sgc=1, shared=128, shared_gate=gate)
+    spec = km.build(oracle, km.MOE_TINY, "b4", seed=23, moe=moe)
+    plain = km.build(oracle, km.MOE_TINY, "b4", seed=23, moe=dict(moe, shared=0))
+    a, b = oracle.Model(spec), oracle.Model(plain)
+    try:
+        h = km.MOE_TINY["hidden"]
+        hidden = np.random.Generator(np.random.PCG64(3)).standard_normal(h).astype(np.float32)
+        with_shared, routed = a.ffn_part(1, hidden), b.ffn_part(1, hidden)
+        ly = spec["layers"][1]
+        sh = ly["moe"]["shared"]
+        x_norm = (hidden * oracle.inv_rms(hidden, km.MOE_TINY["eps"])) * ly["post_norm"]
+        act = oracle.act_populate_fwht(x_norm)
+        gu = oracle.gemv(sh["gate_up"], act).reshape(-1)
+        g, u = gu[:128], gu[128:]
+        sw = ((g / (np.float32(1) + np.exp(-g.astype(np.float64)).astype(np.float32))) * u).astype(np.float32)
+        out = oracle.gemv(sh["down"], oracle.act_populate_fwht(sw)).reshape(-1)
+        if gate:
+            z = oracle.dot_f32(sh["gate_w"], x_norm)
+            scale = np.float32(1) / (np.float32(1) + np.float32(np.exp(-np.float64(z))))
+            out = (out * scale).astype(np.float32)
+        # (shared + w0 e0) + w1 e1 against (0 + w0 e0) + w1 e1: equal up to the rounding of the two sums
+        assert np.allclose(with_shared - routed, out, rtol=0, atol=4e-6 * max(1.0, float(np.max(np.abs(with_shared)))))
+        assert float(np.linalg.norm(out)) > 1e-3          # the shared expert contributes
+        # no routed experts at all (expert parallel emulation, rank 1 of 2 holds no routed expert of this token or some): rank 0 carries the shared output
+        a.L.k2o_model_set_ep(a.h, 64, 0)                   # 64 ranks, rank 0: at most expert 0 is local
+        e, w = a.last_routes(1)
+        if 0 not in list(e):
+            assert np.array_equal(a.ffn_part(1, hidden), out)
+    finally:
+        a.close(); b.close()
