@@ -36,13 +36,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // The same for warps that are ahead of the chain warps and share their schedulers: the hardware may park the thread for
-// up to a microsecond per attempt and the loop sleeps between attempts, so waiting costs the running warps no issue slots.
+// up to a microsecond per attempt (it wakes as soon as the phase completes), so waiting costs the running warps few issue slots.
 __device__ __forceinline__ bool mbar_wait_bounded_idle(uint32_t bar, uint32_t parity) {
     uint32_t ok = 0;
     for (uint32_t spin = 0; spin < EXACT_WAIT_LIMIT && !ok; ++spin) {
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (!ok) __nanosleep(200);
     }
     return ok != 0;
 }
@@ -226,6 +225,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     __shared__ float s_o[HD];
     __shared__ float s_cb[16];
     __shared__ uint32_t s_fail;
+    __shared__ volatile uint32_t s_ready[4];       // direct mode: tiles whose value weights transposing warp w has written
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t qh = blockIdx.x, tok = blockIdx.y, G = a.group, kvh = qh / G, n_q = a.n_kv * G;
     // ring depth; transposing warps: the four that do not share a warp scheduler with a chain warp where that is possible
@@ -240,11 +240,15 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     const uint32_t tiles_t = (uint32_t)__cvta_generic_to_shared(dyn + 128 + (size_t)NST * Sm::STAGE);
     float *W = reinterpret_cast<float *>(dyn + Sm::W_OFF);
     const uint32_t w_stride = a.ctx_cap + 16;                                // floats between the weight vectors of the NF4 groups
+    // direct: the cache holds a block-transposed copy of the value rows (ExactAttnArgs.v_t): tiles land ready for the chains,
+    // the transposing warps only compute the value weights, and the chain warps free the ring stages themselves
+    const bool direct = !KV4 && a.v_t != nullptr && a.ring.window == 0;
     if (tid == 0) {
-        for (uint32_t s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_rows_free + 8 * s, NTW); }
+        for (uint32_t s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_rows_free + 8 * s, direct ? CW : NTW); }
         for (uint32_t s = 0; s < VAL_TBUF; ++s) { mbar_init(bar_t_full + 8 * s, NTW); mbar_init(bar_t_free + 8 * s, CW); }
         fence_mbar_init();
         s_fail = 0;
+        s_ready[0] = s_ready[1] = s_ready[2] = s_ready[3] = 0;
     }
     if (KV4 && tid < 16) s_cb[tid] = NF4_KV_CENTROIDS[tid];
     // The successor (the o_proj GEMV) is released when the chains reach their last two tiles, not here: its CTAs would sit
@@ -267,6 +271,12 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
         const uint32_t st = i % NST, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
         const uint32_t dst = (uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE);
         fence_proxy_async();
+        if (direct) {          // blocks of 16 positions x head_dim x 16 bytes, contiguous: one copy (whole blocks; the rows past ctx are unused)
+            const uint32_t bytes = ((n + 15) / 16) * 16 * ROW;
+            mbar_expect_tx(bar_full + 8 * st, bytes);
+            bulk_g2s(dst, reinterpret_cast<const uint8_t *>(a.v_t) + slot0 * ROW + (size_t)tl * ROW, bytes, bar_full + 8 * st);
+            return;
+        }
         mbar_expect_tx(bar_full + 8 * st, n * ROW);
         // the rows of consecutive active positions are consecutive cache rows except where the sinks end and where the ring
         // wraps: one bulk copy per run (one run without a window)
@@ -342,15 +352,27 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     };
     constexpr uint32_t PRODUCER_WARP = VAL_THREADS / 32 - 1;
     bool failed = false;
+    const uint32_t li = tw * 32 + lane;                            // transposing warps: this lane's position within a tile (and li + NTW * 32)
+    constexpr uint32_t PER = (VAL_TILE + NTW * 32 - 1) / (NTW * 32);
+    float sc_first[4][PER];
     if (warp == 0) {
         float acc = softmax_body_sum((uint32_t)__cvta_generic_to_shared(W), n4, lane);
         if (lane == 0) {
             for (uint32_t t2 = n4; t2 < ctx; ++t2) acc = __fadd_rn(acc, W[t2]);
             s_inv = __fdiv_rn(1.0f, acc);
         }
-    } else if (is_tw) {
+    } else if (is_tw && direct) {
+        // the value scales of the first four tiles are requested while the denominator is summed
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+            for (uint32_t k = 0; k < PER; ++k) {
+                const uint32_t t = u * VAL_TILE + li + k * NTW * 32;
+                sc_first[u][k] = (li + k * NTW * 32 < VAL_TILE && t < ctx) ? __ldcg(a.v_scale + slot0 + t) : 0.0f;
+            }
+    } else if (is_tw && !direct) {
         for (uint32_t i = 0; i < VAL_TBUF && i < n_tiles && !failed; ++i) failed = !transpose_tile(i);
-    } else if (warp == PRODUCER_WARP && lane == 0) {
+    } else if (warp == PRODUCER_WARP && lane == 0 && !direct) {
         for (uint32_t i = 0; i < VAL_TBUF && i < n_tiles && !failed; ++i) failed = !refill_after(i);
     }
     __syncthreads();
@@ -369,10 +391,18 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
             const uint32_t tb = i % VAL_TBUF, tl = i * VAL_TILE, n = min(VAL_TILE, ctx - tl);
             if (i + 2 >= n_tiles) pdl_trigger();       // one thread's call releases the CTA: only the chain warps call it
             const long long tw0 = clock64();
-            if (!mbar_wait_bounded(bar_t_full + 8 * tb, (i / VAL_TBUF) & 1u)) { failed = true; break; }
+            const uint32_t st = i % NST;
+            if (direct) {          // the tile's weights (the weight warps run ahead through all tiles) and its bytes
+                uint32_t spin = 0;
+                while (min(min(s_ready[0], s_ready[1]), min(s_ready[2], s_ready[3])) <= i && ++spin < EXACT_WAIT_LIMIT) {}
+                __threadfence_block();
+                if (spin >= EXACT_WAIT_LIMIT || !mbar_wait_bounded(bar_full + 8 * st, (i / NST) & 1u)) { failed = true; break; }
+            } else if (!mbar_wait_bounded(bar_t_full + 8 * tb, (i / VAL_TBUF) & 1u)) { failed = true; break; }
             t_wait += clock64() - tw0;
-            const uint32_t row = tiles_t + tb * Sm::TILE_T + d * VAL_TILE, wa = wa0 + 4 * tl;
-            auto chunk_at = [&](uint32_t b) { return row + (((b & ~7u) | ((b ^ fd) & 7u)) << 4); };
+            const uint32_t wa = wa0 + 4 * tl;
+            // transposed tile: row d, swizzled chunks; direct: the ring stage as it landed, block b = [dimension][16]
+            const uint32_t row = direct ? (uint32_t)__cvta_generic_to_shared(stages + (size_t)st * Sm::STAGE) + d * 16 : tiles_t + tb * Sm::TILE_T + d * VAL_TILE;
+            auto chunk_at = [&](uint32_t b) { return direct ? row + b * (HD * 16) : row + (((b & ~7u) | ((b ^ fd) & 7u)) << 4); };
             const uint32_t n_full = n / 16, rem = n % 16;
             uint4 x = lds_u32x4(chunk_at(0));
             float4 w0 = lds_f32x4(wa), w1 = lds_f32x4(wa + 16), w2 = lds_f32x4(wa + 32), w3 = lds_f32x4(wa + 48);
@@ -387,7 +417,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
             }
             if (rem != 0) o = value_chain16<KV4>(o, x, w0, w1, w2, w3, cbfa, rem);
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_t_free + 8 * tb);               // this warp is done with the tile
+            if (lane == 0) mbar_arrive(direct ? bar_rows_free + 8 * st : bar_t_free + 8 * tb);      // this warp is done with the tile
         }
         if (failed) atomicExch(&s_fail, 1u);
         if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) a.trace[8] = (unsigned long long)t_wait;
@@ -395,8 +425,6 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     } else if (is_tw) {
         // ---- transposing warps: tile by tile, the value weights (p * inv) * v_scale of its positions (per 64-value group for
         // the NF4 cache), then - from the third tile on - the transposition; the scales of the next tile are requested first
-        const uint32_t li = tw * 32 + lane;                        // this lane's position within a tile (and li + NTW * 32)
-        constexpr uint32_t PER = (VAL_TILE + NTW * 32 - 1) / (NTW * 32);
         const float *vs = a.v_scale + slot0;
         const uint16_t *vs16 = reinterpret_cast<const uint16_t *>(a.v_scale) + slot0 * NB;
         float sc_next[PER][KV4 ? NB : 1];
@@ -414,8 +442,34 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
                 }
             }
         };
-        if (n_tiles > 0) load_scales(0);
-        for (uint32_t i = 0; i < n_tiles && !failed; ++i) {
+        if (direct) {
+            // no tile buffers to wait for: the weights of ALL tiles, the scales of four tiles (eight loads per lane) requested
+            // at a time, each finished tile published through s_ready
+            const float *vsd = a.v_scale + slot0;
+            for (uint32_t i0 = 0; i0 < n_tiles; i0 += 4) {
+                float sc[4][PER];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+                    for (uint32_t k = 0; k < PER; ++k) {
+                        const uint32_t t = (i0 + u) * VAL_TILE + li + k * NTW * 32;
+                        sc[u][k] = i0 == 0 ? sc_first[u][k] : ((li + k * NTW * 32 < VAL_TILE && t < ctx) ? __ldcg(vsd + t) : 0.0f);
+                    }
+#pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    if (i0 + u >= n_tiles) break;
+#pragma unroll
+                    for (uint32_t k = 0; k < PER; ++k) {
+                        const uint32_t t = (i0 + u) * VAL_TILE + li + k * NTW * 32;
+                        if (li + k * NTW * 32 < VAL_TILE && t < ctx) W[t] = __fmul_rn(__fmul_rn(W[t], inv), sc[u][k]);
+                    }
+                    __syncwarp();
+                    if (lane == 0) { __threadfence_block(); s_ready[tw] = i0 + u + 1; }
+                }
+            }
+        }
+        if (n_tiles > 0 && !direct) load_scales(0);
+        for (uint32_t i = 0; i < n_tiles && !failed && !direct; ++i) {
             float sc_cur[PER][KV4 ? NB : 1];
 #pragma unroll
             for (uint32_t k = 0; k < PER; ++k)
@@ -441,7 +495,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
         }
         if (failed) atomicExch(&s_fail, 1u);
     } else if (warp == PRODUCER_WARP && lane == 0) {
-        for (uint32_t i = VAL_TBUF; i < n_tiles && !failed; ++i) failed = !refill_after(i);
+        for (uint32_t i = direct ? 0u : VAL_TBUF; i < n_tiles && !failed; ++i) failed = !refill_after(i);
         if (failed) atomicExch(&s_fail, 1u);
     }
     VAL_MARK(5);

@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
                 fa.out_q = A.act_q; fa.out_scales = A.act_s; fa.out_sums = A.act_m; fa.err_flag = A.err_flag;
                 fa.n_q = A.n_q; fa.n_kv = A.n_kv; fa.head_dim = A.head_dim; fa.max_seq = A.max_seq; fa.layer = l;
                 fa.eps = A.eps; fa.attn_scale = A.attn_scale; fa.qk_norm_after_rope = A.qk_norm_after_rope;
-                fa.kv_bits = A.kv_bits; fa.out_chunk0 = 0; fa.pos_offset = 0; fa.trace = nullptr;
+                fa.kv_bits = A.kv_bits; fa.out_chunk0 = 0; fa.pos_offset = 0; fa.trace = nullptr; fa.early = 0; fa.v_t = A.v_t;
                 attention_head_dispatch<false>(fa, blockIdx.x, pos, s.at);
             }
             tr.mark();

@@ -27,6 +27,7 @@ struct MegaArgs {
     float *hidden_a, *hidden_b, *proj, *qkv, *gate_up, *logits, *attn_tap;
     int8_t *act_q; float *act_s; int32_t *act_m;           // o_proj activation (written by the attention CTAs)
     int8_t *k_q8, *v_q8; float *k_scale, *v_scale;
+    int8_t *v_t;                 // block-transposed copy of the value rows (null when the engine keeps none)
     uint32_t *token, *pos, *step, *history;                // device scalars / token history
     uint32_t *barrier, *err_flag;                          // grid barrier counter (zero at launch), error word
     uint32_t first_token, pos0, n_steps;

@@ -57,6 +57,7 @@ struct KronosCudaEngine {
     bool split_kv = false;                    // long contexts by the split-KV kernels instead (config flag, or the cache is too long for the exact path)
     int32_t *act_m = nullptr;
     int8_t *k_q8 = nullptr, *v_q8 = nullptr;
+    int8_t *v_t = nullptr;      // int8 cache without a window: the value rows once more, transposed in 16-position blocks for the value chains
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
@@ -140,8 +141,8 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
     KronosCudaContext *ctx = e->ctx;
     KronosCudaEngineConfig &c = e->cfg;
     if (bits != 8 && bits != 4) return fail(ctx, "kv_bits must be 8 (int8 Hadamard cache) or 4 (NF4 Hadamard cache)");
-    for (void *p : {(void *)e->k_q8, (void *)e->v_q8, (void *)e->k_scale, (void *)e->v_scale, (void *)e->attn_sc, (void *)e->attn_bmax}) dev_free(e, p);
-    e->k_q8 = e->v_q8 = nullptr; e->k_scale = e->v_scale = e->attn_sc = e->attn_bmax = nullptr;
+    for (void *p : {(void *)e->k_q8, (void *)e->v_q8, (void *)e->v_t, (void *)e->k_scale, (void *)e->v_scale, (void *)e->attn_sc, (void *)e->attn_bmax}) dev_free(e, p);
+    e->k_q8 = e->v_q8 = e->v_t = nullptr; e->k_scale = e->v_scale = e->attn_sc = e->attn_bmax = nullptr;
     c.kv_bits = bits;
     if (window >= 8 && (uint64_t)window + 512u < c.max_seq_len) {
         e->ring.window = window;
@@ -170,7 +171,18 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
                         (cuda_ok(ctx, cudaMemsetAsync(e->k_q8, 0x88, slots * hd / 2, ctx->stream), "fill cache") &&
                          cuda_ok(ctx, cudaMemsetAsync(e->v_q8, 0x88, slots * hd / 2, ctx->stream), "fill cache"));
     for (cudaGraphExec_t &g : e->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }      // captured cache pointers are stale
-    return ok && filled;
+    // the transposed copy of the value rows (zero rows = 0x80 there); not for the NF4 cache, windows or the split-KV kernels
+    bool vt_ok = true;
+    if (ok && bits == 8 && e->ring.window == 0 && !e->split_kv)
+        vt_ok = dev_alloc(e, e->v_t, slots * hd) && cuda_ok(ctx, cudaMemsetAsync(e->v_t, 0x80, slots * hd, ctx->stream), "fill cache");
+    return ok && filled && vt_ok;
+}
+
+// after value rows came from the host (imported blobs, restored snapshots): bring the transposed copy up to date
+bool sync_vt(KronosCudaEngine *e) {
+    if (!e->v_t) return true;
+    const KronosCudaEngineConfig &c = e->cfg;
+    return cuda_ok(e->ctx, launch_vt_rebuild(e->ctx->stream, e->v_q8, e->v_t, (size_t)c.num_layers * c.num_key_value_heads, e->kv_stride, c.head_dim), "rebuild value copy");
 }
 
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
@@ -325,7 +337,7 @@ bool enqueue_attention_batch(KronosCudaEngine *e, uint32_t l, uint32_t T) {
     qa.pos = e->d_pos; qa.pos_offset = 0;
     qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
     qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
-    qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring;
+    qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring; qa.v_t = e->v_t;
     if (!count(e, launch_qkv_post(s, qa, e->pdl, T), "qkv_post")) return false;
     ExactAttnArgs xa{};
     xa.q_i8 = e->q_i8; xa.q_scale = e->q_scale; xa.k_q8 = e->k_q8; xa.v_q8 = e->v_q8; xa.k_scale = e->k_scale; xa.v_scale = e->v_scale;
@@ -335,7 +347,7 @@ bool enqueue_attention_batch(KronosCudaEngine *e, uint32_t l, uint32_t T) {
     xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
     xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
     xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
-    xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err; xa.trace = nullptr;
+    xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err; xa.trace = nullptr; xa.v_t = e->v_t;
     return count(e, launch_attention_exact(s, xa, e->pdl, T), "attention", 2);
 }
 
@@ -361,6 +373,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
             fa.eps = c.rms_norm_eps; fa.attn_scale = 1.0f / sqrtf((float)hd); fa.qk_norm_after_rope = c.qk_norm_after_rope;
             fa.kv_bits = c.kv_bits; fa.out_chunk0 = c.o_chunk0;
             fa.trace = (e->attn_trace && l == 0) ? e->d_dbg : nullptr;
+            fa.v_t = e->v_t;
             fa.early = T == 1 ? 1u : 0u;        // in a batch the launch before is the attention of the token before: it wrote a row this one reads
             if (!count(e, launch_attention_fused(s, fa, e->pdl), "attention")) return false;
         } else {
@@ -369,7 +382,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
             qa.pos = e->d_pos; qa.pos_offset = t;
             qa.q_i8 = e->q_i8; qa.q_scale = e->q_scale; qa.k_q8 = e->k_q8; qa.v_q8 = e->v_q8; qa.k_scale = e->k_scale; qa.v_scale = e->v_scale;
             qa.n_q = c.num_attention_heads; qa.n_kv = c.num_key_value_heads; qa.head_dim = hd; qa.max_seq = e->kv_stride; qa.layer = l;
-            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring;
+            qa.eps = c.rms_norm_eps; qa.qk_norm_after_rope = c.qk_norm_after_rope; qa.kv_bits = c.kv_bits; qa.ring = e->ring; qa.v_t = e->v_t;
             if (!count(e, launch_qkv_post(s, qa, e->pdl), "qkv_post")) return false;
             if (!e->split_kv) {
                 ExactAttnArgs xa{};
@@ -381,7 +394,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
                 xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
                 xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
                 xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err;
-                xa.trace = (e->attn_trace && l == 0) ? e->d_dbg + 16 : nullptr;
+                xa.trace = (e->attn_trace && l == 0) ? e->d_dbg + 16 : nullptr; xa.v_t = e->v_t;
                 return count(e, launch_attention_exact(s, xa, e->pdl), "attention", 2);
             }
             AttnArgs aa{};
@@ -622,7 +635,7 @@ bool decode_mega(KronosCudaEngine *e, uint32_t first_token, uint32_t pos_start, 
     fill_embed_args(e, a.embed);
     a.hidden_a = e->hidden2; a.hidden_b = e->hidden; a.proj = e->proj; a.qkv = e->qkv; a.gate_up = e->gate_up; a.logits = e->logits;
     a.attn_tap = e->attn_tap; a.act_q = e->act_q; a.act_s = e->act_s; a.act_m = e->act_m;
-    a.k_q8 = e->k_q8; a.v_q8 = e->v_q8; a.k_scale = e->k_scale; a.v_scale = e->v_scale;
+    a.k_q8 = e->k_q8; a.v_q8 = e->v_q8; a.k_scale = e->k_scale; a.v_scale = e->v_scale; a.v_t = e->v_t;
     a.token = e->d_token; a.pos = e->d_pos; a.step = e->d_step; a.history = e->d_history;
     a.barrier = e->d_barrier; a.err_flag = ctx->d_err;
     a.first_token = first_token; a.pos0 = pos_start; a.n_steps = n_steps;
@@ -1152,7 +1165,7 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, s
             !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd.data(), R * db, R * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
             !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks.data(), R * sb, R * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
             !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs.data(), R * sb, R * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
-            !sync_and_check(ctx, "kv_import"))
+            !sync_vt(e) || !sync_and_check(ctx, "kv_import"))
             return -1;
         return 0;
     }
@@ -1170,7 +1183,7 @@ int32_t kronos_cuda_engine_kv_import(KronosCudaEngine *e, const uint8_t *data, s
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd.data(), n * db, n * db, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks.data(), n * sb, n * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs.data(), n * sb, n * sb, heads, cudaMemcpyHostToDevice, st), "kv_import") ||
-        !sync_and_check(ctx, "kv_import"))
+        !sync_vt(e) || !sync_and_check(ctx, "kv_import"))
         return -1;
     return 0;
 }
@@ -1266,7 +1279,7 @@ int32_t kronos_cuda_engine_restore_kv_prefix(KronosCudaEngine *e, const uint8_t 
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_q8, S * db, vd, slots * db, cp * db, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->k_scale, S * sb, ks, slots * sb, cp * sb, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
         !cuda_ok(ctx, cudaMemcpy2DAsync(e->v_scale, S * sb, vs, slots * sb, cp * sb, heads, cudaMemcpyHostToDevice, st), "restore_kv_prefix") ||
-        !sync_and_check(ctx, "restore_kv_prefix"))
+        !sync_vt(e) || !sync_and_check(ctx, "restore_kv_prefix"))
         return -1;
     return 0;
 }

@@ -538,12 +538,18 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
             const bool zero = mx <= 1.1920929e-07f;
             const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx), scale = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
             int8_t *cache = reinterpret_cast<int8_t *>(const_cast<uint8_t *>(warp == 1 ? K : V)) + (size_t)pos * HD;
+            // value rows also go to the block-transposed copy the long-context chains read (ExactAttnArgs.v_t)
+            int8_t *vt = (store && warp == 2 && A.v_t != nullptr) ? A.v_t + slot0 * HD + (size_t)(pos / 16) * HD * 16 + pos % 16 : nullptr;
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
                 const char2 pk = make_char2((signed char)q0, (signed char)q1);
                 reinterpret_cast<char2 *>(s.hq + warp * 128 + b * 64)[lane] = pk;
                 if (store) reinterpret_cast<char2 *>(cache + b * 64)[lane] = pk;
+                if (vt != nullptr) {
+                    vt[(b * 64 + 2 * lane) * 16] = (int8_t)(q0 ^ 0x80);
+                    vt[(b * 64 + 2 * lane + 1) * 16] = (int8_t)(q1 ^ 0x80);
+                }
             }
             if (lane == 0) {
                 s.hs[warp] = scale;

@@ -427,11 +427,39 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     }
     const bool zero = mx <= 1.1920929e-07f;
     const float inv = zero ? 0.0f : __fdiv_rn(127.0f, mx);
+    // value rows also go to the block-transposed copy the value chains read ([position / 16][dimension][16], sign flipped)
+    int8_t *vt = nullptr;
+    if (!is_q && !is_k && a.v_t != nullptr) {
+        const uint32_t kvh = head - a.n_q - a.n_kv, row = a.ring.slot_of_pos(pos);
+        vt = a.v_t + ((size_t)a.layer * a.n_kv + kvh) * a.max_seq * hd + (size_t)(row / 16) * hd * 16 + row % 16;
+    }
     for (uint32_t b = 0; b < nb; ++b) {
         const int q0 = zero ? 0 : __float2int_rn(__fmul_rn(v0[b], inv)), q1 = zero ? 0 : __float2int_rn(__fmul_rn(v1[b], inv));
         reinterpret_cast<char2 *>(dst_q + b * 64)[lane] = make_char2((signed char)q0, (signed char)q1);
+        if (vt != nullptr) {
+            vt[(b * 64 + 2 * lane) * 16] = (int8_t)(q0 ^ 0x80);
+            vt[(b * 64 + 2 * lane + 1) * 16] = (int8_t)(q1 ^ 0x80);
+        }
     }
     if (lane == 0) *dst_s = zero ? 0.0f : __fdiv_rn(mx, 127.0f);
+}
+
+// v_t <- v_q8 for whole heads: thread = four dimensions of one cached row
+__global__ void __launch_bounds__(256) vt_rebuild_kernel(const int8_t *__restrict__ v_q8, int8_t *__restrict__ v_t, size_t n_words, uint32_t rows_per_head,
+                                                         uint32_t hd) {
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n_words; i += (size_t)gridDim.x * 256) {
+        const size_t slot = i / (hd / 4), head = slot / rows_per_head;
+        const uint32_t d0 = (uint32_t)(i % (hd / 4)) * 4, row = (uint32_t)(slot % rows_per_head);
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(v_q8 + slot * hd + d0) ^ 0x80808080u;
+        int8_t *dst = v_t + head * rows_per_head * hd + (size_t)(row / 16) * hd * 16 + row % 16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dst[(d0 + k) * 16] = (int8_t)((w >> (8 * k)) & 0xffu);
+    }
+}
+cudaError_t launch_vt_rebuild(cudaStream_t s, const int8_t *v_q8, int8_t *v_t, size_t heads, uint32_t rows_per_head, uint32_t head_dim) {
+    const size_t n_words = heads * rows_per_head * (head_dim / 4);
+    const unsigned grid = (unsigned)std::min<size_t>((n_words + 255) / 256, 148 * 16);
+    return launch_kernel(vt_rebuild_kernel, dim3(grid), dim3(256), 0, s, false, v_q8, v_t, n_words, rows_per_head, head_dim);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -54,6 +54,7 @@ struct QkvPostArgs {
     float eps;
     int32_t qk_norm_after_rope;
     KvRing ring;                 // where the position's cache row lives
+    int8_t *v_t;                 // optional second copy of the int8 value rows, transposed in 16-position blocks (see ExactAttnArgs)
 };
 
 // Contexts up to this many positions are attended by the single fused kernel; longer ones by the three-kernel path in
@@ -93,6 +94,11 @@ struct ExactAttnArgs {           // attention in the reference's summation order
     uint32_t *err_flag;
     unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (8 words)
     KvRing ring;                 // sliding window: active positions and their cache rows; scores then follow causal_gqa_group_q4_or_window for both cache formats
+    // int8 cache without a window: a second copy of the value rows laid out for the chains, per (layer, kv head)
+    // [position / 16][dimension][16 positions], bytes stored with the sign bit flipped (b ^ 0x80).  A 256-position tile is
+    // one contiguous run, and dimension d's chain reads sixteen positions per 16-byte load straight from the landed tile -
+    // no transposing pass through shared memory.  Null: the kernel transposes the row-major rows itself.
+    const int8_t *v_t;
 };
 
 struct FusedAttnArgs {           // one layer's attention from the fused qkv vector to the o_proj activation
@@ -113,6 +119,7 @@ struct FusedAttnArgs {           // one layer's attention from the fused qkv vec
     unsigned long long *trace;   // optional diagnostic: SM clock readings of query head 0 at the phase boundaries (16 words)
     uint32_t early;              // 1: the launch before this one wrote nothing this kernel prefetches (position word, cache rows of
                                  // earlier positions), so those loads are issued before the dependency wait
+    int8_t *v_t;                 // optional block-transposed copy of the value rows (ExactAttnArgs.v_t): the new row is stored there too
 };
 
 struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scoring (sparse_moe.rs:86-182)
@@ -172,6 +179,8 @@ cudaError_t launch_moe_combine(cudaStream_t s, const float *expert_out, const fl
 // sigmoid gate of a shared expert, one value per token of the batch
 cudaError_t launch_shared_gate(cudaStream_t s, const float *gate_w, const float *x_norm, uint32_t n, uint32_t n_tok, float *scale, bool pdl);
 cudaError_t launch_advance_pos(cudaStream_t s, uint32_t *pos, uint32_t by, bool pdl);
+// rebuilds the block-transposed value copy from the row-major int8 value rows (after rows were imported from the host)
+cudaError_t launch_vt_rebuild(cudaStream_t s, const int8_t *v_q8, int8_t *v_t, size_t heads, uint32_t rows_per_head, uint32_t head_dim);
 // one thread that waits about `ns` nanoseconds (bounded): lets a host queue work behind it (measurement only)
 cudaError_t launch_delay(cudaStream_t s, uint64_t ns);
 
