@@ -53,7 +53,7 @@ static TeamShape choose_team(uint32_t n_rb, uint32_t np, uint32_t warp_bytes, ui
 template <int FMT, int NT, bool DOTS>
 static cudaError_t launch_one(cudaStream_t stream, const GemvArgs &a, int sm_count) {
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
-    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(NT), NT * 32 * 4, 1, sm_count);
+    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(NT), NT * 32 * 4 + 16, 1, sm_count);      // hand-off array + turn counter
     cudaError_t e = cudaSuccess;
     e = allow_dynamic_smem(reinterpret_cast<const void *>(gemv_kernel<FMT, NT, DOTS>), t.smem);
     if (e != cudaSuccess) return e;
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) gemv_expert_kernel(GemvArgs a, const Expe
 template <int FMT>
 static cudaError_t launch_expert_fmt(cudaStream_t stream, const GemvArgs &a, const ExpertBatch &b, uint32_t n_slot, int sm_count) {
     const uint32_t n_rb = (a.rows + RS - 1) / RS, np = (a.nc + 31) / 32;
-    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(1), 32 * 4, n_slot, sm_count);
+    const TeamShape t = choose_team(n_rb, np, warp_smem<FMT>(1), 32 * 4 + 16, n_slot, sm_count);
     cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(gemv_expert_kernel<FMT>), t.smem);
     if (e != cudaSuccess) return e;
     return launch_kernel(gemv_expert_kernel<FMT>, dim3(t.teams, n_slot), dim3(32 * t.wk), t.smem, stream, a.pdl != 0, a, b);

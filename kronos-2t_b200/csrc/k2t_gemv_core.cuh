@@ -361,6 +361,18 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
     if (!MEGA) { pdl_wait(); pdl_trigger(); }
     hook();
 
+    // Teams of the stand-alone kernels pass the fp32 chain from pass to pass by TURN: a counter behind the hand-off array
+    // holds the number of chain steps done; the warp that owns pass p of group g waits for g * np + p, runs its step and
+    // publishes the next number.  Unlike a team barrier per step this lets the other warps go on with the dot products of
+    // their next pass while one warp is on the chain (the steps themselves stay serial: each starts from its predecessor's sum):
+    // a 3584 x 18944 b5 launch (ten passes, teams of four) 16.6 -> 14.7 us.
+    volatile uint32_t *s_turn = reinterpret_cast<volatile uint32_t *>(s_f + NT * 32);
+    const bool by_turn = !MEGA && WK > 1 && rounds > 1;       // one round: nothing to overlap, and a barrier costs the waiting warps no issue slots
+    if (by_turn) {
+        if (wid == 0 && lane == 0) *s_turn = 0;
+        team_sync(bar_id, WK);
+    }
+
     // ---- consumer
     int q[NT][16];
     float sx[NT];
@@ -459,7 +471,14 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
             }
             // fp32 chain over the chunks of the passes of this round, in pass order: warp k continues
             // where warp k-1 stopped (f travels through s_f); lane -> row slot
-            for (uint32_t k = 0; k < WK; ++k) {
+            if (by_turn && has) {           // wait for this pass's turn on the chain (bounded)
+                const uint32_t turn = (j0 / GB) * np + p;
+                uint32_t spin = 0;
+                while (*s_turn != turn && ++spin < WAIT_LIMIT) {}
+                if (spin >= WAIT_LIMIT && lane == 0) atomicExch(a.err_flag, 1u);
+                __threadfence_block();
+            }
+            for (uint32_t k = by_turn ? wid : 0; k < (by_turn ? wid + 1 : WK); ++k) {
                 if (k == wid && has && slot_j < in_group) {
                     const uint32_t row = (gw + (j0 + slot_j) * nw) * RS + slot_r;
 #pragma unroll
@@ -478,7 +497,10 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, const int8_t *xq, c
                         else s_f[t * 32 + lane] = ft;
                     }
                 }
-                if (WK > 1) team_sync(bar_id, WK);
+                if (by_turn) {
+                    __syncwarp();
+                    if (has && lane == 0) { __threadfence_block(); *s_turn = (j0 / GB) * np + p + 1; }
+                } else if (WK > 1) team_sync(bar_id, WK);
                 else __syncwarp();
             }
         }

@@ -149,6 +149,35 @@ def test_host_embeddings_equal_device_lookup(ctx, oracle):
         eng.close(); ref.close()
 
 
+def test_imported_session_continues_beyond_512_positions(ctx, oracle):
+    """A session of 560 positions moved into a fresh engine (kv_import, then save / restore of a prefix snapshot): the rows the
+    host wrote are also what the long-context value chains read (their block-transposed copy is rebuilt), so the engine goes
+    on exactly as the oracle does."""
+    import kronos_2t_b200 as k2
+    spec, eng, ref = make(ctx, oracle, LONG4, "b5", seed=31)
+    eng2 = k2.Engine(ctx, spec)
+    try:
+        rng = np.random.Generator(np.random.PCG64(8))
+        tokens = [int(t) for t in rng.integers(0, LONG4["vocab"], 580)]
+        for t in tokens[:560]:
+            ref.forward_token(t, 4)
+        blob = ref.kv_export(0, 560)
+        eng2.kv_import(blob, 560)                                    # rows from the CPU engine
+        want = np.stack([ref.forward_token(t, 4) for t in tokens[560:570]])
+        assert np.array_equal(eng2.forward_token_ids(tokens[560:570], pos_start=560, want_all=True), want)
+        snap = eng2.save_kv_prefix(570, 570)
+        eng.restore_kv_prefix(snap)                                  # and through a prefix snapshot into another engine
+        want = np.stack([ref.forward_token(t, 4) for t in tokens[570:580]])
+        assert np.array_equal(eng.forward_token_ids(tokens[570:580], pos_start=570, want_all=True), want)
+        got = eng.decode_greedy(int(np.argmax(want[-1])), 580, 8)
+        tok, out = int(np.argmax(want[-1])), []
+        for _ in range(8):
+            tok = oracle.argmax(ref.forward_token(tok, 4)); out.append(tok)
+        assert list(got) == out
+    finally:
+        eng.close(); eng2.close(); ref.close()
+
+
 def _greedy_check(eng, ref, prompt, steps):
     want, want_logits = ref.greedy(prompt, steps, threads=8)
     if len(prompt) > 1:
