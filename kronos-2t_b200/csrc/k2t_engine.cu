@@ -298,7 +298,7 @@ bool enqueue_fused_step(KronosCudaEngine *e, bool embed, Tail tail, bool long_ct
             RouterArgs ra{};
             ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm;
             ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
-            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done;
+            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done; ra.err_flag = e->ctx->d_err;
             if (!count(e, launch_moe_router(s, ra, pdl), "router")) return false;
             if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, ra.route_ids, k, e->act_q, e->act_s, e->act_m, 0, 0,
                                               e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, pdl, c.moe_num_experts), "expert gate_up")) return false;
@@ -461,7 +461,7 @@ bool enqueue_batch(KronosCudaEngine *e, uint32_t T, bool embed, Tail tail, bool 
             RouterArgs ra{};
             ra.w = L.router_w; ra.bias = L.router_bias; ra.x = e->x_norm;
             ra.n_experts = c.moe_num_experts; ra.hidden = h; ra.top_k = k; ra.norm_topk = (int32_t)(c.moe_norm_topk & 1u); ra.scoring = c.moe_norm_topk >> 8;
-            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done; ra.route_stride = 32;
+            ra.route_ids = L.d_route_ids; ra.route_w = L.d_route_w; ra.logits = e->router_logits; ra.done = e->router_done; ra.route_stride = 32; ra.err_flag = e->ctx->d_err;
             if (!count(e, launch_moe_router(s, ra, e->pdl, T), "router")) return false;
             if (!count(e, launch_gemv_experts(s, L.gu_dm, L.gu_fmt, L.d_gu_books, L.d_gu_bases, L.d_route_ids, T * k, e->act_q, e->act_s, e->act_m, h, h / 64,
                                               e->moe_gu, (size_t)2 * dff, e->ctx->sm_count, e->ctx->d_err, e->pdl, c.moe_num_experts, k, 32, k), "expert gate_up")) return false;

@@ -179,7 +179,8 @@ __device__ __forceinline__ float exp_cr(float x) { return (float)exp((double)x);
 constexpr uint32_t ROUTER_THREADS = 128, ROUTER_MAX_EXPERTS = 256, ROUTER_MAX_TOPK = 32;
 constexpr uint32_t ROUTER_EXPERTS_PER_CTA = ROUTER_THREADS / 16;
 __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a) {
-    extern __shared__ float s_xr[];          // hidden floats
+    extern __shared__ __align__(128) float s_dyn[];      // x [hidden], then (staged form) the CTA's eight router rows [8][hidden + 16]
+    float *s_xr = s_dyn;
     {   // blockIdx.y = token of the batch
         const size_t t = blockIdx.y;
         a.x += t * a.hidden; a.logits += t * a.n_experts; a.done += t; a.route_ids += t * a.route_stride; a.route_w += t * a.route_stride;
@@ -189,18 +190,67 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
     __shared__ uint32_t s_sel_e[ROUTER_MAX_TOPK];
     __shared__ float s_max;
     __shared__ uint32_t s_last;
+    __shared__ __align__(8) uint64_t s_bar;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, half = lane >> 4, l16 = lane & 15;
+    // The router rows are weights: the CTA's eight rows are requested (one bulk copy each) BEFORE the dependency wait, so the
+    // megabyte of router weights of a layer streams in while the norm kernel in front still runs.  (Read by the lanes from
+    // global memory after the wait, 16 loads in flight per lane, the whole grid had 128 KB in flight: 15 us per layer for
+    // 128 experts of 2048.)  staged = 0: the rows do not fit shared memory, the lanes read them from global memory.
+    const uint32_t row_pitch = a.hidden + 16;             // floats: the two half-warps of a warp read different banks
+    const uint32_t e0 = blockIdx.x * ROUTER_EXPERTS_PER_CTA;
+    const uint32_t n_mine = e0 < a.n_experts ? min(ROUTER_EXPERTS_PER_CTA, a.n_experts - e0) : 0;
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&s_bar);
+    if (a.staged && tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+        fence_proxy_async();
+        mbar_expect_tx(bar, n_mine * a.hidden * 4);
+        for (uint32_t j = 0; j < n_mine; ++j)
+            bulk_g2s((uint32_t)__cvta_generic_to_shared(s_dyn + a.hidden + (size_t)j * row_pitch), a.w + (size_t)(e0 + j) * a.hidden, a.hidden * 4, bar);
+    }
+    // No early release of the successor: it is the expert-batched GEMV, which cannot request a byte before it has read the
+    // routes this kernel writes, so its CTAs would only sit on the SMs (and slow the warps running there) until then.
     pdl_wait();
-    pdl_trigger();
-    for (uint32_t i = tid; i < a.hidden; i += ROUTER_THREADS) s_xr[i] = __ldcg(a.x + i);
+#ifdef K2T_ROUTER_DEBUG
+    unsigned long long dbg_t[8]; int dbg_n = 0;
+#define RDBG() do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); dbg_t[dbg_n++] = t_; } while (0)
+#else
+#define RDBG() do {} while (0)
+#endif
+    RDBG();
+    {   // x: 16-byte loads, four in flight per thread (one load per loop trip cost an L2 round trip each)
+        const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+        const uint32_t n4 = a.hidden / 4;
+        uint32_t i = tid;
+        for (; i + 3 * ROUTER_THREADS < n4; i += 4 * ROUTER_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldcg(x4 + i + u * ROUTER_THREADS);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) reinterpret_cast<float4 *>(s_xr)[i + u * ROUTER_THREADS] = v[u];
+        }
+        for (; i < n4; i += ROUTER_THREADS) reinterpret_cast<float4 *>(s_xr)[i] = __ldcg(x4 + i);
+    }
     __syncthreads();
+    bool copy_failed = false;
+    if (a.staged && n_mine > 0) {
+        uint32_t ok = 0;
+        for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) ok = mbar_try_wait(bar, 0);
+        copy_failed = !ok;
+    }
     {
-        const uint32_t e = blockIdx.x * ROUTER_EXPERTS_PER_CTA + warp * 2 + half;
+        const uint32_t e = e0 + warp * 2 + half;
         float acc = 0.0f;
-        if (e < a.n_experts) {
-            const float *row = a.w + (size_t)e * a.hidden;
+        if (e < a.n_experts && !copy_failed) {
+            if (a.staged) {
+                const float *row = s_dyn + a.hidden + (size_t)(warp * 2 + half) * row_pitch;
 #pragma unroll 16
-            for (uint32_t i = l16; i < a.hidden; i += 16) acc = __fmaf_rn(__ldg(row + i), s_xr[i], acc);
+                for (uint32_t i = l16; i < a.hidden; i += 16) acc = __fmaf_rn(row[i], s_xr[i], acc);
+            } else {
+                const float *row = a.w + (size_t)e * a.hidden;
+#pragma unroll 16
+                for (uint32_t i = l16; i < a.hidden; i += 16) acc = __fmaf_rn(__ldg(row + i), s_xr[i], acc);
+            }
         }
         float t = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));      // within each half: lanes 0..3 and 8..11
         t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 8));
@@ -208,11 +258,14 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2));
         if (l16 == 0 && e < a.n_experts) a.logits[e] = a.bias != nullptr ? __fadd_rn(t, __ldg(a.bias + e)) : t;
     }
+    if (__syncthreads_or(copy_failed) && tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
+    RDBG();
     __threadfence();
     __syncthreads();
     if (tid == 0) s_last = atomicAdd(a.done, 1u) + 1u == gridDim.x ? 1u : 0u;       // per token: its own counter
     __syncthreads();
     if (s_last == 0) return;
+    RDBG();
     __threadfence();
     if (tid == 0) *a.done = 0;               // ready for the next launch (launches of a stream do not overlap here)
     for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __ldcg(a.logits + e);
@@ -241,6 +294,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __fmul_rn(s_z[e], inv_all);
         __syncthreads();
     }
+    RDBG();
     const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
     // Non-finite scores (a NaN ranks before nothing and after nothing) can leave ranks unassigned: every slot starts as
     // a valid route (expert i, weight 0), so the expert kernels never see an id outside [0, n_experts).
@@ -256,10 +310,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         if (rank < k) { s_sel_e[rank] = e; s_sel_w[rank] = sc; }
     }
     __syncthreads();
+    RDBG();
     if (tid == 0) {
-        uint32_t ids[ROUTER_MAX_TOPK];
-        float w[ROUTER_MAX_TOPK];
-        for (uint32_t i = 0; i < k; ++i) { ids[i] = s_sel_e[i]; w[i] = s_sel_w[i]; }
+        // in place in shared memory (k is small; private arrays indexed by loop variables would live in local memory)
+        uint32_t *ids = s_sel_e;
+        float *w = s_sel_w;
         if (a.scoring == 1) {                 // k-way softmax over the selected logits, in selection order
             float max_z = -INFINITY, sum = 0.0f;
             for (uint32_t i = 0; i < k; ++i) max_z = fmaxf(max_z, w[i]);
@@ -278,6 +333,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
             ids[j] = ce; w[j] = cw;
         }
         for (uint32_t i = 0; i < k; ++i) { a.route_ids[i] = min(ids[i], a.n_experts - 1u); a.route_w[i] = w[i]; }
+#ifdef K2T_ROUTER_DEBUG
+        RDBG();
+        static __device__ int shown = 0;
+        if (atomicAdd(&shown, 1) % 97 == 50) printf("router ns: x+dots %llu, to-last %llu, scores %llu, ranks %llu, final %llu\n", dbg_t[1] - dbg_t[0], dbg_t[2] - dbg_t[1], dbg_t[3] - dbg_t[2], dbg_t[4] - dbg_t[3], dbg_t[5] - dbg_t[4]);
+#endif
     }
 }
 
@@ -287,8 +347,7 @@ __global__ void __launch_bounds__(256) expert_swiglu_quant_kernel(const float *_
                                                                   int8_t *__restrict__ q, float *__restrict__ scales,
                                                                   int32_t *__restrict__ sums) {
     const uint32_t lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5), nc = d_ff / 64;
-    pdl_wait();
-    pdl_trigger();
+    pdl_wait();                // the successor (an expert-batched GEMV) is released when this kernel's CTAs exit, see moe_router_kernel
     if (c >= nc) return;
     const size_t slot = blockIdx.y;
     gate_up += slot * 2 * d_ff; q += slot * d_ff; scales += slot * nc; sums += slot * nc;
@@ -928,9 +987,13 @@ cudaError_t launch_rmsnorm_quant(cudaStream_t s, float *hidden, const float *del
                                  int8_t *q, float *scales, int32_t *sums, uint32_t n_tok, bool pdl) {
     return launch_rmsnorm_quant_x(s, hidden, delta, w, n, eps, q, scales, sums, nullptr, n_tok, pdl);
 }
-cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a, bool pdl, uint32_t n_tok) {
+cudaError_t launch_moe_router(cudaStream_t s, const RouterArgs &a_in, bool pdl, uint32_t n_tok) {
+    RouterArgs a = a_in;
     if (a.n_experts > ROUTER_MAX_EXPERTS || a.top_k > ROUTER_MAX_TOPK || a.hidden * 4 > 160 * 1024) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)a.hidden * 4;
+    // staged form: x and the CTA's eight rows in shared memory (rows padded by 16 floats); needs 16-byte rows
+    const size_t staged_bytes = ((size_t)a.hidden + (size_t)ROUTER_EXPERTS_PER_CTA * (a.hidden + 16)) * 4;
+    a.staged = (a.hidden % 4 == 0 && staged_bytes <= 200 * 1024 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0) ? 1u : 0u;
+    const size_t smem = a.staged ? staged_bytes : (size_t)a.hidden * 4;
     {
         cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(moe_router_kernel), smem + 4096);      // beside 3 KiB of static shared memory
         if (e != cudaSuccess) return e;

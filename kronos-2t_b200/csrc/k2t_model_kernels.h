@@ -134,6 +134,8 @@ struct RouterArgs {              // DenseMoeRouter::route_sorted, softmax scorin
     uint32_t *done;              // scratch: CTAs that have written their logits (zero between launches)
     // batches (grid.y = token t): x + t * hidden, route_ids / route_w + t * route_stride, logits + t * n_experts, done + t
     uint32_t route_stride;
+    uint32_t staged;             // set by the launcher: the CTA's router rows are bulk-copied to shared memory before the dependency wait
+    uint32_t *err_flag;          // device error word (1 = a bounded wait for a bulk copy gave up); may be null
 };
 
 // pdl: launch as a programmatic dependent of the previous kernel in the stream (see pdl_wait in k2t_device.cuh).
