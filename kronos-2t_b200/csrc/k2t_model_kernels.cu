@@ -211,13 +211,6 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
     // No early release of the successor: it is the expert-batched GEMV, which cannot request a byte before it has read the
     // routes this kernel writes, so its CTAs would only sit on the SMs (and slow the warps running there) until then.
     pdl_wait();
-#ifdef K2T_ROUTER_DEBUG
-    unsigned long long dbg_t[8]; int dbg_n = 0;
-#define RDBG() do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); dbg_t[dbg_n++] = t_; } while (0)
-#else
-#define RDBG() do {} while (0)
-#endif
-    RDBG();
     {   // x: 16-byte loads, four in flight per thread (one load per loop trip cost an L2 round trip each)
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         const uint32_t n4 = a.hidden / 4;
@@ -259,13 +252,11 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         if (l16 == 0 && e < a.n_experts) a.logits[e] = a.bias != nullptr ? __fadd_rn(t, __ldg(a.bias + e)) : t;
     }
     if (__syncthreads_or(copy_failed) && tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
-    RDBG();
     __threadfence();
     __syncthreads();
     if (tid == 0) s_last = atomicAdd(a.done, 1u) + 1u == gridDim.x ? 1u : 0u;       // per token: its own counter
     __syncthreads();
     if (s_last == 0) return;
-    RDBG();
     __threadfence();
     if (tid == 0) *a.done = 0;               // ready for the next launch (launches of a stream do not overlap here)
     for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __ldcg(a.logits + e);
@@ -294,7 +285,6 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         for (uint32_t e = tid; e < a.n_experts; e += ROUTER_THREADS) s_z[e] = __fmul_rn(s_z[e], inv_all);
         __syncthreads();
     }
-    RDBG();
     const uint32_t k = min(min(a.top_k, a.n_experts), ROUTER_MAX_TOPK);
     // Non-finite scores (a NaN ranks before nothing and after nothing) can leave ranks unassigned: every slot starts as
     // a valid route (expert i, weight 0), so the expert kernels never see an id outside [0, n_experts).
@@ -310,7 +300,6 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
         if (rank < k) { s_sel_e[rank] = e; s_sel_w[rank] = sc; }
     }
     __syncthreads();
-    RDBG();
     if (tid == 0) {
         // in place in shared memory (k is small; private arrays indexed by loop variables would live in local memory)
         uint32_t *ids = s_sel_e;
@@ -333,11 +322,6 @@ __global__ void __launch_bounds__(ROUTER_THREADS) moe_router_kernel(RouterArgs a
             ids[j] = ce; w[j] = cw;
         }
         for (uint32_t i = 0; i < k; ++i) { a.route_ids[i] = min(ids[i], a.n_experts - 1u); a.route_w[i] = w[i]; }
-#ifdef K2T_ROUTER_DEBUG
-        RDBG();
-        static __device__ int shown = 0;
-        if (atomicAdd(&shown, 1) % 97 == 50) printf("router ns: x+dots %llu, to-last %llu, scores %llu, ranks %llu, final %llu\n", dbg_t[1] - dbg_t[0], dbg_t[2] - dbg_t[1], dbg_t[3] - dbg_t[2], dbg_t[4] - dbg_t[3], dbg_t[5] - dbg_t[4]);
-#endif
     }
 }
 
