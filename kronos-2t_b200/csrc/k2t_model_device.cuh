@@ -371,10 +371,7 @@ __device__ __forceinline__ float value_chain16(float o, const uint4 x, const flo
     return o;
 }
 
-#ifndef K2T_CUT_AT
-#define K2T_CUT_AT 99
-#endif
-#define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); if (K2T_CUT_AT == (i)) return; } while (0)
+#define ATTN_MARK(i) do { if (A.trace != nullptr && qh == 0 && threadIdx.x == 0) A.trace[i] = (unsigned long long)clock64(); } while (0)
 
 template <int HD, bool KV4, bool STAGED>
 __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, int pdl_mode) {
@@ -848,10 +845,6 @@ __device__ __noinline__ void attention_head_cta(const FusedAttnArgs &A, uint32_t
 // runtime dispatch on head_dim / cache format
 template <bool STAGED>
 __device__ __forceinline__ void attention_head_dispatch(const FusedAttnArgs &A, uint32_t qh, uint32_t pos, const AttnSmem &s, int pdl_mode = 0) {
-#ifdef K2T_PROBE_HD
-    attention_head_cta<K2T_PROBE_HD, K2T_PROBE_KV4 != 0, STAGED>(A, qh, pos, s, pdl_mode);
-    return;
-#endif
     if (A.kv_bits == 4) {
         if (A.head_dim == 64) attention_head_cta<64, true, STAGED>(A, qh, pos, s, pdl_mode);
         else attention_head_cta<128, true, STAGED>(A, qh, pos, s, pdl_mode);

@@ -73,11 +73,11 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
     uint32_t epoch = 0;
     float *s_d = s_x + n;                    // exchange: the summed delta (the launcher doubles the shared memory)
     if (TP && exchange) {
-        __shared__ int s_budget;             // polls the CTA may still spend on words that have not arrived (signed: concurrent settlements may overdraw it)
+        __shared__ int s_gave_up;            // set by the first thread whose polls ran out: nobody polls on after that
         if (tid == 0) {
             s_epoch = *tp.epoch + 1;
             // a context whose error word is already set (an earlier exchange gave up: a peer has left) does not wait again
-            s_budget = __ldcg(tp.err) != 0 ? 0 : (int)min(tp.wait_polls, 0x40000000u);
+            s_gave_up = __ldcg(tp.err) != 0 ? 1 : 0;
         }
         __syncthreads();
         epoch = s_epoch;
@@ -92,8 +92,12 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
             }
         }
         // receive and add in rank order, ((v0 + v1) + v2) + ...: the same bits on every rank.  The wait is bounded per
-        // kernel, not per word: every miss is charged to the CTA's budget, and once that is spent nobody polls again.
-        int failed = s_budget <= 0 ? 1 : 0;
+        // kernel, not per word: a thread counts its misses over ALL its words (wait_polls of them, about a third of a
+        // microsecond each, is the time a rank may lag behind: first launches, a host thread that was descheduled), and
+        // once one thread has given up the others stop at their next look at the shared mark.
+        int failed = *(volatile int *)&s_gave_up;
+        uint32_t misses = 0;
+        const uint32_t poll_limit = min(tp.wait_polls, 0x40000000u);
         const unsigned long long *mine = tp.peer_ll[tp.rank] + half_off;
         for (uint32_t i = tid; i < n; i += nthr) {
             float acc = 0.0f;
@@ -103,12 +107,12 @@ __global__ void __launch_bounds__(1024) rmsnorm_quant_kernel(float *__restrict__
                     v = __ldcg(delta + i);
                 } else {
                     unsigned long long word = 0;
-                    uint32_t misses = 0;
                     for (;;) {
                         asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(mine + (size_t)r * tp.ll_slot + i) : "memory");
                         if ((uint32_t)(word >> 32) == epoch || failed) break;
-                        if ((++misses & 63u) == 0) {          // settle the bill every 64 misses; the old balance decides
-                            if (atomicSub(&s_budget, 64) < 64 || misses > tp.wait_polls) { failed = 1; break; }
+                        if ((++misses & 63u) == 0) {          // every 64 misses: out of polls, or has somebody else given up?
+                            if (misses > poll_limit) { *(volatile int *)&s_gave_up = 1; failed = 1; break; }
+                            if (*(volatile int *)&s_gave_up) { failed = 1; break; }
                         }
                     }
                     v = __uint_as_float((uint32_t)word);
