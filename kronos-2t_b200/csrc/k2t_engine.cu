@@ -192,14 +192,9 @@ constexpr uint32_t PASS_TOKENS = 4;    // tokens one weight pass serves (the ref
 
 bool gemv_from(KronosCudaEngine *e, const KronosCudaMatrix *m, const int8_t *q, const float *sc, const int32_t *sums, float *out, const char *what,
                uint32_t n_tok) {
-    const size_t cols = m->dm.geom.cols, nc = cols / 64, rows = m->dm.geom.rows;
-    for (uint32_t t0 = 0; t0 < n_tok; t0 += PASS_TOKENS) {
-        uint32_t launched = 0;
-        cudaError_t err = launch_gemv(e->ctx->stream, m->dm, q + (size_t)t0 * cols, sc + (size_t)t0 * nc, sums + (size_t)t0 * nc, std::min(PASS_TOKENS, n_tok - t0),
-                                      out + (size_t)t0 * rows, rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
-        if (!count(e, err, what, launched)) return false;
-    }
-    return true;
+    uint32_t launched = 0;
+    cudaError_t err = launch_gemv_batch(e->ctx->stream, m->dm, q, sc, sums, n_tok, out, m->dm.geom.rows, nullptr, e->ctx->sm_count, e->ctx->d_err, &launched, e->pdl);
+    return count(e, err, what, launched);
 }
 bool gemv(KronosCudaEngine *e, const KronosCudaMatrix *m, float *out, const char *what, uint32_t n_tok = 1, size_t act_tok0 = 0) {
     const size_t cols = m->dm.geom.cols, nc = cols / 64;

@@ -28,20 +28,13 @@ bool check_gemv_args(KronosCudaContext *ctx, const KronosCudaMatrix *m, const vo
     return true;
 }
 
-// Runs the GEMV over n_tok tokens in sub-batches the kernel accepts.
+// Runs the GEMV over n_tok tokens (tensor-core kernel for batches, 4-token weight passes otherwise).
 bool run_gemv(KronosCudaContext *ctx, const KronosCudaMatrix *m, const int8_t *d_xq, const float *d_xs,
               const int32_t *d_xsum, size_t n_tok, float *d_out, size_t out_stride, int32_t *d_dots) {
-    const MatrixGeom &g = m->dm.geom;
-    const uint32_t max_t = gemv_max_tokens(m->dm);
-    for (size_t t0 = 0; t0 < n_tok; t0 += max_t) {
-        uint32_t n = (uint32_t)std::min<size_t>(max_t, n_tok - t0), launched = 0;
-        cudaError_t e = launch_gemv(ctx->stream, m->dm, d_xq + t0 * g.cols, d_xs + t0 * g.nc,
-                                    d_xsum ? d_xsum + t0 * g.nc : nullptr, n, d_out + t0 * out_stride, out_stride,
-                                    d_dots ? d_dots + t0 * (size_t)g.rows * g.nc : nullptr, ctx->sm_count, ctx->d_err, &launched, true);
-        ctx->launches += launched;
-        if (!cuda_ok(ctx, e, "gemv launch")) return false;
-    }
-    return true;
+    uint32_t launched = 0;
+    cudaError_t e = launch_gemv_batch(ctx->stream, m->dm, d_xq, d_xs, d_xsum, n_tok, d_out, out_stride, d_dots, ctx->sm_count, ctx->d_err, &launched, true);
+    ctx->launches += launched;
+    return cuda_ok(ctx, e, "gemv launch");
 }
 
 }  // namespace

@@ -156,6 +156,43 @@ def test_batch_gemv_matches_oracle(ctx, oracle, n_tok):
         _check_gemv(ctx, oracle, m, x)
 
 
+def _wide_matrix(oracle, fmt, rows, cols):
+    if fmt.startswith("b"):
+        return oracle.bipolar_quantize_rtn(normal(rows + cols, (rows, cols), 0.02), int(fmt[1]))
+    if fmt == "e8q2":
+        rng = np.random.Generator(np.random.PCG64(rows + cols))
+        tpl = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+        sgn = rng.integers(0, 256, (rows, cols // 8), dtype=np.uint8)
+        sc = rng.integers(0x3800, 0x3C00, oracle.lib().k2o_nf_scale_count(rows, cols, 2)).astype(np.uint16)
+        return oracle.e8q2_pack(tpl, sgn, sc, 2)
+    bits, sgc = {"nf3": (3, 1), "nf4": (4, 1), "nf4g128": (4, 2), "nf5g128": (5, 2)}[fmt]
+    return oracle.nf_quantize_rtn(normal(rows + cols + bits, (rows, cols), 0.02), bits, sgc)
+
+
+@pytest.mark.parametrize("fmt", ["b4", "b5", "b6", "nf3", "nf4", "nf4g128", "nf5g128", "e8q2"])
+@pytest.mark.parametrize("rows,cols,n_tok", [(54, 192, 8), (71, 1536, 17), (300, 2112, 33), (128, 576, 64), (260, 4160, 100)])
+def test_wide_batch_gemm_on_tensor_cores(ctx, oracle, fmt, rows, cols, n_tok):
+    """Batches of eight tokens and more take the tensor-core kernel (exact int32 chunk dots by tcgen05.mma, the fp32 chains in
+    chunk order): outputs equal the oracle's batch form bit for bit - odd row counts, partial token tiles, more than one pass
+    of 32 chunks, whole chunks of zero activations for some tokens (their chain steps are skipped)."""
+    m = _wide_matrix(oracle, fmt, rows, cols)
+    x = normal(n_tok * 7 + rows, (n_tok, cols))
+    x[n_tok - 1, 64:128] = 0.0
+    x[n_tok // 2, :] = 0.0
+    if cols > 1024:
+        x[:, 960:1024] = 0.0
+    act = oracle.act_populate_fwht(x)
+    dm = upload(ctx, m)
+    try:
+        before = ctx.launch_count
+        out = ctx.gemv(dm, act.q, act.scales, act.sums)
+        assert ctx.launch_count - before == 1, "one launch for the whole batch"
+    finally:
+        dm.free()
+    want = oracle.nibble4_gemv(oracle.nibble4_from_bipolar(m, False), act) if m.kind == 0 else oracle.nf_gemv(m, act)
+    assert np.array_equal(out, want)
+
+
 @pytest.mark.parametrize("rows", [71, 128])
 @pytest.mark.parametrize("bits,sgc", [(3, 1), (3, 2), (4, 1), (4, 2), (5, 1), (5, 2)])
 def test_reference_nf_sdot_case(ctx, oracle, rows, bits, sgc):
