@@ -125,7 +125,7 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
     return cuda_ok(e->ctx, cudaMemsetAsync(p, 0, bytes, e->ctx->stream), "clear");
 }
 
-constexpr uint32_t ATTN_BATCH = 16;    // tokens whose attention runs side by side (= the prompt batch, MAX_BATCH below)
+constexpr uint32_t ATTN_BATCH = 64;    // tokens whose attention runs side by side (= the prompt batch, MAX_BATCH below)
 
 void dev_free(KronosCudaEngine *e, void *p) {
     if (!p) return;
@@ -188,7 +188,6 @@ bool sync_vt(KronosCudaEngine *e) {
 // y[t] = W x[t] for the n_tok tokens of the batch (activations [n_tok][cols] in act_*; one weight pass for up to 4 tokens)
 bool count(KronosCudaEngine *e, cudaError_t err, const char *what, uint32_t n = 1);
 
-constexpr uint32_t PASS_TOKENS = 4;    // tokens one weight pass serves (the reference's 4-token tiles in prompt batches)
 
 bool gemv_from(KronosCudaEngine *e, const KronosCudaMatrix *m, const int8_t *q, const float *sc, const int32_t *sums, float *out, const char *what,
                uint32_t n_tok) {
@@ -223,7 +222,7 @@ bool tp_gather(KronosCudaEngine *e, const float *slice, float *all, uint32_t n) 
     return count(e, launch_tp_exchange(e->ctx->stream, e->tp, slice, all, n, n, e->pdl), "tp gather");
 }
 
-constexpr uint32_t MAX_BATCH = 16;     // tokens per prompt batch: their projections run as weight passes of PASS_TOKENS tokens, their attention side by side
+constexpr uint32_t MAX_BATCH = 64;     // tokens per prompt batch: their projections run on the tensor cores in one weight pass (k2t_gemm_tc.cu), their attention side by side
 static_assert(MAX_BATCH == ATTN_BATCH, "the attention scratch is sized for one prompt batch");
 
 // Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
@@ -1306,7 +1305,7 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
         return 0;
     }
     // prompt: batches of up to MAX_BATCH tokens (forward_prompt / forward_batch_sdot_impl, real_llm.rs:7407-7448, 7450-7860):
-    // every projection as weight passes of 4 tokens, the attention of the batch's tokens side by side
+    // every projection as one tensor-core weight pass over the batch, the attention of the batch's tokens side by side
     if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
     for (size_t t0 = 0, T_done = 0; t0 < n_tok; t0 += T_done) {
         uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
