@@ -394,6 +394,32 @@ def run_b200(args, rank, world, local_rank):
     big_b = sum(c["bytes"] for c in cases if c["m"]["rows"] == 49152)
     big_us = sum(k["us"] for k in big)
     big_us_iso = sum(k["us_isolated"] for k in big)
+    # the wide-batch kernel on the same four large matrices: 64 tokens in one launch (tensor cores for the integer dots)
+    gemm_tc = []
+    for c in cases:
+        if c["m"]["rows"] != 49152:
+            continue
+        cols, rows, nt = c["m"]["cols"], c["m"]["rows"], 64
+        x64 = torch.randn(nt, cols, device=dev)
+        q64 = torch.empty(nt, cols, dtype=torch.int8, device=dev)
+        s64 = torch.empty(nt, cols // 64, dtype=torch.float32, device=dev)
+        m64 = torch.empty(nt, cols // 64, dtype=torch.int32, device=dev)
+        o64 = torch.empty(nt, rows, dtype=torch.float32, device=dev)
+        ctx.fwht_quant_dev(x64.data_ptr(), nt, cols, q64.data_ptr(), s64.data_ptr(), m64.data_ptr())
+        for _ in range(2):
+            ctx.gemv_dev(c["dm"], q64.data_ptr(), s64.data_ptr(), m64.data_ptr(), nt, o64.data_ptr())
+        torch.cuda.synchronize()
+        l0 = ctx.launch_count
+        e0.record(stream)
+        for _ in range(5):
+            ctx.gemv_dev(c["dm"], q64.data_ptr(), s64.data_ptr(), m64.data_ptr(), nt, o64.data_ptr())
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 5
+        tops = 2.0 * rows * cols * nt / us / 1e6
+        gemm_tc.append({"case": f"{c['m']['fmt']} {cols}x{rows} x {nt} tokens", "launches_per_call": (ctx.launch_count - l0) // 5, "us": round(us, 1),
+                        "int8_TOPs": round(tops, 1), "frac_of_nominal_int8": round(tops / 4500.0, 4),
+                        "tok_s_equivalent": round(nt / us * 1e6)})
     achieved = big_b / big_us / 1e3
     traffic, traffic_src = ncu_traffic("b4")
     traffic_per_format = {f: ncu_traffic(f)[0] for f in ("b4", "nf4g128")}
@@ -409,7 +435,10 @@ def run_b200(args, rank, world, local_rank):
                 "traffic_source": traffic_src, "traffic_per_format": traffic_per_format,
                 "all_16_launches": {"achieved": tot_b / tot_us / 1e3, "frac": tot_b / tot_us / 1e3 / peak,
                                     "achieved_isolated": tot_b / tot_us_iso / 1e3, "frac_isolated": tot_b / tot_us_iso / 1e3 / peak},
-                "per_launch": kernels}
+                "per_launch": kernels,
+                "gemm_tc": gemm_tc,
+                "gemm_tc_note": "gemm_tc_kernel (k2t_gemm_tc.cu): bound by the fp32 chains and role hand-offs on the CUDA cores, not by the tensor pipe "
+                                "(4% active, profiles/gemm_tc_nf4g128_2048x16384_t64.md); int8 dense nominal 4500 TOP/s, no measured int8 peak on this pool"}
 
     decode = None
     if not args.no_decode:
@@ -419,15 +448,20 @@ def run_b200(args, rank, world, local_rank):
                                             decode["kv_bytes_at_256"] // 256, peak)]
         if not args.no_decode_models:
             try:
-                decode["models"], roof, attn = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
+                decode["models"], roof, attn, pre = decode_models(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
                 roofline["decode"] += roof
                 roofline["attention"] = attn
+                roofline["prefill"] = pre
             except Exception as exc:      # the headline line must still come out; the failure is reported in it
                 decode["models_error"] = f"{type(exc).__name__}: {exc}"
         if not args.no_decode_moe:
             try:
                 decode["moe"], roof = decode_moe(ctx, lambda fn: timed(fn, 1)[0], rank, world, dist)
                 roofline["decode"] += roof
+                from kronos_2t_b200 import synth as _synth
+                roofline.setdefault("prefill", []).append(_prefill_entry(
+                    "Qwen3-30B-A3B nf3 experts / nf4g128 attention" + ("" if world == 1 else f" ep{world}"), 480, decode["moe"]["prefill_tok_s_480"],
+                    _matmul_ops_per_token(_synth.QWEN3_30B_A3B, dict(top_k=8, d_ff=768)), n_gpus=world))
             except Exception as exc:
                 decode["moe_error"] = f"{type(exc).__name__}: {exc}"
         if world > 1:
@@ -435,6 +469,9 @@ def run_b200(args, rank, world, local_rank):
                 roofline["sharded_parity"] = sharded_parity(ctx, rank, world, dist)
             except Exception as exc:
                 roofline["sharded_parity"] = {"error": f"{type(exc).__name__}: {exc}"}
+        roofline["prefill_note"] = ("prompt batches of 64 tokens: every dense projection is one launch of the tensor-core kernel (tcgen05.mma kind::i8 for the "
+                                    "exact chunk dots, fp32 chains on the CUDA cores in the reference's order), attention of the batch side by side; "
+                                    "int8_TOPs = 2 x multiply-adds of the projections x tok/s; the MoE experts still run as expert-batched GEMVs")
         roofline["decode_note"] = ("frac = bytes_per_token * tok_s / (n_gpus * peak): weights of one step in the reference's file format + the cached "
                                    "rows the token attends to; n_gpus > 1: the Qwen2-7B shape tensor-parallel (tp) and the Qwen3-30B-A3B shape "
                                    "expert-parallel (ep) over all ranks - strong scaling of ONE token stream")
@@ -573,13 +610,28 @@ def decode_tok_s(ctx, stream, timed_region, world):
 
 
 def _prefill(eng, rng, vocab, lo, hi, timed_region=None):
-    """Prompt positions [lo, hi) of random token ids in 4-token weight passes; returns tok/s when timed."""
+    """Prompt positions [lo, hi) of random token ids (batches of 64 tokens: every projection one tensor-core weight pass); returns
+    tok/s when timed - the second of two identical passes, so that no kernel is loaded inside the timed region."""
     toks = rng.integers(0, vocab, hi - lo).astype("uint32")
+    eng.forward_token_ids(toks, pos_start=lo)
     if timed_region is None:
-        eng.forward_token_ids(toks, pos_start=lo)
         return None
     ms = timed_region(lambda: eng.forward_token_ids(toks, pos_start=lo))
     return (hi - lo) / (ms / 1e3)
+
+
+def _matmul_ops_per_token(cfg, moe=None):
+    """Integer multiply-adds x 2 of one token's projections (lm_head left out: a prompt computes it for its last token only)."""
+    h, hd = cfg["hidden"], cfg["head_dim"]
+    attn = (cfg["n_q"] + 2 * cfg["n_kv"]) * hd * h + h * cfg["n_q"] * hd
+    ffn = 3 * cfg["inter"] * h if moe is None else moe["top_k"] * 3 * moe["d_ff"] * h
+    return 2 * cfg["layers"] * (attn + ffn)
+
+
+def _prefill_entry(name, tokens, tok_s, ops_per_token, n_gpus=1):
+    tops = ops_per_token * tok_s / 1e12
+    return {"model": name, "tokens": tokens, "tok_s": round(tok_s, 1), "int8_TOPs": round(tops, 2), "n_gpus": n_gpus,
+            "frac_of_nominal_int8": round(tops / (4500.0 * n_gpus), 4)}
 
 
 def _attention_us(eng, pos, reps=4):
@@ -614,7 +666,7 @@ def decode_models(ctx, timed_region, rank, world, dist):
     from kronos_2t_b200 import synth
     rng = np.random.Generator(np.random.PCG64(23))
     peak, _ = peaks()
-    out, roof, attn = [], [], []
+    out, roof, attn, pre = [], [], [], []
     steps = 64
     name17 = "SmolLM2-1.7B-shaped (hidden 2048, 24 layers, 32q/32kv heads of 64, MLP 8192, vocab 49152), nf4g128"
     if world == 1:
@@ -622,8 +674,8 @@ def decode_models(ctx, timed_region, rank, world, dist):
             kv = "int8" if kv_bits == 8 else "nf4"
             cfg = dict(synth.SMOLLM2_1_7B, kv_bits=kv_bits)
             eng = k2.Engine(ctx, synth.random_model(cfg, "nf4g128", seed=5, share_layers=True))
-            _prefill(eng, rng, cfg["vocab"], 0, 64)                                   # warm-up
             prefill = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region)
+            pre.append(_prefill_entry(f"SmolLM2-1.7B nf4g128, {kv} KV", 1024, prefill, _matmul_ops_per_token(cfg)))
             res = {"model": name17, "kv": kv, "prefill_tok_s_1024": prefill, "weight_bytes_per_token": eng.weight_bytes,
                    "kv_bytes_per_pos": eng.kv_bytes_per_pos}
             for key, pos in (("ctx_512", 512 - steps), ("ctx_8192", 8192)):
@@ -671,8 +723,8 @@ def decode_models(ctx, timed_region, rank, world, dist):
             eng.tp_attach(handles[group * tp:(group + 1) * tp])
             dist.barrier()
         if not split:
-            _prefill(eng, rng, cfg["vocab"], 0, 64)
             res7["prefill_tok_s_1024"] = _prefill(eng, rng, cfg["vocab"], 0, 1024, timed_region) * (world // tp)
+            pre.append(_prefill_entry("Qwen2-7B p55454" + ("" if tp == 1 else f" tp{tp}"), 1024, res7["prefill_tok_s_1024"], _matmul_ops_per_token(cfg), n_gpus=world))
         eng.decode_greedy(1, 4096, 8)
         ms = min(timed_region(lambda: eng.decode_greedy(1, 4096, steps)) for _ in range(2))
         groups = world // tp
@@ -698,7 +750,7 @@ def decode_models(ctx, timed_region, rank, world, dist):
                          "frac": round(kv_layer / a_us / 1e3 / peak, 3)})
         eng.close()
     out.append(res7)
-    return out, roof, attn
+    return out, roof, attn, pre
 
 
 def sharded_parity(ctx, rank, world, dist):
@@ -793,7 +845,6 @@ def decode_moe(ctx, timed_region, rank, world, dist):
         eng.tp_attach(handles)
         dist.barrier()
     steps = 32
-    _prefill(eng, rng, cfg["vocab"], 0, 16)
     prefill = _prefill(eng, rng, cfg["vocab"], 0, 512 - steps, timed_region)
     out = {"model": "Qwen3-30B-A3B-shaped (hidden 2048, 48 layers, 32q/4kv heads of 128, 128 experts of 768, top-8, vocab 151936), "
                     "nf3 experts, nf4g128 attention", "kv": "int8", "ep": world, "build_s": round(build_s, 1),
@@ -826,20 +877,33 @@ def run_decode_only(args, local_rank):
     ctx = k2.Context(local_rank)
     pos = max(args.decode_ctx, 15)
     if args.decode_model == "1.7b":
-        cfg = dict(synth.SMOLLM2_1_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
+        cfg = dict(synth.SMOLLM2_1_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + args.prefill_only + 1)
         spec = synth.random_model(cfg, "nf4g128", seed=5, share_layers=True)
     elif args.decode_model == "moe":
-        cfg = dict(synth.QWEN3_30B_A3B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1, layers=args.decode_layers or 48)
+        cfg = dict(synth.QWEN3_30B_A3B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + args.prefill_only + 1, layers=args.decode_layers or 48)
         spec = synth.random_model(cfg, "nf4g128", seed=9, untied=True, share_layers=True, moe=dict(n_experts=128, top_k=8, d_ff=768, bits=3, sgc=1))
     elif args.decode_model == "7b":
-        cfg = dict(synth.QWEN2_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + 1)
+        cfg = dict(synth.QWEN2_7B, kv_bits=args.kv_bits, max_seq=pos + args.decode_only + args.prefill_only + 1)
         spec = synth.random_model(cfg, "b4", seed=7, modes=synth.P55454, qkv_bias=True, untied=True, share_layers=True)
     else:
-        cfg = dict(synth.SMOLLM2_135M, kv_bits=args.kv_bits, max_seq=max(512, pos + args.decode_only + 1))
+        cfg = dict(synth.SMOLLM2_135M, kv_bits=args.kv_bits, max_seq=max(512, pos + args.decode_only + args.prefill_only + 1))
         spec = synth.random_model(cfg, "b4", seed=3)
     if args.split_kv:
         spec["cfg"]["split_kv_attention"] = True
     eng = k2.Engine(ctx, spec)
+    if args.prefill_only:          # prompt batches alone: N tokens from position --decode-ctx on, twice (the second pass is timed)
+        toks = np.random.Generator(np.random.PCG64(11)).integers(0, cfg["vocab"], args.prefill_only).astype(np.uint32)
+        start = args.decode_ctx if args.decode_ctx > 15 else 0
+        eng.forward_token_ids(toks, pos_start=start)
+        torch.cuda.synchronize()
+        l0, t0 = ctx.launch_count, time.perf_counter()
+        eng.forward_token_ids(toks, pos_start=start)
+        dt = time.perf_counter() - t0
+        print(json.dumps({"mode": "prefill-only", "model": args.decode_model, "kv_bits": args.kv_bits, "pos_start": start, "tokens": args.prefill_only,
+                          "launches": int(ctx.launch_count - l0), "wall_ms": dt * 1e3, "tok_s": args.prefill_only / dt}))
+        eng.close()
+        ctx.close()
+        return
     prompt = np.random.Generator(np.random.PCG64(11)).integers(0, cfg["vocab"], 16).astype(np.uint32)
     l0 = ctx.launch_count
     eng.forward_token_ids(prompt[:-1])
@@ -921,6 +985,8 @@ def main():
     ap.add_argument("--no-decode-models", action="store_true", help="skip the 1.7B / 7B-shaped decode measurements")
     ap.add_argument("--decode-only", type=int, default=0, metavar="N",
                     help="profiling mode: only the whole-token engine - a 16-token prompt, then N greedy steps")
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="N",
+                    help="small run for profilers: a prompt of N tokens from position --decode-ctx on (model: --decode-model), nothing else")
     ap.add_argument("--decode-model", default="135m", choices=["135m", "1.7b", "7b", "moe"], help="--decode-only: model shape")
     ap.add_argument("--decode-layers", type=int, default=0, help="--decode-only, moe: fewer layers than the shape's 48 (profiling)")
     ap.add_argument("--decode-ctx", type=int, default=15, help="--decode-only: position of the first greedy step")
@@ -933,7 +999,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.decode_only:
+    if args.decode_only or args.prefill_only:
         run_decode_only(args, local_rank)
     elif args.case:
         run_case(args, local_rank)

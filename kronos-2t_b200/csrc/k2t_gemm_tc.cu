@@ -1,25 +1,30 @@
 // Wide-batch quantized GEMM on the tensor cores (prompt batches): the same arithmetic contract as the GEMV / small-N
-// kernels (k2t_gemv_core.cuh; reference batch forms src/kernels/simd_lut.rs:4228-4331, 6689-7029), for 8..64 tokens per
+// kernels (k2t_gemv_core.cuh; reference batch forms src/kernels/simd_lut.rs:4228-4331, 6689-7029), for 16..64 tokens per
 // weight pass instead of 4.
 //
 // What the tensor cores can take over without changing a bit of the result is the INTEGER part: per row r, token t and
 // 64-column chunk c the exact int32 dot  a = sum_i code_i * q_i.  The fp32 part stays a chain per (row, token) in
 // ascending chunk order, f = fmaf((float)dot * xs[t][c], w_scale[r][c / sgc], f), and runs on the CUDA cores out of
-// tensor memory.  So a CTA (128 rows x N tokens, N = 16 / 32 / 64) walks the chunks of its rows once:
-//   * four DECODE warps (thread = row): the row's cell of chunk c (2..3 x 16 bytes, fetched eight chunks ahead with
-//     `cp.async` into a thread-private ring) is expanded to 64 int8 codes and stored as the A operand in the K-major
-//     no-swizzle UMMA layout (8-row x 16-byte core matrices); the same threads move the tokens' int8 activations of the
-//     chunk into the B operand (N x 64 bytes, same layout);
-//   * one thread issues two `tcgen05.mma.kind::i8` (M 128, N, K 32 each; signed x signed, int32 accumulators) per
-//     chunk into one of four accumulator buffers in tensor memory and commits to the mbarriers that free the operand
-//     stage and publish the accumulator;
-//   * eight EPILOGUE warps (thread = row, two warps per 32-lane quarter splitting the tokens) read the chunk's N dots of
-//     their row with `tcgen05.ld`, release the buffer, and advance their N/2 chains: one integer multiply-add folds the
-//     bit-plane correction (2a - (2^B - 1) * xsum) and the int -> float conversion constant, then add, multiply, fma.
-// A chunk costs the epilogue about 4.5 instructions per (row, token) against about 25 for the dp4a form, and the weights
-// are read once per 64 tokens instead of once per 4.  Activation scales and corrections of the CTA's tokens sit in shared
-// memory, chunk-major, for the whole launch.  Every wait is bounded; a wait that gives up raises the context's error word
-// and all roles leave their loops, the tensor memory is freed and the kernel returns.
+// tensor memory.  So a CTA (128 rows x N tokens, N = 16 / 32 / 64; 25 warps) walks the chunks of its rows once:
+//   * DECODE groups of 128 threads (thread = row; group g takes chunks g, g + G, ...): the row's cell of the chunk (2..3 x
+//     16 bytes, fetched eight chunks ahead with `cp.async` into a thread-private ring) is expanded to 64 int8 codes and
+//     stored as the A operand in the K-major no-swizzle UMMA layout (8-row x 16-byte core matrices); the same threads move
+//     the tokens' int8 activations of the chunk into the B operand (N x 64 bytes, same layout);
+//   * one thread issues two `tcgen05.mma.kind::i8` (M 128, N, K 32 each; signed x signed, int32 accumulators) per chunk into
+//     the accumulator buffer of the chunk's stage (six stages, six buffers in tensor memory) and commits to the stage's
+//     `done` mbarrier, which both frees the operands and publishes the accumulator;
+//   * EPILOGUE warps (thread = row, two or four warps per 32-lane quarter splitting the tokens) read the chunk's dots of
+//     their row with `tcgen05.ld` one chunk ahead of the arithmetic, hand the buffer back (`drained`: the decode threads
+//     wait for it before they refill the stage, so the issuing thread never waits for the epilogue), and advance their
+//     chains: one integer multiply-add folds the bit-plane correction (2a - (2^B - 1) * xsum) and the int -> float
+//     conversion constant, then add, multiply, fma.
+// Activation scales and corrections of the CTA's tokens sit in shared memory, chunk-major, for the whole launch.  Every
+// wait is bounded; a wait that gives up raises the context's error word and all roles leave their loops, the tensor
+// memory is freed and the kernel returns.
+// Measured (B200): 32 chunks in 16-26 us, 128 chunks in 60 us, whatever the rows up to one CTA per SM - 0.45 us per chunk
+// for 16-token tiles, 0.7 us for 64: the serial hand-offs of a chunk through the roles and the per-chunk work of a warp
+// (13 M warp instructions per 2048 x 16384 x 64 launch, half an instruction per scheduler and cycle, tensor pipe 4%
+// active), not the tensor cores or HBM, bound it.  Against 4-token passes it wins from about 16 tokens on.
 #include <algorithm>
 #include <cstdlib>
 
@@ -32,17 +37,28 @@ int fill_gemv_args(const DeviceMatrix &m, bool has_xsum, GemvArgs &a);      // k
 namespace {
 
 constexpr uint32_t TC_M = 128;              // rows per CTA = UMMA M
-constexpr uint32_t TC_STAGES = 4;           // operand stages (A 8 KiB + B N x 64 bytes each)
-constexpr uint32_t TC_ACC = 4;              // accumulator buffers in tensor memory (N columns each)
-constexpr uint32_t TC_PF = 8;               // chunks the raw weights / activations are requested ahead
-constexpr uint32_t TC_EPI_WARPS = 8, TC_DEC_WARPS = 4;
-constexpr uint32_t TC_THREADS = (TC_EPI_WARPS + TC_DEC_WARPS + 1) * 32;
+constexpr uint32_t TC_STAGES = 6;           // operand stages (A 8 KiB + B N x 64 bytes each), each with its own accumulator buffer
+constexpr uint32_t TC_ACC = TC_STAGES;      // accumulator buffers in tensor memory (N columns each): chunk c uses stage and buffer c % 6
+constexpr uint32_t TC_PF = 8;               // ring slots of the raw weights / activations (slot = chunk % TC_PF): chunks requested ahead
+constexpr uint32_t TC_WARPS = 25;           // 24 decode + epilogue warps and the issuing warp
+constexpr uint32_t TC_THREADS = TC_WARPS * 32;
+// The 24 working warps are divided by the tile's width.  64 tokens: the chains are the larger part - sixteen epilogue warps
+// (four per 32-lane quarter, a quarter of the tokens each) and two decode groups of 128 threads (group g expands chunks
+// g, g + 2, ...).  16 / 32 tokens: the expansion is - eight epilogue warps (half the tokens each), four decode groups.
+template <int N> struct TcRoles {
+    static constexpr uint32_t EPI_WARPS = N == 64 ? 16 : 8;
+    static constexpr uint32_t GROUPS = (TC_WARPS - 1 - EPI_WARPS) / 4;
+    static constexpr uint32_t PFG = TC_PF / GROUPS;          // own chunks a decode group requests ahead
+    static constexpr uint32_t NQ = N / (EPI_WARPS / 4);       // tokens per epilogue warp
+};
 constexpr uint32_t TC_A_STAGE = TC_M * 64;
 constexpr uint32_t TC_HEADER = 1024;        // mbarriers, tensor-memory address, abort word
 constexpr uint32_t TC_SMEM_MAX = 227u * 1024u;
 constexpr uint32_t TC_LBO = 128, TC_SBO = 512;      // K-major no-swizzle: next core matrix along K / next 8-row group
 constexpr int TC_MAGIC_I = 0x4B400000;      // bits of 12582912.0f = 1.5 * 2^23: as_float(MAGIC + d) - 12582912.0f == (float)d for |d| < 2^22
 constexpr float TC_MAGIC_F = 12582912.0f;
+
+__host__ __device__ constexpr uint32_t tc_tmem_cols(uint32_t n) { return TC_ACC * n <= 128 ? 128u : TC_ACC * n <= 256 ? 256u : 512u; }     // allocations are powers of two
 
 template <int FMT> __host__ __device__ constexpr uint32_t tc_cell() { return Cell<FMT>::B0 + Cell<FMT>::B1 + Cell<FMT>::B2; }
 
@@ -55,7 +71,7 @@ template <int FMT, int N> __host__ __device__ inline TcLayout tc_layout(uint32_t
     L.bring = L.wring + TC_PF * TC_M * tc_cell<FMT>();
     L.xs = L.bring + TC_PF * N * 64;
     L.bias = L.xs + nc * N * 4;
-    L.nz = L.bias + nc * N * 4;
+    L.nz = L.bias + (is_bitplane<FMT>() ? nc * N * 4 : 0u);       // codebook formats have no correction term
     L.total = (L.nz + nc + 127u) & ~127u;
     return L;
 }
@@ -104,7 +120,26 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, int (&v)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for the thread's tensor-memory loads.  The loaded registers are operands so that no use of them can be scheduled
+// above the wait (the loads complete asynchronously; the compiler sees only register names).
+__device__ __forceinline__ void tc_ld_wait(int (&v)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])::"memory");
+}
+__device__ __forceinline__ void tc_ld_wait(int (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]),
+                   "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])::"memory");
+}
+template <int K> __device__ __forceinline__ void tc_ld(uint32_t taddr, int (&v)[K]) {
+#pragma unroll
+    for (int k = 0; k < K / 8; ++k) tc_ld8(taddr + k * 8, *reinterpret_cast<int(*)[8]>(&v[k * 8]));
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {      // may sleep up to `ns` inside
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok;
+}
 
 // Bounded wait on an mbarrier phase; gives up when the limit runs out or another role has given up.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_w) {
@@ -115,6 +150,24 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     *abort_w = 1;
     return false;
 }
+// The same for a role that runs ahead of the others (the decode warps): the wait sleeps in the barrier unit instead of
+// taking issue slots from the warps that are behind.
+__device__ __forceinline__ bool tc_wait_idle(uint32_t bar, uint32_t parity, volatile uint32_t *abort_w) {
+    for (uint32_t spin = 0; spin < (WAIT_LIMIT >> 4); ++spin) {
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if ((spin & 15u) == 15u && *abort_w != 0) return false;
+    }
+    *abort_w = 1;
+    return false;
+}
+
+#ifdef K2T_TC_TRACE
+// Build-time diagnostic: cycles CTA 0 spends in the phases of its three roles (lane 0 of the first warp of each).
+__device__ unsigned long long g_tc_trace[32];
+#define TC_ACC_T(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0) { const long long _t1 = clock64(); trace_acc[slot] += (unsigned long long)(_t1 - _tl); _tl = _t1; } } while (0)
+#else
+#define TC_ACC_T(slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
     // start address, leading (K) and stride (8-row group) byte offsets in 16-byte units, descriptor version 1, no swizzle
@@ -125,27 +178,30 @@ template <int FMT, int N>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs args) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const GemvArgs &a = args.g;
-    constexpr uint32_t NH = N / 2;                       // tokens per epilogue warp
+    constexpr uint32_t TC_EPI_WARPS = TcRoles<N>::EPI_WARPS, TC_GROUPS = TcRoles<N>::GROUPS, TC_PFG = TcRoles<N>::PFG, TC_DEC_WARPS = 4 * TC_GROUPS;
+    constexpr uint32_t NQ = TcRoles<N>::NQ;              // tokens per epilogue warp
     constexpr uint32_t CELL = tc_cell<FMT>();
-    constexpr int MUL = is_bitplane<FMT>() ? 2 : 1;
+    constexpr bool BP = is_bitplane<FMT>();
     const TcLayout L = tc_layout<FMT, N>(a.nc);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * N;
     const uint32_t n_here = min((uint32_t)N, args.n_tok - tok0);
     const uint32_t nc = a.nc;
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t bar_full = sbase, bar_empty = sbase + 32, bar_acc_full = sbase + 64, bar_acc_empty = sbase + 96;
-    volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(smem + 128);
-    volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 132);
+    // per stage: full (operands written: decode -> issue), done (the chunk's products are in tensor memory: issue -> decode, which may
+    // reuse the stage, and -> epilogue), drained (the epilogue has read the accumulator: -> decode, which refills the stage only then,
+    // so the issuing thread never waits for the epilogue itself)
+    const uint32_t bar_full = sbase, bar_done = sbase + 64, bar_drained = sbase + 128;
+    volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(smem + 256);
+    volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + 260);
 
     if (tid == 0) {
-        for (uint32_t i = 0; i < TC_STAGES; ++i) { mbar_init(bar_full + 8 * i, TC_DEC_WARPS * 32); mbar_init(bar_empty + 8 * i, 1); }
-        for (uint32_t i = 0; i < TC_ACC; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, TC_EPI_WARPS * 32); }
+        for (uint32_t i = 0; i < TC_STAGES; ++i) { mbar_init(bar_full + 8 * i, TC_M / 32); mbar_init(bar_done + 8 * i, 1); mbar_init(bar_drained + 8 * i, TC_EPI_WARPS); }
         *s_abort = 0;
         fence_mbar_init();
     }
     if (warp == TC_EPI_WARPS + TC_DEC_WARPS) {           // the issuing warp owns the tensor memory: TC_ACC x N columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + 128), "r"((uint32_t)(TC_ACC * N)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + 256), "r"(tc_tmem_cols(N)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -154,15 +210,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
     const uint32_t tmem = *s_tmem;
 
     if (warp < TC_EPI_WARPS) {
-        // ------------------------------------------------------------------ epilogue: thread = row, N/2 chains
-        const uint32_t quarter = warp & 3u, half = warp >> 2;
+        // ------------------------------------------------------------------ epilogue: thread = row, NQ chains
+        const uint32_t quarter = warp & 3u, part = warp >> 2;
         const uint32_t row = row0 + quarter * 32 + lane, row_c = min(row, a.rows_pad - 1);
         float *s_xs = reinterpret_cast<float *>(smem + L.xs);
         int *s_bias = reinterpret_cast<int *>(smem + L.bias);
         uint8_t *s_nz = smem + L.nz;
         pdl_wait();
-        // tables of the CTA's tokens, chunk-major: xs[c][t], bias[c][t] = conversion constant - (2^B - 1) * xsum[t][c];
-        // nz[c] = no real token has a zero scale in chunk c (then no chain step of the chunk is skipped)
+        // tables of the CTA's tokens, chunk-major: xs[c][t] and, for bit-planes, bias[c][t] = conversion constant -
+        // (2^B - 1) * xsum[t][c]; nz[c] = no real token has a zero scale in chunk c (no chain step of the chunk is skipped)
         for (uint32_t c = tid; c < nc; c += TC_EPI_WARPS * 32) s_nz[c] = 1;
         asm volatile("bar.sync 1, %0;" ::"r"(TC_EPI_WARPS * 32) : "memory");
         for (uint32_t i = tid; i < nc * N; i += TC_EPI_WARPS * 32) {
@@ -171,19 +227,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
             int sum = 0;
             if (t < n_here) {
                 sx = __ldg(a.xs + (size_t)(tok0 + t) * nc + c);
-                if (is_bitplane<FMT>()) sum = __ldg(a.xsum + (size_t)(tok0 + t) * nc + c);
+                if (BP) sum = __ldg(a.xsum + (size_t)(tok0 + t) * nc + c);
                 if (sx == 0.0f) s_nz[c] = 0;
             }
             s_xs[i] = sx;
-            s_bias[i] = TC_MAGIC_I - a.max_odd * sum;
+            if (BP) s_bias[i] = TC_MAGIC_I - a.max_odd * sum;
         }
         asm volatile("bar.sync 1, %0;" ::"r"(TC_EPI_WARPS * 32) : "memory");
 
-        float f[NH];
+        float f[NQ];
 #pragma unroll
-        for (uint32_t t = 0; t < NH; ++t) f[t] = 0.0f;
-        const uint32_t xs_sa = sbase + L.xs + half * NH * 4, bias_sa = sbase + L.bias + half * NH * 4;
-        const uint32_t taddr0 = tmem + ((quarter * 32u) << 16) + half * NH;
+        for (uint32_t t = 0; t < NQ; ++t) f[t] = 0.0f;
+        const uint32_t xs_sa = sbase + L.xs + part * NQ * 4, bias_sa = sbase + L.bias + part * NQ * 4;
+        const uint32_t taddr0 = tmem + ((quarter * 32u) << 16) + part * NQ;
         // the row's scale of a chunk, requested one chunk ahead
         const uint8_t *sc_row = nullptr;
         uint32_t sc_g0 = 0;
@@ -195,90 +251,142 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
             }
             return bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(sc_row) + (scale_group_of(a, c) - sc_g0)));
         };
-        float ws_next = scale_of(0);
         bool ok = true;
-        for (uint32_t c = 0; c < nc && ok; ++c) {
-            const uint32_t b = c % TC_ACC;
-            const float ws = ws_next;
-            if (c + 1 < nc) ws_next = scale_of(c + 1);
-            ok = tc_wait(bar_acc_full + 8 * b, (c / TC_ACC) & 1u, s_abort);
-            if (!ok) break;
-            tc_fence_after();
-            int v[NH];
-#pragma unroll
-            for (uint32_t k = 0; k < NH / 8; ++k) tc_ld8(taddr0 + b * N + k * 8, *reinterpret_cast<int(*)[8]>(&v[k * 8]));
-            tc_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * b);
+#ifdef K2T_TC_TRACE
+        unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long _tl = clock64();
+#endif
+        // chain steps of chunk c from the dots in v (already waited for)
+        auto advance = [&](uint32_t c, const int (&v)[NQ], float ws) {
             const uint32_t xo = c * (N * 4);
-            if (s_nz[c]) {
+            if (s_nz[c] != 0) {
 #pragma unroll
-                for (uint32_t t = 0; t < NH; t += 4) {
+                for (uint32_t t = 0; t < NQ; t += 4) {
                     const float4 x4 = lds_f32x4(xs_sa + xo + t * 4);
-                    const uint4 b4 = lds_u32x4_tc(bias_sa + xo + t * 4);
-                    f[t + 0] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(v[t + 0] * MUL + (int)b4.x), -TC_MAGIC_F), x4.x), ws, f[t + 0]);
-                    f[t + 1] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(v[t + 1] * MUL + (int)b4.y), -TC_MAGIC_F), x4.y), ws, f[t + 1]);
-                    f[t + 2] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(v[t + 2] * MUL + (int)b4.z), -TC_MAGIC_F), x4.z), ws, f[t + 2]);
-                    f[t + 3] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(v[t + 3] * MUL + (int)b4.w), -TC_MAGIC_F), x4.w), ws, f[t + 3]);
+                    uint4 b4 = make_uint4(TC_MAGIC_I, TC_MAGIC_I, TC_MAGIC_I, TC_MAGIC_I);
+                    if (BP) b4 = lds_u32x4_tc(bias_sa + xo + t * 4);
+                    const int d0 = BP ? v[t + 0] * 2 + (int)b4.x : v[t + 0] + (int)b4.x, d1 = BP ? v[t + 1] * 2 + (int)b4.y : v[t + 1] + (int)b4.y;
+                    const int d2 = BP ? v[t + 2] * 2 + (int)b4.z : v[t + 2] + (int)b4.z, d3 = BP ? v[t + 3] * 2 + (int)b4.w : v[t + 3] + (int)b4.w;
+                    f[t + 0] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(d0), -TC_MAGIC_F), x4.x), ws, f[t + 0]);
+                    f[t + 1] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(d1), -TC_MAGIC_F), x4.y), ws, f[t + 1]);
+                    f[t + 2] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(d2), -TC_MAGIC_F), x4.z), ws, f[t + 2]);
+                    f[t + 3] = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(d3), -TC_MAGIC_F), x4.w), ws, f[t + 3]);
                 }
             } else {          // a token's zero scale skips its chain step (the reference skips the chunk)
 #pragma unroll
-                for (uint32_t t = 0; t < NH; ++t) {
-                    const float sx = s_xs[c * N + half * NH + t];
-                    const int bb = s_bias[c * N + half * NH + t];
-                    const float r = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(v[t] * MUL + bb), -TC_MAGIC_F), sx), ws, f[t]);
+                for (uint32_t t = 0; t < NQ; ++t) {
+                    const float sx = s_xs[c * N + part * NQ + t];
+                    const int bb = BP ? s_bias[c * N + part * NQ + t] : TC_MAGIC_I;
+                    const int d = BP ? v[t] * 2 + bb : v[t] + bb;
+                    const float r = __fmaf_rn(__fmul_rn(__fadd_rn(__int_as_float(d), -TC_MAGIC_F), sx), ws, f[t]);
                     f[t] = sx != 0.0f ? r : f[t];
                 }
             }
+        };
+        // one step of the software pipeline: the dots of chunk c are on their way into `cur`; once they are in, the buffer goes
+        // back to the issuing thread, the dots of chunk c + 1 are requested into `nxt`, and the chains advance meanwhile
+        auto step = [&](uint32_t c, int (&cur)[NQ], int (&nxt)[NQ], float ws, float &ws_nxt) -> bool {
+            TC_ACC_T(0);
+            tc_ld_wait(cur);
+            TC_ACC_T(1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_drained + 8 * (c % TC_ACC));
+            if (c + 1 < nc) {
+                ws_nxt = scale_of(c + 1);
+                if (!tc_wait(bar_done + 8 * ((c + 1) % TC_ACC), ((c + 1) / TC_ACC) & 1u, s_abort)) return false;
+                tc_fence_after();
+                tc_ld<NQ>(taddr0 + ((c + 1) % TC_ACC) * N, nxt);
+            }
+            TC_ACC_T(2);
+            advance(c, cur, ws);
+            TC_ACC_T(3);
+            return true;
+        };
+        int v0[NQ], v1[NQ];
+        float ws0 = scale_of(0), ws1 = 0.0f;
+        ok = tc_wait(bar_done, 0u, s_abort);
+        if (ok) {
+            tc_fence_after();
+            tc_ld<NQ>(taddr0, v0);
+            for (uint32_t c = 0; c < nc && ok; c += 2) {
+                ok = step(c, v0, v1, ws0, ws1);
+                if (ok && c + 1 < nc) ok = step(c + 1, v1, v0, ws1, ws0);
+            }
         }
+#ifdef K2T_TC_TRACE
+        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) for (int k = 0; k < 4; ++k) g_tc_trace[k] = trace_acc[k];
+#endif
         if (!ok && lane == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
         if (ok && row < a.rows) {
 #pragma unroll
-            for (uint32_t t = 0; t < NH; ++t) {
-                const uint32_t tt = half * NH + t;
+            for (uint32_t t = 0; t < NQ; ++t) {
+                const uint32_t tt = part * NQ + t;
                 if (tt < n_here) a.out[(size_t)(tok0 + tt) * a.out_stride + row] = f[t];
             }
         }
     } else if (warp < TC_EPI_WARPS + TC_DEC_WARPS) {
-        // ------------------------------------------------------------------ decode: thread = row
-        const uint32_t i = tid - TC_EPI_WARPS * 32;                    // 0..127
+        // ------------------------------------------------------------------ decode: group g, thread = row
+        const uint32_t di = tid - TC_EPI_WARPS * 32, grp = di >> 7, i = di & 127u;
         const uint32_t row_c = min(row0 + i, a.rows_pad - 1);          // rows beyond the matrix repeat the last one (never stored)
         if (FMT == FMT_E8Q2) {
             uint32_t *tab = e8q2_templates_smem();
-            if (i < 32) tab[i] = i < 28 ? E8Q2_TEMPLATE_WORDS[i] : 0u;
+            if (di < 32) tab[di] = di < 28 ? E8Q2_TEMPLATE_WORDS[di] : 0u;
             asm volatile("bar.sync 2, %0;" ::"r"(TC_DEC_WARPS * 32) : "memory");
         }
         const uint32_t wring = sbase + L.wring, bring = sbase + L.bring;
         constexpr uint32_t B0 = Cell<FMT>::B0, B1 = Cell<FMT>::B1, B2 = Cell<FMT>::B2;
         constexpr uint32_t PIECES = (N * 4 + TC_M - 1) / TC_M;         // 16-byte activation pieces per thread and chunk
+        // the row's cells of a pass are consecutive: bases per pass, recomputed when the pass changes
+        uint32_t p_cur = 0xffffffffu;
+        const uint8_t *wb0 = nullptr, *wb1 = nullptr, *wb2 = nullptr;
         auto request_w = [&](uint32_t c) {          // the row's cell of chunk c -> ring slot c % TC_PF
-            const uint32_t p = c >> 5, n = tile_chunks(nc, p), slot = wring + (c % TC_PF) * (TC_M * CELL);
-            const size_t cell_i = (size_t)row_c * n + (c & 31u);
-            cp_async16(slot + i * B0, a.plane[0] + tile_code_off(a.rows_pad, B0, p) + cell_i * B0, 16);
-            if (B1 == 16) cp_async16(slot + TC_M * B0 + i * 16, a.plane[1] + tile_code_off(a.rows_pad, 16, p) + cell_i * 16, 16);
-            if (B1 == 8) cp_async8(slot + TC_M * B0 + i * 8, a.plane[1] + tile_code_off(a.rows_pad, 8, p) + cell_i * 8);
-            if (B2 == 16) cp_async16(slot + TC_M * (B0 + B1) + i * 16, a.plane[2] + tile_code_off(a.rows_pad, 16, p) + cell_i * 16, 16);
-            if (B2 == 8) cp_async8(slot + TC_M * (B0 + B1) + i * 8, a.plane[2] + tile_code_off(a.rows_pad, 8, p) + cell_i * 8);
+            const uint32_t p = c >> 5;
+            if (p != p_cur) {
+                p_cur = p;
+                const size_t r_n = (size_t)row_c * tile_chunks(nc, p);
+                wb0 = a.plane[0] + tile_code_off(a.rows_pad, B0, p) + r_n * B0;
+                if (B1) wb1 = a.plane[1] + tile_code_off(a.rows_pad, B1, p) + r_n * B1;
+                if (B2) wb2 = a.plane[2] + tile_code_off(a.rows_pad, B2, p) + r_n * B2;
+            }
+            const uint32_t cc = c & 31u, slot = wring + (c % TC_PF) * (TC_M * CELL);
+            cp_async16(slot + i * B0, wb0 + cc * B0, 16);
+            if (B1 == 16) cp_async16(slot + TC_M * B0 + i * 16, wb1 + cc * 16, 16);
+            if (B1 == 8) cp_async8(slot + TC_M * B0 + i * 8, wb1 + cc * 8);
+            if (B2 == 16) cp_async16(slot + TC_M * (B0 + B1) + i * 16, wb2 + cc * 16, 16);
+            if (B2 == 8) cp_async8(slot + TC_M * (B0 + B1) + i * 8, wb2 + cc * 8);
         };
-        auto request_b = [&](uint32_t c) {          // activation pieces of chunk c: piece j = (token j / 4, bytes 16 (j % 4) ..)
+        // activation pieces of a chunk: piece j = (token j / 4, bytes 16 (j % 4) ..); tokens beyond the batch read as zeros
+        const int8_t *xb[PIECES];
+        uint32_t xb_bytes[PIECES];
+#pragma unroll
+        for (uint32_t k = 0; k < PIECES; ++k) {
+            const uint32_t j = i + k * TC_M, t = j >> 2, kq = j & 3u, tt = min(t, n_here - 1);
+            xb[k] = a.xq + (size_t)(tok0 + tt) * a.cols + kq * 16;
+            xb_bytes[k] = t < n_here ? 16u : 0u;
+        }
+        auto request_b = [&](uint32_t c) {
             const uint32_t slot = bring + (c % TC_PF) * (N * 64);
 #pragma unroll
             for (uint32_t k = 0; k < PIECES; ++k) {
                 const uint32_t j = i + k * TC_M;
-                if (j < N * 4) {
-                    const uint32_t t = j >> 2, kq = j & 3u, tt = min(t, n_here - 1);
-                    cp_async16(slot + j * 16, a.xq + (size_t)(tok0 + tt) * a.cols + (size_t)c * 64 + kq * 16, t < n_here ? 16u : 0u);
-                }
+                if (j < N * 4) cp_async16(slot + j * 16, xb[k] + (size_t)c * 64, xb_bytes[k]);
             }
         };
-        for (uint32_t c = 0; c < TC_PF; ++c) if (c < nc) request_w(c);        // weights do not depend on the predecessor
+        for (uint32_t k = 0; k < TC_PFG; ++k) if (grp + k * TC_GROUPS < nc) request_w(grp + k * TC_GROUPS);     // weights do not depend on the predecessor
         pdl_wait();
         pdl_trigger();
-        for (uint32_t c = 0; c < TC_PF; ++c) { if (c < nc) request_b(c); cp_async_commit(); }
+        for (uint32_t k = 0; k < TC_PFG; ++k) { if (grp + k * TC_GROUPS < nc) request_b(grp + k * TC_GROUPS); cp_async_commit(); }
         bool ok = true;
-        for (uint32_t c = 0; c < nc; ++c) {
+#ifdef K2T_TC_TRACE
+        unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long _tl = clock64();
+#endif
+        for (uint32_t c = grp; c < nc; c += TC_GROUPS) {
             const uint32_t s = c % TC_STAGES;
-            cp_async_wait<TC_PF - 1>();
+            TC_ACC_T(0);
+            cp_async_wait<TC_PFG - 1>();
+            TC_ACC_T(1);
             // raw cell -> registers
             Raw<FMT> w;
             {
@@ -299,15 +407,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
                     piece[k] = j < N * 4 ? lds_u32x4_tc(slot + j * 16) : make_uint4(0, 0, 0, 0);
                 }
             }
-            // the slot is free again: request chunk c + TC_PF (one group per chunk, also when nothing is left)
+            // the slot is free again: request the group's chunk after next (one copy group per chunk, also when nothing is left)
             if (c + TC_PF < nc) { request_w(c + TC_PF); request_b(c + TC_PF); }
             cp_async_commit();
             uint32_t u[16];
             decode<FMT>(w, a.cb, u);
+            TC_ACC_T(2);
             if (c >= TC_STAGES) {
-                ok = tc_wait(bar_empty + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort);
+                ok = tc_wait_idle(bar_done + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort) &&
+                     tc_wait_idle(bar_drained + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort);
                 if (!ok) break;
             }
+            TC_ACC_T(3);
             const uint32_t a_dst = sbase + L.a + s * TC_A_STAGE + (i >> 3) * TC_SBO + (i & 7u) * 16;
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k) sts_u32x4_tc(a_dst + k * TC_LBO, u[4 * k], u[4 * k + 1], u[4 * k + 2], u[4 * k + 3]);
@@ -321,8 +432,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
                 }
             }
             fence_proxy_async();
-            mbar_arrive(bar_full + 8 * s);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full + 8 * s);
+            TC_ACC_T(4);
         }
+#ifdef K2T_TC_TRACE
+        if (di == 0 && blockIdx.x == 0 && blockIdx.y == 0) for (int k = 0; k < 5; ++k) g_tc_trace[8 + k] = trace_acc[k];
+#endif
         cp_async_wait<0>();
         if (!ok && lane == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
     } else if (lane == 0) {
@@ -330,26 +446,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
         // instruction descriptor: int32 accumulators, signed 8-bit A and B, both K-major, N / 8, M / 16
         const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((TC_M >> 4) << 24);
         bool ok = true;
+#ifdef K2T_TC_TRACE
+        unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long _tl = clock64();
+#endif
         for (uint32_t c = 0; c < nc; ++c) {
             const uint32_t s = c % TC_STAGES, b = c % TC_ACC;
+            TC_ACC_T(0);
             ok = tc_wait(bar_full + 8 * s, (c / TC_STAGES) & 1u, s_abort);
-            if (ok && c >= TC_ACC) ok = tc_wait(bar_acc_empty + 8 * b, ((c / TC_ACC) - 1u) & 1u, s_abort);
+            TC_ACC_T(1);
             if (!ok) break;
             tc_fence_after();
             const uint64_t da = tc_smem_desc(sbase + L.a + s * TC_A_STAGE), db = tc_smem_desc(sbase + L.b + s * (N * 64));
             const uint32_t d = tmem + b * N;
             tc_mma_i8(d, da, db, idesc, 0u);
             tc_mma_i8(d, da + ((2 * TC_LBO) >> 4), db + ((2 * TC_LBO) >> 4), idesc, 1u);      // columns 32..63: two core matrices on
-            tc_commit(bar_empty + 8 * s);
-            tc_commit(bar_acc_full + 8 * b);
+            tc_commit(bar_done + 8 * s);
+            TC_ACC_T(3);
         }
+#ifdef K2T_TC_TRACE
+        if (blockIdx.x == 0 && blockIdx.y == 0) for (int k = 0; k < 4; ++k) g_tc_trace[16 + k] = trace_acc[k];
+#endif
         if (!ok && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == TC_EPI_WARPS + TC_DEC_WARPS) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(TC_ACC * N)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tc_tmem_cols(N)) : "memory");
     }
 }
 
@@ -365,11 +489,11 @@ cudaError_t launch_tc_n(cudaStream_t stream, const TcArgs &args, bool pdl) {
 
 template <int FMT>
 cudaError_t launch_tc_fmt(cudaStream_t stream, const TcArgs &args, int sm_count, bool pdl) {
-    // the widest token tile that still gives every SM a CTA; narrower tiles while the grid is short (the fp32 chains, the
-    // bound of this kernel, cost a CTA time in proportion to its tokens)
+    // the narrowest token tile that holds the batch, halved while the grid would leave half the SMs idle: a CTA's time per
+    // chunk is bounded by the expansion of its weights and the hand-offs between its roles, less by its tokens
     const uint32_t row_tiles = (args.g.rows + TC_M - 1) / TC_M;
-    uint32_t n = 64;
-    while (n > 16 && (args.n_tok <= n / 2 || row_tiles * ((args.n_tok + n - 1) / n) < (uint32_t)sm_count)) n /= 2;
+    uint32_t n = args.n_tok > 32 ? 64 : args.n_tok > 16 ? 32 : 16;
+    while (n > 16 && 2 * row_tiles * ((args.n_tok + n - 1) / n) <= (uint32_t)sm_count) n /= 2;
     for (; n >= 16; n /= 2) {          // a tile whose tables do not fit shared memory: try the next narrower one
         cudaError_t e = n == 64 ? launch_tc_n<FMT, 64>(stream, args, pdl) : n == 32 ? launch_tc_n<FMT, 32>(stream, args, pdl) : launch_tc_n<FMT, 16>(stream, args, pdl);
         if (e != cudaErrorNotSupported) return e;
@@ -380,14 +504,14 @@ cudaError_t launch_tc_fmt(cudaStream_t stream, const TcArgs &args, int sm_count,
 uint32_t tc_min_tokens() {
     static const uint32_t v = [] {
         const char *s = std::getenv("KRONOS_CUDA_TC_MIN_TOKENS");          // 0 = never use the tensor-core path
-        return s ? (uint32_t)std::atoi(s) : 8u;
+        return s ? (uint32_t)std::atoi(s) : 16u;
     }();
     return v;
 }
 
 }  // namespace
 
-// y[t] = W x[t] for any number of tokens: batches of at least `KRONOS_CUDA_TC_MIN_TOKENS` (8) go to the tensor-core kernel in
+// y[t] = W x[t] for any number of tokens: batches of at least `KRONOS_CUDA_TC_MIN_TOKENS` (16) go to the tensor-core kernel in
 // one launch, shorter ones (and calls that ask for the integer dots) to the 4-token weight passes.
 cudaError_t launch_gemv_batch(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs, const int32_t *xsum,
                               size_t n_tok, float *out, size_t out_stride, int32_t *int_dots, int sm_count, uint32_t *err_flag,
@@ -428,5 +552,9 @@ cudaError_t launch_gemv_batch(cudaStream_t stream, const DeviceMatrix &m, const 
     }
     return cudaSuccess;
 }
+
+#ifdef K2T_TC_TRACE
+extern "C" int k2t_tc_trace_read(unsigned long long *out) { return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(unsigned long long) * 32); }
+#endif
 
 }  // namespace k2t

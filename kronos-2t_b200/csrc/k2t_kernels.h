@@ -25,7 +25,7 @@ cudaError_t launch_gemv(cudaStream_t stream, const DeviceMatrix &m, const int8_t
                         const int32_t *xsum, uint32_t n_tok, float *out, size_t out_stride, int32_t *int_dots,
                         int sm_count, uint32_t *err_flag, uint32_t *launches, bool pdl = false);
 
-// The same product for any number of tokens: batches of eight tokens or more run on the tensor cores in one launch
+// The same product for any number of tokens: batches of sixteen tokens or more run on the tensor cores in one launch
 // (k2t_gemm_tc.cu: exact int32 chunk dots by `tcgen05.mma`, the fp32 chains in the same order), shorter ones and calls that
 // ask for the integer dots as 4-token weight passes.  Same results either way.
 cudaError_t launch_gemv_batch(cudaStream_t stream, const DeviceMatrix &m, const int8_t *xq, const float *xs, const int32_t *xsum,

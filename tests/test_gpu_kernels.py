@@ -170,9 +170,9 @@ def _wide_matrix(oracle, fmt, rows, cols):
 
 
 @pytest.mark.parametrize("fmt", ["b4", "b5", "b6", "nf3", "nf4", "nf4g128", "nf5g128", "e8q2"])
-@pytest.mark.parametrize("rows,cols,n_tok", [(54, 192, 8), (71, 1536, 17), (300, 2112, 33), (128, 576, 64), (260, 4160, 100)])
+@pytest.mark.parametrize("rows,cols,n_tok", [(54, 192, 16), (71, 1536, 17), (300, 2112, 33), (128, 576, 64), (260, 4160, 100)])
 def test_wide_batch_gemm_on_tensor_cores(ctx, oracle, fmt, rows, cols, n_tok):
-    """Batches of eight tokens and more take the tensor-core kernel (exact int32 chunk dots by tcgen05.mma, the fp32 chains in
+    """Batches of sixteen tokens and more take the tensor-core kernel (exact int32 chunk dots by tcgen05.mma, the fp32 chains in
     chunk order): outputs equal the oracle's batch form bit for bit - odd row counts, partial token tiles, more than one pass
     of 32 chunks, whole chunks of zero activations for some tokens (their chain steps are skipped)."""
     m = _wide_matrix(oracle, fmt, rows, cols)
