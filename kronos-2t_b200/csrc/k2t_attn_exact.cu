@@ -209,7 +209,8 @@ struct ValSmem {
     static constexpr uint32_t TILE_T = VAL_TILE * HD;             // one transposed tile: a byte per value, row = dimension
     static constexpr uint32_t W_OFF = 128 + NST * STAGE + VAL_TBUF * TILE_T;
     // barriers, row ring, transposed tiles, weights (16 floats of slack: the chain requests the next block's weights ahead)
-    static __host__ __device__ size_t bytes(uint32_t ctx_cap) { return W_OFF + (size_t)NW * (ctx_cap + 16) * 4; }
+    static __host__ __device__ uint32_t w_off(bool direct) { return direct ? 128 + NST * STAGE : W_OFF; }
+    static __host__ __device__ size_t bytes(uint32_t ctx_cap, bool direct) { return w_off(direct) + (size_t)NW * (ctx_cap + 16) * 4; }
 };
 
 #define VAL_MARK(i) do { if (a.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.trace[i] = (unsigned long long)clock64(); } while (0)
@@ -238,11 +239,12 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
     const uint32_t bar_full = bar0, bar_rows_free = bar0 + 8 * NST, bar_t_full = bar0 + 16 * NST, bar_t_free = bar0 + 16 * NST + 8 * VAL_TBUF;
     uint8_t *stages = dyn + 128;
     const uint32_t tiles_t = (uint32_t)__cvta_generic_to_shared(dyn + 128 + (size_t)NST * Sm::STAGE);
-    float *W = reinterpret_cast<float *>(dyn + Sm::W_OFF);
-    const uint32_t w_stride = a.ctx_cap + 16;                                // floats between the weight vectors of the NF4 groups
     // direct: the cache holds a block-transposed copy of the value rows (ExactAttnArgs.v_t): tiles land ready for the chains,
-    // the transposing warps only compute the value weights, and the chain warps free the ring stages themselves
+    // the transposing warps only compute the value weights, and the chain warps free the ring stages themselves; no
+    // transposed tiles exist then, and the weights follow the ring at once (the launcher sizes shared memory the same way)
     const bool direct = !KV4 && a.v_t != nullptr && a.ring.window == 0;
+    float *W = reinterpret_cast<float *>(dyn + Sm::w_off(direct));
+    const uint32_t w_stride = a.ctx_cap + 16;                                // floats between the weight vectors of the NF4 groups
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_rows_free + 8 * s, direct ? CW : NTW); }
         for (uint32_t s = 0; s < VAL_TBUF; ++s) { mbar_init(bar_t_full + 8 * s, NTW); mbar_init(bar_t_free + 8 * s, CW); }
@@ -528,7 +530,7 @@ __global__ void __launch_bounds__(VAL_THREADS) attn_values_kernel(const ExactAtt
 // ------------------------------------------------------------------------------------------------
 template <int HD, bool KV4>
 static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl, uint32_t n_tok) {
-    size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap);
+    size_t smem = ValSmem<HD, KV4>::bytes(a.ctx_cap, !KV4 && a.v_t != nullptr && a.ring.window == 0);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
     // One token: few CTAs, each a latency chain.  Asking for more than half an SM's shared memory keeps two of them off the
     // same SM (the block scheduler otherwise puts them wherever the scores kernel frees room first, and chain warps that

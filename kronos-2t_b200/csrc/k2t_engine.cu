@@ -61,6 +61,7 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    uint32_t ctx_bound = 0;                   // prompt batches (launched eagerly, position known on the host): no token of the batch sees more positions; 0 = size launches for the whole cache
     uint32_t kv_stride = 0;                   // cache rows per (layer, kv head): the rows the geometry needs (max_seq_len, or sinks + ring) rounded up to 32, so every 32-row tile of rows and scales starts on 16 bytes
     k2t::KvRing ring{};                       // sliding-window + sink ring (all zero: row = position)
     uint32_t kv_rows = 0;                     // rows in use per (layer, kv head)
@@ -228,6 +229,15 @@ static_assert(MAX_BATCH == ATTN_BATCH, "the attention scratch is sized for one p
 // Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
 // output of a row-parallel projection: the kernel exchanges and sums the ranks' partials itself.
 // `partial`: delta holds this rank's share only (row-parallel projection under tensor parallelism, routed experts under
+// Context the attention launches beyond 512 positions are sized for (grid of the scores kernel, shared memory of the values
+// kernel): the cache's capacity (a captured decode step is replayed at any position), or, for a prompt batch whose last
+// position the host knows, that position rounded up - two values CTAs fit an SM then, and no scores CTA starts for nothing.
+uint32_t attn_ctx_cap(const KronosCudaEngine *e) {
+    const uint32_t full = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride;
+    if (e->ctx_bound == 0) return full;
+    return std::min(full, (e->ctx_bound + 127u) & ~127u);
+}
+
 // expert parallelism).
 bool norm_quant(KronosCudaEngine *e, const float *delta, const float *w, float *x_norm, uint32_t T, bool pdl, bool partial) {
     const KronosCudaEngineConfig &c = e->cfg;
@@ -340,7 +350,7 @@ bool enqueue_attention_batch(KronosCudaEngine *e, uint32_t l, uint32_t T) {
     xa.out_q = e->act_q; xa.out_scales = e->act_s; xa.out_sums = e->act_m; xa.out_chunk0 = c.o_chunk0;
     xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
     xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
-    xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
+    xa.ctx_cap = attn_ctx_cap(e); xa.ring = e->ring;
     xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err; xa.trace = nullptr; xa.v_t = e->v_t;
     return count(e, launch_attention_exact(s, xa, e->pdl, T), "attention", 2);
 }
@@ -386,7 +396,7 @@ bool enqueue_attention(KronosCudaEngine *e, uint32_t l, uint32_t t, uint32_t T, 
                 xa.out_q = oq; xa.out_scales = os; xa.out_sums = om; xa.out_chunk0 = c.o_chunk0;
                 xa.n_kv = c.num_key_value_heads; xa.group = c.num_attention_heads / c.num_key_value_heads; xa.head_dim = hd;
                 xa.max_seq = e->kv_stride; xa.layer = l; xa.sc_stride = e->kv_stride; xa.blk_stride = (e->kv_stride + 127) / 128;
-                xa.ctx_cap = e->ring.window ? (e->ring.window + 3u) & ~3u : e->kv_stride; xa.ring = e->ring;
+                xa.ctx_cap = attn_ctx_cap(e); xa.ring = e->ring;
                 xa.kv_bits = c.kv_bits; xa.attn_scale = 1.0f / sqrtf((float)hd); xa.err_flag = e->ctx->d_err;
                 xa.trace = (e->attn_trace && l == 0) ? e->d_dbg + 16 : nullptr; xa.v_t = e->v_t;
                 return count(e, launch_attention_exact(s, xa, e->pdl), "attention", 2);
@@ -1318,7 +1328,10 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
             if (!cuda_ok(ctx, cudaMemcpyAsync(e->hidden, embeds + t0 * h, (size_t)T * h * 4, cudaMemcpyHostToDevice, ctx->stream), "copy embeddings")) return -1;
         }
         const Tail tail = all_logits ? Tail::AllLogits : (last ? Tail::LastLogits : Tail::None);
-        if (!enqueue_batch(e, T, tokens != nullptr, tail, pos_start + t0 + T > ATTN_EXACT_CTX)) return -1;
+        e->ctx_bound = (uint32_t)(pos_start + t0 + T);
+        const bool queued = enqueue_batch(e, T, tokens != nullptr, tail, pos_start + t0 + T > ATTN_EXACT_CTX);
+        e->ctx_bound = 0;
+        if (!queued) return -1;
         e->last_row = T - 1;
         T_done = T;
         if (all_logits && !cuda_ok(ctx, cudaMemcpyAsync(all_logits + t0 * v, e->logits, (size_t)T * v * 4, cudaMemcpyDeviceToHost, ctx->stream), "copy logits")) return -1;
