@@ -469,7 +469,7 @@ def run_b200(args, rank, world, local_rank):
                 roofline["sharded_parity"] = sharded_parity(ctx, rank, world, dist)
             except Exception as exc:
                 roofline["sharded_parity"] = {"error": f"{type(exc).__name__}: {exc}"}
-        roofline["prefill_note"] = ("prompt batches of 64 tokens: every dense projection is one launch of the tensor-core kernel (tcgen05.mma kind::i8 for the "
+        roofline["prefill_note"] = ("prompt batches of 256 tokens: every dense projection is one launch of the tensor-core kernel (tcgen05.mma kind::i8 for the "
                                     "exact chunk dots, fp32 chains on the CUDA cores in the reference's order), attention of the batch side by side; "
                                     "int8_TOPs = 2 x multiply-adds of the projections x tok/s; the MoE experts still run as expert-batched GEMVs")
         roofline["decode_note"] = ("frac = bytes_per_token * tok_s / (n_gpus * peak): weights of one step in the reference's file format + the cached "
@@ -610,7 +610,7 @@ def decode_tok_s(ctx, stream, timed_region, world):
 
 
 def _prefill(eng, rng, vocab, lo, hi, timed_region=None):
-    """Prompt positions [lo, hi) of random token ids (batches of 64 tokens: every projection one tensor-core weight pass); returns
+    """Prompt positions [lo, hi) of random token ids (batches of 256 tokens: every projection one tensor-core launch); returns
     tok/s when timed - the second of two identical passes, so that no kernel is loaded inside the timed region."""
     toks = rng.integers(0, vocab, hi - lo).astype("uint32")
     eng.forward_token_ids(toks, pos_start=lo)

@@ -34,7 +34,7 @@ struct EngineLayer {
     k2t::ExpertCodebook *d_gu_books = nullptr, *d_dn_books = nullptr; // device tables: decode tables of every expert
     int gu_fmt = -1, dn_fmt = -1;                                     // kernel format of the layer's experts
     uint32_t expert0 = 0;                                             // first expert held by this rank (expert parallelism)
-    uint32_t *d_route_ids = nullptr;                                  // [MAX_BATCH][32] routes of the last batch
+    uint32_t *d_route_ids = nullptr;                                  // [max_batch][32] routes of the last batch
     float *d_route_w = nullptr;
     // shared expert of a MoE layer (SharedMoeExpert, sparse_moe.rs:223-315): its matrices live in gate_up / down above
     uint32_t sh_inter = 0;
@@ -61,6 +61,7 @@ struct KronosCudaEngine {
     float *k_scale = nullptr, *v_scale = nullptr;
     uint32_t *d_token = nullptr, *d_pos = nullptr, *d_step = nullptr, *d_history = nullptr;
     uint32_t n_split = 32;
+    uint32_t max_batch = 256;                 // tokens per prompt batch: their projections run on the tensor cores in one weight pass (k2t_gemm_tc.cu), their attention side by side; every per-token buffer holds this many rows (KRONOS_CUDA_PROMPT_BATCH, 16..512)
     uint32_t ctx_bound = 0;                   // prompt batches (launched eagerly, position known on the host): no token of the batch sees more positions; 0 = size launches for the whole cache
     uint32_t kv_stride = 0;                   // cache rows per (layer, kv head): the rows the geometry needs (max_seq_len, or sinks + ring) rounded up to 32, so every 32-row tile of rows and scales starts on 16 bytes
     k2t::KvRing ring{};                       // sliding-window + sink ring (all zero: row = position)
@@ -69,7 +70,7 @@ struct KronosCudaEngine {
     float *x_norm = nullptr, *moe_gu = nullptr, *moe_out = nullptr, *router_logits = nullptr;
     uint32_t *router_done = nullptr;
     int8_t *moe_q = nullptr; float *moe_s = nullptr; int32_t *moe_m = nullptr;
-    // shared-expert workspace, [MAX_BATCH] rows each: gate_up outputs, the down projection's activation, outputs, gate values
+    // shared-expert workspace, [max_batch] rows each: gate_up outputs, the down projection's activation, outputs, gate values
     uint32_t sh_inter_max = 0;
     float *sh_gu = nullptr, *sh_out = nullptr, *sh_scale = nullptr;
     int8_t *sh_q = nullptr; float *sh_s = nullptr; int32_t *sh_m = nullptr;
@@ -80,7 +81,7 @@ struct KronosCudaEngine {
     uint32_t *tp_done = nullptr;              // CTAs of the current fused exchange that have finished (device word)
     std::vector<void *> tp_peers;            // mappings opened with cudaIpcOpenMemHandle
     bool tp_ready = false;
-    float *logits_local = nullptr;            // this rank's logits slice [MAX_BATCH][vocab_size]
+    float *logits_local = nullptr;            // this rank's logits slice [max_batch][vocab_size]
     KronosCudaMatrix *embed_matrix = nullptr; // whole lm_head for the token lookup (tied embeddings under tp)
     uint32_t last_row = 0;                    // row of `hidden` that holds the last forwarded token (prompt batches)
     bool pdl = true;                          // kernels of a step overlap their prologues with the predecessor's tail
@@ -126,7 +127,6 @@ bool dev_alloc(KronosCudaEngine *e, T *&p, size_t count, const T *host = nullptr
     return cuda_ok(e->ctx, cudaMemsetAsync(p, 0, bytes, e->ctx->stream), "clear");
 }
 
-constexpr uint32_t ATTN_BATCH = 64;    // tokens whose attention runs side by side (= the prompt batch, MAX_BATCH below)
 
 void dev_free(KronosCudaEngine *e, void *p) {
     if (!p) return;
@@ -163,7 +163,7 @@ bool alloc_kv(KronosCudaEngine *e, uint32_t bits, uint32_t window, uint32_t sink
     e->split_kv = e->ring.window == 0 && ((c.flags & KRONOS_CUDA_ENGINE_SPLIT_KV_ATTENTION) != 0 || longest > attention_exact_max_ctx(hd, bits));
     if (e->ring.window && longest > attention_exact_max_ctx(hd, bits)) return fail(ctx, "kv_window is longer than the attention kernel can hold");
     const size_t slots = (size_t)c.num_layers * c.num_key_value_heads * e->kv_stride;
-    const bool ok = dev_alloc(e, e->attn_sc, (size_t)ATTN_BATCH * n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)ATTN_BATCH * n_q * ((e->kv_stride + 127) / 128)) &&
+    const bool ok = dev_alloc(e, e->attn_sc, (size_t)e->max_batch * n_q * e->kv_stride) && dev_alloc(e, e->attn_bmax, (size_t)e->max_batch * n_q * ((e->kv_stride + 127) / 128)) &&
                     dev_alloc(e, e->k_q8, bits == 4 ? slots * hd / 2 : slots * hd) && dev_alloc(e, e->v_q8, bits == 4 ? slots * hd / 2 : slots * hd) &&
                     dev_alloc(e, e->k_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots) &&      // NF4: bf16 per 64 values
                     dev_alloc(e, e->v_scale, bits == 4 ? (slots * (hd / 64) + 1) / 2 : slots);
@@ -223,8 +223,6 @@ bool tp_gather(KronosCudaEngine *e, const float *slice, float *all, uint32_t n) 
     return count(e, launch_tp_exchange(e->ctx->stream, e->tp, slice, all, n, n, e->pdl), "tp gather");
 }
 
-constexpr uint32_t MAX_BATCH = 64;     // tokens per prompt batch: their projections run on the tensor cores in one weight pass (k2t_gemm_tc.cu), their attention side by side
-static_assert(MAX_BATCH == ATTN_BATCH, "the attention scratch is sized for one prompt batch");
 
 // Residual add + RMSNorm + activation of the next projection.  Under tensor parallelism `delta` is this rank's partial
 // output of a row-parallel projection: the kernel exchanges and sums the ranks' partials itself.
@@ -729,7 +727,7 @@ std::string setup_moe_layer(KronosCudaEngine *e, EngineLayer &L, const KronosCud
     }
     if (!dev_alloc(e, L.d_gu_books, E, gu_books.data()) || !dev_alloc(e, L.d_dn_books, E, dn_books.data()) ||
         !dev_alloc(e, L.d_gu_bases, E, gu_bases.data()) || !dev_alloc(e, L.d_dn_bases, E, dn_bases.data()) ||
-        !dev_alloc(e, L.d_route_ids, (size_t)MAX_BATCH * 32) || !dev_alloc(e, L.d_route_w, (size_t)MAX_BATCH * 32) ||
+        !dev_alloc(e, L.d_route_ids, (size_t)e->max_batch * 32) || !dev_alloc(e, L.d_route_w, (size_t)e->max_batch * 32) ||
         !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "MoE tables"))
         return ctx->err;
     e->has_moe = true;
@@ -797,6 +795,10 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
         const uint32_t want = (8u * (uint32_t)ctx->sm_count + c.num_key_value_heads - 1) / c.num_key_value_heads;
         e->n_split = std::min(128u, std::max(32u, (want + 3u) & ~3u));
     }
+    if (const char *v = std::getenv("KRONOS_CUDA_PROMPT_BATCH")) {                  // tokens per prompt batch (default 256: 1.7B-shape prompts 13.5k / 18.8k / 21.8k tok/s at 64 / 128 / 256)
+        const uint32_t n = (uint32_t)std::strtoul(v, nullptr, 10);
+        e->max_batch = std::min(512u, std::max(16u, (n + 15u) & ~15u));
+    }
     if (const char *v = std::getenv("KRONOS_CUDA_PDL")) e->pdl = v[0] != '0';     // measurement switch (default on)
     if (const char *v = std::getenv("KRONOS_CUDA_ATTN_TRACE")) e->attn_trace = v[0] == '1';
     if (const char *v = std::getenv("KRONOS_CUDA_FUSED")) e->fused = v[0] == '1';     // measurement switch
@@ -851,24 +853,24 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     const uint32_t act_n = std::max(std::max(h, q_dim), inter), n_q = c.num_attention_heads;
     bool ok = dev_alloc(e, e->final_norm, h, final_norm) && dev_alloc(e, e->rope, (size_t)c.max_seq_len * hd, rope) &&
               (embed_bf16 == nullptr || dev_alloc(e, e->embed_bf16, (size_t)(c.tp_size > 1 ? c.vocab_total : c.vocab_size) * h, embed_bf16)) &&   // every rank keeps the whole table
-              // per-token vectors hold MAX_BATCH tokens (prompt batches), [token][n]
-              dev_alloc(e, e->hidden, (size_t)MAX_BATCH * h) && dev_alloc(e, e->hidden2, h) && dev_alloc(e, e->proj, (size_t)MAX_BATCH * h) &&
-              dev_alloc(e, e->qkv, (size_t)MAX_BATCH * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)MAX_BATCH * 2 * inter) &&
-              dev_alloc(e, e->logits, (size_t)MAX_BATCH * (c.tp_size > 1 ? c.vocab_total : c.vocab_size)) && dev_alloc(e, e->act_q, (size_t)MAX_BATCH * act_n) &&
-              dev_alloc(e, e->act_s, (size_t)MAX_BATCH * act_n / 64) && dev_alloc(e, e->act_m, (size_t)MAX_BATCH * act_n / 64) &&
-              dev_alloc(e, e->q_i8, (size_t)MAX_BATCH * q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, (size_t)MAX_BATCH * n_q) &&
+              // per-token vectors hold max_batch tokens (prompt batches), [token][n]
+              dev_alloc(e, e->hidden, (size_t)e->max_batch * h) && dev_alloc(e, e->hidden2, h) && dev_alloc(e, e->proj, (size_t)e->max_batch * h) &&
+              dev_alloc(e, e->qkv, (size_t)e->max_batch * qkv_rows) && dev_alloc(e, e->gate_up, (size_t)e->max_batch * 2 * inter) &&
+              dev_alloc(e, e->logits, (size_t)e->max_batch * (c.tp_size > 1 ? c.vocab_total : c.vocab_size)) && dev_alloc(e, e->act_q, (size_t)e->max_batch * act_n) &&
+              dev_alloc(e, e->act_s, (size_t)e->max_batch * act_n / 64) && dev_alloc(e, e->act_m, (size_t)e->max_batch * act_n / 64) &&
+              dev_alloc(e, e->q_i8, (size_t)e->max_batch * q_dim) && dev_alloc(e, e->attn_tap, q_dim) && dev_alloc(e, e->q_scale, (size_t)e->max_batch * n_q) &&
               dev_alloc(e, e->part_m, (size_t)n_q * e->n_split) && dev_alloc(e, e->part_l, (size_t)n_q * e->n_split) &&
               dev_alloc(e, e->part_o, (size_t)n_q * e->n_split * hd) &&
               alloc_kv(e, c.kv_bits, c.kv_window, c.kv_sinks) &&
-              dev_alloc(e, e->d_token, MAX_BATCH) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
+              dev_alloc(e, e->d_token, e->max_batch) && dev_alloc(e, e->d_pos, 1) && dev_alloc(e, e->d_step, 1) &&
               dev_alloc(e, e->d_history, c.max_seq_len) && dev_alloc(e, e->d_dbg, 32) && dev_alloc(e, e->argmax_scratch, ARGMAX_SCRATCH_WORDS);
     const uint32_t xg = c.tp_size > 1 ? c.tp_size : c.ep_size, xr = c.tp_size > 1 ? c.tp_rank : c.ep_rank;     // exchange group
     if (ok && xg > 1) {
         if (e->has_moe && c.tp_size > 1) return bad("engine_create: sparse-MoE layers are not combined with tensor parallelism");
-        const size_t slot = std::max<size_t>((size_t)MAX_BATCH * h, c.vocab_size), floats = 2 * (size_t)xg * slot;
+        const size_t slot = std::max<size_t>((size_t)e->max_batch * h, c.vocab_size), floats = 2 * (size_t)xg * slot;
         void *raw = nullptr;
-        // floats | 256 bytes of flags | (value, call number) words of the fused sums: [2][tp][MAX_BATCH * hidden] x 8 bytes
-        const size_t ll_slot = (size_t)MAX_BATCH * h, total = floats * 4 + 256 + 2 * (size_t)xg * ll_slot * 8;
+        // floats | 256 bytes of flags | (value, call number) words of the fused sums: [2][tp][max_batch * hidden] x 8 bytes
+        const size_t ll_slot = (size_t)e->max_batch * h, total = floats * 4 + 256 + 2 * (size_t)xg * ll_slot * 8;
         ok = cuda_ok(ctx, cudaMalloc(&raw, total), "cudaMalloc(tp exchange)");
         if (ok) {
             e->allocs.push_back(raw);
@@ -878,7 +880,7 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
             e->tp.wait_polls = TP_WAIT_POLLS_DEFAULT;
             if (const char *v = std::getenv("KRONOS_CUDA_PEER_WAIT_POLLS")) e->tp.wait_polls = (uint32_t)std::strtoul(v, nullptr, 10);
             ok = cuda_ok(ctx, cudaMemsetAsync(raw, 0, total, ctx->stream), "clear tp exchange") &&
-                 dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)MAX_BATCH * c.vocab_size);
+                 dev_alloc(e, e->tp.epoch, 1) && dev_alloc(e, e->tp_done, 1) && dev_alloc(e, e->logits_local, (size_t)e->max_batch * c.vocab_size);
             e->tp.tp = xg; e->tp.rank = xr; e->tp.slot = (uint32_t)slot; e->tp.err = ctx->d_err;
             e->tp.peer_data[xr] = e->tp_buf;
             e->tp.peer_flags[xr] = reinterpret_cast<uint32_t *>(e->tp_buf + floats);
@@ -886,14 +888,14 @@ KronosCudaEngine *kronos_cuda_engine_create(KronosCudaContext *ctx, const Kronos
     }
     if (ok && e->has_moe) {
         const uint32_t k = std::min(c.moe_top_k, c.moe_num_experts), dff = c.moe_d_ff;
-        ok = dev_alloc(e, e->x_norm, (size_t)MAX_BATCH * h) && dev_alloc(e, e->router_logits, (size_t)MAX_BATCH * 256) && dev_alloc(e, e->router_done, MAX_BATCH) &&
-             dev_alloc(e, e->moe_gu, (size_t)MAX_BATCH * k * 2 * dff) && dev_alloc(e, e->moe_out, (size_t)MAX_BATCH * k * h) &&
-             dev_alloc(e, e->moe_q, (size_t)MAX_BATCH * k * dff) && dev_alloc(e, e->moe_s, (size_t)MAX_BATCH * k * dff / 64) &&
-             dev_alloc(e, e->moe_m, (size_t)MAX_BATCH * k * dff / 64);
+        ok = dev_alloc(e, e->x_norm, (size_t)e->max_batch * h) && dev_alloc(e, e->router_logits, (size_t)e->max_batch * 256) && dev_alloc(e, e->router_done, e->max_batch) &&
+             dev_alloc(e, e->moe_gu, (size_t)e->max_batch * k * 2 * dff) && dev_alloc(e, e->moe_out, (size_t)e->max_batch * k * h) &&
+             dev_alloc(e, e->moe_q, (size_t)e->max_batch * k * dff) && dev_alloc(e, e->moe_s, (size_t)e->max_batch * k * dff / 64) &&
+             dev_alloc(e, e->moe_m, (size_t)e->max_batch * k * dff / 64);
         if (ok && e->sh_inter_max > 0) {
             const size_t si = e->sh_inter_max;
-            ok = dev_alloc(e, e->sh_gu, (size_t)MAX_BATCH * 2 * si) && dev_alloc(e, e->sh_out, (size_t)MAX_BATCH * h) && dev_alloc(e, e->sh_scale, MAX_BATCH) &&
-                 dev_alloc(e, e->sh_q, (size_t)MAX_BATCH * si) && dev_alloc(e, e->sh_s, (size_t)MAX_BATCH * si / 64) && dev_alloc(e, e->sh_m, (size_t)MAX_BATCH * si / 64);
+            ok = dev_alloc(e, e->sh_gu, (size_t)e->max_batch * 2 * si) && dev_alloc(e, e->sh_out, (size_t)e->max_batch * h) && dev_alloc(e, e->sh_scale, e->max_batch) &&
+                 dev_alloc(e, e->sh_q, (size_t)e->max_batch * si) && dev_alloc(e, e->sh_s, (size_t)e->max_batch * si / 64) && dev_alloc(e, e->sh_m, (size_t)e->max_batch * si / 64);
         }
     }
     if (!ok || !cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "engine_create sync")) return bad(ctx->err);
@@ -1314,11 +1316,11 @@ static int32_t forward_common(KronosCudaEngine *e, const float *embeds, const ui
         if (all_logits) std::memcpy(all_logits, last_logits, v * 4);
         return 0;
     }
-    // prompt: batches of up to MAX_BATCH tokens (forward_prompt / forward_batch_sdot_impl, real_llm.rs:7407-7448, 7450-7860):
+    // prompt: batches of up to max_batch tokens (forward_prompt / forward_batch_sdot_impl, real_llm.rs:7407-7448, 7450-7860):
     // every projection as one tensor-core weight pass over the batch, the attention of the batch's tokens side by side
     if (!set_u32(e, e->d_pos, (uint32_t)pos_start)) return -1;
     for (size_t t0 = 0, T_done = 0; t0 < n_tok; t0 += T_done) {
-        uint32_t T = (uint32_t)std::min<size_t>(MAX_BATCH, n_tok - t0);
+        uint32_t T = (uint32_t)std::min<size_t>(e->max_batch, n_tok - t0);
         const size_t p0 = pos_start + t0;
         if (e->split_kv && p0 < ATTN_EXACT_CTX && p0 + T > ATTN_EXACT_CTX) T = (uint32_t)(ATTN_EXACT_CTX - p0);    // split-KV kernels: a batch stays on one side of the attention switch
         const bool last = t0 + T == n_tok;
