@@ -109,8 +109,9 @@ int32_t kronos_cuda_fwht_quant(KronosCudaContext *ctx, const float *x, size_t n_
                                int8_t *q, float *scales, int32_t *sums);
 
 /* nibble4_sdot_stripe_range_raw (simd_lut.rs:3536-3582) / nf_sdot_stripe_range_raw (5687-5760) for
- * n_tok = 1 and the batch forms (4101-4331, 6689-7029) for any n_tok >= 1 (one weight pass serves up to 4 tokens;
- * longer batches are split into such passes inside the call), over all rows:
+ * n_tok = 1 and the batch forms (4101-4331, 6689-7029) for any n_tok >= 1 (up to 15 tokens run as weight passes
+ * of 4 tokens inside the call; 16 and more in one launch whose integer dots run on the tensor cores - the same results
+ * either way; a call that asks for int_dots always takes the passes), over all rows:
  * out[t*out_stride + r] = sum over chunks of fmaf((float)dot*xs, w_scale, acc), ascending chunks,
  * chunks with xs == 0 skipped.  int_dots (optional, [n_tok][rows][cols/64]) receives the exact
  * int32 chunk dots (bipolar: 2*sum(u*q) - (2^B-1)*xsum; NF: sum(cb[idx]*q)). xsum may be NULL for NF. */

@@ -29,6 +29,24 @@ def make(ctx, oracle, cfg, mode, **kw):
     return spec, k2.Engine(ctx, spec), oracle.Model(spec)
 
 
+@pytest.mark.parametrize("batch", [48, 112])
+def test_ring_wraparound_with_other_prompt_batches(ctx, oracle, monkeypatch, batch):
+    """The ring with prompt batches of other sizes than the default (KRONOS_CUDA_PROMPT_BATCH): batches that straddle the
+    wrap-around and the end of the sinks give the oracle's logits all the same."""
+    monkeypatch.setenv("KRONOS_CUDA_PROMPT_BATCH", str(batch))
+    cfg = dict(GQA64, kv_bits=8, kv_window=40, kv_sinks=6)
+    spec, eng, ref = make(ctx, oracle, cfg, "b5", tied=False)
+    try:
+        n = 700
+        tokens = [(i * 7 + 3) % cfg["vocab"] for i in range(n)]
+        want = np.stack([ref.forward_token(t, threads=4) for t in tokens])
+        got = eng.forward_token_ids(tokens, want_all=True)
+        bad = [t for t in range(n) if not np.array_equal(got[t], want[t])]
+        assert not bad, (bad[:5], len(bad))
+    finally:
+        eng.close(); ref.close()
+
+
 @pytest.mark.parametrize("cfg,mode,kv_bits,window,sinks,n", [(REF_SHAPE, "b4", 4, 16, 4, 640), (REF_SHAPE, "nf4g128", 8, 16, 4, 640),
                                                             (GQA64, "b5", 8, 600, 9, 1300), (GQA64, "b4", 4, 40, 0, 700)])
 def test_ring_wraparound_matches_oracle(ctx, oracle, cfg, mode, kv_bits, window, sinks, n):
@@ -39,7 +57,7 @@ def test_ring_wraparound_matches_oracle(ctx, oracle, cfg, mode, kv_bits, window,
         assert eng.kv_rows == ref.kv_rows == min(sinks, window // 2) + (window - min(sinks, window // 2)) + 512
         tokens = [(i * 13 + 5) % cfg["vocab"] for i in range(n)]
         want = np.stack([ref.forward_token(t, threads=4) for t in tokens])
-        got = eng.forward_token_ids(tokens, want_all=True)            # batch prefill (4-token weight passes)
+        got = eng.forward_token_ids(tokens, want_all=True)            # batch prefill
         bad = [t for t in range(n) if not np.array_equal(got[t], want[t])]
         assert not bad, (bad[:5], len(bad))
         assert np.array_equal(eng.read_attention(), ref.tap_attention())

@@ -131,6 +131,30 @@ def test_sparse_moe_layers_match_oracle(ctx, oracle, mode, moe, kw):
         eng.close(); ref.close()
 
 
+@pytest.mark.parametrize("batch", [16, 48, 112])
+def test_prompt_batch_size_does_not_change_results(ctx, oracle, monkeypatch, batch):
+    """The engine cuts a prompt into batches of KRONOS_CUDA_PROMPT_BATCH tokens (default 256): whatever the size - several batches
+    per prompt, a ragged last one, a batch that crosses position 512 where the attention kernels change, token tiles of every
+    width in the tensor-core launches - logits of every position and the cache rows equal the oracle's token-by-token run."""
+    monkeypatch.setenv("KRONOS_CUDA_PROMPT_BATCH", str(batch))
+    rng = np.random.Generator(np.random.PCG64(batch))
+    cases = [(km.TINY, "b5", dict(qkv_bias=True), 75), (LONG, "nf4g128", {}, LONG["max_seq"] - 1),
+             (km.MOE_TINY, "nf4g128", dict(moe=dict(layers=[0, 2], n_experts=8, top_k=2, d_ff=64, bits=3, sgc=2, shared=128)), 75)]
+    for cfg, mode, kw, n in cases:
+        spec, eng, ref = make(ctx, oracle, cfg, mode, seed=13, **kw)
+        try:
+            tokens = [int(t) for t in rng.integers(0, cfg["vocab"], n)]
+            want = np.stack([ref.forward_token(t, threads=4) for t in tokens])
+            got = eng.forward_token_ids(tokens, want_all=True)
+            bad = [t for t in range(n) if not np.array_equal(got[t], want[t])]
+            assert not bad, (cfg is LONG, mode, bad[:5], len(bad))
+            for pos in (0, n // 2, n - 1):
+                for kvh in range(cfg["n_kv"]):
+                    assert all(np.array_equal(a, b) for a, b in zip(eng.read_kv(cfg["layers"] - 1, kvh, pos), ref.read_kv(cfg["layers"] - 1, kvh, pos)))
+        finally:
+            eng.close(); ref.close()
+
+
 def test_host_embeddings_equal_device_lookup(ctx, oracle):
     spec, eng, ref = make(ctx, oracle, km.TINY, "b5", seed=4)
     try:
