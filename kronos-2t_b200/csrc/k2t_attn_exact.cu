@@ -26,6 +26,7 @@ constexpr uint32_t VAL_THREADS = 288;        // chain warps, transposing warps, 
 constexpr uint32_t VAL_TILE = 256;            // positions per ring stage of the values kernel
 constexpr uint32_t VAL_TBUF = 2;              // transposed tiles in flight between the transposing warps and the chain warps
 constexpr uint32_t EXACT_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t SCORE_TOK = 8;             // tokens of a prompt batch one scores CTA serves from one staged key tile
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -58,24 +59,43 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     __shared__ float s_red[8][SCORE_TILE / 32];
     __shared__ __align__(8) uint64_t s_bar;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t blk = blockIdx.x, kvh = blockIdx.y, tok = blockIdx.z, G = a.group, n_q = a.n_kv * G;
+    // One CTA serves up to SCORE_TOK consecutive tokens of a batch from ONE staged key tile: token t of a prompt batch sees the
+    // rows of the tokens before it (qkv_post_kernel has stored the whole batch), so the tile of the tile's last token holds
+    // the rows of all of them; each token then takes the rows below its own context.
+    const uint32_t blk = blockIdx.x, kvh = blockIdx.y, G = a.group, n_q = a.n_kv * G;
+    const uint32_t tok_lo = blockIdx.z * SCORE_TOK, tok_hi = min(a.n_tok, tok_lo + SCORE_TOK);
     pdl_wait();
     pdl_trigger();
     // sliding window: ctx = the active positions (sinks + the last window - sinks); index t -> position -> ring row
-    const uint32_t seq_len = __ldcg(a.pos) + a.pos_offset + tok + 1, ctx = a.ring.active_len(seq_len), t0 = blk * SCORE_TILE;
+    const uint32_t pos0 = __ldcg(a.pos) + a.pos_offset, t0 = blk * SCORE_TILE;
+    const uint32_t ctx_hi = a.ring.active_len(pos0 + tok_hi);          // context of the tile's last token
     const bool windowed = a.ring.window > 0;
-    if (t0 >= ctx) return;
-    const uint32_t n = min(SCORE_TILE, ctx - t0);
+    if (t0 >= ctx_hi) return;
     const size_t slot0 = ((size_t)a.layer * a.n_kv + kvh) * a.max_seq;
     const uint8_t *K = reinterpret_cast<const uint8_t *>(a.k_q8) + (slot0 + t0) * ROW;
     const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&s_bar);
     if (tid == 0 && !windowed) {
+        const uint32_t n_rows = min(SCORE_TILE, ctx_hi - t0);
         mbar_init(bar, 1);
         fence_mbar_init();
-        asm volatile("fence.proxy.async;" ::: "memory");      // the row qkv_post_kernel stored for this position is read by the copy engine
-        mbar_expect_tx(bar, n * ROW);
-        bulk_g2s((uint32_t)__cvta_generic_to_shared(s_k), K, n * ROW, bar);
+        asm volatile("fence.proxy.async;" ::: "memory");      // the rows qkv_post_kernel stored for these positions are read by the copy engine
+        mbar_expect_tx(bar, n_rows * ROW);
+        bulk_g2s((uint32_t)__cvta_generic_to_shared(s_k), K, n_rows * ROW, bar);
     }
+    __syncthreads();                               // barrier initialised
+    if (!windowed) {
+        const bool arrived = mbar_wait_bounded(bar, 0);
+        if (__syncthreads_or(!arrived)) {
+            if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
+            return;
+        }
+    }
+    const uint32_t t = t0 + tid;
+    for (uint32_t tok = tok_lo; tok < tok_hi; ++tok) {
+    const uint32_t seq_len = pos0 + tok + 1, ctx = a.ring.active_len(seq_len);
+    if (t0 >= ctx) continue;                       // the same for every thread of the CTA
+    const uint32_t n = min(SCORE_TILE, ctx - t0);
+    __syncthreads();                               // the token before is done with the staged queries and the maxima
     // the group's int8 queries (NF4 cache: gathered in the packed column order of a cached row)
     for (uint32_t i = tid; i < G * QW; i += SCORE_TILE) {
         const int8_t *qb = a.q_i8 + ((size_t)tok * n_q + kvh * G + i / QW) * HD;
@@ -89,7 +109,6 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
             s_q[i / QW][wi] = __ldcg(reinterpret_cast<const int *>(qb) + wi);
         }
     }
-    const uint32_t t = t0 + tid;
     const bool on = tid < n;
     const uint32_t row = on ? a.ring.slot_of_pos(a.ring.active_pos(t, seq_len)) : 0u;      // cache row of this lane's position
     float kst[KV4 ? NB : 1];
@@ -103,14 +122,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
     float qas[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) qas[g] = g < (int)G ? __fmul_rn(__ldcg(a.q_scale + (size_t)tok * n_q + kvh * G + g), a.attn_scale) : 0.0f;
-    __syncthreads();                               // queries staged, barrier initialised
-    if (!windowed) {
-        const bool arrived = mbar_wait_bounded(bar, 0);
-        if (__syncthreads_or(!arrived)) {
-            if (tid == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
-            return;
-        }
-    }
+    __syncthreads();                               // queries staged
     int up[8][NB], dn[8][KV4 ? NB : 1];           // integer dots per 64-value group
 #pragma unroll
     for (int g = 0; g < 8; ++g)
@@ -194,6 +206,7 @@ __global__ void __launch_bounds__(SCORE_TILE) attn_scores_kernel(const ExactAttn
         for (uint32_t w = 1; w < SCORE_TILE / 32; ++w) m = fmaxf(m, s_red[tid][w]);
         a.bmax[((size_t)tok * n_q + kvh * G + tid) * a.blk_stride + blk] = m;
     }
+    }          // tokens of the tile
     if (tid == 0 && !windowed) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
@@ -539,9 +552,11 @@ static cudaError_t launch_exact(cudaStream_t s, const ExactAttnArgs &a, bool pdl
     cudaError_t e = allow_dynamic_smem(reinterpret_cast<const void *>(attn_values_kernel<HD, KV4>), smem);
     if (e != cudaSuccess) return e;
     const uint32_t nblk = (a.ctx_cap + SCORE_TILE - 1) / SCORE_TILE;
-    e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv, n_tok), dim3(SCORE_TILE), 0, s, pdl, a);
+    ExactAttnArgs b = a;
+    b.n_tok = n_tok;
+    e = launch_kernel(attn_scores_kernel<HD, KV4>, dim3(nblk, a.n_kv, (n_tok + SCORE_TOK - 1) / SCORE_TOK), dim3(SCORE_TILE), 0, s, pdl, b);
     if (e != cudaSuccess) return e;
-    return launch_kernel(attn_values_kernel<HD, KV4>, dim3(a.n_kv * a.group, n_tok), dim3(VAL_THREADS), smem, s, pdl, a);
+    return launch_kernel(attn_values_kernel<HD, KV4>, dim3(a.n_kv * a.group, n_tok), dim3(VAL_THREADS), smem, s, pdl, b);
 }
 
 size_t attention_exact_max_ctx(uint32_t head_dim, uint32_t kv_bits) {

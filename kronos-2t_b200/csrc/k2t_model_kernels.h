@@ -89,6 +89,7 @@ struct ExactAttnArgs {           // attention in the reference's summation order
     uint32_t n_kv, group, head_dim, max_seq, layer;
     uint32_t sc_stride, blk_stride;
     uint32_t ctx_cap;            // longest context the launch is sized for (a multiple of 4, at most sc_stride)
+    uint32_t n_tok;              // tokens of the launch (set by the launcher)
     uint32_t kv_bits;
     float attn_scale;
     uint32_t *err_flag;
