@@ -209,7 +209,7 @@ def run_reference(args, rank, world):
     print(json.dumps({
         "impl": "reference", "metric": "quantized_gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8xint4..6 -> int32, fp32 epilogue", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x 4..6-bit codes -> int32, fp32 epilogue", "data": "synthetic (random codes)",
         "config": SWEEP_CONFIG,
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
