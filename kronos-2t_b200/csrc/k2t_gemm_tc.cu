@@ -17,12 +17,14 @@
 //     their row with `tcgen05.ld` one chunk ahead of the arithmetic, hand the buffer back (`drained`: the decode threads
 //     wait for it before they refill the stage, so the issuing thread never waits for the epilogue), and advance their
 //     chains: one integer multiply-add folds the bit-plane correction (2a - (2^B - 1) * xsum) and the int -> float
-//     conversion constant, then add, multiply, fma.
+//     conversion constant, then add, multiply, fma.  The row's weight scale of the chunk comes from shared memory: the
+//     decode thread of the row carries it through its ring and publishes it per chunk (a row-strided global load in the
+//     epilogue itself occupied the load / store path for 280 cycles per chunk, in front of the waits on the barriers).
 // Activation scales and corrections of the CTA's tokens sit in shared memory, chunk-major, for the whole launch.  Every
 // wait is bounded; a wait that gives up raises the context's error word and all roles leave their loops, the tensor
 // memory is freed and the kernel returns.
-// Measured (B200): 32 chunks in 16-26 us, 128 chunks in 60 us, whatever the rows up to one CTA per SM - 0.45 us per chunk
-// for 16-token tiles, 0.7 us for 64: the serial hand-offs of a chunk through the roles and the per-chunk work of a warp
+// Measured (B200): 32 chunks in 14-24 us, 128 chunks in 49 us, whatever the rows up to one CTA per SM - 0.36 us per chunk
+// for 16-token tiles, 0.65 us for 64: the serial hand-offs of a chunk through the roles and the per-chunk work of a warp
 // (13 M warp instructions per 2048 x 16384 x 64 launch, half an instruction per scheduler and cycle, tensor pipe 4%
 // active), not the tensor cores or HBM, bound it.  Against 4-token passes it wins from about 16 tokens on.
 #include <algorithm>
@@ -62,17 +64,19 @@ __host__ __device__ constexpr uint32_t tc_tmem_cols(uint32_t n) { return TC_ACC 
 
 template <int FMT> __host__ __device__ constexpr uint32_t tc_cell() { return Cell<FMT>::B0 + Cell<FMT>::B1 + Cell<FMT>::B2; }
 
-struct TcLayout { uint32_t a, b, wring, bring, xs, bias, nz, total; };
+struct TcLayout { uint32_t a, b, wring, bring, xs, bias, nz, ws, total; };
+constexpr uint32_t TC_WS_SLOTS = 16;        // chunks the per-row weight scales stay published (more than the stages in flight)
 template <int FMT, int N> __host__ __device__ inline TcLayout tc_layout(uint32_t nc) {
     TcLayout L;
     L.a = TC_HEADER;
     L.b = L.a + TC_STAGES * TC_A_STAGE;
     L.wring = L.b + TC_STAGES * N * 64;
-    L.bring = L.wring + TC_PF * TC_M * tc_cell<FMT>();
+    L.bring = L.wring + TC_PF * TC_M * (tc_cell<FMT>() + 4);      // a row's cell and the 4-byte word that holds its scale
     L.xs = L.bring + TC_PF * N * 64;
     L.bias = L.xs + nc * N * 4;
     L.nz = L.bias + (is_bitplane<FMT>() ? nc * N * 4 : 0u);       // codebook formats have no correction term
-    L.total = (L.nz + nc + 127u) & ~127u;
+    L.ws = (L.nz + nc + 15u) & ~15u;                              // bf16 scale of (chunk % TC_WS_SLOTS, row)
+    L.total = (L.ws + TC_WS_SLOTS * TC_M * 2 + 127u) & ~127u;
     return L;
 }
 
@@ -99,6 +103,22 @@ __device__ __forceinline__ uint2 lds_u32x2_tc(uint32_t saddr) {
 }
 __device__ __forceinline__ void sts_u32x4_tc(uint32_t saddr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(saddr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t lds_u32_tc(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16_tc(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ void sts_u16_tc(uint32_t saddr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int K> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(K) : "memory"); }
@@ -134,13 +154,6 @@ template <int K> __device__ __forceinline__ void tc_ld(uint32_t taddr, int (&v)[
 #pragma unroll
     for (int k = 0; k < K / 8; ++k) tc_ld8(taddr + k * 8, *reinterpret_cast<int(*)[8]>(&v[k * 8]));
 }
-__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {      // may sleep up to `ns` inside
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
-    return ok;
-}
-
 // Bounded wait on an mbarrier phase; gives up when the limit runs out or another role has given up.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_w) {
     for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
@@ -150,17 +163,6 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     *abort_w = 1;
     return false;
 }
-// The same for a role that runs ahead of the others (the decode warps): the wait sleeps in the barrier unit instead of
-// taking issue slots from the warps that are behind.
-__device__ __forceinline__ bool tc_wait_idle(uint32_t bar, uint32_t parity, volatile uint32_t *abort_w) {
-    for (uint32_t spin = 0; spin < (WAIT_LIMIT >> 4); ++spin) {
-        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
-        if ((spin & 15u) == 15u && *abort_w != 0) return false;
-    }
-    *abort_w = 1;
-    return false;
-}
-
 #ifdef K2T_TC_TRACE
 // Build-time diagnostic: cycles CTA 0 spends in the phases of its three roles (lane 0 of the first warp of each).
 __device__ unsigned long long g_tc_trace[32];
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
     if (warp < TC_EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue: thread = row, NQ chains
         const uint32_t quarter = warp & 3u, part = warp >> 2;
-        const uint32_t row = row0 + quarter * 32 + lane, row_c = min(row, a.rows_pad - 1);
+        const uint32_t row = row0 + quarter * 32 + lane;
         float *s_xs = reinterpret_cast<float *>(smem + L.xs);
         int *s_bias = reinterpret_cast<int *>(smem + L.bias);
         uint8_t *s_nz = smem + L.nz;
@@ -240,24 +242,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
         for (uint32_t t = 0; t < NQ; ++t) f[t] = 0.0f;
         const uint32_t xs_sa = sbase + L.xs + part * NQ * 4, bias_sa = sbase + L.bias + part * NQ * 4;
         const uint32_t taddr0 = tmem + ((quarter * 32u) << 16) + part * NQ;
-        // the row's scale of a chunk, requested one chunk ahead
-        const uint8_t *sc_row = nullptr;
-        uint32_t sc_g0 = 0;
-        auto scale_of = [&](uint32_t c) -> float {
-            if ((c & 31u) == 0 || sc_row == nullptr) {
-                const uint32_t p = c >> 5;
-                sc_row = reinterpret_cast<const uint8_t *>(a.scales) + tile_scale_off(a.rows_pad, p) + (size_t)row_c * tile_scale_pitch(nc, a.sgc, p);
-                sc_g0 = scale_group_of(a, p * 32);
-            }
-            return bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(sc_row) + (scale_group_of(a, c) - sc_g0)));
-        };
+        const uint32_t ws_sa = sbase + L.ws + (quarter * 32 + lane) * 2;      // the row's scale of chunk c: slot c % TC_WS_SLOTS, written by the decode thread of the row
         bool ok = true;
 #ifdef K2T_TC_TRACE
         unsigned long long trace_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long _tl = clock64();
 #endif
         // chain steps of chunk c from the dots in v (already waited for)
-        auto advance = [&](uint32_t c, const int (&v)[NQ], float ws) {
+        auto advance = [&](uint32_t c, const int (&v)[NQ]) {
+            const float ws = bf16_bits_to_f32((uint16_t)lds_u16_tc(ws_sa + (c % TC_WS_SLOTS) * (TC_M * 2)));
             const uint32_t xo = c * (N * 4);
             if (s_nz[c] != 0) {
 #pragma unroll
@@ -285,37 +278,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
         };
         // one step of the software pipeline: the dots of chunk c are on their way into `cur`; once they are in, the buffer goes
         // back to the issuing thread, the dots of chunk c + 1 are requested into `nxt`, and the chains advance meanwhile
-        auto step = [&](uint32_t c, int (&cur)[NQ], int (&nxt)[NQ], float ws, float &ws_nxt) -> bool {
+        auto step = [&](uint32_t c, int (&cur)[NQ], int (&nxt)[NQ]) -> bool {
             TC_ACC_T(0);
             tc_ld_wait(cur);
             TC_ACC_T(1);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_drained + 8 * (c % TC_ACC));
+            TC_ACC_T(4);
             if (c + 1 < nc) {
-                ws_nxt = scale_of(c + 1);
+                TC_ACC_T(5);
+                // `done` (the products) and `full` (already complete by then: it orders this thread after the decode threads' stores of the chunk's scales)
                 if (!tc_wait(bar_done + 8 * ((c + 1) % TC_ACC), ((c + 1) / TC_ACC) & 1u, s_abort)) return false;
+                if (!tc_wait(bar_full + 8 * ((c + 1) % TC_ACC), ((c + 1) / TC_ACC) & 1u, s_abort)) return false;
+                TC_ACC_T(6);
                 tc_fence_after();
                 tc_ld<NQ>(taddr0 + ((c + 1) % TC_ACC) * N, nxt);
             }
             TC_ACC_T(2);
-            advance(c, cur, ws);
+            advance(c, cur);
             TC_ACC_T(3);
             return true;
         };
         int v0[NQ], v1[NQ];
-        float ws0 = scale_of(0), ws1 = 0.0f;
-        ok = tc_wait(bar_done, 0u, s_abort);
+        ok = tc_wait(bar_done, 0u, s_abort) && tc_wait(bar_full, 0u, s_abort);
         if (ok) {
             tc_fence_after();
             tc_ld<NQ>(taddr0, v0);
             for (uint32_t c = 0; c < nc && ok; c += 2) {
-                ok = step(c, v0, v1, ws0, ws1);
-                if (ok && c + 1 < nc) ok = step(c + 1, v1, v0, ws1, ws0);
+                ok = step(c, v0, v1);
+                if (ok && c + 1 < nc) ok = step(c + 1, v1, v0);
             }
         }
 #ifdef K2T_TC_TRACE
-        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) for (int k = 0; k < 4; ++k) g_tc_trace[k] = trace_acc[k];
+        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) for (int k = 0; k < 8; ++k) g_tc_trace[k] = trace_acc[k];
 #endif
         if (!ok && lane == 0 && a.err_flag != nullptr) atomicExch(a.err_flag, 1u);
         if (ok && row < a.rows) {
@@ -339,8 +335,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
         constexpr uint32_t PIECES = (N * 4 + TC_M - 1) / TC_M;         // 16-byte activation pieces per thread and chunk
         // the row's cells of a pass are consecutive: bases per pass, recomputed when the pass changes
         uint32_t p_cur = 0xffffffffu;
-        const uint8_t *wb0 = nullptr, *wb1 = nullptr, *wb2 = nullptr;
-        auto request_w = [&](uint32_t c) {          // the row's cell of chunk c -> ring slot c % TC_PF
+        const uint8_t *wb0 = nullptr, *wb1 = nullptr, *wb2 = nullptr, *wsb = nullptr;
+        uint32_t ws_g0 = 0;
+        constexpr uint32_t SLOT = TC_M * (CELL + 4);
+        auto request_w = [&](uint32_t c) {          // the row's cell of chunk c and the word with its scale -> ring slot c % TC_PF
             const uint32_t p = c >> 5;
             if (p != p_cur) {
                 p_cur = p;
@@ -348,8 +346,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
                 wb0 = a.plane[0] + tile_code_off(a.rows_pad, B0, p) + r_n * B0;
                 if (B1) wb1 = a.plane[1] + tile_code_off(a.rows_pad, B1, p) + r_n * B1;
                 if (B2) wb2 = a.plane[2] + tile_code_off(a.rows_pad, B2, p) + r_n * B2;
+                wsb = reinterpret_cast<const uint8_t *>(a.scales) + tile_scale_off(a.rows_pad, p) + (size_t)row_c * tile_scale_pitch(nc, a.sgc, p);
+                ws_g0 = scale_group_of(a, p * 32);
             }
-            const uint32_t cc = c & 31u, slot = wring + (c % TC_PF) * (TC_M * CELL);
+            const uint32_t cc = c & 31u, slot = wring + (c % TC_PF) * SLOT;
+            cp_async4(slot + TC_M * CELL + i * 4, wsb + (((scale_group_of(a, c) - ws_g0) * 2u) & ~3u));
             cp_async16(slot + i * B0, wb0 + cc * B0, 16);
             if (B1 == 16) cp_async16(slot + TC_M * B0 + i * 16, wb1 + cc * 16, 16);
             if (B1 == 8) cp_async8(slot + TC_M * B0 + i * 8, wb1 + cc * 8);
@@ -387,10 +388,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
             TC_ACC_T(0);
             cp_async_wait<TC_PFG - 1>();
             TC_ACC_T(1);
-            // raw cell -> registers
+            // raw cell (and the word with the row's scale of this chunk) -> registers
             Raw<FMT> w;
+            uint32_t ws_word;
             {
-                const uint32_t slot = wring + (c % TC_PF) * (TC_M * CELL);
+                const uint32_t slot = wring + (c % TC_PF) * SLOT;
+                ws_word = lds_u32_tc(slot + TC_M * CELL + i * 4);
                 const uint4 p0 = lds_u32x4_tc(slot + i * B0);
                 w.w[0] = p0.x; w.w[1] = p0.y; w.w[2] = p0.z; w.w[3] = p0.w;
                 if (B1 == 16) { const uint4 p1 = lds_u32x4_tc(slot + TC_M * B0 + i * 16); w.w[4] = p1.x; w.w[5] = p1.y; w.w[6] = p1.z; w.w[7] = p1.w; }
@@ -414,8 +417,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
             decode<FMT>(w, a.cb, u);
             TC_ACC_T(2);
             if (c >= TC_STAGES) {
-                ok = tc_wait_idle(bar_done + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort) &&
-                     tc_wait_idle(bar_drained + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort);
+                ok = tc_wait(bar_done + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort) &&
+                     tc_wait(bar_drained + 8 * s, ((c / TC_STAGES) - 1u) & 1u, s_abort);
                 if (!ok) break;
             }
             TC_ACC_T(3);
@@ -430,6 +433,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const TcArgs arg
                     const uint32_t t = j >> 2, kq = j & 3u;
                     sts_u32x4_tc(b_stage + (t >> 3) * TC_SBO + kq * TC_LBO + (t & 7u) * 16, piece[k].x, piece[k].y, piece[k].z, piece[k].w);
                 }
+            }
+            {   // the row's scale of this chunk, published for the epilogue (read after the chunk's `done`, which follows this `full`)
+                const uint32_t g = scale_group_of(a, c) - scale_group_of(a, c & ~31u);
+                sts_u16_tc(sbase + L.ws + ((c % TC_WS_SLOTS) * TC_M + i) * 2, (g & 1u) ? ws_word >> 16 : ws_word & 0xFFFFu);
             }
             fence_proxy_async();
             __syncwarp();
